@@ -1,0 +1,138 @@
+/* orbit_b200: C-ABI of the B200 (sm_100a) kernels behind the `backend="cuda"` route of the SSD-MIMO layer.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (as void*), launches on that stream,
+ * allocates nothing (workspaces are the caller's; sizes come from the *_workspace_bytes queries), never aborts or
+ * traps, and returns an int status: 0 = ok, else one of ORBIT_ERR_* with the text available from
+ * orbit_last_error() (thread-local).  dtype codes: 0 = float32, 1 = bfloat16 (the "IO dtype" of activations);
+ * parameters, clocks, decays and states are always float32.
+ *
+ * Each declaration cites the interface of the reference project (d-rochau/OrbitSSM, paths inside that project)
+ * that it stands in for.
+ */
+#ifndef ORBIT_B200_H
+#define ORBIT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ORBIT_OK 0
+#define ORBIT_ERR_BAD_ARG 1
+#define ORBIT_ERR_UNSUPPORTED 2
+#define ORBIT_ERR_CUDA 3
+#define ORBIT_ERR_WORKSPACE 4
+#define ORBIT_ERR_DEVICE_TIMEOUT 5
+
+#define ORBIT_F32 0
+#define ORBIT_BF16 1
+
+#define ORBIT_PRECISION_IEEE 0 /* fp32 operands on the FP32 pipe, any geometry          */
+#define ORBIT_PRECISION_IO 1   /* bf16 operands on tcgen05 tensor cores, fp32 accumulate */
+
+/* Text of the last failure reported on the calling thread ("" if none). */
+const char* orbit_last_error(void);
+/* Library version string, and the compute capability it was built for (100 = sm_100a). */
+const char* orbit_version(void);
+int orbit_built_for_sm(void);
+
+/* ---- depthwise causal conv1d (+bias, +SiLU), token-major ------------------------------------------------------
+ * Stands in for causal_conv1d_cl_fwd / causal_conv1d_cl_bwd (src/orbit_ssm/layers/conv.py:219-277) and their
+ * Triton kernels (src/orbit_ssm/kernels/conv_triton.py:888, 924).
+ *   x       [B, L, C] with element strides (x_batch_stride, x_row_stride, 1): a column slice of a wider buffer is fine
+ *   weight  [C, W] fp32, bias [C] fp32 or NULL, W in 2..4
+ *   window  [B, C, W] fp32 or NULL: the carried state; slots 1..W-1 are the raw inputs preceding x (NULL = zeros)
+ *   y       [B, L, C] contiguous
+ * Backward recomputes the pre-activation from x; dx may again be a strided slice; dwindow [B, C, W] fp32 or NULL
+ * receives the gradient of the carried window; dweight [C, W] / dbias [C] are reduced in a fixed order
+ * (bitwise reproducible) through `workspace`. */
+int orbit_conv1d_fwd(const void* x, int64_t x_batch_stride, int64_t x_row_stride, const float* weight,
+                     const float* bias, const float* window, void* y, int B, int L, int C, int W, int dtype,
+                     int silu, void* stream);
+int64_t orbit_conv1d_bwd_workspace_bytes(int B, int L, int C, int W);
+int orbit_conv1d_bwd(const void* x, int64_t x_batch_stride, int64_t x_row_stride, const float* weight,
+                     const float* bias, const float* window, const void* dy, void* dx, int64_t dx_batch_stride,
+                     int64_t dx_row_stride, float* dwindow, float* dweight, float* dbias, void* workspace,
+                     int64_t workspace_bytes, int B, int L, int C, int W, int dtype, int silu, void* stream);
+
+/* ---- output gate + RMSNorm ------------------------------------------------------------------------------------
+ * Stands in for gated_rms_norm (src/orbit_ssm/layers/norms.py:133-168; kernels src/orbit_ssm/kernels/gated_norm.py:
+ * 30-128) and for the SwiGLU gate the layer applies after the scan (src/orbit_ssm/ssm/ssd_mimo_torch.py:619-622).
+ *   out = rms_norm(y * silu(z)) * w        z == NULL: no gate;  w == NULL: no norm (then rstd may be NULL)
+ *   y, out [M, D] contiguous; z [M, D] with row stride z_row_stride; w [D] fp32; rstd [M] fp32 (saved for backward)
+ * Backward: dy [M, D] contiguous, dz with row stride dz_row_stride, dw [D] fp32 (fixed-order reduction). */
+int orbit_gate_norm_fwd(const void* y, const void* z, int64_t z_row_stride, const float* w, void* out, float* rstd,
+                        int64_t M, int D, float eps, int dtype, void* stream);
+int64_t orbit_gate_norm_bwd_workspace_bytes(int64_t M, int D);
+int orbit_gate_norm_bwd(const void* y, const void* z, int64_t z_row_stride, const float* w, const float* rstd,
+                        const void* dout, void* dy, void* dz, int64_t dz_row_stride, float* dw, void* workspace,
+                        int64_t workspace_bytes, int64_t M, int D, int dtype, void* stream);
+
+/* ---- SSD-MIMO chunked scan ------------------------------------------------------------------------------------
+ * Stands in for ssd_mimo_scan (src/orbit_ssm/kernels/ssd_mimo/autograd.py:2247-2339) and its backward
+ * (_SSDMimoFn.backward, same file :1462); the law is the chunked dual of src/orbit_ssm/ssm/ssd_mimo_torch.py:663-708.
+ * Notation: B batch, L tokens, H heads, R/O input/output rank, G channels per head (P = G*R), N state rows,
+ * T chunk length, nc = ceil(L/T).  Per kernel head (h, r) the maps are built in the kernel from head-shared ones:
+ *   Bbar[s,q,:] = gBp[s,r,:] * Bhat[s,q,:] + beta[h,r,q,:]      Cbar[t,o,:] = gCp[t,o,:] * Chat[t,o,:] + gamma[h,r,o,:]
+ *   y[t,g,o] = sum_r chi_r(t) ( sum_{s<=t,q} W_r[t,s] (Cbar[t,o,:].Bbar[s,q,:]) u[s,g,q] + a_r(t) Cbar[t,o,:].Sin_r[:,g]
+ *                               + Dg[h,g,r,o] u[t,g,r] )
+ *   W_r[t,s] = exp(cs_t - cs_s) w_s (s < t), wd_t (s = t);  cs = prefix sum of dA inside the chunk;  a_r = exp(cs)
+ * All token-indexed tensors are token-major.  Optional pointers are NULL when the feature is off. */
+typedef struct orbit_scan_args {
+  int B, L, H, R, O, G, N;
+  int T, nc;
+  const void* u;      /* [B, L, H, G, R]  drive, IO dtype                                            */
+  const void* Bhat;   /* [B, L, R, N]     IO dtype, token stride b_ts elements                       */
+  const void* gBp;    /* [B, L, R, N]     1 + gB, IO dtype, token stride gb_ts, or NULL              */
+  const void* Chat;   /* [B, L, O, N]     IO dtype, token stride c_ts                                */
+  const void* gCp;    /* [B, L, O, N]     1 + gC, IO dtype, token stride gc_ts, or NULL              */
+  int64_t b_ts, gb_ts, c_ts, gc_ts;
+  const float* beta;  /* [H, R, R, N]  (h, r, q, n) or NULL                                          */
+  const float* gamma; /* [H, R, O, N]  or NULL                                                       */
+  const float* chi;   /* [B, L, H, R]  sibling weights or NULL (= 1)                                 */
+  const float* dA;    /* [B, L, H, R]  log decay                                                     */
+  const float* w;     /* [B, L, H, R]  write weight of earlier tokens                                */
+  const float* wd;    /* [B, L, H, R]  write weight of the own token (Euler: the same buffer as w)   */
+  const float* Dg;    /* [H, G, R, O]  skip gains or NULL                                            */
+  float* Sin;         /* [B, nc, H, R, N, G]  out: state entering each chunk (saved for backward)    */
+  float* atot;        /* [B, nc, H, R]        out: chunk decay (saved for backward)                  */
+  float* dS;          /* [B, nc, H, R, N, G]  backward scratch: gradient of the state leaving chunks */
+  void* y;            /* [B, L, H, G, O]  out, IO dtype                                              */
+  const void* dy;     /* [B, L, H, G, O]  IO dtype                                                   */
+  void* du;           /* [B, L, H, G, R]  out, IO dtype                                              */
+  float* dBhat;       /* [B, L, R, N]  out                                                           */
+  float* dgBp;        /* [B, L, R, N]  out or NULL                                                   */
+  float* dChat;       /* [B, L, O, N]  out                                                           */
+  float* dgCp;        /* [B, L, O, N]  out or NULL                                                   */
+  float* ddA;         /* [B, L, H, R]  out                                                           */
+  float* dw;          /* [B, L, H, R]  out                                                           */
+  float* dwd;         /* [B, L, H, R]  out or NULL (Euler: NULL, dw then holds both)                 */
+  float* dchi;        /* [B, L, H, R]  out or NULL                                                   */
+  float* dbeta_part;  /* [B*nc, H, R, R, N]  out: per-chunk partial sums, or NULL                    */
+  float* dgamma_part; /* [B*nc, H, R, O, N]  out or NULL                                             */
+  float* dDg_part;    /* [B*nc, H, G, R, O]  out or NULL                                             */
+} orbit_scan_args;
+
+/* Largest chunk length (a power of two, <= limit) whose working set fits one CTA for this geometry. */
+int orbit_ssd_scan_pick_chunk(int R, int O, int G, int N, int precision, int backward, int limit);
+/* Forward: S0 [B, H, R, N, G] fp32 or NULL (zero start); S_fin [B, H, R, N, G] fp32 out. */
+int orbit_ssd_scan_fwd(const orbit_scan_args* a, const float* S0, float* S_fin, int dtype, int precision,
+                       void* stream);
+/* Backward: dS_fin [B, H, R, N, G] fp32 or NULL; dS0 [B, H, R, N, G] fp32 out or NULL.  Needs a->Sin and a->atot
+ * as the forward left them. */
+int orbit_ssd_scan_bwd(const orbit_scan_args* a, const float* dS_fin, float* dS0, int dtype, int precision,
+                       void* stream);
+
+/* ---- diagnostics ---------------------------------------------------------------------------------------------
+ * One 128 x N x K tcgen05 tile through the same TMA boxes, shared-memory descriptors and TMEM read-out as the scan
+ * kernels: D[128, N] fp32 = op(A) * op(B), A and B bfloat16.  mode bit 0: A given as [K, 128] (M contiguous) instead
+ * of [128, K]; bit 1: B given as [K, N] instead of [N, K]; bit 2: A staged through registers with the manual swizzle.
+ * K, N in {64, 128}.  *status (device int) becomes nonzero if a bounded device wait gave up.  No counterpart in the
+ * reference (its kernels are Triton; there is no sm_100 path there). */
+int orbit_selftest_umma(const void* A, const void* B, float* D, int mode, int K, int N, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ORBIT_B200_H */

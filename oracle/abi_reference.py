@@ -1,0 +1,146 @@
+"""Torch restatements of the C-ABI operators (TEST INFRASTRUCTURE, not product code).
+
+Each function has the signature and return layout of its counterpart in ``orbitssm_b200/ops.py`` and computes the
+same quantity with plain torch ops (gradients through torch autograd), on any device.  Uses:
+  * ``-m gpu`` tests compare every CUDA kernel with these on the same seeded inputs;
+  * CPU tests substitute them for the kernels to check the layer's host logic (token law, state folding, layout
+    permutations, autograd wiring) against the golden vectors without a GPU.
+The scan follows the reference's chunked dual through ``ssd_oracle.scan_chunked``
+(reference: src/orbit_ssm/ssm/ssd_mimo_torch.py:663-708) after building the per-kernel-head maps
+(reference: src/orbit_ssm/ssm/ssd_mimo_torch.py:195-210).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import ssd_oracle as O
+
+
+def _f(t, dt=torch.float64):
+    return None if t is None else t.detach().to(dt)
+
+
+# ---- conv --------------------------------------------------------------------------------------------
+def _conv(x, weight, bias, window, silu):
+    Bsz, L, C = x.shape
+    W = weight.shape[-1]
+    win = window if window is not None else x.new_zeros(Bsz, C, W)
+    full = torch.cat([win.transpose(1, 2), x], dim=1)
+    acc = (bias if bias is not None else x.new_zeros(C)).expand(Bsz, L, C)
+    for j in range(W):
+        acc = acc + full[:, j + 1: j + 1 + L] * weight[:, j]
+    return F.silu(acc) if silu else acc
+
+
+def conv1d_fwd(x, weight, bias, window, silu=True, compute=torch.float64):
+    y = _conv(_f(x, compute), _f(weight, compute), _f(bias, compute), _f(window, compute), silu)
+    return y.to(x.dtype)
+
+
+def conv1d_bwd(x, weight, bias, window, dy, silu=True, want_dwindow=False, compute=torch.float64):
+    xs = _f(x, compute).requires_grad_(True)
+    ws = _f(weight, compute).requires_grad_(True)
+    bs = _f(bias, compute).requires_grad_(True) if bias is not None else None
+    wins = _f(window, compute).requires_grad_(True) if window is not None else None
+    ins = [t for t in (xs, ws, bs, wins) if t is not None]
+    with torch.enable_grad():
+        y = _conv(xs, ws, bs, wins, silu)
+        gs = torch.autograd.grad(y, ins, _f(dy, compute), allow_unused=True)
+    g = dict(zip([id(t) for t in ins], gs))
+    dwin = None
+    if want_dwindow and wins is not None:
+        dwin = g[id(wins)].to(torch.float32).clone()
+        dwin[..., 0] = 0.0                       # slot 0 of the window never enters the conv
+    return (g[id(xs)].to(x.dtype), dwin, g[id(ws)].to(torch.float32),
+            None if bs is None else g[id(bs)].to(torch.float32))
+
+
+# ---- gate + norm -------------------------------------------------------------------------------------
+def _gate_norm(y, z, w, eps):
+    g = y if z is None else y * F.silu(z)
+    if w is None:
+        return g, None
+    rstd = torch.rsqrt(g.square().mean(-1, keepdim=True) + eps)
+    return g * rstd * w, rstd.squeeze(-1)
+
+
+def gate_norm_fwd(y, z, w, eps, compute=torch.float64):
+    out, rstd = _gate_norm(_f(y, compute), _f(z, compute), _f(w, compute), eps)
+    return out.to(y.dtype), None if rstd is None else rstd.to(torch.float32)
+
+
+def gate_norm_bwd(y, z, w, rstd, dout, eps=1e-5, compute=torch.float64):
+    ys = _f(y, compute).requires_grad_(True)
+    zs = _f(z, compute).requires_grad_(True) if z is not None else None
+    ws = _f(w, compute).requires_grad_(True) if w is not None else None
+    ins = [t for t in (ys, zs, ws) if t is not None]
+    with torch.enable_grad():
+        out, _ = _gate_norm(ys, zs, ws, eps)
+        gs = dict(zip([id(t) for t in ins], torch.autograd.grad(out, ins, _f(dout, compute))))
+    return (gs[id(ys)].to(y.dtype), None if zs is None else gs[id(zs)].to(y.dtype),
+            None if ws is None else gs[id(ws)].to(torch.float32))
+
+
+# ---- scan --------------------------------------------------------------------------------------------
+def _scan(geo, T, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0):
+    Bsz, L = u.shape[:2]
+    H, R, Oo, G, N = geo.H, geo.R, geo.O, geo.G, geo.N
+    Bt = Bhat[:, :, None, None]                                         # [B,L,1,1,q,N]
+    if gBp is not None:
+        Bt = gBp[:, :, None, :, None, :] * Bt                           # [B,L,1,r,q,N]
+    if beta is not None:
+        Bt = Bt + beta
+    Ct = Chat if gCp is None else Chat * gCp
+    Ct = Ct[:, :, None, None]
+    if gamma is not None:
+        Ct = Ct + gamma
+    Bt = Bt.expand(Bsz, L, H, R, R, N)
+    Cq = Ct.expand(Bsz, L, H, R, Oo, N)
+    if chi is not None:
+        Cq = Cq * chi[..., None, None]
+    uu = u.reshape(Bsz, L, H, G, R)
+    y, S_fin = O.scan_chunked(Bt, Cq, uu, dA, w, wd, S0, T)
+    if Dg is not None:
+        uw = uu if chi is None else uu * chi[..., None, :]
+        y = y + torch.einsum("blhgr,hgro->blhgo", uw, Dg)
+    return y.reshape(Bsz, L, H * G * Oo), S_fin
+
+
+def pick_chunk(geo, precision, backward, limit):
+    return min(int(limit), 16)
+
+
+def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0, compute=torch.float64):
+    args = [_f(t, compute) for t in (u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0)]
+    y, S_fin = _scan(geo, T, *args)
+    # the third slot (the kernels' saved chunk states) carries S0 here: this restatement re-runs the forward in backward
+    return y.to(u.dtype), S_fin.to(torch.float32), (None if S0 is None else S0.detach().clone()), None
+
+
+def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, Sin, atot, dy, dS_fin, euler,
+             want_dS0, S0=None, compute=torch.float64):
+    if S0 is None and Sin is not None and Sin.dim() == 5:
+        S0 = Sin
+    names = ("u", "Bhat", "gBp", "Chat", "gCp", "beta", "gamma", "chi", "dA", "w", "wd", "Dg", "S0")
+    vals = dict(zip(names, (u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, None if euler else wd, Dg, S0)))
+    leaf = {k: (None if v is None else _f(v, compute).requires_grad_(True)) for k, v in vals.items()}
+    ins = [(k, v) for k, v in leaf.items() if v is not None]
+    with torch.enable_grad():
+        y, S_fin = _scan(geo, T, leaf["u"], leaf["Bhat"], leaf["gBp"], leaf["Chat"], leaf["gCp"], leaf["beta"],
+                         leaf["gamma"], leaf["chi"], leaf["dA"], leaf["w"], leaf["w"] if euler else leaf["wd"], leaf["Dg"],
+                         leaf["S0"])
+        loss = (y * _f(dy, compute)).sum()
+        if dS_fin is not None:
+            loss = loss + (S_fin * _f(dS_fin, compute)).sum()
+        gs = dict(zip([k for k, _ in ins], torch.autograd.grad(loss, [v for _, v in ins], allow_unused=True)))
+
+    def g(k, dt=torch.float32):
+        t = gs.get(k)
+        if t is None:
+            return None if vals[k] is None else torch.zeros_like(vals[k], dtype=dt)
+        return t.to(dt)
+
+    return dict(du=g("u", u.dtype), dBhat=g("Bhat"), dgBp=g("gBp"), dChat=g("Chat"), dgCp=g("gCp"), dbeta=g("beta"),
+                dgamma=g("gamma"), dchi=g("chi"), ddA=g("dA"), dw=g("w"), dwd=g("wd"), dDg=g("Dg"),
+                dS0=g("S0") if want_dS0 else None)

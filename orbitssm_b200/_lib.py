@@ -1,0 +1,83 @@
+"""ctypes binding of the C-ABI library ``liborbit_b200.so`` (declared in ``include/orbit_b200.h``).
+
+The library is built in-tree by ``orbitssm_b200.build`` (nvcc, sm_100a).  There is no other implementation of these
+entry points in the package: if the library is missing or a call fails, the error is raised, never papered over.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "liborbit_b200.so")
+
+F32, BF16 = 0, 1
+PRECISION_IEEE, PRECISION_IO = 0, 1
+
+_STATUS_EXC = {1: ValueError, 2: NotImplementedError, 3: RuntimeError, 4: ValueError, 5: RuntimeError}
+
+
+class OrbitLibraryError(RuntimeError):
+    pass
+
+
+class ScanArgs(C.Structure):
+    """Mirror of ``orbit_scan_args`` (include/orbit_b200.h); field order and types must match the header."""
+    _fields_ = (
+        [(n, C.c_int) for n in ("B", "L", "H", "R", "O", "G", "N", "T", "nc")]
+        + [(n, C.c_void_p) for n in ("u", "Bhat", "gBp", "Chat", "gCp")]
+        + [(n, C.c_int64) for n in ("b_ts", "gb_ts", "c_ts", "gc_ts")]
+        + [(n, C.c_void_p) for n in ("beta", "gamma", "chi", "dA", "w", "wd", "Dg", "Sin", "atot", "dS", "y", "dy", "du",
+                                     "dBhat", "dgBp", "dChat", "dgCp", "ddA", "dw", "dwd", "dchi", "dbeta_part",
+                                     "dgamma_part", "dDg_part")]
+    )
+
+
+_P, _I, _L, _F = C.c_void_p, C.c_int, C.c_int64, C.c_float
+
+# name -> (restype, argtypes); every symbol include/orbit_b200.h declares
+SIGNATURES = {
+    "orbit_last_error": (C.c_char_p, []),
+    "orbit_version": (C.c_char_p, []),
+    "orbit_built_for_sm": (_I, []),
+    "orbit_conv1d_fwd": (_I, [_P, _L, _L, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "orbit_conv1d_bwd_workspace_bytes": (_L, [_I, _I, _I, _I]),
+    "orbit_conv1d_bwd": (_I, [_P, _L, _L, _P, _P, _P, _P, _P, _L, _L, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P]),
+    "orbit_gate_norm_fwd": (_I, [_P, _P, _L, _P, _P, _P, _L, _I, _F, _I, _P]),
+    "orbit_gate_norm_bwd_workspace_bytes": (_L, [_L, _I]),
+    "orbit_gate_norm_bwd": (_I, [_P, _P, _L, _P, _P, _P, _P, _P, _L, _P, _P, _L, _L, _I, _I, _P]),
+    "orbit_ssd_scan_pick_chunk": (_I, [_I, _I, _I, _I, _I, _I, _I]),
+    "orbit_ssd_scan_fwd": (_I, [C.POINTER(ScanArgs), _P, _P, _I, _I, _P]),
+    "orbit_ssd_scan_bwd": (_I, [C.POINTER(ScanArgs), _P, _P, _I, _I, _P]),
+    "orbit_selftest_umma": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the shared library once; raises `OrbitLibraryError` (with the build command) when it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise OrbitLibraryError(
+            f"{LIB_PATH} is missing: build it with `python -m orbitssm_b200.build` (nvcc, sm_100a). "
+            "backend='cuda' has no other implementation.")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as e:
+            raise OrbitLibraryError(f"{LIB_PATH} does not export {name}; rebuild it") from e
+        fn.restype, fn.argtypes = res, args
+    _lib = lib
+    return lib
+
+
+def check(status: int, who: str):
+    """Raise the Python exception that matches a nonzero status (the message is the library's own text)."""
+    if status == 0:
+        return
+    msg = load().orbit_last_error().decode("utf-8", "replace")
+    raise _STATUS_EXC.get(status, RuntimeError)(f"{who}: {msg} (status {status})")

@@ -1,0 +1,106 @@
+// Shared device/host helpers of the orbit_b200 C-ABI library (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+namespace orbit {
+
+// Status codes returned by every extern "C" entry point (0 = ok).  The text of the last failure on the
+// calling thread is available from orbit_last_error().
+enum Status : int {
+  OK = 0,
+  ERR_BAD_ARG = 1,        // null pointer, negative size, unknown dtype code
+  ERR_UNSUPPORTED = 2,    // shape/alignment outside the kernel's envelope (named in the message)
+  ERR_CUDA = 3,           // a CUDA runtime call failed (message carries cudaGetErrorString)
+  ERR_WORKSPACE = 4,      // workspace too small
+  ERR_DEVICE_TIMEOUT = 5  // a bounded device-side wait gave up (status word set by the kernel)
+};
+
+enum DType : int { F32 = 0, BF16 = 1 };
+
+void set_error(const char* fmt, ...);
+int fail(int code, const char* fmt, ...);
+
+#define ORBIT_CHECK_CUDA(expr)                                                         \
+  do {                                                                                 \
+    cudaError_t _e = (expr);                                                           \
+    if (_e != cudaSuccess)                                                             \
+      return ::orbit::fail(::orbit::ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+  } while (0)
+
+#define ORBIT_CHECK_LAUNCH(name)                                                        \
+  do {                                                                                  \
+    cudaError_t _e = cudaGetLastError();                                                \
+    if (_e != cudaSuccess)                                                              \
+      return ::orbit::fail(::orbit::ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(_e)); \
+  } while (0)
+
+#define ORBIT_REQUIRE(cond, code, ...)                      \
+  do {                                                      \
+    if (!(cond)) return ::orbit::fail(code, __VA_ARGS__);   \
+  } while (0)
+
+// ---- element access -------------------------------------------------------------------------------
+__device__ __forceinline__ float ldf(const float* p) { return *p; }
+__device__ __forceinline__ float ldf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <typename T> struct Vec16;   // 16-byte vector of T
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  float4 v;
+  __device__ __forceinline__ void load(const float* p) { v = *reinterpret_cast<const float4*>(p); }
+  __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }
+  __device__ __forceinline__ float get(int i) const { return reinterpret_cast<const float*>(&v)[i]; }
+  __device__ __forceinline__ void set(int i, float x) { reinterpret_cast<float*>(&v)[i] = x; }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  uint4 v;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void store(__nv_bfloat16* p) const { *reinterpret_cast<uint4*>(p) = v; }
+  __device__ __forceinline__ float get(int i) const {
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(&v)[i]);
+  }
+  __device__ __forceinline__ void set(int i, float x) {
+    reinterpret_cast<__nv_bfloat16*>(&v)[i] = __float2bfloat16_rn(x);
+  }
+};
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float siluf_(float x) { return x * sigmoidf_(x); }
+// d/dx silu(x) = s (1 + x (1 - s))
+__device__ __forceinline__ float silu_gradf_(float x) {
+  float s = sigmoidf_(x);
+  return s * (1.f + x * (1.f - s));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Block-wide sum; `red` is shared scratch of >= 32 floats; every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[wid] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+  if (wid == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace orbit

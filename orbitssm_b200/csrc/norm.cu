@@ -1,0 +1,260 @@
+// Output gate + RMSNorm, forward and backward:   out = rms_norm(y * silu(z)) * w
+//
+// Replaces the reference's fused gated norm (src/orbit_ssm/kernels/gated_norm.py:30-128, router
+// src/orbit_ssm/layers/norms.py:133-168) and the gate epilogue it applies after the scan
+// (src/orbit_ssm/ssm/ssd_mimo_torch.py:619-622).  Either half is optional: z == NULL -> plain RMSNorm,
+// w == NULL -> gate only.  One CTA per row keeps the row in registers: a single pass over HBM.
+// HBM-bound: forward 3*M*D*es bytes (y, z in; out), backward 5*M*D*es (y, z, dout in; dy, dz out).
+#include "common.cuh"
+#include "../../include/orbit_b200.h"
+
+namespace orbit {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAXV = 4;   // 16-byte vectors per thread kept in registers
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(NORM_THREADS) gate_norm_fwd_kernel(const T* __restrict__ y,
+                                                                     const T* __restrict__ z, int64_t zrs,
+                                                                     const float* __restrict__ w, T* __restrict__ out,
+                                                                     float* __restrict__ rstd_out, int D, float eps) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  float g[NV][V];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    int c = (k * NORM_THREADS + threadIdx.x) * V;
+    if (c < D) {
+      Vec16<T> a;
+      a.load(y + row * D + c);
+      if (z != nullptr) {
+        Vec16<T> b;
+        b.load(z + row * zrs + c);
+#pragma unroll
+        for (int i = 0; i < V; ++i) g[k][i] = a.get(i) * siluf_(b.get(i));
+      } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) g[k][i] = a.get(i);
+      }
+#pragma unroll
+      for (int i = 0; i < V; ++i) ss = fmaf(g[k][i], g[k][i], ss);
+    }
+  }
+  float rstd = 1.f;
+  if (w != nullptr) {
+    ss = block_sum(ss, red);
+    rstd = rsqrtf(ss / (float)D + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+  }
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    int c = (k * NORM_THREADS + threadIdx.x) * V;
+    if (c < D) {
+      Vec16<T> o;
+#pragma unroll
+      for (int i = 0; i < V; ++i) o.set(i, w ? g[k][i] * rstd * w[c + i] : g[k][i]);
+      o.store(out + row * D + c);
+    }
+  }
+}
+
+// Backward: each CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; dw partial sums stay in registers and go to
+// `part` [gridDim.x, D] (fixed-order second stage below -> deterministic).
+//   xh = g*rstd, u = dout*w, m = mean(xh*u), dg = rstd*(u - xh*m), dy = dg*silu(z), dz = dg*y*silu'(z)
+template <typename T, int NV>
+__global__ void __launch_bounds__(NORM_THREADS) gate_norm_bwd_kernel(
+    const T* __restrict__ y, const T* __restrict__ z, int64_t zrs, const float* __restrict__ w,
+    const float* __restrict__ rstd_in, const T* __restrict__ dout, T* __restrict__ dy, T* __restrict__ dz,
+    int64_t dzrs, float* __restrict__ part, int64_t M, int D) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float red[32];
+  float dwacc[NV][V];
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+#pragma unroll
+    for (int i = 0; i < V; ++i) dwacc[k][i] = 0.f;
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    float yv[NV][V], sz[NV][V], gz[NV][V], u[NV][V];
+    const float rstd = w ? rstd_in[row] : 1.f;
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      int c = (k * NORM_THREADS + threadIdx.x) * V;
+      if (c < D) {
+        Vec16<T> a, d;
+        a.load(y + row * D + c);
+        d.load(dout + row * D + c);
+        if (z != nullptr) {
+          Vec16<T> b;
+          b.load(z + row * zrs + c);
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            float zz = b.get(i);
+            sz[k][i] = siluf_(zz);
+            gz[k][i] = silu_gradf_(zz);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < V; ++i) { sz[k][i] = 1.f; gz[k][i] = 0.f; }
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          yv[k][i] = a.get(i);
+          float dd = d.get(i);
+          if (w != nullptr) {
+            float xh = yv[k][i] * sz[k][i] * rstd;
+            u[k][i] = dd * w[c + i];
+            dot = fmaf(xh, u[k][i], dot);
+            dwacc[k][i] = fmaf(dd, xh, dwacc[k][i]);
+          } else {
+            u[k][i] = dd;
+          }
+        }
+      }
+    }
+    float m = 0.f;
+    if (w != nullptr) m = block_sum(dot, red) / (float)D;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      int c = (k * NORM_THREADS + threadIdx.x) * V;
+      if (c < D) {
+        Vec16<T> oy, oz;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          float dg = u[k][i];
+          if (w != nullptr) {
+            float xh = yv[k][i] * sz[k][i] * rstd;
+            dg = rstd * (u[k][i] - xh * m);
+          }
+          oy.set(i, dg * sz[k][i]);
+          oz.set(i, dg * yv[k][i] * gz[k][i]);
+        }
+        oy.store(dy + row * D + c);
+        if (z != nullptr) oz.store(dz + row * dzrs + c);
+      }
+    }
+  }
+  if (part != nullptr) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      int c = (k * NORM_THREADS + threadIdx.x) * V;
+      if (c < D) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) part[(int64_t)blockIdx.x * D + c + i] = dwacc[k][i];
+      }
+    }
+  }
+}
+
+__global__ void colsum_kernel(const float* __restrict__ part, float* __restrict__ out, int nslots, int D) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float acc = 0.f;
+  for (int s = 0; s < nslots; ++s) acc += part[(int64_t)s * D + c];
+  out[c] = acc;
+}
+
+static int norm_bwd_slots(int64_t M) {
+  int64_t g = 148 * 4;
+  return (int)(M < g ? (M > 0 ? M : 1) : g);
+}
+
+template <typename T>
+static int norm_nv(int D) {
+  constexpr int V = Vec16<T>::N;
+  int per = NORM_THREADS * V;
+  return (D + per - 1) / per;
+}
+
+}  // namespace orbit
+
+using namespace orbit;
+
+extern "C" int64_t orbit_gate_norm_bwd_workspace_bytes(int64_t M, int D) {
+  return (int64_t)norm_bwd_slots(M) * D * (int64_t)sizeof(float);
+}
+
+template <typename T>
+static int gate_norm_fwd_t(const void* y, const void* z, int64_t zrs, const float* w, void* out, float* rstd,
+                           int64_t M, int D, float eps, cudaStream_t st) {
+  constexpr int V = Vec16<T>::N;
+  ORBIT_REQUIRE(D % V == 0 && (z == nullptr || zrs % V == 0) && aligned16(y) && aligned16(out) &&
+                    (z == nullptr || aligned16(z)),
+                ERR_UNSUPPORTED, "orbit_gate_norm_fwd: D=%d and the z row stride must be multiples of %d elements and "
+                "all pointers 16-byte aligned", D, V);
+  int nv = norm_nv<T>(D);
+  ORBIT_REQUIRE(nv <= NORM_MAXV, ERR_UNSUPPORTED, "orbit_gate_norm_fwd: D=%d exceeds %d", D,
+                NORM_MAXV * NORM_THREADS * V);
+  dim3 grid((unsigned)M);
+#define L_(NV) gate_norm_fwd_kernel<T, NV><<<grid, NORM_THREADS, 0, st>>>((const T*)y, (const T*)z, zrs, w, (T*)out, rstd, D, eps)
+  if (nv <= 1) L_(1); else if (nv == 2) L_(2); else L_(4);
+#undef L_
+  ORBIT_CHECK_LAUNCH("gate_norm_fwd_kernel");
+  return OK;
+}
+
+extern "C" int orbit_gate_norm_fwd(const void* y, const void* z, int64_t z_row_stride, const float* w, void* out,
+                                   float* rstd, int64_t M, int D, float eps, int dtype, void* stream) {
+  ORBIT_REQUIRE(y && out, ERR_BAD_ARG, "orbit_gate_norm_fwd: null y/out");
+  ORBIT_REQUIRE(M >= 0 && D > 0, ERR_BAD_ARG, "orbit_gate_norm_fwd: bad sizes M=%lld D=%d", (long long)M, D);
+  ORBIT_REQUIRE(w == nullptr || rstd != nullptr, ERR_BAD_ARG, "orbit_gate_norm_fwd: rstd is required with a norm");
+  if (M == 0) return OK;
+  if (dtype == BF16) return gate_norm_fwd_t<__nv_bfloat16>(y, z, z_row_stride, w, out, rstd, M, D, eps, (cudaStream_t)stream);
+  if (dtype == F32) return gate_norm_fwd_t<float>(y, z, z_row_stride, w, out, rstd, M, D, eps, (cudaStream_t)stream);
+  return fail(ERR_BAD_ARG, "orbit_gate_norm_fwd: unknown dtype code %d", dtype);
+}
+
+template <typename T>
+static int gate_norm_bwd_t(const void* y, const void* z, int64_t zrs, const float* w, const float* rstd,
+                           const void* dout, void* dy, void* dz, int64_t dzrs, float* dw, float* part, int64_t M,
+                           int D, cudaStream_t st) {
+  constexpr int V = Vec16<T>::N;
+  ORBIT_REQUIRE(D % V == 0 && (z == nullptr || (zrs % V == 0 && dzrs % V == 0)) && aligned16(y) && aligned16(dout) &&
+                    aligned16(dy) && (z == nullptr || (aligned16(z) && aligned16(dz))),
+                ERR_UNSUPPORTED, "orbit_gate_norm_bwd: D=%d and the z/dz row strides must be multiples of %d elements "
+                "and all pointers 16-byte aligned", D, V);
+  int nv = norm_nv<T>(D);
+  ORBIT_REQUIRE(nv <= NORM_MAXV, ERR_UNSUPPORTED, "orbit_gate_norm_bwd: D=%d exceeds %d", D,
+                NORM_MAXV * NORM_THREADS * V);
+  int slots = norm_bwd_slots(M);
+  dim3 grid(slots);
+#define L_(NV) gate_norm_bwd_kernel<T, NV><<<grid, NORM_THREADS, 0, st>>>((const T*)y, (const T*)z, zrs, w, rstd, (const T*)dout, (T*)dy, (T*)dz, dzrs, part, M, D)
+  if (nv <= 1) L_(1); else if (nv == 2) L_(2); else L_(4);
+#undef L_
+  ORBIT_CHECK_LAUNCH("gate_norm_bwd_kernel");
+  if (dw != nullptr) {
+    colsum_kernel<<<(D + 255) / 256, 256, 0, st>>>(part, dw, slots, D);
+    ORBIT_CHECK_LAUNCH("colsum_kernel");
+  }
+  return OK;
+}
+
+extern "C" int orbit_gate_norm_bwd(const void* y, const void* z, int64_t z_row_stride, const float* w,
+                                   const float* rstd, const void* dout, void* dy, void* dz, int64_t dz_row_stride,
+                                   float* dw, void* workspace, int64_t workspace_bytes, int64_t M, int D, int dtype,
+                                   void* stream) {
+  ORBIT_REQUIRE(y && dout && dy, ERR_BAD_ARG, "orbit_gate_norm_bwd: null y/dout/dy");
+  ORBIT_REQUIRE(z == nullptr || dz != nullptr, ERR_BAD_ARG, "orbit_gate_norm_bwd: dz is required with a gate");
+  ORBIT_REQUIRE(w == nullptr || (rstd != nullptr && dw != nullptr), ERR_BAD_ARG,
+                "orbit_gate_norm_bwd: rstd and dw are required with a norm");
+  ORBIT_REQUIRE(M >= 0 && D > 0, ERR_BAD_ARG, "orbit_gate_norm_bwd: bad sizes M=%lld D=%d", (long long)M, D);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (M == 0) {
+    if (dw) ORBIT_CHECK_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * D, st));
+    return OK;
+  }
+  float* part = nullptr;
+  if (w != nullptr) {
+    ORBIT_REQUIRE(workspace && workspace_bytes >= orbit_gate_norm_bwd_workspace_bytes(M, D), ERR_WORKSPACE,
+                  "orbit_gate_norm_bwd: workspace of %lld bytes needed",
+                  (long long)orbit_gate_norm_bwd_workspace_bytes(M, D));
+    part = (float*)workspace;
+  }
+  if (dtype == BF16)
+    return gate_norm_bwd_t<__nv_bfloat16>(y, z, z_row_stride, w, rstd, dout, dy, dz, dz_row_stride, dw, part, M, D, st);
+  if (dtype == F32)
+    return gate_norm_bwd_t<float>(y, z, z_row_stride, w, rstd, dout, dy, dz, dz_row_stride, dw, part, M, D, st);
+  return fail(ERR_BAD_ARG, "orbit_gate_norm_bwd: unknown dtype code %d", dtype);
+}

@@ -1,0 +1,185 @@
+// Entry points of the SSD-MIMO scan: state pass kernels (shared by both precisions) and the phase drivers.
+#include "common.cuh"
+#include "scan_args.h"
+#include <stdarg.h>
+
+namespace orbit {
+
+// ---- error text (thread-local) -------------------------------------------------------------------
+static thread_local char g_err[512] = {0};
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+// ---- state pass ------------------------------------------------------------------------------------
+// Forward: buf[c] holds the chunk-local state Z[c] on entry and the state ENTERING chunk c on exit;
+//   S <- S0;  for c: z = buf[c]; buf[c] = S; S = atot[c] * S + z;   S_fin <- S
+// One thread per state element (n, g) of one (batch, head, sibling); the walk over chunks is the only serial part
+// of the scan (the reference's `_cp_pass`, src/orbit_ssm/kernels/ssd_mimo/chunkpar.py:19-25).
+__global__ void __launch_bounds__(256) state_pass_fwd_kernel(float* __restrict__ buf, const float* __restrict__ atot,
+                                                             const float* __restrict__ S0, float* __restrict__ S_fin,
+                                                             int nc, int HR, int NG) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  const int hr = blockIdx.y, b = blockIdx.z;
+  if (e >= NG) return;
+  float S = S0 ? S0[((int64_t)b * HR + hr) * NG + e] : 0.f;
+  float* p = buf + ((int64_t)b * nc * HR + hr) * NG + e;
+  const float* ap = atot + (int64_t)b * nc * HR + hr;
+  const int64_t cstride = (int64_t)HR * NG;
+  float z = p[0];
+  for (int c = 0; c < nc; ++c) {
+    float znext = (c + 1 < nc) ? p[(int64_t)(c + 1) * cstride] : 0.f;   // prefetch: breaks the load->fma chain
+    p[(int64_t)c * cstride] = S;
+    S = fmaf(ap[(int64_t)c * HR], S, z);
+    z = znext;
+  }
+  S_fin[((int64_t)b * HR + hr) * NG + e] = S;
+}
+
+// Reverse: buf[c] holds the adjoint chunk state Gs[c] on entry and the gradient of the state LEAVING chunk c on exit;
+//   D <- dS_fin;  for c = nc-1..0: g = buf[c]; buf[c] = D; D = atot[c] * D + g;   dS0 <- D
+__global__ void __launch_bounds__(256) state_pass_bwd_kernel(float* __restrict__ buf, const float* __restrict__ atot,
+                                                             const float* __restrict__ dS_fin,
+                                                             float* __restrict__ dS0, int nc, int HR, int NG) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  const int hr = blockIdx.y, b = blockIdx.z;
+  if (e >= NG) return;
+  float D = dS_fin ? dS_fin[((int64_t)b * HR + hr) * NG + e] : 0.f;
+  float* p = buf + ((int64_t)b * nc * HR + hr) * NG + e;
+  const float* ap = atot + (int64_t)b * nc * HR + hr;
+  const int64_t cstride = (int64_t)HR * NG;
+  float g = p[(int64_t)(nc - 1) * cstride];
+  for (int c = nc - 1; c >= 0; --c) {
+    float gnext = (c > 0) ? p[(int64_t)(c - 1) * cstride] : 0.f;
+    p[(int64_t)c * cstride] = D;
+    D = fmaf(ap[(int64_t)c * HR], D, g);
+    g = gnext;
+  }
+  if (dS0) dS0[((int64_t)b * HR + hr) * NG + e] = D;
+}
+
+int launch_state_pass_fwd(const ScanArgs& a, const float* S0, float* S_fin, cudaStream_t st) {
+  const int NG = a.N * a.G, HR = a.H * a.R;
+  dim3 grid((NG + 255) / 256, HR, a.B);
+  state_pass_fwd_kernel<<<grid, 256, 0, st>>>(a.Sin, a.atot, S0, S_fin, a.nc, HR, NG);
+  ORBIT_CHECK_LAUNCH("state_pass_fwd_kernel");
+  return OK;
+}
+
+int launch_state_pass_bwd(const ScanArgs& a, const float* dS_fin, float* dS0, cudaStream_t st) {
+  const int NG = a.N * a.G, HR = a.H * a.R;
+  dim3 grid((NG + 255) / 256, HR, a.B);
+  state_pass_bwd_kernel<<<grid, 256, 0, st>>>(a.dS, a.atot, dS_fin, dS0, a.nc, HR, NG);
+  ORBIT_CHECK_LAUNCH("state_pass_bwd_kernel");
+  return OK;
+}
+
+// precision "ieee" phase launchers (scan_generic.cu)
+int gen_pick_chunk(int R, int O, int G, int N, int backward, int limit);
+int gen_launch_chunk_state(const ScanArgs& a, int dtype, cudaStream_t st);
+int gen_launch_chunk_out(const ScanArgs& a, int dtype, cudaStream_t st);
+int gen_launch_chunk_dstate(const ScanArgs& a, int dtype, cudaStream_t st);
+int gen_launch_chunk_grads(const ScanArgs& a, int dtype, cudaStream_t st);
+// precision "io" phase launchers (scan_tc.cu)
+int tc_supported(const ScanArgs& a, int dtype, const char** why);
+int tc_pick_chunk(int R, int O, int G, int N, int backward, int limit);
+int tc_launch_chunk_state(const ScanArgs& a, cudaStream_t st);
+int tc_launch_chunk_out(const ScanArgs& a, cudaStream_t st);
+int tc_launch_chunk_dstate(const ScanArgs& a, cudaStream_t st);
+int tc_launch_chunk_grads(const ScanArgs& a, cudaStream_t st);
+
+static int check_common(const ScanArgs* a, int dtype, const char* who) {
+  ORBIT_REQUIRE(a != nullptr, ERR_BAD_ARG, "%s: null argument block", who);
+  ORBIT_REQUIRE(dtype == F32 || dtype == BF16, ERR_BAD_ARG, "%s: unknown dtype code %d", who, dtype);
+  ORBIT_REQUIRE(a->B >= 0 && a->L >= 0 && a->H > 0 && a->R > 0 && a->O > 0 && a->G > 0 && a->N > 0, ERR_BAD_ARG,
+                "%s: bad geometry B=%d L=%d H=%d R=%d O=%d G=%d N=%d", who, a->B, a->L, a->H, a->R, a->O, a->G, a->N);
+  ORBIT_REQUIRE(a->R <= SCAN_MAX_RANK && a->O <= SCAN_MAX_RANK, ERR_UNSUPPORTED,
+                "%s: ranks up to %d are served, got R=%d O=%d", who, SCAN_MAX_RANK, a->R, a->O);
+  ORBIT_REQUIRE(a->T > 0 && a->nc == (a->L + a->T - 1) / a->T, ERR_BAD_ARG, "%s: nc=%d does not match L=%d, T=%d", who,
+                a->nc, a->L, a->T);
+  ORBIT_REQUIRE(a->u && a->Bhat && a->Chat && a->dA && a->w && a->wd && a->Sin && a->atot, ERR_BAD_ARG,
+                "%s: null u/Bhat/Chat/dA/w/wd/Sin/atot", who);
+  return OK;
+}
+
+}  // namespace orbit
+
+using namespace orbit;
+
+extern "C" const char* orbit_last_error(void) { return g_err; }
+extern "C" const char* orbit_version(void) { return "orbit_b200 0.1 (sm_100a)"; }
+extern "C" int orbit_built_for_sm(void) { return 100; }
+
+extern "C" int orbit_ssd_scan_pick_chunk(int R, int O, int G, int N, int precision, int backward, int limit) {
+  if (precision == ORBIT_PRECISION_IO) return tc_pick_chunk(R, O, G, N, backward, limit);
+  return gen_pick_chunk(R, O, G, N, backward, limit);
+}
+
+extern "C" int orbit_ssd_scan_fwd(const orbit_scan_args* a, const float* S0, float* S_fin, int dtype, int precision,
+                                  void* stream) {
+  int rc = check_common(a, dtype, "orbit_ssd_scan_fwd");
+  if (rc != OK) return rc;
+  ORBIT_REQUIRE(a->y && S_fin, ERR_BAD_ARG, "orbit_ssd_scan_fwd: null y/S_fin");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t state_elems = (int64_t)a->B * a->H * a->R * a->N * a->G;
+  if (a->B == 0) return OK;
+  if (a->L == 0) {   // nothing to scan: the state passes through
+    if (S0) ORBIT_CHECK_CUDA(cudaMemcpyAsync(S_fin, S0, sizeof(float) * state_elems, cudaMemcpyDeviceToDevice, st));
+    else ORBIT_CHECK_CUDA(cudaMemsetAsync(S_fin, 0, sizeof(float) * state_elems, st));
+    return OK;
+  }
+  if (precision == ORBIT_PRECISION_IO) {
+    const char* why = nullptr;
+    if (!tc_supported(*a, dtype, &why)) return fail(ERR_UNSUPPORTED, "orbit_ssd_scan_fwd: precision 'io' refused: %s", why);
+    if ((rc = tc_launch_chunk_state(*a, st)) != OK) return rc;
+    if ((rc = launch_state_pass_fwd(*a, S0, S_fin, st)) != OK) return rc;
+    return tc_launch_chunk_out(*a, st);
+  }
+  ORBIT_REQUIRE(precision == ORBIT_PRECISION_IEEE, ERR_BAD_ARG, "orbit_ssd_scan_fwd: unknown precision code %d", precision);
+  if ((rc = gen_launch_chunk_state(*a, dtype, st)) != OK) return rc;
+  if ((rc = launch_state_pass_fwd(*a, S0, S_fin, st)) != OK) return rc;
+  return gen_launch_chunk_out(*a, dtype, st);
+}
+
+extern "C" int orbit_ssd_scan_bwd(const orbit_scan_args* a, const float* dS_fin, float* dS0, int dtype, int precision,
+                                  void* stream) {
+  int rc = check_common(a, dtype, "orbit_ssd_scan_bwd");
+  if (rc != OK) return rc;
+  ORBIT_REQUIRE(a->dy && a->du && a->dS && a->dBhat && a->dChat && a->ddA && a->dw, ERR_BAD_ARG,
+                "orbit_ssd_scan_bwd: null dy/du/dS/dBhat/dChat/ddA/dw");
+  ORBIT_REQUIRE((a->gBp == nullptr) == (a->dgBp == nullptr) && (a->gCp == nullptr) == (a->dgCp == nullptr) &&
+                    (a->chi == nullptr) == (a->dchi == nullptr) && (a->beta == nullptr) == (a->dbeta_part == nullptr) &&
+                    (a->gamma == nullptr) == (a->dgamma_part == nullptr) && (a->Dg == nullptr) == (a->dDg_part == nullptr),
+                ERR_BAD_ARG, "orbit_ssd_scan_bwd: each optional operand needs its gradient buffer and vice versa");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t state_elems = (int64_t)a->B * a->H * a->R * a->N * a->G;
+  if (a->B == 0) return OK;
+  if (a->L == 0) {
+    if (dS0) {
+      if (dS_fin) ORBIT_CHECK_CUDA(cudaMemcpyAsync(dS0, dS_fin, sizeof(float) * state_elems, cudaMemcpyDeviceToDevice, st));
+      else ORBIT_CHECK_CUDA(cudaMemsetAsync(dS0, 0, sizeof(float) * state_elems, st));
+    }
+    return OK;
+  }
+  if (precision == ORBIT_PRECISION_IO) {
+    const char* why = nullptr;
+    if (!tc_supported(*a, dtype, &why)) return fail(ERR_UNSUPPORTED, "orbit_ssd_scan_bwd: precision 'io' refused: %s", why);
+    if ((rc = tc_launch_chunk_dstate(*a, st)) != OK) return rc;
+    if ((rc = launch_state_pass_bwd(*a, dS_fin, dS0, st)) != OK) return rc;
+    return tc_launch_chunk_grads(*a, st);
+  }
+  ORBIT_REQUIRE(precision == ORBIT_PRECISION_IEEE, ERR_BAD_ARG, "orbit_ssd_scan_bwd: unknown precision code %d", precision);
+  if ((rc = gen_launch_chunk_dstate(*a, dtype, st)) != OK) return rc;
+  if ((rc = launch_state_pass_bwd(*a, dS_fin, dS0, st)) != OK) return rc;
+  return gen_launch_chunk_grads(*a, dtype, st);
+}

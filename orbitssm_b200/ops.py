@@ -1,0 +1,350 @@
+"""Tensor-level operators over the C-ABI kernels, with their autograd wiring.
+
+Each ``*_fwd`` / ``*_bwd`` function takes CUDA tensors, hands raw pointers to ``liborbit_b200.so`` on the current
+stream and returns tensors; the `torch.autograd.Function` classes below compose them.  They mirror the reference's
+operator seams: `causal_conv1d_cl_fwd/_bwd` (reference: src/orbit_ssm/layers/conv.py:219-277), `gated_rms_norm`
+(src/orbit_ssm/layers/norms.py:133-168) and `ssd_mimo_scan` (src/orbit_ssm/kernels/ssd_mimo/autograd.py:2247).
+A CPU tensor at any of these entries is refused by name (reference: src/orbit_ssm/kernels/input_checks.py).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+_DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def on_device(t) -> bool:
+    """Is `t` where the kernels can reach it (a CUDA tensor)?"""
+    return t.is_cuda
+
+
+def _require_cuda(who, *tensors):
+    for t in tensors:
+        if t is not None and not on_device(t):
+            raise ValueError(f"{who}: got a CPU tensor; backend='cuda' runs on a CUDA device only and has no CPU route "
+                             f"(the reference's backend='torch' is the CPU implementation)")
+
+
+def _dtype_code(who, t):
+    if t.dtype not in _DT:
+        raise NotImplementedError(f"{who}: activations must be float32 or bfloat16, got {t.dtype}")
+    return _DT[t.dtype]
+
+
+def _f32(t):
+    if t is None:
+        return None
+    return t.detach().to(torch.float32).contiguous()
+
+
+# ----------------------------------------------------------------------------------------------------
+#  conv
+# ----------------------------------------------------------------------------------------------------
+def _rows(who, x):
+    """(batch_stride, row_stride) of a [B, L, C] tensor whose channel run is contiguous."""
+    if x.dim() != 3 or (x.shape[-1] > 1 and x.stride(-1) != 1):
+        raise ValueError(f"{who}: expected [B, L, C] with a contiguous channel run, got shape {tuple(x.shape)} "
+                         f"strides {x.stride()}")
+    return x.stride(0), x.stride(1)
+
+
+def conv1d_fwd(x, weight, bias, window, silu=True):
+    """x [B, L, C] (any batch/row strides), weight [C, W] fp32, bias [C] fp32 | None, window [B, C, W] fp32 | None."""
+    _require_cuda("conv1d_fwd", x, weight, bias, window)
+    B, L, Cc = x.shape
+    W = weight.shape[-1]
+    bs, rs = _rows("conv1d_fwd", x)
+    y = torch.empty((B, L, Cc), device=x.device, dtype=x.dtype)
+    lib = _lib.load()
+    _lib.check(lib.orbit_conv1d_fwd(_ptr(x), bs, rs, _ptr(weight), _ptr(bias), _ptr(window), _ptr(y), B, L, Cc, W,
+                                    _dtype_code("conv1d_fwd", x), int(silu), _stream()), "orbit_conv1d_fwd")
+    return y
+
+
+def conv1d_bwd(x, weight, bias, window, dy, silu=True, want_dwindow=False):
+    """Returns (dx [B, L, C] contiguous, dwindow | None, dweight [C, W], dbias [C] | None)."""
+    _require_cuda("conv1d_bwd", x, weight, bias, window, dy)
+    B, L, Cc = x.shape
+    W = weight.shape[-1]
+    bs, rs = _rows("conv1d_bwd", x)
+    dy = dy.contiguous()
+    dx = torch.empty((B, L, Cc), device=x.device, dtype=x.dtype)
+    dwin = torch.empty((B, Cc, W), device=x.device, dtype=torch.float32) if want_dwindow else None
+    dweight = torch.empty((Cc, W), device=x.device, dtype=torch.float32)
+    dbias = torch.empty((Cc,), device=x.device, dtype=torch.float32) if bias is not None else None
+    lib = _lib.load()
+    nbytes = lib.orbit_conv1d_bwd_workspace_bytes(B, L, Cc, W)
+    ws = torch.empty((max(int(nbytes), 4),), device=x.device, dtype=torch.uint8)
+    _lib.check(lib.orbit_conv1d_bwd(_ptr(x), bs, rs, _ptr(weight), _ptr(bias), _ptr(window), _ptr(dy), _ptr(dx),
+                                    dx.stride(0), dx.stride(1), _ptr(dwin), _ptr(dweight), _ptr(dbias), _ptr(ws),
+                                    int(nbytes), B, L, Cc, W, _dtype_code("conv1d_bwd", x), int(silu), _stream()),
+               "orbit_conv1d_bwd")
+    return dx, dwin, dweight, dbias
+
+
+class CausalConvFn(torch.autograd.Function):
+    """y = silu(causal depthwise conv(x) + bias) on token-major x, with the carried window as a differentiable input."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, window):
+        w32, b32, win32 = _f32(weight.reshape(weight.shape[0], -1)), _f32(bias), _f32(window)
+        y = conv1d_fwd(x, w32, b32, win32)
+        ctx.save_for_backward(x, w32, b32, win32)
+        ctx.meta = (weight.shape, weight.dtype, None if bias is None else bias.dtype,
+                    None if window is None else window.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w32, b32, win32 = ctx.saved_tensors
+        wshape, wdt, bdt, windt = ctx.meta
+        want_win = win32 is not None and ctx.needs_input_grad[3]
+        dx, dwin, dw, db = conv1d_bwd(x, w32, b32, win32, dy, want_dwindow=want_win)
+        return (dx if ctx.needs_input_grad[0] else None,
+                dw.reshape(wshape).to(wdt) if ctx.needs_input_grad[1] else None,
+                db.to(bdt) if (db is not None and ctx.needs_input_grad[2]) else None,
+                dwin.to(windt) if want_win else None)
+
+
+# ----------------------------------------------------------------------------------------------------
+#  gate + RMSNorm
+# ----------------------------------------------------------------------------------------------------
+def _rows2(who, t, D):
+    if t.dim() != 2 or t.shape[1] != D or (D > 1 and t.stride(1) != 1):
+        raise ValueError(f"{who}: expected [M, {D}] with a contiguous row, got {tuple(t.shape)} strides {t.stride()}")
+    return t.stride(0)
+
+
+def gate_norm_fwd(y, z, w, eps):
+    """y [M, D] contiguous, z [M, D] (row stride free) | None, w [D] fp32 | None -> (out [M, D], rstd [M] | None)."""
+    _require_cuda("gate_norm_fwd", y, z, w)
+    M, D = y.shape
+    y = y.contiguous()
+    zs = _rows2("gate_norm_fwd", z, D) if z is not None else 0
+    out = torch.empty_like(y)
+    rstd = torch.empty((M,), device=y.device, dtype=torch.float32) if w is not None else None
+    lib = _lib.load()
+    _lib.check(lib.orbit_gate_norm_fwd(_ptr(y), _ptr(z), zs, _ptr(w), _ptr(out), _ptr(rstd), M, D, float(eps),
+                                       _dtype_code("gate_norm_fwd", y), _stream()), "orbit_gate_norm_fwd")
+    return out, rstd
+
+
+def gate_norm_bwd(y, z, w, rstd, dout):
+    """Returns (dy [M, D], dz [M, D] | None, dw [D] | None)."""
+    _require_cuda("gate_norm_bwd", y, z, w, rstd, dout)
+    M, D = y.shape
+    dout = dout.contiguous()
+    zs = _rows2("gate_norm_bwd", z, D) if z is not None else 0
+    dy = torch.empty_like(y)
+    dz = torch.empty((M, D), device=y.device, dtype=y.dtype) if z is not None else None
+    dw = torch.empty((D,), device=y.device, dtype=torch.float32) if w is not None else None
+    lib = _lib.load()
+    nbytes = lib.orbit_gate_norm_bwd_workspace_bytes(M, D)
+    ws = torch.empty((max(int(nbytes), 4),), device=y.device, dtype=torch.uint8)
+    _lib.check(lib.orbit_gate_norm_bwd(_ptr(y), _ptr(z), zs, _ptr(w), _ptr(rstd), _ptr(dout), _ptr(dy), _ptr(dz),
+                                       D, _ptr(dw), _ptr(ws), int(nbytes), M, D, _dtype_code("gate_norm_bwd", y),
+                                       _stream()), "orbit_gate_norm_bwd")
+    return dy, dz, dw
+
+
+class GateNormFn(torch.autograd.Function):
+    """out = rms_norm(y * silu(z)) * w over the last axis; z and/or w may be None."""
+
+    @staticmethod
+    def forward(ctx, y, z, w, eps):
+        shp = y.shape
+        D = shp[-1]
+        y2 = y.reshape(-1, D)
+        z2 = None
+        if z is not None:
+            z2 = z.reshape(-1, D) if z.is_contiguous() else _as_rows(z, D)
+        w32 = _f32(w)
+        out, rstd = gate_norm_fwd(y2, z2, w32, eps)
+        ctx.save_for_backward(y2, z2, w32, rstd)
+        ctx.meta = (shp, None if w is None else w.dtype)
+        return out.reshape(shp)
+
+    @staticmethod
+    def backward(ctx, dout):
+        y2, z2, w32, rstd = ctx.saved_tensors
+        shp, wdt = ctx.meta
+        dy, dz, dw = gate_norm_bwd(y2, z2, w32, rstd, dout.reshape(-1, shp[-1]))
+        return (dy.reshape(shp), None if dz is None else dz.reshape(shp), None if dw is None else dw.to(wdt), None)
+
+
+def _as_rows(t, D):
+    """View [..., D] with uniform row stride as [M, D] without copying when the leading axes collapse; else copy."""
+    try:
+        return t.view(-1, D)
+    except RuntimeError:
+        # leading axes (B, L) of a column slice collapse whenever stride(0) == L * stride(1)
+        if t.dim() == 3 and t.stride(0) == t.shape[1] * t.stride(1) and t.stride(2) == 1:
+            return t.as_strided((t.shape[0] * t.shape[1], D), (t.stride(1), 1))
+        return t.reshape(-1, D)
+
+
+# ----------------------------------------------------------------------------------------------------
+#  SSD-MIMO scan
+# ----------------------------------------------------------------------------------------------------
+@dataclass
+class ScanGeometry:
+    H: int
+    R: int
+    O: int
+    G: int
+    N: int
+
+
+def pick_chunk(geo: ScanGeometry, precision: int, backward: bool, limit: int) -> int:
+    return int(_lib.load().orbit_ssd_scan_pick_chunk(geo.R, geo.O, geo.G, geo.N, precision, int(backward), int(limit)))
+
+
+def _tok_stride(who, t, inner):
+    """Token stride (elements) of a [B, L, X, N] map whose [X, N] block is contiguous and whose batch stride is L * token stride."""
+    if t.dim() != 4 or t.stride(3) != 1 or t.stride(2) != t.shape[3] or t.stride(0) != t.shape[1] * t.stride(1):
+        raise ValueError(f"{who}: expected [B, L, {inner}, N] with contiguous [{inner}, N] blocks and collapsible (B, L), "
+                         f"got shape {tuple(t.shape)} strides {t.stride()}")
+    return t.stride(1)
+
+
+def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0):
+    """Forward scan.  Returns (y [B, L, H*G*O], S_fin [B, H, R, N, G] fp32, Sin, atot)."""
+    _require_cuda("ssd_scan_fwd", u, Bhat, Chat, dA)
+    B, L = u.shape[:2]
+    H, R, O, G, N = geo.H, geo.R, geo.O, geo.G, geo.N
+    nc = max(1, -(-L // T))
+    dev = u.device
+    a = _lib.ScanArgs()
+    a.B, a.L, a.H, a.R, a.O, a.G, a.N, a.T, a.nc = B, L, H, R, O, G, N, T, (-(-L // T))
+    u = u.contiguous()
+    y = torch.empty((B, L, H * G * O), device=dev, dtype=u.dtype)
+    Sin = torch.empty((B, nc, H, R, N, G), device=dev, dtype=torch.float32)
+    atot = torch.empty((B, nc, H, R), device=dev, dtype=torch.float32)
+    S_fin = torch.empty((B, H, R, N, G), device=dev, dtype=torch.float32)
+    keep = _fill_common(a, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg)
+    a.Sin, a.atot, a.y = Sin.data_ptr(), atot.data_ptr(), y.data_ptr()
+    lib = _lib.load()
+    _lib.check(lib.orbit_ssd_scan_fwd(C.byref(a), _ptr(S0), _ptr(S_fin), _dtype_code("ssd_scan_fwd", u), precision,
+                                      _stream()), "orbit_ssd_scan_fwd")
+    del keep
+    return y, S_fin, Sin, atot
+
+
+def _fill_common(a, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg):
+    a.u = u.data_ptr()
+    a.Bhat, a.b_ts = Bhat.data_ptr(), _tok_stride("ssd_scan", Bhat, "R")
+    a.Chat, a.c_ts = Chat.data_ptr(), _tok_stride("ssd_scan", Chat, "O")
+    if gBp is not None:
+        a.gBp, a.gb_ts = gBp.data_ptr(), _tok_stride("ssd_scan", gBp, "R")
+    if gCp is not None:
+        a.gCp, a.gc_ts = gCp.data_ptr(), _tok_stride("ssd_scan", gCp, "O")
+    for name, t in (("beta", beta), ("gamma", gamma), ("chi", chi), ("dA", dA), ("w", w), ("wd", wd), ("Dg", Dg)):
+        if t is not None:
+            if t.dtype != torch.float32 or not t.is_contiguous():
+                raise ValueError(f"ssd_scan: {name} must be contiguous float32")
+            setattr(a, name, t.data_ptr())
+    return (u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg)
+
+
+def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, Sin, atot, dy, dS_fin,
+             euler, want_dS0):
+    """Backward scan.  Returns a dict of gradients (fp32 unless noted): du (IO dtype), dBhat, dgBp, dChat, dgCp, dbeta,
+    dgamma, dchi, ddA, dw, dwd, dDg, dS0."""
+    B, L = u.shape[:2]
+    H, R, O, G, N = geo.H, geo.R, geo.O, geo.G, geo.N
+    nc = Sin.shape[1]
+    dev = u.device
+    f32 = dict(device=dev, dtype=torch.float32)
+    a = _lib.ScanArgs()
+    a.B, a.L, a.H, a.R, a.O, a.G, a.N, a.T, a.nc = B, L, H, R, O, G, N, T, (-(-L // T))
+    u = u.contiguous()
+    dy = dy.contiguous()
+    keep = _fill_common(a, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg)
+    out = dict(du=torch.empty_like(u), dBhat=torch.empty((B, L, R, N), **f32), dChat=torch.empty((B, L, O, N), **f32),
+               ddA=torch.empty((B, L, H, R), **f32), dw=torch.empty((B, L, H, R), **f32))
+    out["dgBp"] = torch.empty((B, L, R, N), **f32) if gBp is not None else None
+    out["dgCp"] = torch.empty((B, L, O, N), **f32) if gCp is not None else None
+    out["dwd"] = None if euler else torch.empty((B, L, H, R), **f32)
+    out["dchi"] = torch.empty((B, L, H, R), **f32) if chi is not None else None
+    slots = B * nc
+    pb = torch.empty((slots, H, R, R, N), **f32) if beta is not None else None
+    pg = torch.empty((slots, H, R, O, N), **f32) if gamma is not None else None
+    pd = torch.empty((slots, H, G, R, O), **f32) if Dg is not None else None
+    dS = torch.empty((B, nc, H, R, N, G), **f32)
+    dS0 = torch.empty((B, H, R, N, G), **f32) if want_dS0 else None
+    a.Sin, a.atot, a.dS, a.dy, a.du = Sin.data_ptr(), atot.data_ptr(), dS.data_ptr(), dy.data_ptr(), out["du"].data_ptr()
+    a.dBhat, a.dChat, a.ddA, a.dw = (out[k].data_ptr() for k in ("dBhat", "dChat", "ddA", "dw"))
+    for k in ("dgBp", "dgCp", "dwd", "dchi"):
+        if out[k] is not None:
+            setattr(a, k, out[k].data_ptr())
+    if pb is not None:
+        a.dbeta_part = pb.data_ptr()
+    if pg is not None:
+        a.dgamma_part = pg.data_ptr()
+    if pd is not None:
+        a.dDg_part = pd.data_ptr()
+    # Euler: one buffer serves both write weights, so the own-token gradient must land in dw as well: the kernel is
+    # given separate buffers and the two are summed here.
+    dwd_tmp = None
+    if euler:
+        dwd_tmp = torch.empty((B, L, H, R), **f32)
+        a.dwd = dwd_tmp.data_ptr()
+    lib = _lib.load()
+    _lib.check(lib.orbit_ssd_scan_bwd(C.byref(a), _ptr(dS_fin), _ptr(dS0), _dtype_code("ssd_scan_bwd", u), precision,
+                                      _stream()), "orbit_ssd_scan_bwd")
+    del keep
+    if euler:
+        out["dw"] = out["dw"] + dwd_tmp
+    out["dbeta"] = pb.sum(0) if pb is not None else None
+    out["dgamma"] = pg.sum(0) if pg is not None else None
+    out["dDg"] = pd.sum(0) if pd is not None else None
+    out["dS0"] = dS0
+    return out
+
+
+class SSDScanFn(torch.autograd.Function):
+    """The chunked SSD-MIMO scan as one autograd node (state in, state out, exact gradients through both)."""
+
+    @staticmethod
+    def forward(ctx, geo, T, precision, euler, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0):
+        tens = [None if t is None else t.detach() for t in (u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0)]
+        u_, Bhat_, gBp_, Chat_, gCp_, beta_, gamma_, chi_, dA_, w_, wd_, Dg_, S0_ = tens
+        y, S_fin, Sin, atot = scan_fwd(geo, T, precision, u_, Bhat_, gBp_, Chat_, gCp_, beta_, gamma_, chi_, dA_, w_,
+                                       w_ if euler else wd_, Dg_, S0_)
+        ctx.save_for_backward(u_, Bhat_, gBp_, Chat_, gCp_, beta_, gamma_, chi_, dA_, w_, wd_, Dg_, Sin, atot)
+        ctx.cfg = (geo, T, precision, euler)
+        ctx.in_dtypes = [None if t is None else t.dtype for t in (u, Bhat, gBp, Chat, gCp)]
+        ctx.set_materialize_grads(False)
+        return y, S_fin
+
+    @staticmethod
+    def backward(ctx, dy, dS_fin):
+        u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, Sin, atot = ctx.saved_tensors
+        geo, T, precision, euler = ctx.cfg
+        if dy is None:
+            dy = torch.zeros((*u.shape[:2], geo.H * geo.G * geo.O), device=u.device, dtype=u.dtype)
+        if dS_fin is not None:
+            dS_fin = dS_fin.to(torch.float32).contiguous()
+        g = scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, w if euler else wd, Dg, Sin,
+                     atot, dy, dS_fin, euler, ctx.needs_input_grad[16])
+        dts = ctx.in_dtypes
+
+        def cast(t, dt):
+            return None if t is None else t.to(dt)
+
+        return (None, None, None, None, g["du"], cast(g["dBhat"], dts[1]), cast(g["dgBp"], dts[2]),
+                cast(g["dChat"], dts[3]), cast(g["dgCp"], dts[4]), g["dbeta"], g["dgamma"], g["dchi"], g["ddA"], g["dw"],
+                g["dwd"], g["dDg"], g["dS0"])

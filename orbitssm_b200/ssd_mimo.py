@@ -1,0 +1,442 @@
+"""`SSDMimoSSM`: the SSD-MIMO layer behind ``backend="cuda"`` on B200.
+
+Same construction, call signature, parameter names/shapes (``state_dict`` interchanges with the reference layer) and
+recurrent-`State` contract as the reference's `SSDMimoSSM` (reference: src/orbit_ssm/ssm/ssd_mimo.py:4145-4658), with
+the hot path on hand-written sm_100a kernels reached through the C-ABI library:
+
+    x -> [one GEMM: drive | gate z | token slab] -> causal conv + SiLU (drive; B|C when ``bc_conv``)
+      -> token law (maps, clocks, decay, write weights) -> chunked SSD-MIMO scan (+ D skip)
+      -> gate y*silu(z) (+ RMSNorm when ``out_norm``) -> out_proj
+
+The two projections are library GEMMs (cuBLAS through torch); everything between them is this package's CUDA.
+There is no CPU route and no other backend here: a CPU tensor is refused by name.
+"""
+from __future__ import annotations
+
+import contextlib
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import _lib, ops
+from .config import BACKENDS, PRECISIONS, Execution, SSDMimoConfig, as_execution, resolve_ssd_spec
+from .state import State, StateLifecycle
+
+
+def _init_dt_bias(n, dt_min, dt_max, floor):
+    """softplus(bias) log-uniform in [dt_min, dt_max] (reference: src/orbit_ssm/layers/init.py:58-71)."""
+    lo, hi = math.log(dt_min), math.log(dt_max)
+    dt = torch.exp(torch.rand(n) * (hi - lo) + lo).clamp(min=floor)
+    return dt + torch.log(-torch.expm1(-dt))
+
+
+def _bc_bias_init(shape, mode, R, N):
+    """"ones", or sibling r offset along the r-th DCT-II row (reference: ssd_mimo.py:501-516)."""
+    base = torch.ones(shape)
+    if mode == "ones" or len(shape) < 4 or R < 2:
+        return base
+    r_off = torch.linspace(0.0, math.log(2.0), R)
+    k = torch.arange(R).float()[:, None]
+    n = torch.arange(N).float()[None, :]
+    dct = torch.cos(math.pi * k * (n + 0.5) / N)
+    return base + (r_off[:, None] * dct)[None, :, :, None]
+
+
+class _BCConv(nn.Module):
+    """Holder that gives the B|C conv its reference parameter names ``bc_conv1d.conv.{weight,bias}``."""
+
+    def __init__(self, channels, d_conv):
+        super().__init__()
+        self.conv = nn.Conv1d(channels, channels, kernel_size=d_conv, groups=channels, padding=d_conv - 1, bias=True)
+
+
+def _pass_min(x, lo):
+    return torch.where(x >= lo, x, x.clamp_min(lo).detach())
+
+
+def _pass_max(x, hi):
+    return torch.where(x <= hi, x, x.clamp_max(hi).detach())
+
+
+class SSDMimoSSM(StateLifecycle, nn.Module):
+    """SSD-MIMO layer; see the module docstring.  ``SSDMimoSSM(config, execution=None)``."""
+
+    config_family = "ssd_mimo"
+
+    def __init__(self, config, execution=None):
+        nn.Module.__init__(self)
+        if isinstance(config, dict):
+            config = SSDMimoConfig.from_dict(config)
+        if not isinstance(config, SSDMimoConfig):
+            raise TypeError(f"config must be an SSDMimoConfig or its dict, got {type(config).__name__}")
+        self.config = config
+        s = self.spec = resolve_ssd_spec(config)
+        H, G, R, O, N = s.H, s.G, s.R, s.O, s.N
+        self.d_model, self.d_inner, self.d_conv, self.d_out, self.d_gate = s.d_model, s.d_inner, s.d_conv, s.d_out, s.d_out
+        self.H, self.P, self.G, self.R, self.O, self.N = H, s.P, G, R, O, N
+        d_sel = s.d_model
+
+        # Parameter creation follows the reference's order (ssd_mimo.py:4278-4306, 646-856) so that the same
+        # torch seed draws the same weights.
+        self.in_proj = nn.Linear(s.d_model, 2 * s.d_inner, bias=False)
+        self.conv1d = (nn.Conv1d(s.d_inner, s.d_inner, kernel_size=s.d_conv, groups=s.d_inner, padding=s.d_conv - 1,
+                                 bias=True) if s.d_conv > 0 else None)
+        if s.skip:
+            shape = {"input_output": (H, G, R, O), "channel": (H, G, R), "head": (H,)}[s.skip_sharing]
+            self.D = nn.Parameter(torch.ones(shape))
+            self.D._no_weight_decay = True
+        if s.r_mix_mode != "none":
+            self.r_mix = nn.Parameter(torch.full((H, R), 1.0 / R))
+            if s.r_mix_dyn:
+                self.r_mix_proj = nn.Linear(d_sel, H * R, bias=False)
+                nn.init.zeros_(self.r_mix_proj.weight)
+        self.B_proj = nn.Linear(d_sel, N * R, bias=False)
+        self.C_proj = nn.Linear(d_sel, N * O, bias=False)
+        self.bc_conv1d = _BCConv(N * R + N * O, s.d_conv) if s.bc_conv else None
+        if s.use_g_b:
+            self.gB_proj = nn.Linear(d_sel, N * R, bias=False)
+            nn.init.zeros_(self.gB_proj.weight)
+        if s.use_g_c:
+            self.gC_proj = nn.Linear(d_sel, N * O, bias=False)
+            nn.init.zeros_(self.gC_proj.weight)
+        self.dt_proj = nn.Linear(d_sel, H * R, bias=True)
+        with torch.no_grad():
+            self.dt_proj.bias.copy_(_init_dt_bias(H * R, s.dt_min, s.dt_max, s.dt_init_floor))
+        self.dt_proj.bias._no_reinit = True
+        if s.a_dyn:
+            self.a_dyn_proj = nn.Linear(d_sel, H * R if s.a_dyn_per_sibling else H, bias=s.a_proj_bias)
+            if self.a_dyn_proj.bias is not None:
+                nn.init.zeros_(self.a_dyn_proj.bias)
+                self.a_dyn_proj.bias._no_weight_decay = True
+        else:
+            r_off = torch.linspace(0.0, math.log(2.0), R)
+            hbase = torch.exp(torch.linspace(math.log(0.05), math.log(2.0), H))
+            self.A_log = nn.Parameter((hbase[:, None] * torch.exp(r_off)[None, :]).log())
+            self.A_log._no_weight_decay = True
+        if s.b_norm:
+            self.B_norm = nn.RMSNorm(N, eps=s.map_eps)
+        if s.c_norm:
+            self.C_norm = nn.RMSNorm(N, eps=s.map_eps)
+        if s.bc_bias:
+            bshape = {"shared": (N,), "head": (H, R, N, R)}[s.bias_gran]
+            cshape = {"shared": (N,), "head": (H, R, N, O)}[s.bias_gran]
+            self.B_bias = nn.Parameter(_bc_bias_init(bshape, s.bc_bias_init, R, N))
+            self.C_bias = nn.Parameter(_bc_bias_init(cshape, s.bc_bias_init, R, N))
+        self.register_buffer("pair_layout_code", torch.tensor(0, dtype=torch.int64), persistent=True)
+        if s.use_trap:
+            self.trap_proj = nn.Linear(d_sel, H, bias=s.trap_proj_bias)
+            if self.trap_proj.bias is not None:
+                nn.init.zeros_(self.trap_proj.bias)
+        if self.d_gate != s.d_inner:
+            self.in_proj = nn.Linear(s.d_model, s.d_inner + self.d_gate, bias=False)
+        self.norm = _OutNorm(self.d_out, s.norm_eps) if s.out_norm else nn.Identity()
+        self.out_proj = nn.Linear(self.d_out, s.d_model, bias=False)
+
+        self.tok_width = s.tok_width
+        self._proj_keys = tuple(k for k, _, _, _ in s.slab)
+        self._proj_attrs = tuple(a for _, a, _, _ in s.slab)
+        self._proj_widths = tuple(w for _, _, w, _ in s.slab)
+        # fused projection width padded so every column slice stays 16-byte aligned in bf16 and fp32
+        self._proj_total = s.d_inner + self.d_gate + s.tok_width
+        self._proj_pad = (-self._proj_total) % 8
+
+        self.backend, self.precision, self.chunk_size, self.kernel_options = "cuda", "io", "auto", {}
+        self._route_note = None
+        self._final_state = None
+        self.set_execution(as_execution(execution))
+
+    # -- execution (reference: ssd_mimo.py:4196-4244, execution.py:111-167) --------------------------------
+    def _check_execution(self, ex: Execution) -> dict:
+        f, out = ex.fields(), {}
+        if "backend" in f:
+            if f["backend"] not in BACKENDS:
+                raise ValueError(f"SSDMimoSSM: backend must be one of {BACKENDS} (this package is the CUDA backend; the "
+                                 f"reference's 'torch' / 'sequential' routes are its own), got {f['backend']!r}")
+            out["backend"] = f["backend"]
+        if "precision" in f:
+            if f["precision"] not in PRECISIONS:
+                raise ValueError(f"SSDMimoSSM: precision must be one of {PRECISIONS}, got {f['precision']!r}")
+            out["precision"] = f["precision"]
+        if "chunk_size" in f:
+            c = f["chunk_size"]
+            if c != "auto" and (isinstance(c, bool) or not isinstance(c, int) or c < 16 or c & (c - 1)):
+                raise ValueError(f"SSDMimoSSM: chunk_size must be 'auto' or a power of two >= 16, got {c!r}")
+            out["chunk_size"] = c
+        if f.get("checkpoint"):
+            raise ValueError("SSDMimoSSM: checkpoint=True is refused (the layer has no activation checkpointing)")
+        if "kernel_options" in f:
+            if not isinstance(f["kernel_options"], dict):
+                raise TypeError("SSDMimoSSM: kernel_options must be a dict")
+            if f["kernel_options"]:
+                raise ValueError(f"SSDMimoSSM: unknown kernel option(s) {sorted(f['kernel_options'])}; this backend has none")
+            out["kernel_options"] = {}
+        return out
+
+    def set_execution(self, execution):
+        out = self._check_execution(as_execution(execution))      # validate everything before changing anything
+        for k, v in out.items():
+            setattr(self, k, v)
+        return self
+
+    @contextlib.contextmanager
+    def execution(self, execution):
+        old = Execution(backend=self.backend, precision=self.precision, chunk_size=self.chunk_size,
+                        kernel_options=dict(self.kernel_options))
+        self.set_execution(execution)
+        try:
+            yield self
+        finally:
+            self.set_execution(old)
+
+    def last_route(self):
+        """Which scan kernels the last forward used ("tcgen05" or "fp32"), and why when it was not the first."""
+        return self._route_note
+
+    # -- state ---------------------------------------------------------------------------------------------
+    def _init_state(self, batch_size, device=None, dtype=None):
+        dev = device if device is not None else next(self.parameters()).device
+        if dtype is None:
+            dtype = self._default_state_dtype()
+        st = State(hidden_state=torch.zeros(batch_size, self.H, self.P, self.N, device=dev, dtype=dtype))
+        if self.spec.use_trap:
+            st["write_prev"] = torch.zeros_like(st["hidden_state"])
+        if self.bc_conv1d is not None:
+            st["bc_conv_state"] = torch.zeros(batch_size, self.N * self.R + self.N * self.O, self.d_conv, device=dev,
+                                              dtype=dtype)
+        if self.conv1d is not None:
+            st["conv_state"] = torch.zeros(batch_size, self.d_inner, self.d_conv, device=dev, dtype=dtype)
+        return st
+
+    def hidden_state_shape(self):
+        return (self.H, self.P, self.N)
+
+    # -- fused projection weights --------------------------------------------------------------------------
+    def tok_proj_weight(self):
+        """Packed token-projection weight [tok_width, d_model] and bias (reference: ssd_mimo.py:1050-1085)."""
+        ws = [getattr(self, a).weight for a in self._proj_attrs]
+        bs = []
+        for a, wd_ in zip(self._proj_attrs, self._proj_widths):
+            b = getattr(self, a).bias
+            bs.append(b if b is not None else ws[0].new_zeros(wd_))
+        return torch.cat(ws, 0), torch.cat(bs, 0)
+
+    def _fused_weight(self, dtype):
+        wt, bt = self.tok_proj_weight()
+        parts_w = [self.in_proj.weight, wt]
+        parts_b = [bt.new_zeros(self.d_inner + self.d_gate), bt]
+        if self._proj_pad:
+            parts_w.append(wt.new_zeros(self._proj_pad, self.d_model))
+            parts_b.append(bt.new_zeros(self._proj_pad))
+        return torch.cat(parts_w, 0).to(dtype), torch.cat(parts_b, 0).to(dtype)
+
+    # -- token law (reference: ssd_mimo_torch.py:161-267, 769-788) ----------------------------------------------
+    def _token_law(self, slab, b_src, c_src, io):
+        """Per-token operands of the scan from the slab columns.  Law arithmetic in fp32; maps handed to the scan in
+        the IO dtype; clocks, decays and weights stay fp32."""
+        s = self.spec
+        Bsz, L = slab.shape[:2]
+        H, R, O, N = s.H, s.R, s.O, s.N
+        f = torch.float32
+
+        def part(key):
+            o, wd_ = s.slab_off[key]
+            return slab[..., o:o + wd_].to(f)
+
+        def base_map(src, X, norm, bias):
+            plain = not (norm is not None or bias is not None)
+            if X == 1 and plain:
+                return src.unsqueeze(2)                                       # [B, L, 1, N] view of the source columns
+            m = src.to(f).reshape(Bsz, L, N, X).transpose(-1, -2)
+            if norm is not None:
+                m = m * torch.rsqrt(m.square().mean(-1, keepdim=True) + s.map_eps) * norm.weight.to(f)
+            if bias is not None:
+                m = m + bias.to(f)
+            return m.to(io).contiguous()
+
+        shared = s.bc_bias and not s.head_bias
+        Bhat = base_map(b_src, R, self.B_norm if s.b_norm else None, self.B_bias if shared else None)
+        Chat = base_map(c_src, O, self.C_norm if s.c_norm else None, self.C_bias if shared else None)
+        gBp = (1.0 + part("gB").reshape(Bsz, L, N, R).transpose(-1, -2)).to(io).contiguous() if s.use_g_b else None
+        gCp = (1.0 + part("gC").reshape(Bsz, L, N, O).transpose(-1, -2)).to(io).contiguous() if s.use_g_c else None
+        beta = self.B_bias.to(f).transpose(-1, -2).contiguous() if s.head_bias else None       # [H, R, q, N]
+        gamma = self.C_bias.to(f).transpose(-1, -2).contiguous() if s.head_bias else None      # [H, R, o, N]
+
+        dt = F.softplus(part("dt")).reshape(Bsz, L, H, R)
+        if s.a_dyn:
+            va = part("a")
+            if s.a_act == "heavy_tail":
+                mag = _pass_min(_pass_min(va, 0.0) + torch.reciprocal(1.0 - _pass_max(va, 0.0)), 1e-4)
+            else:
+                mag = _pass_min(F.softplus(va), 1e-4)
+            rate = mag.reshape(Bsz, L, H, R) if s.a_dyn_per_sibling else mag.reshape(Bsz, L, H, 1)
+        else:
+            rate = self.A_log.to(f).exp()
+        dA = -(dt * rate)
+        lag0 = None
+        if s.use_trap:
+            lam = torch.sigmoid(part("trap"))[..., None]                      # [B, L, H, 1]
+            lag = dt * (1.0 - lam)
+            wd_ = lam * dt
+            w = wd_ + torch.cat([lag[:, 1:], lag.new_zeros(Bsz, 1, H, R)], dim=1)
+            lag0 = lag[:, 0]
+            wd_ = wd_.contiguous()
+        else:
+            w, wd_ = dt, None
+        chi = None
+        if s.r_mix_mode != "none":
+            chi = self.r_mix.to(f)
+            if s.r_mix_dyn:
+                chi = chi + part("rmix").reshape(Bsz, L, H, R)
+            chi = chi.expand(Bsz, L, H, R).contiguous()
+        Dg = None
+        if s.skip:
+            D = self.D.to(f)
+            if s.skip_sharing == "head":
+                Dg = D[:, None, None, None].expand(H, s.G, R, O)
+            elif s.skip_sharing == "channel":
+                Dg = D[..., None].expand(H, s.G, R, O)
+            else:
+                Dg = D
+            Dg = Dg.contiguous()
+        return dict(Bhat=Bhat, Chat=Chat, gBp=gBp, gCp=gCp, beta=beta, gamma=gamma, dA=dA.contiguous(),
+                    w=w.contiguous(), wd=wd_, chi=chi, Dg=Dg, lag0=lag0)
+
+    # -- forward -------------------------------------------------------------------------------------------
+    def forward(self, x, *, state=None, return_state=False):
+        """x [B, L, d_model] -> y [B, L, d_model], or (y, State) with ``return_state=True``; ``state`` continues a
+        previous call (reference: ssd_mimo.py:4367-4400)."""
+        if x.dim() != 3 or x.shape[-1] != self.d_model:
+            raise ValueError(f"SSDMimoSSM: expected x of shape [B, L, {self.d_model}], got {tuple(x.shape)}")
+        if not ops.on_device(x):
+            raise ValueError("SSDMimoSSM(backend='cuda'): got a CPU tensor; this backend runs on a CUDA device only "
+                             "(use the reference's backend='torch' on CPU)")
+        s = self.spec
+        Bsz, L, _ = x.shape
+        H, G, R, O, N, P = s.H, s.G, s.R, s.O, s.N, s.P
+        if state is not None:
+            state = self.resolve_state(state, batch_size=Bsz, device=x.device)
+            if "write_prev" in state and not s.use_trap:
+                raise ValueError("state carry 'write_prev' with write_rule='euler'")
+        io = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else x.dtype
+        if io not in (torch.float32, torch.bfloat16):
+            raise NotImplementedError(f"SSDMimoSSM(backend='cuda'): IO dtype must be float32 or bfloat16, got {io}")
+        want_state = return_state
+        with torch.autocast("cuda", enabled=False):
+            xa = x.to(io)
+            wcat, bcat = self._fused_weight(io)
+            proj = F.linear(xa, wcat, bcat)                                    # [B, L, drive | z | slab | pad]
+            drive_raw = proj[..., :s.d_inner]
+            z = proj[..., s.d_inner:s.d_inner + self.d_gate]
+            slab = proj[..., s.d_inner + self.d_gate:s.d_inner + self.d_gate + s.tok_width]
+            new = State()
+            if self.conv1d is not None:
+                win = state["conv_state"] if state is not None else None
+                u = (ops.CausalConvFn.apply(drive_raw, self.conv1d.weight, self.conv1d.bias, win) if L > 0
+                     else drive_raw.contiguous())
+                if want_state:
+                    new["conv_state"] = _next_window(win, drive_raw, s.d_conv)
+            else:
+                u = drive_raw.contiguous()
+            ob, wb = s.slab_off["B"]
+            oc, wc = s.slab_off["C"]
+            if self.bc_conv1d is not None:
+                bc_raw = slab[..., ob:oc + wc]                                 # B | C adjacent at the slab head
+                win = state["bc_conv_state"] if state is not None else None
+                bc = (ops.CausalConvFn.apply(bc_raw, self.bc_conv1d.conv.weight, self.bc_conv1d.conv.bias, win) if L > 0
+                      else bc_raw.contiguous())
+                if want_state:
+                    new["bc_conv_state"] = _next_window(win, bc_raw, s.d_conv)
+                b_src, c_src = bc[..., :wb], bc[..., wb:]
+            else:
+                b_src, c_src = slab[..., ob:ob + wb], slab[..., oc:oc + wc]
+
+            h0 = state["hidden_state"] if state is not None else None
+            wp = state.get("write_prev") if state is not None else None
+            if L == 0:
+                y = u.new_zeros(Bsz, 0, self.d_out)
+                hidden = h0.to(torch.float32) if h0 is not None else u.new_zeros(Bsz, H, P, N, dtype=torch.float32)
+                v_last = wp.to(torch.float32) if wp is not None else torch.zeros_like(hidden)
+            else:
+                law = self._token_law(slab, b_src, c_src, io)
+                S0 = None
+                if h0 is not None:
+                    S0 = h0.to(torch.float32).reshape(Bsz, H, G, R, N).permute(0, 1, 3, 4, 2)
+                    if wp is not None:
+                        S0 = S0 + wp.to(torch.float32).reshape(Bsz, H, G, R, N).permute(0, 1, 3, 4, 2) \
+                            * law["lag0"][..., None, None]
+                    S0 = S0.contiguous()
+                geo = ops.ScanGeometry(H=H, R=R, O=O, G=G, N=N)
+                precision, T = self._route(io, geo, torch.is_grad_enabled())
+                y, S_fin = ops.SSDScanFn.apply(geo, T, precision, not s.use_trap, u, law["Bhat"], law["gBp"], law["Chat"],
+                                               law["gCp"], law["beta"], law["gamma"], law["chi"], law["dA"], law["w"],
+                                               law["wd"], law["Dg"], S0)
+                hidden = S_fin.permute(0, 1, 4, 2, 3).reshape(Bsz, H, P, N)
+                v_last = None
+                if want_state and s.use_trap:
+                    v_last = self._last_write(u, law, Bsz)
+            y = ops.GateNormFn.apply(y, z, self.norm.weight if s.out_norm else None, s.norm_eps) if L > 0 else y
+            out = F.linear(y, self.out_proj.weight.to(io))
+        if not want_state:
+            return out
+        new["hidden_state"] = hidden
+        if s.use_trap:
+            new["write_prev"] = v_last
+        ordered = State({k: new[k] for k in self._state_schema() if k in new})
+        ordered = self._conform_carries(ordered, state)
+        self._final_state = ordered
+        return out, ordered
+
+    def _route(self, io, geo, needs_grad):
+        lib = _lib.load()
+        limit = 64 if self.chunk_size == "auto" else int(self.chunk_size)
+        if self.precision == "io" and io == torch.bfloat16:
+            T = ops.pick_chunk(geo, _lib.PRECISION_IO, needs_grad, 128 if self.chunk_size == "auto" else limit)
+            if T > 0:
+                self._route_note = "tcgen05"
+                return _lib.PRECISION_IO, T
+            self._route_note = "fp32 (geometry outside the tensor-core tiles)"
+        else:
+            self._route_note = "fp32"
+        T = ops.pick_chunk(geo, _lib.PRECISION_IEEE, needs_grad, limit)
+        return _lib.PRECISION_IEEE, T
+
+    def _last_write(self, u, law, Bsz):
+        """write_prev carry: vtil at the last token, [B, H, P, N] (reference: ssd_mimo_torch.py:789-792)."""
+        s = self.spec
+        f = torch.float32
+        Bl = law["Bhat"][:, -1].to(f)                                          # [B, q, N]
+        Bt = Bl[:, None, None]                                                 # [B, 1, 1, q, N]
+        if law["gBp"] is not None:
+            Bt = law["gBp"][:, -1].to(f)[:, None, :, None, :] * Bt             # [B, 1, r, q, N]
+        if law["beta"] is not None:
+            Bt = Bt + law["beta"]
+        Bt = Bt.expand(Bsz, s.H, s.R, s.R, s.N)
+        ul = u[:, -1].to(f).reshape(Bsz, s.H, s.G, s.R)
+        return torch.einsum("bhgq,bhrqn->bhgrn", ul, Bt).reshape(Bsz, s.H, s.P, s.N)
+
+    def step(self, x_t, state=None):
+        raise NotImplementedError("SSDMimoSSM(backend='cuda'): single-token decode is not part of this backend; call "
+                                  "forward on a length-1 sequence with `state` for exact continuation")
+
+
+class _OutNorm(nn.Module):
+    """Parameter holder for the output RMSNorm (``norm.weight``); the arithmetic runs in the fused gate+norm kernel."""
+
+    def __init__(self, d, eps):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(d))
+
+
+def _next_window(prev, raw, W):
+    """The carried window after this call: the last W raw inputs [B, C, W], index -1 newest, left-filled from the
+    previous window (zeros at sequence start).  Differentiable (reference: ssd_mimo.py:4585-4591)."""
+    Bsz, L, Cc = raw.shape
+    cur = raw.transpose(1, 2)
+    if L >= W:
+        return cur[..., L - W:]
+    if prev is None:
+        prev = raw.new_zeros(Bsz, Cc, W)
+    return torch.cat([prev.to(raw.dtype), cur], dim=-1)[..., -W:]

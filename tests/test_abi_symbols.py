@@ -1,0 +1,45 @@
+"""The C-ABI library loads without a GPU and exports exactly what include/orbit_b200.h declares (no compute calls)."""
+import ctypes
+import os
+import re
+
+from orbitssm_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared():
+    text = open(os.path.join(ROOT, "include", "orbit_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(orbit_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    names = declared()
+    assert len(names) >= 12
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in the header but not exported"
+    assert sorted(_lib.SIGNATURES) == names, "ctypes signatures and header declarations differ"
+
+
+def test_scan_args_mirror_matches_header_field_order():
+    text = open(os.path.join(ROOT, "include", "orbit_b200.h")).read()
+    body = re.search(r"typedef struct orbit_scan_args \{(.*?)\} orbit_scan_args;", text, flags=re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = []
+    for decl in body.split(";"):
+        decl = decl.strip()
+        if not decl:
+            continue
+        names = decl.split(",")
+        first = names[0].split()[-1]
+        fields += [first.lstrip("*")] + [n.strip().lstrip("*") for n in names[1:]]
+    assert fields == [f[0] for f in _lib.ScanArgs._fields_]
+
+
+def test_pure_queries_run_on_cpu():
+    lib = _lib.load()
+    assert lib.orbit_built_for_sm() == 100
+    assert lib.orbit_conv1d_bwd_workspace_bytes(2, 64, 8, 4) == 2 * 2 * 8 * 5 * 4
+    assert lib.orbit_ssd_scan_pick_chunk(1, 1, 64, 128, _lib.PRECISION_IEEE, 1, 64) in (16, 32, 64)

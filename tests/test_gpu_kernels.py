@@ -1,0 +1,196 @@
+"""-m gpu: every C-ABI kernel against its torch restatement (oracle/abi_reference.py, fp64) on the same seeded inputs.
+
+Tolerances (normwise relative error ||a - r|| / ||r||):
+  fp32 IO: 2e-5 forward, 2e-4 gradients (fp32 arithmetic against an fp64 restatement; sums of O(chunk * N) terms);
+  bf16 IO: 6e-3 (outputs are rounded once to bfloat16, eps = 2^-8 = 3.9e-3; inputs are identical rounded values).
+"""
+import pytest
+import torch
+
+from orbitssm_b200 import _lib, ops
+from oracle import abi_reference as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel(a, b):
+    a, b = a.detach().double().cpu(), b.detach().double().cpu()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def tol(dtype, grad=False):
+    if dtype == torch.bfloat16:
+        return 6e-3
+    return 2e-4 if grad else 2e-5
+
+
+# ---------------------------------------------------------------------------------------------------- conv
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,L,C,W,pad,use_win", [(2, 77, 64, 4, 24, True), (1, 5, 16, 3, 0, True), (3, 130, 24, 2, 8, False),
+                                                 (2, 33, 20, 4, 3, True), (1, 1, 8, 4, 0, True), (2, 256, 256, 4, 128, False)])
+def test_conv(dtype, B, L, C, W, pad, use_win):
+    g = torch.Generator().manual_seed(0)
+    wide = torch.randn(B, L, C + pad, generator=g).to(dtype).to(DEV)
+    x = wide[..., pad // 2: pad // 2 + C] if pad else wide            # column slice of a wider buffer (any row stride)
+    weight = (torch.randn(C, W, generator=g) * 0.5).to(DEV)
+    bias = torch.randn(C, generator=g).to(DEV)
+    win = torch.randn(B, C, W, generator=g).to(DEV) if use_win else None
+    dy = torch.randn(B, L, C, generator=g).to(dtype).to(DEV)
+    y = ops.conv1d_fwd(x, weight, bias, win)
+    y_ref = R.conv1d_fwd(x, weight, bias, win)
+    assert rel(y, y_ref) < tol(dtype)
+    dx, dwin, dw, db = ops.conv1d_bwd(x, weight, bias, win, dy, want_dwindow=use_win)
+    rx, rwin, rw, rb = R.conv1d_bwd(x, weight, bias, win, dy, want_dwindow=use_win)
+    assert rel(dx, rx) < tol(dtype, True)
+    assert rel(dw, rw) < tol(dtype, True) and rel(db, rb) < tol(dtype, True)
+    if use_win:
+        assert rel(dwin, rwin) < tol(dtype, True)
+    # bitwise reproducible (fixed-order reductions)
+    dx2, _, dw2, db2 = ops.conv1d_bwd(x, weight, bias, win, dy, want_dwindow=use_win)
+    assert torch.equal(dw, dw2) and torch.equal(db, db2) and torch.equal(dx, dx2)
+
+
+def test_conv_empty_and_refusals():
+    x = torch.zeros(2, 0, 16, device=DEV)
+    w = torch.zeros(16, 4, device=DEV)
+    assert ops.conv1d_fwd(x, w, None, None).shape == (2, 0, 16)
+    with pytest.raises(NotImplementedError):
+        ops.conv1d_fwd(torch.zeros(1, 4, 16, device=DEV), torch.zeros(16, 7, device=DEV), None, None)
+    with pytest.raises(ValueError, match="CPU tensor"):
+        ops.conv1d_fwd(torch.zeros(1, 4, 16), torch.zeros(16, 4), None, None)
+
+
+# ---------------------------------------------------------------------------------------------------- gate + norm
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,D,gate,norm", [(37, 256, True, True), (5, 2048, True, True), (64, 4096, True, True),
+                                           (19, 64, False, True), (19, 64, True, False), (300, 1024, True, True)])
+def test_gate_norm(dtype, M, D, gate, norm):
+    g = torch.Generator().manual_seed(1)
+    y = torch.randn(M, D, generator=g).to(dtype).to(DEV)
+    zwide = torch.randn(M, D + 64, generator=g).to(dtype).to(DEV)
+    z = zwide[:, 32:32 + D] if gate else None
+    w = (1.0 + 0.1 * torch.randn(D, generator=g)).to(DEV) if norm else None
+    dout = torch.randn(M, D, generator=g).to(dtype).to(DEV)
+    out, rstd = ops.gate_norm_fwd(y, z, w, 1e-5)
+    ro, rr = R.gate_norm_fwd(y, z, w, 1e-5)
+    assert rel(out, ro) < tol(dtype)
+    if norm:
+        assert rel(rstd, rr) < 1e-5
+    dy, dz, dw = ops.gate_norm_bwd(y, z, w, rstd, dout)
+    ry, rz, rw = R.gate_norm_bwd(y, z, w, rstd, dout)
+    assert rel(dy, ry) < tol(dtype, True)
+    if gate:
+        assert rel(dz, rz) < tol(dtype, True)
+    if norm:
+        assert rel(dw, rw) < tol(dtype, True)
+        dy2, _, dw2 = ops.gate_norm_bwd(y, z, w, rstd, dout)
+        assert torch.equal(dw, dw2) and torch.equal(dy, dy2)
+
+
+# ---------------------------------------------------------------------------------------------------- scan
+def scan_case(B, L, H, R, O, G, N, dtype, gates, biases, chi, skip, trap, s0, seed=0):
+    g = torch.Generator().manual_seed(seed)
+
+    def rn(*s, scale=1.0):
+        return torch.randn(*s, generator=g) * scale
+
+    geo = ops.ScanGeometry(H=H, R=R, O=O, G=G, N=N)
+    c = dict(geo=geo)
+    c["u"] = rn(B, L, H * G * R).to(dtype).to(DEV)
+    bc = rn(B, L, (R + O) * N + 16, scale=N ** -0.5 * 2).to(dtype).to(DEV)      # maps live as column slices of a slab
+    c["Bhat"] = bc[..., :R * N].unflatten(-1, (R, N))
+    c["Chat"] = bc[..., R * N:(R + O) * N].unflatten(-1, (O, N))
+    c["gBp"] = (1 + rn(B, L, R, N, scale=0.3)).to(dtype).to(DEV) if gates else None
+    c["gCp"] = (1 + rn(B, L, O, N, scale=0.3)).to(dtype).to(DEV) if gates else None
+    c["beta"] = rn(H, R, R, N, scale=0.2).to(DEV) if biases else None
+    c["gamma"] = rn(H, R, O, N, scale=0.2).to(DEV) if biases else None
+    c["chi"] = (0.5 + rn(B, L, H, R, scale=0.2)).to(DEV) if chi else None
+    dt = torch.nn.functional.softplus(rn(B, L, H, R) - 2.0)
+    rate = torch.exp(torch.rand(H, R, generator=g) * 2.77)                       # 1 .. 16
+    c["dA"] = (-(dt * rate)).to(DEV)
+    if trap:
+        lam = torch.sigmoid(rn(B, L, H, 1))
+        lag = dt * (1 - lam)
+        wd = lam * dt
+        c["w"] = (wd + torch.cat([lag[:, 1:], torch.zeros(B, 1, H, R)], 1)).contiguous().to(DEV)
+        c["wd"] = wd.expand(B, L, H, R).contiguous().to(DEV)
+    else:
+        c["w"] = dt.to(DEV)
+        c["wd"] = None
+    c["Dg"] = (1 + rn(H, G, R, O, scale=0.3)).to(DEV) if skip else None
+    c["S0"] = rn(B, H, R, N, G).to(DEV) if s0 else None
+    c["dy"] = rn(B, L, H * G * O).to(dtype).to(DEV)
+    c["dS_fin"] = rn(B, H, R, N, G).to(DEV)
+    c["euler"] = not trap
+    return c
+
+
+SCAN_CASES = [
+    # B, L, H, R, O, G, N, gates, biases, chi, skip, trap, s0
+    (2, 70, 3, 1, 1, 16, 16, False, False, False, True, False, False),
+    (1, 128, 2, 1, 1, 64, 128, False, False, False, True, False, True),
+    (2, 45, 2, 1, 1, 16, 16, False, True, False, True, True, True),
+    (1, 37, 2, 4, 4, 16, 128, True, True, True, True, True, True),
+    (2, 19, 3, 2, 1, 3, 8, False, False, False, True, False, True),
+    (1, 23, 2, 2, 3, 4, 8, True, True, True, False, True, False),
+    (1, 1, 1, 1, 1, 8, 8, False, False, False, False, False, True),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", SCAN_CASES)
+def test_scan_ieee(dtype, case):
+    B, L, H, Rr, O, G, N, gates, biases, chi, skip, trap, s0 = case
+    c = scan_case(B, L, H, Rr, O, G, N, dtype, gates, biases, chi, skip, trap, s0)
+    geo = c["geo"]
+    T = ops.pick_chunk(geo, _lib.PRECISION_IEEE, True, 16)
+    args = (c["u"], c["Bhat"], c["gBp"], c["Chat"], c["gCp"], c["beta"], c["gamma"], c["chi"], c["dA"], c["w"],
+            c["w"] if c["euler"] else c["wd"], c["Dg"])
+    y, S_fin, Sin, atot = ops.scan_fwd(geo, T, _lib.PRECISION_IEEE, *args, c["S0"])
+    ry, rS, _, _ = R.scan_fwd(geo, T, 0, *args, c["S0"])
+    assert rel(y, ry) < tol(dtype), "y"
+    assert rel(S_fin, rS) < 2e-5, "S_fin"
+    g = ops.scan_bwd(geo, T, _lib.PRECISION_IEEE, *args, Sin, atot, c["dy"], c["dS_fin"], c["euler"], c["S0"] is not None)
+    rg = R.scan_bwd(geo, T, 0, *args, None, None, c["dy"], c["dS_fin"], c["euler"], c["S0"] is not None, S0=c["S0"])
+    for k, v in rg.items():
+        if v is None:
+            assert g[k] is None, k
+            continue
+        t = tol(dtype, True) if k == "du" else 2e-4
+        assert rel(g[k], v) < t, (k, rel(g[k], v))
+    g2 = ops.scan_bwd(geo, T, _lib.PRECISION_IEEE, *args, Sin, atot, c["dy"], c["dS_fin"], c["euler"], c["S0"] is not None)
+    for k, v in g.items():
+        if v is not None:
+            assert torch.equal(v, g2[k]), ("not reproducible", k)
+
+
+@pytest.mark.parametrize("T", [8, 16, 32, 64])
+def test_scan_chunk_length_is_scheduling_only(T):
+    c = scan_case(2, 100, 2, 1, 1, 16, 32, torch.float32, False, False, False, True, True, True, seed=3)
+    args = (c["u"], c["Bhat"], c["gBp"], c["Chat"], c["gCp"], c["beta"], c["gamma"], c["chi"], c["dA"], c["w"], c["wd"], c["Dg"])
+    y, S, _, _ = ops.scan_fwd(c["geo"], T, _lib.PRECISION_IEEE, *args, c["S0"])
+    ry, rS, _, _ = R.scan_fwd(c["geo"], 100, 0, *args, c["S0"])
+    assert rel(y, ry) < 2e-5 and rel(S, rS) < 2e-5
+
+
+# ---------------------------------------------------------------------------------------------------- tcgen05 tile
+@pytest.mark.parametrize("mode", [0, 1, 2, 3, 4, 6])
+@pytest.mark.parametrize("K,N", [(64, 64), (128, 64), (128, 128), (64, 128)])
+def test_umma_tile(mode, K, N):
+    g = torch.Generator().manual_seed(mode * 100 + K + N)
+    A = torch.randn(128, K, generator=g).to(torch.bfloat16)
+    Bm = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    want = A.float() @ Bm.float().T
+    Ad = (A.T.contiguous() if mode & 1 else A).to(DEV)
+    Bd = (Bm.T.contiguous() if mode & 2 else Bm).to(DEV)
+    D = torch.full((128, N), float("nan"), device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    lib = _lib.load()
+    import ctypes as C
+    _lib.check(lib.orbit_selftest_umma(C.c_void_p(Ad.data_ptr()), C.c_void_p(Bd.data_ptr()), C.c_void_p(D.data_ptr()), mode, K,
+                                       N, C.c_void_p(status.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+               "orbit_selftest_umma")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded device wait gave up"
+    assert rel(D, want) < 1e-5, (mode, K, N, rel(D, want))

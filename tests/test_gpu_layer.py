@@ -1,0 +1,118 @@
+"""-m gpu: the whole `SSDMimoSSM` layer on the CUDA kernels against vectors produced by the reference
+(tests/golden/*.pt: fp64 oracle results for output, carried State and every gradient).
+
+Bounds (normwise relative error), after the reference's own CUDA-vs-oracle bounds
+(reference: tests/test_ssd_endpoint.py:252-274, 303, 326, 432-436):
+  fp32 IO, precision "ieee":  y, state 2e-4;  gradients 5e-3
+  bf16 IO (fp32 parameters, the training convention):  y, state 2.5e-2;  gradients 6e-2
+"""
+import pytest
+import torch
+
+from conftest import GOLDEN_CASES, load_golden
+from orbitssm_b200.config import SSDMimoConfig
+from orbitssm_b200.ssd_mimo import SSDMimoSSM
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BOUNDS = {torch.float32: (2e-4, 5e-3), torch.bfloat16: (2.5e-2, 6e-2)}
+
+
+def rel(a, b):
+    a, b = a.detach().double().cpu(), b.detach().double().cpu()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def build(rec, precision):
+    layer = SSDMimoSSM(SSDMimoConfig(**rec["config"]), execution={"precision": precision})
+    layer.load_state_dict(rec["state_dict"], strict=True)
+    return layer.to(DEV)
+
+
+def run(layer, rec, x, dy, state, exact, io):
+    x = x.to(DEV).to(io).requires_grad_(True)
+    if state is not None:
+        state = {k: v.to(DEV).float().requires_grad_(True) for k, v in state.items()}
+    layer.zero_grad()
+    if exact:
+        y = layer(x)
+        (y.float() ** 2).mean().backward()
+        st = None
+    else:
+        y, st = layer(x, state=state, return_state=True)
+        loss = (y.float() * dy.to(DEV)).sum() + (st["hidden_state"] * rec["gh"].to(DEV)).sum()
+        if "write_prev" in st:
+            loss = loss + (st["write_prev"] * rec["gw"].to(DEV)).sum()
+        loss.backward()
+    grads = {n: p.grad for n, p in layer.named_parameters() if p.grad is not None}
+    grads["x"] = x.grad
+    if state is not None:
+        for k, v in state.items():
+            if v.grad is not None:
+                grads["state." + k] = v.grad
+    return y.detach(), st, grads
+
+
+def check(got, want, bounds, what):
+    y, st, grads = got
+    ty, tg = bounds
+    worst = {}
+    assert rel(y, want["y"]) < ty, (what, "y", rel(y, want["y"]))
+    if want.get("state") is not None:
+        assert list(st) == list(want["state"])
+        for k, v in want["state"].items():
+            assert rel(st[k], v) < ty, (what, "state", k, rel(st[k], v))
+    for k, v in want["grads"].items():
+        assert k in grads, (what, "missing grad", k)
+        worst[k] = rel(grads[k], v)
+    bad = {k: e for k, e in worst.items() if not e < tg}
+    assert not bad, (what, "gradients out of bound", bad)
+
+
+@pytest.mark.parametrize("io", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_layer_matches_reference(name, io):
+    rec = load_golden(name)
+    layer = build(rec, "ieee" if io == torch.float32 else "io")
+    got = run(layer, rec, rec["x"], rec["dy"], None, rec["exact"], io)
+    check(got, rec["f64"], BOUNDS[io], name)
+    if "f64_cont" in rec:
+        c = rec["f64_cont"]
+        s = c["split"]
+        got = run(layer, rec, rec["x"][:, s:], rec["dy"][:, s:], c["state_in"], False, io)
+        check(got, c, BOUNDS[io], name + " continuation")
+
+
+def test_config1_known_answer():
+    rec = load_golden("cfg1_exact")
+    layer = build(rec, "ieee")
+    y = layer(rec["x"].to(DEV))
+    got = float((y.double() ** 2).mean())
+    assert abs(got - rec["mean_y2_f32"]) < 1e-4 * rec["mean_y2_f32"]
+
+
+def test_autocast_convention():
+    """fp32 input and parameters under bf16 autocast: the training convention of the reference's benchmarks."""
+    rec = load_golden("cfg2_small")
+    layer = build(rec, "io")
+    x = rec["x"].to(DEV)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = layer(x)
+    assert y.dtype == torch.bfloat16
+    assert rel(y, rec["f64"]["y"]) < 2.5e-2
+
+
+def test_split_equals_whole_and_is_reproducible():
+    rec = load_golden("dyn_trap_conv")
+    layer = build(rec, "ieee")
+    x = rec["x"].to(DEV)
+    y_all, s_all = layer(x, return_state=True)
+    y_again, _ = layer(x, return_state=True)
+    assert torch.equal(y_all, y_again)
+    st, ys = None, []
+    for a, b in ((0, 5), (5, 6), (6, 6), (6, 37)):
+        y, st = layer(x[:, a:b], state=st, return_state=True)
+        ys.append(y)
+    assert rel(torch.cat(ys, 1), y_all) < 1e-5
+    for k in s_all:
+        assert rel(st[k], s_all[k]) < 1e-5, k
