@@ -1,0 +1,314 @@
+"""Benchmark of the SSD-MIMO layer hot path: layer forward + backward tokens/s on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg3|cfg2|cfg5] [--impl reference]
+
+One "step" = y = layer(x); y.backward(dy) on one batch of synthetic input (x ~ N(0,1), fixed random dy; bf16
+activations over fp32 parameters).  Workloads (BASELINE.json `configs`):
+  cfg3  SSD-MIMO rank-4 layer, d_model 2048, x [4, 4096, 2048]   (the configuration the metric is quoted on; default)
+  cfg2  Mamba-2 preset SISO layer, d_model 1024, x [8, 2048, 1024]
+  cfg5  Mamba-2 preset SISO layer, d_model 2048, x [4, 4096, 2048] (the per-GPU layer of the multi-GPU config)
+With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same per-GPU batch on its own shard of the
+batch: no collective on the data path, weak scaling.  Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "layer fwd+bwd tokens/s (SSD-MIMO d2048 bf16)"
+WORKLOADS = {
+    "cfg3": dict(B=4, L=4096, d_model=2048, kind="mimo4", chunk_acct=32,
+                 desc="SSD-MIMO rank-4 (R=O=4, G=16, H=64, N=128) trapezoid layer, d_model 2048, x [4,4096,2048]"),
+    "cfg2": dict(B=8, L=2048, d_model=1024, kind="m2", chunk_acct=64,
+                 desc="SSD-MIMO SISO Mamba-2 preset (H=32, P=64, N=128) layer, d_model 1024, x [8,2048,1024]"),
+    "cfg5": dict(B=4, L=4096, d_model=2048, kind="m2", chunk_acct=64,
+                 desc="SSD-MIMO SISO Mamba-2 preset (H=64, P=64, N=128) layer, d_model 2048, x [4,4096,2048]"),
+}
+
+
+def make_config(wl):
+    from orbitssm_b200 import SSDMimoConfig, mamba2_config
+    if wl["kind"] == "m2":
+        return mamba2_config(wl["d_model"])
+    return SSDMimoConfig(d_model=wl["d_model"], expand=2.0, d_state=128, d_ssm_in=4, d_ssm_out=4, n_heads=64, d_head=64,
+                         d_conv=4, write_rule="trapezoid", row_blocks=[{"frac": 1.0, "decay": "head_static"}])
+
+
+def init_params(layer, seed=0):
+    """A_log <- log U(log 1, log 16) per (head, sibling) as BASELINE.json states; everything else default init."""
+    g = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        if hasattr(layer, "A_log"):
+            lo, hi = 0.0, float(torch.log(torch.tensor(16.0)))
+            layer.A_log.copy_((torch.rand(layer.A_log.shape, generator=g) * (hi - lo) + lo).log().clamp_min(-20.0)
+                              if False else torch.log(torch.exp(torch.rand(layer.A_log.shape, generator=g) * (hi - lo) + lo)))
+
+
+def scan_flops(spec, B, L, T):
+    """Algorithmic flops of the scan per forward and per phase kernel (dense contractions only):
+    per (batch, kernel head, chunk): s1 = (O T)(R T) N score, s2 = (O T)(R T) G intra output, s3 = N (R T) G chunk state,
+    s4 = (O T) N G state read; forward = 2 (s1+s2+s3+s4); backward = 2 x forward."""
+    R, O, G, N, Hk = spec.R, spec.O, spec.G, spec.N, spec.H * spec.R
+    nc = -(-L // T)
+    s1, s2, s3, s4 = (O * T) * (R * T) * N, (O * T) * (R * T) * G, N * (R * T) * G, (O * T) * N * G
+    unit = B * Hk * nc
+    return dict(fwd=2 * unit * (s1 + s2 + s3 + s4), scan_chunk_state=2 * unit * s3, scan_chunk_out=2 * unit * (s1 + s2 + s4),
+                scan_chunk_dstate=2 * unit * s4, scan_chunk_grads=2 * unit * (2 * s1 + 2 * s2 + 2 * s3 + s4))
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 9 for n, v in zip(names, r[5:9]) if v.lower().startswith("active")})
+        busy = [s for s in sm if s > 0.5 * max(sm)] if sm else []
+        return dict(sm_mhz=statistics.median(busy) if busy else None, sm_max_mhz=max(mx) if mx else None, reasons=reasons,
+                    samples=len(sm))
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], tflops=d["bf16_tflops_sustained"], source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback")
+
+
+# ----------------------------------------------------------------------------------------------------
+#  CPU arm: the reference's CPU route restated in oracle/ (the only place the bench runs it), bounded sample
+# ----------------------------------------------------------------------------------------------------
+def cpu_step_time(wl, sample_B, sample_L, steps, warmup):
+    from orbitssm_b200.config import resolve_ssd_spec
+    from orbitssm_b200 import SSDMimoSSM
+    from oracle import ssd_oracle
+    torch.manual_seed(0)
+    cfg = make_config(wl)
+    spec = resolve_ssd_spec(cfg)
+    layer = SSDMimoSSM(cfg)
+    init_params(layer)
+    prm = {k: v.detach().clone().requires_grad_(v.is_floating_point()) for k, v in layer.state_dict().items()}
+    x = torch.randn(sample_B, sample_L, wl["d_model"], requires_grad=True)
+    dy = torch.randn(sample_B, sample_L, wl["d_model"])
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        y = ssd_oracle.ssd_layer(spec, prm, x)
+        y.backward(dy)
+        dt = time.perf_counter() - t0
+        for v in prm.values():
+            v.grad = None
+        x.grad = None
+        if i >= warmup:
+            times.append(dt)
+    return statistics.median(times)
+
+
+def run_reference(args, wl, name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample_B, sample_L = 1, 256 if wl["kind"] == "m2" else 128
+    t = cpu_step_time(wl, sample_B, sample_L, max(1, min(args.steps, 5)), max(1, min(args.warmup, 1)))
+    tok = sample_B * sample_L / t
+    cores = torch.get_num_threads()
+    sample = f"x [{sample_B},{sample_L},{wl['d_model']}] fp32 of the same layer (tokens/s is linear in tokens), median step"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": tok, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": name + ": " + wl["desc"]},
+        "cpu_baseline": {"value": tok, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample,
+                         "host_cpus": os.cpu_count()},
+        "e2e": {"value": tok, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+# ----------------------------------------------------------------------------------------------------
+#  GPU arm
+# ----------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return run_reference(args, wl, args.workload)
+
+    from orbitssm_b200 import SSDMimoSSM, ops
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    args.warmup = max(args.warmup, 3)
+
+    torch.manual_seed(0)
+    cfg = make_config(wl)
+    layer = SSDMimoSSM(cfg, execution={"precision": "io"})
+    init_params(layer)
+    layer = layer.to(dev)
+    B, L, dm = wl["B"], wl["L"], wl["d_model"]
+    g = torch.Generator().manual_seed(100 + rank)                     # each rank: its own shard of the global batch
+    x_host = torch.randn(B, L, dm, generator=g).to(torch.bfloat16).pin_memory()
+    dy_host = torch.randn(B, L, dm, generator=g).to(torch.bfloat16).pin_memory()
+    y_host = torch.empty(B, L, dm, dtype=torch.bfloat16).pin_memory()
+    dx_host = torch.empty(B, L, dm, dtype=torch.bfloat16).pin_memory()
+    x = x_host.to(dev).requires_grad_(True)
+    dy = dy_host.to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # > 126 MB L2
+
+    def step():
+        x.grad = None
+        for p in layer.parameters():
+            p.grad = None
+        y = layer(x)
+        y.backward(dy)
+        return y
+
+    def step_e2e():
+        xd = x_host.to(dev, non_blocking=True).requires_grad_(True)
+        dyd = dy_host.to(dev, non_blocking=True)
+        for p in layer.parameters():
+            p.grad = None
+        y = layer(xd)
+        y.backward(dyd)
+        y_host.copy_(y, non_blocking=True)
+        dx_host.copy_(xd.grad, non_blocking=True)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    sync_all()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    timing = []
+    ops.set_timing(timing)
+    launches0 = ops.LAUNCHES
+    ev = []
+    sync_all()
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step()
+        e1.record()
+        ev.append((e0, e1))
+    sync_all()
+    launches = ops.LAUNCHES - launches0
+    ops.set_timing(None)
+    total_ms = sum(a.elapsed_time(b) for a, b in ev)
+    per_kernel = {}
+    for name, a, b in timing:
+        per_kernel.setdefault(name, []).append(a.elapsed_time(b))
+    # end to end: host buffers in, host buffers out
+    for _ in range(2):
+        step_e2e()
+    sync_all()
+    ev2 = []
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step_e2e()
+        e1.record()
+        ev2.append((e0, e1))
+    sync_all()
+    e2e_ms = sum(a.elapsed_time(b) for a, b in ev2)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([total_ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = float(t[0]), float(t[1])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    tokens = B * L * world * args.steps
+    value = tokens / (total_ms * 1e-3)
+    pk = peaks()
+    spec = layer.spec
+    fl = scan_flops(spec, B, L, wl["chunk_acct"])
+    kern_ms = {k: statistics.mean(v) for k, v in per_kernel.items()}
+    scan_names = [k for k in kern_ms if k in fl]
+    dom = max(scan_names, key=lambda k: kern_ms[k]) if scan_names else None
+    roofline = None
+    if dom:
+        ach = fl[dom] / (kern_ms[dom] * 1e-3) / 1e12
+        roofline = dict(bound="tensor", kernel=dom, achieved=ach, peak=pk["tflops"], unit="TFLOP/s", frac=ach / pk["tflops"],
+                        traffic=None, peak_source=pk["source"] + " (sustained bf16 GEMM)", ms_per_launch=kern_ms[dom],
+                        route=layer.last_route())
+    out = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload + ": " + wl["desc"], "per_gpu_batch": B, "seq_len": L,
+                   "l2": "256 MB buffer written between timed steps", "parallelism": f"batch-sharded x{world}, no collective"},
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * x_host.numel() * 2,
+                "d2h_bytes_per_step": 2 * y_host.numel() * 2},
+        "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
+        "kernel_ms": {k: round(v, 4) for k, v in sorted(kern_ms.items())},
+        "kernel_ms_sum": round(sum(kern_ms[k] * len(per_kernel[k]) for k in kern_ms) / args.steps, 4),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        sB, sL = 1, 256 if wl["kind"] == "m2" else 128
+        tcpu = cpu_step_time(wl, sB, sL, 3, 1)
+        out["cpu_baseline"] = {"value": sB * sL / tcpu, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": f"x [{sB},{sL},{dm}] fp32 of the same layer, median of 3 steps after 1 warm-up",
+                               "host_cpus": os.cpu_count()}
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -114,6 +114,26 @@ typedef struct orbit_scan_args {
   float* dDg_part;    /* [B*nc, H, G, R, O]  out or NULL                                             */
 } orbit_scan_args;
 
+/* The scan runs as three chunk-parallel phases per direction (the decomposition of the reference's chunk-parallel
+ * route, src/orbit_ssm/kernels/ssd_mimo/chunkpar.py:15-33); orbit_ssd_scan_fwd / _bwd run them in order, and
+ * orbit_ssd_scan_phase runs one (for callers that time or overlap them):
+ *   CHUNK_STATE     chunk-local states into a->Sin, chunk decays into a->atot
+ *   STATE_PASS      serial walk over chunks: a->Sin becomes the state entering each chunk; state_in = S0 or NULL,
+ *                   state_out = S_fin
+ *   CHUNK_OUT       y
+ *   CHUNK_DSTATE    adjoint chunk states into a->dS
+ *   STATE_PASS_BWD  reverse walk: a->dS becomes the gradient of the state leaving each chunk; state_in = dS_fin or
+ *                   NULL, state_out = dS0 or NULL
+ *   CHUNK_GRADS     every other gradient */
+#define ORBIT_PHASE_CHUNK_STATE 0
+#define ORBIT_PHASE_STATE_PASS 1
+#define ORBIT_PHASE_CHUNK_OUT 2
+#define ORBIT_PHASE_CHUNK_DSTATE 3
+#define ORBIT_PHASE_STATE_PASS_BWD 4
+#define ORBIT_PHASE_CHUNK_GRADS 5
+int orbit_ssd_scan_phase(const orbit_scan_args* a, int phase, const float* state_in, float* state_out, int dtype,
+                         int precision, void* stream);
+
 /* Largest chunk length (a power of two, <= limit) whose working set fits one CTA for this geometry. */
 int orbit_ssd_scan_pick_chunk(int R, int O, int G, int N, int precision, int backward, int limit);
 /* Forward: S0 [B, H, R, N, G] fp32 or NULL (zero start); S_fin [B, H, R, N, G] fp32 out. */

@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_HERE, "liborbit_b200.so")
 
 F32, BF16 = 0, 1
 PRECISION_IEEE, PRECISION_IO = 0, 1
+PHASE_CHUNK_STATE, PHASE_STATE_PASS, PHASE_CHUNK_OUT, PHASE_CHUNK_DSTATE, PHASE_STATE_PASS_BWD, PHASE_CHUNK_GRADS = range(6)
 
 _STATUS_EXC = {1: ValueError, 2: NotImplementedError, 3: RuntimeError, 4: ValueError, 5: RuntimeError}
 
@@ -47,6 +48,7 @@ SIGNATURES = {
     "orbit_gate_norm_bwd_workspace_bytes": (_L, [_L, _I]),
     "orbit_gate_norm_bwd": (_I, [_P, _P, _L, _P, _P, _P, _P, _P, _L, _P, _P, _L, _L, _I, _I, _P]),
     "orbit_ssd_scan_pick_chunk": (_I, [_I, _I, _I, _I, _I, _I, _I]),
+    "orbit_ssd_scan_phase": (_I, [C.POINTER(ScanArgs), _I, _P, _P, _I, _I, _P]),
     "orbit_ssd_scan_fwd": (_I, [C.POINTER(ScanArgs), _P, _P, _I, _I, _P]),
     "orbit_ssd_scan_bwd": (_I, [C.POINTER(ScanArgs), _P, _P, _I, _I, _P]),
     "orbit_selftest_umma": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),

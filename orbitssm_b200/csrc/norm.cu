@@ -148,6 +148,70 @@ __global__ void __launch_bounds__(NORM_THREADS) gate_norm_bwd_kernel(
   }
 }
 
+// Scalar variants for widths or strides that are not multiples of a 16-byte vector (small test geometries).
+template <typename T>
+__global__ void __launch_bounds__(NORM_THREADS) gate_norm_fwd_scalar_kernel(const T* __restrict__ y, const T* __restrict__ z,
+                                                                            int64_t zrs, const float* __restrict__ w,
+                                                                            T* __restrict__ out, float* __restrict__ rstd_out,
+                                                                            int D, float eps) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < D; c += NORM_THREADS) {
+    float g = ldf(y + row * D + c);
+    if (z) g *= siluf_(ldf(z + row * zrs + c));
+    ss = fmaf(g, g, ss);
+  }
+  float rstd = 1.f;
+  if (w != nullptr) {
+    ss = block_sum(ss, red);
+    rstd = rsqrtf(ss / (float)D + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+  }
+  for (int c = threadIdx.x; c < D; c += NORM_THREADS) {
+    float g = ldf(y + row * D + c);
+    if (z) g *= siluf_(ldf(z + row * zrs + c));
+    stf(out + row * D + c, w ? g * rstd * w[c] : g);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NORM_THREADS) gate_norm_bwd_scalar_kernel(
+    const T* __restrict__ y, const T* __restrict__ z, int64_t zrs, const float* __restrict__ w,
+    const float* __restrict__ rstd_in, const T* __restrict__ dout, T* __restrict__ dy, T* __restrict__ dz, int64_t dzrs,
+    float* __restrict__ part, int64_t M, int D) {
+  __shared__ float red[32];
+  bool first = true;
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const float rstd = w ? rstd_in[row] : 1.f;
+    float dot = 0.f;
+    if (w != nullptr) {
+      for (int c = threadIdx.x; c < D; c += NORM_THREADS) {
+        float sz = z ? siluf_(ldf(z + row * zrs + c)) : 1.f;
+        float xh = ldf(y + row * D + c) * sz * rstd;
+        float dd = ldf(dout + row * D + c);
+        dot = fmaf(xh, dd * w[c], dot);
+        float* p = part + (int64_t)blockIdx.x * D + c;
+        *p = (first ? 0.f : *p) + dd * xh;
+      }
+    }
+    float m = w ? block_sum(dot, red) / (float)D : 0.f;
+    for (int c = threadIdx.x; c < D; c += NORM_THREADS) {
+      float zz = z ? ldf(z + row * zrs + c) : 0.f;
+      float sz = z ? siluf_(zz) : 1.f;
+      float yv = ldf(y + row * D + c);
+      float dg = ldf(dout + row * D + c);
+      if (w != nullptr) {
+        float xh = yv * sz * rstd;
+        dg = rstd * (dg * w[c] - xh * m);
+      }
+      stf(dy + row * D + c, dg * sz);
+      if (z) stf(dz + row * dzrs + c, dg * yv * silu_gradf_(zz));
+    }
+    first = false;
+  }
+}
+
 __global__ void colsum_kernel(const float* __restrict__ part, float* __restrict__ out, int nslots, int D) {
   int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= D) return;
@@ -180,14 +244,15 @@ template <typename T>
 static int gate_norm_fwd_t(const void* y, const void* z, int64_t zrs, const float* w, void* out, float* rstd,
                            int64_t M, int D, float eps, cudaStream_t st) {
   constexpr int V = Vec16<T>::N;
-  ORBIT_REQUIRE(D % V == 0 && (z == nullptr || zrs % V == 0) && aligned16(y) && aligned16(out) &&
-                    (z == nullptr || aligned16(z)),
-                ERR_UNSUPPORTED, "orbit_gate_norm_fwd: D=%d and the z row stride must be multiples of %d elements and "
-                "all pointers 16-byte aligned", D, V);
-  int nv = norm_nv<T>(D);
-  ORBIT_REQUIRE(nv <= NORM_MAXV, ERR_UNSUPPORTED, "orbit_gate_norm_fwd: D=%d exceeds %d", D,
-                NORM_MAXV * NORM_THREADS * V);
   dim3 grid((unsigned)M);
+  int nv = norm_nv<T>(D);
+  const bool vec = D % V == 0 && (z == nullptr || zrs % V == 0) && aligned16(y) && aligned16(out) &&
+                   (z == nullptr || aligned16(z)) && nv <= NORM_MAXV;
+  if (!vec) {
+    gate_norm_fwd_scalar_kernel<T><<<grid, NORM_THREADS, 0, st>>>((const T*)y, (const T*)z, zrs, w, (T*)out, rstd, D, eps);
+    ORBIT_CHECK_LAUNCH("gate_norm_fwd_scalar_kernel");
+    return OK;
+  }
 #define L_(NV) gate_norm_fwd_kernel<T, NV><<<grid, NORM_THREADS, 0, st>>>((const T*)y, (const T*)z, zrs, w, (T*)out, rstd, D, eps)
   if (nv <= 1) L_(1); else if (nv == 2) L_(2); else L_(4);
 #undef L_
@@ -211,15 +276,21 @@ static int gate_norm_bwd_t(const void* y, const void* z, int64_t zrs, const floa
                            const void* dout, void* dy, void* dz, int64_t dzrs, float* dw, float* part, int64_t M,
                            int D, cudaStream_t st) {
   constexpr int V = Vec16<T>::N;
-  ORBIT_REQUIRE(D % V == 0 && (z == nullptr || (zrs % V == 0 && dzrs % V == 0)) && aligned16(y) && aligned16(dout) &&
-                    aligned16(dy) && (z == nullptr || (aligned16(z) && aligned16(dz))),
-                ERR_UNSUPPORTED, "orbit_gate_norm_bwd: D=%d and the z/dz row strides must be multiples of %d elements "
-                "and all pointers 16-byte aligned", D, V);
   int nv = norm_nv<T>(D);
-  ORBIT_REQUIRE(nv <= NORM_MAXV, ERR_UNSUPPORTED, "orbit_gate_norm_bwd: D=%d exceeds %d", D,
-                NORM_MAXV * NORM_THREADS * V);
   int slots = norm_bwd_slots(M);
   dim3 grid(slots);
+  const bool vec = D % V == 0 && (z == nullptr || (zrs % V == 0 && dzrs % V == 0)) && aligned16(y) && aligned16(dout) &&
+                   aligned16(dy) && (z == nullptr || (aligned16(z) && aligned16(dz))) && nv <= NORM_MAXV;
+  if (!vec) {
+    gate_norm_bwd_scalar_kernel<T><<<grid, NORM_THREADS, 0, st>>>((const T*)y, (const T*)z, zrs, w, rstd, (const T*)dout,
+                                                                  (T*)dy, (T*)dz, dzrs, part, M, D);
+    ORBIT_CHECK_LAUNCH("gate_norm_bwd_scalar_kernel");
+    if (dw != nullptr) {
+      colsum_kernel<<<(D + 255) / 256, 256, 0, st>>>(part, dw, slots, D);
+      ORBIT_CHECK_LAUNCH("colsum_kernel");
+    }
+    return OK;
+  }
 #define L_(NV) gate_norm_bwd_kernel<T, NV><<<grid, NORM_THREADS, 0, st>>>((const T*)y, (const T*)z, zrs, w, rstd, (const T*)dout, (T*)dy, (T*)dz, dzrs, part, M, D)
   if (nv <= 1) L_(1); else if (nv == 2) L_(2); else L_(4);
 #undef L_

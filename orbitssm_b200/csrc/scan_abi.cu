@@ -125,6 +125,41 @@ extern "C" int orbit_ssd_scan_pick_chunk(int R, int O, int G, int N, int precisi
   return gen_pick_chunk(R, O, G, N, backward, limit);
 }
 
+// One phase of the scan (see include/orbit_b200.h for the phase codes).
+extern "C" int orbit_ssd_scan_phase(const orbit_scan_args* a, int phase, const float* state_in, float* state_out, int dtype,
+                                    int precision, void* stream) {
+  int rc = check_common(a, dtype, "orbit_ssd_scan_phase");
+  if (rc != OK) return rc;
+  ORBIT_REQUIRE(a->B > 0 && a->L > 0, ERR_BAD_ARG, "orbit_ssd_scan_phase: empty problem (B=%d, L=%d)", a->B, a->L);
+  ORBIT_REQUIRE(precision == ORBIT_PRECISION_IEEE || precision == ORBIT_PRECISION_IO, ERR_BAD_ARG,
+                "orbit_ssd_scan_phase: unknown precision code %d", precision);
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool io = precision == ORBIT_PRECISION_IO;
+  if (io) {
+    const char* why = nullptr;
+    if (!tc_supported(*a, dtype, &why)) return fail(ERR_UNSUPPORTED, "orbit_ssd_scan_phase: precision 'io' refused: %s", why);
+  }
+  if (phase >= ORBIT_PHASE_CHUNK_DSTATE) {
+    ORBIT_REQUIRE(a->dy && a->dS, ERR_BAD_ARG, "orbit_ssd_scan_phase: null dy/dS");
+  }
+  switch (phase) {
+    case ORBIT_PHASE_CHUNK_STATE: return io ? tc_launch_chunk_state(*a, st) : gen_launch_chunk_state(*a, dtype, st);
+    case ORBIT_PHASE_STATE_PASS:
+      ORBIT_REQUIRE(state_out != nullptr, ERR_BAD_ARG, "orbit_ssd_scan_phase: the forward pass needs state_out (S_fin)");
+      return launch_state_pass_fwd(*a, state_in, state_out, st);
+    case ORBIT_PHASE_CHUNK_OUT:
+      ORBIT_REQUIRE(a->y != nullptr, ERR_BAD_ARG, "orbit_ssd_scan_phase: null y");
+      return io ? tc_launch_chunk_out(*a, st) : gen_launch_chunk_out(*a, dtype, st);
+    case ORBIT_PHASE_CHUNK_DSTATE: return io ? tc_launch_chunk_dstate(*a, st) : gen_launch_chunk_dstate(*a, dtype, st);
+    case ORBIT_PHASE_STATE_PASS_BWD: return launch_state_pass_bwd(*a, state_in, state_out, st);
+    case ORBIT_PHASE_CHUNK_GRADS:
+      ORBIT_REQUIRE(a->du && a->dBhat && a->dChat && a->ddA && a->dw, ERR_BAD_ARG,
+                    "orbit_ssd_scan_phase: null du/dBhat/dChat/ddA/dw");
+      return io ? tc_launch_chunk_grads(*a, st) : gen_launch_chunk_grads(*a, dtype, st);
+    default: return fail(ERR_BAD_ARG, "orbit_ssd_scan_phase: unknown phase %d", phase);
+  }
+}
+
 extern "C" int orbit_ssd_scan_fwd(const orbit_scan_args* a, const float* S0, float* S_fin, int dtype, int precision,
                                   void* stream) {
   int rc = check_common(a, dtype, "orbit_ssd_scan_fwd");

@@ -18,6 +18,38 @@ from . import _lib
 _DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
 
 
+#: number of this library's kernel launches since import (each C-ABI call adds the launches it makes)
+LAUNCHES = 0
+#: when a list, every timed region appends (name, start_event, end_event) recorded on the current stream
+_TIMING = None
+
+
+def set_timing(collector):
+    """Give a list to collect (name, start, end) CUDA-event triples around every kernel group; None switches it off."""
+    global _TIMING
+    _TIMING = collector
+
+
+class _timed:
+    def __init__(self, name, launches):
+        self.name, self.launches = name, launches
+
+    def __enter__(self):
+        global LAUNCHES
+        LAUNCHES += self.launches
+        if _TIMING is not None:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if _TIMING is not None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            _TIMING.append((self.name, self.e0, e1))
+        return False
+
+
 def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
@@ -68,9 +100,14 @@ def conv1d_fwd(x, weight, bias, window, silu=True):
     W = weight.shape[-1]
     bs, rs = _rows("conv1d_fwd", x)
     y = torch.empty((B, L, Cc), device=x.device, dtype=x.dtype)
+    if B * L == 0:
+        return y
+    if W < 2 or W > 4:
+        raise NotImplementedError(f"conv1d_fwd: conv width W={W}: the kernel serves 2..4")
     lib = _lib.load()
-    _lib.check(lib.orbit_conv1d_fwd(_ptr(x), bs, rs, _ptr(weight), _ptr(bias), _ptr(window), _ptr(y), B, L, Cc, W,
-                                    _dtype_code("conv1d_fwd", x), int(silu), _stream()), "orbit_conv1d_fwd")
+    with _timed("conv1d_fwd", 1):
+        _lib.check(lib.orbit_conv1d_fwd(_ptr(x), bs, rs, _ptr(weight), _ptr(bias), _ptr(window), _ptr(y), B, L, Cc, W,
+                                        _dtype_code("conv1d_fwd", x), int(silu), _stream()), "orbit_conv1d_fwd")
     return y
 
 
@@ -88,10 +125,11 @@ def conv1d_bwd(x, weight, bias, window, dy, silu=True, want_dwindow=False):
     lib = _lib.load()
     nbytes = lib.orbit_conv1d_bwd_workspace_bytes(B, L, Cc, W)
     ws = torch.empty((max(int(nbytes), 4),), device=x.device, dtype=torch.uint8)
-    _lib.check(lib.orbit_conv1d_bwd(_ptr(x), bs, rs, _ptr(weight), _ptr(bias), _ptr(window), _ptr(dy), _ptr(dx),
-                                    dx.stride(0), dx.stride(1), _ptr(dwin), _ptr(dweight), _ptr(dbias), _ptr(ws),
-                                    int(nbytes), B, L, Cc, W, _dtype_code("conv1d_bwd", x), int(silu), _stream()),
-               "orbit_conv1d_bwd")
+    with _timed("conv1d_bwd", 2 if B * L else 0):
+        _lib.check(lib.orbit_conv1d_bwd(_ptr(x), bs, rs, _ptr(weight), _ptr(bias), _ptr(window), _ptr(dy), _ptr(dx),
+                                        dx.stride(0), dx.stride(1), _ptr(dwin), _ptr(dweight), _ptr(dbias), _ptr(ws),
+                                        int(nbytes), B, L, Cc, W, _dtype_code("conv1d_bwd", x), int(silu), _stream()),
+                   "orbit_conv1d_bwd")
     return dx, dwin, dweight, dbias
 
 
@@ -137,8 +175,9 @@ def gate_norm_fwd(y, z, w, eps):
     out = torch.empty_like(y)
     rstd = torch.empty((M,), device=y.device, dtype=torch.float32) if w is not None else None
     lib = _lib.load()
-    _lib.check(lib.orbit_gate_norm_fwd(_ptr(y), _ptr(z), zs, _ptr(w), _ptr(out), _ptr(rstd), M, D, float(eps),
-                                       _dtype_code("gate_norm_fwd", y), _stream()), "orbit_gate_norm_fwd")
+    with _timed("gate_norm_fwd", 1 if M else 0):
+        _lib.check(lib.orbit_gate_norm_fwd(_ptr(y), _ptr(z), zs, _ptr(w), _ptr(out), _ptr(rstd), M, D, float(eps),
+                                           _dtype_code("gate_norm_fwd", y), _stream()), "orbit_gate_norm_fwd")
     return out, rstd
 
 
@@ -154,9 +193,10 @@ def gate_norm_bwd(y, z, w, rstd, dout):
     lib = _lib.load()
     nbytes = lib.orbit_gate_norm_bwd_workspace_bytes(M, D)
     ws = torch.empty((max(int(nbytes), 4),), device=y.device, dtype=torch.uint8)
-    _lib.check(lib.orbit_gate_norm_bwd(_ptr(y), _ptr(z), zs, _ptr(w), _ptr(rstd), _ptr(dout), _ptr(dy), _ptr(dz),
-                                       D, _ptr(dw), _ptr(ws), int(nbytes), M, D, _dtype_code("gate_norm_bwd", y),
-                                       _stream()), "orbit_gate_norm_bwd")
+    with _timed("gate_norm_bwd", (2 if w is not None else 1) if M else 0):
+        _lib.check(lib.orbit_gate_norm_bwd(_ptr(y), _ptr(z), zs, _ptr(w), _ptr(rstd), _ptr(dout), _ptr(dy), _ptr(dz),
+                                           D, _ptr(dw), _ptr(ws), int(nbytes), M, D, _dtype_code("gate_norm_bwd", y),
+                                           _stream()), "orbit_gate_norm_bwd")
     return dy, dz, dw
 
 
@@ -214,7 +254,9 @@ def pick_chunk(geo: ScanGeometry, precision: int, backward: bool, limit: int) ->
 
 def _tok_stride(who, t, inner):
     """Token stride (elements) of a [B, L, X, N] map whose [X, N] block is contiguous and whose batch stride is L * token stride."""
-    if t.dim() != 4 or t.stride(3) != 1 or t.stride(2) != t.shape[3] or t.stride(0) != t.shape[1] * t.stride(1):
+    ok = (t.dim() == 4 and (t.shape[3] == 1 or t.stride(3) == 1) and (t.shape[2] == 1 or t.stride(2) == t.shape[3])
+          and (t.shape[0] == 1 or t.stride(0) == t.shape[1] * t.stride(1)))
+    if not ok:
         raise ValueError(f"{who}: expected [B, L, {inner}, N] with contiguous [{inner}, N] blocks and collapsible (B, L), "
                          f"got shape {tuple(t.shape)} strides {t.stride()}")
     return t.stride(1)
@@ -237,8 +279,13 @@ def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     keep = _fill_common(a, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg)
     a.Sin, a.atot, a.y = Sin.data_ptr(), atot.data_ptr(), y.data_ptr()
     lib = _lib.load()
-    _lib.check(lib.orbit_ssd_scan_fwd(C.byref(a), _ptr(S0), _ptr(S_fin), _dtype_code("ssd_scan_fwd", u), precision,
-                                      _stream()), "orbit_ssd_scan_fwd")
+    dt = _dtype_code("ssd_scan_fwd", u)
+    for name, phase, sin, sout in (("scan_chunk_state", _lib.PHASE_CHUNK_STATE, None, None),
+                                   ("scan_state_pass", _lib.PHASE_STATE_PASS, S0, S_fin),
+                                   ("scan_chunk_out", _lib.PHASE_CHUNK_OUT, None, None)):
+        with _timed(name, 1):
+            _lib.check(lib.orbit_ssd_scan_phase(C.byref(a), phase, _ptr(sin), _ptr(sout), dt, precision, _stream()),
+                       "orbit_ssd_scan_phase(" + name + ")")
     del keep
     return y, S_fin, Sin, atot
 
@@ -303,8 +350,13 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
         dwd_tmp = torch.empty((B, L, H, R), **f32)
         a.dwd = dwd_tmp.data_ptr()
     lib = _lib.load()
-    _lib.check(lib.orbit_ssd_scan_bwd(C.byref(a), _ptr(dS_fin), _ptr(dS0), _dtype_code("ssd_scan_bwd", u), precision,
-                                      _stream()), "orbit_ssd_scan_bwd")
+    dt = _dtype_code("ssd_scan_bwd", u)
+    for name, phase, sin, sout in (("scan_chunk_dstate", _lib.PHASE_CHUNK_DSTATE, None, None),
+                                   ("scan_state_pass_bwd", _lib.PHASE_STATE_PASS_BWD, dS_fin, dS0),
+                                   ("scan_chunk_grads", _lib.PHASE_CHUNK_GRADS, None, None)):
+        with _timed(name, 1):
+            _lib.check(lib.orbit_ssd_scan_phase(C.byref(a), phase, _ptr(sin), _ptr(sout), dt, precision, _stream()),
+                       "orbit_ssd_scan_phase(" + name + ")")
     del keep
     if euler:
         out["dw"] = out["dw"] + dwd_tmp

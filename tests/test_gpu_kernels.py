@@ -64,7 +64,8 @@ def test_conv_empty_and_refusals():
 # ---------------------------------------------------------------------------------------------------- gate + norm
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("M,D,gate,norm", [(37, 256, True, True), (5, 2048, True, True), (64, 4096, True, True),
-                                           (19, 64, False, True), (19, 64, True, False), (300, 1024, True, True)])
+                                           (19, 64, False, True), (19, 64, True, False), (300, 1024, True, True), (7, 12, True, True),
+                                           (9, 9000, True, True)])
 def test_gate_norm(dtype, M, D, gate, norm):
     g = torch.Generator().manual_seed(1)
     y = torch.randn(M, D, generator=g).to(dtype).to(DEV)
