@@ -69,6 +69,25 @@ int orbit_gate_norm_bwd(const void* y, const void* z, int64_t z_row_stride, cons
                         const void* dout, void* dy, void* dz, int64_t dz_row_stride, float* dw, void* workspace,
                         int64_t workspace_bytes, int64_t M, int D, int dtype, void* stream);
 
+/* Gate + RMSNorm backward for callers that cannot allocate device memory.  No counterpart in the reference.
+ * Some hosts of this library never get to call cudaMalloc: a plugin loaded into a runtime that owns all device memory
+ * and hands the plugin only its input and output pointers (a cgo / JNI / ctypes binding without an allocator of its
+ * own), or a serving process whose device arena is carved up at start-up and closed afterwards, where a late
+ * allocation would stall the device or simply fail.  For them this variant of orbit_gate_norm_bwd keeps the partial
+ * sums of the weight gradient in a device array built into the library (9.25 MiB, held by every GPU that loads the
+ * library until the process exits) instead of a caller workspace.  Arguments and results are those of
+ * orbit_gate_norm_bwd without `workspace`.
+ *   Limit: min(M, 592) * D <= 592 * 4096 floats (any M when D <= 4096); larger problems are refused with
+ *          ORBIT_ERR_UNSUPPORTED and a message naming the sizes.
+ *   The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *   current) and remembers it; make that first call before any stream capture begins.
+ *   It calls no cudaMalloc, cudaFree or other allocating routine.
+ *   All calls on a device share the one array, which keeps whatever the last call left in it; nothing in it needs
+ *   clearing between calls, but two calls that overlap on the GPU (different streams) race on it: serialise them. */
+int orbit_gate_norm_bwd_noalloc(const void* y, const void* z, int64_t z_row_stride, const float* w, const float* rstd,
+                                const void* dout, void* dy, void* dz, int64_t dz_row_stride, float* dw, int64_t M, int D,
+                                int dtype, void* stream);
+
 /* ---- SSD-MIMO chunked scan ------------------------------------------------------------------------------------
  * Stands in for ssd_mimo_scan (src/orbit_ssm/kernels/ssd_mimo/autograd.py:2247-2339) and its backward
  * (_SSDMimoFn.backward, same file :1462); the law is the chunked dual of src/orbit_ssm/ssm/ssd_mimo_torch.py:663-708.
@@ -112,6 +131,7 @@ typedef struct orbit_scan_args {
   float* dbeta_part;  /* [B*nc, H, R, R, N]  out: per-chunk partial sums, or NULL                    */
   float* dgamma_part; /* [B*nc, H, R, O, N]  out or NULL                                             */
   float* dDg_part;    /* [B*nc, H, G, R, O]  out or NULL                                             */
+  int* status;        /* device int or NULL: set to 1 by a kernel whose bounded wait gave up         */
 } orbit_scan_args;
 
 /* The scan runs as three chunk-parallel phases per direction (the decomposition of the reference's chunk-parallel

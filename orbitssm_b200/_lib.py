@@ -30,7 +30,7 @@ class ScanArgs(C.Structure):
         + [(n, C.c_int64) for n in ("b_ts", "gb_ts", "c_ts", "gc_ts")]
         + [(n, C.c_void_p) for n in ("beta", "gamma", "chi", "dA", "w", "wd", "Dg", "Sin", "atot", "dS", "y", "dy", "du",
                                      "dBhat", "dgBp", "dChat", "dgCp", "ddA", "dw", "dwd", "dchi", "dbeta_part",
-                                     "dgamma_part", "dDg_part")]
+                                     "dgamma_part", "dDg_part", "status")]
     )
 
 
@@ -47,6 +47,7 @@ SIGNATURES = {
     "orbit_gate_norm_fwd": (_I, [_P, _P, _L, _P, _P, _P, _L, _I, _F, _I, _P]),
     "orbit_gate_norm_bwd_workspace_bytes": (_L, [_L, _I]),
     "orbit_gate_norm_bwd": (_I, [_P, _P, _L, _P, _P, _P, _P, _P, _L, _P, _P, _L, _L, _I, _I, _P]),
+    "orbit_gate_norm_bwd_noalloc": (_I, [_P, _P, _L, _P, _P, _P, _P, _P, _L, _P, _L, _I, _I, _P]),
     "orbit_ssd_scan_pick_chunk": (_I, [_I, _I, _I, _I, _I, _I, _I]),
     "orbit_ssd_scan_phase": (_I, [C.POINTER(ScanArgs), _I, _P, _P, _I, _I, _P]),
     "orbit_ssd_scan_fwd": (_I, [C.POINTER(ScanArgs), _P, _P, _I, _I, _P]),

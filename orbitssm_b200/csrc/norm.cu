@@ -7,6 +7,7 @@
 // HBM-bound: forward 3*M*D*es bytes (y, z in; out), backward 5*M*D*es (y, z, dout in; dy, dz out).
 #include "common.cuh"
 #include "../../include/orbit_b200.h"
+#include <mutex>
 
 namespace orbit {
 
@@ -328,4 +329,65 @@ extern "C" int orbit_gate_norm_bwd(const void* y, const void* z, int64_t z_row_s
   if (dtype == F32)
     return gate_norm_bwd_t<float>(y, z, z_row_stride, w, rstd, dout, dy, dz, dz_row_stride, dw, part, M, D, st);
   return fail(ERR_BAD_ARG, "orbit_gate_norm_bwd: unknown dtype code %d", dtype);
+}
+
+
+// ---- gate + RMSNorm backward without any allocation ---------------------------------------------------------------
+// Same arithmetic as orbit_gate_norm_bwd; the partial-sum buffer of the weight gradient lives in this file-scope device
+// array instead of a caller workspace.  Every GPU that loads the library holds the array (9.25 MiB) until exit.
+namespace orbit {
+constexpr int64_t NORM_NOALLOC_FLOATS = 592LL * 4096;   // slots(M) * D must fit: e.g. any M with D <= 4096
+static __device__ __align__(256) float g_norm_bwd_scratch[NORM_NOALLOC_FLOATS];
+
+// In host code the array's name is only a handle; the device address comes from cudaGetSymbolAddress, asked once per
+// device with that device current.
+static float* g_norm_bwd_scratch_ptr[64] = {nullptr};
+static std::mutex g_norm_bwd_scratch_mu;
+
+static int norm_noalloc_scratch(float** out) {
+  int dev = -1;
+  ORBIT_CHECK_CUDA(cudaGetDevice(&dev));
+  ORBIT_REQUIRE(dev >= 0 && dev < 64, ERR_UNSUPPORTED, "orbit_gate_norm_bwd_noalloc: device index %d outside 0..63", dev);
+  std::lock_guard<std::mutex> lock(g_norm_bwd_scratch_mu);
+  if (g_norm_bwd_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    ORBIT_CHECK_CUDA(cudaGetSymbolAddress(&p, g_norm_bwd_scratch));
+    ORBIT_REQUIRE(p != nullptr, ERR_CUDA, "orbit_gate_norm_bwd_noalloc: cudaGetSymbolAddress returned a null address");
+    g_norm_bwd_scratch_ptr[dev] = (float*)p;
+  }
+  *out = g_norm_bwd_scratch_ptr[dev];
+  return OK;
+}
+}  // namespace orbit
+
+extern "C" int orbit_gate_norm_bwd_noalloc(const void* y, const void* z, int64_t z_row_stride, const float* w,
+                                           const float* rstd, const void* dout, void* dy, void* dz,
+                                           int64_t dz_row_stride, float* dw, int64_t M, int D, int dtype, void* stream) {
+  ORBIT_REQUIRE(y && dout && dy, ERR_BAD_ARG, "orbit_gate_norm_bwd_noalloc: null y/dout/dy");
+  ORBIT_REQUIRE(z == nullptr || dz != nullptr, ERR_BAD_ARG, "orbit_gate_norm_bwd_noalloc: dz is required with a gate");
+  ORBIT_REQUIRE(w == nullptr || (rstd != nullptr && dw != nullptr), ERR_BAD_ARG,
+                "orbit_gate_norm_bwd_noalloc: rstd and dw are required with a norm");
+  ORBIT_REQUIRE(M >= 0 && D > 0, ERR_BAD_ARG, "orbit_gate_norm_bwd_noalloc: bad sizes M=%lld D=%d", (long long)M, D);
+  const int64_t need = (int64_t)norm_bwd_slots(M) * D;
+  ORBIT_REQUIRE(need <= NORM_NOALLOC_FLOATS, ERR_UNSUPPORTED,
+                "orbit_gate_norm_bwd_noalloc: min(M, 592) * D = %lld floats of scratch exceed the built-in %lld (M=%lld, D=%d); "
+                "use orbit_gate_norm_bwd with a caller workspace", (long long)need, (long long)NORM_NOALLOC_FLOATS,
+                (long long)M, D);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (M == 0) {
+    if (dw) ORBIT_CHECK_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * D, st));
+    return OK;
+  }
+  float* part = nullptr;
+  if (w != nullptr) {
+    int rc = norm_noalloc_scratch(&part);
+    if (rc != OK) return rc;
+    // nothing in the scratch has to start at zero: each CTA overwrites its whole row of partial sums before the
+    // fixed-order column sum reads exactly the rows that were written
+  }
+  if (dtype == BF16)
+    return gate_norm_bwd_t<__nv_bfloat16>(y, z, z_row_stride, w, rstd, dout, dy, dz, dz_row_stride, dw, part, M, D, st);
+  if (dtype == F32)
+    return gate_norm_bwd_t<float>(y, z, z_row_stride, w, rstd, dout, dy, dz, dz_row_stride, dw, part, M, D, st);
+  return fail(ERR_BAD_ARG, "orbit_gate_norm_bwd_noalloc: unknown dtype code %d", dtype);
 }
