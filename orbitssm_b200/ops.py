@@ -290,8 +290,29 @@ def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     return y, S_fin, Sin, atot
 
 
+_STATUS = {}
+
+
+def _status_word(device):
+    """Per-device int32 the tensor-core kernels set when one of their bounded waits gives up."""
+    key = (device.type, device.index)
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+def check_device_status(device=None):
+    """Raise if a kernel reported a wait that ran out (synchronises the device; for tests and end-of-run checks)."""
+    for key, t in _STATUS.items():
+        if int(t.item()) != 0:
+            t.zero_()
+            raise RuntimeError(f"orbit_b200: a bounded device-side wait gave up on {key} (status {_lib.load() and 5})")
+
+
 def _fill_common(a, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg):
     a.u = u.data_ptr()
+    if u.is_cuda:
+        a.status = _status_word(u.device).data_ptr()
     a.Bhat, a.b_ts = Bhat.data_ptr(), _tok_stride("ssd_scan", Bhat, "R")
     a.Chat, a.c_ts = Chat.data_ptr(), _tok_stride("ssd_scan", Chat, "O")
     if gBp is not None:

@@ -391,8 +391,11 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
     def _route(self, io, geo, needs_grad):
         lib = _lib.load()
         limit = 64 if self.chunk_size == "auto" else int(self.chunk_size)
+        s = self.spec
+        shared_maps = not (s.use_g_b or s.use_g_c or s.head_bias or s.r_mix_mode != "none")
         if self.precision == "io" and io == torch.bfloat16:
-            T = ops.pick_chunk(geo, _lib.PRECISION_IO, needs_grad, 128 if self.chunk_size == "auto" else limit)
+            T = ops.pick_chunk(geo, _lib.PRECISION_IO, needs_grad, 128 if self.chunk_size == "auto" else limit) \
+                if shared_maps else 0
             if T > 0:
                 self._route_note = "tcgen05"
                 return _lib.PRECISION_IO, T

@@ -195,3 +195,31 @@ def test_umma_tile(mode, K, N):
     torch.cuda.synchronize()
     assert int(status.item()) == 0, "a bounded device wait gave up"
     assert rel(D, want) < 1e-5, (mode, K, N, rel(D, want))
+
+
+# ---------------------------------------------------------------------------------------------------- scan, tcgen05
+TC_CASES = [
+    # B, L, H, skip, trap, s0
+    (1, 128, 1, False, False, False),
+    (2, 256, 3, True, False, True),
+    (1, 200, 2, True, True, True),
+    (2, 37, 2, True, False, True),
+    (1, 640, 4, True, True, False),
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+def test_scan_tc_forward(case):
+    """Forward on the tensor-core tiles (bf16 operands, fp32 accumulate) against the fp64 restatement on the same
+    bf16-rounded inputs: y within 1e-2 (operands of the second contraction are rounded to bf16: masked scores and
+    entering states), final state within 2e-3."""
+    B, L, H, skip, trap, s0 = case
+    c = scan_case(B, L, H, 1, 1, 64, 128, torch.bfloat16, False, False, False, skip, trap, s0, seed=5)
+    geo = c["geo"]
+    args = (c["u"], c["Bhat"], None, c["Chat"], None, None, None, None, c["dA"], c["w"],
+            c["w"] if c["euler"] else c["wd"], c["Dg"])
+    y, S_fin, Sin, atot = ops.scan_fwd(geo, 128, _lib.PRECISION_IO, *args, c["S0"])
+    ops.check_device_status()
+    ry, rS, _, _ = R.scan_fwd(geo, 128, 0, *args, c["S0"])
+    assert rel(S_fin, rS) < 2e-3, ("S_fin", rel(S_fin, rS))
+    assert rel(y, ry) < 1e-2, ("y", rel(y, ry))
