@@ -40,6 +40,11 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   return false;
 }
 
+// Same, with a warp-uniform answer: code under it may use .sync.aligned instructions and full-mask shuffles.
+__device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag) ? 1 : 0) != 0;
+}
+
 // Inclusive prefix over the 128 values held by threads 0..127 -> cs[0..127]; every thread of the CTA must call.
 __device__ __forceinline__ void chunk_prefix(float v, float* cs, float* wsum) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -131,7 +136,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_state_kernel(const __g
 
   auto epilogue = [&](int hh) {
     const int be = hh & 1;
-    if (wait_or_abort(&bar_mma[be], (uint32_t)((hh >> 1) & 1), abort_flag)) {
+    if (wait_warp(&bar_mma[be], (uint32_t)((hh >> 1) & 1), abort_flag)) {
       tc_fence_after_sync();
       uint32_t r[32];
       tmem_ld32(tmem_addr(tbase, q * 32, be * 64 + wg * 32), r);
@@ -157,7 +162,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_state_kernel(const __g
     if (tid < 128) fv[tid] = mode == 0 ? __expf(cs[127] - cs[tid]) * wt : __expf(cs[tid]);
     if (tid == 0 && mode == 0) a.atot[((int64_t)b * a.nc + c) * H + h] = __expf(cs[127]);
     __syncthreads();
-    if (wait_or_abort(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag)) {
+    if (wait_warp(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag)) {
       const int row = tid & 127, half = tid >> 7;
       const float f = fv[row];
 #pragma unroll
@@ -262,7 +267,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
     }
   }
   __syncthreads();
-  bool cb_ok = wait_or_abort(&bar_cb, 0, abort_flag);
+  bool cb_ok = wait_warp(&bar_cb, 0, abort_flag);
   tc_fence_after_sync();
   const uint32_t idesc_y = idesc_bf16(128, 64, 0, 1);
   __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(a.y);
@@ -339,7 +344,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
         umma_commit(&bar_y);
       }
     }
-    if (wait_or_abort(&bar_y, (uint32_t)(h & 1), abort_flag)) {
+    if (wait_warp(&bar_y, (uint32_t)(h & 1), abort_flag)) {
       tc_fence_after_sync();
       uint32_t r1[32], r2[32];
       tmem_ld32(tmem_addr(tbase, q * 32, TM_Y1 + wg * 32), r1);
@@ -384,6 +389,557 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
   if (warp == 0) tmem_dealloc(tbase, 256);
 }
 
+// Deterministic CTA-wide sum of one float per thread (fixed tree); result returned to every thread.  `red` >= 8 floats.
+__device__ __forceinline__ float cta_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int w = 0; w < TC_THREADS / 32; ++w) t += red[w];
+  return t;
+}
+
+// Column sums over the 32 rows held by a warp: in: v[i] = value of (row = lane, column i); out: v[0] = sum over the
+// warp's rows of column `lane` (butterfly reduce-scatter, 31 shuffles, fixed order).
+__device__ __forceinline__ void warp_colsum32(float (&v)[32], int lane) {
+#pragma unroll
+  for (int off = 16, n = 16; off >= 1; off >>= 1, n >>= 1) {
+    const bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int k = 0; k < n; ++k) {
+      float send = upper ? v[k] : v[k + n];
+      float keep = upper ? v[k + n] : v[k];
+      v[k] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+  }
+}
+
+// fp32 [128 n][64 p] state tile -> bf16 swizzled block; optionally accumulates sum(src * other) per thread
+__device__ __forceinline__ float load_state_bf16(const float* __restrict__ src, const float* __restrict__ other, uint8_t* dst) {
+  float acc = 0.f;
+  const float4* s4 = reinterpret_cast<const float4*>(src);
+  const float4* o4 = reinterpret_cast<const float4*>(other);
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int idx = it * TC_THREADS + threadIdx.x;
+    const int n = idx >> 4, c4 = idx & 15;
+    float4 v = s4[idx];
+    if (other != nullptr) {
+      float4 o = o4[idx];
+      acc = fmaf(v.x, o.x, fmaf(v.y, o.y, fmaf(v.z, o.z, fmaf(v.w, o.w, acc))));
+    }
+    *reinterpret_cast<uint2*>(dst + sw128_offset(n, c4 >> 1) + (c4 & 1) * 8) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+  }
+  return acc;
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// chunk_grads, part 1 (state path).  Per head:
+//   da[t]   = sum_p dy[t,p] (C Sin)[t,p]                       -> a.ddA (scratch use; part 2 turns it into d dA)
+//   datot   = sum_{n,p} dSo[n,p] Sin[n,p]                      -> a.dw at the chunk's first token (scratch use)
+//   dCx[t,n] += a_t sum_p dy[t,p] Sin[n,p]                     accumulated over heads in TMEM -> a.dChat
+//   dBx[s,n] += e_s sum_p u[s,p]  dSo[n,p]                     accumulated over heads in TMEM -> a.dBhat
+// ------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(const __grid_constant__ CUtensorMap tmC,
+                                                                             const __grid_constant__ CUtensorMap tmU,
+                                                                             const __grid_constant__ CUtensorMap tmDY,
+                                                                             const ScanArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = align1024(smem_raw);
+  uint8_t* sC = sm;                      // 2 blocks
+  uint8_t* sX = sm + 2 * BLK;            // 2 buffers
+  uint8_t* sDY = sm + 4 * BLK;           // 2 buffers
+  uint8_t* sADY = sm + 6 * BLK;          // a_t * dy
+  uint8_t* sEX = sm + 7 * BLK;           // e_s * u
+  uint8_t* sS = sm + 8 * BLK;            // Sin  bf16 [n][p]
+  uint8_t* sdS = sm + 9 * BLK;           // dSo  bf16 [n][p]
+  float* cs = reinterpret_cast<float*>(sm + 10 * BLK);
+  float* fa = cs + 128;                  // a_t
+  float* fe = fa + 128;                  // e_s
+  float* dapart = fe + 128;              // [2][128]
+  float* wsum = dapart + 256;            // 8
+  float* red = wsum + 8;                 // 8
+  __shared__ uint64_t bar_map, bar_x[2], bar_m;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = warp & 3, wg = warp >> 2;
+  const int c = blockIdx.x, b = blockIdx.y, t0 = c * TC_T;
+  const int Tv = min(TC_T, a.L - t0);
+  const int H = a.H;
+  const int t = q * 32 + lane;
+
+  if (tid == 0) {
+    mbar_init(&bar_map, 1);
+    mbar_init(&bar_x[0], 1);
+    mbar_init(&bar_x[1], 1);
+    mbar_init(&bar_m, 1);
+    mbar_fence_init();
+    s_abort = 0;
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_slot;
+  volatile int* abort_flag = &s_abort;
+  const uint32_t TM_DCX = 0, TM_DBX = 128, TM_YCU = 256;
+
+  if (tid == 0) {
+    mbar_expect_tx(&bar_map, 2 * BLK);
+    tma_load_3d(sC, &tmC, &bar_map, 0, t0, b);
+    tma_load_3d(sC + BLK, &tmC, &bar_map, 64, t0, b);
+    for (int i = 0; i < 2 && i < H; ++i) {
+      mbar_expect_tx(&bar_x[i], 2 * BLK);
+      tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], i * TC_G, t0, b);
+      tma_load_3d(sDY + i * BLK, &tmDY, &bar_x[i], i * TC_G, t0, b);
+    }
+  }
+  const uint32_t id_y = idesc_bf16(128, 64, 0, 1), id_acc = idesc_bf16(128, 128, 0, 0);
+
+  for (int h = 0; h < H; ++h) {
+    const int buf = h & 1;
+    float d = 0.f, wt = 0.f;
+    if (tid < Tv) {
+      int64_t i = ((int64_t)b * a.L + t0 + tid) * H + h;
+      d = a.dA[i];
+      wt = a.w[i];
+    }
+    chunk_prefix(d, cs, wsum);
+    if (tid < 128) {
+      fa[tid] = __expf(cs[tid]);
+      fe[tid] = __expf(cs[127] - cs[tid]) * wt;
+    }
+    const int64_t so = (((int64_t)b * a.nc + c) * H + h) * (int64_t)(TC_N * TC_G);
+    float part = load_state_bf16(a.Sin + so, a.dS + so, sS);
+    load_state_bf16(a.dS + so, nullptr, sdS);
+    const float datot = cta_sum(part, red);       // contains __syncthreads: fa/fe visible afterwards
+    if (tid == 0) a.dw[((int64_t)b * a.L + t0) * H + h] = datot;
+    if (wait_warp(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag)) {
+      const int row = tid & 127, half = tid >> 7;
+      const float f1 = fa[row], f2 = fe[row];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t off = sw128_offset(row, half * 4 + j);
+        uint4 v = *reinterpret_cast<const uint4*>(sDY + buf * BLK + off);
+        uint4 x = *reinterpret_cast<const uint4*>(sX + buf * BLK + off);
+        uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
+        uint32_t* px = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float lo, hi;
+          unpack_bf16(pv[k], lo, hi);
+          pv[k] = pack_bf16(lo * f1, hi * f1);
+          unpack_bf16(px[k], lo, hi);
+          px[k] = pack_bf16(lo * f2, hi * f2);
+        }
+        *reinterpret_cast<uint4*>(sADY + off) = v;
+        *reinterpret_cast<uint4*>(sEX + off) = x;
+      }
+    }
+    fence_proxy_async();
+    __syncthreads();
+    if (tid == 0 && !*abort_flag) {
+      bool ok = (h > 0) || wait_or_abort(&bar_map, 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        const uint32_t ac = smem_u32(sC), bs = smem_u32(sS), bd = smem_u32(sdS), aa = smem_u32(sADY), ae = smem_u32(sEX);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_YCU, desc_k(ac, ks), desc_mn(bs, ks), id_y, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) umma_bf16(tbase + TM_DCX, desc_k(aa, ks), desc_k(bs, ks), id_acc, (h > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) umma_bf16(tbase + TM_DBX, desc_k(ae, ks), desc_k(bd, ks), id_acc, (h > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&bar_m);
+      }
+    }
+    float dsum = 0.f;
+    if (wait_warp(&bar_m, (uint32_t)(h & 1), abort_flag)) {
+      tc_fence_after_sync();
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tbase, q * 32, TM_YCU + wg * 32), r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4) {
+        uint4 dv = *reinterpret_cast<const uint4*>(sDY + buf * BLK + sw128_offset(t, wg * 4 + k4));
+        const uint32_t* dp = reinterpret_cast<const uint32_t*>(&dv);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float lo, hi;
+          unpack_bf16(dp[k], lo, hi);
+          dsum = fmaf(lo, __uint_as_float(r[k4 * 8 + 2 * k]), dsum);
+          dsum = fmaf(hi, __uint_as_float(r[k4 * 8 + 2 * k + 1]), dsum);
+        }
+      }
+    }
+    dapart[wg * 128 + t] = dsum;
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid < Tv) a.ddA[((int64_t)b * a.L + t0 + tid) * H + h] = dapart[tid] + dapart[128 + tid];
+    if (tid == 0 && !*abort_flag && h + 2 < H) {
+      mbar_expect_tx(&bar_x[buf], 2 * BLK);
+      tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h + 2) * TC_G, t0, b);
+      tma_load_3d(sDY + buf * BLK, &tmDY, &bar_x[buf], (h + 2) * TC_G, t0, b);
+    }
+  }
+  // accumulated cross terms -> global (fp32 rows of N)
+  if (!*abort_flag) {
+    tc_fence_after_sync();
+#pragma unroll
+    for (int jj = 0; jj < 2; ++jj) {
+      const int col = wg * 64 + jj * 32;
+      uint32_t r1[32], r2[32];
+      tmem_ld32(tmem_addr(tbase, q * 32, TM_DCX + col), r1);
+      tmem_ld32(tmem_addr(tbase, q * 32, TM_DBX + col), r2);
+      tmem_ld_wait();
+      if (t < Tv) {
+        float* dc = a.dChat + ((int64_t)b * a.L + t0 + t) * TC_N + col;
+        float* db = a.dBhat + ((int64_t)b * a.L + t0 + t) * TC_N + col;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          *reinterpret_cast<float4*>(dc + j) = make_float4(__uint_as_float(r1[j]), __uint_as_float(r1[j + 1]), __uint_as_float(r1[j + 2]), __uint_as_float(r1[j + 3]));
+          *reinterpret_cast<float4*>(db + j) = make_float4(__uint_as_float(r2[j]), __uint_as_float(r2[j + 1]), __uint_as_float(r2[j + 2]), __uint_as_float(r2[j + 3]));
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag && a.status) atomicExch(a.status, 1);
+  if (warp == 0) tmem_dealloc(tbase, 512);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// chunk_grads, part 2 (score path + everything per token).  Per head, with dM = dy u^T, K = dM o CB, W the decay mask:
+//   du[s,p]  = sum_{t>=s} (CB o W)[t,s] dy[t,p] + e_s (B dSo)[s,p] + D[h,p] dy[s,p]
+//   de[s]    = sum_p u[s,p] (B dSo)[s,p]
+//   d cs, dw, dwd from row / column sums of K o E, da (part 1), de, datot (part 1);  d dA = reverse prefix of d cs
+//   dScoreSum += dM o W   (registers, summed over heads)
+// and after the head loop   dC = dScoreSum B + dCx,   dB = dScoreSum^T C + dBx   (dCx, dBx from part 1).
+// ------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(const __grid_constant__ CUtensorMap tmB,
+                                                                             const __grid_constant__ CUtensorMap tmC,
+                                                                             const __grid_constant__ CUtensorMap tmU,
+                                                                             const __grid_constant__ CUtensorMap tmDY,
+                                                                             const ScanArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = align1024(smem_raw);
+  uint8_t* sB = sm;                      // 2 blocks
+  uint8_t* sC = sm + 2 * BLK;            // 2 blocks
+  uint8_t* sX = sm + 4 * BLK;            // 2 buffers
+  uint8_t* sDY = sm + 6 * BLK;           // 2 buffers
+  uint8_t* sMs = sm + 8 * BLK;           // masked scores, later the summed score gradient; 2 blocks
+  uint8_t* sdS = sm + 10 * BLK;          // dSo bf16 [n][p]
+  float* cs = reinterpret_cast<float*>(sm + 11 * BLK);
+  float* wv = cs + 128;
+  float* wdv = wv + 128;
+  float* rowpart = wdv + 128;            // [2][128]
+  float* colpart = rowpart + 256;        // [4][128]
+  float* depart = colpart + 512;         // [2][128]
+  float* kdiag = depart + 256;           // [128]
+  float* ddpart = kdiag + 128;           // [4][64]
+  float* gcs = ddpart + 256;             // [128]
+  float* wsum = gcs + 128;               // 8
+  float* red = wsum + 8;                 // 8
+  __shared__ uint64_t bar_map, bar_x[2], bar_cb, bar_a, bar_b;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = warp & 3, wg = warp >> 2;
+  const int c = blockIdx.x, b = blockIdx.y, t0 = c * TC_T;
+  const int Tv = min(TC_T, a.L - t0);
+  const int H = a.H;
+  const int t = q * 32 + lane;
+
+  if (tid == 0) {
+    mbar_init(&bar_map, 1);
+    mbar_init(&bar_x[0], 1);
+    mbar_init(&bar_x[1], 1);
+    mbar_init(&bar_cb, 1);
+    mbar_init(&bar_a, 1);
+    mbar_init(&bar_b, 1);
+    mbar_fence_init();
+    s_abort = 0;
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_slot;
+  volatile int* abort_flag = &s_abort;
+  const uint32_t TM_CB = 0, TM_DM = 128, TM_DX1 = 128, TM_DX2 = 256;
+
+  if (tid == 0) {
+    mbar_expect_tx(&bar_map, 4 * BLK);
+    tma_load_3d(sB, &tmB, &bar_map, 0, t0, b);
+    tma_load_3d(sB + BLK, &tmB, &bar_map, 64, t0, b);
+    tma_load_3d(sC, &tmC, &bar_map, 0, t0, b);
+    tma_load_3d(sC + BLK, &tmC, &bar_map, 64, t0, b);
+    for (int i = 0; i < 2 && i < H; ++i) {
+      mbar_expect_tx(&bar_x[i], 2 * BLK);
+      tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], i * TC_G, t0, b);
+      tma_load_3d(sDY + i * BLK, &tmDY, &bar_x[i], i * TC_G, t0, b);
+    }
+    if (wait_or_abort(&bar_map, 0, abort_flag)) {
+      tc_fence_after_sync();
+      const uint32_t ac = smem_u32(sC), bb = smem_u32(sB);
+      const uint32_t id = idesc_bf16(128, 128, 0, 0);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_CB, desc_k(ac, ks), desc_k(bb, ks), id, ks > 0 ? 1u : 0u);
+      umma_commit(&bar_cb);
+    }
+  }
+  __syncthreads();
+  const bool cb_ok = wait_warp(&bar_cb, 0, abort_flag);
+  tc_fence_after_sync();
+
+  float acc[2][32];                      // summed score gradient of this thread's row, slabs 2*wg and 2*wg+1
+#pragma unroll
+  for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc[jj][i] = 0.f;
+  __nv_bfloat16* duout = reinterpret_cast<__nv_bfloat16*>(a.du);
+  const uint32_t id_dm = idesc_bf16(128, 128, 0, 0), id_x2 = idesc_bf16(128, 64, 0, 1), id_x1 = idesc_bf16(128, 64, 1, 1);
+
+  for (int h = 0; h < H; ++h) {
+    const int buf = h & 1;
+    float d = 0.f, wt = 0.f, wdt = 0.f, da_t = 0.f;
+    int64_t gi = 0;
+    if (tid < Tv) {
+      gi = ((int64_t)b * a.L + t0 + tid) * H + h;
+      d = a.dA[gi];
+      wt = a.w[gi];
+      wdt = a.wd[gi];
+      da_t = a.ddA[gi];                                  // part 1 left da here
+    }
+    const float datot = a.dw[((int64_t)b * a.L + t0) * H + h];   // part 1 left datot here
+    if (tid < 128) {
+      wv[tid] = wt;
+      wdv[tid] = wdt;
+    }
+    chunk_prefix(d, cs, wsum);
+    const int64_t so = (((int64_t)b * a.nc + c) * H + h) * (int64_t)(TC_N * TC_G);
+    load_state_bf16(a.dS + so, nullptr, sdS);
+    fence_proxy_async();
+    __syncthreads();
+    if (tid == 0 && !*abort_flag) {
+      if (wait_or_abort(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag)) {
+        tc_fence_after_sync();
+        const uint32_t ady = smem_u32(sDY + buf * BLK), bx = smem_u32(sX + buf * BLK), ab = smem_u32(sB), bd = smem_u32(sdS);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) umma_bf16(tbase + TM_DM, desc_k(ady, ks), desc_k(bx, ks), id_dm, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DX2, desc_k(ab, ks), desc_mn(bd, ks), id_x2, ks > 0 ? 1u : 0u);
+        umma_commit(&bar_a);
+      }
+    }
+    // ---- score pass: this thread owns row t, slabs j = 2*wg, 2*wg+1 ----
+    float rowS = 0.f;
+    if (wait_warp(&bar_a, (uint32_t)(h & 1), abort_flag) && cb_ok) {
+      tc_fence_after_sync();
+      const float cst = cs[t], wdt_t = wdv[t];
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        const int j = wg * 2 + jj;
+        uint32_t pk[16];
+        float colv[32];
+        if (j > q) {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) pk[k] = 0u;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) colv[i] = 0.f;
+        } else {
+          uint32_t rm[32], rc[32];
+          tmem_ld32(tmem_addr(tbase, q * 32, TM_DM + j * 32), rm);
+          tmem_ld32(tmem_addr(tbase, q * 32, TM_CB + j * 32), rc);
+          tmem_ld_wait();
+          float mv[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int s = j * 32 + i;
+            const float dm = __uint_as_float(rm[i]), cb = __uint_as_float(rc[i]);
+            const float kv = dm * cb;
+            float wgt = 0.f, ce = 0.f;
+            if (s < t) {
+              const float E = __expf(cst - cs[s]);
+              wgt = E * wv[s];
+              ce = kv * E;
+              rowS = fmaf(ce, wv[s], rowS);
+            } else if (s == t) {
+              wgt = wdt_t;
+              kdiag[t] = kv;
+            }
+            colv[i] = ce;
+            acc[jj][i] = fmaf(dm, wgt, acc[jj][i]);
+            mv[i] = cb * wgt;
+          }
+#pragma unroll
+          for (int k = 0; k < 16; ++k) pk[k] = pack_bf16(mv[2 * k], mv[2 * k + 1]);
+        }
+        uint8_t* dstb = sMs + (j >> 1) * BLK;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          *reinterpret_cast<uint4*>(dstb + sw128_offset(t, (j & 1) * 4 + k)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
+        warp_colsum32(colv, lane);
+        colpart[q * 128 + j * 32 + lane] = colv[0];
+      }
+    }
+    rowpart[wg * 128 + t] = rowS;
+    tc_fence_before_sync();
+    fence_proxy_async();
+    __syncthreads();
+    if (tid == 0 && !*abort_flag) {
+      tc_fence_after_sync();
+      const uint32_t am = smem_u32(sMs), bdy = smem_u32(sDY + buf * BLK);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DX1, desc_mn(am, ks), desc_mn(bdy, ks), id_x1, ks > 0 ? 1u : 0u);
+      umma_commit(&bar_b);
+    }
+    // ---- du, de, dD ----
+    float de_half = 0.f;
+    float ddv[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) ddv[i] = 0.f;
+    if (wait_warp(&bar_b, (uint32_t)(h & 1), abort_flag)) {
+      tc_fence_after_sync();
+      uint32_t r1[32], r2[32];
+      tmem_ld32(tmem_addr(tbase, q * 32, TM_DX1 + wg * 32), r1);
+      tmem_ld32(tmem_addr(tbase, q * 32, TM_DX2 + wg * 32), r2);
+      tmem_ld_wait();
+      const float es = __expf(cs[127] - cs[t]) * wv[t];
+      uint32_t outp[16];
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4) {
+        uint4 uv = *reinterpret_cast<const uint4*>(sX + buf * BLK + sw128_offset(t, wg * 4 + k4));
+        uint4 dv = *reinterpret_cast<const uint4*>(sDY + buf * BLK + sw128_offset(t, wg * 4 + k4));
+        const uint32_t* up = reinterpret_cast<const uint32_t*>(&uv);
+        const uint32_t* dp = reinterpret_cast<const uint32_t*>(&dv);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int i = k4 * 8 + k * 2;
+          float u0, u1, g0, g1;
+          unpack_bf16(up[k], u0, u1);
+          unpack_bf16(dp[k], g0, g1);
+          const float x20 = __uint_as_float(r2[i]), x21 = __uint_as_float(r2[i + 1]);
+          float d0 = 0.f, d1 = 0.f;
+          if (a.Dg) {
+            d0 = a.Dg[h * TC_G + wg * 32 + i];
+            d1 = a.Dg[h * TC_G + wg * 32 + i + 1];
+          }
+          outp[k4 * 4 + k] = pack_bf16(__uint_as_float(r1[i]) + es * x20 + d0 * g0, __uint_as_float(r1[i + 1]) + es * x21 + d1 * g1);
+          de_half = fmaf(u0, x20, fmaf(u1, x21, de_half));
+          ddv[i] = g0 * u0;
+          ddv[i + 1] = g1 * u1;
+        }
+      }
+      if (t < Tv) {
+        uint4* dst = reinterpret_cast<uint4*>(duout + ((int64_t)b * a.L + t0 + t) * (int64_t)(H * TC_G) + h * TC_G + wg * 32);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) dst[k] = make_uint4(outp[4 * k], outp[4 * k + 1], outp[4 * k + 2], outp[4 * k + 3]);
+      }
+    }
+    depart[wg * 128 + t] = de_half;
+    if (a.dDg_part) {
+      warp_colsum32(ddv, lane);
+      ddpart[q * 64 + wg * 32 + lane] = ddv[0];
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0 && !*abort_flag && h + 2 < H) {
+      mbar_expect_tx(&bar_x[buf], 2 * BLK);
+      tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h + 2) * TC_G, t0, b);
+      tma_load_3d(sDY + buf * BLK, &tmDY, &bar_x[buf], (h + 2) * TC_G, t0, b);
+    }
+    // ---- per-token clock gradients (threads 0..127 own token tid; every thread joins the reductions) ----
+    float g_cs = 0.f, g_w = 0.f, ede = 0.f;
+    if (tid < 128) {
+      const float colS = colpart[tid] + colpart[128 + tid] + colpart[256 + tid] + colpart[384 + tid];
+      const float rS = rowpart[tid] + rowpart[128 + tid];
+      const float de = depart[tid] + depart[128 + tid];
+      const float ET = __expf(cs[127] - cs[tid]);
+      g_cs = rS - colS * wt + __expf(cs[tid]) * da_t - ET * wt * de;
+      g_w = colS + ET * de;
+      ede = ET * wt * de;
+    }
+    const float tail = cta_sum(ede, red) + __expf(cs[127]) * datot;
+    if (tid == 127) g_cs += tail;
+    if (tid < 128) gcs[tid] = g_cs;
+    __syncthreads();
+    // reverse prefix: gcs[i] <- sum_{k<=i} g_cs[127-k]; the argument is read before chunk_prefix's first barrier,
+    // the result written after it
+    chunk_prefix(tid < 128 ? gcs[127 - tid] : 0.f, gcs, wsum);
+    if (tid < 128) {
+      const int tt = 127 - tid;          // prefix index tid holds the reverse-inclusive sum for token tt
+      if (tt < Tv) {
+        const int64_t go = ((int64_t)b * a.L + t0 + tt) * H + h;
+        a.ddA[go] = gcs[tid];
+      }
+      if (tid < Tv) {
+        a.dw[gi] = g_w;
+        if (a.dwd) a.dwd[gi] = kdiag[tid];
+      }
+    }
+    if (a.dDg_part && tid < 64)
+      a.dDg_part[(((int64_t)b * a.nc + c) * H + h) * TC_G + tid] = ddpart[tid] + ddpart[64 + tid] + ddpart[128 + tid] + ddpart[192 + tid];
+    __syncthreads();
+  }
+
+  // ---- summed score gradient -> dC, dB ----
+  {
+#pragma unroll
+    for (int jj = 0; jj < 2; ++jj) {
+      const int j = wg * 2 + jj;
+      uint8_t* dstb = sMs + (j >> 1) * BLK;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        *reinterpret_cast<uint4*>(dstb + sw128_offset(t, (j & 1) * 4 + k)) =
+            make_uint4(pack_bf16(acc[jj][8 * k], acc[jj][8 * k + 1]), pack_bf16(acc[jj][8 * k + 2], acc[jj][8 * k + 3]),
+                       pack_bf16(acc[jj][8 * k + 4], acc[jj][8 * k + 5]), pack_bf16(acc[jj][8 * k + 6], acc[jj][8 * k + 7]));
+    }
+  }
+  tc_fence_before_sync();
+  fence_proxy_async();
+  __syncthreads();
+  if (tid == 0 && !*abort_flag) {
+    tc_fence_after_sync();
+    const uint32_t am = smem_u32(sMs), bb = smem_u32(sB), bc = smem_u32(sC);
+    const uint32_t id_c = idesc_bf16(128, 128, 0, 1), id_b = idesc_bf16(128, 128, 1, 1);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + 128, desc_k(am, ks), desc_mn(bb, ks), id_c, ks > 0 ? 1u : 0u);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + 0, desc_mn(am, ks), desc_mn(bc, ks), id_b, ks > 0 ? 1u : 0u);
+    umma_commit(&bar_cb);
+  }
+  if (wait_warp(&bar_cb, 1, abort_flag)) {
+    tc_fence_after_sync();
+#pragma unroll
+    for (int jj = 0; jj < 2; ++jj) {
+      const int col = wg * 64 + jj * 32;
+      uint32_t r1[32], r2[32];
+      tmem_ld32(tmem_addr(tbase, q * 32, 128 + col), r1);   // dC intra
+      tmem_ld32(tmem_addr(tbase, q * 32, 0 + col), r2);     // dB intra
+      tmem_ld_wait();
+      if (t < Tv) {
+        float4* dc = reinterpret_cast<float4*>(a.dChat + ((int64_t)b * a.L + t0 + t) * TC_N + col);
+        float4* db = reinterpret_cast<float4*>(a.dBhat + ((int64_t)b * a.L + t0 + t) * TC_N + col);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float4 x = dc[j], y = db[j];
+          x.x += __uint_as_float(r1[4 * j]); x.y += __uint_as_float(r1[4 * j + 1]); x.z += __uint_as_float(r1[4 * j + 2]); x.w += __uint_as_float(r1[4 * j + 3]);
+          y.x += __uint_as_float(r2[4 * j]); y.y += __uint_as_float(r2[4 * j + 1]); y.z += __uint_as_float(r2[4 * j + 2]); y.w += __uint_as_float(r2[4 * j + 3]);
+          dc[j] = x;
+          db[j] = y;
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag && a.status) atomicExch(a.status, 1);
+  if (warp == 0) tmem_dealloc(tbase, 512);
+}
+
 // ------------------------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------------------------
@@ -397,8 +953,7 @@ int tc_supported(const ScanArgs& a, int dtype, const char** why) {
   return *why == nullptr;
 }
 
-int tc_pick_chunk(int R, int O, int G, int N, int backward, int limit) {
-  if (backward) return 0;   // backward tiles not built yet: training takes the fp32 kernels
+int tc_pick_chunk(int R, int O, int G, int N, int, int limit) {
   return (R == 1 && O == 1 && G == TC_G && N == TC_N && limit >= TC_T) ? TC_T : 0;
 }
 
@@ -444,6 +999,25 @@ int tc_launch_chunk_out(const ScanArgs& a, cudaStream_t st) {
   return OK;
 }
 
-int tc_launch_chunk_grads(const ScanArgs&, cudaStream_t) { return fail(ERR_UNSUPPORTED, "precision 'io' backward tiles not built"); }
+constexpr int SMEM_GSTATE = 10 * BLK + 4096 + 1024;
+constexpr int SMEM_GSCORE = 11 * BLK + 8192 + 1024;
+
+int tc_launch_chunk_grads(const ScanArgs& a, cudaStream_t st) {
+  CUtensorMap tmB, tmC, tmU, tmDY;
+  int rc;
+  ORBIT_REQUIRE(aligned16(a.dy) && aligned16(a.du) && aligned16(a.dBhat) && aligned16(a.dChat), ERR_UNSUPPORTED,
+                "dy, du, dBhat, dChat must be 16-byte aligned");
+  if ((rc = map_rows(&tmB, a.Bhat, TC_N, a.b_ts, a.L, a.B)) != OK) return rc;
+  if ((rc = map_rows(&tmC, a.Chat, TC_N, a.c_ts, a.L, a.B)) != OK) return rc;
+  if ((rc = map_rows(&tmU, a.u, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
+  if ((rc = map_rows(&tmDY, a.dy, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
+  ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_grads_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GSTATE));
+  ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_grads_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GSCORE));
+  tc_chunk_grads_state_kernel<<<dim3(a.nc, a.B), TC_THREADS, SMEM_GSTATE, st>>>(tmC, tmU, tmDY, a);
+  ORBIT_CHECK_LAUNCH("tc_chunk_grads_state_kernel");
+  tc_chunk_grads_score_kernel<<<dim3(a.nc, a.B), TC_THREADS, SMEM_GSCORE, st>>>(tmB, tmC, tmU, tmDY, a);
+  ORBIT_CHECK_LAUNCH("tc_chunk_grads_score_kernel");
+  return OK;
+}
 
 }  // namespace orbit

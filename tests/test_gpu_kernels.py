@@ -223,3 +223,26 @@ def test_scan_tc_forward(case):
     ry, rS, _, _ = R.scan_fwd(geo, 128, 0, *args, c["S0"])
     assert rel(S_fin, rS) < 2e-3, ("S_fin", rel(S_fin, rS))
     assert rel(y, ry) < 1e-2, ("y", rel(y, ry))
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+def test_scan_tc_backward(case):
+    """Backward on the tensor-core tiles against the fp64 restatement on the same bf16-rounded inputs.  Every MMA
+    operand (scores, masks, scaled drives, states, summed score gradient) is rounded to bfloat16 (eps 3.9e-3) and
+    accumulated in fp32, so gradients are held to 2e-2 normwise; results must be bitwise reproducible."""
+    B, L, H, skip, trap, s0 = case
+    c = scan_case(B, L, H, 1, 1, 64, 128, torch.bfloat16, False, False, False, skip, trap, s0, seed=7)
+    geo = c["geo"]
+    args = (c["u"], c["Bhat"], None, c["Chat"], None, None, None, None, c["dA"], c["w"],
+            c["w"] if c["euler"] else c["wd"], c["Dg"])
+    y, S_fin, Sin, atot = ops.scan_fwd(geo, 128, _lib.PRECISION_IO, *args, c["S0"])
+    g = ops.scan_bwd(geo, 128, _lib.PRECISION_IO, *args, Sin, atot, c["dy"], c["dS_fin"], c["euler"], c["S0"] is not None)
+    ops.check_device_status()
+    rg = R.scan_bwd(geo, 128, 0, *args, None, None, c["dy"], c["dS_fin"], c["euler"], c["S0"] is not None, S0=c["S0"])
+    errs = {k: rel(g[k], v) for k, v in rg.items() if v is not None}
+    bad = {k: e for k, e in errs.items() if not e < 2e-2}
+    assert not bad, (bad, errs)
+    g2 = ops.scan_bwd(geo, 128, _lib.PRECISION_IO, *args, Sin, atot, c["dy"], c["dS_fin"], c["euler"], c["S0"] is not None)
+    for k, v in g.items():
+        if v is not None:
+            assert torch.equal(v, g2[k]), ("not reproducible", k)
