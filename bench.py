@@ -35,6 +35,11 @@ WORKLOADS = {
                  desc="SSD-MIMO SISO Mamba-2 preset (H=32, P=64, N=128) layer, d_model 1024, x [8,2048,1024]"),
     "cfg5": dict(B=4, L=4096, d_model=2048, kind="m2", chunk_acct=64,
                  desc="SSD-MIMO SISO Mamba-2 preset (H=64, P=64, N=128) layer, d_model 2048, x [4,4096,2048]"),
+    # reduced batches of the same layers, for profiler captures that must stay small
+    "cfg5s": dict(B=1, L=2048, d_model=2048, kind="m2", chunk_acct=64,
+                  desc="profiling case: the cfg5 layer at x [1,2048,2048]"),
+    "cfg3s": dict(B=1, L=1024, d_model=2048, kind="mimo4", chunk_acct=32,
+                  desc="profiling case: the cfg3 layer at x [1,1024,2048]"),
 }
 
 

@@ -132,6 +132,9 @@ typedef struct orbit_scan_args {
   float* dgamma_part; /* [B*nc, H, R, O, N]  out or NULL                                             */
   float* dDg_part;    /* [B*nc, H, G, R, O]  out or NULL                                             */
   int* status;        /* device int or NULL: set to 1 by a kernel whose bounded wait gave up         */
+  void* Sin16;        /* [B, nc, H, R, N, G] bfloat16 copy of Sin written by the forward pass, or NULL;
+                         required (with dS16 in backward) by precision "io", whose tiles read it by TMA */
+  void* dS16;         /* [B, nc, H, R, N, G] bfloat16 copy of dS written by the reverse pass, or NULL  */
 } orbit_scan_args;
 
 /* The scan runs as three chunk-parallel phases per direction (the decomposition of the reference's chunk-parallel

@@ -79,19 +79,29 @@ __global__ void __launch_bounds__(128) conv_fwd_kernel(const T* __restrict__ x, 
 #pragma unroll
   for (int j = 0; j < W - 1; ++j) load_xin<T, VEC, W>(ring[j + 1], x, xbs, xrs, window, b, t0 - (W - 1) + j, c0, C);
   const int t1 = min(t0 + CONV_TL, L);
-  for (int t = t0; t < t1; ++t) {
+  constexpr int NB = 8;   // rows fetched per batch: keeps NB 16-byte loads in flight per thread
+  for (int tb = t0; tb < t1; tb += NB) {
+    ChanVec<T, VEC> in[NB];
 #pragma unroll
-    for (int j = 0; j < W - 1; ++j) ring[j] = ring[j + 1];
-    ring[W - 1].load(x + b * xbs + (int64_t)t * xrs + c0);
-    ChanVec<T, VEC> o;
+    for (int k = 0; k < NB; ++k)
+      if (tb + k < t1) in[k].load(x + b * xbs + (int64_t)(tb + k) * xrs + c0);
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-      float acc = bs[i];
+    for (int k = 0; k < NB; ++k) {
+      if (tb + k < t1) {
 #pragma unroll
-      for (int j = 0; j < W; ++j) acc = fmaf(w[i][j], ring[j].v[i], acc);
-      o.v[i] = SILU ? siluf_(acc) : acc;
+        for (int j = 0; j < W - 1; ++j) ring[j] = ring[j + 1];
+        ring[W - 1] = in[k];
+        ChanVec<T, VEC> o;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          float acc = bs[i];
+#pragma unroll
+          for (int j = 0; j < W; ++j) acc = fmaf(w[i][j], ring[j].v[i], acc);
+          o.v[i] = SILU ? siluf_(acc) : acc;
+        }
+        o.store(y + ((int64_t)b * L + tb + k) * C + c0);
+      }
     }
-    o.store(y + ((int64_t)b * L + t) * C + c0);
   }
 }
 
@@ -132,50 +142,61 @@ __global__ void __launch_bounds__(128) conv_bwd_kernel(const T* __restrict__ x, 
   for (int j = 0; j < W - 1; ++j) load_xin<T, VEC, W>(ring[j + 1], x, xbs, xrs, window, b, t0 - (W - 1) + j, c0, C);
   const int t_own_end = min(t0 + CONV_TL, L);
   const int t_end = min(t0 + CONV_TL + W - 1, L + W - 1);   // walk far enough to emit dx of the last owned token
-  for (int t = t0; t < t_end; ++t) {
+  constexpr int NB = 4;   // rows of x and dy fetched per batch
+  for (int tb = t0; tb < t_end; tb += NB) {
+    ChanVec<T, VEC> xin[NB], gin[NB];
 #pragma unroll
-    for (int k = W - 1; k > 0; --k)
+    for (int k = 0; k < NB; ++k)
+      if (tb + k < t_end && tb + k < L) {
+        xin[k].load(x + b * xbs + (int64_t)(tb + k) * xrs + c0);
+        gin[k].load(dy + ((int64_t)b * L + tb + k) * C + c0);
+      }
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) dz[k][i] = dz[k - 1][i];
-    if (t < L) {
+    for (int kk = 0; kk < NB; ++kk) {
+      const int t = tb + kk;
+      if (t >= t_end) break;
 #pragma unroll
-      for (int j = 0; j < W - 1; ++j) ring[j] = ring[j + 1];
-      ring[W - 1].load(x + b * xbs + (int64_t)t * xrs + c0);
-      ChanVec<T, VEC> g;
-      g.load(dy + ((int64_t)b * L + t) * C + c0);
+      for (int k = W - 1; k > 0; --k)
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        float pre = bs[i];
+        for (int i = 0; i < VEC; ++i) dz[k][i] = dz[k - 1][i];
+      if (t < L) {
 #pragma unroll
-        for (int j = 0; j < W; ++j) pre = fmaf(w[i][j], ring[j].v[i], pre);
-        float d = SILU ? g.v[i] * silu_gradf_(pre) : g.v[i];
-        dz[0][i] = d;
-        if (t < t_own_end) {
-          dbacc[i] += d;
+        for (int j = 0; j < W - 1; ++j) ring[j] = ring[j + 1];
+        ring[W - 1] = xin[kk];
 #pragma unroll
-          for (int j = 0; j < W; ++j) dwacc[i][j] = fmaf(d, ring[j].v[i], dwacc[i][j]);
+        for (int i = 0; i < VEC; ++i) {
+          float pre = bs[i];
+#pragma unroll
+          for (int j = 0; j < W; ++j) pre = fmaf(w[i][j], ring[j].v[i], pre);
+          float d = SILU ? gin[kk].v[i] * silu_gradf_(pre) : gin[kk].v[i];
+          dz[0][i] = d;
+          if (t < t_own_end) {
+            dbacc[i] += d;
+#pragma unroll
+            for (int j = 0; j < W; ++j) dwacc[i][j] = fmaf(d, ring[j].v[i], dwacc[i][j]);
+          }
         }
+      } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) dz[0][i] = 0.f;
       }
-    } else {
+      // dx[t'] with t' = t-(W-1):  sum_j w[j] dz[t'+(W-1)-j] = sum_j w[j] dz_at(t-j)
+      const int tp = t - (W - 1);
+      if (tp >= t0 || (t0 == 0 && dwindow != nullptr)) {
+        ChanVec<T, VEC> o;
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) dz[0][i] = 0.f;
-    }
-    // dx[t'] with t' = t-(W-1):  sum_j w[j] dz[t'+(W-1)-j] = sum_j w[j] dz_at(t-j)
-    const int tp = t - (W - 1);
-    if (tp >= t0 || (t0 == 0 && dwindow != nullptr)) {
-      ChanVec<T, VEC> o;
+        for (int i = 0; i < VEC; ++i) {
+          float acc = 0.f;
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        float acc = 0.f;
+          for (int j = 0; j < W; ++j) acc = fmaf(w[i][j], dz[j][i], acc);
+          o.v[i] = acc;
+        }
+        if (tp >= t0) {
+          if (tp < t_own_end) o.store(dx + b * dxbs + (int64_t)tp * dxrs + c0);
+        } else if (tp >= -(W - 1)) {   // gradient of the carried window (slots 1..W-1)
 #pragma unroll
-        for (int j = 0; j < W; ++j) acc = fmaf(w[i][j], dz[j][i], acc);
-        o.v[i] = acc;
-      }
-      if (tp >= t0) {
-        if (tp < t_own_end) o.store(dx + b * dxbs + (int64_t)tp * dxrs + c0);
-      } else if (tp >= -(W - 1)) {   // gradient of the carried window (slots 1..W-1)
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) dwindow[((int64_t)b * C + c0 + i) * W + (W + tp)] = o.v[i];
+          for (int i = 0; i < VEC; ++i) dwindow[((int64_t)b * C + c0 + i) * W + (W + tp)] = o.v[i];
+        }
       }
     }
   }

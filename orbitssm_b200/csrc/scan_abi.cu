@@ -24,64 +24,90 @@ int fail(int code, const char* fmt, ...) {
 // ---- state pass ------------------------------------------------------------------------------------
 // Forward: buf[c] holds the chunk-local state Z[c] on entry and the state ENTERING chunk c on exit;
 //   S <- S0;  for c: z = buf[c]; buf[c] = S; S = atot[c] * S + z;   S_fin <- S
-// One thread per state element (n, g) of one (batch, head, sibling); the walk over chunks is the only serial part
-// of the scan (the reference's `_cp_pass`, src/orbit_ssm/kernels/ssd_mimo/chunkpar.py:19-25).
-__global__ void __launch_bounds__(256) state_pass_fwd_kernel(float* __restrict__ buf, const float* __restrict__ atot,
-                                                             const float* __restrict__ S0, float* __restrict__ S_fin,
-                                                             int nc, int HR, int NG) {
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+// One thread per VEC state elements of one (batch, head, sibling); the walk over chunks is the only serial part of
+// the scan (the reference's `_cp_pass`, src/orbit_ssm/kernels/ssd_mimo/chunkpar.py:19-25).  Loads are issued PASS_NB
+// chunks ahead of the dependent multiply-add chain, so the kernel runs at memory speed, not at load latency.
+// With REVERSE the walk runs from the last chunk down (the adjoint pass):
+//   D <- dS_fin;  for c = nc-1..0: g = buf[c]; buf[c] = D; D = atot[c] * D + g;   dS0 <- D
+// `copy16` (optional) receives a bfloat16 copy of what is written to buf (operand tiles of the tensor-core kernels).
+constexpr int PASS_NB = 8;
+
+template <int VEC, bool REVERSE>
+__global__ void __launch_bounds__(256) state_pass_kernel(float* __restrict__ buf, const float* __restrict__ atot,
+                                                         const float* __restrict__ s_in, float* __restrict__ s_out,
+                                                         __nv_bfloat16* __restrict__ copy16, int nc, int HR, int NG) {
+  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   const int hr = blockIdx.y, b = blockIdx.z;
   if (e >= NG) return;
-  float S = S0 ? S0[((int64_t)b * HR + hr) * NG + e] : 0.f;
-  float* p = buf + ((int64_t)b * nc * HR + hr) * NG + e;
+  float S[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) S[i] = s_in ? s_in[((int64_t)b * HR + hr) * NG + e + i] : 0.f;
+  const int64_t base = ((int64_t)b * nc * HR + hr) * NG + e;
   const float* ap = atot + (int64_t)b * nc * HR + hr;
   const int64_t cstride = (int64_t)HR * NG;
-  float z = p[0];
-  for (int c = 0; c < nc; ++c) {
-    float znext = (c + 1 < nc) ? p[(int64_t)(c + 1) * cstride] : 0.f;   // prefetch: breaks the load->fma chain
-    p[(int64_t)c * cstride] = S;
-    S = fmaf(ap[(int64_t)c * HR], S, z);
-    z = znext;
+  for (int c0 = 0; c0 < nc; c0 += PASS_NB) {
+    float z[PASS_NB][VEC], av[PASS_NB];
+#pragma unroll
+    for (int k = 0; k < PASS_NB; ++k) {
+      const int cc = REVERSE ? nc - 1 - (c0 + k) : c0 + k;
+      if (c0 + k < nc) {
+        av[k] = ap[(int64_t)cc * HR];
+        if constexpr (VEC == 4) {
+          float4 v = *reinterpret_cast<const float4*>(buf + base + cc * cstride);
+          z[k][0] = v.x; z[k][1] = v.y; z[k][2] = v.z; z[k][3] = v.w;
+        } else {
+          z[k][0] = buf[base + cc * cstride];
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < PASS_NB; ++k) {
+      const int cc = REVERSE ? nc - 1 - (c0 + k) : c0 + k;
+      if (c0 + k < nc) {
+        if constexpr (VEC == 4) {
+          *reinterpret_cast<float4*>(buf + base + cc * cstride) = make_float4(S[0], S[1], S[2], S[3]);
+          if (copy16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(S[0], S[1]), hi = __floats2bfloat162_rn(S[2], S[3]);
+            *reinterpret_cast<uint2*>(copy16 + base + cc * cstride) =
+                make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+          }
+        } else {
+          buf[base + cc * cstride] = S[0];
+          if (copy16) copy16[base + cc * cstride] = __float2bfloat16_rn(S[0]);
+        }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) S[i] = fmaf(av[k], S[i], z[k][i]);
+      }
+    }
   }
-  S_fin[((int64_t)b * HR + hr) * NG + e] = S;
+  if (s_out) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) s_out[((int64_t)b * HR + hr) * NG + e + i] = S[i];
+  }
 }
 
-// Reverse: buf[c] holds the adjoint chunk state Gs[c] on entry and the gradient of the state LEAVING chunk c on exit;
-//   D <- dS_fin;  for c = nc-1..0: g = buf[c]; buf[c] = D; D = atot[c] * D + g;   dS0 <- D
-__global__ void __launch_bounds__(256) state_pass_bwd_kernel(float* __restrict__ buf, const float* __restrict__ atot,
-                                                             const float* __restrict__ dS_fin,
-                                                             float* __restrict__ dS0, int nc, int HR, int NG) {
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
-  const int hr = blockIdx.y, b = blockIdx.z;
-  if (e >= NG) return;
-  float D = dS_fin ? dS_fin[((int64_t)b * HR + hr) * NG + e] : 0.f;
-  float* p = buf + ((int64_t)b * nc * HR + hr) * NG + e;
-  const float* ap = atot + (int64_t)b * nc * HR + hr;
-  const int64_t cstride = (int64_t)HR * NG;
-  float g = p[(int64_t)(nc - 1) * cstride];
-  for (int c = nc - 1; c >= 0; --c) {
-    float gnext = (c > 0) ? p[(int64_t)(c - 1) * cstride] : 0.f;
-    p[(int64_t)c * cstride] = D;
-    D = fmaf(ap[(int64_t)c * HR], D, g);
-    g = gnext;
+template <bool REVERSE>
+static int launch_state_pass(float* buf, const float* atot, const float* s_in, float* s_out, void* copy16,
+                             const ScanArgs& a, cudaStream_t st) {
+  const int NG = a.N * a.G, HR = a.H * a.R;
+  const bool vec = NG % 4 == 0 && aligned16(buf) && (copy16 == nullptr || (reinterpret_cast<uintptr_t>(copy16) & 7u) == 0);
+  if (vec) {
+    dim3 grid((NG / 4 + 255) / 256, HR, a.B);
+    state_pass_kernel<4, REVERSE><<<grid, 256, 0, st>>>(buf, atot, s_in, s_out, (__nv_bfloat16*)copy16, a.nc, HR, NG);
+  } else {
+    dim3 grid((NG + 255) / 256, HR, a.B);
+    state_pass_kernel<1, REVERSE><<<grid, 256, 0, st>>>(buf, atot, s_in, s_out, (__nv_bfloat16*)copy16, a.nc, HR, NG);
   }
-  if (dS0) dS0[((int64_t)b * HR + hr) * NG + e] = D;
+  ORBIT_CHECK_LAUNCH("state_pass_kernel");
+  return OK;
 }
 
 int launch_state_pass_fwd(const ScanArgs& a, const float* S0, float* S_fin, cudaStream_t st) {
-  const int NG = a.N * a.G, HR = a.H * a.R;
-  dim3 grid((NG + 255) / 256, HR, a.B);
-  state_pass_fwd_kernel<<<grid, 256, 0, st>>>(a.Sin, a.atot, S0, S_fin, a.nc, HR, NG);
-  ORBIT_CHECK_LAUNCH("state_pass_fwd_kernel");
-  return OK;
+  return launch_state_pass<false>(a.Sin, a.atot, S0, S_fin, a.Sin16, a, st);
 }
 
 int launch_state_pass_bwd(const ScanArgs& a, const float* dS_fin, float* dS0, cudaStream_t st) {
-  const int NG = a.N * a.G, HR = a.H * a.R;
-  dim3 grid((NG + 255) / 256, HR, a.B);
-  state_pass_bwd_kernel<<<grid, 256, 0, st>>>(a.dS, a.atot, dS_fin, dS0, a.nc, HR, NG);
-  ORBIT_CHECK_LAUNCH("state_pass_bwd_kernel");
-  return OK;
+  return launch_state_pass<true>(a.dS, a.atot, dS_fin, dS0, a.dS16, a, st);
 }
 
 // precision "ieee" phase launchers (scan_generic.cu)

@@ -150,13 +150,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_state_kernel(const __g
     tc_fence_before_sync();
   };
 
+  // clocks of the next head are fetched one head ahead (their latency hides behind the current head's work)
+  float d_n = 0.f, wt_n = 0.f;
+  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H;
+  if (tid < Tv) {
+    d_n = a.dA[ck];
+    wt_n = a.w[ck];
+  }
   for (int h = 0; h < H; ++h) {
     const int buf = h & 1;
-    float d = 0.f, wt = 0.f;
-    if (tid < Tv) {
-      int64_t i = ((int64_t)b * a.L + t0 + tid) * H + h;
-      d = a.dA[i];
-      wt = a.w[i];
+    const float d = d_n, wt = wt_n;
+    if (tid < Tv && h + 1 < H) {
+      d_n = a.dA[ck + h + 1];
+      wt_n = a.w[ck + h + 1];
     }
     chunk_prefix(d, cs, wsum);
     if (tid < 128) fv[tid] = mode == 0 ? __expf(cs[127] - cs[tid]) * wt : __expf(cs[tid]);
@@ -209,6 +215,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_state_kernel(const __g
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __grid_constant__ CUtensorMap tmB,
                                                                      const __grid_constant__ CUtensorMap tmC,
                                                                      const __grid_constant__ CUtensorMap tmU,
+                                                                     const __grid_constant__ CUtensorMap tmS,
                                                                      const ScanArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
@@ -216,8 +223,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
   uint8_t* sC = sm + 2 * BLK;            // 2 blocks
   uint8_t* sX = sm + 4 * BLK;            // 2 buffers
   uint8_t* sMs = sm + 6 * BLK;           // masked scores [128 t][128 s], 2 blocks
-  uint8_t* sS = sm + 8 * BLK;            // entering state [128 n][64 p] bf16, 1 block
-  float* cs = reinterpret_cast<float*>(sm + 9 * BLK);
+  uint8_t* sS = sm + 8 * BLK;            // entering state [128 n][64 p] bf16, 2 buffers
+  float* cs = reinterpret_cast<float*>(sm + 10 * BLK);
   float* wv = cs + 128;
   float* wdv = wv + 128;
   float* wsum = wdv + 128;
@@ -229,6 +236,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
   const int Tv = min(TC_T, a.L - t0);
   const int H = a.H;
   const int t = q * 32 + lane;           // this thread's token row in TMEM
+  const int64_t srow0 = ((int64_t)b * a.nc + c) * H;   // index of this chunk's first [128 x 64] state tile
 
   if (tid == 0) {
     mbar_init(&bar_map, 1);
@@ -254,8 +262,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
     tma_load_3d(sC, &tmC, &bar_map, 0, t0, b);
     tma_load_3d(sC + BLK, &tmC, &bar_map, 64, t0, b);
     for (int i = 0; i < 2 && i < H; ++i) {
-      mbar_expect_tx(&bar_x[i], BLK);
+      mbar_expect_tx(&bar_x[i], 2 * BLK);
       tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], i * TC_G, t0, b);
+      tma_load_2d(sS + i * BLK, &tmS, &bar_x[i], 0, (int)(srow0 + i) * TC_N);
     }
     if (wait_or_abort(&bar_map, 0, abort_flag)) {
       tc_fence_after_sync();
@@ -272,32 +281,26 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
   const uint32_t idesc_y = idesc_bf16(128, 64, 0, 1);
   __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(a.y);
 
+  float d_n = 0.f, wt_n = 0.f, wdt_n = 0.f;
+  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H;
+  if (tid < Tv) {
+    d_n = a.dA[ck];
+    wt_n = a.w[ck];
+    wdt_n = a.wd[ck];
+  }
   for (int h = 0; h < H; ++h) {
     const int buf = h & 1;
-    float d = 0.f, wt = 0.f, wdt = 0.f;
-    if (tid < Tv) {
-      int64_t i = ((int64_t)b * a.L + t0 + tid) * H + h;
-      d = a.dA[i];
-      wt = a.w[i];
-      wdt = a.wd[i];
+    const float d = d_n, wt = wt_n, wdt = wdt_n;
+    if (tid < Tv && h + 1 < H) {
+      d_n = a.dA[ck + h + 1];
+      wt_n = a.w[ck + h + 1];
+      wdt_n = a.wd[ck + h + 1];
     }
     if (tid < 128) {
       wv[tid] = wt;
       wdv[tid] = wdt;
     }
     chunk_prefix(d, cs, wsum);
-    // entering state fp32 [n][p] -> bf16 swizzled rows (coalesced 16-byte loads)
-    {
-      const float4* src = reinterpret_cast<const float4*>(a.Sin + (((int64_t)b * a.nc + c) * H + h) * (int64_t)(TC_N * TC_G));
-#pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int idx = it * TC_THREADS + tid;
-        const int n = idx >> 4, c4 = idx & 15;
-        float4 v = src[idx];
-        uint2 pk = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
-        *reinterpret_cast<uint2*>(sS + sw128_offset(n, c4 >> 1) + (c4 & 1) * 8) = pk;
-      }
-    }
     // masked scores: this thread owns row t, column slabs 2*wg and 2*wg+1 (32 columns each)
     if (cb_ok) {
       const float cst = cs[t], wdt_t = wdv[t];
@@ -336,7 +339,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
     if (tid == 0 && !*abort_flag) {
       if (wait_or_abort(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag)) {
         tc_fence_after_sync();
-        const uint32_t am = smem_u32(sMs), bx = smem_u32(sX + buf * BLK), ac = smem_u32(sC), bs = smem_u32(sS);
+        const uint32_t am = smem_u32(sMs), bx = smem_u32(sX + buf * BLK), ac = smem_u32(sC), bs = smem_u32(sS + buf * BLK);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_Y1, desc_k(am, ks), desc_mn(bx, ks), idesc_y, ks > 0 ? 1u : 0u);
 #pragma unroll
@@ -380,8 +383,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
     tc_fence_before_sync();
     __syncthreads();
     if (tid == 0 && !*abort_flag && h + 2 < H) {
-      mbar_expect_tx(&bar_x[buf], BLK);
+      mbar_expect_tx(&bar_x[buf], 2 * BLK);
       tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h + 2) * TC_G, t0, b);
+      tma_load_2d(sS + buf * BLK, &tmS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
     }
   }
   __syncthreads();
@@ -446,6 +450,8 @@ __device__ __forceinline__ float load_state_bf16(const float* __restrict__ src, 
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(const __grid_constant__ CUtensorMap tmC,
                                                                              const __grid_constant__ CUtensorMap tmU,
                                                                              const __grid_constant__ CUtensorMap tmDY,
+                                                                             const __grid_constant__ CUtensorMap tmS,
+                                                                             const __grid_constant__ CUtensorMap tmDS,
                                                                              const ScanArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
@@ -454,9 +460,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
   uint8_t* sDY = sm + 4 * BLK;           // 2 buffers
   uint8_t* sADY = sm + 6 * BLK;          // a_t * dy
   uint8_t* sEX = sm + 7 * BLK;           // e_s * u
-  uint8_t* sS = sm + 8 * BLK;            // Sin  bf16 [n][p]
-  uint8_t* sdS = sm + 9 * BLK;           // dSo  bf16 [n][p]
-  float* cs = reinterpret_cast<float*>(sm + 10 * BLK);
+  uint8_t* sS = sm + 8 * BLK;            // Sin  bf16 [n][p], 2 buffers
+  uint8_t* sdS = sm + 10 * BLK;          // dSo  bf16 [n][p], 2 buffers
+  float* cs = reinterpret_cast<float*>(sm + 12 * BLK);
   float* fa = cs + 128;                  // a_t
   float* fe = fa + 128;                  // e_s
   float* dapart = fe + 128;              // [2][128]
@@ -470,6 +476,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
   const int Tv = min(TC_T, a.L - t0);
   const int H = a.H;
   const int t = q * 32 + lane;
+  const int64_t srow0 = ((int64_t)b * a.nc + c) * H;
 
   if (tid == 0) {
     mbar_init(&bar_map, 1);
@@ -492,34 +499,54 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
     tma_load_3d(sC, &tmC, &bar_map, 0, t0, b);
     tma_load_3d(sC + BLK, &tmC, &bar_map, 64, t0, b);
     for (int i = 0; i < 2 && i < H; ++i) {
-      mbar_expect_tx(&bar_x[i], 2 * BLK);
+      mbar_expect_tx(&bar_x[i], 4 * BLK);
       tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], i * TC_G, t0, b);
       tma_load_3d(sDY + i * BLK, &tmDY, &bar_x[i], i * TC_G, t0, b);
+      tma_load_2d(sS + i * BLK, &tmS, &bar_x[i], 0, (int)(srow0 + i) * TC_N);
+      tma_load_2d(sdS + i * BLK, &tmDS, &bar_x[i], 0, (int)(srow0 + i) * TC_N);
     }
   }
   const uint32_t id_y = idesc_bf16(128, 64, 0, 1), id_acc = idesc_bf16(128, 128, 0, 0);
 
+  float d_n = 0.f, wt_n = 0.f;
+  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H;
+  if (tid < Tv) {
+    d_n = a.dA[ck];
+    wt_n = a.w[ck];
+  }
   for (int h = 0; h < H; ++h) {
     const int buf = h & 1;
-    float d = 0.f, wt = 0.f;
-    if (tid < Tv) {
-      int64_t i = ((int64_t)b * a.L + t0 + tid) * H + h;
-      d = a.dA[i];
-      wt = a.w[i];
+    const float d = d_n, wt = wt_n;
+    if (tid < Tv && h + 1 < H) {
+      d_n = a.dA[ck + h + 1];
+      wt_n = a.w[ck + h + 1];
     }
     chunk_prefix(d, cs, wsum);
     if (tid < 128) {
       fa[tid] = __expf(cs[tid]);
       fe[tid] = __expf(cs[127] - cs[tid]) * wt;
     }
-    const int64_t so = (((int64_t)b * a.nc + c) * H + h) * (int64_t)(TC_N * TC_G);
-    float part = load_state_bf16(a.Sin + so, a.dS + so, sS);
-    load_state_bf16(a.dS + so, nullptr, sdS);
-    const float datot = cta_sum(part, red);       // contains __syncthreads: fa/fe visible afterwards
-    if (tid == 0) a.dw[((int64_t)b * a.L + t0) * H + h] = datot;
+    __syncthreads();
+    float part = 0.f;
     if (wait_warp(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag)) {
       const int row = tid & 127, half = tid >> 7;
       const float f1 = fa[row], f2 = fe[row];
+      // <dSo, Sin> over this thread's share of the two state tiles (bf16 operands, fp32 sum)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t off = buf * BLK + sw128_offset(row, half * 4 + j);
+        uint4 p1 = *reinterpret_cast<const uint4*>(sS + off);
+        uint4 p2 = *reinterpret_cast<const uint4*>(sdS + off);
+        const uint32_t* q1 = reinterpret_cast<const uint32_t*>(&p1);
+        const uint32_t* q2 = reinterpret_cast<const uint32_t*>(&p2);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float a0, a1, b0, b1;
+          unpack_bf16(q1[k], a0, a1);
+          unpack_bf16(q2[k], b0, b1);
+          part = fmaf(a0, b0, fmaf(a1, b1, part));
+        }
+      }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const uint32_t off = sw128_offset(row, half * 4 + j);
@@ -540,12 +567,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
       }
     }
     fence_proxy_async();
-    __syncthreads();
+    const float datot = cta_sum(part, red);       // ends after a CTA barrier: the scaled tiles are complete
+    if (tid == 0) a.dw[((int64_t)b * a.L + t0) * H + h] = datot;
     if (tid == 0 && !*abort_flag) {
       bool ok = (h > 0) || wait_or_abort(&bar_map, 0, abort_flag);
       if (ok) {
         tc_fence_after_sync();
-        const uint32_t ac = smem_u32(sC), bs = smem_u32(sS), bd = smem_u32(sdS), aa = smem_u32(sADY), ae = smem_u32(sEX);
+        const uint32_t ac = smem_u32(sC), bs = smem_u32(sS + buf * BLK), bd = smem_u32(sdS + buf * BLK), aa = smem_u32(sADY),
+                       ae = smem_u32(sEX);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_YCU, desc_k(ac, ks), desc_mn(bs, ks), id_y, ks > 0 ? 1u : 0u);
 #pragma unroll
@@ -579,9 +608,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
     __syncthreads();
     if (tid < Tv) a.ddA[((int64_t)b * a.L + t0 + tid) * H + h] = dapart[tid] + dapart[128 + tid];
     if (tid == 0 && !*abort_flag && h + 2 < H) {
-      mbar_expect_tx(&bar_x[buf], 2 * BLK);
+      mbar_expect_tx(&bar_x[buf], 4 * BLK);
       tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h + 2) * TC_G, t0, b);
       tma_load_3d(sDY + buf * BLK, &tmDY, &bar_x[buf], (h + 2) * TC_G, t0, b);
+      tma_load_2d(sS + buf * BLK, &tmS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
+      tma_load_2d(sdS + buf * BLK, &tmDS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
     }
   }
   // accumulated cross terms -> global (fp32 rows of N)
@@ -623,6 +654,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
                                                                              const __grid_constant__ CUtensorMap tmC,
                                                                              const __grid_constant__ CUtensorMap tmU,
                                                                              const __grid_constant__ CUtensorMap tmDY,
+                                                                             const __grid_constant__ CUtensorMap tmDS,
                                                                              const ScanArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
@@ -631,8 +663,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
   uint8_t* sX = sm + 4 * BLK;            // 2 buffers
   uint8_t* sDY = sm + 6 * BLK;           // 2 buffers
   uint8_t* sMs = sm + 8 * BLK;           // masked scores, later the summed score gradient; 2 blocks
-  uint8_t* sdS = sm + 10 * BLK;          // dSo bf16 [n][p]
-  float* cs = reinterpret_cast<float*>(sm + 11 * BLK);
+  uint8_t* sdS = sm + 10 * BLK;          // dSo bf16 [n][p], 2 buffers
+  float* cs = reinterpret_cast<float*>(sm + 12 * BLK);
   float* wv = cs + 128;
   float* wdv = wv + 128;
   float* rowpart = wdv + 128;            // [2][128]
@@ -651,6 +683,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
   const int Tv = min(TC_T, a.L - t0);
   const int H = a.H;
   const int t = q * 32 + lane;
+  const int64_t srow0 = ((int64_t)b * a.nc + c) * H;
 
   if (tid == 0) {
     mbar_init(&bar_map, 1);
@@ -677,9 +710,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
     tma_load_3d(sC, &tmC, &bar_map, 0, t0, b);
     tma_load_3d(sC + BLK, &tmC, &bar_map, 64, t0, b);
     for (int i = 0; i < 2 && i < H; ++i) {
-      mbar_expect_tx(&bar_x[i], 2 * BLK);
+      mbar_expect_tx(&bar_x[i], 3 * BLK);
       tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], i * TC_G, t0, b);
       tma_load_3d(sDY + i * BLK, &tmDY, &bar_x[i], i * TC_G, t0, b);
+      tma_load_2d(sdS + i * BLK, &tmDS, &bar_x[i], 0, (int)(srow0 + i) * TC_N);
     }
     if (wait_or_abort(&bar_map, 0, abort_flag)) {
       tc_fence_after_sync();
@@ -702,31 +736,39 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
   __nv_bfloat16* duout = reinterpret_cast<__nv_bfloat16*>(a.du);
   const uint32_t id_dm = idesc_bf16(128, 128, 0, 0), id_x2 = idesc_bf16(128, 64, 0, 1), id_x1 = idesc_bf16(128, 64, 1, 1);
 
+  // clocks (and what part 1 left in ddA / dw) of the next head are fetched one head ahead
+  float d_n = 0.f, wt_n = 0.f, wdt_n = 0.f, da_n = 0.f, datot_n;
+  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H;
+  if (tid < Tv) {
+    d_n = a.dA[ck];
+    wt_n = a.w[ck];
+    wdt_n = a.wd[ck];
+    da_n = a.ddA[ck];
+  }
+  datot_n = a.dw[((int64_t)b * a.L + t0) * H];
   for (int h = 0; h < H; ++h) {
     const int buf = h & 1;
-    float d = 0.f, wt = 0.f, wdt = 0.f, da_t = 0.f;
-    int64_t gi = 0;
-    if (tid < Tv) {
-      gi = ((int64_t)b * a.L + t0 + tid) * H + h;
-      d = a.dA[gi];
-      wt = a.w[gi];
-      wdt = a.wd[gi];
-      da_t = a.ddA[gi];                                  // part 1 left da here
+    const float d = d_n, wt = wt_n, wdt = wdt_n, da_t = da_n, datot = datot_n;
+    const int64_t gi = ck + h;
+    if (h + 1 < H) {
+      if (tid < Tv) {
+        d_n = a.dA[ck + h + 1];
+        wt_n = a.w[ck + h + 1];
+        wdt_n = a.wd[ck + h + 1];
+        da_n = a.ddA[ck + h + 1];                        // part 1 left da here
+      }
+      datot_n = a.dw[((int64_t)b * a.L + t0) * H + h + 1];   // part 1 left datot here
     }
-    const float datot = a.dw[((int64_t)b * a.L + t0) * H + h];   // part 1 left datot here
     if (tid < 128) {
       wv[tid] = wt;
       wdv[tid] = wdt;
     }
     chunk_prefix(d, cs, wsum);
-    const int64_t so = (((int64_t)b * a.nc + c) * H + h) * (int64_t)(TC_N * TC_G);
-    load_state_bf16(a.dS + so, nullptr, sdS);
-    fence_proxy_async();
-    __syncthreads();
     if (tid == 0 && !*abort_flag) {
       if (wait_or_abort(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag)) {
         tc_fence_after_sync();
-        const uint32_t ady = smem_u32(sDY + buf * BLK), bx = smem_u32(sX + buf * BLK), ab = smem_u32(sB), bd = smem_u32(sdS);
+        const uint32_t ady = smem_u32(sDY + buf * BLK), bx = smem_u32(sX + buf * BLK), ab = smem_u32(sB),
+                       bd = smem_u32(sdS + buf * BLK);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) umma_bf16(tbase + TM_DM, desc_k(ady, ks), desc_k(bx, ks), id_dm, ks > 0 ? 1u : 0u);
 #pragma unroll
@@ -847,9 +889,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
     tc_fence_before_sync();
     __syncthreads();
     if (tid == 0 && !*abort_flag && h + 2 < H) {
-      mbar_expect_tx(&bar_x[buf], 2 * BLK);
+      mbar_expect_tx(&bar_x[buf], 3 * BLK);
       tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h + 2) * TC_G, t0, b);
       tma_load_3d(sDY + buf * BLK, &tmDY, &bar_x[buf], (h + 2) * TC_G, t0, b);
+      tma_load_2d(sdS + buf * BLK, &tmDS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
     }
     // ---- per-token clock gradients (threads 0..127 own token tid; every thread joins the reductions) ----
     float g_cs = 0.f, g_w = 0.f, ede = 0.f;
@@ -965,7 +1008,19 @@ static int map_rows(CUtensorMap* m, const void* base, int cols, int64_t token_st
 }
 
 constexpr int SMEM_STATE = 6 * BLK + 2048 + 1024;
-constexpr int SMEM_OUT = 9 * BLK + 2048 + 1024;
+constexpr int SMEM_OUT = 10 * BLK + 2048 + 1024;
+
+// [B*nc*H*128 rows][64 p] bfloat16 view of a state-tile buffer: one [128 x 64] box per (batch, chunk, head)
+static int map_state(CUtensorMap* m, const void* base, const ScanArgs& a) {
+  const uint64_t rows = (uint64_t)a.B * a.nc * a.H * TC_N;
+  ORBIT_REQUIRE(base != nullptr, ERR_BAD_ARG, "precision 'io' needs the bfloat16 state-tile buffers (Sin16 / dS16)");
+  ORBIT_REQUIRE(rows < (1ull << 31), ERR_UNSUPPORTED, "state-tile buffer of %llu rows exceeds the tensor-map coordinate range",
+                (unsigned long long)rows);
+  uint64_t dims[2] = {(uint64_t)TC_G, rows};
+  uint64_t str[1] = {(uint64_t)TC_G * 2};
+  uint32_t box[2] = {64, 128};
+  return make_tensor_map_bf16(m, base, 2, dims, str, box);
+}
 
 static int launch_state(const ScanArgs& a, int mode, cudaStream_t st) {
   CUtensorMap tmM, tmX;
@@ -988,23 +1043,26 @@ int tc_launch_chunk_state(const ScanArgs& a, cudaStream_t st) { return launch_st
 int tc_launch_chunk_dstate(const ScanArgs& a, cudaStream_t st) { return launch_state(a, 1, st); }
 
 int tc_launch_chunk_out(const ScanArgs& a, cudaStream_t st) {
-  CUtensorMap tmB, tmC, tmU;
+  CUtensorMap tmB, tmC, tmU, tmS;
   int rc;
   if ((rc = map_rows(&tmB, a.Bhat, TC_N, a.b_ts, a.L, a.B)) != OK) return rc;
   if ((rc = map_rows(&tmC, a.Chat, TC_N, a.c_ts, a.L, a.B)) != OK) return rc;
   if ((rc = map_rows(&tmU, a.u, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
+  if ((rc = map_state(&tmS, a.Sin16, a)) != OK) return rc;
   ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_OUT));
-  tc_chunk_out_kernel<<<dim3(a.nc, a.B), TC_THREADS, SMEM_OUT, st>>>(tmB, tmC, tmU, a);
+  tc_chunk_out_kernel<<<dim3(a.nc, a.B), TC_THREADS, SMEM_OUT, st>>>(tmB, tmC, tmU, tmS, a);
   ORBIT_CHECK_LAUNCH("tc_chunk_out_kernel");
   return OK;
 }
 
-constexpr int SMEM_GSTATE = 10 * BLK + 4096 + 1024;
-constexpr int SMEM_GSCORE = 11 * BLK + 8192 + 1024;
+constexpr int SMEM_GSTATE = 12 * BLK + 4096 + 1024;
+constexpr int SMEM_GSCORE = 12 * BLK + 8192 + 1024;
 
 int tc_launch_chunk_grads(const ScanArgs& a, cudaStream_t st) {
-  CUtensorMap tmB, tmC, tmU, tmDY;
+  CUtensorMap tmB, tmC, tmU, tmDY, tmS, tmDS;
   int rc;
+  if ((rc = map_state(&tmS, a.Sin16, a)) != OK) return rc;
+  if ((rc = map_state(&tmDS, a.dS16, a)) != OK) return rc;
   ORBIT_REQUIRE(aligned16(a.dy) && aligned16(a.du) && aligned16(a.dBhat) && aligned16(a.dChat), ERR_UNSUPPORTED,
                 "dy, du, dBhat, dChat must be 16-byte aligned");
   if ((rc = map_rows(&tmB, a.Bhat, TC_N, a.b_ts, a.L, a.B)) != OK) return rc;
@@ -1013,9 +1071,9 @@ int tc_launch_chunk_grads(const ScanArgs& a, cudaStream_t st) {
   if ((rc = map_rows(&tmDY, a.dy, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
   ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_grads_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GSTATE));
   ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_grads_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GSCORE));
-  tc_chunk_grads_state_kernel<<<dim3(a.nc, a.B), TC_THREADS, SMEM_GSTATE, st>>>(tmC, tmU, tmDY, a);
+  tc_chunk_grads_state_kernel<<<dim3(a.nc, a.B), TC_THREADS, SMEM_GSTATE, st>>>(tmC, tmU, tmDY, tmS, tmDS, a);
   ORBIT_CHECK_LAUNCH("tc_chunk_grads_state_kernel");
-  tc_chunk_grads_score_kernel<<<dim3(a.nc, a.B), TC_THREADS, SMEM_GSCORE, st>>>(tmB, tmC, tmU, tmDY, a);
+  tc_chunk_grads_score_kernel<<<dim3(a.nc, a.B), TC_THREADS, SMEM_GSCORE, st>>>(tmB, tmC, tmU, tmDY, tmDS, a);
   ORBIT_CHECK_LAUNCH("tc_chunk_grads_score_kernel");
   return OK;
 }

@@ -263,7 +263,8 @@ def _tok_stride(who, t, inner):
 
 
 def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0):
-    """Forward scan.  Returns (y [B, L, H*G*O], S_fin [B, H, R, N, G] fp32, Sin, atot)."""
+    """Forward scan.  Returns (y [B, L, H*G*O], S_fin [B, H, R, N, G] fp32, Sin, atot); with the tensor-core precision
+    `Sin` is the pair (Sin fp32, Sin16 bfloat16 tiles) that the backward needs."""
     _require_cuda("ssd_scan_fwd", u, Bhat, Chat, dA)
     B, L = u.shape[:2]
     H, R, O, G, N = geo.H, geo.R, geo.O, geo.G, geo.N
@@ -278,6 +279,10 @@ def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     S_fin = torch.empty((B, H, R, N, G), device=dev, dtype=torch.float32)
     keep = _fill_common(a, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg)
     a.Sin, a.atot, a.y = Sin.data_ptr(), atot.data_ptr(), y.data_ptr()
+    Sin16 = None
+    if precision == _lib.PRECISION_IO:
+        Sin16 = torch.empty((B, nc, H, R, N, G), device=dev, dtype=torch.bfloat16)
+        a.Sin16 = Sin16.data_ptr()
     lib = _lib.load()
     dt = _dtype_code("ssd_scan_fwd", u)
     for name, phase, sin, sout in (("scan_chunk_state", _lib.PHASE_CHUNK_STATE, None, None),
@@ -287,7 +292,7 @@ def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
             _lib.check(lib.orbit_ssd_scan_phase(C.byref(a), phase, _ptr(sin), _ptr(sout), dt, precision, _stream()),
                        "orbit_ssd_scan_phase(" + name + ")")
     del keep
-    return y, S_fin, Sin, atot
+    return y, S_fin, (Sin if Sin16 is None else (Sin, Sin16)), atot
 
 
 _STATUS = {}
@@ -333,6 +338,7 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     dgamma, dchi, ddA, dw, dwd, dDg, dS0."""
     B, L = u.shape[:2]
     H, R, O, G, N = geo.H, geo.R, geo.O, geo.G, geo.N
+    Sin, Sin16 = Sin if isinstance(Sin, tuple) else (Sin, None)
     nc = Sin.shape[1]
     dev = u.device
     f32 = dict(device=dev, dtype=torch.float32)
@@ -353,6 +359,10 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     pd = torch.empty((slots, H, G, R, O), **f32) if Dg is not None else None
     dS = torch.empty((B, nc, H, R, N, G), **f32)
     dS0 = torch.empty((B, H, R, N, G), **f32) if want_dS0 else None
+    dS16 = None
+    if precision == _lib.PRECISION_IO:
+        dS16 = torch.empty((B, nc, H, R, N, G), device=dev, dtype=torch.bfloat16)
+        a.Sin16, a.dS16 = Sin16.data_ptr(), dS16.data_ptr()
     a.Sin, a.atot, a.dS, a.dy, a.du = Sin.data_ptr(), atot.data_ptr(), dS.data_ptr(), dy.data_ptr(), out["du"].data_ptr()
     a.dBhat, a.dChat, a.ddA, a.dw = (out[k].data_ptr() for k in ("dBhat", "dChat", "ddA", "dw"))
     for k in ("dgBp", "dgCp", "dwd", "dchi"):
@@ -397,7 +407,8 @@ class SSDScanFn(torch.autograd.Function):
         u_, Bhat_, gBp_, Chat_, gCp_, beta_, gamma_, chi_, dA_, w_, wd_, Dg_, S0_ = tens
         y, S_fin, Sin, atot = scan_fwd(geo, T, precision, u_, Bhat_, gBp_, Chat_, gCp_, beta_, gamma_, chi_, dA_, w_,
                                        w_ if euler else wd_, Dg_, S0_)
-        ctx.save_for_backward(u_, Bhat_, gBp_, Chat_, gCp_, beta_, gamma_, chi_, dA_, w_, wd_, Dg_, Sin, atot)
+        Sin, Sin16 = Sin if isinstance(Sin, tuple) else (Sin, None)
+        ctx.save_for_backward(u_, Bhat_, gBp_, Chat_, gCp_, beta_, gamma_, chi_, dA_, w_, wd_, Dg_, Sin, atot, Sin16)
         ctx.cfg = (geo, T, precision, euler)
         ctx.in_dtypes = [None if t is None else t.dtype for t in (u, Bhat, gBp, Chat, gCp)]
         ctx.set_materialize_grads(False)
@@ -405,7 +416,9 @@ class SSDScanFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy, dS_fin):
-        u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, Sin, atot = ctx.saved_tensors
+        u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, Sin, atot, Sin16 = ctx.saved_tensors
+        if Sin16 is not None:
+            Sin = (Sin, Sin16)
         geo, T, precision, euler = ctx.cfg
         if dy is None:
             dy = torch.zeros((*u.shape[:2], geo.H * geo.G * geo.O), device=u.device, dtype=u.dtype)
