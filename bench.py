@@ -56,9 +56,8 @@ def init_params(layer, seed=0):
     g = torch.Generator().manual_seed(seed)
     with torch.no_grad():
         if hasattr(layer, "A_log"):
-            lo, hi = 0.0, float(torch.log(torch.tensor(16.0)))
-            layer.A_log.copy_((torch.rand(layer.A_log.shape, generator=g) * (hi - lo) + lo).log().clamp_min(-20.0)
-                              if False else torch.log(torch.exp(torch.rand(layer.A_log.shape, generator=g) * (hi - lo) + lo)))
+            hi = float(torch.log(torch.tensor(16.0)))
+            layer.A_log.copy_(torch.rand(layer.A_log.shape, generator=g) * hi)      # A = exp(A_log) in [1, 16], log-uniform
 
 
 def scan_flops(spec, B, L, T):

@@ -5,7 +5,8 @@ Host side mirrors the reference's config + execution interface (`SSDMimoConfig`,
 declared in ``include/orbit_b200.h``.
 """
 from .config import Execution, SSDMimoConfig, mamba2_config
+from .model import BlockStack, ResidualBlock
 from .ssd_mimo import SSDMimoSSM
 from .state import State
 
-__all__ = ["Execution", "SSDMimoConfig", "SSDMimoSSM", "State", "mamba2_config"]
+__all__ = ["BlockStack", "ResidualBlock", "Execution", "SSDMimoConfig", "SSDMimoSSM", "State", "mamba2_config"]

@@ -9,15 +9,36 @@
 // HBM-bound: forward 2*B*L*C*es bytes, backward 3*B*L*C*es (x, dy in; dx out).
 #include "common.cuh"
 #include "../../include/orbit_b200.h"
+#include <type_traits>
 
 namespace orbit {
 
 constexpr int CONV_MAXW = 4;
-constexpr int CONV_TL = 32;   // tokens per thread run
+constexpr int CONV_TL = 16;   // tokens per thread run
+
+// Raw in-flight copy of one channel vector (kept unconverted while the load is outstanding: 4 registers, not VEC).
+template <typename T, int VEC>
+struct RawVec {
+  using Store = typename std::conditional<VEC == 1, T, uint4>::type;
+  Store r;
+  __device__ __forceinline__ void load(const T* p) {
+    if constexpr (VEC == 1) r = *p;
+    else r = *reinterpret_cast<const uint4*>(p);
+  }
+};
 
 template <typename T, int VEC>
 struct ChanVec {
   float v[VEC];
+  __device__ __forceinline__ void from_raw(const RawVec<T, VEC>& raw) {
+    if constexpr (VEC == 1) {
+      v[0] = ldf(&raw.r);
+    } else {
+      const T* e = reinterpret_cast<const T*>(&raw.r);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[i] = ldf(e + i);
+    }
+  }
   __device__ __forceinline__ void load(const T* p) {
     if constexpr (VEC == 1) {
       v[0] = ldf(p);
@@ -81,7 +102,7 @@ __global__ void __launch_bounds__(128) conv_fwd_kernel(const T* __restrict__ x, 
   const int t1 = min(t0 + CONV_TL, L);
   constexpr int NB = 8;   // rows fetched per batch: keeps NB 16-byte loads in flight per thread
   for (int tb = t0; tb < t1; tb += NB) {
-    ChanVec<T, VEC> in[NB];
+    RawVec<T, VEC> in[NB];
 #pragma unroll
     for (int k = 0; k < NB; ++k)
       if (tb + k < t1) in[k].load(x + b * xbs + (int64_t)(tb + k) * xrs + c0);
@@ -90,7 +111,7 @@ __global__ void __launch_bounds__(128) conv_fwd_kernel(const T* __restrict__ x, 
       if (tb + k < t1) {
 #pragma unroll
         for (int j = 0; j < W - 1; ++j) ring[j] = ring[j + 1];
-        ring[W - 1] = in[k];
+        ring[W - 1].from_raw(in[k]);
         ChanVec<T, VEC> o;
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
@@ -144,7 +165,7 @@ __global__ void __launch_bounds__(128) conv_bwd_kernel(const T* __restrict__ x, 
   const int t_end = min(t0 + CONV_TL + W - 1, L + W - 1);   // walk far enough to emit dx of the last owned token
   constexpr int NB = 4;   // rows of x and dy fetched per batch
   for (int tb = t0; tb < t_end; tb += NB) {
-    ChanVec<T, VEC> xin[NB], gin[NB];
+    RawVec<T, VEC> xin[NB], gin[NB];
 #pragma unroll
     for (int k = 0; k < NB; ++k)
       if (tb + k < t_end && tb + k < L) {
@@ -162,13 +183,15 @@ __global__ void __launch_bounds__(128) conv_bwd_kernel(const T* __restrict__ x, 
       if (t < L) {
 #pragma unroll
         for (int j = 0; j < W - 1; ++j) ring[j] = ring[j + 1];
-        ring[W - 1] = xin[kk];
+        ring[W - 1].from_raw(xin[kk]);
+        ChanVec<T, VEC> gv;
+        gv.from_raw(gin[kk]);
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
           float pre = bs[i];
 #pragma unroll
           for (int j = 0; j < W; ++j) pre = fmaf(w[i][j], ring[j].v[i], pre);
-          float d = SILU ? gin[kk].v[i] * silu_gradf_(pre) : gin[kk].v[i];
+          float d = SILU ? gv.v[i] * silu_gradf_(pre) : gv.v[i];
           dz[0][i] = d;
           if (t < t_own_end) {
             dbacc[i] += d;

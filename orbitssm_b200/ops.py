@@ -83,6 +83,38 @@ def _f32(t):
 
 
 # ----------------------------------------------------------------------------------------------------
+#  fused projection output -> column views
+# ----------------------------------------------------------------------------------------------------
+class SplitColumnsFn(torch.autograd.Function):
+    """Column views of the fused projection output; the backward assembles the views' gradients into ONE buffer in a
+    single pass (autograd's own slice backward would zero-fill and add one full-width buffer per view)."""
+
+    @staticmethod
+    def forward(ctx, proj, *sizes):
+        ctx.sizes, ctx.shape = sizes, proj.shape
+        outs, o = [], 0
+        for w in sizes:
+            outs.append(proj[..., o:o + w])
+            o += w
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        ref = next(g for g in grads if g is not None)
+        out = torch.empty(ctx.shape, device=ref.device, dtype=ref.dtype)
+        o = 0
+        for w, g in zip(ctx.sizes, grads):
+            if g is None:
+                out[..., o:o + w].zero_()
+            else:
+                out[..., o:o + w].copy_(g)
+            o += w
+        if o < ctx.shape[-1]:
+            out[..., o:].zero_()
+        return (out,) + (None,) * len(ctx.sizes)
+
+
+# ----------------------------------------------------------------------------------------------------
 #  conv
 # ----------------------------------------------------------------------------------------------------
 def _rows(who, x):

@@ -327,9 +327,7 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
             xa = x.to(io)
             wcat, bcat = self._fused_weight(io)
             proj = F.linear(xa, wcat, bcat)                                    # [B, L, drive | z | slab | pad]
-            drive_raw = proj[..., :s.d_inner]
-            z = proj[..., s.d_inner:s.d_inner + self.d_gate]
-            slab = proj[..., s.d_inner + self.d_gate:s.d_inner + self.d_gate + s.tok_width]
+            drive_raw, z, slab = ops.SplitColumnsFn.apply(proj, s.d_inner, self.d_gate, s.tok_width)
             new = State()
             if self.conv1d is not None:
                 win = state["conv_state"] if state is not None else None

