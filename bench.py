@@ -35,6 +35,14 @@ WORKLOADS = {
                  desc="SSD-MIMO SISO Mamba-2 preset (H=32, P=64, N=128) layer, d_model 1024, x [8,2048,1024]"),
     "cfg5": dict(B=4, L=4096, d_model=2048, kind="m2", chunk_acct=64,
                  desc="SSD-MIMO SISO Mamba-2 preset (H=64, P=64, N=128) layer, d_model 2048, x [4,4096,2048]"),
+    # BASELINE config 5: (a) a 4-block BlockStack of the d2048 SISO layer, batch-sharded, 8 rows per GPU (B = 64 at
+    # 8 GPUs); (b) one layer, B = 1, L = 262144, context-parallel over the GPUs (strong scaling)
+    "cfg5a": dict(B=8, L=4096, d_model=2048, kind="m2", chunk_acct=64, blocks=4,
+                  desc="4-block BlockStack of the SSD-MIMO SISO Mamba-2 preset layer (H=64, P=64, N=128), d_model 2048, "
+                       "x [8,4096,2048] per GPU"),
+    "cfg5b": dict(B=1, L=262144, d_model=2048, kind="m2", chunk_acct=64, cp=True,
+                  desc="one SSD-MIMO SISO Mamba-2 preset layer, d_model 2048, B=1, L=262144 split over the GPUs "
+                       "(context parallel: chunk state all-gathered over NVLink)"),
     # reduced batches of the same layers, for profiler captures that must stay small
     "cfg5s": dict(B=1, L=2048, d_model=2048, kind="m2", chunk_acct=64,
                   desc="profiling case: the cfg5 layer at x [1,2048,2048]"),
@@ -191,10 +199,22 @@ def main():
 
     torch.manual_seed(0)
     cfg = make_config(wl)
-    layer = SSDMimoSSM(cfg, execution={"precision": "io"})
-    init_params(layer)
-    layer = layer.to(dev)
+    nblocks = wl.get("blocks", 1)
+    mixers = [SSDMimoSSM(cfg, execution={"precision": "io"}) for _ in range(nblocks)]
+    for m in mixers:
+        init_params(m)
+    mixer0 = mixers[0]
+    if nblocks > 1:
+        from orbitssm_b200 import BlockStack
+        layer = BlockStack.from_mixers(mixers, wl["d_model"]).to(dev)
+    else:
+        layer = mixer0.to(dev)
+    use_cp = bool(wl.get("cp")) and world > 1
+    if use_cp:
+        mixer0.set_context_parallel("world")
     B, L, dm = wl["B"], wl["L"], wl["d_model"]
+    if wl.get("cp"):
+        L = L // world                                                # this rank's segment of the sequence
     g = torch.Generator().manual_seed(100 + rank)                     # each rank: its own shard of the global batch
     x_host = torch.randn(B, L, dm, generator=g).to(torch.bfloat16).pin_memory()
     dy_host = torch.randn(B, L, dm, generator=g).to(torch.bfloat16).pin_memory()
@@ -204,11 +224,14 @@ def main():
     dy = dy_host.to(dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # > 126 MB L2
 
+    bf16_cast = nblocks > 1       # the stack's own norms follow the activations: run it under bf16 autocast
+
     def step():
         x.grad = None
         for p in layer.parameters():
             p.grad = None
-        y = layer(x)
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=bf16_cast):
+            y = layer(x)
         y.backward(dy)
         return y
 
@@ -217,7 +240,8 @@ def main():
         dyd = dy_host.to(dev, non_blocking=True)
         for p in layer.parameters():
             p.grad = None
-        y = layer(xd)
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=bf16_cast):
+            y = layer(xd)
         y.backward(dyd)
         y_host.copy_(y, non_blocking=True)
         dx_host.copy_(xd.grad, non_blocking=True)
@@ -277,10 +301,10 @@ def main():
             dist.destroy_process_group()
         return
 
-    tokens = B * L * world * args.steps
+    tokens = B * L * world * args.steps                              # cfg5b: L is the per-rank segment
     value = tokens / (total_ms * 1e-3)
     pk = peaks()
-    spec = layer.spec
+    spec = mixer0.spec
     fl = scan_flops(spec, B, L, wl["chunk_acct"])
     kern_ms = {k: statistics.mean(v) for k, v in per_kernel.items()}
     scan_names = [k for k in kern_ms if k in fl]
@@ -290,13 +314,15 @@ def main():
         ach = fl[dom] / (kern_ms[dom] * 1e-3) / 1e12
         roofline = dict(bound="tensor", kernel=dom, achieved=ach, peak=pk["tflops"], unit="TFLOP/s", frac=ach / pk["tflops"],
                         traffic=None, peak_source=pk["source"] + " (sustained bf16 GEMM)", ms_per_launch=kern_ms[dom],
-                        route=layer.last_route())
+                        route=mixer0.last_route())
     out = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong" if wl.get("cp") else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload + ": " + wl["desc"], "per_gpu_batch": B, "seq_len": L,
-                   "l2": "256 MB buffer written between timed steps", "parallelism": f"batch-sharded x{world}, no collective"},
+        "config": {"workload": args.workload + ": " + wl["desc"], "per_gpu_batch": B, "seq_len": L, "blocks": nblocks,
+                   "l2": "256 MB buffer written between timed steps",
+                   "parallelism": (f"context-parallel x{world}: all-gather of segment states + conv halos" if use_cp
+                                   else f"batch-sharded x{world}, no collective")},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * x_host.numel() * 2,
                 "d2h_bytes_per_step": 2 * y_host.numel() * 2},
         "gpu_launches": launches, "clocks": clocks, "roofline": roofline,

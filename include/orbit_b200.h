@@ -147,13 +147,18 @@ typedef struct orbit_scan_args {
  *   CHUNK_DSTATE    adjoint chunk states into a->dS
  *   STATE_PASS_BWD  reverse walk: a->dS becomes the gradient of the state leaving each chunk; state_in = dS_fin or
  *                   NULL, state_out = dS0 or NULL
- *   CHUNK_GRADS     every other gradient */
+ *   CHUNK_GRADS     every other gradient
+ *   STATE_PASS_DRY / STATE_PASS_BWD_DRY   the same walks without writing a->Sin / a->dS: only state_out is produced.
+ *                   Context parallelism uses them: a rank first learns what its segment contributes to the state
+ *                   (zero state_in), exchanges that with its peers, then runs the real walk from the true state. */
 #define ORBIT_PHASE_CHUNK_STATE 0
 #define ORBIT_PHASE_STATE_PASS 1
 #define ORBIT_PHASE_CHUNK_OUT 2
 #define ORBIT_PHASE_CHUNK_DSTATE 3
 #define ORBIT_PHASE_STATE_PASS_BWD 4
 #define ORBIT_PHASE_CHUNK_GRADS 5
+#define ORBIT_PHASE_STATE_PASS_DRY 6
+#define ORBIT_PHASE_STATE_PASS_BWD_DRY 7
 int orbit_ssd_scan_phase(const orbit_scan_args* a, int phase, const float* state_in, float* state_out, int dtype,
                          int precision, void* stream);
 

@@ -144,3 +144,120 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     return dict(du=g("u", u.dtype), dBhat=g("Bhat"), dgBp=g("gBp"), dChat=g("Chat"), dgCp=g("gCp"), dbeta=g("beta"),
                 dgamma=g("gamma"), dchi=g("chi"), ddA=g("dA"), dw=g("w"), dwd=g("wd"), dDg=g("Dg"),
                 dS0=g("S0") if want_dS0 else None)
+
+
+# ---- scan, phase by phase (the decomposition the kernels use; drives the context-parallel tests on CPU) -------
+def _chunk_local(geo, T, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, Sin):
+    """Chunk-local quantities with the entering states `Sin` [B, nc, H, R, N, G] taken as given:
+    y [B, L, H*G*O], Z [B, nc, H, R, N, G] (chunk-local state), tot [B, nc, H, R] (chunk decay)."""
+    Bsz, L = u.shape[:2]
+    H, R, Oo, G, N = geo.H, geo.R, geo.O, geo.G, geo.N
+    Bt = Bhat[:, :, None, None]
+    if gBp is not None:
+        Bt = gBp[:, :, None, :, None, :] * Bt
+    if beta is not None:
+        Bt = Bt + beta
+    Ct = Chat if gCp is None else Chat * gCp
+    Ct = Ct[:, :, None, None]
+    if gamma is not None:
+        Ct = Ct + gamma
+    Bt = Bt.expand(Bsz, L, H, R, R, N)
+    Cq = Ct.expand(Bsz, L, H, R, Oo, N)
+    if chi is not None:
+        Cq = Cq * chi[..., None, None]
+    uu = u.reshape(Bsz, L, H, G, R)
+    nc = -(-L // T)
+    pad = nc * T - L
+
+    def ch(t):
+        if pad:
+            t = torch.cat([t, t.new_zeros(Bsz, pad, *t.shape[2:])], dim=1)
+        return t.reshape(Bsz, nc, T, *t.shape[2:])
+
+    Bc, Cc, uc, dAc, wc, wdc = (ch(t) for t in (Bt, Cq, uu, dA, w, wd))
+    cs = torch.cumsum(dAc, dim=2)
+    tri = torch.ones(T, T, dtype=torch.bool, device=u.device).tril(-1)
+    diff = (cs[:, :, :, None] - cs[:, :, None, :]).masked_fill(~tri[None, None, :, :, None, None], float("-inf"))
+    Wm = torch.exp(diff) * wc[:, :, None, :]
+    eye = torch.eye(T, dtype=torch.bool, device=u.device)[None, None, :, :, None, None]
+    Wm = torch.where(eye, wdc[:, :, :, None], Wm)
+    score = torch.einsum("bcthron,bcshrqn->bchrotqs", Cc, Bc)
+    M = (score * Wm.permute(0, 1, 4, 5, 2, 3)[:, :, :, :, None, :, None, :]).sum(3)
+    y = torch.einsum("bchotqs,bcshgq->bcthgo", M, uc)
+    dend = torch.exp(cs[:, :, -1:, :, :] - cs) * wc
+    Z = torch.einsum("bcshrqn,bcshr,bcshgq->bchrng", Bc, dend, uc)
+    tot = cs[:, :, -1].exp()
+    y = y + torch.einsum("bcthron,bchrng,bcthr->bcthgo", Cc, Sin, cs.exp())
+    y = y.reshape(Bsz, nc * T, H, G, Oo)[:, :L]
+    if Dg is not None:
+        uw = uu if chi is None else uu * chi[..., None, :]
+        y = y + torch.einsum("blhgr,hgro->blhgo", uw, Dg)
+    return y.reshape(Bsz, L, H * G * Oo), Z, tot
+
+
+def run_phase(a, name, phase, state_in, state_out, dtype_code, precision, compute=torch.float64):
+    """Torch restatement of `orbit_ssd_scan_phase` on the tensors named in ``a.t`` (same in-place buffer protocol)."""
+    t = a.t
+    geo, T = t["geo"], a.T
+    names = ("u", "Bhat", "gBp", "Chat", "gCp", "beta", "gamma", "chi", "dA", "w", "wd", "Dg")
+    Sin, atot = t["Sin"], t["atot"]
+    nc = a.nc
+    if phase == 0:                                            # chunk_state
+        ins = [_f(t[k], compute) for k in names]
+        _, Z, tot = _chunk_local(geo, T, *ins, _f(Sin, compute)[:, :nc] * 0)
+        Sin[:, :nc].copy_(Z)
+        atot[:, :nc].copy_(tot)
+    elif phase in (1, 6):                                     # state pass (6: dry)
+        S = torch.zeros_like(Sin[:, 0]) if state_in is None else state_in.clone().to(Sin.dtype)
+        for c in range(nc):
+            z = Sin[:, c].clone()
+            if phase == 1:
+                Sin[:, c] = S
+            S = atot[:, c][..., None, None] * S + z
+        state_out.copy_(S)
+    elif phase == 2:                                          # chunk_out
+        ins = [_f(t[k], compute) for k in names]
+        y, _, _ = _chunk_local(geo, T, *ins, _f(Sin, compute)[:, :nc])
+        t["y"].copy_(y)
+    elif phase == 3:                                          # chunk_dstate
+        ins = [_f(t[k], compute) for k in names]
+        S = _f(Sin, compute)[:, :nc].requires_grad_(True)
+        with torch.enable_grad():
+            y, _, _ = _chunk_local(geo, T, *ins, S)
+            (g,) = torch.autograd.grad(y, S, _f(t["dy"], compute))
+        t["dS"][:, :nc].copy_(g)
+    elif phase in (4, 7):                                     # reverse pass (7: dry)
+        dS = t["dS"]
+        D = torch.zeros_like(dS[:, 0]) if state_in is None else state_in.clone().to(dS.dtype)
+        for c in range(nc - 1, -1, -1):
+            g = dS[:, c].clone()
+            if phase == 4:
+                dS[:, c] = D
+            D = atot[:, c][..., None, None] * D + g
+        if state_out is not None:
+            state_out.copy_(D)
+    elif phase == 5:                                          # chunk_grads
+        leaf = {k: (None if t[k] is None else _f(t[k], compute).requires_grad_(True)) for k in names}
+        with torch.enable_grad():
+            y, Z, tot = _chunk_local(geo, T, *[leaf[k] for k in names], _f(Sin, compute)[:, :nc])
+            Sout = tot[..., None, None] * _f(Sin, compute)[:, :nc] + Z
+            loss = (y * _f(t["dy"], compute)).sum() + (Sout * _f(t["dS"], compute)[:, :nc]).sum()
+            ins = [(k, v) for k, v in leaf.items() if v is not None]
+            gs = dict(zip([k for k, _ in ins], torch.autograd.grad(loss, [v for _, v in ins], allow_unused=True)))
+        out = t["out"]
+
+        def put(dst, key):
+            if dst is not None:
+                g = gs.get(key)
+                dst.copy_(torch.zeros_like(dst) if g is None else g.reshape(dst.shape))
+
+        put(out["du"], "u"); put(out["dBhat"], "Bhat"); put(out["dgBp"], "gBp"); put(out["dChat"], "Chat")
+        put(out["dgCp"], "gCp"); put(out["ddA"], "dA"); put(out["dw"], "w"); put(out["dchi"], "chi")
+        if t["dwd"] is not None:
+            put(t["dwd"], "wd")                               # own-token weight: a separate buffer even when w and wd coincide
+        for part, key in ((t["dbeta_part"], "beta"), (t["dgamma_part"], "gamma"), (t["dDg_part"], "Dg")):
+            if part is not None:
+                part.zero_()
+                part[0].copy_(gs[key])
+    else:
+        raise ValueError(f"unknown phase {phase}")

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "liborbit_b200.so")
 F32, BF16 = 0, 1
 PRECISION_IEEE, PRECISION_IO = 0, 1
 PHASE_CHUNK_STATE, PHASE_STATE_PASS, PHASE_CHUNK_OUT, PHASE_CHUNK_DSTATE, PHASE_STATE_PASS_BWD, PHASE_CHUNK_GRADS = range(6)
+PHASE_STATE_PASS_DRY, PHASE_STATE_PASS_BWD_DRY = 6, 7
 
 _STATUS_EXC = {1: ValueError, 2: NotImplementedError, 3: RuntimeError, 4: ValueError, 5: RuntimeError}
 

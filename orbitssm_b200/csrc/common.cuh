@@ -70,7 +70,25 @@ template <> struct Vec16<__nv_bfloat16> {
   }
 };
 
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoidf_(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+__device__ __forceinline__ float tanh_approx_(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// Activation arithmetic by IO dtype: fp32 activations keep ~2 ulp sigmoids; bfloat16 activations (eps 2^-8) take the
+// single-MUFU tanh form (abs error ~2^-11), which keeps the HBM-bound kernels from becoming issue-bound.
+template <typename T> struct Act {
+  static __device__ __forceinline__ float sigmoid(float x) { return sigmoidf_(x); }
+};
+template <> struct Act<__nv_bfloat16> {
+  static __device__ __forceinline__ float sigmoid(float x) { return fmaf(0.5f, tanh_approx_(0.5f * x), 0.5f); }
+};
+template <typename T> __device__ __forceinline__ float silu_t(float x) { return x * Act<T>::sigmoid(x); }
+template <typename T> __device__ __forceinline__ float silu_grad_t(float x) {
+  float s = Act<T>::sigmoid(x);
+  return s * fmaf(x, 1.f - s, 1.f);
+}
 __device__ __forceinline__ float siluf_(float x) { return x * sigmoidf_(x); }
 // d/dx silu(x) = s (1 + x (1 - s))
 __device__ __forceinline__ float silu_gradf_(float x) {

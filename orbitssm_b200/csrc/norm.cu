@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(NORM_THREADS) gate_norm_fwd_kernel(const T* __
         Vec16<T> b;
         b.load(z + row * zrs + c);
 #pragma unroll
-        for (int i = 0; i < V; ++i) g[k][i] = a.get(i) * siluf_(b.get(i));
+        for (int i = 0; i < V; ++i) g[k][i] = a.get(i) * silu_t<T>(b.get(i));
       } else {
 #pragma unroll
         for (int i = 0; i < V; ++i) g[k][i] = a.get(i);
@@ -93,8 +93,8 @@ __global__ void __launch_bounds__(NORM_THREADS) gate_norm_bwd_kernel(
 #pragma unroll
           for (int i = 0; i < V; ++i) {
             float zz = b.get(i);
-            sz[k][i] = siluf_(zz);
-            gz[k][i] = silu_gradf_(zz);
+            sz[k][i] = silu_t<T>(zz);
+            gz[k][i] = silu_grad_t<T>(zz);
           }
         } else {
 #pragma unroll
@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(NORM_THREADS) gate_norm_fwd_scalar_kernel(cons
   float ss = 0.f;
   for (int c = threadIdx.x; c < D; c += NORM_THREADS) {
     float g = ldf(y + row * D + c);
-    if (z) g *= siluf_(ldf(z + row * zrs + c));
+    if (z) g *= silu_t<T>(ldf(z + row * zrs + c));
     ss = fmaf(g, g, ss);
   }
   float rstd = 1.f;
@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(NORM_THREADS) gate_norm_fwd_scalar_kernel(cons
   }
   for (int c = threadIdx.x; c < D; c += NORM_THREADS) {
     float g = ldf(y + row * D + c);
-    if (z) g *= siluf_(ldf(z + row * zrs + c));
+    if (z) g *= silu_t<T>(ldf(z + row * zrs + c));
     stf(out + row * D + c, w ? g * rstd * w[c] : g);
   }
 }
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(NORM_THREADS) gate_norm_bwd_scalar_kernel(
     float dot = 0.f;
     if (w != nullptr) {
       for (int c = threadIdx.x; c < D; c += NORM_THREADS) {
-        float sz = z ? siluf_(ldf(z + row * zrs + c)) : 1.f;
+        float sz = z ? silu_t<T>(ldf(z + row * zrs + c)) : 1.f;
         float xh = ldf(y + row * D + c) * sz * rstd;
         float dd = ldf(dout + row * D + c);
         dot = fmaf(xh, dd * w[c], dot);
@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(NORM_THREADS) gate_norm_bwd_scalar_kernel(
     float m = w ? block_sum(dot, red) / (float)D : 0.f;
     for (int c = threadIdx.x; c < D; c += NORM_THREADS) {
       float zz = z ? ldf(z + row * zrs + c) : 0.f;
-      float sz = z ? siluf_(zz) : 1.f;
+      float sz = z ? silu_t<T>(zz) : 1.f;
       float yv = ldf(y + row * D + c);
       float dg = ldf(dout + row * D + c);
       if (w != nullptr) {
@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(NORM_THREADS) gate_norm_bwd_scalar_kernel(
         dg = rstd * (dg * w[c] - xh * m);
       }
       stf(dy + row * D + c, dg * sz);
-      if (z) stf(dz + row * dzrs + c, dg * yv * silu_gradf_(zz));
+      if (z) stf(dz + row * dzrs + c, dg * yv * silu_grad_t<T>(zz));
     }
     first = false;
   }

@@ -32,7 +32,7 @@ int fail(int code, const char* fmt, ...) {
 // `copy16` (optional) receives a bfloat16 copy of what is written to buf (operand tiles of the tensor-core kernels).
 constexpr int PASS_NB = 8;
 
-template <int VEC, bool REVERSE>
+template <int VEC, bool REVERSE, bool WRITE>
 __global__ void __launch_bounds__(256) state_pass_kernel(float* __restrict__ buf, const float* __restrict__ atot,
                                                          const float* __restrict__ s_in, float* __restrict__ s_out,
                                                          __nv_bfloat16* __restrict__ copy16, int nc, int HR, int NG) {
@@ -64,7 +64,9 @@ __global__ void __launch_bounds__(256) state_pass_kernel(float* __restrict__ buf
     for (int k = 0; k < PASS_NB; ++k) {
       const int cc = REVERSE ? nc - 1 - (c0 + k) : c0 + k;
       if (c0 + k < nc) {
-        if constexpr (VEC == 4) {
+        if constexpr (!WRITE) {
+          // dry walk: only the carried value is wanted (context-parallel exchange), the buffer keeps its content
+        } else if constexpr (VEC == 4) {
           *reinterpret_cast<float4*>(buf + base + cc * cstride) = make_float4(S[0], S[1], S[2], S[3]);
           if (copy16) {
             __nv_bfloat162 lo = __floats2bfloat162_rn(S[0], S[1]), hi = __floats2bfloat162_rn(S[2], S[3]);
@@ -86,28 +88,30 @@ __global__ void __launch_bounds__(256) state_pass_kernel(float* __restrict__ buf
   }
 }
 
-template <bool REVERSE>
+template <bool REVERSE, bool WRITE>
 static int launch_state_pass(float* buf, const float* atot, const float* s_in, float* s_out, void* copy16,
                              const ScanArgs& a, cudaStream_t st) {
   const int NG = a.N * a.G, HR = a.H * a.R;
   const bool vec = NG % 4 == 0 && aligned16(buf) && (copy16 == nullptr || (reinterpret_cast<uintptr_t>(copy16) & 7u) == 0);
   if (vec) {
     dim3 grid((NG / 4 + 255) / 256, HR, a.B);
-    state_pass_kernel<4, REVERSE><<<grid, 256, 0, st>>>(buf, atot, s_in, s_out, (__nv_bfloat16*)copy16, a.nc, HR, NG);
+    state_pass_kernel<4, REVERSE, WRITE><<<grid, 256, 0, st>>>(buf, atot, s_in, s_out, (__nv_bfloat16*)copy16, a.nc, HR, NG);
   } else {
     dim3 grid((NG + 255) / 256, HR, a.B);
-    state_pass_kernel<1, REVERSE><<<grid, 256, 0, st>>>(buf, atot, s_in, s_out, (__nv_bfloat16*)copy16, a.nc, HR, NG);
+    state_pass_kernel<1, REVERSE, WRITE><<<grid, 256, 0, st>>>(buf, atot, s_in, s_out, (__nv_bfloat16*)copy16, a.nc, HR, NG);
   }
   ORBIT_CHECK_LAUNCH("state_pass_kernel");
   return OK;
 }
 
-int launch_state_pass_fwd(const ScanArgs& a, const float* S0, float* S_fin, cudaStream_t st) {
-  return launch_state_pass<false>(a.Sin, a.atot, S0, S_fin, a.Sin16, a, st);
+int launch_state_pass_fwd(const ScanArgs& a, const float* S0, float* S_fin, cudaStream_t st, bool dry = false) {
+  if (dry) return launch_state_pass<false, false>(a.Sin, a.atot, S0, S_fin, nullptr, a, st);
+  return launch_state_pass<false, true>(a.Sin, a.atot, S0, S_fin, a.Sin16, a, st);
 }
 
-int launch_state_pass_bwd(const ScanArgs& a, const float* dS_fin, float* dS0, cudaStream_t st) {
-  return launch_state_pass<true>(a.dS, a.atot, dS_fin, dS0, a.dS16, a, st);
+int launch_state_pass_bwd(const ScanArgs& a, const float* dS_fin, float* dS0, cudaStream_t st, bool dry = false) {
+  if (dry) return launch_state_pass<true, false>(a.dS, a.atot, dS_fin, dS0, nullptr, a, st);
+  return launch_state_pass<true, true>(a.dS, a.atot, dS_fin, dS0, a.dS16, a, st);
 }
 
 // precision "ieee" phase launchers (scan_generic.cu)
@@ -165,7 +169,7 @@ extern "C" int orbit_ssd_scan_phase(const orbit_scan_args* a, int phase, const f
     const char* why = nullptr;
     if (!tc_supported(*a, dtype, &why)) return fail(ERR_UNSUPPORTED, "orbit_ssd_scan_phase: precision 'io' refused: %s", why);
   }
-  if (phase >= ORBIT_PHASE_CHUNK_DSTATE) {
+  if (phase >= ORBIT_PHASE_CHUNK_DSTATE && phase != ORBIT_PHASE_STATE_PASS_DRY) {
     ORBIT_REQUIRE(a->dy && a->dS, ERR_BAD_ARG, "orbit_ssd_scan_phase: null dy/dS");
   }
   switch (phase) {
@@ -178,6 +182,12 @@ extern "C" int orbit_ssd_scan_phase(const orbit_scan_args* a, int phase, const f
       return io ? tc_launch_chunk_out(*a, st) : gen_launch_chunk_out(*a, dtype, st);
     case ORBIT_PHASE_CHUNK_DSTATE: return io ? tc_launch_chunk_dstate(*a, st) : gen_launch_chunk_dstate(*a, dtype, st);
     case ORBIT_PHASE_STATE_PASS_BWD: return launch_state_pass_bwd(*a, state_in, state_out, st);
+    case ORBIT_PHASE_STATE_PASS_DRY:
+      ORBIT_REQUIRE(state_out != nullptr, ERR_BAD_ARG, "orbit_ssd_scan_phase: the dry pass needs state_out");
+      return launch_state_pass_fwd(*a, state_in, state_out, st, true);
+    case ORBIT_PHASE_STATE_PASS_BWD_DRY:
+      ORBIT_REQUIRE(state_out != nullptr, ERR_BAD_ARG, "orbit_ssd_scan_phase: the dry reverse pass needs state_out");
+      return launch_state_pass_bwd(*a, state_in, state_out, st, true);
     case ORBIT_PHASE_CHUNK_GRADS:
       ORBIT_REQUIRE(a->du && a->dBhat && a->dChat && a->ddA && a->dw, ERR_BAD_ARG,
                     "orbit_ssd_scan_phase: null du/dBhat/dChat/ddA/dw");

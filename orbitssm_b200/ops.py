@@ -294,9 +294,103 @@ def _tok_stride(who, t, inner):
     return t.stride(1)
 
 
-def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0):
+def run_phase(a, name, phase, state_in, state_out, dtype_code, precision):
+    """One phase of the scan through the C-ABI (`a` is the filled argument block; `a.t` names its tensors)."""
+    with _timed(name, 2 if (precision == _lib.PRECISION_IO and phase == _lib.PHASE_CHUNK_GRADS) else 1):
+        _lib.check(_lib.load().orbit_ssd_scan_phase(C.byref(a), phase, _ptr(state_in), _ptr(state_out), dtype_code, precision,
+                                                    _stream()), "orbit_ssd_scan_phase(" + name + ")")
+
+
+class ContextParallel:
+    """The ranks of one context-parallel group: consecutive ranks hold consecutive segments of the sequence.
+
+    The recurrence is linear in the state, so a rank needs from its predecessors only what their segments contribute:
+    F_j (final state of segment j started from zero) and A_j (its total log-decay per kernel head).  One all-gather of
+    (F, A) per direction replaces a serial hand-off:  S_r = sum_{j<r} exp(A_{j+1} + .. + A_{r-1}) F_j  (and the mirror
+    image for the state gradient in backward).  The same terms as the reference's in-GPU chunk-parallel pass
+    (src/orbit_ssm/kernels/ssd_mimo/chunkpar.py:19-25) and its state continuation contract
+    (src/orbit_ssm/ssm/ssd_mimo_torch.py:677-679).
+    """
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        self.dist, self.group = dist, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+
+    def all_gather(self, t):
+        outs = [torch.empty_like(t) for _ in range(self.world)]
+        self.dist.all_gather(outs, t.contiguous(), group=self.group)
+        return outs
+
+    def entering(self, F, logA):
+        """State entering this rank's segment (None on rank 0: the sequence starts from zero):
+        S_0 = 0,  S_{j+1} = exp(A_j) S_j + F_j."""
+        Fs, As = self.all_gather(F), self.all_gather(logA)
+        S = None
+        for j in range(self.rank):
+            S = Fs[j] if S is None else S * As[j].exp()[..., None, None] + Fs[j]
+        return S
+
+    def leaving_grad(self, E, logA, ext):
+        """Gradient of the state LEAVING this rank's segment.  E_j: what segment j's own outputs ask of its entering
+        state; ext_j: gradient a caller put on the state returned by rank j (None = zero).  With d_j the gradient of
+        the state leaving segment j:  d_{W-1} = ext_{W-1},  d_{j-1} = ext_{j-1} + E_j + exp(A_j) d_j."""
+        Es, As = self.all_gather(E), self.all_gather(logA)
+        Xs = self.all_gather(ext if ext is not None else torch.zeros_like(E))
+        d = Xs[self.world - 1]
+        for j in range(self.world - 1, self.rank, -1):
+            d = Xs[j - 1] + Es[j] + d * As[j].exp()[..., None, None]
+        return d
+
+
+class HaloFn(torch.autograd.Function):
+    """Conv window of a context-parallel segment: the last W-1 raw rows of the previous rank's segment (zeros on
+    rank 0), as a [B, C, W] window whose slot 0 is unused.  Backward returns the window's gradient to its owner."""
+
+    @staticmethod
+    def forward(ctx, tail, cp, W):
+        # tail [B, W-1, C]: this rank's own last rows, sent to the next rank
+        ctx.cp, ctx.W = cp, W
+        dist = cp.dist
+        tail = tail.contiguous()
+        recv = torch.zeros_like(tail)
+        reqs = []
+        if cp.rank + 1 < cp.world:
+            reqs.append(dist.P2POp(dist.isend, tail, dist.get_global_rank(cp.group, cp.rank + 1) if cp.group else cp.rank + 1,
+                                   group=cp.group))
+        if cp.rank > 0:
+            reqs.append(dist.P2POp(dist.irecv, recv, dist.get_global_rank(cp.group, cp.rank - 1) if cp.group else cp.rank - 1,
+                                   group=cp.group))
+        if reqs:
+            for r in dist.batch_isend_irecv(reqs):
+                r.wait()
+        win = tail.new_zeros(tail.shape[0], tail.shape[2], W)
+        win[..., 1:] = recv.transpose(1, 2)
+        return win
+
+    @staticmethod
+    def backward(ctx, dwin):
+        cp, W = ctx.cp, ctx.W
+        dist = cp.dist
+        send = dwin[..., 1:].transpose(1, 2).contiguous()          # gradient of the previous rank's last rows
+        recv = torch.zeros_like(send)
+        reqs = []
+        if cp.rank > 0:
+            reqs.append(dist.P2POp(dist.isend, send, dist.get_global_rank(cp.group, cp.rank - 1) if cp.group else cp.rank - 1,
+                                   group=cp.group))
+        if cp.rank + 1 < cp.world:
+            reqs.append(dist.P2POp(dist.irecv, recv, dist.get_global_rank(cp.group, cp.rank + 1) if cp.group else cp.rank + 1,
+                                   group=cp.group))
+        if reqs:
+            for r in dist.batch_isend_irecv(reqs):
+                r.wait()
+        return recv, None, None
+
+
+def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0, cp=None):
     """Forward scan.  Returns (y [B, L, H*G*O], S_fin [B, H, R, N, G] fp32, Sin, atot); with the tensor-core precision
-    `Sin` is the pair (Sin fp32, Sin16 bfloat16 tiles) that the backward needs."""
+    `Sin` is the pair (Sin fp32, Sin16 bfloat16 tiles) that the backward needs.  With `cp` (a `ContextParallel`) the
+    segment is continued from its predecessors' segments and S_fin is the state at this segment's end."""
     _require_cuda("ssd_scan_fwd", u, Bhat, Chat, dA)
     B, L = u.shape[:2]
     H, R, O, G, N = geo.H, geo.R, geo.O, geo.G, geo.N
@@ -310,19 +404,26 @@ def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     atot = torch.empty((B, nc, H, R), device=dev, dtype=torch.float32)
     S_fin = torch.empty((B, H, R, N, G), device=dev, dtype=torch.float32)
     keep = _fill_common(a, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg)
-    a.Sin, a.atot, a.y = Sin.data_ptr(), atot.data_ptr(), y.data_ptr()
+    if u.is_cuda:
+        a.Sin, a.atot, a.y = Sin.data_ptr(), atot.data_ptr(), y.data_ptr()
     Sin16 = None
     if precision == _lib.PRECISION_IO:
         Sin16 = torch.empty((B, nc, H, R, N, G), device=dev, dtype=torch.bfloat16)
         a.Sin16 = Sin16.data_ptr()
-    lib = _lib.load()
+    a.t = dict(geo=geo, u=u, Bhat=Bhat, gBp=gBp, Chat=Chat, gCp=gCp, beta=beta, gamma=gamma, chi=chi, dA=dA, w=w, wd=wd,
+               Dg=Dg, Sin=Sin, atot=atot, y=y)
     dt = _dtype_code("ssd_scan_fwd", u)
-    for name, phase, sin, sout in (("scan_chunk_state", _lib.PHASE_CHUNK_STATE, None, None),
-                                   ("scan_state_pass", _lib.PHASE_STATE_PASS, S0, S_fin),
-                                   ("scan_chunk_out", _lib.PHASE_CHUNK_OUT, None, None)):
-        with _timed(name, 1):
-            _lib.check(lib.orbit_ssd_scan_phase(C.byref(a), phase, _ptr(sin), _ptr(sout), dt, precision, _stream()),
-                       "orbit_ssd_scan_phase(" + name + ")")
+    run_phase(a, "scan_chunk_state", _lib.PHASE_CHUNK_STATE, None, None, dt, precision)
+    if cp is not None:
+        F = torch.empty_like(S_fin)
+        run_phase(a, "scan_state_pass_dry", _lib.PHASE_STATE_PASS_DRY, None, F, dt, precision)
+        if S0 is not None:
+            raise NotImplementedError("ssd_scan: an initial state together with context parallelism is not served")
+        S0 = cp.entering(F, dA.sum(1))
+        if S0 is not None:
+            S0 = S0.contiguous()
+    run_phase(a, "scan_state_pass", _lib.PHASE_STATE_PASS, S0, S_fin, dt, precision)
+    run_phase(a, "scan_chunk_out", _lib.PHASE_CHUNK_OUT, None, None, dt, precision)
     del keep
     return y, S_fin, (Sin if Sin16 is None else (Sin, Sin16)), atot
 
@@ -365,7 +466,7 @@ def _fill_common(a, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg):
 
 
 def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, Sin, atot, dy, dS_fin,
-             euler, want_dS0):
+             euler, want_dS0, cp=None):
     """Backward scan.  Returns a dict of gradients (fp32 unless noted): du (IO dtype), dBhat, dgBp, dChat, dgCp, dbeta,
     dgamma, dchi, ddA, dw, dwd, dDg, dS0."""
     B, L = u.shape[:2]
@@ -412,14 +513,17 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     if euler:
         dwd_tmp = torch.empty((B, L, H, R), **f32)
         a.dwd = dwd_tmp.data_ptr()
-    lib = _lib.load()
+    a.t = dict(geo=geo, u=u, Bhat=Bhat, gBp=gBp, Chat=Chat, gCp=gCp, beta=beta, gamma=gamma, chi=chi, dA=dA, w=w, wd=wd,
+               Dg=Dg, Sin=Sin, atot=atot, dy=dy, dS=dS, out=out, dbeta_part=pb, dgamma_part=pg, dDg_part=pd,
+               dwd=(dwd_tmp if euler else out["dwd"]))
     dt = _dtype_code("ssd_scan_bwd", u)
-    for name, phase, sin, sout in (("scan_chunk_dstate", _lib.PHASE_CHUNK_DSTATE, None, None),
-                                   ("scan_state_pass_bwd", _lib.PHASE_STATE_PASS_BWD, dS_fin, dS0),
-                                   ("scan_chunk_grads", _lib.PHASE_CHUNK_GRADS, None, None)):
-        with _timed(name, 1):
-            _lib.check(lib.orbit_ssd_scan_phase(C.byref(a), phase, _ptr(sin), _ptr(sout), dt, precision, _stream()),
-                       "orbit_ssd_scan_phase(" + name + ")")
+    run_phase(a, "scan_chunk_dstate", _lib.PHASE_CHUNK_DSTATE, None, None, dt, precision)
+    if cp is not None:
+        E = torch.empty((B, H, R, N, G), **f32)
+        run_phase(a, "scan_state_pass_bwd_dry", _lib.PHASE_STATE_PASS_BWD_DRY, None, E, dt, precision)
+        dS_fin = cp.leaving_grad(E, dA.sum(1), dS_fin).contiguous()
+    run_phase(a, "scan_state_pass_bwd", _lib.PHASE_STATE_PASS_BWD, dS_fin, dS0, dt, precision)
+    run_phase(a, "scan_chunk_grads", _lib.PHASE_CHUNK_GRADS, None, None, dt, precision)
     del keep
     if euler:
         out["dw"] = out["dw"] + dwd_tmp
@@ -434,14 +538,14 @@ class SSDScanFn(torch.autograd.Function):
     """The chunked SSD-MIMO scan as one autograd node (state in, state out, exact gradients through both)."""
 
     @staticmethod
-    def forward(ctx, geo, T, precision, euler, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0):
+    def forward(ctx, geo, T, precision, euler, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0, cp=None):
         tens = [None if t is None else t.detach() for t in (u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0)]
         u_, Bhat_, gBp_, Chat_, gCp_, beta_, gamma_, chi_, dA_, w_, wd_, Dg_, S0_ = tens
         y, S_fin, Sin, atot = scan_fwd(geo, T, precision, u_, Bhat_, gBp_, Chat_, gCp_, beta_, gamma_, chi_, dA_, w_,
-                                       w_ if euler else wd_, Dg_, S0_)
+                                       w_ if euler else wd_, Dg_, S0_, cp=cp)
         Sin, Sin16 = Sin if isinstance(Sin, tuple) else (Sin, None)
         ctx.save_for_backward(u_, Bhat_, gBp_, Chat_, gCp_, beta_, gamma_, chi_, dA_, w_, wd_, Dg_, Sin, atot, Sin16)
-        ctx.cfg = (geo, T, precision, euler)
+        ctx.cfg = (geo, T, precision, euler, cp)
         ctx.in_dtypes = [None if t is None else t.dtype for t in (u, Bhat, gBp, Chat, gCp)]
         ctx.set_materialize_grads(False)
         return y, S_fin
@@ -451,13 +555,13 @@ class SSDScanFn(torch.autograd.Function):
         u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, Sin, atot, Sin16 = ctx.saved_tensors
         if Sin16 is not None:
             Sin = (Sin, Sin16)
-        geo, T, precision, euler = ctx.cfg
+        geo, T, precision, euler, cp = ctx.cfg
         if dy is None:
             dy = torch.zeros((*u.shape[:2], geo.H * geo.G * geo.O), device=u.device, dtype=u.dtype)
         if dS_fin is not None:
             dS_fin = dS_fin.to(torch.float32).contiguous()
         g = scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, w if euler else wd, Dg, Sin,
-                     atot, dy, dS_fin, euler, ctx.needs_input_grad[16])
+                     atot, dy, dS_fin, euler, ctx.needs_input_grad[16], cp=cp)
         dts = ctx.in_dtypes
 
         def cast(t, dt):
@@ -465,4 +569,4 @@ class SSDScanFn(torch.autograd.Function):
 
         return (None, None, None, None, g["du"], cast(g["dBhat"], dts[1]), cast(g["dgBp"], dts[2]),
                 cast(g["dChat"], dts[3]), cast(g["dgCp"], dts[4]), g["dbeta"], g["dgamma"], g["dchi"], g["ddA"], g["dw"],
-                g["dwd"], g["dDg"], g["dS0"])
+                g["dwd"], g["dDg"], g["dS0"], None)

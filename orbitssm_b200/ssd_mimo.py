@@ -145,7 +145,20 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         self.backend, self.precision, self.chunk_size, self.kernel_options = "cuda", "io", "auto", {}
         self._route_note = None
         self._final_state = None
+        self._cp = None
         self.set_execution(as_execution(execution))
+
+    def set_context_parallel(self, group="world"):
+        """Split the SEQUENCE across the ranks of `group` (a torch.distributed process group; "world" = the default
+        group; None switches it off): rank r's `forward` then takes the r-th contiguous segment of the sequence and
+        returns that segment's outputs.  The chunk state and the conv windows cross ranks inside the layer, forward
+        and backward.  No counterpart in the reference, which is single-process; the exchanged quantities are those
+        of its State continuation contract (reference: src/orbit_ssm/ssm/ssd_mimo.py:4377-4400, 4565)."""
+        if group is None:
+            self._cp = None
+        else:
+            self._cp = ops.ContextParallel(None if group == "world" else group)
+        return self
 
     # -- execution (reference: ssd_mimo.py:4196-4244, execution.py:111-167) --------------------------------
     def _check_execution(self, ex: Execution) -> dict:
@@ -315,6 +328,15 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         s = self.spec
         Bsz, L, _ = x.shape
         H, G, R, O, N, P = s.H, s.G, s.R, s.O, s.N, s.P
+        cp = self._cp if (self._cp is not None and self._cp.world > 1) else None
+        if cp is not None:
+            if state is not None:
+                raise NotImplementedError("SSDMimoSSM: a carried `state` together with context parallelism is not served")
+            if s.use_trap:
+                raise NotImplementedError("SSDMimoSSM: context parallelism serves write_rule='euler' (the two-endpoint "
+                                          "write needs the neighbour's lag term)")
+            if L < max(s.d_conv, 1):
+                raise ValueError(f"SSDMimoSSM: a context-parallel segment needs at least d_conv={s.d_conv} tokens")
         if state is not None:
             state = self.resolve_state(state, batch_size=Bsz, device=x.device)
             if "write_prev" in state and not s.use_trap:
@@ -331,6 +353,8 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
             new = State()
             if self.conv1d is not None:
                 win = state["conv_state"] if state is not None else None
+                if cp is not None:
+                    win = ops.HaloFn.apply(drive_raw[:, L - (s.d_conv - 1):], cp, s.d_conv)
                 u = (ops.CausalConvFn.apply(drive_raw, self.conv1d.weight, self.conv1d.bias, win) if L > 0
                      else drive_raw.contiguous())
                 if want_state:
@@ -342,6 +366,8 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
             if self.bc_conv1d is not None:
                 bc_raw = slab[..., ob:oc + wc]                                 # B | C adjacent at the slab head
                 win = state["bc_conv_state"] if state is not None else None
+                if cp is not None:
+                    win = ops.HaloFn.apply(bc_raw[:, L - (s.d_conv - 1):], cp, s.d_conv)
                 bc = (ops.CausalConvFn.apply(bc_raw, self.bc_conv1d.conv.weight, self.bc_conv1d.conv.bias, win) if L > 0
                       else bc_raw.contiguous())
                 if want_state:
@@ -369,7 +395,7 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
                 precision, T = self._route(io, geo, torch.is_grad_enabled())
                 y, S_fin = ops.SSDScanFn.apply(geo, T, precision, not s.use_trap, u, law["Bhat"], law["gBp"], law["Chat"],
                                                law["gCp"], law["beta"], law["gamma"], law["chi"], law["dA"], law["w"],
-                                               law["wd"], law["Dg"], S0)
+                                               law["wd"], law["Dg"], S0, cp)
                 hidden = S_fin.permute(0, 1, 4, 2, 3).reshape(Bsz, H, P, N)
                 v_last = None
                 if want_state and s.use_trap:

@@ -1,0 +1,71 @@
+"""Context parallelism on CPU: two gloo ranks each take half of the sequence through the product's own protocol
+(halo exchange of the conv windows, all-gather of the segment states, the mirror image in backward); the kernels are
+replaced by their torch restatements.  Outputs and gradients must equal the single-rank golden vectors of the
+reference."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from conftest import load_golden
+        from orbitssm_b200 import ops
+        from orbitssm_b200.config import SSDMimoConfig
+        from orbitssm_b200.ssd_mimo import SSDMimoSSM
+        from oracle import abi_reference as R
+        for name in ("conv1d_fwd", "conv1d_bwd", "gate_norm_fwd", "gate_norm_bwd", "pick_chunk", "run_phase"):
+            setattr(ops, name, getattr(R, name))
+        ops.on_device = lambda t: True
+        ops._dtype_code = lambda who, t: 0
+        torch.set_num_threads(2)
+        rec = load_golden("cfg2_small")
+        layer = SSDMimoSSM(SSDMimoConfig(**rec["config"]))
+        layer.load_state_dict(rec["state_dict"])
+        layer.set_context_parallel("world")
+        L = rec["x"].shape[1]
+        cuts = [0, 41, L] if world == 2 else [0, 30, 61, L]
+        a, b = cuts[rank], cuts[rank + 1]
+        x = rec["x"][:, a:b].clone().requires_grad_(True)
+        y, st = layer(x, return_state=True)
+        loss = (y * rec["dy"][:, a:b]).sum()
+        if rank == world - 1:
+            loss = loss + (st["hidden_state"] * rec["gh"]).sum()
+        loss.backward()
+        want = rec["f64"]
+
+        def rel(p, q):
+            p, q = p.detach().double(), q.double()
+            return float((p - q).norm() / q.norm().clamp_min(1e-300))
+
+        errs = {"y": rel(y, want["y"][:, a:b]), "dx": rel(x.grad, want["grads"]["x"][:, a:b])}
+        if rank == world - 1:
+            errs["hidden"] = rel(st["hidden_state"], want["state"]["hidden_state"])
+        for n, p in layer.named_parameters():
+            g = p.grad.clone()
+            dist.all_reduce(g)                                   # parameter gradients add over the segments
+            errs["d" + n] = rel(g, want["grads"][n])
+        out[rank] = errs
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_two_segments_equal_the_whole_sequence(world):
+    port = 29500 + (os.getpid() % 2000) + world
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_worker, args=(world, port, out), nprocs=world, join=True)
+    for rank in range(world):
+        bad = {k: e for k, e in out[rank].items() if not e < 2e-4}
+        assert not bad, (rank, bad)
