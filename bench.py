@@ -4,9 +4,13 @@
 
 One "step" = y = layer(x); y.backward(dy) on one batch of synthetic input (x ~ N(0,1), fixed random dy; bf16
 activations over fp32 parameters).  Workloads (BASELINE.json `configs`):
-  cfg3  SSD-MIMO rank-4 layer, d_model 2048, x [4, 4096, 2048]   (the configuration the metric is quoted on; default)
+  cfg5a (default) BASELINE config 5a: 4-block BlockStack of the d_model-2048 SISO layer, batch-sharded, x [8, 4096, 2048]
+        per GPU: the d2048 bf16 configuration the metric is quoted on "at 1/2/4/8 B200" (weak scaling, no collective)
+  cfg5b BASELINE config 5b: one d_model-2048 layer, B = 1, L = 262144 split over the GPUs (context parallel, strong scaling)
+  cfg3  SSD-MIMO rank-4 layer, d_model 2048, x [4, 4096, 2048] (runs on the fp32 scan kernels: its tensor-core tiles are
+        not built yet); at N = 1 the default run also measures it briefly and reports it under "other_workloads"
   cfg2  Mamba-2 preset SISO layer, d_model 1024, x [8, 2048, 1024]
-  cfg5  Mamba-2 preset SISO layer, d_model 2048, x [4, 4096, 2048] (the per-GPU layer of the multi-GPU config)
+  cfg5  one layer of cfg5a at x [4, 4096, 2048]
 With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same per-GPU batch on its own shard of the
 batch: no collective on the data path, weak scaling.  Prints ONE JSON line on rank 0.
 """
@@ -170,6 +174,32 @@ def run_reference(args, wl, name):
         "e2e": {"value": tok, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
+def side_measure(wl, dev, steps=2, warmup=1):
+    """A short device-timed measurement of another workload (same step definition), reported beside the headline."""
+    from orbitssm_b200 import SSDMimoSSM
+    torch.manual_seed(0)
+    layer = SSDMimoSSM(make_config(wl), execution={"precision": "io"})
+    init_params(layer)
+    layer = layer.to(dev)
+    x = torch.randn(wl["B"], wl["L"], wl["d_model"], device=dev).to(torch.bfloat16).requires_grad_(True)
+    dy = torch.randn(wl["B"], wl["L"], wl["d_model"], device=dev).to(torch.bfloat16)
+    ms = []
+    for i in range(warmup + steps):
+        x.grad = None
+        for p in layer.parameters():
+            p.grad = None
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        layer(x).backward(dy)
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            ms.append(e0.elapsed_time(e1))
+    t = statistics.mean(ms)
+    return {"workload": wl["desc"], "value": wl["B"] * wl["L"] / (t * 1e-3), "unit": "tokens/s", "ms_per_step": t,
+            "route": layer.last_route(), "steps": steps, "warmup": warmup}
+
+
 # ----------------------------------------------------------------------------------------------------
 #  GPU arm
 # ----------------------------------------------------------------------------------------------------
@@ -178,7 +208,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg5a", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -194,6 +224,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ["NCCL_DEBUG"] = "WARN"          # keep NCCL's banner off stdout: the driver reads one JSON line
         dist.init_process_group("nccl", device_id=dev)
     args.warmup = max(args.warmup, 3)
 
@@ -335,6 +366,8 @@ def main():
         out["cpu_baseline"] = {"value": sB * sL / tcpu, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                                "sample": f"x [{sB},{sL},{dm}] fp32 of the same layer, median of 3 steps after 1 warm-up",
                                "host_cpus": os.cpu_count()}
+    if world == 1 and args.workload == "cfg5a" and not args.no_cpu_baseline:
+        out["other_workloads"] = {"cfg3": side_measure(WORKLOADS["cfg3"], dev)}
     print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
