@@ -143,9 +143,18 @@ def cpu_step_time(wl, sample_B, sample_L, steps, warmup):
     x = torch.randn(sample_B, sample_L, wl["d_model"], requires_grad=True)
     dy = torch.randn(sample_B, sample_L, wl["d_model"])
     times = []
+    blocks = wl.get("blocks", 1)
+
+    def rms(h):
+        return h * torch.rsqrt(h.square().mean(-1, keepdim=True) + 1e-5)
+
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        y = ssd_oracle.ssd_layer(spec, prm, x)
+        y = x
+        for _ in range(blocks):                       # a BlockStack: x + layer(norm(x)) per block, then the final norm
+            y = y + ssd_oracle.ssd_layer(spec, prm, rms(y)) if blocks > 1 else ssd_oracle.ssd_layer(spec, prm, y)
+        if blocks > 1:
+            y = rms(y)
         y.backward(dy)
         dt = time.perf_counter() - t0
         for v in prm.values():

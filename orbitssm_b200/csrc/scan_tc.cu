@@ -14,74 +14,12 @@
 #include "common.cuh"
 #include "scan_args.h"
 #include "tc_common.cuh"
+#include "tc_scan_common.cuh"
 
 namespace orbit {
 using namespace tc;
 
-constexpr int TC_T = 128, TC_N = 128, TC_G = 64, TC_THREADS = 256;
-constexpr uint32_t BLK = 128 * 128;   // bytes of one [128 x 64] bf16 block
-
-// ---- bounded waits with a CTA-wide abort flag --------------------------------------------------------------------
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if ((i & 63u) == 63u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
-// Same, with a warp-uniform answer: code under it may use .sync.aligned instructions and full-mask shuffles.
-__device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag) ? 1 : 0) != 0;
-}
-
-// Inclusive prefix over the 128 values held by threads 0..127 -> cs[0..127]; every thread of the CTA must call.
-__device__ __forceinline__ void chunk_prefix(float v, float* cs, float* wsum) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  float x = v;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    float y = __shfl_up_sync(0xffffffffu, x, o);
-    if (lane >= o) x += y;
-  }
-  if (warp < 4 && lane == 31) wsum[warp] = x;
-  __syncthreads();
-  if (warp < 4) {
-    float off = 0.f;
-    for (int w = 0; w < warp; ++w) off += wsum[w];
-    cs[tid] = x + off;
-  }
-  __syncthreads();
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-__device__ __forceinline__ void unpack_bf16(uint32_t w, float& lo, float& hi) {
-  __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&w);
-  lo = __low2float(v);
-  hi = __high2float(v);
-}
-
-__device__ __forceinline__ uint8_t* align1024(uint8_t* p) { return (uint8_t*)(((uintptr_t)p + 1023) & ~(uintptr_t)1023); }
-
-// K-major descriptor of k-step `ks` (16 columns) of a [128 x 128] operand stored as two 64-column blocks
-__device__ __forceinline__ uint64_t desc_k(uint32_t base, int ks) {
-  return smem_desc_sw128(base + (uint32_t)(ks >> 2) * BLK + (uint32_t)(ks & 3) * 32u, 16u, 1024u);
-}
-// MN-major descriptor of k-step `ks` (16 rows); 64-wide MN blocks are BLK bytes apart
-__device__ __forceinline__ uint64_t desc_mn(uint32_t base, int ks) { return smem_desc_sw128(base + (uint32_t)ks * 2048u, BLK, 1024u); }
+constexpr int TC_T = 128, TC_N = 128, TC_G = 64;
 
 // ------------------------------------------------------------------------------------------------------------------
 // chunk_state (mode 0):  Z[n,p] = sum_s B[s,n] e_s u[s,p],   e_s = exp(cs_T - cs_s) w_s          -> a.Sin, a.atot
@@ -391,34 +329,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
   __syncthreads();
   if (tid == 0 && *abort_flag && a.status) atomicExch(a.status, 1);
   if (warp == 0) tmem_dealloc(tbase, 256);
-}
-
-// Deterministic CTA-wide sum of one float per thread (fixed tree); result returned to every thread.  `red` >= 8 floats.
-__device__ __forceinline__ float cta_sum(float v, float* red) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float t = 0.f;
-#pragma unroll
-  for (int w = 0; w < TC_THREADS / 32; ++w) t += red[w];
-  return t;
-}
-
-// Column sums over the 32 rows held by a warp: in: v[i] = value of (row = lane, column i); out: v[0] = sum over the
-// warp's rows of column `lane` (butterfly reduce-scatter, 31 shuffles, fixed order).
-__device__ __forceinline__ void warp_colsum32(float (&v)[32], int lane) {
-#pragma unroll
-  for (int off = 16, n = 16; off >= 1; off >>= 1, n >>= 1) {
-    const bool upper = (lane & off) != 0;
-#pragma unroll
-    for (int k = 0; k < n; ++k) {
-      float send = upper ? v[k] : v[k + n];
-      float keep = upper ? v[k + n] : v[k];
-      v[k] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-    }
-  }
 }
 
 // fp32 [128 n][64 p] state tile -> bf16 swizzled block; optionally accumulates sum(src * other) per thread
@@ -986,8 +896,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
 // ------------------------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------------------------
+// rank-4 tiles (scan_tc_mimo.cu)
+bool mimo_tc_geometry(int R, int O, int G, int N);
+int mimo_tc_supported(const ScanArgs& a, int dtype, const char** why);
+int mimo_tc_launch_state(const ScanArgs& a, int mode, cudaStream_t stream);
+int mimo_tc_launch_out(const ScanArgs& a, cudaStream_t stream);
+
 int tc_supported(const ScanArgs& a, int dtype, const char** why) {
   *why = nullptr;
+  if (mimo_tc_geometry(a.R, a.O, a.G, a.N)) return mimo_tc_supported(a, dtype, why);
   if (dtype != BF16) *why = "activations must be bfloat16";
   else if (a.R != 1 || a.O != 1 || a.N != TC_N || a.G != TC_G) *why = "tensor-core tiles serve R = O = 1, N = 128, G = 64";
   else if (a.gBp || a.gCp || a.beta || a.gamma || a.chi) *why = "tensor-core tiles serve head-shared maps (no gates, per-head biases or sibling mix)";
@@ -996,7 +913,8 @@ int tc_supported(const ScanArgs& a, int dtype, const char** why) {
   return *why == nullptr;
 }
 
-int tc_pick_chunk(int R, int O, int G, int N, int, int limit) {
+int tc_pick_chunk(int R, int O, int G, int N, int backward, int limit) {
+  if (mimo_tc_geometry(R, O, G, N)) return (!backward && limit >= 32) ? 32 : 0;
   return (R == 1 && O == 1 && G == TC_G && N == TC_N && limit >= TC_T) ? TC_T : 0;
 }
 
@@ -1039,10 +957,15 @@ static int launch_state(const ScanArgs& a, int mode, cudaStream_t st) {
   return OK;
 }
 
-int tc_launch_chunk_state(const ScanArgs& a, cudaStream_t st) { return launch_state(a, 0, st); }
-int tc_launch_chunk_dstate(const ScanArgs& a, cudaStream_t st) { return launch_state(a, 1, st); }
+int tc_launch_chunk_state(const ScanArgs& a, cudaStream_t st) {
+  return mimo_tc_geometry(a.R, a.O, a.G, a.N) ? mimo_tc_launch_state(a, 0, st) : launch_state(a, 0, st);
+}
+int tc_launch_chunk_dstate(const ScanArgs& a, cudaStream_t st) {
+  return mimo_tc_geometry(a.R, a.O, a.G, a.N) ? mimo_tc_launch_state(a, 1, st) : launch_state(a, 1, st);
+}
 
 int tc_launch_chunk_out(const ScanArgs& a, cudaStream_t st) {
+  if (mimo_tc_geometry(a.R, a.O, a.G, a.N)) return mimo_tc_launch_out(a, st);
   CUtensorMap tmB, tmC, tmU, tmS;
   int rc;
   if ((rc = map_rows(&tmB, a.Bhat, TC_N, a.b_ts, a.L, a.B)) != OK) return rc;
@@ -1059,6 +982,7 @@ constexpr int SMEM_GSTATE = 12 * BLK + 4096 + 1024;
 constexpr int SMEM_GSCORE = 12 * BLK + 8192 + 1024;
 
 int tc_launch_chunk_grads(const ScanArgs& a, cudaStream_t st) {
+  if (mimo_tc_geometry(a.R, a.O, a.G, a.N)) return fail(ERR_UNSUPPORTED, "rank-4 tensor-core tiles have no chunk_grads kernel");
   CUtensorMap tmB, tmC, tmU, tmDY, tmS, tmDS;
   int rc;
   if ((rc = map_state(&tmS, a.Sin16, a)) != OK) return rc;

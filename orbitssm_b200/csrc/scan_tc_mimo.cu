@@ -1,0 +1,514 @@
+// SSD-MIMO chunked scan, precision "io", rank-4 tiles: R = O = 4, G = 16, N = 128, chunk T = 32, so that the
+// (output column, token) rows and the (input column, token) columns of a kernel head's score are both 128 wide:
+//   row  rho   = o * 32 + t        col  sigma = q * 32 + s
+//   Sc_{h,r}[rho, sigma] = Cbar_{h,r}[rho, :] . Bbar_{h,r}[sigma, :]        one 128 x 128 x 128 tcgen05 tile per kernel head
+//   Cbar_{h,r}[(o,t), :] = gCp[t,o,:] Chat[t,o,:] + gamma[h,r,o,:]          Bbar_{h,r}[(q,s), :] = gBp[s,r,:] Bhat[s,q,:] + beta[h,r,q,:]
+// One CTA owns one (batch, chunk).  The head-shared products (gate x map) are formed once; the per-kernel-head biases
+// enter either through the linearity of the contraction (state kernels: a rank-4 correction on the FP32 pipe) or when
+// the operand tile of that kernel head is written to shared memory (output kernel).
+// Thread t of the CTA works on TMEM lane (warp % 4) * 32 + lane: its row is (o or q = warp % 4, token = lane).
+#include "common.cuh"
+#include "scan_args.h"
+#include "tc_common.cuh"
+#include "tc_scan_common.cuh"
+
+namespace orbit {
+using namespace tc;
+
+constexpr int MM_T = 32, MM_N = 128, MM_G = 16, MM_R = 4;
+constexpr uint32_t XT_BLK = 16 * 128;      // one [16 x 64] bf16 K-block of a transposed drive tile (16 rows of 128 bytes)
+
+// K-major descriptor of k-step `ks` of a [16 rows x 128 cols] tile stored as two [16 x 64] blocks
+__device__ __forceinline__ uint64_t desc_k16(uint32_t base, int ks) {
+  return smem_desc_sw128(base + (uint32_t)(ks >> 2) * XT_BLK + (uint32_t)(ks & 3) * 32u, 16u, 1024u);
+}
+// byte offset of element (row g, column c) in such a tile
+__device__ __forceinline__ uint32_t xt_offset(int g, int c) {
+  return (uint32_t)(c >> 6) * XT_BLK + sw128_offset((uint32_t)g, (uint32_t)((c & 63) >> 3)) + (uint32_t)(c & 7) * 2u;
+}
+
+__device__ __forceinline__ float warp_prefix32(float x, int lane) {
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    float y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  return x;
+}
+
+__device__ __forceinline__ void tmem_ld16f(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  tmem_ld16(taddr, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// gate x map product of this thread's row (x in 0..3, token = lane) for the 64 state columns of its column half:
+// out[k] packs columns 2k, 2k+1 (relative to n0).  hat / gate rows are [B, L, X, N] with token strides; gate == null -> 1.
+__device__ __forceinline__ void gated_row(const __nv_bfloat16* hat, int64_t hat_ts, const __nv_bfloat16* gate, int64_t gate_ts,
+                                          int64_t tok, int xh, int xg, int n0, bool valid, uint32_t (&out)[32]) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 hv = make_uint4(0, 0, 0, 0), gv;
+    if (valid) hv = *reinterpret_cast<const uint4*>(hat + tok * hat_ts + xh * MM_N + n0 + c * 8);
+    const uint32_t* hp = reinterpret_cast<const uint32_t*>(&hv);
+    if (gate != nullptr && valid) {
+      gv = *reinterpret_cast<const uint4*>(gate + tok * gate_ts + xg * MM_N + n0 + c * 8);
+      const uint32_t* gp = reinterpret_cast<const uint32_t*>(&gv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float a0, a1, b0, b1;
+        unpack_bf16(hp[k], a0, a1);
+        unpack_bf16(gp[k], b0, b1);
+        out[c * 4 + k] = pack_bf16(a0 * b0, a1 * b1);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) out[c * 4 + k] = hp[k];
+    }
+  }
+}
+
+// write this thread's 64 packed columns (+ optional fp32 bias row) into block `wg` of a [128 x 128] operand tile
+__device__ __forceinline__ void store_row(uint8_t* tile, int row, int wg, const uint32_t (&v)[32], const float* bias) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (bias != nullptr) {
+        float a0, a1;
+        unpack_bf16(v[c * 4 + k], a0, a1);
+        w[k] = pack_bf16(a0 + bias[c * 8 + 2 * k], a1 + bias[c * 8 + 2 * k + 1]);
+      } else {
+        w[k] = v[c * 4 + k];
+      }
+    }
+    *reinterpret_cast<uint4*>(tile + wg * BLK + sw128_offset(row, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// Transposed, row-scaled drive tile of one head: XT[g][x * 32 + s] = f[s] * src[b, t0 + s, (h * 16 + g) * 4 + x]
+// (x = input column q for the drive u, output column o for dy).  One 16-byte load per thread.
+__device__ __forceinline__ void build_xt(uint8_t* xt, const __nv_bfloat16* src, int64_t row_stride, int64_t tok0, int h, int Tv,
+                                         const float* f) {
+  const int s = threadIdx.x >> 3, v = threadIdx.x & 7;
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  if (s < Tv) raw = *reinterpret_cast<const uint4*>(src + (tok0 + s) * row_stride + h * 64 + v * 8);
+  const float fs = f ? f[s] : 1.f;
+  const uint32_t* rp = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float a0, a1;
+    unpack_bf16(rp[k], a0, a1);
+    const int ch0 = v * 8 + 2 * k;                      // channel = g * 4 + x
+    *reinterpret_cast<__nv_bfloat16*>(xt + xt_offset(ch0 >> 2, (ch0 & 3) * 32 + s)) = __float2bfloat16_rn(a0 * fs);
+    *reinterpret_cast<__nv_bfloat16*>(xt + xt_offset((ch0 + 1) >> 2, ((ch0 + 1) & 3) * 32 + s)) = __float2bfloat16_rn(a1 * fs);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// chunk_state  (mode 0):  Z_{h,r}[n,g]  = sum_{q,s} e_r[s] Bbar_{h,r}[(q,s),n] u[s,g,q]            -> a.Sin, a.atot
+// chunk_dstate (mode 1):  Gs_{h,r}[n,g] = sum_{o,t} chi_r(t) a_r(t) Cbar_{h,r}[(o,t),n] dy[t,g,o]   -> a.dS
+// by linearity:  (gate x map)^T (f o X)  on the tensor cores  +  bias^T (sum_s f[s] X[s])  on the FP32 pipe.
+// ------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_state_kernel(const ScanArgs a, const int mode) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = align1024(smem_raw);
+  uint8_t* sMap = sm;                            // gate x map tile [128 rows][128 n], 2 blocks
+  uint8_t* sXT = sm + 2 * BLK;                   // scaled transposed drive, 2 buffers of 2 * XT_BLK
+  float* fvec = reinterpret_cast<float*>(sm + 2 * BLK + 4 * XT_BLK);   // [32]
+  float* xbar = fvec + 32;                       // [2][64]  sum_s f[s] X[s]  as [x][g]
+  __shared__ uint64_t bar_mma[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, qw = warp & 3, wg = warp >> 2;
+  const int c = blockIdx.x, b = blockIdx.y, t0 = c * MM_T;
+  const int Tv = min(MM_T, a.L - t0);
+  const int H = a.H;
+  const int row = qw * 32 + lane;
+  const int64_t tok0 = (int64_t)b * a.L + t0;
+
+  if (tid == 0) {
+    mbar_init(&bar_mma[0], 1);
+    mbar_init(&bar_mma[1], 1);
+    mbar_fence_init();
+    s_abort = 0;
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 32);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_slot;
+  volatile int* abort_flag = &s_abort;
+  const __nv_bfloat16* hat = reinterpret_cast<const __nv_bfloat16*>(mode == 0 ? a.Bhat : a.Chat);
+  const __nv_bfloat16* gate = reinterpret_cast<const __nv_bfloat16*>(mode == 0 ? a.gBp : a.gCp);
+  const int64_t hat_ts = mode == 0 ? a.b_ts : a.c_ts, gate_ts = mode == 0 ? a.gb_ts : a.gc_ts;
+  const __nv_bfloat16* xsrc = reinterpret_cast<const __nv_bfloat16*>(mode == 0 ? a.u : a.dy);
+  const float* bias = mode == 0 ? a.beta : a.gamma;
+  float* outbuf = mode == 0 ? a.Sin : a.dS;
+  const uint32_t idesc = idesc_bf16(128, 16, 1, 0);
+  uint32_t n_issued[2] = {0, 0};                 // per accumulator: MMAs committed so far (parity of the wait)
+
+  // epilogue of kernel head `itp` (warps 0..3: one state row n per thread): bias correction and store
+  auto epilogue = [&](int itp) {
+    const int hb = itp & 1, hh = itp % H, rr = itp / H;
+    const bool ok = wait_warp(&bar_mma[hb], n_issued[hb] & 1u, abort_flag);
+    n_issued[hb]++;
+    if (ok && wg == 0) {
+      tc_fence_after_sync();
+      float z[16];
+      tmem_ld16f(tmem_addr(tbase, qw * 32, hb * 16), z);
+      if (bias != nullptr) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const float bv = bias[(((int64_t)hh * MM_R + rr) * 4 + x) * MM_N + row];
+#pragma unroll
+          for (int g = 0; g < 16; ++g) z[g] = fmaf(bv, xbar[hb * 64 + x * 16 + g], z[g]);
+        }
+      }
+      float* dst = outbuf + (((((int64_t)b * a.nc + c) * H + hh) * MM_R + rr) * MM_N + row) * MM_G;
+#pragma unroll
+      for (int g = 0; g < 16; g += 4) *reinterpret_cast<float4*>(dst + g) = make_float4(z[g], z[g + 1], z[g + 2], z[g + 3]);
+    }
+    tc_fence_before_sync();
+  };
+  for (int r = 0; r < MM_R; ++r) {
+    if (mode == 0 || r == 0) {
+      uint32_t v[32];
+      // state: row (q, s) takes gate column r;  dstate: row (o, t) takes gate row o (independent of r)
+      gated_row(hat, hat_ts, gate, gate_ts, tok0 + lane, qw, mode == 0 ? r : qw, wg * 64, lane < Tv, v);
+      store_row(sMap, row, wg, v, nullptr);
+    }
+    for (int h = 0; h < H; ++h) {
+      const int it = r * H + h, buf = it & 1;
+      // clocks of kernel head (h, r): every warp forms the 32-token prefix on its own
+      float d = 0.f, wt = 0.f, ch = 1.f;
+      if (lane < Tv) {
+        const int64_t i = ((tok0 + lane) * H + h) * MM_R + r;
+        d = a.dA[i];
+        wt = a.w[i];
+        if (a.chi) ch = a.chi[i];
+      }
+      const float cs = warp_prefix32(d, lane);
+      const float tot = __shfl_sync(0xffffffffu, cs, 31);
+      if (warp == 0) {
+        fvec[lane] = mode == 0 ? __expf(tot - cs) * wt : ch * __expf(cs);
+        if (lane == 0 && mode == 0) a.atot[(((int64_t)b * a.nc + c) * H + h) * MM_R + r] = __expf(tot);
+      }
+      __syncthreads();
+      build_xt(sXT + buf * 2 * XT_BLK, xsrc, (int64_t)H * 64, tok0, h, Tv, fvec);
+      fence_proxy_async();
+      __syncthreads();
+      if (tid < 64) {                            // xbar[x][g] = sum_s XT[g][x * 32 + s]
+        const int g = tid >> 2, x = tid & 3;
+        float acc = 0.f;
+        for (int s = 0; s < 32; ++s)
+          acc += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sXT + buf * 2 * XT_BLK + xt_offset(g, x * 32 + s)));
+        xbar[buf * 64 + x * 16 + g] = acc;
+      }
+      if (tid == 0 && !*abort_flag) {
+        tc_fence_after_sync();
+        const uint32_t am = smem_u32(sMap), bx = smem_u32(sXT + buf * 2 * XT_BLK);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + buf * 16, desc_mn(am, ks), desc_k16(bx, ks), idesc, ks > 0 ? 1u : 0u);
+        umma_commit(&bar_mma[buf]);
+      }
+      if (h > 0) epilogue(it - 1);
+      __syncthreads();
+    }
+    // drain the last head of this sibling (its tiles read sMap, which the next sibling rewrites)
+    epilogue(r * H + H - 1);
+    __syncthreads();
+  }
+  __syncthreads();
+  if (tid == 0 && *abort_flag && a.status) atomicExch(a.status, 1);
+  if (warp == 0) tmem_dealloc(tbase, 32);
+}
+
+
+// ------------------------------------------------------------------------------------------------------------------
+// chunk_out:  y[t,g,o] = sum_r [ (chi_r W_r o Cbar_r Bbar_r^T) u  +  chi_r(t) a_r(t) Cbar_r Sin_r  +  chi_r(t) D[h,g,r,o] u[t,g,r] ]
+// Heads outer, siblings inner: the drive tile of a head is transposed once and the four masked scores accumulate into
+// one TMEM tile of y; the four entering-state products keep their own 16 columns each and are scaled by a_r(t) chi_r(t)
+// in the epilogue (the scale differs per sibling, so they cannot share an accumulator).
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int TAB_LD = 33;
+struct MimoOutSmem {
+  static constexpr uint32_t C = 0, B = 2 * BLK, MS = 4 * BLK, GB = 6 * BLK, UT = 8 * BLK, SINT = UT + 2 * XT_BLK,
+                            TAB = SINT + 2 * XT_BLK, CLK = TAB + 32 * TAB_LD * 4, YST = CLK + 12 * 32 * 4,
+                            TOTAL = YST + 32 * 65 * 4 + 1024;
+};
+
+// swizzled offset of 16-byte chunk `ck` (0..15) of gate row (s, r) in the [32][4][128] bf16 gate tile
+__device__ __forceinline__ uint32_t gate_offset(int s, int r, int ck) {
+  return (uint32_t)s * 1024u + (uint32_t)r * 256u + ((uint32_t)(ck ^ (s & 15)) << 4);
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_out_kernel(const ScanArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = align1024(smem_raw);
+  uint8_t* sC = sm + MimoOutSmem::C;
+  uint8_t* sB = sm + MimoOutSmem::B;
+  uint8_t* sMs = sm + MimoOutSmem::MS;
+  uint8_t* sGB = sm + MimoOutSmem::GB;
+  uint8_t* sUT = sm + MimoOutSmem::UT;
+  uint8_t* sSinT = sm + MimoOutSmem::SINT;
+  float* tab = reinterpret_cast<float*>(sm + MimoOutSmem::TAB);          // [32 t][33]  chi_t W[t][s]
+  float* clk = reinterpret_cast<float*>(sm + MimoOutSmem::CLK);          // cs, w, wd, chi [32] + f[4][32] + chis[4][32]
+  float *s_cs = clk, *s_w = clk + 32, *s_wd = clk + 64, *s_chi = clk + 96, *s_f = clk + 128, *s_chis = clk + 256;
+  float* sY = reinterpret_cast<float*>(sm + MimoOutSmem::YST);           // [32 t][65]
+  __shared__ uint64_t bar_s, bar_y;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, qw = warp & 3, wg = warp >> 2;
+  const int c = blockIdx.x, b = blockIdx.y, t0 = c * MM_T;
+  const int Tv = min(MM_T, a.L - t0);
+  const int H = a.H;
+  const int row = qw * 32 + lane;
+  const int64_t tok0 = (int64_t)b * a.L + t0;
+  constexpr uint32_t TS = 0, TY1 = 128, TYC = 144;   // TMEM columns: score, y accumulator, 4 x entering-state products
+
+  if (tid == 0) {
+    mbar_init(&bar_s, 1);
+    mbar_init(&bar_y, 1);
+    mbar_fence_init();
+    s_abort = 0;
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 256);
+  // head-shared pieces: this thread's rows of Bhat and of gCp x Chat stay in registers, the gB tile in shared memory
+  uint32_t bh[32], cg[32];
+  gated_row(reinterpret_cast<const __nv_bfloat16*>(a.Bhat), a.b_ts, nullptr, 0, tok0 + lane, qw, 0, wg * 64, lane < Tv, bh);
+  gated_row(reinterpret_cast<const __nv_bfloat16*>(a.Chat), a.c_ts, reinterpret_cast<const __nv_bfloat16*>(a.gCp), a.gc_ts,
+            tok0 + lane, qw, qw, wg * 64, lane < Tv, cg);
+  if (a.gBp != nullptr) {
+    const __nv_bfloat16* gB = reinterpret_cast<const __nv_bfloat16*>(a.gBp);
+    for (int idx = tid; idx < 32 * 4 * 16; idx += TC_THREADS) {
+      const int s = idx >> 6, r = (idx >> 4) & 3, ck = idx & 15;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (s < Tv) v = *reinterpret_cast<const uint4*>(gB + (tok0 + s) * a.gb_ts + r * MM_N + ck * 8);
+      *reinterpret_cast<uint4*>(sGB + gate_offset(s, r, ck)) = v;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_slot;
+  volatile int* abort_flag = &s_abort;
+  const uint32_t idesc_s = idesc_bf16(128, 128, 0, 0), idesc_y = idesc_bf16(128, 16, 0, 0);
+  uint32_t ph_s = 0, ph_y = 0;
+  bool alive = true;
+
+  for (int h = 0; h < H && alive; ++h) {
+    build_xt(sUT, reinterpret_cast<const __nv_bfloat16*>(a.u), (int64_t)H * 64, tok0, h, Tv, nullptr);
+    for (int r = 0; r < MM_R; ++r) {
+      // ---- clocks of kernel head (h, r)
+      float d = 0.f, wt = 0.f, wdt = 0.f, ch = 1.f;
+      if (lane < Tv) {
+        const int64_t i = ((tok0 + lane) * H + h) * MM_R + r;
+        d = a.dA[i];
+        wt = a.w[i];
+        wdt = a.wd[i];
+        if (a.chi) ch = a.chi[i];
+      }
+      const float cs = warp_prefix32(d, lane);
+      if (warp == 0) {
+        s_cs[lane] = cs;
+        s_w[lane] = wt;
+        s_wd[lane] = wdt;
+        s_chi[lane] = ch;
+        s_f[r * 32 + lane] = ch * __expf(cs);
+        s_chis[r * 32 + lane] = ch;
+      }
+      __syncthreads();
+      // ---- decay table, operand tiles of this kernel head, transposed entering state
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int idx = tid + k * TC_THREADS, t = idx >> 5, s = idx & 31;
+        float v = 0.f;
+        if (s < t) v = __expf(s_cs[t] - s_cs[s]) * s_w[s];
+        else if (s == t) v = s_wd[t];
+        tab[t * TAB_LD + s] = v * s_chi[t];
+      }
+      {
+        const float* be = a.beta ? a.beta + (((int64_t)h * MM_R + r) * 4 + qw) * MM_N + wg * 64 : nullptr;
+        const float* ga = a.gamma ? a.gamma + (((int64_t)h * MM_R + r) * 4 + qw) * MM_N + wg * 64 : nullptr;
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          uint32_t wv[4];
+          uint4 gv = make_uint4(0, 0, 0, 0);
+          if (a.gBp != nullptr) gv = *reinterpret_cast<const uint4*>(sGB + gate_offset(lane, r, wg * 8 + cc));
+          const uint32_t* gp = reinterpret_cast<const uint32_t*>(&gv);
+          float bb[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if (be != nullptr) {
+            const float4 b0 = *reinterpret_cast<const float4*>(be + cc * 8), b1 = *reinterpret_cast<const float4*>(be + cc * 8 + 4);
+            bb[0] = b0.x; bb[1] = b0.y; bb[2] = b0.z; bb[3] = b0.w; bb[4] = b1.x; bb[5] = b1.y; bb[6] = b1.z; bb[7] = b1.w;
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            float x0, x1, g0 = 1.f, g1 = 1.f;
+            unpack_bf16(bh[cc * 4 + k], x0, x1);
+            if (a.gBp != nullptr) unpack_bf16(gp[k], g0, g1);
+            wv[k] = pack_bf16(fmaf(x0, g0, bb[2 * k]), fmaf(x1, g1, bb[2 * k + 1]));
+          }
+          *reinterpret_cast<uint4*>(sB + wg * BLK + sw128_offset(row, cc)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+          float gg[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if (ga != nullptr) {
+            const float4 b0 = *reinterpret_cast<const float4*>(ga + cc * 8), b1 = *reinterpret_cast<const float4*>(ga + cc * 8 + 4);
+            gg[0] = b0.x; gg[1] = b0.y; gg[2] = b0.z; gg[3] = b0.w; gg[4] = b1.x; gg[5] = b1.y; gg[6] = b1.z; gg[7] = b1.w;
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            float x0, x1;
+            unpack_bf16(cg[cc * 4 + k], x0, x1);
+            wv[k] = pack_bf16(x0 + gg[2 * k], x1 + gg[2 * k + 1]);
+          }
+          *reinterpret_cast<uint4*>(sC + wg * BLK + sw128_offset(row, cc)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+        }
+      }
+      {
+        // SinT[g][n] (bf16) from the entering state Sin[n][g] (fp32): thread -> (n, 8 of the 16 g)
+        const int n = tid >> 1, g0 = (tid & 1) * 8;
+        const float* src = a.Sin + (((((int64_t)b * a.nc + c) * H + h) * MM_R + r) * MM_N + n) * MM_G + g0;
+        const float4 v0 = *reinterpret_cast<const float4*>(src), v1 = *reinterpret_cast<const float4*>(src + 4);
+        const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) *reinterpret_cast<__nv_bfloat16*>(sSinT + xt_offset(g0 + k, n)) = __float2bfloat16_rn(vv[k]);
+      }
+      fence_proxy_async();
+      __syncthreads();
+      // ---- score and entering-state product
+      if (tid == 0 && !*abort_flag) {
+        tc_fence_after_sync();
+        const uint32_t ac = smem_u32(sC), ab = smem_u32(sB), as = smem_u32(sSinT);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TS, desc_k(ac, ks), desc_k(ab, ks), idesc_s, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TYC + r * 16, desc_k(ac, ks), desc_k16(as, ks), idesc_y, ks > 0 ? 1u : 0u);
+        umma_commit(&bar_s);
+      }
+      alive = wait_warp(&bar_s, ph_s, abort_flag);
+      ph_s ^= 1u;
+      if (alive) {
+        tc_fence_after_sync();
+        // ---- mask: row (o, t = lane), columns (q = 2 wg + j, s)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          uint32_t v[32];
+          tmem_ld32(tmem_addr(tbase, qw * 32, TS + wg * 64 + j * 32), v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t wv[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int s = cc * 8 + 2 * k;
+              wv[k] = pack_bf16(__uint_as_float(v[s]) * tab[lane * TAB_LD + s], __uint_as_float(v[s + 1]) * tab[lane * TAB_LD + s + 1]);
+            }
+            *reinterpret_cast<uint4*>(sMs + wg * BLK + sw128_offset(row, j * 4 + cc)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+          }
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before_sync();
+      __syncthreads();
+      if (tid == 0 && !*abort_flag) {
+        tc_fence_after_sync();
+        const uint32_t am = smem_u32(sMs), au = smem_u32(sUT);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TY1, desc_k(am, ks), desc_k16(au, ks), idesc_y, (r > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&bar_y);
+      }
+      alive = wait_warp(&bar_y, ph_y, abort_flag) && alive;
+      ph_y ^= 1u;
+      alive = __syncthreads_and(alive ? 1 : 0) != 0;
+      if (!alive) break;
+    }
+    if (!alive) break;
+    // ---- epilogue of head h: thread (o, t) gathers 8 of the 16 g (warp group picks the half)
+    {
+      tc_fence_after_sync();
+      uint32_t y1[8], yc[8];
+      float acc[8];
+      tmem_ld8(tmem_addr(tbase, qw * 32, TY1 + wg * 8), y1);
+      tmem_ld_wait();
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = __uint_as_float(y1[k]);
+#pragma unroll
+      for (int r = 0; r < MM_R; ++r) {
+        tmem_ld8(tmem_addr(tbase, qw * 32, TYC + r * 16 + wg * 8), yc);
+        tmem_ld_wait();
+        const float f = s_f[r * 32 + lane];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = fmaf(f, __uint_as_float(yc[k]), acc[k]);
+        if (a.Dg != nullptr) {
+          const float chr = s_chis[r * 32 + lane];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int g = wg * 8 + k;
+            const float uv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sUT + xt_offset(g, r * 32 + lane)));
+            acc[k] = fmaf(chr * a.Dg[(((int64_t)h * MM_G + g) * MM_R + r) * 4 + qw], uv, acc[k]);
+          }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) sY[lane * 65 + (wg * 8 + k) * 4 + qw] = acc[k];
+      tc_fence_before_sync();
+      __syncthreads();
+      const int t = tid >> 3, v = tid & 7;
+      if (t < Tv) {
+        uint32_t wv[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) wv[k] = pack_bf16(sY[t * 65 + v * 8 + 2 * k], sY[t * 65 + v * 8 + 2 * k + 1]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.y) + ((tok0 + t) * H + h) * 64 + v * 8) =
+            make_uint4(wv[0], wv[1], wv[2], wv[3]);
+      }
+      __syncthreads();
+    }
+  }
+  __syncthreads();
+  if (tid == 0 && *abort_flag && a.status) atomicExch(a.status, 1);
+  if (warp == 0) tmem_dealloc(tbase, 256);
+}
+
+// ---- launchers ---------------------------------------------------------------------------------------------------
+bool mimo_tc_geometry(int R, int O, int G, int N) { return R == MM_R && O == MM_R && G == MM_G && N == MM_N; }
+
+int mimo_tc_supported(const ScanArgs& a, int dtype, const char** why) {
+  *why = nullptr;
+  if (dtype != BF16) *why = "activations must be bfloat16";
+  else if (a.T != MM_T) *why = "rank-4 tensor-core tiles use chunk length 32";
+  else if (a.b_ts % 8 || a.c_ts % 8 || !aligned16(a.Bhat) || !aligned16(a.Chat) || !aligned16(a.u) ||
+           (a.gBp && (a.gb_ts % 8 || !aligned16(a.gBp))) || (a.gCp && (a.gc_ts % 8 || !aligned16(a.gCp))) ||
+           (a.dy && !aligned16(a.dy)) || (a.y && !aligned16(a.y)) || (a.beta && !aligned16(a.beta)) ||
+           (a.gamma && !aligned16(a.gamma)))
+    *why = "maps, gates, biases and drive must be 16-byte aligned with token strides that are multiples of 8 elements";
+  return *why == nullptr;
+}
+
+int mimo_tc_launch_state(const ScanArgs& a, int mode, cudaStream_t stream) {
+  const size_t smem = 2 * BLK + 4 * XT_BLK + 32 * 4 + 2 * 64 * 4 + 1024;
+  static bool attr = false;
+  if (!attr) {
+    ORBIT_CHECK_CUDA(cudaFuncSetAttribute(mimo_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr = true;
+  }
+  mimo_chunk_state_kernel<<<dim3(a.nc, a.B), TC_THREADS, smem, stream>>>(a, mode);
+  ORBIT_CHECK_LAUNCH("mimo_chunk_state_kernel");
+  return OK;
+}
+
+int mimo_tc_launch_out(const ScanArgs& a, cudaStream_t stream) {
+  const size_t smem = MimoOutSmem::TOTAL;
+  static bool attr = false;
+  if (!attr) {
+    ORBIT_CHECK_CUDA(cudaFuncSetAttribute(mimo_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr = true;
+  }
+  mimo_chunk_out_kernel<<<dim3(a.nc, a.B), TC_THREADS, smem, stream>>>(a);
+  ORBIT_CHECK_LAUNCH("mimo_chunk_out_kernel");
+  return OK;
+}
+
+}  // namespace orbit

@@ -407,7 +407,7 @@ def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     if u.is_cuda:
         a.Sin, a.atot, a.y = Sin.data_ptr(), atot.data_ptr(), y.data_ptr()
     Sin16 = None
-    if precision == _lib.PRECISION_IO:
+    if precision == _lib.PRECISION_IO and geo.R == 1:    # bf16 state tiles are read by the rank-1 tensor-core kernels only
         Sin16 = torch.empty((B, nc, H, R, N, G), device=dev, dtype=torch.bfloat16)
         a.Sin16 = Sin16.data_ptr()
     a.t = dict(geo=geo, u=u, Bhat=Bhat, gBp=gBp, Chat=Chat, gCp=gCp, beta=beta, gamma=gamma, chi=chi, dA=dA, w=w, wd=wd,

@@ -246,3 +246,34 @@ def test_scan_tc_backward(case):
     for k, v in g.items():
         if v is not None:
             assert torch.equal(v, g2[k]), ("not reproducible", k)
+
+
+# ---------------------------------------------------------------------------------------------------- scan, tcgen05 rank 4
+MIMO_CASES = [
+    # B, L, H, gates, biases, chi, skip, trap, s0
+    (1, 32, 1, False, False, False, False, False, False),
+    (1, 64, 2, False, True, False, True, False, True),
+    (2, 96, 2, True, False, True, True, True, False),
+    (1, 77, 3, True, True, True, True, True, True),
+    (2, 37, 2, True, True, True, True, False, True),
+]
+
+
+@pytest.mark.parametrize("case", MIMO_CASES)
+def test_scan_tc_mimo_forward(case):
+    """Forward on the rank-4 tensor-core tiles (R = O = 4, G = 16, N = 128, chunk 32) against the fp64 restatement on
+    the same bf16-rounded inputs.  Operand tiles (gate x map + bias, masked scores, entering states) are rounded to
+    bfloat16 and accumulated in fp32: y within 1e-2, final state within 4e-3."""
+    B, L, H, gates, biases, chi, skip, trap, s0 = case
+    c = scan_case(B, L, H, 4, 4, 16, 128, torch.bfloat16, gates, biases, chi, skip, trap, s0, seed=11)
+    geo = c["geo"]
+    assert ops.pick_chunk(geo, _lib.PRECISION_IO, False, 64) == 32
+    args = (c["u"], c["Bhat"], c["gBp"], c["Chat"], c["gCp"], c["beta"], c["gamma"], c["chi"], c["dA"], c["w"],
+            c["w"] if c["euler"] else c["wd"], c["Dg"])
+    y, S_fin, Sin, atot = ops.scan_fwd(geo, 32, _lib.PRECISION_IO, *args, c["S0"])
+    ops.check_device_status()
+    ry, rS, _, _ = R.scan_fwd(geo, 32, 0, *args, c["S0"])
+    assert rel(S_fin, rS) < 4e-3, ("S_fin", rel(S_fin, rS))
+    assert rel(y, ry) < 1e-2, ("y", rel(y, ry))
+    y2, S2, _, _ = ops.scan_fwd(geo, 32, _lib.PRECISION_IO, *args, c["S0"])
+    assert torch.equal(y, y2) and torch.equal(S_fin, S2)
