@@ -135,6 +135,8 @@ typedef struct orbit_scan_args {
   void* Sin16;        /* [B, nc, H, R, N, G] bfloat16 copy of Sin written by the forward pass, or NULL;
                          required (with dS16 in backward) by precision "io", whose tiles read it by TMA */
   void* dS16;         /* [B, nc, H, R, N, G] bfloat16 copy of dS written by the reverse pass, or NULL  */
+  float* du32;        /* [B, L, H, G, R] fp32 scratch, or NULL; required by CHUNK_GRADS of precision "io" at rank 4
+                         (R = O = 4), which sums the drive gradient of a head over its siblings there          */
 } orbit_scan_args;
 
 /* The scan runs as three chunk-parallel phases per direction (the decomposition of the reference's chunk-parallel

@@ -31,7 +31,7 @@ class ScanArgs(C.Structure):
         + [(n, C.c_int64) for n in ("b_ts", "gb_ts", "c_ts", "gc_ts")]
         + [(n, C.c_void_p) for n in ("beta", "gamma", "chi", "dA", "w", "wd", "Dg", "Sin", "atot", "dS", "y", "dy", "du",
                                      "dBhat", "dgBp", "dChat", "dgCp", "ddA", "dw", "dwd", "dchi", "dbeta_part",
-                                     "dgamma_part", "dDg_part", "status", "Sin16", "dS16")]
+                                     "dgamma_part", "dDg_part", "status", "Sin16", "dS16", "du32")]
     )
 
 

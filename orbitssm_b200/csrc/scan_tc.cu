@@ -901,6 +901,7 @@ bool mimo_tc_geometry(int R, int O, int G, int N);
 int mimo_tc_supported(const ScanArgs& a, int dtype, const char** why);
 int mimo_tc_launch_state(const ScanArgs& a, int mode, cudaStream_t stream);
 int mimo_tc_launch_out(const ScanArgs& a, cudaStream_t stream);
+int mimo_tc_launch_grads(const ScanArgs& a, cudaStream_t stream);
 
 int tc_supported(const ScanArgs& a, int dtype, const char** why) {
   *why = nullptr;
@@ -914,7 +915,7 @@ int tc_supported(const ScanArgs& a, int dtype, const char** why) {
 }
 
 int tc_pick_chunk(int R, int O, int G, int N, int backward, int limit) {
-  if (mimo_tc_geometry(R, O, G, N)) return (!backward && limit >= 32) ? 32 : 0;
+  if (mimo_tc_geometry(R, O, G, N)) return limit >= 32 ? 32 : 0;
   return (R == 1 && O == 1 && G == TC_G && N == TC_N && limit >= TC_T) ? TC_T : 0;
 }
 
@@ -982,7 +983,7 @@ constexpr int SMEM_GSTATE = 12 * BLK + 4096 + 1024;
 constexpr int SMEM_GSCORE = 12 * BLK + 8192 + 1024;
 
 int tc_launch_chunk_grads(const ScanArgs& a, cudaStream_t st) {
-  if (mimo_tc_geometry(a.R, a.O, a.G, a.N)) return fail(ERR_UNSUPPORTED, "rank-4 tensor-core tiles have no chunk_grads kernel");
+  if (mimo_tc_geometry(a.R, a.O, a.G, a.N)) return mimo_tc_launch_grads(a, st);
   CUtensorMap tmB, tmC, tmU, tmDY, tmS, tmDS;
   int rc;
   if ((rc = map_state(&tmS, a.Sin16, a)) != OK) return rc;

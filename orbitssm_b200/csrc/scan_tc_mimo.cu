@@ -472,6 +472,529 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_out_kernel(const Sca
   if (warp == 0) tmem_dealloc(tbase, 256);
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// chunk_grads.  Siblings outer, heads inner, so that the gate of the input map (indexed by the sibling) factors out of
+// the head sum:   dBhat[s,q,:] = sum_r gBp[s,r,:] (sum_h dBbar_{h,r}[(q,s),:])       dChat[t,o,:] = gCp[t,o,:] sum_{h,r} dCbar_{h,r}[(o,t),:]
+// Both sums live in TMEM for the whole inner loop (X_r: 128 columns, reset per sibling; dC: 128 columns, never reset).
+// Per kernel head (h, r), rows rho = (o, t), columns sigma = (q, s):
+//   dM  = DY U^T                       (K = 16, copied to shared memory as bf16; its TMEM columns are then reused by Sc)
+//   Sc  = Cbar Bbar^T,   Ycr = Cbar Sin,   Dd = Bbar dSo
+//   dSc = dM o chi W,    Ms = Sc o chi W                                  (threads; also every clock gradient's partial sums)
+//   dC += dSc Bbar + (f o DY) Sin^T        X_r += dSc^T Cbar + (e o U) dSo^T
+//   D1  = Ms^T DY  (du through the scores)    Dgam = Bbar^T RS^T    Dbet = Cbar^T CB^T   (bias gradients from block sums)
+// du of a head collects four siblings at four different times: it is summed in an fp32 scratch (a.du32) by the same
+// thread each time and rounded to the IO dtype by the last sibling.
+// ------------------------------------------------------------------------------------------------------------------
+struct MimoGradSmem {
+  static constexpr uint32_t C = 0, B = 2 * BLK, DSC = 4 * BLK, MS = 6 * BLK, DM = 8 * BLK, XT = 10 * BLK;
+  static constexpr uint32_t XT_SZ = 2 * XT_BLK;
+  static constexpr uint32_t UT = XT, DYT = XT + XT_SZ, FDYT = XT + 2 * XT_SZ, EUT = XT + 3 * XT_SZ, SINT = XT + 4 * XT_SZ,
+                            DSOT = XT + 5 * XT_SZ, RS = XT + 6 * XT_SZ, CB = XT + 7 * XT_SZ;
+  static constexpr uint32_t TABW = XT + 8 * XT_SZ, TABE = TABW + 32 * TAB_LD * 4, CLK = TABE + 32 * TAB_LD * 4,
+                            PART = CLK + 8 * 32 * 4, XBAR = PART + 6 * 8 * 32 * 4, DU = XBAR + 2 * 64 * 4 + 64,
+                            TOTAL = DU + 32 * 65 * 4 + 1024;
+};
+
+// MN-major descriptor of a [16 k rows x 128] transposed drive tile (one k-step of 16)
+__device__ __forceinline__ uint64_t desc_xt_mn(uint32_t base) { return smem_desc_sw128(base, XT_BLK, 1024u); }
+
+// two transposed drive tiles from one load: plain and row-scaled
+__device__ __forceinline__ void build_xt_pair(uint8_t* plain, uint8_t* scaled, const __nv_bfloat16* src, int64_t row_stride,
+                                              int64_t tok0, int h, int Tv, const float* f) {
+  const int s = threadIdx.x >> 3, v = threadIdx.x & 7;
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  if (s < Tv) raw = *reinterpret_cast<const uint4*>(src + (tok0 + s) * row_stride + h * 64 + v * 8);
+  const float fs = f[s];
+  const uint32_t* rp = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float a0, a1;
+    unpack_bf16(rp[k], a0, a1);
+    const int ch0 = v * 8 + 2 * k;
+    const uint32_t o0 = xt_offset(ch0 >> 2, (ch0 & 3) * 32 + s), o1 = xt_offset((ch0 + 1) >> 2, ((ch0 + 1) & 3) * 32 + s);
+    *reinterpret_cast<__nv_bfloat16*>(plain + o0) = __float2bfloat16_rn(a0);
+    *reinterpret_cast<__nv_bfloat16*>(plain + o1) = __float2bfloat16_rn(a1);
+    *reinterpret_cast<__nv_bfloat16*>(scaled + o0) = __float2bfloat16_rn(a0 * fs);
+    *reinterpret_cast<__nv_bfloat16*>(scaled + o1) = __float2bfloat16_rn(a1 * fs);
+  }
+}
+
+__device__ __forceinline__ float xt_read(const uint8_t* xt, int g, int c) {
+  return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(xt + xt_offset(g, c)));
+}
+
+__device__ __forceinline__ void tmem_ld8f(uint32_t taddr, float (&v)[8]) {
+  uint32_t r[8];
+  tmem_ld8(taddr, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const ScanArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = align1024(smem_raw);
+  using L = MimoGradSmem;
+  uint8_t *sC = sm + L::C, *sB = sm + L::B, *sDSc = sm + L::DSC, *sMs = sm + L::MS, *sDM = sm + L::DM;
+  uint8_t *sUT = sm + L::UT, *sDYT = sm + L::DYT, *sFDYT = sm + L::FDYT, *sEUT = sm + L::EUT, *sSinT = sm + L::SINT,
+          *sDSoT = sm + L::DSOT, *sRS = sm + L::RS, *sCB = sm + L::CB;
+  float* tabW = reinterpret_cast<float*>(sm + L::TABW);   // [t][s]  W: E w_s below the diagonal, wd_t on it
+  float* tabE = reinterpret_cast<float*>(sm + L::TABE);   // [t][s]  E = exp(cs_t - cs_s) below the diagonal
+  float* clk = reinterpret_cast<float*>(sm + L::CLK);
+  float *s_cs = clk, *s_w = clk + 32, *s_wd = clk + 64, *s_chi = clk + 96, *s_at = clk + 128, *s_et = clk + 160, *s_f = clk + 192,
+        *s_e = clk + 224;
+  float* part = reinterpret_cast<float*>(sm + L::PART);   // [6][8 warps][32 tokens]
+  float *p_row = part, *p_diag = part + 256, *p_col = part + 512, *p_da = part + 768, *p_de = part + 1024, *p_sk = part + 1280;
+  float* xbar = reinterpret_cast<float*>(sm + L::XBAR);   // dybar[4 o][16 g], ubar[4 q][16 g], red[8]
+  float* red = xbar + 128;
+  float* sDU = reinterpret_cast<float*>(sm + L::DU);      // [32 s][65]
+  __shared__ uint64_t bar_a, bar_b, bar_c;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, qw = warp & 3, wg = warp >> 2;
+  const int c = blockIdx.x, b = blockIdx.y, t0 = c * MM_T;
+  const int Tv = min(MM_T, a.L - t0);
+  const int H = a.H;
+  const int row = qw * 32 + lane;
+  const int64_t tok0 = (int64_t)b * a.L + t0;
+  const int64_t slot = (int64_t)b * a.nc + c;
+  constexpr uint32_t TS = 0, TDC = 128, TX = 256, TDU = 384, TYC = 400, TDD = 416, TDG = 432, TDB = 448;
+
+  if (tid == 0) {
+    mbar_init(&bar_a, 1);
+    mbar_init(&bar_b, 1);
+    mbar_init(&bar_c, 1);
+    mbar_fence_init();
+    s_abort = 0;
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 512);
+  for (int i = tid; i < 2 * (int)L::XT_SZ / 16; i += TC_THREADS) reinterpret_cast<uint4*>(sRS)[i] = make_uint4(0, 0, 0, 0);   // RS and CB
+  uint32_t cg[32], bg[32];
+  gated_row(reinterpret_cast<const __nv_bfloat16*>(a.Chat), a.c_ts, reinterpret_cast<const __nv_bfloat16*>(a.gCp), a.gc_ts,
+            tok0 + lane, qw, qw, wg * 64, lane < Tv, cg);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_slot;
+  volatile int* abort_flag = &s_abort;
+  const uint32_t id_kk = idesc_bf16(128, 128, 0, 0), id_km = idesc_bf16(128, 128, 0, 1), id_mm = idesc_bf16(128, 128, 1, 1),
+                 id_k16 = idesc_bf16(128, 16, 0, 0), id_m16 = idesc_bf16(128, 16, 1, 0);
+  bool alive = true;
+  const __nv_bfloat16* up = reinterpret_cast<const __nv_bfloat16*>(a.u);
+  const __nv_bfloat16* dyp = reinterpret_cast<const __nv_bfloat16*>(a.dy);
+
+  for (int r = 0; r < MM_R && alive; ++r) {
+    gated_row(reinterpret_cast<const __nv_bfloat16*>(a.Bhat), a.b_ts, reinterpret_cast<const __nv_bfloat16*>(a.gBp), a.gb_ts,
+              tok0 + lane, qw, r, wg * 64, lane < Tv, bg);
+    for (int h = 0; h < H; ++h) {
+      const int it = r * H + h;
+      const uint32_t par = (uint32_t)it & 1u;
+      const int64_t so = (((slot * H + h) * MM_R + r) * MM_N) * MM_G;
+      // ================= stage A: clocks, tables, operand tiles
+      float d = 0.f, wt = 0.f, wdt = 0.f, ch = 1.f;
+      if (lane < Tv) {
+        const int64_t i = ((tok0 + lane) * H + h) * MM_R + r;
+        d = a.dA[i];
+        wt = a.w[i];
+        wdt = a.wd[i];
+        if (a.chi) ch = a.chi[i];
+      }
+      const float cs = warp_prefix32(d, lane);
+      const float tot = __shfl_sync(0xffffffffu, cs, 31);
+      if (warp == 0) {
+        const float at = __expf(cs), et = __expf(tot - cs);
+        s_cs[lane] = cs; s_w[lane] = wt; s_wd[lane] = wdt; s_chi[lane] = ch; s_at[lane] = at; s_et[lane] = et;
+        s_f[lane] = ch * at;
+        s_e[lane] = et * wt;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int idx = tid + k * TC_THREADS, t = idx >> 5, s = idx & 31;
+        float e = 0.f, wv = 0.f;
+        if (s < t) { e = __expf(s_cs[t] - s_cs[s]); wv = e * s_w[s]; }
+        else if (s == t) wv = s_wd[t];
+        tabE[t * TAB_LD + s] = e;
+        tabW[t * TAB_LD + s] = wv;
+      }
+      build_xt_pair(sUT, sEUT, up, (int64_t)H * 64, tok0, h, Tv, s_e);
+      build_xt_pair(sDYT, sFDYT, dyp, (int64_t)H * 64, tok0, h, Tv, s_f);
+      {
+        const float* be = a.beta ? a.beta + (((int64_t)h * MM_R + r) * 4 + qw) * MM_N + wg * 64 : nullptr;
+        const float* ga = a.gamma ? a.gamma + (((int64_t)h * MM_R + r) * 4 + qw) * MM_N + wg * 64 : nullptr;
+        store_row(sB, row, wg, bg, be);
+        store_row(sC, row, wg, cg, ga);
+      }
+      {
+        // SinT[g][n], dSoT[g][n] (bf16) from Sin[n][g], dSo[n][g] (fp32); <dSo, Sin> on the way
+        const int n = tid >> 1, g0 = (tid & 1) * 8;
+        const float* s1 = a.Sin + so + n * MM_G + g0;
+        const float* s2 = a.dS + so + n * MM_G + g0;
+        const float4 v0 = *reinterpret_cast<const float4*>(s1), v1 = *reinterpret_cast<const float4*>(s1 + 4);
+        const float4 w0 = *reinterpret_cast<const float4*>(s2), w1 = *reinterpret_cast<const float4*>(s2 + 4);
+        const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        float dot = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          *reinterpret_cast<__nv_bfloat16*>(sSinT + xt_offset(g0 + k, n)) = __float2bfloat16_rn(vv[k]);
+          *reinterpret_cast<__nv_bfloat16*>(sDSoT + xt_offset(g0 + k, n)) = __float2bfloat16_rn(ww[k]);
+          dot = fmaf(vv[k], ww[k], dot);
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) red[warp] = dot;
+      }
+      fence_proxy_async();
+      __syncthreads();
+      // ================= MMA group 1: dM, Ycr, Dd
+      if (tid == 0 && !*abort_flag) {
+        tc_fence_after_sync();
+        umma_bf16(tbase + TS, desc_xt_mn(smem_u32(sDYT)), desc_xt_mn(smem_u32(sUT)), id_mm, 0u);
+        const uint32_t ac = smem_u32(sC), ab = smem_u32(sB), as = smem_u32(sSinT), ad = smem_u32(sDSoT);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TYC, desc_k(ac, ks), desc_k16(as, ks), id_k16, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TDD, desc_k(ab, ks), desc_k16(ad, ks), id_k16, ks > 0 ? 1u : 0u);
+        umma_commit(&bar_a);
+      }
+      if (tid < 128) {   // dybar[o][g] = sum_t FDYT[g][o*32+t],  ubar[q][g] = sum_s EUT[g][q*32+s]
+        const uint8_t* src = tid < 64 ? sFDYT : sEUT;
+        const int g = (tid & 63) >> 2, x = tid & 3;
+        float acc = 0.f;
+        for (int s = 0; s < 32; ++s) acc += xt_read(src, g, x * 32 + s);
+        xbar[(tid >> 6) * 64 + x * 16 + g] = acc;
+      }
+      bool ok = wait_warp(&bar_a, par, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        // dM -> shared memory (bf16), same swizzled layout as the operand tiles
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          uint32_t v[32];
+          tmem_ld32(tmem_addr(tbase, qw * 32, TS + wg * 64 + j * 32), v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t wv[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) wv[k] = pack_bf16(__uint_as_float(v[cc * 8 + 2 * k]), __uint_as_float(v[cc * 8 + 2 * k + 1]));
+            *reinterpret_cast<uint4*>(sDM + wg * BLK + sw128_offset(row, j * 4 + cc)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+          }
+        }
+        // da, de and the skip part of dchi: partial sums over this thread's 8 g
+        float yc[8], dd[8];
+        tmem_ld8f(tmem_addr(tbase, qw * 32, TYC + wg * 8), yc);
+        tmem_ld8f(tmem_addr(tbase, qw * 32, TDD + wg * 8), dd);
+        float pda = 0.f, pde = 0.f, psk = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int g = wg * 8 + k;
+          const float dyv = xt_read(sDYT, g, qw * 32 + lane);
+          pda = fmaf(yc[k], dyv, pda);
+          pde = fmaf(dd[k], xt_read(sUT, g, qw * 32 + lane), pde);
+          if (a.Dg) psk = fmaf(dyv * a.Dg[(((int64_t)h * MM_G + g) * MM_R + r) * 4 + qw], xt_read(sUT, g, r * 32 + lane), psk);
+        }
+        p_da[warp * 32 + lane] = pda;
+        p_de[warp * 32 + lane] = pde;
+        p_sk[warp * 32 + lane] = psk;
+      }
+      tc_fence_before_sync();
+      alive = __syncthreads_and(ok ? 1 : 0) != 0;
+      if (!alive) break;
+      // ================= MMA group 2: scores (into the columns dM has left)
+      if (tid == 0) {
+        tc_fence_after_sync();
+        const uint32_t ac = smem_u32(sC), ab = smem_u32(sB);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TS, desc_k(ac, ks), desc_k(ab, ks), id_kk, ks > 0 ? 1u : 0u);
+        umma_commit(&bar_b);
+      }
+      ok = wait_warp(&bar_b, par, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        const float chi_t = s_chi[lane];
+        float prow = 0.f, pdiag = 0.f;
+        float vE[32];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          uint32_t v[32];
+          float vR[32];
+          tmem_ld32(tmem_addr(tbase, qw * 32, TS + wg * 64 + j * 32), v);
+          tmem_ld_wait();
+          float cbsum = 0.f;
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            const uint4 dmv = *reinterpret_cast<const uint4*>(sDM + wg * BLK + sw128_offset(row, j * 4 + cc));
+            const uint32_t* dmp = reinterpret_cast<const uint32_t*>(&dmv);
+            uint32_t w1[4], w2[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              float dm[2], ds[2], ms[2];
+              unpack_bf16(dmp[k], dm[0], dm[1]);
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int s = cc * 8 + 2 * k + e;
+                const float sc = __uint_as_float(v[s]);
+                const float Wt = tabW[lane * TAB_LD + s], Et = tabE[lane * TAB_LD + s];
+                const float p = dm[e] * sc;
+                prow = fmaf(p, Wt, prow);
+                pdiag += (s == lane) ? p : 0.f;
+                const float pe = chi_t * p * Et;
+                vE[s] = j == 0 ? pe : vE[s] + pe;
+                const float cw = chi_t * Wt;
+                ds[e] = dm[e] * cw;
+                ms[e] = sc * cw;
+                cbsum += ds[e];
+                vR[s] = ds[e];
+              }
+              w1[k] = pack_bf16(ds[0], ds[1]);
+              w2[k] = pack_bf16(ms[0], ms[1]);
+            }
+            *reinterpret_cast<uint4*>(sDSc + wg * BLK + sw128_offset(row, j * 4 + cc)) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+            *reinterpret_cast<uint4*>(sMs + wg * BLK + sw128_offset(row, j * 4 + cc)) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+          }
+          const int q = wg * 2 + j;
+          *reinterpret_cast<__nv_bfloat16*>(sCB + xt_offset(q, row)) = __float2bfloat16_rn(cbsum);
+          warp_colsum32(vR, lane);
+          *reinterpret_cast<__nv_bfloat16*>(sRS + xt_offset(qw, q * 32 + lane)) = __float2bfloat16_rn(vR[0]);
+        }
+        warp_colsum32(vE, lane);
+        p_row[warp * 32 + lane] = prow;
+        p_diag[warp * 32 + lane] = pdiag;
+        p_col[warp * 32 + lane] = vE[0];
+      }
+      fence_proxy_async();
+      tc_fence_before_sync();
+      alive = __syncthreads_and(ok ? 1 : 0) != 0;
+      if (!alive) break;
+      // ================= MMA group 3: every product of the masked tiles
+      if (tid == 0) {
+        tc_fence_after_sync();
+        const uint32_t ac = smem_u32(sC), ab = smem_u32(sB), ads = smem_u32(sDSc), ams = smem_u32(sMs);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TDC, desc_k(ads, ks), desc_mn(ab, ks), id_km, (it > 0 || ks > 0) ? 1u : 0u);
+        umma_bf16(tbase + TDC, desc_xt_mn(smem_u32(sFDYT)), desc_xt_mn(smem_u32(sSinT)), id_mm, 1u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TX, desc_mn(ads, ks), desc_mn(ac, ks), id_mm, (h > 0 || ks > 0) ? 1u : 0u);
+        umma_bf16(tbase + TX, desc_xt_mn(smem_u32(sEUT)), desc_xt_mn(smem_u32(sDSoT)), id_mm, 1u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TDU, desc_mn(ams, ks), desc_k16(smem_u32(sDYT), ks), id_m16, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TDG, desc_mn(ab, ks), desc_k16(smem_u32(sRS), ks), id_m16, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TDB, desc_mn(ac, ks), desc_k16(smem_u32(sCB), ks), id_m16, ks > 0 ? 1u : 0u);
+        umma_commit(&bar_c);
+      }
+      // ---- while the tensor cores run: clock gradients (warp 0, lane = token), skip-gain partials (warps 2, 3)
+      if (warp == 0) {
+        float rowW = 0.f, diag = 0.f, colE = 0.f, da = 0.f, de = 0.f, sk = 0.f, datot = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          rowW += p_row[k * 32 + lane]; diag += p_diag[k * 32 + lane]; colE += p_col[k * 32 + lane];
+          da += p_da[k * 32 + lane]; de += p_de[k * 32 + lane]; sk += p_sk[k * 32 + lane];
+          datot += red[k];
+        }
+        const float chi_t = s_chi[lane], w_t = s_w[lane], wd_t = s_wd[lane], at = s_at[lane], et = s_et[lane];
+        const float g_chi = rowW + at * da + sk;
+        float g_cs = chi_t * (rowW - wd_t * diag) - colE * w_t + chi_t * at * da - et * w_t * de;
+        const float g_w = colE + et * de;
+        const float endterm = warp_sum(et * w_t * de) + s_at[31] * datot;
+        if (lane == 31) g_cs += endterm;
+        // d dA[k] = sum_{t >= k} d cs[t]
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float y = __shfl_down_sync(0xffffffffu, g_cs, o);
+          if (lane + o < 32) g_cs += y;
+        }
+        if (lane < Tv) {
+          const int64_t i = ((tok0 + lane) * H + h) * MM_R + r;
+          a.ddA[i] = g_cs;
+          a.dw[i] = g_w;
+          if (a.dwd) a.dwd[i] = chi_t * diag;
+          if (a.dchi) a.dchi[i] = g_chi;
+        }
+      } else if ((warp == 2 || warp == 3) && a.dDg_part != nullptr) {
+        const int idx = tid - 64, o = idx & 3, g = idx >> 2;
+        float acc = 0.f;
+        for (int t = 0; t < 32; ++t) acc = fmaf(s_chi[t] * xt_read(sDYT, g, o * 32 + t), xt_read(sUT, g, r * 32 + t), acc);
+        a.dDg_part[(slot * H + h) * (MM_G * MM_R * 4) + (g * MM_R + r) * 4 + o] = acc;
+      }
+      ok = wait_warp(&bar_c, par, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        // du of this kernel head: row sigma = (q, s), 8 of the 16 g
+        float d1[8], dd[8];
+        tmem_ld8f(tmem_addr(tbase, qw * 32, TDU + wg * 8), d1);
+        tmem_ld8f(tmem_addr(tbase, qw * 32, TDD + wg * 8), dd);
+        const float es = s_e[lane], chs = s_chi[lane];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int g = wg * 8 + k;
+          float v = fmaf(es, dd[k], d1[k]);
+          if (a.Dg && qw == r) {
+            float sk = 0.f;
+#pragma unroll
+            for (int o = 0; o < 4; ++o) sk = fmaf(a.Dg[(((int64_t)h * MM_G + g) * MM_R + r) * 4 + o], xt_read(sDYT, g, o * 32 + lane), sk);
+            v = fmaf(chs, sk, v);
+          }
+          sDU[lane * 65 + g * 4 + qw] = v;
+        }
+        // bias gradients of this kernel head: state row n = row; warps 0..3 gamma, warps 4..7 beta
+        float* dst = wg == 0 ? a.dgamma_part : a.dbeta_part;
+        if (dst != nullptr) {
+          float dv[8];
+          tmem_ld8f(tmem_addr(tbase, qw * 32, wg == 0 ? TDG : TDB), dv);
+          const float* st = (wg == 0 ? a.Sin : a.dS) + so + row * MM_G;
+          float sv[16];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float4 x = *reinterpret_cast<const float4*>(st + 4 * k);
+            sv[4 * k] = x.x; sv[4 * k + 1] = x.y; sv[4 * k + 2] = x.z; sv[4 * k + 3] = x.w;
+          }
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            float acc = dv[x];
+#pragma unroll
+            for (int g = 0; g < 16; ++g) acc = fmaf(sv[g], xbar[wg * 64 + x * 16 + g], acc);
+            dst[((((slot * H + h) * MM_R + r) * 4 + x) * MM_N) + row] = acc;
+          }
+        }
+      }
+      tc_fence_before_sync();
+      alive = __syncthreads_and(ok ? 1 : 0) != 0;
+      if (!alive) break;
+      {
+        // du flush: thread -> (token, 8 channels); fp32 running sum over siblings, IO dtype from the last one
+        const int t = tid >> 3, v = tid & 7;
+        if (t < Tv) {
+          float acc[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[k] = sDU[t * 65 + v * 8 + k];
+          float* p32 = a.du32 + ((tok0 + t) * H + h) * 64 + v * 8;
+          if (r > 0) {
+            const float4 x0 = *reinterpret_cast<const float4*>(p32), x1 = *reinterpret_cast<const float4*>(p32 + 4);
+            acc[0] += x0.x; acc[1] += x0.y; acc[2] += x0.z; acc[3] += x0.w; acc[4] += x1.x; acc[5] += x1.y; acc[6] += x1.z; acc[7] += x1.w;
+          }
+          if (r < MM_R - 1) {
+            *reinterpret_cast<float4*>(p32) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            *reinterpret_cast<float4*>(p32 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+          } else {
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.du) + ((tok0 + t) * H + h) * 64 + v * 8) =
+                make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+          }
+        }
+      }
+      __syncthreads();
+    }
+    if (!alive) break;
+    // ================= sibling epilogue: X_r -> dBhat (+= gBp_r X_r), dgBp[:, r] = sum_q Bhat_q X_r
+    {
+      tc_fence_after_sync();
+      float* stage = reinterpret_cast<float*>(sDSc);   // [8 warps][32][65] fp32 over the (now idle) masked-tile buffers
+      const __nv_bfloat16* Bh = reinterpret_cast<const __nv_bfloat16*>(a.Bhat);
+      const __nv_bfloat16* gB = reinterpret_cast<const __nv_bfloat16*>(a.gBp);
+      const int64_t tok = tok0 + lane;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        uint32_t v[32];
+        tmem_ld32(tmem_addr(tbase, qw * 32, TX + wg * 64 + j * 32), v);
+        tmem_ld_wait();
+        if (lane < Tv) {
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            const int n0 = wg * 64 + j * 32 + cc * 8;
+            float gv[8], hv[8];
+            if (gB != nullptr) {
+              const uint4 graw = *reinterpret_cast<const uint4*>(gB + tok * a.gb_ts + r * MM_N + n0);
+              const uint4 hraw = *reinterpret_cast<const uint4*>(Bh + tok * a.b_ts + qw * MM_N + n0);
+              const uint32_t* gp = reinterpret_cast<const uint32_t*>(&graw);
+              const uint32_t* hp = reinterpret_cast<const uint32_t*>(&hraw);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) { unpack_bf16(gp[k], gv[2 * k], gv[2 * k + 1]); unpack_bf16(hp[k], hv[2 * k], hv[2 * k + 1]); }
+            } else {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) { gv[k] = 1.f; hv[k] = 0.f; }
+            }
+            float* dbh = a.dBhat + (tok * MM_R + qw) * MM_N + n0;
+            float o8[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o8[k] = __uint_as_float(v[cc * 8 + k]) * gv[k];
+            if (r > 0) {
+              const float4 x0 = *reinterpret_cast<const float4*>(dbh), x1 = *reinterpret_cast<const float4*>(dbh + 4);
+              o8[0] += x0.x; o8[1] += x0.y; o8[2] += x0.z; o8[3] += x0.w; o8[4] += x1.x; o8[5] += x1.y; o8[6] += x1.z; o8[7] += x1.w;
+            }
+            *reinterpret_cast<float4*>(dbh) = make_float4(o8[0], o8[1], o8[2], o8[3]);
+            *reinterpret_cast<float4*>(dbh + 4) = make_float4(o8[4], o8[5], o8[6], o8[7]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) stage[(warp * 32 + lane) * 65 + j * 32 + cc * 8 + k] = __uint_as_float(v[cc * 8 + k]) * hv[k];
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncthreads();
+      if (a.dgBp != nullptr) {
+        for (int idx = tid; idx < 32 * MM_N; idx += TC_THREADS) {
+          const int s = idx >> 7, n = idx & 127, half = n >> 6, col = n & 63;
+          if (s < Tv) {
+            float acc = 0.f;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc += stage[((half * 4 + q) * 32 + s) * 65 + col];
+            a.dgBp[((tok0 + s) * MM_R + r) * MM_N + n] = acc;
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  if (alive) {
+    // ================= final epilogue: dC -> dChat = gCp dC, dgCp = Chat dC
+    tc_fence_after_sync();
+    const __nv_bfloat16* Ch = reinterpret_cast<const __nv_bfloat16*>(a.Chat);
+    const __nv_bfloat16* gC = reinterpret_cast<const __nv_bfloat16*>(a.gCp);
+    const int64_t tok = tok0 + lane;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      uint32_t v[32];
+      tmem_ld32(tmem_addr(tbase, qw * 32, TDC + wg * 64 + j * 32), v);
+      tmem_ld_wait();
+      if (lane < Tv) {
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const int n0 = wg * 64 + j * 32 + cc * 8;
+          float gv[8], hv[8];
+          if (gC != nullptr) {
+            const uint4 graw = *reinterpret_cast<const uint4*>(gC + tok * a.gc_ts + qw * MM_N + n0);
+            const uint4 hraw = *reinterpret_cast<const uint4*>(Ch + tok * a.c_ts + qw * MM_N + n0);
+            const uint32_t* gp = reinterpret_cast<const uint32_t*>(&graw);
+            const uint32_t* hp = reinterpret_cast<const uint32_t*>(&hraw);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { unpack_bf16(gp[k], gv[2 * k], gv[2 * k + 1]); unpack_bf16(hp[k], hv[2 * k], hv[2 * k + 1]); }
+          } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { gv[k] = 1.f; hv[k] = 0.f; }
+          }
+          float* dch = a.dChat + (tok * 4 + qw) * MM_N + n0;
+          *reinterpret_cast<float4*>(dch) = make_float4(__uint_as_float(v[cc * 8]) * gv[0], __uint_as_float(v[cc * 8 + 1]) * gv[1],
+                                                        __uint_as_float(v[cc * 8 + 2]) * gv[2], __uint_as_float(v[cc * 8 + 3]) * gv[3]);
+          *reinterpret_cast<float4*>(dch + 4) = make_float4(__uint_as_float(v[cc * 8 + 4]) * gv[4], __uint_as_float(v[cc * 8 + 5]) * gv[5],
+                                                            __uint_as_float(v[cc * 8 + 6]) * gv[6], __uint_as_float(v[cc * 8 + 7]) * gv[7]);
+          if (a.dgCp != nullptr) {
+            float* dg = a.dgCp + (tok * 4 + qw) * MM_N + n0;
+            *reinterpret_cast<float4*>(dg) = make_float4(__uint_as_float(v[cc * 8]) * hv[0], __uint_as_float(v[cc * 8 + 1]) * hv[1],
+                                                         __uint_as_float(v[cc * 8 + 2]) * hv[2], __uint_as_float(v[cc * 8 + 3]) * hv[3]);
+            *reinterpret_cast<float4*>(dg + 4) = make_float4(__uint_as_float(v[cc * 8 + 4]) * hv[4], __uint_as_float(v[cc * 8 + 5]) * hv[5],
+                                                             __uint_as_float(v[cc * 8 + 6]) * hv[6], __uint_as_float(v[cc * 8 + 7]) * hv[7]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag && a.status) atomicExch(a.status, 1);
+  if (warp == 0) tmem_dealloc(tbase, 512);
+}
+
 // ---- launchers ---------------------------------------------------------------------------------------------------
 bool mimo_tc_geometry(int R, int O, int G, int N) { return R == MM_R && O == MM_R && G == MM_G && N == MM_N; }
 
@@ -496,6 +1019,22 @@ int mimo_tc_launch_state(const ScanArgs& a, int mode, cudaStream_t stream) {
   }
   mimo_chunk_state_kernel<<<dim3(a.nc, a.B), TC_THREADS, smem, stream>>>(a, mode);
   ORBIT_CHECK_LAUNCH("mimo_chunk_state_kernel");
+  return OK;
+}
+
+int mimo_tc_launch_grads(const ScanArgs& a, cudaStream_t stream) {
+  ORBIT_REQUIRE(a.du32 != nullptr, ERR_BAD_ARG, "rank-4 tensor-core chunk_grads needs the fp32 drive-gradient scratch (du32)");
+  ORBIT_REQUIRE(aligned16(a.du32) && aligned16(a.du) && aligned16(a.dBhat) && aligned16(a.dChat) && aligned16(a.dS) &&
+                    aligned16(a.Sin) && (!a.dgBp || aligned16(a.dgBp)) && (!a.dgCp || aligned16(a.dgCp)),
+                ERR_UNSUPPORTED, "du32, du, dBhat, dChat, dgBp, dgCp, Sin, dS must be 16-byte aligned");
+  const size_t smem = MimoGradSmem::TOTAL;
+  static bool attr = false;
+  if (!attr) {
+    ORBIT_CHECK_CUDA(cudaFuncSetAttribute(mimo_chunk_grads_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr = true;
+  }
+  mimo_chunk_grads_kernel<<<dim3(a.nc, a.B), TC_THREADS, smem, stream>>>(a);
+  ORBIT_CHECK_LAUNCH("mimo_chunk_grads_kernel");
   return OK;
 }
 

@@ -296,7 +296,7 @@ def _tok_stride(who, t, inner):
 
 def run_phase(a, name, phase, state_in, state_out, dtype_code, precision):
     """One phase of the scan through the C-ABI (`a` is the filled argument block; `a.t` names its tensors)."""
-    with _timed(name, 2 if (precision == _lib.PRECISION_IO and phase == _lib.PHASE_CHUNK_GRADS) else 1):
+    with _timed(name, 2 if (precision == _lib.PRECISION_IO and phase == _lib.PHASE_CHUNK_GRADS and a.R == 1) else 1):
         _lib.check(_lib.load().orbit_ssd_scan_phase(C.byref(a), phase, _ptr(state_in), _ptr(state_out), dtype_code, precision,
                                                     _stream()), "orbit_ssd_scan_phase(" + name + ")")
 
@@ -492,10 +492,13 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     pd = torch.empty((slots, H, G, R, O), **f32) if Dg is not None else None
     dS = torch.empty((B, nc, H, R, N, G), **f32)
     dS0 = torch.empty((B, H, R, N, G), **f32) if want_dS0 else None
-    dS16 = None
-    if precision == _lib.PRECISION_IO:
+    dS16 = du32 = None
+    if precision == _lib.PRECISION_IO and R == 1:        # rank-1 tensor-core tiles read bf16 state tiles by TMA
         dS16 = torch.empty((B, nc, H, R, N, G), device=dev, dtype=torch.bfloat16)
         a.Sin16, a.dS16 = Sin16.data_ptr(), dS16.data_ptr()
+    elif precision == _lib.PRECISION_IO:                 # rank-4 tiles sum du over the siblings of a head in fp32
+        du32 = torch.empty(u.shape, **f32)
+        a.du32 = du32.data_ptr()
     a.Sin, a.atot, a.dS, a.dy, a.du = Sin.data_ptr(), atot.data_ptr(), dS.data_ptr(), dy.data_ptr(), out["du"].data_ptr()
     a.dBhat, a.dChat, a.ddA, a.dw = (out[k].data_ptr() for k in ("dBhat", "dChat", "ddA", "dw"))
     for k in ("dgBp", "dgCp", "dwd", "dchi"):
@@ -515,7 +518,7 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
         a.dwd = dwd_tmp.data_ptr()
     a.t = dict(geo=geo, u=u, Bhat=Bhat, gBp=gBp, Chat=Chat, gCp=gCp, beta=beta, gamma=gamma, chi=chi, dA=dA, w=w, wd=wd,
                Dg=Dg, Sin=Sin, atot=atot, dy=dy, dS=dS, out=out, dbeta_part=pb, dgamma_part=pg, dDg_part=pd,
-               dwd=(dwd_tmp if euler else out["dwd"]))
+               dwd=(dwd_tmp if euler else out["dwd"]), du32=du32, dS16=dS16)
     dt = _dtype_code("ssd_scan_bwd", u)
     run_phase(a, "scan_chunk_dstate", _lib.PHASE_CHUNK_DSTATE, None, None, dt, precision)
     if cp is not None:

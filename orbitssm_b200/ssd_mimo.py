@@ -418,8 +418,10 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         s = self.spec
         shared_maps = not (s.use_g_b or s.use_g_c or s.head_bias or s.r_mix_mode != "none")
         if self.precision == "io" and io == torch.bfloat16:
+            # rank-1 tiles serve head-shared maps only; rank-4 tiles take gates, per-head biases and the sibling mix
+            rank1 = geo.R == 1 and geo.O == 1
             T = ops.pick_chunk(geo, _lib.PRECISION_IO, needs_grad, 128 if self.chunk_size == "auto" else limit) \
-                if shared_maps else 0
+                if (shared_maps or not rank1) else 0
             if T > 0:
                 self._route_note = "tcgen05"
                 return _lib.PRECISION_IO, T

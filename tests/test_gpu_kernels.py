@@ -277,3 +277,27 @@ def test_scan_tc_mimo_forward(case):
     assert rel(y, ry) < 1e-2, ("y", rel(y, ry))
     y2, S2, _, _ = ops.scan_fwd(geo, 32, _lib.PRECISION_IO, *args, c["S0"])
     assert torch.equal(y, y2) and torch.equal(S_fin, S2)
+
+
+@pytest.mark.parametrize("case", MIMO_CASES)
+def test_scan_tc_mimo_backward(case):
+    """Backward on the rank-4 tensor-core tiles against the fp64 restatement on the same bf16-rounded inputs: every MMA
+    operand is rounded to bfloat16 and accumulated in fp32, gradients are held to 2e-2 normwise and must be bitwise
+    reproducible."""
+    B, L, H, gates, biases, chi, skip, trap, s0 = case
+    c = scan_case(B, L, H, 4, 4, 16, 128, torch.bfloat16, gates, biases, chi, skip, trap, s0, seed=13)
+    geo = c["geo"]
+    assert ops.pick_chunk(geo, _lib.PRECISION_IO, True, 64) == 32
+    args = (c["u"], c["Bhat"], c["gBp"], c["Chat"], c["gCp"], c["beta"], c["gamma"], c["chi"], c["dA"], c["w"],
+            c["w"] if c["euler"] else c["wd"], c["Dg"])
+    y, S_fin, Sin, atot = ops.scan_fwd(geo, 32, _lib.PRECISION_IO, *args, c["S0"])
+    g = ops.scan_bwd(geo, 32, _lib.PRECISION_IO, *args, Sin, atot, c["dy"], c["dS_fin"], c["euler"], c["S0"] is not None)
+    ops.check_device_status()
+    rg = R.scan_bwd(geo, 32, 0, *args, None, None, c["dy"], c["dS_fin"], c["euler"], c["S0"] is not None, S0=c["S0"])
+    errs = {k: rel(g[k], v) for k, v in rg.items() if v is not None}
+    bad = {k: e for k, e in errs.items() if not e < 2e-2}
+    assert not bad, (bad, errs)
+    g2 = ops.scan_bwd(geo, 32, _lib.PRECISION_IO, *args, Sin, atot, c["dy"], c["dS_fin"], c["euler"], c["S0"] is not None)
+    for k, v in g.items():
+        if v is not None:
+            assert torch.equal(v, g2[k]), ("not reproducible", k)
