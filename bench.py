@@ -7,8 +7,8 @@ activations over fp32 parameters).  Workloads (BASELINE.json `configs`):
   cfg5a (default) BASELINE config 5a: 4-block BlockStack of the d_model-2048 SISO layer, batch-sharded, x [8, 4096, 2048]
         per GPU: the d2048 bf16 configuration the metric is quoted on "at 1/2/4/8 B200" (weak scaling, no collective)
   cfg5b BASELINE config 5b: one d_model-2048 layer, B = 1, L = 262144 split over the GPUs (context parallel, strong scaling)
-  cfg3  SSD-MIMO rank-4 layer, d_model 2048, x [4, 4096, 2048] (runs on the fp32 scan kernels: its tensor-core tiles are
-        not built yet); at N = 1 the default run also measures it briefly and reports it under "other_workloads"
+  cfg3  SSD-MIMO rank-4 layer, d_model 2048, x [4, 4096, 2048] (rank-4 tcgen05 tiles); at N = 1 the default run also
+        measures it briefly and reports it under "other_workloads"
   cfg2  Mamba-2 preset SISO layer, d_model 1024, x [8, 2048, 1024]
   cfg5  one layer of cfg5a at x [4, 4096, 2048]
 With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same per-GPU batch on its own shard of the
@@ -48,10 +48,11 @@ WORKLOADS = {
                   desc="one SSD-MIMO SISO Mamba-2 preset layer, d_model 2048, B=1, L=262144 split over the GPUs "
                        "(context parallel: chunk state all-gathered over NVLink)"),
     # reduced batches of the same layers, for profiler captures that must stay small
-    "cfg5s": dict(B=1, L=2048, d_model=2048, kind="m2", chunk_acct=64,
-                  desc="profiling case: the cfg5 layer at x [1,2048,2048]"),
-    "cfg3s": dict(B=1, L=1024, d_model=2048, kind="mimo4", chunk_acct=32,
-                  desc="profiling case: the cfg3 layer at x [1,1024,2048]"),
+    # (sized so that the scan kernels launch exactly one CTA per SM: 4 x 37 chunks = 148)
+    "cfg5s": dict(B=4, L=4736, d_model=2048, kind="m2", chunk_acct=64,
+                  desc="profiling case: the cfg5 layer at x [4,4736,2048]"),
+    "cfg3s": dict(B=4, L=1184, d_model=2048, kind="mimo4", chunk_acct=32,
+                  desc="profiling case: the cfg3 layer at x [4,1184,2048]"),
 }
 
 
