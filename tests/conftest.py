@@ -30,3 +30,4 @@ def load_golden(name):
 
 
 GOLDEN_CASES = ("cfg1_exact", "cfg2_small", "cfg3_small", "dyn_trap_conv", "softplus_sib", "euler_r2o1")
+HM_GOLDEN_CASES = ("hm_small", "hm_cfg4_small", "hm_euler")

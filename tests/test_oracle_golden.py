@@ -2,8 +2,9 @@
 import pytest
 import torch
 
-from conftest import GOLDEN_CASES, load_golden
+from conftest import GOLDEN_CASES, HM_GOLDEN_CASES, load_golden
 from orbitssm_b200.config import SSDMimoConfig, resolve_ssd_spec
+from oracle import hm_oracle as HM
 from oracle import ssd_oracle as O
 
 
@@ -99,3 +100,37 @@ def test_empty_and_single_token():
     assert _rel(st["hidden_state"], s_all["hidden_state"]) < 1e-10
     y0, s0 = O.ssd_layer(spec, prm, x[:, :0], state=s_all, return_state=True)
     assert y0.shape[1] == 0 and torch.equal(s0["hidden_state"], s_all["hidden_state"].reshape(s0["hidden_state"].shape))
+
+
+# ---------------------------------------------------------------------------------------------------- HybridMamba
+def _run_hm(cfg, prm, x, dy, gs, state):
+    prm = {k: v.double().requires_grad_(v.is_floating_point() and v.dim() > 0) for k, v in prm.items()}
+    x = x.double().requires_grad_(True)
+    if state is not None:
+        state = {k: v.double().requires_grad_(True) for k, v in state.items()}
+    y, st = HM.hm_layer(cfg, prm, x, state, True)
+    loss = (y * dy.double()).sum()
+    for k, g in gs.items():
+        if k in st:
+            loss = loss + (st[k] * g.double()).sum()
+    loss.backward()
+    grads = {k: v.grad for k, v in prm.items() if v.grad is not None}
+    grads["x"] = x.grad
+    if state is not None:
+        for k, v in state.items():
+            if v.grad is not None:
+                grads["state." + k] = v.grad
+    return y.detach(), st, grads
+
+
+@pytest.mark.parametrize("name", HM_GOLDEN_CASES)
+def test_hm_oracle_matches_reference_fp64(name):
+    """oracle/hm_oracle.py against the reference's own fp64 results: output, every carry, every gradient, and a
+    continuation segment started from the first segment's State."""
+    rec = load_golden(name)
+    got = _run_hm(rec["config"], rec["state_dict"], rec["x"], rec["dy"], rec["gs"], None)
+    _check(got, rec["f64"], 1e-9, name)
+    c = rec["f64_cont"]
+    s = c["split"]
+    got = _run_hm(rec["config"], rec["state_dict"], rec["x"][:, s:], rec["dy"][:, s:], rec["gs"], c["state_in"])
+    _check(got, c, 1e-9, name + " continuation")
