@@ -174,6 +174,67 @@ int orbit_ssd_scan_fwd(const orbit_scan_args* a, const float* S0, float* S_fin, 
 int orbit_ssd_scan_bwd(const orbit_scan_args* a, const float* dS_fin, float* dS0, int dtype, int precision,
                        void* stream);
 
+/* ---- HybridMamba coordinate-decay scan -----------------------------------------------------------------------
+ * Replaces the reference's `mh_scan` (src/orbit_ssm/kernels/hybrid_mamba_mh/functions.py:665-677; law restated from
+ * src/orbit_ssm/kernels/hybrid_mamba_mh/torch_scan.py:44-76, 180-279) for `coord_static` rows, real and rotating:
+ *   a_t[h,p,n] = exp(-exp(A_log[h,p,n]) delta_t[h])
+ *   Theta_t[h,k] = Theta_{t-1}[h,k] + delta_t[h] feat_t[k]                       (pairs k with rot[k] != 0)
+ *   Bt_t[h,:] = Rot(Theta_t)(Bh_t + beta_b[h]),  Ct_t[h,:] = Rot(Theta_t + theta_h[h])(Ch_t + beta_c[h])
+ *   raw_t[p,n] = x_t[p] Bt_t[n];  h_t = a_t (h_{t-1} + delta_t (1 - lam_t) raw_{t-1}) + delta_t lam_t raw_t   (lam = 1: Euler)
+ *   y_t[p] = sum_n Ct_t[n] h_t[p,n] + D[h] x_t[p]
+ * Token-major tensors; the scan is sequential in time inside one CTA per (batch, head); the state entering every
+ * chunk of `Tc` tokens (and the phase) is saved for the backward, which recomputes chunk interiors.
+ * Envelope: P and N multiples of 4, N/4 a power of two <= 32, (P/4)(N/4) <= 256, Tc a multiple of 8 (32 for the backward). */
+typedef struct orbit_hm_args {
+  int B, L, H, P, N;
+  int Tc, nck;              /* checkpoint interval in tokens, number of chunks = ceil(L / Tc)                   */
+  const void* x;            /* [B, L, H*P]  IO dtype                                                            */
+  const float* delta;       /* [B, L, H]    after softplus                                                      */
+  const float* A_log;       /* [H, P, N]                                                                        */
+  const float* Bh;          /* [B, L, N]    write map (after its norm)                                          */
+  const float* Ch;          /* [B, L, N]    read map                                                            */
+  const float* beta_b;      /* [H, N] or NULL                                                                   */
+  const float* beta_c;      /* [H, N] or NULL                                                                   */
+  const float* feat;        /* [B, L, N/2]  angle feature per pair, or NULL (no rotation)                       */
+  const unsigned char* rot; /* [N/2]  1 = the pair rotates (required with feat)                                 */
+  const float* theta_h;     /* [H, N/2] read offset in the scan's frame, or NULL                                */
+  const float* lam;         /* [B, L, H] trapezoid weight, or NULL (Euler)                                      */
+  const float* D;           /* [H] or NULL                                                                      */
+  const float* h_init;      /* [B, H, P, N] or NULL                                                             */
+  const float* write_prev;  /* [B, H, P, N] raw write of the token before the call, or NULL                     */
+  const float* theta_init;  /* [B, H, N/2] or NULL                                                              */
+  void* y;                  /* [B, L, H*P]  out, IO dtype                                                       */
+  float* h_final;           /* [B, H, P, N] out                                                                 */
+  float* theta_final;       /* [B, H, N/2]  out or NULL                                                         */
+  float* write_last;        /* [B, H, P, N] out or NULL: raw write of the last token                            */
+  float* hck;               /* [B, H, nck, P, N] out or NULL: state entering each chunk (saved for backward)    */
+  float* thck;              /* [B, H, nck, N/2]  out or NULL: phase entering each chunk                         */
+  /* backward only */
+  const void* dy;           /* [B, L, H*P] IO dtype                                                             */
+  const float* dh_final;    /* [B, H, P, N] or NULL                                                             */
+  const float* dtheta_final;/* [B, H, N/2] or NULL                                                              */
+  const float* dwrite_last; /* [B, H, P, N] or NULL                                                             */
+  void* dx;                 /* [B, L, H*P] out, IO dtype                                                        */
+  float* ddelta;            /* [B, L, H] out                                                                    */
+  float* dlam;              /* [B, L, H] out or NULL                                                            */
+  float* dA_log_part;       /* [B, H, P, N] out: per-batch partial sums                                         */
+  float* dBh_part;          /* [H, B, L, N] out: per-head partial sums                                          */
+  float* dCh_part;          /* [H, B, L, N] out                                                                 */
+  float* dbeta_b_part;      /* [B, H, N] out or NULL                                                            */
+  float* dbeta_c_part;      /* [B, H, N] out or NULL                                                            */
+  float* dfeat_part;        /* [H, B, L, N/2] out or NULL                                                       */
+  float* dtheta_h_part;     /* [B, H, N/2] out or NULL                                                          */
+  float* dD_part;           /* [B, H] out or NULL                                                               */
+  float* dh_init;           /* [B, H, P, N] out or NULL                                                         */
+  float* dwrite_prev;       /* [B, H, P, N] out or NULL                                                         */
+  float* dtheta_init;       /* [B, H, N/2] out or NULL                                                          */
+} orbit_hm_args;
+
+int orbit_hm_scan_fwd(const orbit_hm_args* a, int dtype, void* stream);
+/* Needs hck / thck written by the forward with the same Tc.  Every partial-sum buffer is written in full (no
+ * accumulation into caller memory, no atomics): the caller sums them over their leading axis. */
+int orbit_hm_scan_bwd(const orbit_hm_args* a, int dtype, void* stream);
+
 /* ---- diagnostics ---------------------------------------------------------------------------------------------
  * One 128 x N x K tcgen05 tile through the same TMA boxes, shared-memory descriptors and TMEM read-out as the scan
  * kernels: D[128, N] fp32 = op(A) * op(B), A and B bfloat16.  mode bit 0: A given as [K, 128] (M contiguous) instead

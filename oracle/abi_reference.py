@@ -261,3 +261,88 @@ def run_phase(a, name, phase, state_in, state_out, dtype_code, precision, comput
                 part[0].copy_(gs[key])
     else:
         raise ValueError(f"unknown phase {phase}")
+
+
+# ---- HybridMamba coordinate-decay scan ------------------------------------------------------------------
+_HM_KEYS = ("x", "delta", "A_log", "Bh", "Ch", "beta_b", "beta_c", "feat", "theta_h", "lam", "D", "h_init", "write_prev",
+            "theta_init")
+
+
+def _hm(ins, rot):
+    from . import hm_oracle as HM
+    rot_rows = None if rot is None else torch.repeat_interleave(rot.to(torch.bool).cpu(), 2).to(ins["x"].device)
+    return HM.hm_scan(ins["x"], ins["delta"], ins["A_log"], ins["Bh"], ins["Ch"], beta_b=ins["beta_b"], beta_c=ins["beta_c"],
+                      feat=ins["feat"], rot_rows=rot_rows, theta_h=ins["theta_h"], lam=ins["lam"], D=ins["D"],
+                      h_init=ins["h_init"], write_prev=ins["write_prev"], theta_init=ins["theta_init"])
+
+
+def hm_scan_fwd(x, delta, A_log, Bh, Ch, beta_b, beta_c, feat, rot, theta_h, lam, D, h_init, write_prev, theta_init,
+                compute=torch.float64):
+    """Same arguments as ``ops.hm_scan_fwd``; returns (y, h_final, theta_final, write_last) in `compute` precision."""
+    ins = dict(zip(_HM_KEYS, (x, delta, A_log, Bh, Ch, beta_b, beta_c, feat, theta_h, lam, D, h_init, write_prev, theta_init)))
+    ins = {k: _f(v, compute) for k, v in ins.items()}
+    return _hm(ins, rot)
+
+
+def hm_scan_bwd(x, delta, A_log, Bh, Ch, beta_b, beta_c, feat, rot, theta_h, lam, D, h_init, write_prev, theta_init,
+                dy, dh_final, dtheta_final, dwrite_last, compute=torch.float64):
+    """Gradients of sum(y dy) + sum(h_final dh_final) + ... with respect to every floating argument (dict keyed like the
+    arguments), through torch autograd over the token loop."""
+    ins = dict(zip(_HM_KEYS, (x, delta, A_log, Bh, Ch, beta_b, beta_c, feat, theta_h, lam, D, h_init, write_prev, theta_init)))
+    ins = {k: (None if v is None else _f(v, compute).requires_grad_(True)) for k, v in ins.items()}
+    with torch.enable_grad():
+        y, hN, thN, wl = _hm(ins, rot)
+        loss = (y * _f(dy, compute)).sum()
+        if dh_final is not None:
+            loss = loss + (hN * _f(dh_final, compute)).sum()
+        if dtheta_final is not None and thN is not None:
+            loss = loss + (thN * _f(dtheta_final, compute)).sum()
+        if dwrite_last is not None:
+            loss = loss + (wl * _f(dwrite_last, compute)).sum()
+        live = [k for k, v in ins.items() if v is not None]
+        grads = torch.autograd.grad(loss, [ins[k] for k in live], allow_unused=True)
+    out = {k: None for k in _HM_KEYS}
+    for k, gv in zip(live, grads):
+        out[k] = torch.zeros_like(ins[k]) if gv is None else gv
+    return out
+
+
+def run_hm(a, name, backward, dtype_code, compute=torch.float64):
+    """Torch restatement of `orbit_hm_scan_fwd` / `_bwd` on the tensors named in ``a.t`` (same buffer protocol: the
+    forward fills y, carries and the chunk-entering states; the backward fills the partial-sum buffers, whole sums in
+    slot 0 of their leading axis)."""
+    t = a.t
+    args = [t.get(k) for k in ("x", "delta", "A_log", "Bh", "Ch", "beta_b", "beta_c", "feat", "rot", "theta_h", "lam", "D",
+                               "h_init", "write_prev", "theta_init")]
+    if not backward:
+        y, hN, thN, wl = hm_scan_fwd(*args, compute=compute)
+        t["y"].copy_(y.reshape(t["y"].shape))
+        t["h_final"].copy_(hN)
+        t["write_last"].copy_(wl)
+        if t["theta_final"] is not None:
+            t["theta_final"].copy_(thN)
+        t["hck"].zero_()                                  # this restatement replays from the inputs, not from checkpoints
+        if t["thck"] is not None:
+            t["thck"].zero_()
+        return
+    g = hm_scan_bwd(*args, t["dy"], t["dh_final"], t["dtheta_final"], t["dwrite_last"], compute=compute)
+    t["dx"].copy_(g["x"].reshape(t["dx"].shape))
+    t["ddelta"].copy_(g["delta"])
+    for dst, key in (("dlam", "lam"), ("dh_init", "h_init"), ("dwrite_prev", "write_prev"), ("dtheta_init", "theta_init")):
+        if t.get(dst) is not None:
+            if g[key] is None:
+                # gradient of an absent (zero) carry: differentiate again with an explicit zero carry
+                zero = dict(h_init=torch.zeros_like(t["dh_init"]), write_prev=torch.zeros_like(t["dh_init"]),
+                            theta_init=None if t.get("dtheta_init") is None else torch.zeros_like(t["dtheta_init"]))
+                args2 = list(args)
+                for i, k in ((12, "h_init"), (13, "write_prev"), (14, "theta_init")):
+                    if args2[i] is None and zero[k] is not None and (k != "write_prev" or t.get("lam") is not None):
+                        args2[i] = zero[k]
+                g2 = hm_scan_bwd(*args2, t["dy"], t["dh_final"], t["dtheta_final"], t["dwrite_last"], compute=compute)
+                g = {**g, **{k: g2[k] for k in ("h_init", "write_prev", "theta_init")}}
+            t[dst].copy_(g[key])
+    for dst, key in (("dA_log_part", "A_log"), ("dBh_part", "Bh"), ("dCh_part", "Ch"), ("dbeta_b_part", "beta_b"),
+                     ("dbeta_c_part", "beta_c"), ("dfeat_part", "feat"), ("dtheta_h_part", "theta_h"), ("dD_part", "D")):
+        if t.get(dst) is not None:
+            t[dst].zero_()
+            t[dst][0].copy_(g[key])

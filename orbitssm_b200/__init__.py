@@ -1,12 +1,14 @@
-"""orbitssm_b200: the B200 (sm_100a) ``backend="cuda"`` of the SSD-MIMO layer hot path.
+"""orbitssm_b200: the B200 (sm_100a) ``backend="cuda"`` of the SSD-MIMO and HybridMamba layer hot paths.
 
-Host side mirrors the reference's config + execution interface (`SSDMimoConfig`, `Execution`, `SSDMimoSSM`,
-`State`); the arithmetic between the two projection GEMMs runs in hand-written CUDA behind the C-ABI library
+Host side mirrors the reference's config + execution interface (`SSDMimoConfig`, `HybridMambaConfig`, `Execution`,
+`SSDMimoSSM`, `HybridMambaSSM`, `State`); the arithmetic between the two projection GEMMs runs in hand-written CUDA behind the C-ABI library
 declared in ``include/orbit_b200.h``.
 """
-from .config import Execution, SSDMimoConfig, mamba2_config
+from .config import Execution, HybridMambaConfig, SSDMimoConfig, mamba2_config
+from .hybrid_mamba import HybridMambaSSM
 from .model import BlockStack, ResidualBlock
 from .ssd_mimo import SSDMimoSSM
 from .state import State
 
-__all__ = ["BlockStack", "ResidualBlock", "Execution", "SSDMimoConfig", "SSDMimoSSM", "State", "mamba2_config"]
+__all__ = ["BlockStack", "ResidualBlock", "Execution", "HybridMambaConfig", "HybridMambaSSM", "SSDMimoConfig", "SSDMimoSSM",
+           "State", "mamba2_config"]

@@ -35,6 +35,21 @@ class ScanArgs(C.Structure):
     )
 
 
+class HmArgs(C.Structure):
+    """Mirror of ``orbit_hm_args`` (include/orbit_b200.h); field order and types must match the header."""
+    _fields_ = (
+        [(n, C.c_int) for n in ("B", "L", "H", "P", "N", "Tc", "nck")]
+        + [(n, C.c_void_p) for n in (
+            "x", "delta", "A_log", "Bh", "Ch", "beta_b", "beta_c", "feat", "rot", "theta_h", "lam", "D", "h_init",
+            "write_prev", "theta_init", "y", "h_final", "theta_final", "write_last", "hck", "thck",
+            "dy", "dh_final", "dtheta_final", "dwrite_last", "dx", "ddelta", "dlam", "dA_log_part", "dBh_part",
+            "dCh_part", "dbeta_b_part", "dbeta_c_part", "dfeat_part", "dtheta_h_part", "dD_part", "dh_init",
+            "dwrite_prev", "dtheta_init")]
+    )
+
+
+HM_CHUNK = 32     # checkpoint interval (tokens) the HybridMamba backward kernel is written for
+
 _P, _I, _L, _F = C.c_void_p, C.c_int, C.c_int64, C.c_float
 
 # name -> (restype, argtypes); every symbol include/orbit_b200.h declares
@@ -53,6 +68,8 @@ SIGNATURES = {
     "orbit_ssd_scan_phase": (_I, [C.POINTER(ScanArgs), _I, _P, _P, _I, _I, _P]),
     "orbit_ssd_scan_fwd": (_I, [C.POINTER(ScanArgs), _P, _P, _I, _I, _P]),
     "orbit_ssd_scan_bwd": (_I, [C.POINTER(ScanArgs), _P, _P, _I, _I, _P]),
+    "orbit_hm_scan_fwd": (_I, [C.POINTER(HmArgs), _I, _P]),
+    "orbit_hm_scan_bwd": (_I, [C.POINTER(HmArgs), _I, _P]),
     "orbit_selftest_umma": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
 }
 

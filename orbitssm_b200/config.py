@@ -338,3 +338,199 @@ def resolve_ssd_spec(cfg: SSDMimoConfig, d_model: int | None = None) -> SimpleNa
         skip=bool(cfg.skip), skip_sharing=cfg.skip_sharing, bc_conv=bc_conv, out_norm=bool(cfg.out_norm),
         dt_min=cfg.dt_min, dt_max=cfg.dt_max, dt_init_floor=cfg.dt_init_floor,
         slab=tuple(slab), slab_off=offs, tok_width=o, norm_eps=1e-5, map_eps=1e-5)
+
+
+# ----------------------------------------------------------------------------------------------------
+#  HybridMamba
+# ----------------------------------------------------------------------------------------------------
+COORD_STATIC = "coord_static"
+
+
+@dataclass(kw_only=True)
+class HybridMambaConfig:
+    """Architecture of a `HybridMambaSSM` layer (reference: src/orbit_ssm/ssm/hybrid_mamba.py:2904-3100).
+
+    Every field has the reference's name, meaning and default.  The CUDA backend serves the per-coordinate static
+    decay law (``coord_static`` row blocks, real or rotating pairs), Euler or trapezoid write, B/C RMSNorm, per-head
+    additive map biases, learned pair frequencies and read offsets; gates, the dynamic / potential laws, flat
+    (per-head) laws, ``proj_source="main_branch"`` and the joint B|C conv are refused by name when the layer is built.
+    """
+    d_model: int | None = None
+    d_state: int = 64
+    expand: float | None = None
+    d_conv: int = 4
+    d_inner: int | None = None
+    d_ssm_in: int = 1
+    d_ssm_out: int | None = None
+    n_groups: int | None = None
+    n_heads: int | None = None
+    d_head: int | None = None
+    write_rule: str | None = None
+    proj_source: str | None = None
+    bc_conv: bool | None = None
+    dt_min: float = 1e-3
+    dt_max: float = 1e-1
+    dt_init_floor: float = 1e-4
+    skip: bool = True
+    skip_sharing: str = "head"
+    out_norm: bool = False
+    row_blocks: list | tuple | None = field(default_factory=lambda: [{"frac": 1.0, "decay": COORD_STATIC}])
+    theta_per_head: bool | None = None
+    learn_theta_freq: bool | None = None
+    use_theta_h: bool | None = None
+    omega_layout: str | None = None
+    theta_init: str | None = None
+    b_norm: bool | None = None
+    c_norm: bool | None = None
+    bc_bias: str | None = None
+    b_gate: bool | None = None
+    c_gate: bool | None = None
+    bc_gate_act: str | None = None
+    bc_gate_bias: bool | None = None
+    bc_gate_pos: str | None = None
+    dt_rank: int | str | None = "adaptive"
+    force_dt_dense: bool = False
+    dt_init: str | None = "random"
+    dt_scale: float = 1.0
+    dyn_res: str = "n"
+    dyn_act: str | int = "heavy_tail"
+    mu_res: str = "n"
+    mu_cap: float = 4.0
+    a_floor: float = 1e-4
+    a_act: str = "heavy_tail"
+    norm_eps: float = 1e-5
+    learnable_h_init: bool = False
+    gate_init: str = "kaiming_uniform"
+
+    def __post_init__(self):
+        _check_bool_fields(self)
+        if isinstance(self.d_conv, bool) or not isinstance(self.d_conv, int) or self.d_conv < 0:
+            raise ValueError(f"d_conv must be a nonnegative int, got {self.d_conv!r}")
+        for name in ("d_model", "d_state", "d_inner", "n_heads", "d_head"):
+            if getattr(self, name) is not None:
+                _positive_int(getattr(self, name), name)
+        # fields this family cannot honour (reference: hybrid_mamba.py:3077-3081)
+        if self.d_ssm_in != 1 or self.d_ssm_out not in (None, 1) or self.n_groups is not None:
+            raise ValueError("HybridMambaConfig: d_ssm_in != 1, d_ssm_out other than 1 and n_groups are not part of this family")
+        if self.expand is not None and not self.expand > 0:
+            raise ValueError(f"expand must be positive, got {self.expand!r}")
+        if not (0 < self.dt_min <= self.dt_max) or self.dt_init_floor <= 0:
+            raise ValueError("need 0 < dt_min <= dt_max and dt_init_floor > 0")
+        if self.write_rule is not None and self.write_rule not in WRITE_RULES:
+            raise ValueError(f"write_rule must be one of {WRITE_RULES} or None, got {self.write_rule!r}")
+        if self.width() is not None:
+            resolve_hm_spec(self)
+
+    width = SSDMimoConfig.width
+
+    def layer_width(self) -> int:
+        if self.d_model is not None:
+            return self.d_model
+        if self.d_inner is not None and self.expand is None:
+            return self.d_inner
+        raise TypeError("HybridMambaConfig: the layer width d_model is not set; give d_model or build with config.build(d_model)")
+
+    def replace(self, **kw):
+        return dataclasses.replace(self, **kw)
+
+    @classmethod
+    def from_dict(cls, d):
+        return _strict_from_dict(cls, d)
+
+    def to_dict(self) -> dict:
+        return {f.name: getattr(self, f.name) for f in fields(self)}
+
+    def build(self, d_model=None, execution=None):
+        from .hybrid_mamba import HybridMambaSSM
+        cfg = self if d_model is None else self.replace(d_model=d_model)
+        return HybridMambaSSM(cfg, execution=execution)
+
+
+def resolve_dt_rank(dt_rank, *, d_sel, heads, d_model, force_dt_dense=False):
+    """Rank of the clock projection: None = dense; "auto" = ceil(width / 16); "adaptive" = that rank only when it saves
+    multiplies (reference: src/orbit_ssm/configuration.py:21-42)."""
+    if force_dt_dense:
+        if dt_rank is not None and dt_rank != "adaptive":
+            raise ValueError("force_dt_dense conflicts with an explicit bottleneck dt_rank")
+        return None
+    if dt_rank is None:
+        return None
+    if dt_rank not in ("adaptive", "auto"):
+        return _positive_int(dt_rank, "dt_rank")
+    rank = (d_model + 15) // 16
+    if dt_rank == "auto" or rank * (d_sel + heads) < d_sel * heads:
+        return rank
+    return None
+
+
+def resolve_hm_spec(cfg: HybridMambaConfig, d_model: int | None = None) -> SimpleNamespace:
+    """Resolved geometry and row plan of a HybridMamba layer; refuses, by name, what the CUDA backend does not serve
+    (reference: hybrid_mamba.py:540-735 row plan and pair-tied stores, 2620-2675 layer geometry)."""
+    who = "HybridMambaSSM(backend='cuda')"
+    d_model = cfg.d_model if d_model is None else d_model
+    if d_model is None:
+        d_model = cfg.layer_width()
+    d_inner = cfg.width(d_model)
+    N = cfg.d_state
+    if cfg.n_heads is not None and cfg.d_head is not None and cfg.n_heads * cfg.d_head != d_inner:
+        raise ValueError(f"conflicting n_heads={cfg.n_heads}, d_head={cfg.d_head} for d_inner={d_inner}")
+    P = cfg.d_head if cfg.d_head is not None else (d_inner // cfg.n_heads if cfg.n_heads is not None else 64)
+    if d_inner % P:
+        raise ValueError(f"d_inner={d_inner} is not a multiple of d_head={P}")
+    H = d_inner // P
+    blocks = list(cfg.row_blocks or [{"frac": 1.0, "decay": COORD_STATIC}])
+    rot, used = [], 0
+    for i, blk in enumerate(blocks):
+        if not isinstance(blk, dict) or "decay" not in blk:
+            raise TypeError("row_blocks entries are dicts with 'frac' and 'decay'")
+        unknown = set(blk) - {"frac", "decay", "complex", "gate"}
+        if unknown:
+            raise TypeError(f"row_blocks: unknown key(s) {sorted(unknown)}")
+        if blk["decay"] != COORD_STATIC:
+            raise NotImplementedError(f"{who}: row block decay {blk['decay']!r} is not served (only 'coord_static')")
+        if blk.get("gate"):
+            raise NotImplementedError(f"{who}: gated row blocks are not served")
+        rows = N - used if i == len(blocks) - 1 else int(round(float(blk.get("frac", 1.0)) * N))
+        if rows <= 0:
+            raise ValueError("row_blocks: every block needs at least one row and the fractions must sum to 1")
+        cx = bool(blk.get("complex", False))
+        if cx and rows % 2:
+            raise ValueError(f"a rotating block needs an even row count, got {rows}")
+        if cx and used % 2:
+            raise ValueError("a rotating block must start on an even row")
+        rot += [cx] * rows
+        used += rows
+    if used != N:
+        raise ValueError(f"row_blocks sizes sum to {used}, d_state is {N}")
+    has_rot = any(rot)
+    for name, served in (("b_gate", (None, False)), ("c_gate", (None, False)), ("bc_gate_act", (None,)),
+                         ("bc_gate_bias", (None, False)), ("bc_gate_pos", (None,)), ("proj_source", (None, "layer_input")),
+                         ("bc_conv", (None, False)), ("theta_per_head", (None, False)), ("omega_layout", (None, "pair")),
+                         ("theta_init", (None, "kaiming")), ("learnable_h_init", (False,)), ("skip_sharing", ("head",)),
+                         ("bc_bias", (None, "head", "none"))):
+        if getattr(cfg, name) not in served:
+            raise NotImplementedError(f"{who}: {name}={getattr(cfg, name)!r} is not served")
+    rep = [n - 1 if (rot[n] and n % 2) else n for n in range(N)]
+    store = [n for n in range(N) if rep[n] == n]
+    col = {n: i for i, n in enumerate(store)}
+    a_idx = [col[rep[n]] for n in range(N)]
+    # S4D-real ladder restarting in each block; a rotating block's ladder runs over its pairs
+    ladder, pos = [], 0
+    for i, blk in enumerate(blocks):
+        rows = (N - pos) if i == len(blocks) - 1 else int(round(float(blk.get("frac", 1.0)) * N))
+        ladder += list(range(1, (rows // 2 if blk.get("complex", False) else rows) + 1))
+        pos += rows
+    rot_pairs = [k for k in range(N // 2) if rot[2 * k]] if has_rot else []
+    use_trap = cfg.write_rule is None or cfg.write_rule == "trapezoid"
+    bias = "head" if cfg.bc_bias is None else cfg.bc_bias
+    dt_rank = resolve_dt_rank(cfg.dt_rank, d_sel=d_model, heads=H, d_model=d_model, force_dt_dense=cfg.force_dt_dense)
+    if cfg.dt_init not in (None, "random", "constant"):
+        raise ValueError("dt_init must be None, 'random', or 'constant'")
+    return SimpleNamespace(
+        d_model=d_model, d_inner=d_inner, d_conv=cfg.d_conv, H=H, P=P, N=N, K=N // 2, rot=rot, has_rot=has_rot,
+        rot_pairs=rot_pairs, a_idx=a_idx, n_store=len(store), ladder=ladder, use_trap=use_trap,
+        b_norm=cfg.b_norm is None or cfg.b_norm, c_norm=cfg.c_norm is None or cfg.c_norm, bc_bias=bias == "head",
+        learn_theta_freq=has_rot and (cfg.learn_theta_freq is None or cfg.learn_theta_freq),
+        use_theta_h=has_rot and (cfg.use_theta_h is None or cfg.use_theta_h), skip=cfg.skip, out_norm=cfg.out_norm,
+        dt_rank=dt_rank, dt_init=cfg.dt_init, dt_scale=float(cfg.dt_scale), dt_min=cfg.dt_min, dt_max=cfg.dt_max,
+        dt_init_floor=cfg.dt_init_floor, norm_eps=cfg.norm_eps)

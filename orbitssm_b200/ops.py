@@ -573,3 +573,148 @@ class SSDScanFn(torch.autograd.Function):
         return (None, None, None, None, g["du"], cast(g["dBhat"], dts[1]), cast(g["dgBp"], dts[2]),
                 cast(g["dChat"], dts[3]), cast(g["dgCp"], dts[4]), g["dbeta"], g["dgamma"], g["dchi"], g["ddA"], g["dw"],
                 g["dwd"], g["dDg"], g["dS0"], None)
+
+
+# ----------------------------------------------------------------------------------------------------
+#  HybridMamba coordinate-decay scan
+# ----------------------------------------------------------------------------------------------------
+def run_hm(a, name, backward, dtype_code):
+    """One HybridMamba scan launch through the C-ABI.  `a.t` carries the tensors behind the pointers (the CPU host-logic
+    tests replace this function with a torch restatement that reads and fills them)."""
+    fn = _lib.load().orbit_hm_scan_bwd if backward else _lib.load().orbit_hm_scan_fwd
+    with _timed(name, 1):
+        _lib.check(fn(C.byref(a), dtype_code, _stream()), name)
+
+
+_HM_IN = ("x", "delta", "A_log", "Bh", "Ch", "beta_b", "beta_c", "feat", "rot", "theta_h", "lam", "D", "h_init",
+          "write_prev", "theta_init")
+
+
+def _hm_fill(a, t):
+    x = t["x"]
+    B, L, H, P = x.shape
+    N = t["A_log"].shape[-1]
+    a.B, a.L, a.H, a.P, a.N = B, L, H, P, N
+    a.Tc = _lib.HM_CHUNK
+    a.nck = -(-L // a.Tc)
+    if x.is_cuda:
+        for k in _HM_IN:
+            if t.get(k) is not None:
+                setattr(a, k, t[k].data_ptr())
+    a.t = t
+
+
+def hm_scan_fwd(x, delta, A_log, Bh, Ch, beta_b, beta_c, feat, rot, theta_h, lam, D, h_init, write_prev, theta_init):
+    """Forward of the coordinate-decay scan.  x [B, L, H, P] (IO dtype); delta, lam [B, L, H]; A_log [H, P, N];
+    Bh, Ch [B, L, N]; feat [B, L, N/2]; rot uint8 [N/2]; theta_h [H, N/2]; D [H]; carries h_init / write_prev
+    [B, H, P, N], theta_init [B, H, N/2] (fp32; None = zero).  Returns (y [B, L, H, P], h_final, theta_final or None,
+    write_last, saved) with `saved` = (hck, thck), the chunk-entering states the backward replays from."""
+    _require_cuda("hm_scan", x, delta, A_log, Bh, Ch)
+    B, L, H, P = x.shape
+    N = A_log.shape[-1]
+    K = N // 2
+    dev = x.device
+    f32 = dict(device=dev, dtype=torch.float32)
+    t = dict(x=x.contiguous(), delta=_f32(delta), A_log=_f32(A_log), Bh=_f32(Bh), Ch=_f32(Ch), beta_b=_f32(beta_b),
+             beta_c=_f32(beta_c), feat=_f32(feat), rot=rot, theta_h=_f32(theta_h), lam=_f32(lam), D=_f32(D),
+             h_init=_f32(h_init), write_prev=_f32(write_prev), theta_init=_f32(theta_init))
+    a = _lib.HmArgs()
+    _hm_fill(a, t)
+    t["y"] = torch.empty_like(t["x"])
+    t["h_final"] = torch.empty((B, H, P, N), **f32)
+    t["theta_final"] = torch.empty((B, H, K), **f32) if feat is not None else None
+    t["write_last"] = torch.empty((B, H, P, N), **f32)
+    t["hck"] = torch.empty((B, H, a.nck, P, N), **f32)
+    t["thck"] = torch.empty((B, H, a.nck, K), **f32) if feat is not None else None
+    if x.is_cuda:
+        for k in ("y", "h_final", "theta_final", "write_last", "hck", "thck"):
+            if t[k] is not None:
+                setattr(a, k, t[k].data_ptr())
+    run_hm(a, "hm_scan_fwd", False, _dtype_code("hm_scan", x))
+    return t["y"], t["h_final"], t["theta_final"], t["write_last"], (t["hck"], t["thck"])
+
+
+def hm_scan_bwd(x, delta, A_log, Bh, Ch, beta_b, beta_c, feat, rot, theta_h, lam, D, h_init, write_prev, theta_init,
+                saved, dy, dh_final, dtheta_final, dwrite_last):
+    """Backward of the coordinate-decay scan: a dict of gradients keyed like the forward's arguments (fp32; dx in the IO
+    dtype).  Sums over batch (parameters) and heads (shared maps) of the kernel's partial buffers are taken here."""
+    B, L, H, P = x.shape
+    N = A_log.shape[-1]
+    K = N // 2
+    dev = x.device
+    f32 = dict(device=dev, dtype=torch.float32)
+    hck, thck = saved
+    t = dict(x=x.contiguous(), delta=_f32(delta), A_log=_f32(A_log), Bh=_f32(Bh), Ch=_f32(Ch), beta_b=_f32(beta_b),
+             beta_c=_f32(beta_c), feat=_f32(feat), rot=rot, theta_h=_f32(theta_h), lam=_f32(lam), D=_f32(D),
+             h_init=_f32(h_init), write_prev=_f32(write_prev), theta_init=_f32(theta_init))
+    a = _lib.HmArgs()
+    _hm_fill(a, t)
+    t.update(hck=hck, thck=thck, dy=dy.contiguous(), dh_final=_f32(dh_final), dtheta_final=_f32(dtheta_final),
+             dwrite_last=_f32(dwrite_last))
+    t["dx"] = torch.empty_like(t["x"])
+    t["ddelta"] = torch.empty((B, L, H), **f32)
+    t["dlam"] = torch.empty((B, L, H), **f32) if lam is not None else None
+    t["dA_log_part"] = torch.empty((B, H, P, N), **f32)
+    t["dBh_part"] = torch.empty((H, B, L, N), **f32)
+    t["dCh_part"] = torch.empty((H, B, L, N), **f32)
+    t["dbeta_b_part"] = torch.empty((B, H, N), **f32) if beta_b is not None else None
+    t["dbeta_c_part"] = torch.empty((B, H, N), **f32) if beta_c is not None else None
+    t["dfeat_part"] = torch.empty((H, B, L, K), **f32) if feat is not None else None
+    t["dtheta_h_part"] = torch.empty((B, H, K), **f32) if theta_h is not None else None
+    t["dD_part"] = torch.empty((B, H), **f32) if D is not None else None
+    t["dh_init"] = torch.empty((B, H, P, N), **f32)
+    t["dwrite_prev"] = torch.empty((B, H, P, N), **f32) if lam is not None else None
+    t["dtheta_init"] = torch.empty((B, H, K), **f32) if feat is not None else None
+    if x.is_cuda:
+        for k in ("hck", "thck", "dy", "dh_final", "dtheta_final", "dwrite_last", "dx", "ddelta", "dlam", "dA_log_part",
+                  "dBh_part", "dCh_part", "dbeta_b_part", "dbeta_c_part", "dfeat_part", "dtheta_h_part", "dD_part",
+                  "dh_init", "dwrite_prev", "dtheta_init"):
+            if t[k] is not None:
+                setattr(a, k, t[k].data_ptr())
+    run_hm(a, "hm_scan_bwd", True, _dtype_code("hm_scan", x))
+
+    def s0(v):
+        return None if v is None else v.sum(0)
+
+    return dict(x=t["dx"], delta=t["ddelta"], A_log=t["dA_log_part"].sum(0), Bh=t["dBh_part"].sum(0), Ch=t["dCh_part"].sum(0),
+                beta_b=s0(t["dbeta_b_part"]), beta_c=s0(t["dbeta_c_part"]), feat=s0(t["dfeat_part"]),
+                theta_h=s0(t["dtheta_h_part"]), lam=t["dlam"], D=s0(t["dD_part"]), h_init=t["dh_init"],
+                write_prev=t["dwrite_prev"], theta_init=t["dtheta_init"])
+
+
+class HMScanFn(torch.autograd.Function):
+    """The coordinate-decay scan as one autograd node: carries in (h_init, write_prev, theta_init), carries out
+    (h_final, theta_final, write_last), exact gradients through all of them."""
+
+    @staticmethod
+    def forward(ctx, rot, x, delta, A_log, Bh, Ch, beta_b, beta_c, feat, theta_h, lam, D, h_init, write_prev, theta_init):
+        ins = [None if v is None else v.detach() for v in
+               (x, delta, A_log, Bh, Ch, beta_b, beta_c, feat, theta_h, lam, D, h_init, write_prev, theta_init)]
+        x_, delta_, A_, Bh_, Ch_, bb_, bc_, feat_, thh_, lam_, D_, h0_, wp_, th0_ = ins
+        y, hN, thN, wl, saved = hm_scan_fwd(x_, delta_, A_, Bh_, Ch_, bb_, bc_, feat_, rot, thh_, lam_, D_, h0_, wp_, th0_)
+        ctx.save_for_backward(*ins, saved[0], saved[1])
+        ctx.rot = rot
+        ctx.in_dtypes = [None if v is None else v.dtype for v in
+                         (x, delta, A_log, Bh, Ch, beta_b, beta_c, feat, theta_h, lam, D, h_init, write_prev, theta_init)]
+        ctx.set_materialize_grads(False)
+        if thN is None:
+            thN = x.new_zeros((), dtype=torch.float32)
+        return y, hN, thN, wl
+
+    @staticmethod
+    def backward(ctx, dy, dhN, dthN, dwl):
+        *ins, hck, thck = ctx.saved_tensors
+        x, delta, A_log, Bh, Ch, bb, bc, feat, thh, lam, D, h0, wp, th0 = ins
+        if dy is None:
+            dy = torch.zeros_like(x)
+        if feat is None:
+            dthN = None
+        g = hm_scan_bwd(x, delta, A_log, Bh, Ch, bb, bc, feat, ctx.rot, thh, lam, D, h0, wp, th0, (hck, thck), dy.to(x.dtype),
+                        dhN, dthN, dwl)
+        keys = ("x", "delta", "A_log", "Bh", "Ch", "beta_b", "beta_c", "feat", "theta_h", "lam", "D", "h_init", "write_prev",
+                "theta_init")
+        out = []
+        for k, v, dt in zip(keys, ins, ctx.in_dtypes):
+            gv = g[k] if v is not None else None
+            out.append(None if gv is None else gv.to(dt))
+        return (None, *out)

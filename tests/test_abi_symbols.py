@@ -23,9 +23,13 @@ def test_every_declared_symbol_is_exported_and_bound():
     assert sorted(_lib.SIGNATURES) == names, "ctypes signatures and header declarations differ"
 
 
-def test_scan_args_mirror_matches_header_field_order():
+import pytest
+
+
+@pytest.mark.parametrize("struct,mirror", [("orbit_scan_args", "ScanArgs"), ("orbit_hm_args", "HmArgs")])
+def test_args_mirror_matches_header_field_order(struct, mirror):
     text = open(os.path.join(ROOT, "include", "orbit_b200.h")).read()
-    body = re.search(r"typedef struct orbit_scan_args \{(.*?)\} orbit_scan_args;", text, flags=re.S).group(1)
+    body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (struct, struct), text, flags=re.S).group(1)
     body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
     fields = []
     for decl in body.split(";"):
@@ -35,7 +39,7 @@ def test_scan_args_mirror_matches_header_field_order():
         names = decl.split(",")
         first = names[0].split()[-1]
         fields += [first.lstrip("*")] + [n.strip().lstrip("*") for n in names[1:]]
-    assert fields == [f[0] for f in _lib.ScanArgs._fields_]
+    assert fields == [f[0] for f in getattr(_lib, mirror)._fields_]
 
 
 def test_pure_queries_run_on_cpu():

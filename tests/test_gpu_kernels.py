@@ -301,3 +301,76 @@ def test_scan_tc_mimo_backward(case):
     for k, v in g.items():
         if v is not None:
             assert torch.equal(v, g2[k]), ("not reproducible", k)
+
+
+# ---------------------------------------------------------------------------------------------------- HybridMamba scan
+def hm_case(B, L, H, P, N, nrot, trap, carries, dtype, seed=0):
+    g = torch.Generator().manual_seed(seed)
+
+    def rn(*s, scale=1.0):
+        return torch.randn(*s, generator=g) * scale
+
+    K = N // 2
+    c = {}
+    c["x"] = rn(B, L, H, P).to(dtype).to(DEV)
+    c["delta"] = torch.nn.functional.softplus(rn(B, L, H) - 2.0).to(DEV)
+    c["A_log"] = torch.log(1 + 15 * torch.rand(H, P, N, generator=g)).to(DEV)
+    if nrot:                                              # rotating pairs share one modulus
+        A = c["A_log"].clone()
+        A[..., N - 2 * nrot + 1::2] = A[..., N - 2 * nrot::2]
+        c["A_log"] = A
+    c["Bh"], c["Ch"] = rn(B, L, N).to(DEV), rn(B, L, N).to(DEV)
+    c["beta_b"], c["beta_c"] = rn(H, N, scale=0.3).to(DEV), rn(H, N, scale=0.3).to(DEV)
+    rot = torch.zeros(K, dtype=torch.uint8)
+    rot[K - nrot:] = 1
+    c["rot"] = rot.to(DEV) if nrot else None
+    c["feat"] = (rn(B, L, K, scale=2.0) * rot).to(DEV) if nrot else None
+    c["theta_h"] = (rn(H, K, scale=0.5) * rot).to(DEV) if nrot else None
+    c["lam"] = torch.sigmoid(rn(B, L, H)).to(DEV) if trap else None
+    c["D"] = (1 + rn(H, scale=0.3)).to(DEV)
+    c["h_init"] = rn(B, H, P, N).to(DEV) if carries else None
+    c["write_prev"] = rn(B, H, P, N).to(DEV) if (carries and trap) else None
+    c["theta_init"] = (rn(B, H, K) * rot).to(DEV) if (carries and nrot) else None
+    c["dy"] = rn(B, L, H, P).to(dtype).to(DEV)
+    c["dh_final"] = rn(B, H, P, N).to(DEV)
+    c["dtheta_final"] = (rn(B, H, K) * rot).to(DEV) if nrot else None
+    c["dwrite_last"] = rn(B, H, P, N).to(DEV)
+    return c
+
+
+HM_CASES = [
+    # B, L, H, P, N, rotating pairs, trapezoid, carries
+    (2, 40, 3, 16, 16, 4, True, True),
+    (1, 77, 2, 64, 64, 16, True, True),
+    (2, 19, 2, 8, 8, 0, False, False),
+    (1, 100, 2, 32, 128, 64, True, False),
+    (1, 33, 1, 64, 64, 0, True, True),
+]
+HM_ARGS = ("x", "delta", "A_log", "Bh", "Ch", "beta_b", "beta_c", "feat", "rot", "theta_h", "lam", "D", "h_init", "write_prev",
+           "theta_init")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", HM_CASES)
+def test_hm_scan(dtype, case):
+    """Coordinate-decay scan kernels against the fp64 token loop on the same (dtype-rounded) inputs: outputs and carries
+    within 2e-4 (fp32) / the bf16 output rounding, every gradient within 5e-3 (fp32 arithmetic, fast exp), results
+    bitwise reproducible."""
+    c = hm_case(*case, dtype)
+    args = [c[k] for k in HM_ARGS]
+    y, hN, thN, wl, saved = ops.hm_scan_fwd(*args)
+    ry, rh, rth, rwl = R.hm_scan_fwd(*args)
+    assert rel(y, ry) < (6e-3 if dtype == torch.bfloat16 else 2e-4), ("y", rel(y, ry))
+    assert rel(hN, rh) < 2e-4 and rel(wl, rwl) < 1e-5, (rel(hN, rh), rel(wl, rwl))
+    if thN is not None:
+        assert rel(thN, rth) < 1e-5
+    seeds = (c["dy"], c["dh_final"], c["dtheta_final"], c["dwrite_last"])
+    g = ops.hm_scan_bwd(*args, saved, *seeds)
+    rg = R.hm_scan_bwd(*args, *seeds)
+    errs = {k: rel(g[k], v) for k, v in rg.items() if v is not None and g.get(k) is not None}
+    bad = {k: e for k, e in errs.items() if not e < (8e-3 if (k == "x" and dtype == torch.bfloat16) else 5e-3)}
+    assert not bad, (bad, errs)
+    g2 = ops.hm_scan_bwd(*args, saved, *seeds)
+    for k, v in g.items():
+        if v is not None:
+            assert torch.equal(v, g2[k]), ("not reproducible", k)

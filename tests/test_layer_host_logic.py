@@ -155,3 +155,79 @@ def test_state_lifecycle(cpu_kernels):
     assert all(v.dtype == torch.bfloat16 for v in s2.values())          # a returned carry keeps the supplied dtype
     layer.reset_state(s1, mask=torch.tensor([True, False]))
     assert float(s1["hidden_state"][0].abs().sum()) == 0.0 and float(s1["hidden_state"][1].abs().sum()) > 0.0
+
+
+# ---------------------------------------------------------------------------------------------------- HybridMamba
+from conftest import HM_GOLDEN_CASES                                    # noqa: E402
+from orbitssm_b200.config import HybridMambaConfig                      # noqa: E402
+from orbitssm_b200.hybrid_mamba import HybridMambaSSM                   # noqa: E402
+
+
+@pytest.fixture
+def cpu_hm_kernels(monkeypatch):
+    for name in ("conv1d_fwd", "conv1d_bwd", "gate_norm_fwd", "gate_norm_bwd", "run_hm"):
+        monkeypatch.setattr(ops, name, getattr(R, name))
+    monkeypatch.setattr(ops, "on_device", lambda t: True)
+    monkeypatch.setattr(ops, "_require_cuda", lambda who, *t: None)
+    monkeypatch.setattr(ops, "_dtype_code", lambda who, t: 0)
+
+
+def _run_hm(layer, rec, x, dy, state):
+    x = x.clone().requires_grad_(True)
+    if state is not None:
+        state = {k: v.clone().to(torch.float32).requires_grad_(True) for k, v in state.items()}
+    layer.zero_grad()
+    y, st = layer(x, state=state, return_state=True)
+    loss = (y * dy).sum()
+    for k, g in rec["gs"].items():
+        if k in st:
+            loss = loss + (st[k] * g).sum()
+    loss.backward()
+    grads = {n: p.grad for n, p in layer.named_parameters() if p.grad is not None}
+    grads["x"] = x.grad
+    if state is not None:
+        for k, v in state.items():
+            if v.grad is not None:
+                grads["state." + k] = v.grad
+    return y.detach(), st, grads
+
+
+@pytest.mark.parametrize("name", HM_GOLDEN_CASES)
+def test_hm_layer_matches_reference(name, cpu_hm_kernels):
+    """`HybridMambaSSM` host logic (fused projection, maps, pair-tied stores, carries, autograd wiring) against the
+    reference's fp64 results, with the C-ABI kernels replaced by their torch restatements."""
+    rec = load_golden(name)
+    layer = HybridMambaSSM(HybridMambaConfig(**rec["config"]))
+    layer.load_state_dict(rec["state_dict"], strict=True)
+    got = _run_hm(layer, rec, rec["x"], rec["dy"], None)
+    _check(got, rec["f64"], 2e-4, name)
+    c = rec["f64_cont"]
+    s = c["split"]
+    got = _run_hm(layer, rec, rec["x"][:, s:], rec["dy"][:, s:], c["state_in"])
+    _check(got, c, 2e-4, name + " continuation")
+
+
+@pytest.mark.parametrize("name", HM_GOLDEN_CASES)
+def test_hm_same_seed_same_weights(name):
+    """Parameter creation order and initialisers match the reference: the same torch seed draws the same weights."""
+    rec = load_golden(name)
+    torch.manual_seed(0)
+    layer = HybridMambaSSM(HybridMambaConfig(**rec["config"]))
+    sd = layer.state_dict()
+    assert list(sd) == list(rec["fresh_state_dict"]), (list(sd), list(rec["fresh_state_dict"]))
+    for k, v in rec["fresh_state_dict"].items():
+        assert sd[k].shape == v.shape and torch.equal(sd[k].float(), v), k
+
+
+def test_hm_refusals():
+    with pytest.raises(NotImplementedError):
+        HybridMambaSSM(HybridMambaConfig(d_model=32, d_state=8, d_head=8, row_blocks=[{"frac": 1.0, "decay": "coord_dynamic"}]))
+    with pytest.raises(NotImplementedError):
+        HybridMambaSSM(HybridMambaConfig(d_model=32, d_state=8, d_head=8, b_gate=True))
+    with pytest.raises(ValueError):
+        HybridMambaConfig(d_model=32, d_ssm_in=2)
+    layer = HybridMambaSSM(HybridMambaConfig(d_model=32, d_state=8, d_head=8))
+    with pytest.raises(ValueError):
+        layer(torch.zeros(1, 4, 32))                    # CPU tensor: refused by name, no CPU route
+    with pytest.raises(ValueError):
+        layer.set_execution({"precision": "ieee"})
