@@ -1,6 +1,6 @@
 """Benchmark of the SSD-MIMO layer hot path: layer forward + backward tokens/s on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg3|cfg2|cfg5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5a|cfg5b|cfg5|cfg4|cfg3|cfg2] [--impl reference]
 
 One "step" = y = layer(x); y.backward(dy) on one batch of synthetic input (x ~ N(0,1), fixed random dy; bf16
 activations over fp32 parameters).  Workloads (BASELINE.json `configs`):
@@ -9,6 +9,8 @@ activations over fp32 parameters).  Workloads (BASELINE.json `configs`):
   cfg5b BASELINE config 5b: one d_model-2048 layer, B = 1, L = 262144 split over the GPUs (context parallel, strong scaling)
   cfg3  SSD-MIMO rank-4 layer, d_model 2048, x [4, 4096, 2048] (rank-4 tcgen05 tiles); at N = 1 the default run also
         measures it briefly and reports it under "other_workloads"
+  cfg4  HybridMamba layer (coordinate-decay rows, half of them rotating pairs), d_model 1024, x [8, 2048, 1024]; also
+        reported under "other_workloads" by the default run
   cfg2  Mamba-2 preset SISO layer, d_model 1024, x [8, 2048, 1024]
   cfg5  one layer of cfg5a at x [4, 4096, 2048]
 With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same per-GPU batch on its own shard of the
@@ -39,6 +41,9 @@ WORKLOADS = {
                  desc="SSD-MIMO SISO Mamba-2 preset (H=32, P=64, N=128) layer, d_model 1024, x [8,2048,1024]"),
     "cfg5": dict(B=4, L=4096, d_model=2048, kind="m2", chunk_acct=64,
                  desc="SSD-MIMO SISO Mamba-2 preset (H=64, P=64, N=128) layer, d_model 2048, x [4,4096,2048]"),
+    "cfg4": dict(B=8, L=2048, d_model=1024, kind="hm", chunk_acct=32,
+                 desc="HybridMamba layer (H=32, P=64, N=64: 32 real rows + 16 rotating pairs, coord_static, trapezoid, gated "
+                      "RMSNorm), d_model 1024, x [8,2048,1024]"),
     # BASELINE config 5: (a) a 4-block BlockStack of the d2048 SISO layer, batch-sharded, 8 rows per GPU (B = 64 at
     # 8 GPUs); (b) one layer, B = 1, L = 262144, context-parallel over the GPUs (strong scaling)
     "cfg5a": dict(B=8, L=4096, d_model=2048, kind="m2", chunk_acct=64, blocks=4,
@@ -57,18 +62,30 @@ WORKLOADS = {
 
 
 def make_config(wl):
-    from orbitssm_b200 import SSDMimoConfig, mamba2_config
+    from orbitssm_b200 import HybridMambaConfig, SSDMimoConfig, mamba2_config
     if wl["kind"] == "m2":
         return mamba2_config(wl["d_model"])
+    if wl["kind"] == "hm":
+        return HybridMambaConfig(d_model=wl["d_model"], d_state=64, expand=2, d_conv=4, out_norm=True,
+                                 row_blocks=[{"frac": .5, "decay": "coord_static"},
+                                             {"frac": .5, "decay": "coord_static", "complex": True}])
     return SSDMimoConfig(d_model=wl["d_model"], expand=2.0, d_state=128, d_ssm_in=4, d_ssm_out=4, n_heads=64, d_head=64,
                          d_conv=4, write_rule="trapezoid", row_blocks=[{"frac": 1.0, "decay": "head_static"}])
 
 
+def make_mixer(cfg, execution=None):
+    from orbitssm_b200 import HybridMambaConfig, HybridMambaSSM, SSDMimoSSM
+    if isinstance(cfg, HybridMambaConfig):
+        return HybridMambaSSM(cfg)
+    return SSDMimoSSM(cfg, execution=execution)
+
+
 def init_params(layer, seed=0):
-    """A_log <- log U(log 1, log 16) per (head, sibling) as BASELINE.json states; everything else default init."""
+    """A_log <- log U(log 1, log 16) per (head, sibling) as BASELINE.json states; everything else default init
+    (HybridMamba keeps its default per-coordinate ladder)."""
     g = torch.Generator().manual_seed(seed)
     with torch.no_grad():
-        if hasattr(layer, "A_log"):
+        if hasattr(layer, "A_log") and layer.config_family == "ssd_mimo":
             hi = float(torch.log(torch.tensor(16.0)))
             layer.A_log.copy_(torch.rand(layer.A_log.shape, generator=g) * hi)      # A = exp(A_log) in [1, 16], log-uniform
 
@@ -131,7 +148,30 @@ def peaks():
 # ----------------------------------------------------------------------------------------------------
 #  CPU arm: the reference's CPU route restated in oracle/ (the only place the bench runs it), bounded sample
 # ----------------------------------------------------------------------------------------------------
+def cpu_step_time_hm(wl, sample_B, sample_L, steps, warmup):
+    from oracle import hm_oracle
+    torch.manual_seed(0)
+    cfg = make_config(wl)
+    layer = make_mixer(cfg)
+    prm = {k: v.detach().clone().requires_grad_(v.is_floating_point() and v.dim() > 0) for k, v in layer.state_dict().items()}
+    x = torch.randn(sample_B, sample_L, wl["d_model"], requires_grad=True)
+    dy = torch.randn(sample_B, sample_L, wl["d_model"])
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        hm_oracle.hm_layer(cfg.to_dict(), prm, x).backward(dy)
+        dt = time.perf_counter() - t0
+        for v in prm.values():
+            v.grad = None
+        x.grad = None
+        if i >= warmup:
+            times.append(dt)
+    return statistics.median(times)
+
+
 def cpu_step_time(wl, sample_B, sample_L, steps, warmup):
+    if wl["kind"] == "hm":
+        return cpu_step_time_hm(wl, sample_B, sample_L, steps, warmup)
     from orbitssm_b200.config import resolve_ssd_spec
     from orbitssm_b200 import SSDMimoSSM
     from oracle import ssd_oracle
@@ -186,9 +226,8 @@ def run_reference(args, wl, name):
 
 def side_measure(wl, dev, steps=2, warmup=1):
     """A short device-timed measurement of another workload (same step definition), reported beside the headline."""
-    from orbitssm_b200 import SSDMimoSSM
     torch.manual_seed(0)
-    layer = SSDMimoSSM(make_config(wl), execution={"precision": "io"})
+    layer = make_mixer(make_config(wl), execution={"precision": "io"})
     init_params(layer)
     layer = layer.to(dev)
     x = torch.randn(wl["B"], wl["L"], wl["d_model"], device=dev).to(torch.bfloat16).requires_grad_(True)
@@ -226,7 +265,7 @@ def main():
     if args.impl == "reference":
         return run_reference(args, wl, args.workload)
 
-    from orbitssm_b200 import SSDMimoSSM, ops
+    from orbitssm_b200 import ops
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -241,7 +280,7 @@ def main():
     torch.manual_seed(0)
     cfg = make_config(wl)
     nblocks = wl.get("blocks", 1)
-    mixers = [SSDMimoSSM(cfg, execution={"precision": "io"}) for _ in range(nblocks)]
+    mixers = [make_mixer(cfg, execution={"precision": "io"}) for _ in range(nblocks)]
     for m in mixers:
         init_params(m)
     mixer0 = mixers[0]
@@ -346,12 +385,28 @@ def main():
     value = tokens / (total_ms * 1e-3)
     pk = peaks()
     spec = mixer0.spec
-    fl = scan_flops(spec, B, L, wl["chunk_acct"])
     kern_ms = {k: statistics.mean(v) for k, v in per_kernel.items()}
-    scan_names = [k for k in kern_ms if k in fl]
-    dom = max(scan_names, key=lambda k: kern_ms[k]) if scan_names else None
     roofline = None
-    if dom:
+    fl, dom = {}, None
+    if wl["kind"] == "hm":
+        # the coordinate scan has no contraction: it is bound by exp (MUFU) and FP32 issue; HBM is the nearest roofline
+        # the contract names.  Algorithmic bytes = compulsory IO of the launch: drive in, output (or its gradient) in/out,
+        # maps and clocks (and their gradients) once; checkpoints and partial-sum buffers are not counted.
+        es, D_in, Nn, Hh = 2, spec.d_inner, spec.N, spec.H
+        maps = B * L * (2 * Nn + spec.K + 2 * Hh) * 4
+        byts = {"hm_scan_fwd": B * L * D_in * es * 2 + maps, "hm_scan_bwd": B * L * D_in * es * 3 + 2 * maps}
+        dom = max(byts, key=lambda k: kern_ms.get(k, 0.0))
+        ach = byts[dom] / (kern_ms[dom] * 1e-3) / 1e9
+        upd = B * L * Hh * spec.P * Nn / (kern_ms[dom] * 1e-3)
+        roofline = dict(bound="hbm", kernel=dom, achieved=ach, peak=pk["hbm_gbs"], unit="GB/s", frac=ach / pk["hbm_gbs"],
+                        traffic=None, peak_source=pk["source"] + " (copy)", ms_per_launch=kern_ms[dom],
+                        note="issue-bound (one exp + ~10 FP32 ops per state element per token), not HBM-bound",
+                        state_updates_per_s=upd, route=mixer0.last_route())
+    else:
+        fl = scan_flops(spec, B, L, wl["chunk_acct"])
+        scan_names = [k for k in kern_ms if k in fl]
+        dom = max(scan_names, key=lambda k: kern_ms[k]) if scan_names else None
+    if dom and wl["kind"] != "hm":
         ach = fl[dom] / (kern_ms[dom] * 1e-3) / 1e12
         roofline = dict(bound="tensor", kernel=dom, achieved=ach, peak=pk["tflops"], unit="TFLOP/s", frac=ach / pk["tflops"],
                         traffic=None, peak_source=pk["source"] + " (sustained bf16 GEMM)", ms_per_launch=kern_ms[dom],
@@ -377,7 +432,7 @@ def main():
                                "sample": f"x [{sB},{sL},{dm}] fp32 of the same layer, median of 3 steps after 1 warm-up",
                                "host_cpus": os.cpu_count()}
     if world == 1 and args.workload == "cfg5a" and not args.no_cpu_baseline:
-        out["other_workloads"] = {"cfg3": side_measure(WORKLOADS["cfg3"], dev)}
+        out["other_workloads"] = {"cfg3": side_measure(WORKLOADS["cfg3"], dev), "cfg4": side_measure(WORKLOADS["cfg4"], dev)}
     print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

@@ -116,3 +116,64 @@ def test_split_equals_whole_and_is_reproducible():
     assert rel(torch.cat(ys, 1), y_all) < 1e-5
     for k in s_all:
         assert rel(st[k], s_all[k]) < 1e-5, k
+
+
+# ---------------------------------------------------------------------------------------------------- HybridMamba
+from conftest import HM_GOLDEN_CASES                                    # noqa: E402
+from orbitssm_b200.config import HybridMambaConfig                      # noqa: E402
+from orbitssm_b200.hybrid_mamba import HybridMambaSSM                   # noqa: E402
+
+
+def run_hm(layer, rec, x, dy, state, io):
+    x = x.to(DEV).to(io).requires_grad_(True)
+    if state is not None:
+        state = {k: v.to(DEV).float().requires_grad_(True) for k, v in state.items()}
+    layer.zero_grad()
+    y, st = layer(x, state=state, return_state=True)
+    loss = (y.float() * dy.to(DEV)).sum()
+    for k, g in rec["gs"].items():
+        if k in st:
+            loss = loss + (st[k] * g.to(DEV)).sum()
+    loss.backward()
+    grads = {n: p.grad for n, p in layer.named_parameters() if p.grad is not None}
+    grads["x"] = x.grad
+    if state is not None:
+        for k, v in state.items():
+            if v.grad is not None:
+                grads["state." + k] = v.grad
+    return y.detach(), st, grads
+
+
+@pytest.mark.parametrize("io", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", HM_GOLDEN_CASES)
+def test_hm_layer_matches_reference(name, io):
+    """The whole `HybridMambaSSM` layer on the CUDA kernels against the reference's fp64 results (same bounds as the
+    SSD layer), first segment and continuation from the reference's own carried State."""
+    rec = load_golden(name)
+    layer = HybridMambaSSM(HybridMambaConfig(**rec["config"]))
+    layer.load_state_dict(rec["state_dict"], strict=True)
+    layer = layer.to(DEV)
+    got = run_hm(layer, rec, rec["x"], rec["dy"], None, io)
+    check(got, rec["f64"], BOUNDS[io], name)
+    c = rec["f64_cont"]
+    s = c["split"]
+    got = run_hm(layer, rec, rec["x"][:, s:], rec["dy"][:, s:], c["state_in"], io)
+    check(got, c, BOUNDS[io], name + " continuation")
+
+
+def test_hm_split_equals_whole_and_is_reproducible():
+    rec = load_golden("hm_small")
+    layer = HybridMambaSSM(HybridMambaConfig(**rec["config"]))
+    layer.load_state_dict(rec["state_dict"], strict=True)
+    layer = layer.to(DEV)
+    x = rec["x"].to(DEV)
+    y_all, s_all = layer(x, return_state=True)
+    y_again, _ = layer(x, return_state=True)
+    assert torch.equal(y_all, y_again)
+    st, ys = None, []
+    for a, b in ((0, 5), (5, 6), (6, 33), (33, 40)):
+        y, st = layer(x[:, a:b], state=st, return_state=True)
+        ys.append(y)
+    assert rel(torch.cat(ys, 1), y_all) < 1e-5
+    for k in s_all:
+        assert rel(st[k], s_all[k]) < 1e-5, k
