@@ -56,6 +56,8 @@ WORKLOADS = {
     # (sized so that the scan kernels launch exactly one CTA per SM: 4 x 37 chunks = 148)
     "cfg5s": dict(B=4, L=4736, d_model=2048, kind="m2", chunk_acct=64,
                   desc="profiling case: the cfg5 layer at x [4,4736,2048]"),
+    "cfg4s": dict(B=4, L=1024, d_model=1024, kind="hm", chunk_acct=32,
+                  desc="profiling case: the cfg4 layer at x [4,1024,1024]"),
     "cfg3s": dict(B=4, L=1184, d_model=2048, kind="mimo4", chunk_acct=32,
                   desc="profiling case: the cfg3 layer at x [4,1184,2048]"),
 }
