@@ -63,6 +63,16 @@ WORKLOADS = {
 }
 
 
+# DRAM bytes per token (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the profiling cases cfg5s /
+# cfg3s / cfg4s, divided by their token counts; profiles/scan_dram_traffic.md).  Traffic grows in proportion to the tokens
+# a launch processes, so `roofline.traffic` of a full-size launch is this figure times its tokens.
+DRAM_BYTES_PER_TOKEN = {
+    "m2": {"scan_chunk_grads": 68451.0, "scan_chunk_out": 23852.0, "scan_chunk_state": 22452.0},
+    "mimo4": {"scan_chunk_grads": 416387.0},
+    "hm": {"hm_scan_bwd": 42650.0, "hm_scan_fwd": 12522.0},
+}
+
+
 def make_config(wl):
     from orbitssm_b200 import HybridMambaConfig, SSDMimoConfig, mamba2_config
     if wl["kind"] == "m2":
@@ -413,6 +423,11 @@ def main():
         roofline = dict(bound="tensor", kernel=dom, achieved=ach, peak=pk["tflops"], unit="TFLOP/s", frac=ach / pk["tflops"],
                         traffic=None, peak_source=pk["source"] + " (sustained bf16 GEMM)", ms_per_launch=kern_ms[dom],
                         route=mixer0.last_route())
+    if roofline is not None:
+        per_tok = DRAM_BYTES_PER_TOKEN.get(wl["kind"], {}).get(roofline["kernel"])
+        if per_tok is not None:
+            roofline["traffic"] = per_tok * B * L
+            roofline["traffic_source"] = "ncu capture of the profiling case, scaled by tokens per launch"
     out = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong" if wl.get("cp") else "weak", "vs_baseline": None,

@@ -38,7 +38,7 @@ def conv1d_fwd(x, weight, bias, window, silu=True, compute=torch.float64):
     return y.to(x.dtype)
 
 
-def conv1d_bwd(x, weight, bias, window, dy, silu=True, want_dwindow=False, compute=torch.float64):
+def conv1d_bwd(x, weight, bias, window, dy, silu=True, want_dwindow=False, dx_out=None, compute=torch.float64):
     xs = _f(x, compute).requires_grad_(True)
     ws = _f(weight, compute).requires_grad_(True)
     bs = _f(bias, compute).requires_grad_(True) if bias is not None else None
@@ -52,8 +52,11 @@ def conv1d_bwd(x, weight, bias, window, dy, silu=True, want_dwindow=False, compu
     if want_dwindow and wins is not None:
         dwin = g[id(wins)].to(torch.float32).clone()
         dwin[..., 0] = 0.0                       # slot 0 of the window never enters the conv
-    return (g[id(xs)].to(x.dtype), dwin, g[id(ws)].to(torch.float32),
-            None if bs is None else g[id(bs)].to(torch.float32))
+    dx = g[id(xs)].to(x.dtype)
+    if dx_out is not None:
+        dx_out.copy_(dx)
+        dx = dx_out
+    return (dx, dwin, g[id(ws)].to(torch.float32), None if bs is None else g[id(bs)].to(torch.float32))
 
 
 # ---- gate + norm -------------------------------------------------------------------------------------
@@ -70,7 +73,7 @@ def gate_norm_fwd(y, z, w, eps, compute=torch.float64):
     return out.to(y.dtype), None if rstd is None else rstd.to(torch.float32)
 
 
-def gate_norm_bwd(y, z, w, rstd, dout, eps=1e-5, compute=torch.float64):
+def gate_norm_bwd(y, z, w, rstd, dout, eps=1e-5, dz_out=None, compute=torch.float64):
     ys = _f(y, compute).requires_grad_(True)
     zs = _f(z, compute).requires_grad_(True) if z is not None else None
     ws = _f(w, compute).requires_grad_(True) if w is not None else None
@@ -78,8 +81,11 @@ def gate_norm_bwd(y, z, w, rstd, dout, eps=1e-5, compute=torch.float64):
     with torch.enable_grad():
         out, _ = _gate_norm(ys, zs, ws, eps)
         gs = dict(zip([id(t) for t in ins], torch.autograd.grad(out, ins, _f(dout, compute))))
-    return (gs[id(ys)].to(y.dtype), None if zs is None else gs[id(zs)].to(y.dtype),
-            None if ws is None else gs[id(ws)].to(torch.float32))
+    dz = None if zs is None else gs[id(zs)].to(y.dtype)
+    if dz is not None and dz_out is not None:
+        dz_out.copy_(dz)
+        dz = dz_out
+    return (gs[id(ys)].to(y.dtype), dz, None if ws is None else gs[id(ws)].to(torch.float32))
 
 
 # ---- scan --------------------------------------------------------------------------------------------

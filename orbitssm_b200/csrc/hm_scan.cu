@@ -144,6 +144,24 @@ __device__ __forceinline__ float cross_group_sum(float v, int NG) {
   return v;
 }
 
+// Sums 4 per-row partials over the NG lanes of a row group with a reduce-scatter (NG >= 4): 3 + log2(NG/4) shuffles
+// instead of 4 log2(NG).  Every lane returns the total of row `row` (rows are dealt by two bits of the lane's position).
+__device__ __forceinline__ float group_reduce4(const float (&v)[4], int NG, int ng, int& row) {
+  const int hA = NG >> 1, hB = NG >> 2;
+  const bool upA = (ng & hA) != 0, upB = (ng & hB) != 0;
+  float k0 = upA ? v[2] : v[0], k1 = upA ? v[3] : v[1];
+  const float s0 = upA ? v[0] : v[2], s1 = upA ? v[1] : v[3];
+  k0 += __shfl_xor_sync(0xffffffffu, s0, hA);
+  k1 += __shfl_xor_sync(0xffffffffu, s1, hA);
+  float k = upB ? k1 : k0;
+  const float s = upB ? k0 : k1;
+  k += __shfl_xor_sync(0xffffffffu, s, hB);
+  for (int o = hB >> 1; o > 0; o >>= 1) k += __shfl_xor_sync(0xffffffffu, k, o);
+  row = (upA ? 2 : 0) + (upB ? 1 : 0);
+  return k;
+}
+__device__ __forceinline__ float pick4(const float (&v)[4], int i) { return i == 0 ? v[0] : i == 1 ? v[1] : i == 2 ? v[2] : v[3]; }
+
 struct HmThread {
   int pg, ng;        // channel group (4 channels), row group (4 rows)
   bool active;
@@ -218,19 +236,32 @@ __global__ void __launch_bounds__(256) hm_fwd_kernel(const HmArgs a) {
     }
     hm_build_tile<T, false>(a, g, tl, b, h, t0);
     const int nv = min(HM_TT, a.L - t0);
-    for (int tt = 0; tt < nv; ++tt) {
-      const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + (tt + 1) * g.P + th.pg * 4);
-      const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + (tt + 1) * g.N + th.ng * 4);
-      const float4 c4 = *reinterpret_cast<const float4*>(tl.Ct + (tt + 1) * g.N + th.ng * 4);
-      hm_step(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1], trap);
-      const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, xv[4] = {x4.x, x4.y, x4.z, x4.w};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float yp = 0.f;
+    for (int tt = 0; tt < HM_TT; ++tt) {
+      if (tt < nv) {
+        const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + (tt + 1) * g.P + th.pg * 4);
+        const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + (tt + 1) * g.N + th.ng * 4);
+        const float4 c4 = *reinterpret_cast<const float4*>(tl.Ct + (tt + 1) * g.N + th.ng * 4);
+        hm_step(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1], trap);
+        const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, xv[4] = {x4.x, x4.y, x4.z, x4.w};
+        float yp[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) yp = fmaf(cv[j], hs[i * 4 + j], yp);
-        yp = group_sum(yp, g.NG);
-        if (th.active && th.ng == 0) ys[tt * g.P + th.pg * 4 + i] = fmaf(Dh, xv[i], yp);
+        for (int i = 0; i < 4; ++i) {
+          yp[i] = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) yp[i] = fmaf(cv[j], hs[i * 4 + j], yp[i]);
+        }
+        if (g.NG >= 4) {
+          int row;
+          const float tot = group_reduce4(yp, g.NG, th.ng, row);
+          if (th.active && (th.ng & ((g.NG >> 2) - 1)) == 0) ys[tt * g.P + th.pg * 4 + row] = fmaf(Dh, pick4(xv, row), tot);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float tot = group_sum(yp[i], g.NG);
+            if (th.active && th.ng == 0) ys[tt * g.P + th.pg * 4 + i] = fmaf(Dh, xv[i], tot);
+          }
+        }
       }
     }
     __syncthreads();
@@ -406,10 +437,19 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
           lagn = dg;
         }
         if (!th.active) { sD = 0.f; sL = 0.f; }
+        if (g.NG >= 4) {
+          int row;
+          const float tot = group_reduce4(px, g.NG, th.ng, row);
+          if (th.active && (th.ng & ((g.NG >> 2) - 1)) == 0) dxs[tt * g.P + th.pg * 4 + row] = fmaf(Dh, pick4(dyv, row), tot);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float v = group_sum(px[i], g.NG);
+            if (th.active && th.ng == 0) dxs[tt * g.P + th.pg * 4 + i] = fmaf(Dh, dyv[i], v);
+          }
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          float v = group_sum(px[i], g.NG);
-          if (th.active && th.ng == 0) dxs[tt * g.P + th.pg * 4 + i] = fmaf(Dh, dyv[i], v);
           float vb = th.active ? pB[i] : 0.f, vc = th.active ? pC[i] : 0.f;
           vb = cross_group_sum(vb, g.NG);
           vc = cross_group_sum(vc, g.NG);
@@ -418,9 +458,15 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
             partC[(tt * g.nwarp + warp) * g.N + lane * 4 + i] = vc;
           }
         }
-        sD = warp_sum(sD);
-        sL = warp_sum(sL);
-        if (lane == 0) { partS[(tt * g.nwarp + warp) * 2] = sD; partS[(tt * g.nwarp + warp) * 2 + 1] = sL; }
+        {
+          // both clock partials in one butterfly: lanes 0..15 end with the ddelta sum, lanes 16..31 with the dlam sum
+          const bool up = (lane & 16) != 0;
+          float k = up ? sL : sD;
+          k += __shfl_xor_sync(0xffffffffu, up ? sD : sL, 16);
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) k += __shfl_xor_sync(0xffffffffu, k, o);
+          if ((lane & 15) == 0) partS[(tt * g.nwarp + warp) * 2 + (up ? 1 : 0)] = k;
+        }
       }
       __syncthreads();
       // ---- finish the sub-chunk: sum the per-warp partials in warp order

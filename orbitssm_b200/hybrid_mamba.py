@@ -241,11 +241,12 @@ class HybridMambaSSM(StateLifecycle, nn.Module):
         with torch.autocast("cuda", enabled=False):
             xa = x.to(io)
             proj = F.linear(xa, self._fused_weight(io))
-            drive_raw, z, slab = ops.SplitColumnsFn.apply(proj, s.d_inner, s.d_inner, self.tok_width)
+            arena = ops.GradArena()        # conv and gate backward write d(drive), dz straight into d(proj)
+            drive_raw, z, slab = ops.SplitColumnsFn.apply(proj, arena, s.d_inner, s.d_inner, self.tok_width)
             new = State()
             if self.conv1d is not None:
                 win = state["conv_state"] if state is not None else None
-                u = ops.CausalConvFn.apply(drive_raw, self.conv1d.weight, self.conv1d.bias, win)
+                u = ops.CausalConvFn.apply(drive_raw, self.conv1d.weight, self.conv1d.bias, win, (arena, 0))
                 if return_state:
                     new["conv_state"] = _next_window(win, drive_raw, s.d_conv)
             else:
@@ -262,7 +263,8 @@ class HybridMambaSSM(StateLifecycle, nn.Module):
                 None if self.beta_b is None else self.beta_b.to(f), None if self.beta_c is None else self.beta_c.to(f),
                 feat, th_h, lam, None if self.D is None else self.D.to(f), h0, wp, th0)
             self._route_note = "fp32 coordinate scan"
-            y = ops.GateNormFn.apply(y.reshape(Bsz, L, s.d_inner), z, self.norm.weight if s.out_norm else None, s.norm_eps)
+            y = ops.GateNormFn.apply(y.reshape(Bsz, L, s.d_inner), z, self.norm.weight if s.out_norm else None, s.norm_eps,
+                                     (arena, 1))
             out = F.linear(y, self.out_proj.weight.to(io))
         if not return_state:
             return out

@@ -85,13 +85,45 @@ def _f32(t):
 # ----------------------------------------------------------------------------------------------------
 #  fused projection output -> column views
 # ----------------------------------------------------------------------------------------------------
+class GradArena:
+    """The gradient buffer of one fused projection output, shared by the consumers of its column views: the conv and
+    gate backward kernels write their input gradients straight into their column range (strided rows), so that
+    `SplitColumnsFn.backward` has nothing left to copy for those ranges.  One arena per forward call."""
+
+    def __init__(self):
+        self.buf = None
+        self.shape = self.offsets = None
+
+    def bind(self, shape, sizes):
+        self.shape, self.offsets, o = tuple(shape), [], 0
+        for w in sizes:
+            self.offsets.append((o, w))
+            o += w
+
+    def view(self, index, like):
+        """Column range `index` of the (lazily allocated) buffer, or None when the arena cannot serve `like`."""
+        if self.shape is None or like.dim() != len(self.shape) or tuple(like.shape[:-1]) != self.shape[:-1]:
+            return None
+        o, w = self.offsets[index]
+        if like.shape[-1] != w:
+            return None
+        if self.buf is None:
+            self.buf = torch.empty(self.shape, device=like.device, dtype=like.dtype)
+        if self.buf.dtype != like.dtype:
+            return None
+        return self.buf[..., o:o + w]
+
+
 class SplitColumnsFn(torch.autograd.Function):
     """Column views of the fused projection output; the backward assembles the views' gradients into ONE buffer in a
-    single pass (autograd's own slice backward would zero-fill and add one full-width buffer per view)."""
+    single pass (autograd's own slice backward would zero-fill and add one full-width buffer per view).  With a
+    `GradArena` the ranges whose gradient was already written in place by its producer are not copied at all."""
 
     @staticmethod
-    def forward(ctx, proj, *sizes):
-        ctx.sizes, ctx.shape = sizes, proj.shape
+    def forward(ctx, proj, arena, *sizes):
+        ctx.sizes, ctx.shape, ctx.arena = sizes, proj.shape, arena
+        if arena is not None:
+            arena.bind(proj.shape, sizes)
         outs, o = [], 0
         for w in sizes:
             outs.append(proj[..., o:o + w])
@@ -101,17 +133,22 @@ class SplitColumnsFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *grads):
         ref = next(g for g in grads if g is not None)
-        out = torch.empty(ctx.shape, device=ref.device, dtype=ref.dtype)
+        arena = ctx.arena
+        if arena is not None and arena.buf is not None and arena.buf.dtype == ref.dtype:
+            out = arena.buf
+        else:
+            out = torch.empty(ctx.shape, device=ref.device, dtype=ref.dtype)
         o = 0
         for w, g in zip(ctx.sizes, grads):
+            dst = out[..., o:o + w]
             if g is None:
-                out[..., o:o + w].zero_()
-            else:
-                out[..., o:o + w].copy_(g)
+                dst.zero_()
+            elif not (g.data_ptr() == dst.data_ptr() and g.stride() == dst.stride() and g.shape == dst.shape):
+                dst.copy_(g)
             o += w
         if o < ctx.shape[-1]:
             out[..., o:].zero_()
-        return (out,) + (None,) * len(ctx.sizes)
+        return (out, None) + (None,) * len(ctx.sizes)
 
 
 # ----------------------------------------------------------------------------------------------------
@@ -143,14 +180,15 @@ def conv1d_fwd(x, weight, bias, window, silu=True):
     return y
 
 
-def conv1d_bwd(x, weight, bias, window, dy, silu=True, want_dwindow=False):
-    """Returns (dx [B, L, C] contiguous, dwindow | None, dweight [C, W], dbias [C] | None)."""
+def conv1d_bwd(x, weight, bias, window, dy, silu=True, want_dwindow=False, dx_out=None):
+    """Returns (dx [B, L, C], dwindow | None, dweight [C, W], dbias [C] | None); `dx_out` (same shape, contiguous
+    channel run, any row strides) receives dx in place."""
     _require_cuda("conv1d_bwd", x, weight, bias, window, dy)
     B, L, Cc = x.shape
     W = weight.shape[-1]
     bs, rs = _rows("conv1d_bwd", x)
     dy = dy.contiguous()
-    dx = torch.empty((B, L, Cc), device=x.device, dtype=x.dtype)
+    dx = dx_out if dx_out is not None else torch.empty((B, L, Cc), device=x.device, dtype=x.dtype)
     dwin = torch.empty((B, Cc, W), device=x.device, dtype=torch.float32) if want_dwindow else None
     dweight = torch.empty((Cc, W), device=x.device, dtype=torch.float32)
     dbias = torch.empty((Cc,), device=x.device, dtype=torch.float32) if bias is not None else None
@@ -169,12 +207,13 @@ class CausalConvFn(torch.autograd.Function):
     """y = silu(causal depthwise conv(x) + bias) on token-major x, with the carried window as a differentiable input."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, window):
+    def forward(ctx, x, weight, bias, window, slot=None):
         w32, b32, win32 = _f32(weight.reshape(weight.shape[0], -1)), _f32(bias), _f32(window)
         y = conv1d_fwd(x, w32, b32, win32)
         ctx.save_for_backward(x, w32, b32, win32)
         ctx.meta = (weight.shape, weight.dtype, None if bias is None else bias.dtype,
                     None if window is None else window.dtype)
+        ctx.slot = slot            # (GradArena, column-range index) of x, or None
         return y
 
     @staticmethod
@@ -182,11 +221,15 @@ class CausalConvFn(torch.autograd.Function):
         x, w32, b32, win32 = ctx.saved_tensors
         wshape, wdt, bdt, windt = ctx.meta
         want_win = win32 is not None and ctx.needs_input_grad[3]
-        dx, dwin, dw, db = conv1d_bwd(x, w32, b32, win32, dy, want_dwindow=want_win)
+        dx_out = ctx.slot[0].view(ctx.slot[1], x) if (ctx.slot is not None and ctx.needs_input_grad[0]) else None
+        if dx_out is not None:
+            dx, dwin, dw, db = conv1d_bwd(x, w32, b32, win32, dy, want_dwindow=want_win, dx_out=dx_out)
+        else:
+            dx, dwin, dw, db = conv1d_bwd(x, w32, b32, win32, dy, want_dwindow=want_win)
         return (dx if ctx.needs_input_grad[0] else None,
                 dw.reshape(wshape).to(wdt) if ctx.needs_input_grad[1] else None,
                 db.to(bdt) if (db is not None and ctx.needs_input_grad[2]) else None,
-                dwin.to(windt) if want_win else None)
+                dwin.to(windt) if want_win else None, None)
 
 
 # ----------------------------------------------------------------------------------------------------
@@ -213,21 +256,23 @@ def gate_norm_fwd(y, z, w, eps):
     return out, rstd
 
 
-def gate_norm_bwd(y, z, w, rstd, dout):
-    """Returns (dy [M, D], dz [M, D] | None, dw [D] | None)."""
+def gate_norm_bwd(y, z, w, rstd, dout, dz_out=None):
+    """Returns (dy [M, D], dz [M, D] | None, dw [D] | None); `dz_out` ([M, D], contiguous rows, any row stride)
+    receives dz in place."""
     _require_cuda("gate_norm_bwd", y, z, w, rstd, dout)
     M, D = y.shape
     dout = dout.contiguous()
     zs = _rows2("gate_norm_bwd", z, D) if z is not None else 0
     dy = torch.empty_like(y)
-    dz = torch.empty((M, D), device=y.device, dtype=y.dtype) if z is not None else None
+    dz = (dz_out if dz_out is not None else torch.empty((M, D), device=y.device, dtype=y.dtype)) if z is not None else None
+    dzs = D if dz is None else dz.stride(0)
     dw = torch.empty((D,), device=y.device, dtype=torch.float32) if w is not None else None
     lib = _lib.load()
     nbytes = lib.orbit_gate_norm_bwd_workspace_bytes(M, D)
     ws = torch.empty((max(int(nbytes), 4),), device=y.device, dtype=torch.uint8)
     with _timed("gate_norm_bwd", (2 if w is not None else 1) if M else 0):
         _lib.check(lib.orbit_gate_norm_bwd(_ptr(y), _ptr(z), zs, _ptr(w), _ptr(rstd), _ptr(dout), _ptr(dy), _ptr(dz),
-                                           D, _ptr(dw), _ptr(ws), int(nbytes), M, D, _dtype_code("gate_norm_bwd", y),
+                                           dzs, _ptr(dw), _ptr(ws), int(nbytes), M, D, _dtype_code("gate_norm_bwd", y),
                                            _stream()), "orbit_gate_norm_bwd")
     return dy, dz, dw
 
@@ -236,7 +281,8 @@ class GateNormFn(torch.autograd.Function):
     """out = rms_norm(y * silu(z)) * w over the last axis; z and/or w may be None."""
 
     @staticmethod
-    def forward(ctx, y, z, w, eps):
+    def forward(ctx, y, z, w, eps, slot=None):
+        ctx.slot = slot            # (GradArena, column-range index) of z, or None
         shp = y.shape
         D = shp[-1]
         y2 = y.reshape(-1, D)
@@ -253,8 +299,16 @@ class GateNormFn(torch.autograd.Function):
     def backward(ctx, dout):
         y2, z2, w32, rstd = ctx.saved_tensors
         shp, wdt = ctx.meta
-        dy, dz, dw = gate_norm_bwd(y2, z2, w32, rstd, dout.reshape(-1, shp[-1]))
-        return (dy.reshape(shp), None if dz is None else dz.reshape(shp), None if dw is None else dw.to(wdt), None)
+        dz_view = None
+        if ctx.slot is not None and z2 is not None and ctx.needs_input_grad[1]:
+            dz_view = ctx.slot[0].view(ctx.slot[1], dout)
+        if dz_view is not None:
+            dy, dz, dw = gate_norm_bwd(y2, z2, w32, rstd, dout.reshape(-1, shp[-1]), dz_out=dz_view.view(-1, shp[-1]))
+            dz = dz_view
+        else:
+            dy, dz, dw = gate_norm_bwd(y2, z2, w32, rstd, dout.reshape(-1, shp[-1]))
+            dz = None if dz is None else dz.reshape(shp)
+        return (dy.reshape(shp), dz, None if dw is None else dw.to(wdt), None, None)
 
 
 def _as_rows(t, D):

@@ -349,13 +349,14 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
             xa = x.to(io)
             wcat, bcat = self._fused_weight(io)
             proj = F.linear(xa, wcat, bcat)                                    # [B, L, drive | z | slab | pad]
-            drive_raw, z, slab = ops.SplitColumnsFn.apply(proj, s.d_inner, self.d_gate, s.tok_width)
+            arena = ops.GradArena()        # conv and gate backward write d(drive), dz straight into d(proj)
+            drive_raw, z, slab = ops.SplitColumnsFn.apply(proj, arena, s.d_inner, self.d_gate, s.tok_width)
             new = State()
             if self.conv1d is not None:
                 win = state["conv_state"] if state is not None else None
                 if cp is not None:
                     win = ops.HaloFn.apply(drive_raw[:, L - (s.d_conv - 1):], cp, s.d_conv)
-                u = (ops.CausalConvFn.apply(drive_raw, self.conv1d.weight, self.conv1d.bias, win) if L > 0
+                u = (ops.CausalConvFn.apply(drive_raw, self.conv1d.weight, self.conv1d.bias, win, (arena, 0)) if L > 0
                      else drive_raw.contiguous())
                 if want_state:
                     new["conv_state"] = _next_window(win, drive_raw, s.d_conv)
@@ -400,7 +401,7 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
                 v_last = None
                 if want_state and s.use_trap:
                     v_last = self._last_write(u, law, Bsz)
-            y = ops.GateNormFn.apply(y, z, self.norm.weight if s.out_norm else None, s.norm_eps) if L > 0 else y
+            y = ops.GateNormFn.apply(y, z, self.norm.weight if s.out_norm else None, s.norm_eps, (arena, 1)) if L > 0 else y
             out = F.linear(y, self.out_proj.weight.to(io))
         if not want_state:
             return out
