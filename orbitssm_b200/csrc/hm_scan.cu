@@ -64,38 +64,101 @@ __device__ inline float* hm_tile_carve(HmTile& t, float* p, const HmGeo& g, bool
   return p;
 }
 
-// Fill the tile for tokens [t0 - 1, t0 + 8).  tile.thc holds the phase entering token t0 and leaves holding the phase
-// after token t0 + 7.  Tokens outside [0, L) read as zero drive, zero clock.  Ends with a __syncthreads().
+// ---- raw staging of the next tile (cp.async, double-buffered): the global-memory latency of a tile is paid while the
+// previous tile computes, not at the top of every tile.
+struct HmRaw {
+  unsigned char *x, *dy;     // [9][P], [8][P] in the IO dtype
+  float *B, *C, *feat, *dt, *lam;   // [9][N], [9][N], [8][K], [9], [9]
+};
+__host__ __device__ inline size_t hm_raw_floats(const HmGeo& g) { return 9 * g.P + 8 * g.P + 2 * 9 * g.N + r4(8 * g.K) + 12 + 12; }
+__device__ inline float* hm_raw_carve(HmRaw& r, float* p, const HmGeo& g) {
+  r.x = reinterpret_cast<unsigned char*>(p); p += 9 * g.P;
+  r.dy = reinterpret_cast<unsigned char*>(p); p += 8 * g.P;
+  r.B = p; p += 9 * g.N;
+  r.C = p; p += 9 * g.N;
+  r.feat = p; p += r4(8 * g.K);
+  r.dt = p; p += 12;
+  r.lam = p; p += 12;
+  return p;
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  const int sz = valid ? 4 : 0;                 // src-size 0: the 4 destination bytes are zero-filled
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gsrc), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Issue the copies of tokens [t0 - 1, t0 + 8) (t0 < 0: nothing).  Tokens outside [0, L) are zero-filled.
 template <typename T, bool BWD>
-__device__ __forceinline__ void hm_build_tile(const HmArgs& a, const HmGeo& g, HmTile& tl, int b, int h, int t0) {
-  const int tid = threadIdx.x, nt = blockDim.x;
-  const T* x = (const T*)a.x;
-  for (int idx = tid; idx < 9 * g.P; idx += nt) {
-    const int r = idx / g.P, p = idx % g.P, tok = t0 - 1 + r;
-    tl.xs[idx] = (tok >= 0 && tok < a.L) ? ldf(x + ((int64_t)b * a.L + tok) * a.H * g.P + h * g.P + p) : 0.f;
-  }
-  if (BWD) {
-    const T* dy = (const T*)a.dy;
-    for (int idx = tid; idx < 8 * g.P; idx += nt) {
-      const int r = idx / g.P, p = idx % g.P, tok = t0 + r;
-      tl.dys[idx] = tok < a.L ? ldf(dy + ((int64_t)b * a.L + tok) * a.H * g.P + h * g.P + p) : 0.f;
+__device__ __forceinline__ void hm_prefetch(const HmArgs& a, const HmGeo& g, const HmRaw& rw, int b, int h, int t0) {
+  if (t0 >= 0) {
+    const int tid = threadIdx.x, nt = blockDim.x;
+    constexpr int EPW = 4 / (int)sizeof(T);          // elements per 4-byte word
+    const int wpr = g.P / EPW;                       // words per row
+    const T* x = (const T*)a.x;
+    for (int idx = tid; idx < 9 * wpr; idx += nt) {
+      const int r = idx / wpr, w = idx % wpr, tok = t0 - 1 + r;
+      const bool ok = tok >= 0 && tok < a.L;
+      cp_async4(rw.x + (size_t)idx * 4, x + ((int64_t)b * a.L + (ok ? tok : 0)) * a.H * g.P + h * g.P + w * EPW, ok);
+    }
+    if (BWD) {
+      const T* dy = (const T*)a.dy;
+      for (int idx = tid; idx < 8 * wpr; idx += nt) {
+        const int r = idx / wpr, w = idx % wpr, tok = t0 + r;
+        const bool ok = tok < a.L;
+        cp_async4(rw.dy + (size_t)idx * 4, dy + ((int64_t)b * a.L + (ok ? tok : 0)) * a.H * g.P + h * g.P + w * EPW, ok);
+      }
+    }
+    for (int idx = tid; idx < 9 * g.N; idx += nt) {
+      const int r = idx / g.N, n = idx % g.N, tok = t0 - 1 + r;
+      const bool ok = tok >= 0 && tok < a.L;
+      const int64_t o = ((int64_t)b * a.L + (ok ? tok : 0)) * g.N + n;
+      cp_async4(rw.B + idx, a.Bh + o, ok);
+      cp_async4(rw.C + idx, a.Ch + o, ok);
+    }
+    if (a.feat != nullptr)
+      for (int idx = tid; idx < 8 * g.K; idx += nt) {
+        const int r = idx / g.K, k = idx % g.K, tok = t0 + r;
+        const bool ok = tok < a.L;
+        cp_async4(rw.feat + idx, a.feat + ((int64_t)b * a.L + (ok ? tok : 0)) * g.K + k, ok);
+      }
+    if (tid < 9) {
+      const int tok = t0 - 1 + tid;
+      const bool ok = tok >= 0 && tok < a.L;
+      const int64_t o = ((int64_t)b * a.L + (ok ? tok : 0)) * a.H + h;
+      cp_async4(rw.dt + tid, a.delta + o, ok);
+      if (a.lam != nullptr) cp_async4(rw.lam + tid, a.lam + o, ok);
     }
   }
-  if (tid < 9) {
-    const int tok = t0 - 1 + tid;
-    const bool ok = tok >= 0 && tok < a.L;
-    tl.dts[tid] = ok ? a.delta[((int64_t)b * a.L + tok) * a.H + h] : 0.f;
-    tl.lams[tid] = (ok && a.lam) ? a.lam[((int64_t)b * a.L + tok) * a.H + h] : 1.f;
-  }
+  cp_async_commit();
+}
+
+// Build the tile of tokens [t0 - 1, t0 + 8) from its staged raw copy.  tile.thc holds the phase entering token t0 and
+// leaves holding the phase after token t0 + 7.  Ends with a __syncthreads().
+template <typename T, bool BWD>
+__device__ __forceinline__ void hm_build_tile(const HmArgs& a, const HmGeo& g, HmTile& tl, const HmRaw& rw, int b, int h, int t0) {
+  const int tid = threadIdx.x, nt = blockDim.x;
+  cp_async_wait_all();
   __syncthreads();
+  const T* rx = reinterpret_cast<const T*>(rw.x);
+  for (int idx = tid; idx < 9 * g.P; idx += nt) tl.xs[idx] = ldf(rx + idx);
+  if (BWD) {
+    const T* rdy = reinterpret_cast<const T*>(rw.dy);
+    for (int idx = tid; idx < 8 * g.P; idx += nt) tl.dys[idx] = ldf(rdy + idx);
+  }
+  if (tid < 9) {
+    tl.dts[tid] = rw.dt[tid];
+    tl.lams[tid] = a.lam ? rw.lam[tid] : 1.f;
+  }
   // running phase per pair: row 0 (token t0 - 1) sees the entering phase, row r the phase after token t0 + r - 1
   float* ang = tl.Ct;   // rows of Ct are not yet written: borrow [9][K] of it for the angles
   if (a.feat != nullptr && tid < g.K) {
     float th = tl.thc[tid];
     ang[tid] = th;
+#pragma unroll
     for (int r = 1; r < 9; ++r) {
-      const int tok = t0 + r - 1;
-      if (tok < a.L) th = fmaf(tl.dts[r], a.feat[((int64_t)b * a.L + tok) * g.K + tid], th);
+      th = fmaf(rw.dt[r], rw.feat[(r - 1) * g.K + tid], th);       // zero-filled past the end of the sequence
       ang[r * g.K + tid] = th;
     }
     tl.thc[tid] = th;
@@ -114,8 +177,7 @@ __device__ __forceinline__ void hm_build_tile(const HmArgs& a, const HmGeo& g, H
     const int r = idx / g.K, k = idx % g.K, tok = t0 - 1 + r;
     float b0 = 0.f, b1 = 0.f, c0 = 0.f, c1 = 0.f;
     if (tok >= 0 && tok < a.L) {
-      const int64_t o = ((int64_t)b * a.L + tok) * g.N + 2 * k;
-      b0 = a.Bh[o]; b1 = a.Bh[o + 1]; c0 = a.Ch[o]; c1 = a.Ch[o + 1];
+      b0 = rw.B[r * g.N + 2 * k]; b1 = rw.B[r * g.N + 2 * k + 1]; c0 = rw.C[r * g.N + 2 * k]; c1 = rw.C[r * g.N + 2 * k + 1];
       if (a.beta_b) { b0 += a.beta_b[h * g.N + 2 * k]; b1 += a.beta_b[h * g.N + 2 * k + 1]; }
       if (a.beta_c) { c0 += a.beta_c[h * g.N + 2 * k]; c1 += a.beta_c[h * g.N + 2 * k + 1]; }
     }
@@ -175,9 +237,18 @@ __device__ __forceinline__ HmThread hm_thread(const HmGeo& g) {
   return t;
 }
 
-// one forward token on the thread's 4 x 4 tile; returns the 4 partial outputs (over this thread's rows)
-__device__ __forceinline__ void hm_step(float (&hs)[16], float (&prv)[16], const float (&rate)[16], const float4 x4,
-                                        const float4 b4, float d, float lm, bool trap) {
+constexpr float HM_LOG2E = 1.4426950408889634f, HM_LN2 = 0.6931471805599453f;
+// 2^x on the MUFU pipe (one instruction; the decay exponents are <= 0, flush-to-zero of denormal results is harmless)
+__device__ __forceinline__ float fast_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// one forward token on the thread's 4 x 4 tile.  rate2 = -exp(A_log) log2(e), so that a = 2^(rate2 delta).
+template <bool TRAP>
+__device__ __forceinline__ void hm_step(float (&hs)[16], float (&prv)[16], const float (&rate2)[16], const float4 x4,
+                                        const float4 b4, float d, float lm) {
   const float xv[4] = {x4.x, x4.y, x4.z, x4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
   const float dl = d * lm, dg = d * (1.f - lm);
 #pragma unroll
@@ -185,9 +256,10 @@ __device__ __forceinline__ void hm_step(float (&hs)[16], float (&prv)[16], const
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int e = i * 4 + j;
-      const float av = __expf(rate[e] * d);
+      const float av = fast_ex2(rate2[e] * d);
       const float raw = xv[i] * bv[j];
-      hs[e] = trap ? fmaf(av, fmaf(dg, prv[e], hs[e]), dl * raw) : fmaf(av, hs[e], d * raw);
+      if (TRAP) hs[e] = fmaf(av, fmaf(dg, prv[e], hs[e]), dl * raw);
+      else hs[e] = fmaf(av, hs[e], d * raw);
       prv[e] = raw;
     }
 }
@@ -208,20 +280,24 @@ __device__ __forceinline__ void store16(const float (&v)[16], float* base, const
 // ---------------------------------------------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool TRAP>
 __global__ void __launch_bounds__(256) hm_fwd_kernel(const HmArgs a) {
   extern __shared__ __align__(16) float smf[];
   const HmGeo g = hm_geo(a.P, a.N);
   HmTile tl;
   float* ys = hm_tile_carve(tl, smf, g, false);      // [8][P]
+  HmRaw raw[2];
+  float* rp = hm_raw_carve(raw[0], ys + 8 * g.P, g);
+  hm_raw_carve(raw[1], rp, g);
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  hm_prefetch<T, false>(a, g, raw[0], b, h, 0);
   const HmThread th = hm_thread(g);
-  const bool trap = a.lam != nullptr;
+  constexpr bool trap = TRAP;
   const int64_t bh = (int64_t)b * a.H + h;
   float hs[16], prv[16], rate[16];
   load16(rate, a.A_log + (int64_t)h * g.P * g.N, th, g.N);
 #pragma unroll
-  for (int e = 0; e < 16; ++e) { rate[e] = -__expf(rate[e]); hs[e] = 0.f; prv[e] = 0.f; }
+  for (int e = 0; e < 16; ++e) { rate[e] = -__expf(rate[e]) * HM_LOG2E; hs[e] = 0.f; prv[e] = 0.f; }
   if (a.h_init) load16(hs, a.h_init + bh * g.P * g.N, th, g.N);
   if (a.write_prev && trap) load16(prv, a.write_prev + bh * g.P * g.N, th, g.N);
   if (tid < g.K) tl.thc[tid] = a.theta_init ? a.theta_init[bh * g.K + tid] : 0.f;
@@ -234,7 +310,9 @@ __global__ void __launch_bounds__(256) hm_fwd_kernel(const HmArgs a) {
       if (th.active) store16(hs, a.hck + (bh * a.nck + c) * g.P * g.N, th, g.N);
       if (a.thck != nullptr && tid < g.K) a.thck[(bh * a.nck + c) * g.K + tid] = tl.thc[tid];
     }
-    hm_build_tile<T, false>(a, g, tl, b, h, t0);
+    const int it = t0 / HM_TT;
+    hm_build_tile<T, false>(a, g, tl, raw[it & 1], b, h, t0);
+    hm_prefetch<T, false>(a, g, raw[(it + 1) & 1], b, h, t0 + HM_TT < a.L ? t0 + HM_TT : -1);
     const int nv = min(HM_TT, a.L - t0);
 #pragma unroll
     for (int tt = 0; tt < HM_TT; ++tt) {
@@ -242,7 +320,7 @@ __global__ void __launch_bounds__(256) hm_fwd_kernel(const HmArgs a) {
         const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + (tt + 1) * g.P + th.pg * 4);
         const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + (tt + 1) * g.N + th.ng * 4);
         const float4 c4 = *reinterpret_cast<const float4*>(tl.Ct + (tt + 1) * g.N + th.ng * 4);
-        hm_step(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1], trap);
+        hm_step<TRAP>(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1]);
         const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, xv[4] = {x4.x, x4.y, x4.z, x4.w};
         float yp[4];
 #pragma unroll
@@ -281,7 +359,7 @@ __global__ void __launch_bounds__(256) hm_fwd_kernel(const HmArgs a) {
 // ---------------------------------------------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool TRAP>
 __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
   extern __shared__ __align__(16) float smf[];
   const HmGeo g = hm_geo(a.P, a.N);
@@ -294,17 +372,35 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
   float* partS = p; p += 8 * g.nwarp * 2;                // [tt][warp][ddelta, dlam]
   float* dxs = p;   p += 8 * g.P;
   float* phs = p;   p += 8 * g.K;                        // [tt][k] feat * suffix (phase part of ddelta)
-  float* Ssuf = p;  p += g.K;                            // suffix sum of dTheta carried backwards in time
+  float* Ssuf = p;  p += r4(g.K);                          // suffix sum of dTheta carried backwards in time
   float* red = p;   p += 32;
+  HmRaw raw[2];
+  p = hm_raw_carve(raw[0], p, g);
+  p = hm_raw_carve(raw[1], p, g);
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // The tiles are visited in a fixed order: per chunk (last first) the first nsub - 1 sub-chunks forwards (replay), then
+  // all nsub sub-chunks backwards.  item_t0(c, k) = first token of the k-th visit of chunk c, continuing into chunk c - 1.
+  auto n_sub = [&](int c) { return min(HM_SUB, (a.L - c * HM_TC + HM_TT - 1) / HM_TT); };
+  auto item_t0 = [&](int c, int k) -> int {
+    int ns = n_sub(c);
+    if (k >= 2 * ns - 1) {
+      c -= 1;
+      k = 0;
+      if (c < 0) return -1;
+      ns = HM_SUB;
+    }
+    return c * HM_TC + (k < ns - 1 ? k : (ns - 1) - (k - (ns - 1))) * HM_TT;
+  };
+  int seq = 0;
+  hm_prefetch<T, true>(a, g, raw[0], b, h, item_t0(a.nck - 1, 0));
   const HmThread th = hm_thread(g);
-  const bool trap = a.lam != nullptr;
+  constexpr bool trap = TRAP;
   const int64_t bh = (int64_t)b * a.H + h;
   const int64_t PN = (int64_t)g.P * g.N;
   float rate[16], G[16], dA[16];
   load16(rate, a.A_log + (int64_t)h * PN, th, g.N);
 #pragma unroll
-  for (int e = 0; e < 16; ++e) { rate[e] = -__expf(rate[e]); G[e] = 0.f; dA[e] = 0.f; }
+  for (int e = 0; e < 16; ++e) { rate[e] = -__expf(rate[e]) * HM_LOG2E; G[e] = 0.f; dA[e] = 0.f; }
   if (a.dh_final) load16(G, a.dh_final + bh * PN, th, g.N);
   if (tid < g.K) Ssuf[tid] = a.dtheta_final ? a.dtheta_final[bh * g.K + tid] : 0.f;
   float lagn = 0.f;                       // delta_{t+1} (1 - lam_{t+1}) of the token processed just before (in reverse)
@@ -317,6 +413,7 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
 
   for (int c = a.nck - 1; c >= 0; --c) {
     const int tc0 = c * HM_TC;
+    int item = 0;
     // ---- replay the chunk once, keeping the state and phase that enter each sub-chunk
     {
       float hs[16], prv[16];
@@ -328,8 +425,11 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
         if (t0 >= a.L) break;
         if (th.active) store16(hs, hsub + (size_t)j * PN, th, g.N);
         if (tid < g.K) thsub[j * g.K + tid] = tl.thc[tid];
-        if (j == HM_SUB - 1) break;        // the last sub-chunk is replayed below anyway
-        hm_build_tile<T, false>(a, g, tl, b, h, t0);
+        if (j == n_sub(c) - 1) break;      // the last sub-chunk is replayed below anyway
+        hm_build_tile<T, false>(a, g, tl, raw[seq & 1], b, h, t0);
+        ++item;
+        ++seq;
+        hm_prefetch<T, true>(a, g, raw[seq & 1], b, h, item_t0(c, item));
         if (j == 0) {
 #pragma unroll
           for (int e = 0; e < 16; ++e) prv[e] = 0.f;
@@ -349,7 +449,7 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
         for (int tt = 0; tt < nv; ++tt) {
           const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + (tt + 1) * g.P + th.pg * 4);
           const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + (tt + 1) * g.N + th.ng * 4);
-          hm_step(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1], trap);
+          hm_step<TRAP>(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1]);
         }
         __syncthreads();
       }
@@ -361,7 +461,10 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
       if (t0 >= a.L) continue;
       if (tid < g.K) tl.thc[tid] = thsub[j * g.K + tid];
       __syncthreads();
-      hm_build_tile<T, true>(a, g, tl, b, h, t0);
+      hm_build_tile<T, true>(a, g, tl, raw[seq & 1], b, h, t0);
+      ++item;
+      ++seq;
+      hm_prefetch<T, true>(a, g, raw[seq & 1], b, h, item_t0(c, item));
       float hist[8][16];
       float prv0[16];
       {
@@ -386,7 +489,7 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
         for (int tt = 0; tt < HM_TT; ++tt) {       // tokens past L: zero clock and drive leave the state unchanged
           const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + (tt + 1) * g.P + th.pg * 4);
           const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + (tt + 1) * g.N + th.ng * 4);
-          hm_step(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1], trap);
+          hm_step<TRAP>(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1]);
 #pragma unroll
           for (int e = 0; e < 16; ++e) hist[tt][e] = hs[e];
         }
@@ -406,7 +509,7 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
         const float bv[4] = {b4.x, b4.y, b4.z, b4.w}, bpv[4] = {bp4.x, bp4.y, bp4.z, bp4.w};
         const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, dyv[4] = {dy4.x, dy4.y, dy4.z, dy4.w};
         float px[4] = {0.f, 0.f, 0.f, 0.f}, pB[4] = {0.f, 0.f, 0.f, 0.f}, pC[4] = {0.f, 0.f, 0.f, 0.f};
-        float sD = 0.f, sL = 0.f;
+        float sQ = 0.f, S1 = 0.f, S2 = 0.f;        // sums of dlog rate2, G raw, (a G) raw_prev over this thread's tile
         const float dl = d * lm, dg = d * (1.f - lm);
         const bool last = (tok == a.L - 1) && a.dwrite_last != nullptr;
         if (tok < a.L) {
@@ -418,24 +521,25 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
               const float Gt = fmaf(cv[jn], dyv[i], G[e]);
               pC[jn] = fmaf(dyv[i], hist[tt][e], pC[jn]);
               const float raw = xv[i] * bv[jn];
-              float rawp = 0.f;
-              if (trap) rawp = (tt == 0) ? prv0[e] : xpv[i] * bpv[jn];
-              const float dlog = Gt * (hist[tt][e] - dl * raw);          // dL / d log a_t
-              dA[e] = fmaf(dlog, rate[e] * d, dA[e]);
-              sD = fmaf(dlog, rate[e], sD);
-              const float av = __expf(rate[e] * d);
-              const float aG = av * Gt;
+              const float u1 = Gt * raw;
+              const float q = fmaf(Gt, hist[tt][e], -dl * u1) * rate[e];   // dL / d log a_t, times rate2
+              dA[e] = fmaf(q, d, dA[e]);
+              sQ += q;
+              const float aG = fast_ex2(rate[e] * d) * Gt;
               float draw = fmaf(dl, Gt, lagn * G[e]);
               if (last) draw += a.dwrite_last[bh * PN + (int64_t)(th.pg * 4 + i) * g.N + th.ng * 4 + jn];
-              sD = fmaf(Gt * lm, raw, sD);
-              sD = fmaf(aG * (1.f - lm), rawp, sD);
-              sL = fmaf(d, Gt * raw - aG * rawp, sL);
+              S1 += u1;
+              if (TRAP) {
+                const float rawp = (tt == 0) ? prv0[e] : xpv[i] * bpv[jn];
+                S2 = fmaf(aG, rawp, S2);
+              }
               px[i] = fmaf(draw, bv[jn], px[i]);
               pB[jn] = fmaf(draw, xv[i], pB[jn]);
               G[e] = aG;
             }
           lagn = dg;
         }
+        float sD = fmaf(HM_LN2, sQ, fmaf(lm, S1, (1.f - lm) * S2)), sL = d * (S1 - S2);
         if (!th.active) { sD = 0.f; sL = 0.f; }
         if (g.NG >= 4) {
           int row;
@@ -500,7 +604,7 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
             gb[0] = g0; gb[1] = g1; gc[0] = e0; gc[1] = e1;
             acc_th += dthC;
             S += dthB + dthC;
-            const float ft = a.feat[((int64_t)b * a.L + tok) * g.K + k];
+            const float ft = raw[(seq + 1) & 1].feat[tt * g.K + k];      // this tile's staged copy (seq already advanced)
             ph = ft * S;
             if (a.dfeat_part) a.dfeat_part[(((int64_t)h * a.B + b) * a.L + tok) * g.K + k] = tl.dts[r] * S;
           } else if (a.dfeat_part) {
@@ -548,6 +652,8 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
       for (int e = 0; e < 16; ++e) wv[e] = lagn * G[e];
       store16(wv, a.dwrite_prev + bh * PN, th, g.N);
     }
+#pragma unroll
+    for (int e = 0; e < 16; ++e) dA[e] *= HM_LN2;       // the sums were taken with rate2 = rate log2(e)
     store16(dA, a.dA_log_part + bh * PN, th, g.N);
   }
   if (tid < g.N) {
@@ -597,10 +703,10 @@ static int hm_check(const HmArgs* a, int dtype, const char* who, bool bwd) {
   return OK;
 }
 
-static size_t hm_smem_fwd(const HmGeo& g) { return sizeof(float) * (hm_tile_floats(g, false) + 8 * g.P); }
+static size_t hm_smem_fwd(const HmGeo& g) { return sizeof(float) * (hm_tile_floats(g, false) + 8 * g.P + 2 * hm_raw_floats(g)); }
 static size_t hm_smem_bwd(const HmGeo& g) {
   return sizeof(float) * (hm_tile_floats(g, true) + (size_t)HM_SUB * g.P * g.N + r4(HM_SUB * g.K) + 2 * 8 * g.nwarp * g.N +
-                          8 * g.nwarp * 2 + 8 * g.P + 8 * g.K + g.K + 32);
+                          8 * g.nwarp * 2 + 8 * g.P + 8 * g.K + r4(g.K) + 32 + 2 * hm_raw_floats(g));
 }
 
 }  // namespace orbit
@@ -615,13 +721,15 @@ extern "C" int orbit_hm_scan_fwd(const orbit_hm_args* a, int dtype, void* stream
   ORBIT_REQUIRE(smem <= 200 * 1024, ERR_UNSUPPORTED, "orbit_hm_scan_fwd: tile needs %zu bytes of shared memory", smem);
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(a->H, a->B);
-  if (dtype == BF16) {
-    ORBIT_CHECK_CUDA(cudaFuncSetAttribute(hm_fwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    hm_fwd_kernel<__nv_bfloat16><<<grid, g.nthr, smem, st>>>(*a);
-  } else {
-    ORBIT_CHECK_CUDA(cudaFuncSetAttribute(hm_fwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    hm_fwd_kernel<float><<<grid, g.nthr, smem, st>>>(*a);
-  }
+  auto go = [&](auto kernel) -> int {
+    ORBIT_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<grid, g.nthr, smem, st>>>(*a);
+    return OK;
+  };
+  const bool trap = a->lam != nullptr;
+  rc = dtype == BF16 ? (trap ? go(hm_fwd_kernel<__nv_bfloat16, true>) : go(hm_fwd_kernel<__nv_bfloat16, false>))
+                     : (trap ? go(hm_fwd_kernel<float, true>) : go(hm_fwd_kernel<float, false>));
+  if (rc != OK) return rc;
   ORBIT_CHECK_LAUNCH("hm_fwd_kernel");
   return OK;
 }
@@ -635,13 +743,15 @@ extern "C" int orbit_hm_scan_bwd(const orbit_hm_args* a, int dtype, void* stream
                 a->P, a->N, smem);
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(a->H, a->B);
-  if (dtype == BF16) {
-    ORBIT_CHECK_CUDA(cudaFuncSetAttribute(hm_bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    hm_bwd_kernel<__nv_bfloat16><<<grid, g.nthr, smem, st>>>(*a);
-  } else {
-    ORBIT_CHECK_CUDA(cudaFuncSetAttribute(hm_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    hm_bwd_kernel<float><<<grid, g.nthr, smem, st>>>(*a);
-  }
+  auto go = [&](auto kernel) -> int {
+    ORBIT_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<grid, g.nthr, smem, st>>>(*a);
+    return OK;
+  };
+  const bool trap = a->lam != nullptr;
+  rc = dtype == BF16 ? (trap ? go(hm_bwd_kernel<__nv_bfloat16, true>) : go(hm_bwd_kernel<__nv_bfloat16, false>))
+                     : (trap ? go(hm_bwd_kernel<float, true>) : go(hm_bwd_kernel<float, false>));
+  if (rc != OK) return rc;
   ORBIT_CHECK_LAUNCH("hm_bwd_kernel");
   return OK;
 }
