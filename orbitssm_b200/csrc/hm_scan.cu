@@ -465,8 +465,13 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
       ++item;
       ++seq;
       hm_prefetch<T, true>(a, g, raw[seq & 1], b, h, item_t0(c, item));
-      float hist[8][16];
-      float prv0[16];
+      // The sub-chunk is walked in two halves of 4 tokens (second half first): a half's 4 states are held in registers;
+      // the first half is replayed once more from the sub-chunk boundary.  (Keeping all 8 states costs 128 registers
+      // and an unrolled body that no longer fits the instruction cache.)
+      float hist[4][16];
+#pragma unroll 1
+      for (int half = 1; half >= 0; --half) {
+      float prv0[16];                            // raw write of the token before token 4 * half
       {
         float hs[16], prv[16];
         load16(hs, hsub + (size_t)j * PN, th, g.N);
@@ -483,20 +488,30 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
             for (int e = 0; e < 16; ++e) prv[e] = xv[e >> 2] * bv[e & 3];
           }
         }
+        if (half == 1) {
+#pragma unroll
+          for (int tt = 0; tt < 4; ++tt) {
+            const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + (tt + 1) * g.P + th.pg * 4);
+            const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + (tt + 1) * g.N + th.ng * 4);
+            hm_step<TRAP>(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1]);
+          }
+        }
 #pragma unroll
         for (int e = 0; e < 16; ++e) prv0[e] = prv[e];
 #pragma unroll
-        for (int tt = 0; tt < HM_TT; ++tt) {       // tokens past L: zero clock and drive leave the state unchanged
+        for (int k = 0; k < 4; ++k) {              // tokens past L: zero clock and drive leave the state unchanged
+          const int tt = half * 4 + k;
           const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + (tt + 1) * g.P + th.pg * 4);
           const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + (tt + 1) * g.N + th.ng * 4);
           hm_step<TRAP>(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1]);
 #pragma unroll
-          for (int e = 0; e < 16; ++e) hist[tt][e] = hs[e];
+          for (int e = 0; e < 16; ++e) hist[k][e] = hs[e];
         }
       }
       // ---- reverse walk
 #pragma unroll
-      for (int tt = HM_TT - 1; tt >= 0; --tt) {
+      for (int k = 3; k >= 0; --k) {
+        const int tt = half * 4 + k;
         const int tok = t0 + tt;
         const float d = tl.dts[tt + 1], lm = tl.lams[tt + 1];
         const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + (tt + 1) * g.P + th.pg * 4);
@@ -519,10 +534,10 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
             for (int jn = 0; jn < 4; ++jn) {
               const int e = i * 4 + jn;
               const float Gt = fmaf(cv[jn], dyv[i], G[e]);
-              pC[jn] = fmaf(dyv[i], hist[tt][e], pC[jn]);
+              pC[jn] = fmaf(dyv[i], hist[k][e], pC[jn]);
               const float raw = xv[i] * bv[jn];
               const float u1 = Gt * raw;
-              const float q = fmaf(Gt, hist[tt][e], -dl * u1) * rate[e];   // dL / d log a_t, times rate2
+              const float q = fmaf(Gt, hist[k][e], -dl * u1) * rate[e];   // dL / d log a_t, times rate2
               dA[e] = fmaf(q, d, dA[e]);
               sQ += q;
               const float aG = fast_ex2(rate[e] * d) * Gt;
@@ -530,7 +545,7 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
               if (last) draw += a.dwrite_last[bh * PN + (int64_t)(th.pg * 4 + i) * g.N + th.ng * 4 + jn];
               S1 += u1;
               if (TRAP) {
-                const float rawp = (tt == 0) ? prv0[e] : xpv[i] * bpv[jn];
+                const float rawp = (k == 0) ? prv0[e] : xpv[i] * bpv[jn];
                 S2 = fmaf(aG, rawp, S2);
               }
               px[i] = fmaf(draw, bv[jn], px[i]);
@@ -572,6 +587,7 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
           if ((lane & 15) == 0) partS[(tt * g.nwarp + warp) * 2 + (up ? 1 : 0)] = k;
         }
       }
+      }   // half
       __syncthreads();
       // ---- finish the sub-chunk: sum the per-warp partials in warp order
       // A warp holds 32 / NG channel groups; when NG == 32 lanes map 1:1 to row groups.  Rows n = ng * 4 + i.
