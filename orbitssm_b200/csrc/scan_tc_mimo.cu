@@ -91,11 +91,14 @@ __device__ __forceinline__ void store_row(uint8_t* tile, int row, int wg, const 
 
 // Transposed, row-scaled drive tile of one head: XT[g][x * 32 + s] = f[s] * src[b, t0 + s, (h * 16 + g) * 4 + x]
 // (x = input column q for the drive u, output column o for dy).  One 16-byte load per thread.
-__device__ __forceinline__ void build_xt(uint8_t* xt, const __nv_bfloat16* src, int64_t row_stride, int64_t tok0, int h, int Tv,
-                                         const float* f) {
+__device__ __forceinline__ uint4 load_xt_row(const __nv_bfloat16* src, int64_t row_stride, int64_t tok0, int h, int Tv) {
   const int s = threadIdx.x >> 3, v = threadIdx.x & 7;
   uint4 raw = make_uint4(0, 0, 0, 0);
   if (s < Tv) raw = *reinterpret_cast<const uint4*>(src + (tok0 + s) * row_stride + h * 64 + v * 8);
+  return raw;
+}
+__device__ __forceinline__ void build_xt_from(uint8_t* xt, const uint4 raw, const float* f) {
+  const int s = threadIdx.x >> 3, v = threadIdx.x & 7;
   const float fs = f ? f[s] : 1.f;
   const uint32_t* rp = reinterpret_cast<const uint32_t*>(&raw);
 #pragma unroll
@@ -107,13 +110,17 @@ __device__ __forceinline__ void build_xt(uint8_t* xt, const __nv_bfloat16* src, 
     *reinterpret_cast<__nv_bfloat16*>(xt + xt_offset((ch0 + 1) >> 2, ((ch0 + 1) & 3) * 32 + s)) = __float2bfloat16_rn(a1 * fs);
   }
 }
+__device__ __forceinline__ void build_xt(uint8_t* xt, const __nv_bfloat16* src, int64_t row_stride, int64_t tok0, int h, int Tv,
+                                         const float* f) {
+  build_xt_from(xt, load_xt_row(src, row_stride, tok0, h, Tv), f);
+}
 
 // ------------------------------------------------------------------------------------------------------------------
 // chunk_state  (mode 0):  Z_{h,r}[n,g]  = sum_{q,s} e_r[s] Bbar_{h,r}[(q,s),n] u[s,g,q]            -> a.Sin, a.atot
 // chunk_dstate (mode 1):  Gs_{h,r}[n,g] = sum_{o,t} chi_r(t) a_r(t) Cbar_{h,r}[(o,t),n] dy[t,g,o]   -> a.dS
 // by linearity:  (gate x map)^T (f o X)  on the tensor cores  +  bias^T (sum_s f[s] X[s])  on the FP32 pipe.
 // ------------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_state_kernel(const ScanArgs a, const int mode) {
+__global__ void __launch_bounds__(TC_THREADS, 2) mimo_chunk_state_kernel(const ScanArgs a, const int mode) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   uint8_t* sMap = sm;                            // gate x map tile [128 rows][128 n], 2 blocks
@@ -151,8 +158,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_state_kernel(const S
   const uint32_t idesc = idesc_bf16(128, 16, 1, 0);
   uint32_t n_issued[2] = {0, 0};                 // per accumulator: MMAs committed so far (parity of the wait)
 
-  // epilogue of kernel head `itp` (warps 0..3: one state row n per thread): bias correction and store
-  auto epilogue = [&](int itp) {
+  // epilogue of kernel head `itp` (warps 0..3: one state row n per thread): bias correction (bv: its 4 bias values) and store
+  auto load_bias = [&](int itp, float (&bv)[4]) {
+    const int hh = itp % H, rr = itp / H;
+#pragma unroll
+    for (int x = 0; x < 4; ++x) bv[x] = (bias != nullptr && wg == 0) ? bias[(((int64_t)hh * MM_R + rr) * 4 + x) * MM_N + row] : 0.f;
+  };
+  auto epilogue = [&](int itp, const float (&bv)[4]) {
     const int hb = itp & 1, hh = itp % H, rr = itp / H;
     const bool ok = wait_warp(&bar_mma[hb], n_issued[hb] & 1u, abort_flag);
     n_issued[hb]++;
@@ -163,9 +175,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_state_kernel(const S
       if (bias != nullptr) {
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
-          const float bv = bias[(((int64_t)hh * MM_R + rr) * 4 + x) * MM_N + row];
 #pragma unroll
-          for (int g = 0; g < 16; ++g) z[g] = fmaf(bv, xbar[hb * 64 + x * 16 + g], z[g]);
+          for (int g = 0; g < 16; ++g) z[g] = fmaf(bv[x], xbar[hb * 64 + x * 16 + g], z[g]);
         }
       }
       float* dst = outbuf + (((((int64_t)b * a.nc + c) * H + hh) * MM_R + rr) * MM_N + row) * MM_G;
@@ -174,6 +185,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_state_kernel(const S
     }
     tc_fence_before_sync();
   };
+  // global operands of a kernel head are fetched one kernel head ahead (clocks, drive rows) so that their latency is
+  // hidden behind the previous head's tile work
+  auto load_clock = [&](int hh, int rr, float& d, float& wt, float& ch) {
+    d = 0.f; wt = 0.f; ch = 1.f;
+    if (lane < Tv) {
+      const int64_t i = ((tok0 + lane) * H + hh) * MM_R + rr;
+      d = a.dA[i];
+      wt = a.w[i];
+      if (a.chi) ch = a.chi[i];
+    }
+  };
+  float d_n, wt_n, ch_n;
+  load_clock(0, 0, d_n, wt_n, ch_n);
+  uint4 raw_n = load_xt_row(xsrc, (int64_t)H * 64, tok0, 0, Tv);
   for (int r = 0; r < MM_R; ++r) {
     if (mode == 0 || r == 0) {
       uint32_t v[32];
@@ -184,12 +209,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_state_kernel(const S
     for (int h = 0; h < H; ++h) {
       const int it = r * H + h, buf = it & 1;
       // clocks of kernel head (h, r): every warp forms the 32-token prefix on its own
-      float d = 0.f, wt = 0.f, ch = 1.f;
-      if (lane < Tv) {
-        const int64_t i = ((tok0 + lane) * H + h) * MM_R + r;
-        d = a.dA[i];
-        wt = a.w[i];
-        if (a.chi) ch = a.chi[i];
+      const float d = d_n, wt = wt_n, ch = ch_n;
+      const uint4 raw = raw_n;
+      float bv[4];
+      if (h > 0) load_bias(it - 1, bv);
+      {
+        const int itn = it + 1;
+        if (itn < MM_R * H) {
+          load_clock(itn % H, itn / H, d_n, wt_n, ch_n);
+          raw_n = load_xt_row(xsrc, (int64_t)H * 64, tok0, itn % H, Tv);
+        }
       }
       const float cs = warp_prefix32(d, lane);
       const float tot = __shfl_sync(0xffffffffu, cs, 31);
@@ -198,12 +227,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_state_kernel(const S
         if (lane == 0 && mode == 0) a.atot[(((int64_t)b * a.nc + c) * H + h) * MM_R + r] = __expf(tot);
       }
       __syncthreads();
-      build_xt(sXT + buf * 2 * XT_BLK, xsrc, (int64_t)H * 64, tok0, h, Tv, fvec);
+      build_xt_from(sXT + buf * 2 * XT_BLK, raw, fvec);
       fence_proxy_async();
       __syncthreads();
       if (tid < 64) {                            // xbar[x][g] = sum_s XT[g][x * 32 + s]
         const int g = tid >> 2, x = tid & 3;
         float acc = 0.f;
+#pragma unroll 8
         for (int s = 0; s < 32; ++s)
           acc += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sXT + buf * 2 * XT_BLK + xt_offset(g, x * 32 + s)));
         xbar[buf * 64 + x * 16 + g] = acc;
@@ -215,11 +245,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_state_kernel(const S
         for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + buf * 16, desc_mn(am, ks), desc_k16(bx, ks), idesc, ks > 0 ? 1u : 0u);
         umma_commit(&bar_mma[buf]);
       }
-      if (h > 0) epilogue(it - 1);
+      if (h > 0) epilogue(it - 1, bv);
       __syncthreads();
     }
     // drain the last head of this sibling (its tiles read sMap, which the next sibling rewrites)
-    epilogue(r * H + H - 1);
+    {
+      float bv[4];
+      load_bias(r * H + H - 1, bv);
+      epilogue(r * H + H - 1, bv);
+    }
     __syncthreads();
   }
   __syncthreads();
@@ -238,7 +272,10 @@ constexpr int TAB_LD = 33;
 struct MimoOutSmem {
   static constexpr uint32_t C = 0, B = 2 * BLK, MS = 4 * BLK, GB = 6 * BLK, UT = 8 * BLK, SINT = UT + 2 * XT_BLK,
                             TAB = SINT + 2 * XT_BLK, CLK = TAB + 32 * TAB_LD * 4, YST = CLK + 12 * 32 * 4,
-                            TOTAL = YST + 32 * 65 * 4 + 1024;
+                            RAWS = YST + 32 * 65 * 4 + 64,      // [2][128 n][16 g] fp32 entering state of the next kernel head
+                            RAWB = RAWS + 2 * 8192,             // [2][beta 4 x 128 | gamma 4 x 128] fp32
+                            RAWC = RAWB + 2 * 4096,             // [2][dA, w, wd, chi][32] fp32
+                            TOTAL = RAWC + 2 * 512 + 1024;
 };
 
 // swizzled offset of 16-byte chunk `ck` (0..15) of gate row (s, r) in the [32][4][128] bf16 gate tile
@@ -300,18 +337,39 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_out_kernel(const Sca
   uint32_t ph_s = 0, ph_y = 0;
   bool alive = true;
 
+  // Global operands of kernel head `itn` (entering state, biases, clocks) are staged into shared memory by cp.async one
+  // kernel head ahead, so that their latency is hidden behind the previous kernel head's tiles.
+  float* rawS = reinterpret_cast<float*>(sm + MimoOutSmem::RAWS);
+  float* rawB = reinterpret_cast<float*>(sm + MimoOutSmem::RAWB);
+  float* rawC = reinterpret_cast<float*>(sm + MimoOutSmem::RAWC);
+  auto stage = [&](int itn) {
+    if (itn < H * MM_R) {
+      const int hh = itn >> 2, rr = itn & 3, pb = itn & 1;
+      const float* src = a.Sin + ((((int64_t)b * a.nc + c) * H + hh) * MM_R + rr) * (int64_t)(MM_N * MM_G);
+      cp_async16(rawS + pb * 2048 + tid * 4, src + tid * 4);
+      cp_async16(rawS + pb * 2048 + 1024 + tid * 4, src + 1024 + tid * 4);
+      const float* bsrc = tid < 128 ? a.beta : a.gamma;
+      if (bsrc != nullptr) cp_async16(rawB + pb * 1024 + tid * 4, bsrc + ((int64_t)hh * MM_R + rr) * 512 + (tid & 127) * 4);
+      if (tid < 128) {
+        const int which = tid >> 5;
+        const float* arr = which == 0 ? a.dA : which == 1 ? a.w : which == 2 ? a.wd : a.chi;
+        const bool ok = lane < Tv && arr != nullptr;
+        cp_async4z(rawC + pb * 128 + tid, (ok ? arr : a.dA) + ((tok0 + (ok ? lane : 0)) * H + hh) * MM_R + rr, ok);
+      }
+    }
+    cp_async_commit();
+  };
+  stage(0);
+  cp_async_wait_all();
+  __syncthreads();
+
   for (int h = 0; h < H && alive; ++h) {
     build_xt(sUT, reinterpret_cast<const __nv_bfloat16*>(a.u), (int64_t)H * 64, tok0, h, Tv, nullptr);
     for (int r = 0; r < MM_R; ++r) {
+      const int it = h * MM_R + r, pb = it & 1;
       // ---- clocks of kernel head (h, r)
-      float d = 0.f, wt = 0.f, wdt = 0.f, ch = 1.f;
-      if (lane < Tv) {
-        const int64_t i = ((tok0 + lane) * H + h) * MM_R + r;
-        d = a.dA[i];
-        wt = a.w[i];
-        wdt = a.wd[i];
-        if (a.chi) ch = a.chi[i];
-      }
+      const float d = rawC[pb * 128 + lane], wt = rawC[pb * 128 + 32 + lane], wdt = rawC[pb * 128 + 64 + lane];
+      const float ch = (a.chi != nullptr && lane < Tv) ? rawC[pb * 128 + 96 + lane] : 1.f;
       const float cs = warp_prefix32(d, lane);
       if (warp == 0) {
         s_cs[lane] = cs;
@@ -322,6 +380,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_out_kernel(const Sca
         s_chis[r * 32 + lane] = ch;
       }
       __syncthreads();
+      stage(it + 1);          // into the other staging buffer (its last readers finished before the previous barrier)
       // ---- decay table, operand tiles of this kernel head, transposed entering state
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -332,8 +391,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_out_kernel(const Sca
         tab[t * TAB_LD + s] = v * s_chi[t];
       }
       {
-        const float* be = a.beta ? a.beta + (((int64_t)h * MM_R + r) * 4 + qw) * MM_N + wg * 64 : nullptr;
-        const float* ga = a.gamma ? a.gamma + (((int64_t)h * MM_R + r) * 4 + qw) * MM_N + wg * 64 : nullptr;
+        const float* be = a.beta ? rawB + pb * 1024 + qw * MM_N + wg * 64 : nullptr;
+        const float* ga = a.gamma ? rawB + pb * 1024 + 512 + qw * MM_N + wg * 64 : nullptr;
 #pragma unroll
         for (int cc = 0; cc < 8; ++cc) {
           uint32_t wv[4];
@@ -370,7 +429,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_out_kernel(const Sca
       {
         // SinT[g][n] (bf16) from the entering state Sin[n][g] (fp32): thread -> (n, 8 of the 16 g)
         const int n = tid >> 1, g0 = (tid & 1) * 8;
-        const float* src = a.Sin + (((((int64_t)b * a.nc + c) * H + h) * MM_R + r) * MM_N + n) * MM_G + g0;
+        const float* src = rawS + pb * 2048 + n * MM_G + g0;
         const float4 v0 = *reinterpret_cast<const float4*>(src), v1 = *reinterpret_cast<const float4*>(src + 4);
         const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
@@ -422,6 +481,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_out_kernel(const Sca
       }
       alive = wait_warp(&bar_y, ph_y, abort_flag) && alive;
       ph_y ^= 1u;
+      cp_async_wait_all();    // this thread's staged copies of the next kernel head have landed; the barrier publishes them
       alive = __syncthreads_and(alive ? 1 : 0) != 0;
       if (!alive) break;
     }
@@ -499,11 +559,8 @@ struct MimoGradSmem {
 __device__ __forceinline__ uint64_t desc_xt_mn(uint32_t base) { return smem_desc_sw128(base, XT_BLK, 1024u); }
 
 // two transposed drive tiles from one load: plain and row-scaled
-__device__ __forceinline__ void build_xt_pair(uint8_t* plain, uint8_t* scaled, const __nv_bfloat16* src, int64_t row_stride,
-                                              int64_t tok0, int h, int Tv, const float* f) {
+__device__ __forceinline__ void build_xt_pair(uint8_t* plain, uint8_t* scaled, const uint4 raw, const float* f) {
   const int s = threadIdx.x >> 3, v = threadIdx.x & 7;
-  uint4 raw = make_uint4(0, 0, 0, 0);
-  if (s < Tv) raw = *reinterpret_cast<const uint4*>(src + (tok0 + s) * row_stride + h * 64 + v * 8);
   const float fs = f[s];
   const uint32_t* rp = reinterpret_cast<const uint32_t*>(&raw);
 #pragma unroll
@@ -583,22 +640,50 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
   const __nv_bfloat16* up = reinterpret_cast<const __nv_bfloat16*>(a.u);
   const __nv_bfloat16* dyp = reinterpret_cast<const __nv_bfloat16*>(a.dy);
 
+  // Global operands of the NEXT kernel head (entering state and its gradient, biases, clocks, this thread's drive and dy
+  // rows) are staged by cp.async into the dM buffer, which is idle from the end of the mask stage of one kernel head to
+  // the dM read-out of the next; stage A then reads shared memory only.
+  float* stg = reinterpret_cast<float*>(sDM);
+  float *rawS = stg, *rawD = stg + 2048, *rawB = stg + 4096, *rawC = stg + 5120;
+  uint4* slotU = reinterpret_cast<uint4*>(sDM + 21504);
+  uint4* slotDY = reinterpret_cast<uint4*>(sDM + 25600);
+  auto stage = [&](int itn) {
+    if (itn < H * MM_R) {
+      const int hh = itn % H, rr = itn / H;
+      const int64_t son = (((slot * H + hh) * MM_R + rr) * MM_N) * MM_G;
+      cp_async16(rawS + tid * 4, a.Sin + son + tid * 4);
+      cp_async16(rawS + 1024 + tid * 4, a.Sin + son + 1024 + tid * 4);
+      cp_async16(rawD + tid * 4, a.dS + son + tid * 4);
+      cp_async16(rawD + 1024 + tid * 4, a.dS + son + 1024 + tid * 4);
+      const float* bsrc = tid < 128 ? a.beta : a.gamma;
+      if (bsrc != nullptr) cp_async16(rawB + tid * 4, bsrc + ((int64_t)hh * MM_R + rr) * 512 + (tid & 127) * 4);
+      if (tid < 128) {
+        const int which = tid >> 5;
+        const float* arr = which == 0 ? a.dA : which == 1 ? a.w : which == 2 ? a.wd : a.chi;
+        const bool ok = lane < Tv && arr != nullptr;
+        cp_async4z(rawC + tid, (ok ? arr : a.dA) + ((tok0 + (ok ? lane : 0)) * H + hh) * MM_R + rr, ok);
+      }
+      const int s = tid >> 3, v = tid & 7;
+      const bool ok = s < Tv;
+      const int64_t ro = (tok0 + (ok ? s : 0)) * (int64_t)H * 64 + hh * 64 + v * 8;
+      cp_async16z(slotU + tid, up + ro, ok);
+      cp_async16z(slotDY + tid, dyp + ro, ok);
+    }
+    cp_async_commit();
+  };
+  stage(0);
+  cp_async_wait_all();
+  __syncthreads();
+
   for (int r = 0; r < MM_R && alive; ++r) {
     gated_row(reinterpret_cast<const __nv_bfloat16*>(a.Bhat), a.b_ts, reinterpret_cast<const __nv_bfloat16*>(a.gBp), a.gb_ts,
               tok0 + lane, qw, r, wg * 64, lane < Tv, bg);
     for (int h = 0; h < H; ++h) {
       const int it = r * H + h;
       const uint32_t par = (uint32_t)it & 1u;
-      const int64_t so = (((slot * H + h) * MM_R + r) * MM_N) * MM_G;
-      // ================= stage A: clocks, tables, operand tiles
-      float d = 0.f, wt = 0.f, wdt = 0.f, ch = 1.f;
-      if (lane < Tv) {
-        const int64_t i = ((tok0 + lane) * H + h) * MM_R + r;
-        d = a.dA[i];
-        wt = a.w[i];
-        wdt = a.wd[i];
-        if (a.chi) ch = a.chi[i];
-      }
+      // ================= stage A: clocks, tables, operand tiles (all from the staged copies)
+      const float d = rawC[lane], wt = rawC[32 + lane], wdt = rawC[64 + lane];
+      const float ch = (a.chi != nullptr && lane < Tv) ? rawC[96 + lane] : 1.f;
       const float cs = warp_prefix32(d, lane);
       const float tot = __shfl_sync(0xffffffffu, cs, 31);
       if (warp == 0) {
@@ -617,19 +702,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
         tabE[t * TAB_LD + s] = e;
         tabW[t * TAB_LD + s] = wv;
       }
-      build_xt_pair(sUT, sEUT, up, (int64_t)H * 64, tok0, h, Tv, s_e);
-      build_xt_pair(sDYT, sFDYT, dyp, (int64_t)H * 64, tok0, h, Tv, s_f);
+      build_xt_pair(sUT, sEUT, slotU[tid], s_e);
+      build_xt_pair(sDYT, sFDYT, slotDY[tid], s_f);
       {
-        const float* be = a.beta ? a.beta + (((int64_t)h * MM_R + r) * 4 + qw) * MM_N + wg * 64 : nullptr;
-        const float* ga = a.gamma ? a.gamma + (((int64_t)h * MM_R + r) * 4 + qw) * MM_N + wg * 64 : nullptr;
+        const float* be = a.beta ? rawB + qw * MM_N + wg * 64 : nullptr;
+        const float* ga = a.gamma ? rawB + 512 + qw * MM_N + wg * 64 : nullptr;
         store_row(sB, row, wg, bg, be);
         store_row(sC, row, wg, cg, ga);
       }
       {
         // SinT[g][n], dSoT[g][n] (bf16) from Sin[n][g], dSo[n][g] (fp32); <dSo, Sin> on the way
         const int n = tid >> 1, g0 = (tid & 1) * 8;
-        const float* s1 = a.Sin + so + n * MM_G + g0;
-        const float* s2 = a.dS + so + n * MM_G + g0;
+        const float* s1 = rawS + n * MM_G + g0;
+        const float* s2 = rawD + n * MM_G + g0;
         const float4 v0 = *reinterpret_cast<const float4*>(s1), v1 = *reinterpret_cast<const float4*>(s1 + 4);
         const float4 w0 = *reinterpret_cast<const float4*>(s2), w1 = *reinterpret_cast<const float4*>(s2 + 4);
         const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
@@ -767,6 +852,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
       tc_fence_before_sync();
       alive = __syncthreads_and(ok ? 1 : 0) != 0;
       if (!alive) break;
+      stage(it + 1);          // the dM buffer is idle from here to the next kernel head's dM read-out
       // ================= MMA group 3: every product of the masked tiles
       if (tid == 0) {
         tc_fence_after_sync();
@@ -844,13 +930,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
         if (dst != nullptr) {
           float dv[8];
           tmem_ld8f(tmem_addr(tbase, qw * 32, wg == 0 ? TDG : TDB), dv);
-          const float* st = (wg == 0 ? a.Sin : a.dS) + so + row * MM_G;
+          // state term from the bf16 tiles still in shared memory (the MMAs above used the same rounded values)
+          const uint8_t* stt = wg == 0 ? sSinT : sDSoT;
           float sv[16];
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const float4 x = *reinterpret_cast<const float4*>(st + 4 * k);
-            sv[4 * k] = x.x; sv[4 * k + 1] = x.y; sv[4 * k + 2] = x.z; sv[4 * k + 3] = x.w;
-          }
+          for (int g = 0; g < 16; ++g) sv[g] = xt_read(stt, g, row);
 #pragma unroll
           for (int x = 0; x < 4; ++x) {
             float acc = dv[x];
@@ -871,26 +955,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
 #pragma unroll
           for (int k = 0; k < 8; ++k) acc[k] = sDU[t * 65 + v * 8 + k];
           float* p32 = a.du32 + ((tok0 + t) * H + h) * 64 + v * 8;
-          if (r > 0) {
-            const float4 x0 = *reinterpret_cast<const float4*>(p32), x1 = *reinterpret_cast<const float4*>(p32 + 4);
-            acc[0] += x0.x; acc[1] += x0.y; acc[2] += x0.z; acc[3] += x0.w; acc[4] += x1.x; acc[5] += x1.y; acc[6] += x1.z; acc[7] += x1.w;
-          }
-          if (r < MM_R - 1) {
+          if (r == 0) {
             *reinterpret_cast<float4*>(p32) = make_float4(acc[0], acc[1], acc[2], acc[3]);
             *reinterpret_cast<float4*>(p32 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+          } else if (r < MM_R - 1) {
+            // no-return reductions: nothing to wait for; this thread is the only writer of these addresses
+#pragma unroll
+            for (int k = 0; k < 8; ++k) atomicAdd(p32 + k, acc[k]);
           } else {
+            // read at L2, where the reductions above were applied
+            const float4 x0 = __ldcg(reinterpret_cast<const float4*>(p32)), x1 = __ldcg(reinterpret_cast<const float4*>(p32 + 4));
+            acc[0] += x0.x; acc[1] += x0.y; acc[2] += x0.z; acc[3] += x0.w; acc[4] += x1.x; acc[5] += x1.y; acc[6] += x1.z; acc[7] += x1.w;
             *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.du) + ((tok0 + t) * H + h) * 64 + v * 8) =
                 make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
           }
         }
       }
+      cp_async_wait_all();    // the staged operands of the next kernel head have landed; the barrier publishes them
       __syncthreads();
     }
     if (!alive) break;
     // ================= sibling epilogue: X_r -> dBhat (+= gBp_r X_r), dgBp[:, r] = sum_q Bhat_q X_r
     {
       tc_fence_after_sync();
-      float* stage = reinterpret_cast<float*>(sDSc);   // [8 warps][32][65] fp32 over the (now idle) masked-tile buffers
+      // [8 warps][32][64] fp32 = exactly the two (now idle) masked-tile buffers; the dM buffer behind them already holds
+      // the staged operands of the next kernel head and must not be touched
+      float* qsum = reinterpret_cast<float*>(sDSc);
       const __nv_bfloat16* Bh = reinterpret_cast<const __nv_bfloat16*>(a.Bhat);
       const __nv_bfloat16* gB = reinterpret_cast<const __nv_bfloat16*>(a.gBp);
       const int64_t tok = tok0 + lane;
@@ -926,7 +1016,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
             *reinterpret_cast<float4*>(dbh) = make_float4(o8[0], o8[1], o8[2], o8[3]);
             *reinterpret_cast<float4*>(dbh + 4) = make_float4(o8[4], o8[5], o8[6], o8[7]);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) stage[(warp * 32 + lane) * 65 + j * 32 + cc * 8 + k] = __uint_as_float(v[cc * 8 + k]) * hv[k];
+            for (int k = 0; k < 8; ++k) qsum[(warp * 32 + lane) * 64 + ((j * 32 + cc * 8 + k + lane) & 63)] = __uint_as_float(v[cc * 8 + k]) * hv[k];
           }
         }
       }
@@ -938,7 +1028,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
           if (s < Tv) {
             float acc = 0.f;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) acc += stage[((half * 4 + q) * 32 + s) * 65 + col];
+            for (int q = 0; q < 4; ++q) acc += qsum[((half * 4 + q) * 32 + s) * 64 + ((col + s) & 63)];
             a.dgBp[((tok0 + s) * MM_R + r) * MM_N + n] = acc;
           }
         }

@@ -9,6 +9,22 @@ using namespace tc;
 constexpr int TC_THREADS = 256;
 constexpr uint32_t BLK = 128 * 128;   // bytes of one [128 x 64] bf16 block
 
+// ---- cp.async staging (global -> shared without a register round trip) -------------------------------------------
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async16z(void* smem_dst, const void* gsrc, bool valid) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(sz) : "memory");
+}
+// 4-byte copy; `valid` false zero-fills the destination (the source address must still be mapped)
+__device__ __forceinline__ void cp_async4z(void* smem_dst, const void* gsrc, bool valid) {
+  const int sz = valid ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // ---- bounded waits with a CTA-wide abort flag --------------------------------------------------------------------
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   uint32_t addr = smem_u32(bar);
