@@ -33,7 +33,7 @@ int fail(int code, const char* fmt, ...) {
 constexpr int PASS_NB = 8;
 
 template <int VEC, bool REVERSE, bool WRITE>
-__global__ void __launch_bounds__(256) state_pass_kernel(float* __restrict__ buf, const float* __restrict__ atot,
+__global__ void __launch_bounds__(256, 3) state_pass_kernel(float* __restrict__ buf, const float* __restrict__ atot,
                                                          const float* __restrict__ s_in, float* __restrict__ s_out,
                                                          __nv_bfloat16* __restrict__ copy16, int nc, int HR, int NG) {
   const int e = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;

@@ -551,7 +551,7 @@ struct MimoGradSmem {
   static constexpr uint32_t UT = XT, DYT = XT + XT_SZ, FDYT = XT + 2 * XT_SZ, EUT = XT + 3 * XT_SZ, SINT = XT + 4 * XT_SZ,
                             DSOT = XT + 5 * XT_SZ, RS = XT + 6 * XT_SZ, CB = XT + 7 * XT_SZ;
   static constexpr uint32_t TABW = XT + 8 * XT_SZ, TABE = TABW + 32 * TAB_LD * 4, CLK = TABE + 32 * TAB_LD * 4,
-                            PART = CLK + 8 * 32 * 4, XBAR = PART + 6 * 8 * 32 * 4, DU = XBAR + 2 * 64 * 4 + 64,
+                            PART = CLK + 8 * 32 * 4, XBAR = PART + 6 * 8 * 32 * 4, DU = XBAR + 2 * 64 * 4 + 64 + 256,
                             TOTAL = DU + 32 * 65 * 4 + 1024;
 };
 
@@ -604,6 +604,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
   float *p_row = part, *p_diag = part + 256, *p_col = part + 512, *p_da = part + 768, *p_de = part + 1024, *p_sk = part + 1280;
   float* xbar = reinterpret_cast<float*>(sm + L::XBAR);   // dybar[4 o][16 g], ubar[4 q][16 g], red[8]
   float* red = xbar + 128;
+  float* sDg = xbar + 144;                                // [16 g][4 o] skip gains of this kernel head
   float* sDU = reinterpret_cast<float*>(sm + L::DU);      // [32 s][65]
   __shared__ uint64_t bar_a, bar_b, bar_c;
   __shared__ uint32_t tmem_slot;
@@ -644,7 +645,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
   // rows) are staged by cp.async into the dM buffer, which is idle from the end of the mask stage of one kernel head to
   // the dM read-out of the next; stage A then reads shared memory only.
   float* stg = reinterpret_cast<float*>(sDM);
-  float *rawS = stg, *rawD = stg + 2048, *rawB = stg + 4096, *rawC = stg + 5120;
+  float *rawS = stg, *rawD = stg + 2048, *rawB = stg + 4096, *rawC = stg + 5120, *rawDg = stg + 5248;
   uint4* slotU = reinterpret_cast<uint4*>(sDM + 21504);
   uint4* slotDY = reinterpret_cast<uint4*>(sDM + 25600);
   auto stage = [&](int itn) {
@@ -662,6 +663,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
         const float* arr = which == 0 ? a.dA : which == 1 ? a.w : which == 2 ? a.wd : a.chi;
         const bool ok = lane < Tv && arr != nullptr;
         cp_async4z(rawC + tid, (ok ? arr : a.dA) + ((tok0 + (ok ? lane : 0)) * H + hh) * MM_R + rr, ok);
+      }
+      if (tid >= 192 && a.Dg != nullptr) {
+        const int i = tid - 192;             // (g, o)
+        cp_async4z(rawDg + i, a.Dg + (((int64_t)hh * MM_G + (i >> 2)) * MM_R + rr) * 4 + (i & 3), true);
       }
       const int s = tid >> 3, v = tid & 7;
       const bool ok = s < Tv;
@@ -702,6 +707,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
         tabE[t * TAB_LD + s] = e;
         tabW[t * TAB_LD + s] = wv;
       }
+      if (tid < 64) sDg[tid] = a.Dg ? rawDg[tid] : 0.f;
       build_xt_pair(sUT, sEUT, slotU[tid], s_e);
       build_xt_pair(sDYT, sFDYT, slotDY[tid], s_f);
       {
@@ -777,7 +783,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
           const float dyv = xt_read(sDYT, g, qw * 32 + lane);
           pda = fmaf(yc[k], dyv, pda);
           pde = fmaf(dd[k], xt_read(sUT, g, qw * 32 + lane), pde);
-          if (a.Dg) psk = fmaf(dyv * a.Dg[(((int64_t)h * MM_G + g) * MM_R + r) * 4 + qw], xt_read(sUT, g, r * 32 + lane), psk);
+          if (a.Dg) psk = fmaf(dyv * sDg[g * 4 + qw], xt_read(sUT, g, r * 32 + lane), psk);
         }
         p_da[warp * 32 + lane] = pda;
         p_de[warp * 32 + lane] = pde;
@@ -920,7 +926,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
           if (a.Dg && qw == r) {
             float sk = 0.f;
 #pragma unroll
-            for (int o = 0; o < 4; ++o) sk = fmaf(a.Dg[(((int64_t)h * MM_G + g) * MM_R + r) * 4 + o], xt_read(sDYT, g, o * 32 + lane), sk);
+            for (int o = 0; o < 4; ++o) sk = fmaf(sDg[g * 4 + o], xt_read(sDYT, g, o * 32 + lane), sk);
             v = fmaf(chs, sk, v);
           }
           sDU[lane * 65 + g * 4 + qw] = v;
