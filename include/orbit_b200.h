@@ -174,6 +174,52 @@ int orbit_ssd_scan_fwd(const orbit_scan_args* a, const float* S0, float* S_fin, 
 int orbit_ssd_scan_bwd(const orbit_scan_args* a, const float* dS_fin, float* dS0, int dtype, int precision,
                        void* stream);
 
+/* ---- token tails of the SSD-MIMO layer -------------------------------------------------------------------------
+ * Replace the reference's `token_law` (src/orbit_ssm/ssm/ssd_mimo_torch.py:161-267; fused CUDA form `token_tails`,
+ * src/orbit_ssm/layers/tails.py:829).  Slab columns are read in place (row strides in elements); gradients are written
+ * in place into the gradient of the slab.
+ *
+ * Map tail: out[m, x, n] = (weight ? src[m, n*X + x] * rstd[m, x] * weight[n] : src[m, n*X + x]) + bias[n] + add, with
+ * rstd[m, x] = rsqrt(mean_n src[m, n*X + x]^2 + eps)  (B / C maps: RMSNorm over the N state rows of each input / output
+ * column; gates: weight = bias = NULL, add = 1).  src [M, N*X] IO dtype, out [M, X, N] IO dtype contiguous, rstd [M, X]. */
+int orbit_token_map_fwd(const void* src, int64_t src_row_stride, const float* weight, const float* bias, float add, float eps,
+                        void* out, float* rstd, int64_t M, int X, int N, int dtype, void* stream);
+int64_t orbit_token_map_bwd_workspace_bytes(int N);
+/* dsrc [M, N*X] (row stride dsrc_row_stride) receives the input gradient; dweight / dbias [N] (or NULL) the parameter
+ * gradients (fixed-order two-stage sums through `workspace`). */
+int orbit_token_map_bwd(const void* src, int64_t src_row_stride, const float* weight, const float* rstd, const void* dout,
+                        void* dsrc, int64_t dsrc_row_stride, float* dweight, float* dbias, void* workspace,
+                        int64_t workspace_bytes, int64_t M, int X, int N, int dtype, void* stream);
+
+/* Clock tail: per (token, head, sibling)
+ *   dt = softplus(dt_raw) (threshold 20);  rate = exp(A_log[h,r]) (a_act 0) | heavy tail (1) | softplus (2) of a_raw, floor 1e-4
+ *   dA = -dt rate;  trapezoid (trap_raw != NULL): lam = sigmoid(trap_raw[h]), wd = lam dt, w_t = wd_t + dt_{t+1} (1 - lam_{t+1}),
+ *   lag0 = dt_0 (1 - lam_0);  Euler: w = dt;  chi = r_mix[h,r] + rmix_raw.
+ * Raw inputs are slab columns [M, .] in the IO dtype with their own row strides; outputs are fp32 [M, H, R]. */
+typedef struct orbit_clock_args {
+  int64_t M;                 /* rows = B * L                                                                       */
+  int L, H, R;
+  int a_act, a_per_sibling;  /* 0 static A_log; 1 heavy tail; 2 softplus.  a_raw is [M, H*R] if per sibling else [M, H]   */
+  const void* dt_raw;   int64_t dt_rs;
+  const void* a_raw;    int64_t a_rs;
+  const void* trap_raw; int64_t trap_rs;      /* [M, H] or NULL (Euler)                                            */
+  const void* rmix_raw; int64_t rmix_rs;      /* [M, H*R] or NULL                                                  */
+  const float* A_log;        /* [H, R] or NULL                                                                     */
+  const float* r_mix;        /* [H, R] or NULL (no chi)                                                            */
+  float *dA, *w, *wd, *chi;  /* out [M, H, R]; wd only with a trapezoid, chi only with r_mix                       */
+  float* lag0;               /* out [B, H, R] or NULL                                                              */
+  /* backward */
+  const float *ddA, *dw, *dwd, *dchi;   /* [M, H, R]; dwd / dchi may be NULL                                       */
+  const float* dlag0;                   /* [B, H, R] or NULL                                                       */
+  void* d_dt_raw;   int64_t ddt_rs;
+  void* d_a_raw;    int64_t da_rs;
+  void* d_trap_raw; int64_t dtrap_rs;
+  void* d_rmix_raw; int64_t drmix_rs;
+  float* g_alog;             /* out [M, H, R]: per-row term of dA_log (a_act 0); the caller sums it over rows      */
+} orbit_clock_args;
+int orbit_token_clock_fwd(const orbit_clock_args* a, int dtype, void* stream);
+int orbit_token_clock_bwd(const orbit_clock_args* a, int dtype, void* stream);
+
 /* ---- HybridMamba coordinate-decay scan -----------------------------------------------------------------------
  * Replaces the reference's `mh_scan` (src/orbit_ssm/kernels/hybrid_mamba_mh/functions.py:665-677; law restated from
  * src/orbit_ssm/kernels/hybrid_mamba_mh/torch_scan.py:44-76, 180-279) for `coord_static` rows, real and rotating:

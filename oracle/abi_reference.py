@@ -352,3 +352,103 @@ def run_hm(a, name, backward, dtype_code, compute=torch.float64):
         if t.get(dst) is not None:
             t[dst].zero_()
             t[dst][0].copy_(g[key])
+
+
+# ---- token tails ------------------------------------------------------------------------------------------
+def _map(src, weight, bias, add, eps, X, N):
+    B, L = src.shape[:2]
+    m = src.reshape(B, L, N, X).transpose(-1, -2)
+    if weight is not None:
+        m = m * torch.rsqrt(m.square().mean(-1, keepdim=True) + eps) * weight
+    if bias is not None:
+        m = m + bias
+    return m + add
+
+
+def token_map_fwd(src, weight, bias, add, eps, X, N, compute=torch.float64):
+    s = _f(src, compute)
+    out = _map(s, _f(weight, compute), _f(bias, compute), add, eps, X, N)
+    rstd = None
+    if weight is not None:
+        B, L = src.shape[:2]
+        rstd = torch.rsqrt(s.reshape(B, L, N, X).transpose(-1, -2).square().mean(-1) + eps).to(torch.float32)
+    return out.to(src.dtype).contiguous(), rstd
+
+
+def token_map_bwd(src, weight, rstd, dout, X, N, want_dbias, dsrc_out=None, eps=1e-5, compute=torch.float64):
+    s = _f(src, compute).requires_grad_(True)
+    w = _f(weight, compute).requires_grad_(True) if weight is not None else None
+    b = torch.zeros(N, dtype=compute, device=src.device, requires_grad=True) if want_dbias else None
+    ins = [t for t in (s, w, b) if t is not None]
+    with torch.enable_grad():
+        out = _map(s, w, b, 0.0, eps, X, N)
+        gs = dict(zip([id(t) for t in ins], torch.autograd.grad(out, ins, _f(dout, compute))))
+    dsrc = gs[id(s)].to(src.dtype)
+    if dsrc_out is not None:
+        dsrc_out.copy_(dsrc)
+        dsrc = dsrc_out
+    return (dsrc, None if w is None else gs[id(w)].to(torch.float32), None if b is None else gs[id(b)].to(torch.float32))
+
+
+def _clock(t, compute, leaves=False):
+    dev = t["dt_raw"].device
+    B, L = t["dt_raw"].shape[:2]
+    H, Rr = t["H"], t["R"]
+
+    def leaf(v):
+        if v is None:
+            return None
+        v = _f(v, compute)
+        return v.requires_grad_(True) if leaves else v
+
+    dt_raw, a_raw, trap_raw, rmix_raw = leaf(t["dt_raw"]), leaf(t.get("a_raw")), leaf(t.get("trap_raw")), leaf(t.get("rmix_raw"))
+    A_log, r_mix = leaf(t.get("A_log")), leaf(t.get("r_mix"))
+    dt = F.softplus(dt_raw).reshape(B, L, H, Rr)
+    if t["a_act"] == 0:
+        rate = A_log.exp().reshape(H, Rr)
+    else:
+        mag = (O._pass_min(O._pass_min(a_raw, 0.0) + torch.reciprocal(1.0 - O._pass_max(a_raw, 0.0)), 1e-4) if t["a_act"] == 1
+               else O._pass_min(F.softplus(a_raw), 1e-4))
+        rate = mag.reshape(B, L, H, Rr) if t["a_per_sibling"] else mag.reshape(B, L, H, 1)
+    dA = -(dt * rate)
+    wd = lag0 = chi = None
+    if trap_raw is not None:
+        lam = torch.sigmoid(trap_raw)[..., None]
+        lag = dt * (1.0 - lam)
+        wd = lam * dt
+        w = wd + torch.cat([lag[:, 1:], lag.new_zeros(B, 1, H, Rr)], dim=1)
+        lag0 = lag[:, 0]
+    else:
+        w = dt
+    if r_mix is not None:
+        chi = r_mix.reshape(H, Rr) + (rmix_raw.reshape(B, L, H, Rr) if rmix_raw is not None else 0.0)
+        chi = chi.expand(B, L, H, Rr)
+    return dict(dA=dA, w=w, wd=wd, chi=chi, lag0=lag0), dict(dt_raw=dt_raw, a_raw=a_raw, trap_raw=trap_raw, rmix_raw=rmix_raw,
+                                                              A_log=A_log, r_mix=r_mix)
+
+
+def run_clock(a, name, backward, dtype_code, compute=torch.float64):
+    """Torch restatement of `orbit_token_clock_fwd` / `_bwd` on the tensors named in ``a.t``."""
+    t = a.t
+    if not backward:
+        out, _ = _clock(t, compute)
+        for k in ("dA", "w", "wd", "chi", "lag0"):
+            if t.get(k) is not None:
+                t[k].copy_(out[k])
+        return
+    with torch.enable_grad():
+        out, leaves = _clock(t, compute, leaves=True)
+        loss = (out["dA"] * _f(t["ddA"], compute)).sum() + (out["w"] * _f(t["dw"], compute)).sum()
+        for k, gk in (("wd", "dwd"), ("chi", "dchi"), ("lag0", "dlag0")):
+            if out[k] is not None and t.get(gk) is not None:
+                loss = loss + (out[k] * _f(t[gk], compute)).sum()
+        live = [k for k, v in leaves.items() if v is not None]
+        gs = dict(zip(live, torch.autograd.grad(loss, [leaves[k] for k in live], allow_unused=True)))
+    for key in ("dt_raw", "a_raw", "trap_raw", "rmix_raw"):
+        dst = t.get("d_" + key)
+        if dst is not None:
+            gv = gs.get(key)
+            dst.copy_(torch.zeros_like(leaves[key]) if gv is None else gv)
+    if t.get("g_alog") is not None:
+        # per-row term of dA_log: d dA / d A_log = dA itself (rate = exp(A_log))
+        t["g_alog"].copy_(_f(t["ddA"], compute) * out["dA"].detach())

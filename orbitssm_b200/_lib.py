@@ -48,6 +48,21 @@ class HmArgs(C.Structure):
     )
 
 
+class ClockArgs(C.Structure):
+    """Mirror of ``orbit_clock_args`` (include/orbit_b200.h); field order and types must match the header."""
+    _fields_ = [
+        ("M", C.c_int64), ("L", C.c_int), ("H", C.c_int), ("R", C.c_int), ("a_act", C.c_int), ("a_per_sibling", C.c_int),
+        ("dt_raw", C.c_void_p), ("dt_rs", C.c_int64), ("a_raw", C.c_void_p), ("a_rs", C.c_int64),
+        ("trap_raw", C.c_void_p), ("trap_rs", C.c_int64), ("rmix_raw", C.c_void_p), ("rmix_rs", C.c_int64),
+        ("A_log", C.c_void_p), ("r_mix", C.c_void_p),
+        ("dA", C.c_void_p), ("w", C.c_void_p), ("wd", C.c_void_p), ("chi", C.c_void_p), ("lag0", C.c_void_p),
+        ("ddA", C.c_void_p), ("dw", C.c_void_p), ("dwd", C.c_void_p), ("dchi", C.c_void_p), ("dlag0", C.c_void_p),
+        ("d_dt_raw", C.c_void_p), ("ddt_rs", C.c_int64), ("d_a_raw", C.c_void_p), ("da_rs", C.c_int64),
+        ("d_trap_raw", C.c_void_p), ("dtrap_rs", C.c_int64), ("d_rmix_raw", C.c_void_p), ("drmix_rs", C.c_int64),
+        ("g_alog", C.c_void_p),
+    ]
+
+
 HM_CHUNK = 32     # checkpoint interval (tokens) the HybridMamba backward kernel is written for
 
 _P, _I, _L, _F = C.c_void_p, C.c_int, C.c_int64, C.c_float
@@ -68,6 +83,11 @@ SIGNATURES = {
     "orbit_ssd_scan_phase": (_I, [C.POINTER(ScanArgs), _I, _P, _P, _I, _I, _P]),
     "orbit_ssd_scan_fwd": (_I, [C.POINTER(ScanArgs), _P, _P, _I, _I, _P]),
     "orbit_ssd_scan_bwd": (_I, [C.POINTER(ScanArgs), _P, _P, _I, _I, _P]),
+    "orbit_token_map_fwd": (_I, [_P, _L, _P, _P, _F, _F, _P, _P, _L, _I, _I, _I, _P]),
+    "orbit_token_map_bwd_workspace_bytes": (_L, [_I]),
+    "orbit_token_map_bwd": (_I, [_P, _L, _P, _P, _P, _P, _L, _P, _P, _P, _L, _L, _I, _I, _I, _P]),
+    "orbit_token_clock_fwd": (_I, [C.POINTER(ClockArgs), _I, _P]),
+    "orbit_token_clock_bwd": (_I, [C.POINTER(ClockArgs), _I, _P]),
     "orbit_hm_scan_fwd": (_I, [C.POINTER(HmArgs), _I, _P]),
     "orbit_hm_scan_bwd": (_I, [C.POINTER(HmArgs), _I, _P]),
     "orbit_selftest_umma": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),

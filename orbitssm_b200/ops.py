@@ -101,7 +101,8 @@ class GradArena:
             o += w
 
     def view(self, index, like):
-        """Column range `index` of the (lazily allocated) buffer, or None when the arena cannot serve `like`."""
+        """Column range `index` of the (lazily allocated) buffer, or None when the arena cannot serve `like` (a tensor
+        of the range's shape: [..., width])."""
         if self.shape is None or like.dim() != len(self.shape) or tuple(like.shape[:-1]) != self.shape[:-1]:
             return None
         o, w = self.offsets[index]
@@ -627,6 +628,183 @@ class SSDScanFn(torch.autograd.Function):
         return (None, None, None, None, g["du"], cast(g["dBhat"], dts[1]), cast(g["dgBp"], dts[2]),
                 cast(g["dChat"], dts[3]), cast(g["dgCp"], dts[4]), g["dbeta"], g["dgamma"], g["dchi"], g["ddA"], g["dw"],
                 g["dwd"], g["dDg"], g["dS0"], None)
+
+
+# ----------------------------------------------------------------------------------------------------
+#  token tails (maps and clocks between the input GEMM and the scan)
+# ----------------------------------------------------------------------------------------------------
+def _row_view(who, t):
+    """[B, L, W] tensor with a contiguous last axis whose batch stride equals L * row stride -> (rows M, row stride)."""
+    if t.dim() != 3 or (t.shape[-1] > 1 and t.stride(-1) != 1) or (t.shape[0] > 1 and t.stride(0) != t.shape[1] * t.stride(1)):
+        raise ValueError(f"{who}: expected [B, L, W] rows with uniform row stride, got shape {tuple(t.shape)} strides {t.stride()}")
+    return t.shape[0] * t.shape[1], t.stride(1)
+
+
+def token_map_fwd(src, weight, bias, add, eps, X, N):
+    """src [B, L, N*X] (slab columns, (n, x) interleaved) -> (out [B, L, X, N] IO dtype, rstd [B, L, X] | None)."""
+    _require_cuda("token_map_fwd", src, weight, bias)
+    M, rs = _row_view("token_map_fwd", src)
+    B, L = src.shape[:2]
+    out = torch.empty((B, L, X, N), device=src.device, dtype=src.dtype)
+    rstd = torch.empty((B, L, X), device=src.device, dtype=torch.float32) if weight is not None else None
+    with _timed("token_map_fwd", 1 if M else 0):
+        _lib.check(_lib.load().orbit_token_map_fwd(_ptr(src), rs, _ptr(weight), _ptr(bias), float(add), float(eps), _ptr(out),
+                                                   _ptr(rstd), M, X, N, _dtype_code("token_map_fwd", src), _stream()),
+                   "orbit_token_map_fwd")
+    return out, rstd
+
+
+def token_map_bwd(src, weight, rstd, dout, X, N, want_dbias, dsrc_out=None):
+    """Returns (dsrc [B, L, N*X], dweight [N] | None, dbias [N] | None); `dsrc_out` receives dsrc in place."""
+    _require_cuda("token_map_bwd", src, weight, rstd, dout)
+    M, rs = _row_view("token_map_bwd", src)
+    dout = dout.contiguous()
+    dsrc = dsrc_out if dsrc_out is not None else torch.empty(src.shape, device=src.device, dtype=src.dtype)
+    _, drs = _row_view("token_map_bwd", dsrc)
+    f32 = dict(device=src.device, dtype=torch.float32)
+    dweight = torch.empty((N,), **f32) if weight is not None else None
+    dbias = torch.empty((N,), **f32) if want_dbias else None
+    lib = _lib.load()
+    nbytes = lib.orbit_token_map_bwd_workspace_bytes(N)
+    ws = torch.empty((int(nbytes),), device=src.device, dtype=torch.uint8) if (dweight is not None or dbias is not None) else None
+    with _timed("token_map_bwd", (2 if ws is not None else 1) if M else 0):
+        _lib.check(lib.orbit_token_map_bwd(_ptr(src), rs, _ptr(weight), _ptr(rstd), _ptr(dout), _ptr(dsrc), drs, _ptr(dweight),
+                                           _ptr(dbias), _ptr(ws), int(nbytes) if ws is not None else 0, M, X, N,
+                                           _dtype_code("token_map_bwd", src), _stream()), "orbit_token_map_bwd")
+    return dsrc, dweight, dbias
+
+
+class TokenMapFn(torch.autograd.Function):
+    """out[b, l, x, :] = rmsnorm_N(src[b, l, n*X + x]) * weight + bias + add  (weight / bias optional)."""
+
+    @staticmethod
+    def forward(ctx, src, weight, bias, add, eps, X, N, slot=None):
+        w32, b32 = _f32(weight), _f32(bias)
+        out, rstd = token_map_fwd(src, w32, b32, add, eps, X, N)
+        ctx.save_for_backward(src, w32, rstd)
+        ctx.meta = (X, N, None if weight is None else weight.dtype, None if bias is None else bias.dtype, slot)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        src, w32, rstd = ctx.saved_tensors
+        X, N, wdt, bdt, slot = ctx.meta
+        dsrc_out = slot[0].view(slot[1], src) if slot is not None else None
+        dsrc, dw, db = token_map_bwd(src, w32, rstd, dout.to(src.dtype), X, N, bdt is not None, dsrc_out=dsrc_out)
+        return (dsrc, None if dw is None else dw.to(wdt), None if db is None else db.to(bdt), None, None, None, None, None)
+
+
+def _fill_clock(a, t):
+    dt_raw = t["dt_raw"]
+    B, L = dt_raw.shape[:2]
+    a.M, a.L, a.H, a.R = B * L, L, t["H"], t["R"]
+    a.a_act, a.a_per_sibling = t["a_act"], int(t["a_per_sibling"])
+    for key, rs in (("dt_raw", "dt_rs"), ("a_raw", "a_rs"), ("trap_raw", "trap_rs"), ("rmix_raw", "rmix_rs"),
+                    ("d_dt_raw", "ddt_rs"), ("d_a_raw", "da_rs"), ("d_trap_raw", "dtrap_rs"), ("d_rmix_raw", "drmix_rs")):
+        v = t.get(key)
+        if v is not None:
+            _, stride = _row_view("token_clock", v)
+            setattr(a, rs, stride)
+            if v.is_cuda:
+                setattr(a, key, v.data_ptr())
+    for key in ("A_log", "r_mix", "dA", "w", "wd", "chi", "lag0", "ddA", "dw", "dwd", "dchi", "dlag0", "g_alog"):
+        v = t.get(key)
+        if v is not None and v.is_cuda:
+            setattr(a, key, v.data_ptr())
+    a.t = t
+
+
+def run_clock(a, name, backward, dtype_code):
+    """One clock-tail launch through the C-ABI (`a.t`: the tensors behind the pointers, for the CPU host-logic tests)."""
+    fn = _lib.load().orbit_token_clock_bwd if backward else _lib.load().orbit_token_clock_fwd
+    with _timed(name, 1 if a.M else 0):
+        _lib.check(fn(C.byref(a), dtype_code, _stream()), name)
+
+
+def token_clock_fwd(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, a_per_sibling, H, R):
+    """Raw slab columns [B, L, .] -> dict(dA, w, wd | None, chi | None, lag0 | None), fp32 [B, L, H, R] ([B, H, R] for lag0)."""
+    _require_cuda("token_clock_fwd", dt_raw, a_raw, trap_raw, rmix_raw)
+    B, L = dt_raw.shape[:2]
+    f32 = dict(device=dt_raw.device, dtype=torch.float32)
+    t = dict(dt_raw=dt_raw, a_raw=a_raw, trap_raw=trap_raw, rmix_raw=rmix_raw, A_log=_f32(A_log), r_mix=_f32(r_mix), a_act=a_act,
+             a_per_sibling=a_per_sibling, H=H, R=R)
+    t["dA"] = torch.empty((B, L, H, R), **f32)
+    t["w"] = torch.empty((B, L, H, R), **f32)
+    t["wd"] = torch.empty((B, L, H, R), **f32) if trap_raw is not None else None
+    t["lag0"] = torch.empty((B, H, R), **f32) if trap_raw is not None else None
+    t["chi"] = torch.empty((B, L, H, R), **f32) if r_mix is not None else None
+    a = _lib.ClockArgs()
+    _fill_clock(a, t)
+    run_clock(a, "token_clock_fwd", False, _dtype_code("token_clock_fwd", dt_raw))
+    return {k: t[k] for k in ("dA", "w", "wd", "chi", "lag0")}
+
+
+def token_clock_bwd(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, a_per_sibling, H, R, g, outs=None):
+    """`g`: dict of gradients ddA, dw, dwd, dchi, dlag0 (None = zero).  Returns dict(dt_raw, a_raw, trap_raw, rmix_raw,
+    A_log, r_mix); `outs` may carry in-place destinations for the four raw gradients."""
+    B, L = dt_raw.shape[:2]
+    dev = dt_raw.device
+    f32 = dict(device=dev, dtype=torch.float32)
+    outs = outs or {}
+
+    def dest(key, like):
+        if like is None:
+            return None
+        v = outs.get(key)
+        return v if v is not None else torch.empty(like.shape, device=dev, dtype=like.dtype)
+
+    def zeros_like_out(v, shape):
+        return torch.zeros(shape, **f32) if v is None else v.to(torch.float32).contiguous()
+
+    t = dict(dt_raw=dt_raw, a_raw=a_raw, trap_raw=trap_raw, rmix_raw=rmix_raw, A_log=_f32(A_log), r_mix=_f32(r_mix), a_act=a_act,
+             a_per_sibling=a_per_sibling, H=H, R=R)
+    t["ddA"] = zeros_like_out(g.get("ddA"), (B, L, H, R))
+    t["dw"] = zeros_like_out(g.get("dw"), (B, L, H, R))
+    t["dwd"] = None if (trap_raw is None or g.get("dwd") is None) else g["dwd"].to(torch.float32).contiguous()
+    t["dchi"] = None if (r_mix is None or g.get("dchi") is None) else g["dchi"].to(torch.float32).contiguous()
+    t["dlag0"] = None if (trap_raw is None or g.get("dlag0") is None) else g["dlag0"].to(torch.float32).contiguous()
+    t["d_dt_raw"] = dest("dt_raw", dt_raw)
+    t["d_a_raw"] = dest("a_raw", a_raw)
+    t["d_trap_raw"] = dest("trap_raw", trap_raw)
+    t["d_rmix_raw"] = dest("rmix_raw", rmix_raw)
+    t["g_alog"] = torch.empty((B, L, H, R), **f32) if a_act == 0 else None
+    a = _lib.ClockArgs()
+    _fill_clock(a, t)
+    run_clock(a, "token_clock_bwd", True, _dtype_code("token_clock_bwd", dt_raw))
+    return dict(dt_raw=t["d_dt_raw"], a_raw=t["d_a_raw"], trap_raw=t["d_trap_raw"], rmix_raw=t["d_rmix_raw"],
+                A_log=None if t["g_alog"] is None else t["g_alog"].sum((0, 1)),
+                r_mix=None if t["dchi"] is None else t["dchi"].sum((0, 1)))
+
+
+class TokenClockFn(torch.autograd.Function):
+    """Clocks of the scan from the raw slab columns; absent outputs (wd, chi, lag0) come back as empty tensors."""
+
+    @staticmethod
+    def forward(ctx, dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, a_per_sibling, H, R, slots=None):
+        o = token_clock_fwd(dt_raw, a_raw, trap_raw, rmix_raw, None if A_log is None else A_log.detach(),
+                            None if r_mix is None else r_mix.detach(), a_act, a_per_sibling, H, R)
+        ctx.save_for_backward(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix)
+        ctx.meta = (a_act, a_per_sibling, H, R, slots or {})
+        ctx.set_materialize_grads(False)
+        empty = o["dA"].new_zeros(0)
+        return o["dA"], o["w"], (o["wd"] if o["wd"] is not None else empty), (o["chi"] if o["chi"] is not None else empty), \
+            (o["lag0"] if o["lag0"] is not None else empty)
+
+    @staticmethod
+    def backward(ctx, ddA, dw, dwd, dchi, dlag0):
+        dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix = ctx.saved_tensors
+        a_act, a_per_sibling, H, R, slots = ctx.meta
+        outs = {}
+        for key, like in (("dt_raw", dt_raw), ("a_raw", a_raw), ("trap_raw", trap_raw), ("rmix_raw", rmix_raw)):
+            if like is not None and key in slots:
+                outs[key] = slots[key][0].view(slots[key][1], like)
+        g = token_clock_bwd(dt_raw, a_raw, trap_raw, rmix_raw, None if A_log is None else A_log.detach(),
+                            None if r_mix is None else r_mix.detach(), a_act, a_per_sibling, H, R,
+                            dict(ddA=ddA, dw=dw, dwd=dwd, dchi=dchi, dlag0=dlag0), outs)
+        return (g["dt_raw"], g["a_raw"], g["trap_raw"], g["rmix_raw"],
+                None if (A_log is None or g["A_log"] is None) else g["A_log"].reshape(A_log.shape).to(A_log.dtype),
+                None if (r_mix is None or g["r_mix"] is None) else g["r_mix"].reshape(r_mix.shape).to(r_mix.dtype),
+                None, None, None, None, None)
 
 
 # ----------------------------------------------------------------------------------------------------

@@ -135,6 +135,11 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         self.out_proj = nn.Linear(self.d_out, s.d_model, bias=False)
 
         self.tok_width = s.tok_width
+        # column ranges of the slab as the forward splits them (B | C kept together when they share a conv)
+        pk = [(k, w) for k, _, w, _ in s.slab]
+        if s.bc_conv:
+            pk = [("BC", pk[0][1] + pk[1][1])] + pk[2:]
+        self._part_keys, self._part_widths = tuple(k for k, _ in pk), tuple(w for _, w in pk)
         self._proj_keys = tuple(k for k, _, _, _ in s.slab)
         self._proj_attrs = tuple(a for _, a, _, _ in s.slab)
         self._proj_widths = tuple(w for _, _, w, _ in s.slab)
@@ -245,64 +250,44 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         return torch.cat(parts_w, 0).to(dtype), torch.cat(parts_b, 0).to(dtype)
 
     # -- token law (reference: ssd_mimo_torch.py:161-267, 769-788) ----------------------------------------------
-    def _token_law(self, slab, b_src, c_src, io):
-        """Per-token operands of the scan from the slab columns.  Law arithmetic in fp32; maps handed to the scan in
-        the IO dtype; clocks, decays and weights stay fp32."""
+    def _token_law(self, parts, b_src, c_src, io, arena=None, slot_of=None):
+        """Per-token operands of the scan from the slab columns (`parts`: key -> column view).  Maps and clocks run in the
+        token-tail kernels (fp32 arithmetic; maps handed to the scan in the IO dtype; clocks, decays, weights fp32)."""
         s = self.spec
-        Bsz, L = slab.shape[:2]
         H, R, O, N = s.H, s.R, s.O, s.N
         f = torch.float32
+        slot_of = slot_of or {}
 
-        def part(key):
-            o, wd_ = s.slab_off[key]
-            return slab[..., o:o + wd_].to(f)
+        def slot(key):
+            return (arena, slot_of[key]) if (arena is not None and key in slot_of) else None
 
-        def base_map(src, X, norm, bias):
+        def base_map(src, key, X, norm, bias):
             plain = not (norm is not None or bias is not None)
             if X == 1 and plain:
                 return src.unsqueeze(2)                                       # [B, L, 1, N] view of the source columns
-            m = src.to(f).reshape(Bsz, L, N, X).transpose(-1, -2)
-            if norm is not None:
-                m = m * torch.rsqrt(m.square().mean(-1, keepdim=True) + s.map_eps) * norm.weight.to(f)
-            if bias is not None:
-                m = m + bias.to(f)
-            return m.to(io).contiguous()
+            return ops.TokenMapFn.apply(src, None if norm is None else norm.weight, bias, 0.0, s.map_eps, X, N,
+                                        slot(key) if src is parts.get(key) else None)
 
         shared = s.bc_bias and not s.head_bias
-        Bhat = base_map(b_src, R, self.B_norm if s.b_norm else None, self.B_bias if shared else None)
-        Chat = base_map(c_src, O, self.C_norm if s.c_norm else None, self.C_bias if shared else None)
-        gBp = (1.0 + part("gB").reshape(Bsz, L, N, R).transpose(-1, -2)).to(io).contiguous() if s.use_g_b else None
-        gCp = (1.0 + part("gC").reshape(Bsz, L, N, O).transpose(-1, -2)).to(io).contiguous() if s.use_g_c else None
+        Bhat = base_map(b_src, "B", R, self.B_norm if s.b_norm else None, self.B_bias if shared else None)
+        Chat = base_map(c_src, "C", O, self.C_norm if s.c_norm else None, self.C_bias if shared else None)
+        gBp = ops.TokenMapFn.apply(parts["gB"], None, None, 1.0, s.map_eps, R, N, slot("gB")) if s.use_g_b else None
+        gCp = ops.TokenMapFn.apply(parts["gC"], None, None, 1.0, s.map_eps, O, N, slot("gC")) if s.use_g_c else None
         beta = self.B_bias.to(f).transpose(-1, -2).contiguous() if s.head_bias else None       # [H, R, q, N]
         gamma = self.C_bias.to(f).transpose(-1, -2).contiguous() if s.head_bias else None      # [H, R, o, N]
 
-        dt = F.softplus(part("dt")).reshape(Bsz, L, H, R)
-        if s.a_dyn:
-            va = part("a")
-            if s.a_act == "heavy_tail":
-                mag = _pass_min(_pass_min(va, 0.0) + torch.reciprocal(1.0 - _pass_max(va, 0.0)), 1e-4)
-            else:
-                mag = _pass_min(F.softplus(va), 1e-4)
-            rate = mag.reshape(Bsz, L, H, R) if s.a_dyn_per_sibling else mag.reshape(Bsz, L, H, 1)
-        else:
-            rate = self.A_log.to(f).exp()
-        dA = -(dt * rate)
-        lag0 = None
-        if s.use_trap:
-            lam = torch.sigmoid(part("trap"))[..., None]                      # [B, L, H, 1]
-            lag = dt * (1.0 - lam)
-            wd_ = lam * dt
-            w = wd_ + torch.cat([lag[:, 1:], lag.new_zeros(Bsz, 1, H, R)], dim=1)
-            lag0 = lag[:, 0]
-            wd_ = wd_.contiguous()
-        else:
-            w, wd_ = dt, None
-        chi = None
-        if s.r_mix_mode != "none":
-            chi = self.r_mix.to(f)
-            if s.r_mix_dyn:
-                chi = chi + part("rmix").reshape(Bsz, L, H, R)
-            chi = chi.expand(Bsz, L, H, R).contiguous()
+        a_act = 0 if not s.a_dyn else (1 if s.a_act == "heavy_tail" else 2)
+        rmix_raw = parts.get("rmix") if (s.r_mix_mode != "none" and s.r_mix_dyn) else None
+        slots = {k2: slot(k) for k, k2 in (("dt", "dt_raw"), ("a", "a_raw"), ("trap", "trap_raw"), ("rmix", "rmix_raw"))
+                 if slot(k) is not None}
+        dA, w, wd_, chi, lag0 = ops.TokenClockFn.apply(
+            parts["dt"], parts.get("a") if s.a_dyn else None, parts.get("trap") if s.use_trap else None, rmix_raw,
+            None if s.a_dyn else self.A_log, self.r_mix if s.r_mix_mode != "none" else None, a_act,
+            bool(s.a_dyn and s.a_dyn_per_sibling), H, R, slots)
+        if not s.use_trap:
+            wd_, lag0 = None, None
+        if s.r_mix_mode == "none":
+            chi = None
         Dg = None
         if s.skip:
             D = self.D.to(f)
@@ -313,8 +298,7 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
             else:
                 Dg = D
             Dg = Dg.contiguous()
-        return dict(Bhat=Bhat, Chat=Chat, gBp=gBp, gCp=gCp, beta=beta, gamma=gamma, dA=dA.contiguous(),
-                    w=w.contiguous(), wd=wd_, chi=chi, Dg=Dg, lag0=lag0)
+        return dict(Bhat=Bhat, Chat=Chat, gBp=gBp, gCp=gCp, beta=beta, gamma=gamma, dA=dA, w=w, wd=wd_, chi=chi, Dg=Dg, lag0=lag0)
 
     # -- forward -------------------------------------------------------------------------------------------
     def forward(self, x, *, state=None, return_state=False):
@@ -349,8 +333,12 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
             xa = x.to(io)
             wcat, bcat = self._fused_weight(io)
             proj = F.linear(xa, wcat, bcat)                                    # [B, L, drive | z | slab | pad]
-            arena = ops.GradArena()        # conv and gate backward write d(drive), dz straight into d(proj)
-            drive_raw, z, slab = ops.SplitColumnsFn.apply(proj, arena, s.d_inner, self.d_gate, s.tok_width)
+            # every consumer of a column range writes that range of d(proj) in place (conv, gate, token tails)
+            arena = ops.GradArena()
+            keys, widths = self._part_keys, self._part_widths
+            drive_raw, z, *cols = ops.SplitColumnsFn.apply(proj, arena, s.d_inner, self.d_gate, *widths)
+            parts = dict(zip(keys, cols))
+            slot_of = {k: 2 + i for i, k in enumerate(keys)}
             new = State()
             if self.conv1d is not None:
                 win = state["conv_state"] if state is not None else None
@@ -362,20 +350,20 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
                     new["conv_state"] = _next_window(win, drive_raw, s.d_conv)
             else:
                 u = drive_raw.contiguous()
-            ob, wb = s.slab_off["B"]
-            oc, wc = s.slab_off["C"]
+            wb, wc = s.slab_off["B"][1], s.slab_off["C"][1]
             if self.bc_conv1d is not None:
-                bc_raw = slab[..., ob:oc + wc]                                 # B | C adjacent at the slab head
+                bc_raw = parts["BC"]                                           # B | C adjacent at the slab head
                 win = state["bc_conv_state"] if state is not None else None
                 if cp is not None:
                     win = ops.HaloFn.apply(bc_raw[:, L - (s.d_conv - 1):], cp, s.d_conv)
-                bc = (ops.CausalConvFn.apply(bc_raw, self.bc_conv1d.conv.weight, self.bc_conv1d.conv.bias, win) if L > 0
+                bc = (ops.CausalConvFn.apply(bc_raw, self.bc_conv1d.conv.weight, self.bc_conv1d.conv.bias, win,
+                                             (arena, slot_of["BC"])) if L > 0
                       else bc_raw.contiguous())
                 if want_state:
                     new["bc_conv_state"] = _next_window(win, bc_raw, s.d_conv)
                 b_src, c_src = bc[..., :wb], bc[..., wb:]
             else:
-                b_src, c_src = slab[..., ob:ob + wb], slab[..., oc:oc + wc]
+                b_src, c_src = parts["B"], parts["C"]
 
             h0 = state["hidden_state"] if state is not None else None
             wp = state.get("write_prev") if state is not None else None
@@ -384,7 +372,7 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
                 hidden = h0.to(torch.float32) if h0 is not None else u.new_zeros(Bsz, H, P, N, dtype=torch.float32)
                 v_last = wp.to(torch.float32) if wp is not None else torch.zeros_like(hidden)
             else:
-                law = self._token_law(slab, b_src, c_src, io)
+                law = self._token_law(parts, b_src, c_src, io, arena, slot_of)
                 S0 = None
                 if h0 is not None:
                     S0 = h0.to(torch.float32).reshape(Bsz, H, G, R, N).permute(0, 1, 3, 4, 2)

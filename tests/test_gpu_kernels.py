@@ -374,3 +374,74 @@ def test_hm_scan(dtype, case):
     for k, v in g.items():
         if v is not None:
             assert torch.equal(v, g2[k]), ("not reproducible", k)
+
+
+# ---------------------------------------------------------------------------------------------------- token tails
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,L,X,N,norm,bias,add", [(2, 37, 4, 128, True, False, 0.0), (1, 5, 1, 16, True, True, 0.0),
+                                                   (3, 19, 2, 8, False, False, 1.0), (2, 64, 4, 128, False, False, 1.0),
+                                                   (1, 9, 3, 200, True, True, 0.0)])
+def test_token_map(dtype, B, L, X, N, norm, bias, add):
+    g = torch.Generator().manual_seed(B * 100 + L)
+    slab = torch.randn(B, L, N * X + 24, generator=g).to(dtype).to(DEV)       # the map reads a column range of a wider slab
+    src = slab[..., 8:8 + N * X]
+    w = (1 + 0.3 * torch.randn(N, generator=g)).to(DEV) if norm else None
+    b = (0.2 * torch.randn(N, generator=g)).to(DEV) if bias else None
+    out, rstd = ops.token_map_fwd(src, w, b, add, 1e-5, X, N)
+    rout, rr = R.token_map_fwd(src, w, b, add, 1e-5, X, N)
+    assert rel(out, rout) < tol(dtype)
+    if norm:
+        assert rel(rstd, rr) < 1e-5
+    dout = torch.randn(B, L, X, N, generator=g).to(dtype).to(DEV)
+    dslab = torch.full_like(slab, float("nan"))
+    dsrc, dw, db = ops.token_map_bwd(src, w, rstd, dout, X, N, bias, dsrc_out=dslab[..., 8:8 + N * X])
+    rd, rw, rb = R.token_map_bwd(src, w, rstd, dout, X, N, bias)
+    assert dsrc.data_ptr() == dslab[..., 8:8 + N * X].data_ptr()
+    assert rel(dsrc, rd) < tol(dtype, True)
+    assert torch.isnan(dslab[..., :8]).all() and torch.isnan(dslab[..., 8 + N * X:]).all()      # nothing written outside the range
+    if norm:
+        assert rel(dw, rw) < 2e-4 if dtype == torch.float32 else rel(dw, rw) < 6e-3
+    if bias:
+        assert rel(db, rb) < 2e-5
+    d2, w2, b2 = ops.token_map_bwd(src, w, rstd, dout, X, N, bias)
+    assert torch.equal(d2, dsrc) and (dw is None or torch.equal(dw, w2)) and (db is None or torch.equal(db, b2))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("a_act,per_sib,trap,rmix", [(0, False, False, False), (0, False, True, True), (1, False, True, True),
+                                                     (1, True, False, True), (2, True, True, False)])
+def test_token_clock(dtype, a_act, per_sib, trap, rmix):
+    import ctypes as C
+    B, L, H, Rr = 2, 23, 3, 2
+    g = torch.Generator().manual_seed(a_act * 10 + trap)
+    slab = torch.randn(B, L, 64, generator=g).to(dtype).to(DEV)
+    dt_raw = slab[..., 0:H * Rr]
+    a_raw = (slab[..., 8:8 + (H * Rr if per_sib else H)] * 2.0) if a_act else None
+    if a_raw is not None:
+        a_raw = a_raw.contiguous()
+    trap_raw = slab[..., 20:20 + H] if trap else None
+    rmix_raw = slab[..., 32:32 + H * Rr] if rmix else None
+    A_log = torch.randn(H, Rr, generator=g).to(DEV) if a_act == 0 else None
+    r_mix = torch.randn(H, Rr, generator=g).to(DEV) if rmix else None
+    o = ops.token_clock_fwd(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, per_sib, H, Rr)
+    t = dict(dt_raw=dt_raw, a_raw=a_raw, trap_raw=trap_raw, rmix_raw=rmix_raw, A_log=A_log, r_mix=r_mix, a_act=a_act,
+             a_per_sibling=per_sib, H=H, R=Rr)
+    ro, _ = R._clock(t, torch.float64)
+    for k in ("dA", "w", "wd", "chi", "lag0"):
+        if ro[k] is None:
+            assert o[k] is None, k
+        else:
+            assert rel(o[k], ro[k]) < 2e-6, (k, rel(o[k], ro[k]))
+    gr = {k: torch.randn(B, L, H, Rr, generator=g).to(DEV) for k in ("ddA", "dw", "dwd", "dchi")}
+    gr["dlag0"] = torch.randn(B, H, Rr, generator=g).to(DEV)
+    got = ops.token_clock_bwd(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, per_sib, H, Rr, gr)
+    with torch.enable_grad():
+        ro, leaves = R._clock(t, torch.float64, leaves=True)
+        loss = sum((ro[k] * gr["d" + k].double()).sum() for k in ("dA", "w", "wd", "chi", "lag0") if ro[k] is not None)
+        live = [k for k, v in leaves.items() if v is not None]
+        want = dict(zip(live, torch.autograd.grad(loss, [leaves[k] for k in live], allow_unused=True)))
+    for k, v in want.items():
+        if v is None:
+            continue
+        lim = 2e-5 if (dtype == torch.float32 or k in ("A_log", "r_mix")) else 6e-3
+        assert rel(got[k].reshape(v.shape), v) < lim, (k, rel(got[k].reshape(v.shape), v))
