@@ -199,12 +199,12 @@ class HybridMambaSSM(StateLifecycle, nn.Module):
         if self.dt_low is not None:
             dt_lin = F.linear(dt_lin, self.dt_proj.weight.to(io))
         delta = F.softplus(dt_lin.to(f) + self.dt_bias.to(f))
-        bc = out["bc"].to(f)
-        Bh, Ch = bc[..., :s.N], bc[..., s.N:]
-        if self.b_norm is not None:
-            Bh = Bh * torch.rsqrt(Bh.square().mean(-1, keepdim=True) + s.norm_eps) * self.b_norm.weight.to(f)
-        if self.c_norm is not None:
-            Ch = Ch * torch.rsqrt(Ch.square().mean(-1, keepdim=True) + s.norm_eps) * self.c_norm.weight.to(f)
+        # B / C maps: RMSNorm over the N state rows in the token-tail kernel (IO dtype out, like the drive)
+        Braw, Craw = out["bc"][..., :s.N], out["bc"][..., s.N:]
+        Bh = (ops.TokenMapFn.apply(Braw, self.b_norm.weight, None, 0.0, s.norm_eps, 1, s.N, None).squeeze(2)
+              if self.b_norm is not None else Braw.to(f))
+        Ch = (ops.TokenMapFn.apply(Craw, self.c_norm.weight, None, 0.0, s.norm_eps, 1, s.N, None).squeeze(2)
+              if self.c_norm is not None else Craw.to(f))
         feat = th_h = None
         if s.has_rot:
             q = out["theta"].to(f)

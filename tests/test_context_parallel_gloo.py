@@ -24,9 +24,11 @@ def _worker(rank, world, port, out):
         from orbitssm_b200.config import SSDMimoConfig
         from orbitssm_b200.ssd_mimo import SSDMimoSSM
         from oracle import abi_reference as R
-        for name in ("conv1d_fwd", "conv1d_bwd", "gate_norm_fwd", "gate_norm_bwd", "pick_chunk", "run_phase"):
+        for name in ("conv1d_fwd", "conv1d_bwd", "gate_norm_fwd", "gate_norm_bwd", "pick_chunk", "run_phase", "token_map_fwd",
+                     "token_map_bwd", "run_clock"):
             setattr(ops, name, getattr(R, name))
         ops.on_device = lambda t: True
+        ops._require_cuda = lambda who, *t: None
         ops._dtype_code = lambda who, t: 0
         torch.set_num_threads(2)
         rec = load_golden("cfg2_small")
