@@ -101,6 +101,9 @@ int orbit_gate_norm_bwd_noalloc(const void* y, const void* z, int64_t z_row_stri
 typedef struct orbit_scan_args {
   int B, L, H, R, O, G, N;
   int T, nc;
+  int hsplit;         /* 0 / 1: one CTA walks all heads of a (batch, chunk).  k > 1 (dividing H; rank-1 tensor-core
+                         tiles only): k CTAs walk H/k heads each, and CHUNK_GRADS writes dBhat / dChat as k partial
+                         buffers [k, B, L, R|O, N] that the caller sums                                       */
   const void* u;      /* [B, L, H, G, R]  drive, IO dtype                                            */
   const void* Bhat;   /* [B, L, R, N]     IO dtype, token stride b_ts elements                       */
   const void* gBp;    /* [B, L, R, N]     1 + gB, IO dtype, token stride gb_ts, or NULL              */

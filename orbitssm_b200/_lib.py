@@ -26,7 +26,7 @@ class OrbitLibraryError(RuntimeError):
 class ScanArgs(C.Structure):
     """Mirror of ``orbit_scan_args`` (include/orbit_b200.h); field order and types must match the header."""
     _fields_ = (
-        [(n, C.c_int) for n in ("B", "L", "H", "R", "O", "G", "N", "T", "nc")]
+        [(n, C.c_int) for n in ("B", "L", "H", "R", "O", "G", "N", "T", "nc", "hsplit")]
         + [(n, C.c_void_p) for n in ("u", "Bhat", "gBp", "Chat", "gCp")]
         + [(n, C.c_int64) for n in ("b_ts", "gb_ts", "c_ts", "gc_ts")]
         + [(n, C.c_void_p) for n in ("beta", "gamma", "chi", "dA", "w", "wd", "Dg", "Sin", "atot", "dS", "y", "dy", "du",

@@ -173,8 +173,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
   const int c = blockIdx.x, b = blockIdx.y, t0 = c * TC_T;
   const int Tv = min(TC_T, a.L - t0);
   const int H = a.H;
+  // heads [h0, h0 + Hl) of this (batch, chunk): blockIdx.z splits the head loop (gradients of head-shared maps then go
+  // to per-split partial buffers); `h` below counts from h0
+  const int nsplit = gridDim.z, Hl = H / nsplit, h0 = blockIdx.z * Hl;
   const int t = q * 32 + lane;           // this thread's token row in TMEM
-  const int64_t srow0 = ((int64_t)b * a.nc + c) * H;   // index of this chunk's first [128 x 64] state tile
+  const int64_t srow0 = ((int64_t)b * a.nc + c) * H + h0;   // index of this chunk's first [128 x 64] state tile
 
   if (tid == 0) {
     mbar_init(&bar_map, 1);
@@ -199,9 +202,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
     tma_load_3d(sB + BLK, &tmB, &bar_map, 64, t0, b);
     tma_load_3d(sC, &tmC, &bar_map, 0, t0, b);
     tma_load_3d(sC + BLK, &tmC, &bar_map, 64, t0, b);
-    for (int i = 0; i < 2 && i < H; ++i) {
+    for (int i = 0; i < 2 && i < Hl; ++i) {
       mbar_expect_tx(&bar_x[i], 2 * BLK);
-      tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], i * TC_G, t0, b);
+      tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], (h0 + i) * TC_G, t0, b);
       tma_load_2d(sS + i * BLK, &tmS, &bar_x[i], 0, (int)(srow0 + i) * TC_N);
     }
     if (wait_or_abort(&bar_map, 0, abort_flag)) {
@@ -220,16 +223,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
   __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(a.y);
 
   float d_n = 0.f, wt_n = 0.f, wdt_n = 0.f;
-  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H;
+  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H + h0;
   if (tid < Tv) {
     d_n = a.dA[ck];
     wt_n = a.w[ck];
     wdt_n = a.wd[ck];
   }
-  for (int h = 0; h < H; ++h) {
+  for (int h = 0; h < Hl; ++h) {
     const int buf = h & 1;
     const float d = d_n, wt = wt_n, wdt = wdt_n;
-    if (tid < Tv && h + 1 < H) {
+    if (tid < Tv && h + 1 < Hl) {
       d_n = a.dA[ck + h + 1];
       wt_n = a.w[ck + h + 1];
       wdt_n = a.wd[ck + h + 1];
@@ -304,8 +307,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
           unpack_bf16(up[k], u0, u1);
           float d0 = 0.f, d1 = 0.f;
           if (a.Dg) {
-            d0 = a.Dg[h * TC_G + wg * 32 + i];
-            d1 = a.Dg[h * TC_G + wg * 32 + i + 1];
+            d0 = a.Dg[(h0 + h) * TC_G + wg * 32 + i];
+            d1 = a.Dg[(h0 + h) * TC_G + wg * 32 + i + 1];
           }
           float y0 = __uint_as_float(r1[i]) + at * __uint_as_float(r2[i]) + d0 * u0;
           float y1 = __uint_as_float(r1[i + 1]) + at * __uint_as_float(r2[i + 1]) + d1 * u1;
@@ -313,16 +316,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
         }
       }
       if (t < Tv) {
-        uint4* dst = reinterpret_cast<uint4*>(yout + ((int64_t)b * a.L + t0 + t) * (int64_t)(H * TC_G) + h * TC_G + wg * 32);
+        uint4* dst = reinterpret_cast<uint4*>(yout + ((int64_t)b * a.L + t0 + t) * (int64_t)(H * TC_G) + (h0 + h) * TC_G + wg * 32);
 #pragma unroll
         for (int k = 0; k < 4; ++k) dst[k] = make_uint4(outp[4 * k], outp[4 * k + 1], outp[4 * k + 2], outp[4 * k + 3]);
       }
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (tid == 0 && !*abort_flag && h + 2 < H) {
+    if (tid == 0 && !*abort_flag && h + 2 < Hl) {
       mbar_expect_tx(&bar_x[buf], 2 * BLK);
-      tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h + 2) * TC_G, t0, b);
+      tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
       tma_load_2d(sS + buf * BLK, &tmS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
     }
   }
@@ -385,8 +388,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
   const int c = blockIdx.x, b = blockIdx.y, t0 = c * TC_T;
   const int Tv = min(TC_T, a.L - t0);
   const int H = a.H;
+  // heads [h0, h0 + Hl) of this (batch, chunk): blockIdx.z splits the head loop (gradients of head-shared maps then go
+  // to per-split partial buffers); `h` below counts from h0
+  const int nsplit = gridDim.z, Hl = H / nsplit, h0 = blockIdx.z * Hl;
   const int t = q * 32 + lane;
-  const int64_t srow0 = ((int64_t)b * a.nc + c) * H;
+  const int64_t srow0 = ((int64_t)b * a.nc + c) * H + h0;
 
   if (tid == 0) {
     mbar_init(&bar_map, 1);
@@ -408,10 +414,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
     mbar_expect_tx(&bar_map, 2 * BLK);
     tma_load_3d(sC, &tmC, &bar_map, 0, t0, b);
     tma_load_3d(sC + BLK, &tmC, &bar_map, 64, t0, b);
-    for (int i = 0; i < 2 && i < H; ++i) {
+    for (int i = 0; i < 2 && i < Hl; ++i) {
       mbar_expect_tx(&bar_x[i], 4 * BLK);
-      tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], i * TC_G, t0, b);
-      tma_load_3d(sDY + i * BLK, &tmDY, &bar_x[i], i * TC_G, t0, b);
+      tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], (h0 + i) * TC_G, t0, b);
+      tma_load_3d(sDY + i * BLK, &tmDY, &bar_x[i], (h0 + i) * TC_G, t0, b);
       tma_load_2d(sS + i * BLK, &tmS, &bar_x[i], 0, (int)(srow0 + i) * TC_N);
       tma_load_2d(sdS + i * BLK, &tmDS, &bar_x[i], 0, (int)(srow0 + i) * TC_N);
     }
@@ -419,15 +425,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
   const uint32_t id_y = idesc_bf16(128, 64, 0, 1), id_acc = idesc_bf16(128, 128, 0, 0);
 
   float d_n = 0.f, wt_n = 0.f;
-  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H;
+  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H + h0;
   if (tid < Tv) {
     d_n = a.dA[ck];
     wt_n = a.w[ck];
   }
-  for (int h = 0; h < H; ++h) {
+  for (int h = 0; h < Hl; ++h) {
     const int buf = h & 1;
     const float d = d_n, wt = wt_n;
-    if (tid < Tv && h + 1 < H) {
+    if (tid < Tv && h + 1 < Hl) {
       d_n = a.dA[ck + h + 1];
       wt_n = a.w[ck + h + 1];
     }
@@ -478,7 +484,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
     }
     fence_proxy_async();
     const float datot = cta_sum(part, red);       // ends after a CTA barrier: the scaled tiles are complete
-    if (tid == 0) a.dw[((int64_t)b * a.L + t0) * H + h] = datot;
+    if (tid == 0) a.dw[((int64_t)b * a.L + t0) * H + h0 + h] = datot;
     if (tid == 0 && !*abort_flag) {
       bool ok = (h > 0) || wait_or_abort(&bar_map, 0, abort_flag);
       if (ok) {
@@ -516,11 +522,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
     dapart[wg * 128 + t] = dsum;
     tc_fence_before_sync();
     __syncthreads();
-    if (tid < Tv) a.ddA[((int64_t)b * a.L + t0 + tid) * H + h] = dapart[tid] + dapart[128 + tid];
-    if (tid == 0 && !*abort_flag && h + 2 < H) {
+    if (tid < Tv) a.ddA[((int64_t)b * a.L + t0 + tid) * H + h0 + h] = dapart[tid] + dapart[128 + tid];
+    if (tid == 0 && !*abort_flag && h + 2 < Hl) {
       mbar_expect_tx(&bar_x[buf], 4 * BLK);
-      tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h + 2) * TC_G, t0, b);
-      tma_load_3d(sDY + buf * BLK, &tmDY, &bar_x[buf], (h + 2) * TC_G, t0, b);
+      tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
+      tma_load_3d(sDY + buf * BLK, &tmDY, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
       tma_load_2d(sS + buf * BLK, &tmS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
       tma_load_2d(sdS + buf * BLK, &tmDS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
     }
@@ -536,8 +542,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
       tmem_ld32(tmem_addr(tbase, q * 32, TM_DBX + col), r2);
       tmem_ld_wait();
       if (t < Tv) {
-        float* dc = a.dChat + ((int64_t)b * a.L + t0 + t) * TC_N + col;
-        float* db = a.dBhat + ((int64_t)b * a.L + t0 + t) * TC_N + col;
+        float* dc = a.dChat + (((int64_t)blockIdx.z * a.B + b) * a.L + t0 + t) * TC_N + col;
+        float* db = a.dBhat + (((int64_t)blockIdx.z * a.B + b) * a.L + t0 + t) * TC_N + col;
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
           *reinterpret_cast<float4*>(dc + j) = make_float4(__uint_as_float(r1[j]), __uint_as_float(r1[j + 1]), __uint_as_float(r1[j + 2]), __uint_as_float(r1[j + 3]));
@@ -592,8 +598,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
   const int c = blockIdx.x, b = blockIdx.y, t0 = c * TC_T;
   const int Tv = min(TC_T, a.L - t0);
   const int H = a.H;
+  // heads [h0, h0 + Hl) of this (batch, chunk): blockIdx.z splits the head loop (gradients of head-shared maps then go
+  // to per-split partial buffers); `h` below counts from h0
+  const int nsplit = gridDim.z, Hl = H / nsplit, h0 = blockIdx.z * Hl;
   const int t = q * 32 + lane;
-  const int64_t srow0 = ((int64_t)b * a.nc + c) * H;
+  const int64_t srow0 = ((int64_t)b * a.nc + c) * H + h0;
 
   if (tid == 0) {
     mbar_init(&bar_map, 1);
@@ -619,10 +628,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
     tma_load_3d(sB + BLK, &tmB, &bar_map, 64, t0, b);
     tma_load_3d(sC, &tmC, &bar_map, 0, t0, b);
     tma_load_3d(sC + BLK, &tmC, &bar_map, 64, t0, b);
-    for (int i = 0; i < 2 && i < H; ++i) {
+    for (int i = 0; i < 2 && i < Hl; ++i) {
       mbar_expect_tx(&bar_x[i], 3 * BLK);
-      tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], i * TC_G, t0, b);
-      tma_load_3d(sDY + i * BLK, &tmDY, &bar_x[i], i * TC_G, t0, b);
+      tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], (h0 + i) * TC_G, t0, b);
+      tma_load_3d(sDY + i * BLK, &tmDY, &bar_x[i], (h0 + i) * TC_G, t0, b);
       tma_load_2d(sdS + i * BLK, &tmDS, &bar_x[i], 0, (int)(srow0 + i) * TC_N);
     }
     if (wait_or_abort(&bar_map, 0, abort_flag)) {
@@ -648,26 +657,26 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
 
   // clocks (and what part 1 left in ddA / dw) of the next head are fetched one head ahead
   float d_n = 0.f, wt_n = 0.f, wdt_n = 0.f, da_n = 0.f, datot_n;
-  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H;
+  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H + h0;
   if (tid < Tv) {
     d_n = a.dA[ck];
     wt_n = a.w[ck];
     wdt_n = a.wd[ck];
     da_n = a.ddA[ck];
   }
-  datot_n = a.dw[((int64_t)b * a.L + t0) * H];
-  for (int h = 0; h < H; ++h) {
+  datot_n = a.dw[((int64_t)b * a.L + t0) * H + h0];
+  for (int h = 0; h < Hl; ++h) {
     const int buf = h & 1;
     const float d = d_n, wt = wt_n, wdt = wdt_n, da_t = da_n, datot = datot_n;
     const int64_t gi = ck + h;
-    if (h + 1 < H) {
+    if (h + 1 < Hl) {
       if (tid < Tv) {
         d_n = a.dA[ck + h + 1];
         wt_n = a.w[ck + h + 1];
         wdt_n = a.wd[ck + h + 1];
         da_n = a.ddA[ck + h + 1];                        // part 1 left da here
       }
-      datot_n = a.dw[((int64_t)b * a.L + t0) * H + h + 1];   // part 1 left datot here
+      datot_n = a.dw[((int64_t)b * a.L + t0) * H + h0 + h + 1];   // part 1 left datot here
     }
     if (tid < 128) {
       wv[tid] = wt;
@@ -776,8 +785,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
           const float x20 = __uint_as_float(r2[i]), x21 = __uint_as_float(r2[i + 1]);
           float d0 = 0.f, d1 = 0.f;
           if (a.Dg) {
-            d0 = a.Dg[h * TC_G + wg * 32 + i];
-            d1 = a.Dg[h * TC_G + wg * 32 + i + 1];
+            d0 = a.Dg[(h0 + h) * TC_G + wg * 32 + i];
+            d1 = a.Dg[(h0 + h) * TC_G + wg * 32 + i + 1];
           }
           outp[k4 * 4 + k] = pack_bf16(__uint_as_float(r1[i]) + es * x20 + d0 * g0, __uint_as_float(r1[i + 1]) + es * x21 + d1 * g1);
           de_half = fmaf(u0, x20, fmaf(u1, x21, de_half));
@@ -786,7 +795,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
         }
       }
       if (t < Tv) {
-        uint4* dst = reinterpret_cast<uint4*>(duout + ((int64_t)b * a.L + t0 + t) * (int64_t)(H * TC_G) + h * TC_G + wg * 32);
+        uint4* dst = reinterpret_cast<uint4*>(duout + ((int64_t)b * a.L + t0 + t) * (int64_t)(H * TC_G) + (h0 + h) * TC_G + wg * 32);
 #pragma unroll
         for (int k = 0; k < 4; ++k) dst[k] = make_uint4(outp[4 * k], outp[4 * k + 1], outp[4 * k + 2], outp[4 * k + 3]);
       }
@@ -798,10 +807,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (tid == 0 && !*abort_flag && h + 2 < H) {
+    if (tid == 0 && !*abort_flag && h + 2 < Hl) {
       mbar_expect_tx(&bar_x[buf], 3 * BLK);
-      tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h + 2) * TC_G, t0, b);
-      tma_load_3d(sDY + buf * BLK, &tmDY, &bar_x[buf], (h + 2) * TC_G, t0, b);
+      tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
+      tma_load_3d(sDY + buf * BLK, &tmDY, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
       tma_load_2d(sdS + buf * BLK, &tmDS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
     }
     // ---- per-token clock gradients (threads 0..127 own token tid; every thread joins the reductions) ----
@@ -825,7 +834,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
     if (tid < 128) {
       const int tt = 127 - tid;          // prefix index tid holds the reverse-inclusive sum for token tt
       if (tt < Tv) {
-        const int64_t go = ((int64_t)b * a.L + t0 + tt) * H + h;
+        const int64_t go = ((int64_t)b * a.L + t0 + tt) * H + h0 + h;
         a.ddA[go] = gcs[tid];
       }
       if (tid < Tv) {
@@ -834,7 +843,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
       }
     }
     if (a.dDg_part && tid < 64)
-      a.dDg_part[(((int64_t)b * a.nc + c) * H + h) * TC_G + tid] = ddpart[tid] + ddpart[64 + tid] + ddpart[128 + tid] + ddpart[192 + tid];
+      a.dDg_part[(((int64_t)b * a.nc + c) * H + h0 + h) * TC_G + tid] = ddpart[tid] + ddpart[64 + tid] + ddpart[128 + tid] + ddpart[192 + tid];
     __syncthreads();
   }
 
@@ -874,8 +883,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
       tmem_ld32(tmem_addr(tbase, q * 32, 0 + col), r2);     // dB intra
       tmem_ld_wait();
       if (t < Tv) {
-        float4* dc = reinterpret_cast<float4*>(a.dChat + ((int64_t)b * a.L + t0 + t) * TC_N + col);
-        float4* db = reinterpret_cast<float4*>(a.dBhat + ((int64_t)b * a.L + t0 + t) * TC_N + col);
+        float4* dc = reinterpret_cast<float4*>(a.dChat + (((int64_t)blockIdx.z * a.B + b) * a.L + t0 + t) * TC_N + col);
+        float4* db = reinterpret_cast<float4*>(a.dBhat + (((int64_t)blockIdx.z * a.B + b) * a.L + t0 + t) * TC_N + col);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           float4 x = dc[j], y = db[j];
@@ -910,6 +919,7 @@ int tc_supported(const ScanArgs& a, int dtype, const char** why) {
   else if (a.R != 1 || a.O != 1 || a.N != TC_N || a.G != TC_G) *why = "tensor-core tiles serve R = O = 1, N = 128, G = 64";
   else if (a.gBp || a.gCp || a.beta || a.gamma || a.chi) *why = "tensor-core tiles serve head-shared maps (no gates, per-head biases or sibling mix)";
   else if (a.T != TC_T) *why = "tensor-core tiles use chunk length 128";
+  else if (a.hsplit > 1 && a.H % a.hsplit) *why = "hsplit must divide the number of heads";
   else if (a.b_ts % 8 || a.c_ts % 8 || !aligned16(a.Bhat) || !aligned16(a.Chat) || !aligned16(a.u)) *why = "maps and drive must be 16-byte aligned with token strides that are multiples of 8 elements";
   return *why == nullptr;
 }
@@ -918,6 +928,9 @@ int tc_pick_chunk(int R, int O, int G, int N, int backward, int limit) {
   if (mimo_tc_geometry(R, O, G, N)) return limit >= 32 ? 32 : 0;
   return (R == 1 && O == 1 && G == TC_G && N == TC_N && limit >= TC_T) ? TC_T : 0;
 }
+
+// number of head ranges a (batch, chunk) is split into (a.hsplit, 0 = 1); must divide H
+static int head_split(const ScanArgs& a) { return a.hsplit > 1 ? a.hsplit : 1; }
 
 static int map_rows(CUtensorMap* m, const void* base, int cols, int64_t token_stride, int L, int B) {
   uint64_t dims[3] = {(uint64_t)cols, (uint64_t)L, (uint64_t)B};
@@ -974,7 +987,7 @@ int tc_launch_chunk_out(const ScanArgs& a, cudaStream_t st) {
   if ((rc = map_rows(&tmU, a.u, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
   if ((rc = map_state(&tmS, a.Sin16, a)) != OK) return rc;
   ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_OUT));
-  tc_chunk_out_kernel<<<dim3(a.nc, a.B), TC_THREADS, SMEM_OUT, st>>>(tmB, tmC, tmU, tmS, a);
+  tc_chunk_out_kernel<<<dim3(a.nc, a.B, head_split(a)), TC_THREADS, SMEM_OUT, st>>>(tmB, tmC, tmU, tmS, a);
   ORBIT_CHECK_LAUNCH("tc_chunk_out_kernel");
   return OK;
 }
@@ -996,9 +1009,9 @@ int tc_launch_chunk_grads(const ScanArgs& a, cudaStream_t st) {
   if ((rc = map_rows(&tmDY, a.dy, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
   ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_grads_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GSTATE));
   ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_grads_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GSCORE));
-  tc_chunk_grads_state_kernel<<<dim3(a.nc, a.B), TC_THREADS, SMEM_GSTATE, st>>>(tmC, tmU, tmDY, tmS, tmDS, a);
+  tc_chunk_grads_state_kernel<<<dim3(a.nc, a.B, head_split(a)), TC_THREADS, SMEM_GSTATE, st>>>(tmC, tmU, tmDY, tmS, tmDS, a);
   ORBIT_CHECK_LAUNCH("tc_chunk_grads_state_kernel");
-  tc_chunk_grads_score_kernel<<<dim3(a.nc, a.B), TC_THREADS, SMEM_GSCORE, st>>>(tmB, tmC, tmU, tmDY, tmDS, a);
+  tc_chunk_grads_score_kernel<<<dim3(a.nc, a.B, head_split(a)), TC_THREADS, SMEM_GSCORE, st>>>(tmB, tmC, tmU, tmDY, tmDS, a);
   ORBIT_CHECK_LAUNCH("tc_chunk_grads_score_kernel");
   return OK;
 }

@@ -1098,6 +1098,7 @@ int mimo_tc_supported(const ScanArgs& a, int dtype, const char** why) {
   *why = nullptr;
   if (dtype != BF16) *why = "activations must be bfloat16";
   else if (a.T != MM_T) *why = "rank-4 tensor-core tiles use chunk length 32";
+  else if (a.hsplit > 1) *why = "rank-4 tensor-core tiles walk all heads in one CTA (hsplit must be 0 or 1)";
   else if (a.b_ts % 8 || a.c_ts % 8 || !aligned16(a.Bhat) || !aligned16(a.Chat) || !aligned16(a.u) ||
            (a.gBp && (a.gb_ts % 8 || !aligned16(a.gBp))) || (a.gCp && (a.gc_ts % 8 || !aligned16(a.gCp))) ||
            (a.dy && !aligned16(a.dy)) || (a.y && !aligned16(a.y)) || (a.beta && !aligned16(a.beta)) ||

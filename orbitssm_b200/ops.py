@@ -335,6 +335,24 @@ class ScanGeometry:
     N: int
 
 
+def head_split(B, nc, H, R, precision, device) -> int:
+    """How many head ranges a (batch, chunk) of the rank-1 tensor-core scan is split into: the smallest k in {1, 2, 4, 8}
+    dividing H whose grid B * nc * k fills whole waves of one CTA per SM best (one CTA per (batch, chunk) leaves the
+    last wave partly empty: 256 CTAs on 148 SMs run as long as 296)."""
+    if precision != _lib.PRECISION_IO or R != 1 or device.type != "cuda":
+        return 1
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    best, best_eff = 1, 0.0
+    for k in (1, 2, 4, 8):
+        if H % k:
+            continue
+        units = B * nc * k
+        eff = units / (-(-units // sms) * sms)
+        if eff > best_eff + 0.02:
+            best, best_eff = k, eff
+    return best
+
+
 def pick_chunk(geo: ScanGeometry, precision: int, backward: bool, limit: int) -> int:
     return int(_lib.load().orbit_ssd_scan_pick_chunk(geo.R, geo.O, geo.G, geo.N, precision, int(backward), int(limit)))
 
@@ -465,6 +483,7 @@ def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     if precision == _lib.PRECISION_IO and geo.R == 1:    # bf16 state tiles are read by the rank-1 tensor-core kernels only
         Sin16 = torch.empty((B, nc, H, R, N, G), device=dev, dtype=torch.bfloat16)
         a.Sin16 = Sin16.data_ptr()
+    a.hsplit = head_split(B, nc, H, R, precision, dev)
     a.t = dict(geo=geo, u=u, Bhat=Bhat, gBp=gBp, Chat=Chat, gCp=gCp, beta=beta, gamma=gamma, chi=chi, dA=dA, w=w, wd=wd,
                Dg=Dg, Sin=Sin, atot=atot, y=y)
     dt = _dtype_code("ssd_scan_fwd", u)
@@ -521,7 +540,7 @@ def _fill_common(a, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg):
 
 
 def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, Sin, atot, dy, dS_fin,
-             euler, want_dS0, cp=None):
+             euler, want_dS0, cp=None, hsplit=1):
     """Backward scan.  Returns a dict of gradients (fp32 unless noted): du (IO dtype), dBhat, dgBp, dChat, dgCp, dbeta,
     dgamma, dchi, ddA, dw, dwd, dDg, dS0."""
     B, L = u.shape[:2]
@@ -556,6 +575,13 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
         a.du32 = du32.data_ptr()
     a.Sin, a.atot, a.dS, a.dy, a.du = Sin.data_ptr(), atot.data_ptr(), dS.data_ptr(), dy.data_ptr(), out["du"].data_ptr()
     a.dBhat, a.dChat, a.ddA, a.dw = (out[k].data_ptr() for k in ("dBhat", "dChat", "ddA", "dw"))
+    # The gradient kernels keep one CTA per (batch, chunk) by default: their per-CTA epilogue (128 KB of map gradients
+    # written, then read and written again) outweighs the wave-quantisation gain of a head split (measured at configs 2, 5).
+    a.hsplit = int(hsplit) if (precision == _lib.PRECISION_IO and R == 1 and H % max(int(hsplit), 1) == 0) else 1
+    parts = None
+    if a.hsplit > 1:          # every head range writes its own partial of the head-shared map gradients
+        parts = (torch.empty((a.hsplit, B, L, R, N), **f32), torch.empty((a.hsplit, B, L, O, N), **f32))
+        a.dBhat, a.dChat = parts[0].data_ptr(), parts[1].data_ptr()
     for k in ("dgBp", "dgCp", "dwd", "dchi"):
         if out[k] is not None:
             setattr(a, k, out[k].data_ptr())
@@ -583,6 +609,8 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     run_phase(a, "scan_state_pass_bwd", _lib.PHASE_STATE_PASS_BWD, dS_fin, dS0, dt, precision)
     run_phase(a, "scan_chunk_grads", _lib.PHASE_CHUNK_GRADS, None, None, dt, precision)
     del keep
+    if parts is not None:
+        out["dBhat"], out["dChat"] = parts[0].sum(0), parts[1].sum(0)
     if euler:
         out["dw"] = out["dw"] + dwd_tmp
     out["dbeta"] = pb.sum(0) if pb is not None else None

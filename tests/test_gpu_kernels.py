@@ -246,6 +246,13 @@ def test_scan_tc_backward(case):
     for k, v in g.items():
         if v is not None:
             assert torch.equal(v, g2[k]), ("not reproducible", k)
+    if H % 2 == 0:
+        # head ranges on separate CTAs (partial buffers of the head-shared map gradients summed by the host)
+        g3 = ops.scan_bwd(geo, 128, _lib.PRECISION_IO, *args, Sin, atot, c["dy"], c["dS_fin"], c["euler"], c["S0"] is not None,
+                          hsplit=2)
+        for k, v in g.items():
+            if v is not None:
+                assert rel(g3[k], v) < 1e-5, ("head split", k, rel(g3[k], v))
 
 
 # ---------------------------------------------------------------------------------------------------- scan, tcgen05 rank 4
