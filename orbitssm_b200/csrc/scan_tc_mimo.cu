@@ -134,6 +134,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) mimo_chunk_state_kernel(const S
   const int c = blockIdx.x, b = blockIdx.y, t0 = c * MM_T;
   const int Tv = min(MM_T, a.L - t0);
   const int H = a.H;
+  // heads [h0, h0 + Hl) of this (batch, chunk): blockIdx.z splits the head loop (a.hsplit)
+  const int Hl = H / (int)gridDim.z, h0 = (int)blockIdx.z * Hl;
   const int row = qw * 32 + lane;
   const int64_t tok0 = (int64_t)b * a.L + t0;
 
@@ -160,12 +162,12 @@ __global__ void __launch_bounds__(TC_THREADS, 2) mimo_chunk_state_kernel(const S
 
   // epilogue of kernel head `itp` (warps 0..3: one state row n per thread): bias correction (bv: its 4 bias values) and store
   auto load_bias = [&](int itp, float (&bv)[4]) {
-    const int hh = itp % H, rr = itp / H;
+    const int hh = h0 + itp % Hl, rr = itp / Hl;
 #pragma unroll
     for (int x = 0; x < 4; ++x) bv[x] = (bias != nullptr && wg == 0) ? bias[(((int64_t)hh * MM_R + rr) * 4 + x) * MM_N + row] : 0.f;
   };
   auto epilogue = [&](int itp, const float (&bv)[4]) {
-    const int hb = itp & 1, hh = itp % H, rr = itp / H;
+    const int hb = itp & 1, hh = h0 + itp % Hl, rr = itp / Hl;
     const bool ok = wait_warp(&bar_mma[hb], n_issued[hb] & 1u, abort_flag);
     n_issued[hb]++;
     if (ok && wg == 0) {
@@ -197,8 +199,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) mimo_chunk_state_kernel(const S
     }
   };
   float d_n, wt_n, ch_n;
-  load_clock(0, 0, d_n, wt_n, ch_n);
-  uint4 raw_n = load_xt_row(xsrc, (int64_t)H * 64, tok0, 0, Tv);
+  load_clock(h0, 0, d_n, wt_n, ch_n);
+  uint4 raw_n = load_xt_row(xsrc, (int64_t)H * 64, tok0, h0, Tv);
   for (int r = 0; r < MM_R; ++r) {
     if (mode == 0 || r == 0) {
       uint32_t v[32];
@@ -206,18 +208,18 @@ __global__ void __launch_bounds__(TC_THREADS, 2) mimo_chunk_state_kernel(const S
       gated_row(hat, hat_ts, gate, gate_ts, tok0 + lane, qw, mode == 0 ? r : qw, wg * 64, lane < Tv, v);
       store_row(sMap, row, wg, v, nullptr);
     }
-    for (int h = 0; h < H; ++h) {
-      const int it = r * H + h, buf = it & 1;
+    for (int hl = 0; hl < Hl; ++hl) {
+      const int h = h0 + hl, it = r * Hl + hl, buf = it & 1;
       // clocks of kernel head (h, r): every warp forms the 32-token prefix on its own
       const float d = d_n, wt = wt_n, ch = ch_n;
       const uint4 raw = raw_n;
       float bv[4];
-      if (h > 0) load_bias(it - 1, bv);
+      if (hl > 0) load_bias(it - 1, bv);
       {
         const int itn = it + 1;
-        if (itn < MM_R * H) {
-          load_clock(itn % H, itn / H, d_n, wt_n, ch_n);
-          raw_n = load_xt_row(xsrc, (int64_t)H * 64, tok0, itn % H, Tv);
+        if (itn < MM_R * Hl) {
+          load_clock(h0 + itn % Hl, itn / Hl, d_n, wt_n, ch_n);
+          raw_n = load_xt_row(xsrc, (int64_t)H * 64, tok0, h0 + itn % Hl, Tv);
         }
       }
       const float cs = warp_prefix32(d, lane);
@@ -245,14 +247,14 @@ __global__ void __launch_bounds__(TC_THREADS, 2) mimo_chunk_state_kernel(const S
         for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + buf * 16, desc_mn(am, ks), desc_k16(bx, ks), idesc, ks > 0 ? 1u : 0u);
         umma_commit(&bar_mma[buf]);
       }
-      if (h > 0) epilogue(it - 1, bv);
+      if (hl > 0) epilogue(it - 1, bv);
       __syncthreads();
     }
     // drain the last head of this sibling (its tiles read sMap, which the next sibling rewrites)
     {
       float bv[4];
-      load_bias(r * H + H - 1, bv);
-      epilogue(r * H + H - 1, bv);
+      load_bias(r * Hl + Hl - 1, bv);
+      epilogue(r * Hl + Hl - 1, bv);
     }
     __syncthreads();
   }
@@ -303,6 +305,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_out_kernel(const Sca
   const int c = blockIdx.x, b = blockIdx.y, t0 = c * MM_T;
   const int Tv = min(MM_T, a.L - t0);
   const int H = a.H;
+  // heads [h0, h0 + Hl) of this (batch, chunk): blockIdx.z splits the head loop (a.hsplit)
+  const int Hl = H / (int)gridDim.z, h0 = (int)blockIdx.z * Hl;
   const int row = qw * 32 + lane;
   const int64_t tok0 = (int64_t)b * a.L + t0;
   constexpr uint32_t TS = 0, TY1 = 128, TYC = 144;   // TMEM columns: score, y accumulator, 4 x entering-state products
@@ -343,8 +347,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_out_kernel(const Sca
   float* rawB = reinterpret_cast<float*>(sm + MimoOutSmem::RAWB);
   float* rawC = reinterpret_cast<float*>(sm + MimoOutSmem::RAWC);
   auto stage = [&](int itn) {
-    if (itn < H * MM_R) {
-      const int hh = itn >> 2, rr = itn & 3, pb = itn & 1;
+    if (itn < Hl * MM_R) {
+      const int hh = h0 + (itn >> 2), rr = itn & 3, pb = itn & 1;
       const float* src = a.Sin + ((((int64_t)b * a.nc + c) * H + hh) * MM_R + rr) * (int64_t)(MM_N * MM_G);
       cp_async16(rawS + pb * 2048 + tid * 4, src + tid * 4);
       cp_async16(rawS + pb * 2048 + 1024 + tid * 4, src + 1024 + tid * 4);
@@ -363,10 +367,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_out_kernel(const Sca
   cp_async_wait_all();
   __syncthreads();
 
-  for (int h = 0; h < H && alive; ++h) {
+  for (int hl = 0; hl < Hl && alive; ++hl) {
+    const int h = h0 + hl;
     build_xt(sUT, reinterpret_cast<const __nv_bfloat16*>(a.u), (int64_t)H * 64, tok0, h, Tv, nullptr);
     for (int r = 0; r < MM_R; ++r) {
-      const int it = h * MM_R + r, pb = it & 1;
+      const int it = hl * MM_R + r, pb = it & 1;
       // ---- clocks of kernel head (h, r)
       const float d = rawC[pb * 128 + lane], wt = rawC[pb * 128 + 32 + lane], wdt = rawC[pb * 128 + 64 + lane];
       const float ch = (a.chi != nullptr && lane < Tv) ? rawC[pb * 128 + 96 + lane] : 1.f;
@@ -613,9 +618,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
   const int c = blockIdx.x, b = blockIdx.y, t0 = c * MM_T;
   const int Tv = min(MM_T, a.L - t0);
   const int H = a.H;
+  // heads [h0, h0 + Hl) of this (batch, chunk): blockIdx.z splits the head loop (a.hsplit)
+  const int Hl = H / (int)gridDim.z, h0 = (int)blockIdx.z * Hl;
   const int row = qw * 32 + lane;
   const int64_t tok0 = (int64_t)b * a.L + t0;
   const int64_t slot = (int64_t)b * a.nc + c;
+  const int64_t zoff = (int64_t)blockIdx.z * a.B * a.L * (MM_R * MM_N);   // this head range's partial of the map gradients
   constexpr uint32_t TS = 0, TDC = 128, TX = 256, TDU = 384, TYC = 400, TDD = 416, TDG = 432, TDB = 448;
 
   if (tid == 0) {
@@ -649,8 +657,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
   uint4* slotU = reinterpret_cast<uint4*>(sDM + 21504);
   uint4* slotDY = reinterpret_cast<uint4*>(sDM + 25600);
   auto stage = [&](int itn) {
-    if (itn < H * MM_R) {
-      const int hh = itn % H, rr = itn / H;
+    if (itn < Hl * MM_R) {
+      const int hh = h0 + itn % Hl, rr = itn / Hl;
       const int64_t son = (((slot * H + hh) * MM_R + rr) * MM_N) * MM_G;
       cp_async16(rawS + tid * 4, a.Sin + son + tid * 4);
       cp_async16(rawS + 1024 + tid * 4, a.Sin + son + 1024 + tid * 4);
@@ -683,8 +691,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
   for (int r = 0; r < MM_R && alive; ++r) {
     gated_row(reinterpret_cast<const __nv_bfloat16*>(a.Bhat), a.b_ts, reinterpret_cast<const __nv_bfloat16*>(a.gBp), a.gb_ts,
               tok0 + lane, qw, r, wg * 64, lane < Tv, bg);
-    for (int h = 0; h < H; ++h) {
-      const int it = r * H + h;
+    for (int hl = 0; hl < Hl; ++hl) {
+      const int h = h0 + hl, it = r * Hl + hl;
       const uint32_t par = (uint32_t)it & 1u;
       // ================= stage A: clocks, tables, operand tiles (all from the staged copies)
       const float d = rawC[lane], wt = rawC[32 + lane], wdt = rawC[64 + lane];
@@ -867,7 +875,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
         for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TDC, desc_k(ads, ks), desc_mn(ab, ks), id_km, (it > 0 || ks > 0) ? 1u : 0u);
         umma_bf16(tbase + TDC, desc_xt_mn(smem_u32(sFDYT)), desc_xt_mn(smem_u32(sSinT)), id_mm, 1u);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TX, desc_mn(ads, ks), desc_mn(ac, ks), id_mm, (h > 0 || ks > 0) ? 1u : 0u);
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TX, desc_mn(ads, ks), desc_mn(ac, ks), id_mm, (hl > 0 || ks > 0) ? 1u : 0u);
         umma_bf16(tbase + TX, desc_xt_mn(smem_u32(sEUT)), desc_xt_mn(smem_u32(sDSoT)), id_mm, 1u);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TDU, desc_mn(ams, ks), desc_k16(smem_u32(sDYT), ks), id_m16, ks > 0 ? 1u : 0u);
@@ -1011,7 +1019,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
 #pragma unroll
               for (int k = 0; k < 8; ++k) { gv[k] = 1.f; hv[k] = 0.f; }
             }
-            float* dbh = a.dBhat + (tok * MM_R + qw) * MM_N + n0;
+            float* dbh = a.dBhat + zoff + (tok * MM_R + qw) * MM_N + n0;
             float o8[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) o8[k] = __uint_as_float(v[cc * 8 + k]) * gv[k];
@@ -1035,7 +1043,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
             float acc = 0.f;
 #pragma unroll
             for (int q = 0; q < 4; ++q) acc += qsum[((half * 4 + q) * 32 + s) * 64 + ((col + s) & 63)];
-            a.dgBp[((tok0 + s) * MM_R + r) * MM_N + n] = acc;
+            a.dgBp[zoff + ((tok0 + s) * MM_R + r) * MM_N + n] = acc;
           }
         }
       }
@@ -1069,13 +1077,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
 #pragma unroll
             for (int k = 0; k < 8; ++k) { gv[k] = 1.f; hv[k] = 0.f; }
           }
-          float* dch = a.dChat + (tok * 4 + qw) * MM_N + n0;
+          float* dch = a.dChat + zoff + (tok * 4 + qw) * MM_N + n0;
           *reinterpret_cast<float4*>(dch) = make_float4(__uint_as_float(v[cc * 8]) * gv[0], __uint_as_float(v[cc * 8 + 1]) * gv[1],
                                                         __uint_as_float(v[cc * 8 + 2]) * gv[2], __uint_as_float(v[cc * 8 + 3]) * gv[3]);
           *reinterpret_cast<float4*>(dch + 4) = make_float4(__uint_as_float(v[cc * 8 + 4]) * gv[4], __uint_as_float(v[cc * 8 + 5]) * gv[5],
                                                             __uint_as_float(v[cc * 8 + 6]) * gv[6], __uint_as_float(v[cc * 8 + 7]) * gv[7]);
           if (a.dgCp != nullptr) {
-            float* dg = a.dgCp + (tok * 4 + qw) * MM_N + n0;
+            float* dg = a.dgCp + zoff + (tok * 4 + qw) * MM_N + n0;
             *reinterpret_cast<float4*>(dg) = make_float4(__uint_as_float(v[cc * 8]) * hv[0], __uint_as_float(v[cc * 8 + 1]) * hv[1],
                                                          __uint_as_float(v[cc * 8 + 2]) * hv[2], __uint_as_float(v[cc * 8 + 3]) * hv[3]);
             *reinterpret_cast<float4*>(dg + 4) = make_float4(__uint_as_float(v[cc * 8 + 4]) * hv[4], __uint_as_float(v[cc * 8 + 5]) * hv[5],
@@ -1098,7 +1106,7 @@ int mimo_tc_supported(const ScanArgs& a, int dtype, const char** why) {
   *why = nullptr;
   if (dtype != BF16) *why = "activations must be bfloat16";
   else if (a.T != MM_T) *why = "rank-4 tensor-core tiles use chunk length 32";
-  else if (a.hsplit > 1) *why = "rank-4 tensor-core tiles walk all heads in one CTA (hsplit must be 0 or 1)";
+  else if (a.hsplit > 1 && a.H % a.hsplit) *why = "hsplit must divide the number of heads";
   else if (a.b_ts % 8 || a.c_ts % 8 || !aligned16(a.Bhat) || !aligned16(a.Chat) || !aligned16(a.u) ||
            (a.gBp && (a.gb_ts % 8 || !aligned16(a.gBp))) || (a.gCp && (a.gc_ts % 8 || !aligned16(a.gCp))) ||
            (a.dy && !aligned16(a.dy)) || (a.y && !aligned16(a.y)) || (a.beta && !aligned16(a.beta)) ||
@@ -1114,7 +1122,7 @@ int mimo_tc_launch_state(const ScanArgs& a, int mode, cudaStream_t stream) {
     ORBIT_CHECK_CUDA(cudaFuncSetAttribute(mimo_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr = true;
   }
-  mimo_chunk_state_kernel<<<dim3(a.nc, a.B), TC_THREADS, smem, stream>>>(a, mode);
+  mimo_chunk_state_kernel<<<dim3(a.nc, a.B, a.hsplit > 1 ? a.hsplit : 1), TC_THREADS, smem, stream>>>(a, mode);
   ORBIT_CHECK_LAUNCH("mimo_chunk_state_kernel");
   return OK;
 }
@@ -1130,7 +1138,7 @@ int mimo_tc_launch_grads(const ScanArgs& a, cudaStream_t stream) {
     ORBIT_CHECK_CUDA(cudaFuncSetAttribute(mimo_chunk_grads_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr = true;
   }
-  mimo_chunk_grads_kernel<<<dim3(a.nc, a.B), TC_THREADS, smem, stream>>>(a);
+  mimo_chunk_grads_kernel<<<dim3(a.nc, a.B, a.hsplit > 1 ? a.hsplit : 1), TC_THREADS, smem, stream>>>(a);
   ORBIT_CHECK_LAUNCH("mimo_chunk_grads_kernel");
   return OK;
 }
@@ -1142,7 +1150,7 @@ int mimo_tc_launch_out(const ScanArgs& a, cudaStream_t stream) {
     ORBIT_CHECK_CUDA(cudaFuncSetAttribute(mimo_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr = true;
   }
-  mimo_chunk_out_kernel<<<dim3(a.nc, a.B), TC_THREADS, smem, stream>>>(a);
+  mimo_chunk_out_kernel<<<dim3(a.nc, a.B, a.hsplit > 1 ? a.hsplit : 1), TC_THREADS, smem, stream>>>(a);
   ORBIT_CHECK_LAUNCH("mimo_chunk_out_kernel");
   return OK;
 }

@@ -336,10 +336,10 @@ class ScanGeometry:
 
 
 def head_split(B, nc, H, R, precision, device) -> int:
-    """How many head ranges a (batch, chunk) of the rank-1 tensor-core scan is split into: the smallest k in {1, 2, 4, 8}
+    """How many head ranges a (batch, chunk) of the tensor-core scan is split into: the smallest k in {1, 2, 4, 8}
     dividing H whose grid B * nc * k fills whole waves of one CTA per SM best (one CTA per (batch, chunk) leaves the
     last wave partly empty: 256 CTAs on 148 SMs run as long as 296)."""
-    if precision != _lib.PRECISION_IO or R != 1 or device.type != "cuda":
+    if precision != _lib.PRECISION_IO or device.type != "cuda":
         return 1
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     best, best_eff = 1, 0.0
@@ -575,15 +575,28 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
         a.du32 = du32.data_ptr()
     a.Sin, a.atot, a.dS, a.dy, a.du = Sin.data_ptr(), atot.data_ptr(), dS.data_ptr(), dy.data_ptr(), out["du"].data_ptr()
     a.dBhat, a.dChat, a.ddA, a.dw = (out[k].data_ptr() for k in ("dBhat", "dChat", "ddA", "dw"))
-    # The gradient kernels keep one CTA per (batch, chunk) by default: their per-CTA epilogue (128 KB of map gradients
-    # written, then read and written again) outweighs the wave-quantisation gain of a head split (measured at configs 2, 5).
-    a.hsplit = int(hsplit) if (precision == _lib.PRECISION_IO and R == 1 and H % max(int(hsplit), 1) == 0) else 1
+    # The rank-1 gradient kernels keep one CTA per (batch, chunk) by default: their per-CTA epilogue (128 KB of map
+    # gradients written, then read and written again) outweighs the wave-quantisation gain of a head split (measured at
+    # configs 2 and 5).  The rank-4 kernels walk 4 H kernel heads per CTA, so their epilogue is negligible: they split.
+    if precision != _lib.PRECISION_IO:
+        a.hsplit = 1
+    elif R == 1:
+        a.hsplit = int(hsplit) if H % max(int(hsplit), 1) == 0 else 1
+    else:
+        a.hsplit = head_split(B, nc, H, R, precision, dev) if hsplit == 1 else int(hsplit)
     parts = None
     if a.hsplit > 1:          # every head range writes its own partial of the head-shared map gradients
-        parts = (torch.empty((a.hsplit, B, L, R, N), **f32), torch.empty((a.hsplit, B, L, O, N), **f32))
-        a.dBhat, a.dChat = parts[0].data_ptr(), parts[1].data_ptr()
+        k = a.hsplit
+        parts = dict(dBhat=torch.empty((k, B, L, R, N), **f32), dChat=torch.empty((k, B, L, O, N), **f32))
+        if R > 1:
+            if out["dgBp"] is not None:
+                parts["dgBp"] = torch.empty((k, B, L, R, N), **f32)
+            if out["dgCp"] is not None:
+                parts["dgCp"] = torch.empty((k, B, L, O, N), **f32)
+        for key, v in parts.items():
+            setattr(a, key, v.data_ptr())
     for k in ("dgBp", "dgCp", "dwd", "dchi"):
-        if out[k] is not None:
+        if out[k] is not None and not (parts is not None and k in parts):
             setattr(a, k, out[k].data_ptr())
     if pb is not None:
         a.dbeta_part = pb.data_ptr()
@@ -610,7 +623,8 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     run_phase(a, "scan_chunk_grads", _lib.PHASE_CHUNK_GRADS, None, None, dt, precision)
     del keep
     if parts is not None:
-        out["dBhat"], out["dChat"] = parts[0].sum(0), parts[1].sum(0)
+        for key, v in parts.items():
+            out[key] = v.sum(0)
     if euler:
         out["dw"] = out["dw"] + dwd_tmp
     out["dbeta"] = pb.sum(0) if pb is not None else None
