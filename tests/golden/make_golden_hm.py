@@ -14,7 +14,9 @@ import warnings
 
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: python " + sys.argv[0] + " /path/to/the/reference/checkout")
+REF = sys.argv[1]
 sys.dont_write_bytecode = True
 sys.path.insert(0, REF + "/src")
 warnings.filterwarnings("ignore")
