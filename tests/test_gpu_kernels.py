@@ -250,9 +250,9 @@ def test_scan_tc_backward(case):
         # head ranges on separate CTAs (partial buffers of the head-shared map gradients summed by the host)
         g3 = ops.scan_bwd(geo, 128, _lib.PRECISION_IO, *args, Sin, atot, c["dy"], c["dS_fin"], c["euler"], c["S0"] is not None,
                           hsplit=2)
-        for k, v in g.items():
-            if v is not None:
-                assert rel(g3[k], v) < 1e-5, ("head split", k, rel(g3[k], v))
+        errs3 = {k: rel(g3[k], v) for k, v in rg.items() if v is not None}
+        bad3 = {k: e for k, e in errs3.items() if not e < 2e-2}      # each range rounds its own summed score gradient
+        assert not bad3, ("head split", bad3)
 
 
 # ---------------------------------------------------------------------------------------------------- scan, tcgen05 rank 4
