@@ -279,5 +279,13 @@ class HybridMambaSSM(StateLifecycle, nn.Module):
         return out, ordered
 
     def step(self, x_t, state=None):
-        raise NotImplementedError("HybridMambaSSM(backend='cuda'): the single-token step is not built; call forward on "
-                                  "[B, 1, d_model] with `state`")
+        """One token: ``x_t [B, d_model]``, ``state`` from `init_state` or a previous call -> ``(y_t [B, d_model], State)``
+        (reference: hybrid_mamba.py:2876).  Runs the layer on a length-1 sequence: the same kernels and the same carry contract as
+        `forward`, so a sequence stepped token by token equals the sequence run at once; there is no separate decode
+        kernel (a step costs the layer's launch count)."""
+        if x_t.dim() != 2 or x_t.shape[-1] != self.d_model:
+            raise ValueError(f"HybridMambaSSM.step: expected x_t of shape [B, {self.d_model}], got {tuple(x_t.shape)}")
+        if state is None:
+            state = self.init_state(x_t.shape[0], device=x_t.device)
+        y, new = self.forward(x_t.unsqueeze(1), state=state, return_state=True)
+        return y.squeeze(1), new

@@ -435,8 +435,16 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         return torch.einsum("bhgq,bhrqn->bhgrn", ul, Bt).reshape(Bsz, s.H, s.P, s.N)
 
     def step(self, x_t, state=None):
-        raise NotImplementedError("SSDMimoSSM(backend='cuda'): single-token decode is not part of this backend; call "
-                                  "forward on a length-1 sequence with `state` for exact continuation")
+        """One token: ``x_t [B, d_model]``, ``state`` from `init_state` or a previous call -> ``(y_t [B, d_model], State)``
+        (reference: ssd_mimo.py:4629).  Runs the layer on a length-1 sequence: the same kernels and the same carry contract as
+        `forward`, so a sequence stepped token by token equals the sequence run at once; there is no separate decode
+        kernel (a step costs the layer's launch count)."""
+        if x_t.dim() != 2 or x_t.shape[-1] != self.d_model:
+            raise ValueError(f"SSDMimoSSM.step: expected x_t of shape [B, {self.d_model}], got {tuple(x_t.shape)}")
+        if state is None:
+            raise ValueError("SSDMimoSSM.step: `state` is required (start from layer.init_state(batch_size))")
+        y, new = self.forward(x_t.unsqueeze(1), state=state, return_state=True)
+        return y.squeeze(1), new
 
 
 class _OutNorm(nn.Module):

@@ -233,3 +233,40 @@ def test_hm_refusals():
         layer(torch.zeros(1, 4, 32))                    # CPU tensor: refused by name, no CPU route
     with pytest.raises(ValueError):
         layer.set_execution({"precision": "ieee"})
+
+
+# ---------------------------------------------------------------------------------------------------- decode step
+def test_step_equals_forward(cpu_kernels):
+    """`step` token by token from a carried State equals `forward` on the same tokens (outputs and every carry)."""
+    rec = load_golden("dyn_trap_conv")
+    layer = _layer(rec)
+    x = rec["x"][:, :9]
+    with torch.no_grad():
+        y_all, s_all = layer(x, return_state=True)
+        y_head, st = layer(x[:, :5], return_state=True)
+        ys = [y_head]
+        for t in range(5, 9):
+            y_t, st = layer.step(x[:, t], st)
+            assert y_t.shape == (x.shape[0], layer.d_model)
+            ys.append(y_t.unsqueeze(1))
+    assert _rel(torch.cat(ys, 1), y_all) < 1e-5
+    for k in s_all:
+        assert _rel(st[k], s_all[k]) < 1e-5, k
+    with pytest.raises(ValueError):
+        layer.step(x[:, 0], None)
+
+
+def test_hm_step_equals_forward(cpu_hm_kernels):
+    rec = load_golden("hm_small")
+    layer = HybridMambaSSM(HybridMambaConfig(**rec["config"]))
+    layer.load_state_dict(rec["state_dict"], strict=True)
+    x = rec["x"][:, :8]
+    with torch.no_grad():
+        y_all, s_all = layer(x, return_state=True)
+        st, ys = None, []
+        for t in range(8):
+            y_t, st = layer.step(x[:, t], st)
+            ys.append(y_t.unsqueeze(1))
+    assert _rel(torch.cat(ys, 1), y_all) < 1e-5
+    for k in s_all:
+        assert _rel(st[k], s_all[k]) < 1e-5, k
