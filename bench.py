@@ -68,8 +68,8 @@ WORKLOADS = {
 # a launch processes, so `roofline.traffic` of a full-size launch is this figure times its tokens.
 DRAM_BYTES_PER_TOKEN = {
     "m2": {"scan_chunk_grads": 68451.0, "scan_chunk_out": 23852.0, "scan_chunk_state": 22452.0},
-    "mimo4": {"scan_chunk_grads": 416387.0},
-    "hm": {"hm_scan_bwd": 42650.0, "hm_scan_fwd": 12522.0},
+    "mimo4": {"scan_chunk_grads": 416550.0},
+    "hm": {"hm_scan_bwd": 41920.0, "hm_scan_fwd": 13610.0},
 }
 
 
