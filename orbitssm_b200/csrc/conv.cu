@@ -16,52 +16,44 @@ namespace orbit {
 constexpr int CONV_MAXW = 4;
 constexpr int CONV_TL = 16;   // tokens per thread run
 
-// Raw in-flight copy of one channel vector (kept unconverted while the load is outstanding: 4 registers, not VEC).
+// Raw in-flight copy of one channel vector (kept unconverted while the load is outstanding).  The vector is one
+// naturally aligned load of VEC * sizeof(T) bytes: 2, 4, 8 or 16.
+template <int BYTES> struct RawStore;
+template <> struct RawStore<2> { using type = unsigned short; };
+template <> struct RawStore<4> { using type = unsigned; };
+template <> struct RawStore<8> { using type = uint2; };
+template <> struct RawStore<16> { using type = uint4; };
+
 template <typename T, int VEC>
 struct RawVec {
-  using Store = typename std::conditional<VEC == 1, T, uint4>::type;
+  using Store = typename RawStore<VEC * (int)sizeof(T)>::type;
   Store r;
-  __device__ __forceinline__ void load(const T* p) {
-    if constexpr (VEC == 1) r = *p;
-    else r = *reinterpret_cast<const uint4*>(p);
-  }
+  __device__ __forceinline__ void load(const T* p) { r = *reinterpret_cast<const Store*>(p); }
 };
 
 template <typename T, int VEC>
 struct ChanVec {
   float v[VEC];
   __device__ __forceinline__ void from_raw(const RawVec<T, VEC>& raw) {
-    if constexpr (VEC == 1) {
-      v[0] = ldf(&raw.r);
-    } else {
-      const T* e = reinterpret_cast<const T*>(&raw.r);
+    const T* e = reinterpret_cast<const T*>(&raw.r);
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) v[i] = ldf(e + i);
-    }
+    for (int i = 0; i < VEC; ++i) v[i] = ldf(e + i);
   }
   __device__ __forceinline__ void load(const T* p) {
-    if constexpr (VEC == 1) {
-      v[0] = ldf(p);
-    } else {
-      Vec16<T> r;
-      r.load(p);
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) v[i] = r.get(i);
-    }
+    RawVec<T, VEC> raw;
+    raw.load(p);
+    from_raw(raw);
   }
   __device__ __forceinline__ void zero() {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) v[i] = 0.f;
   }
   __device__ __forceinline__ void store(T* p) const {
-    if constexpr (VEC == 1) {
-      stf(p, v[0]);
-    } else {
-      Vec16<T> r;
+    typename RawVec<T, VEC>::Store r;
+    T* e = reinterpret_cast<T*>(&r);
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) r.set(i, v[i]);
-      r.store(p);
-    }
+    for (int i = 0; i < VEC; ++i) stf(e + i, v[i]);
+    *reinterpret_cast<typename RawVec<T, VEC>::Store*>(p) = r;
   }
 };
 
@@ -278,7 +270,7 @@ __device__ __forceinline__ void load_taps(float (&w)[VEC][W], float (&bs)[VEC], 
 constexpr int CT_NT = 4;         // consecutive token tiles per CTA (taps stay in registers across them)
 
 template <typename T, int VEC, int W, bool SILU>
-__global__ void __launch_bounds__(256, 2) conv_fwd_tiled_kernel(const T* __restrict__ x, int64_t xbs, int64_t xrs,
+__global__ void __launch_bounds__(256, (VEC * sizeof(T) >= 16) ? 2 : 4) conv_fwd_tiled_kernel(const T* __restrict__ x, int64_t xbs, int64_t xrs,
                                                              const float* __restrict__ weight, const float* __restrict__ bias,
                                                              const float* __restrict__ window, T* __restrict__ y, int L, int C) {
   __shared__ RawVec<T, VEC> tile[CT_TT + W - 1][32];
@@ -324,7 +316,7 @@ constexpr int CTB_TT = 32;       // backward: tokens per tile
 constexpr int CTB_WARPS = 4;
 
 template <typename T, int VEC, int W, bool SILU>
-__global__ void __launch_bounds__(CTB_WARPS * 32, 2) conv_bwd_tiled_kernel(const T* __restrict__ x, int64_t xbs, int64_t xrs,
+__global__ void __launch_bounds__(CTB_WARPS * 32, (VEC * sizeof(T) >= 16) ? 2 : 4) conv_bwd_tiled_kernel(const T* __restrict__ x, int64_t xbs, int64_t xrs,
                                                              const float* __restrict__ weight, const float* __restrict__ bias,
                                                              const float* __restrict__ window, const T* __restrict__ dy,
                                                              T* __restrict__ dx, int64_t dxbs, int64_t dxrs,
@@ -524,6 +516,10 @@ extern "C" int orbit_conv1d_fwd(const void* x, int64_t x_batch_stride, int64_t x
   if (dtype == BF16) {
     using T = __nv_bfloat16;
     if (conv_vec_ok<T>(x, x_batch_stride, x_row_stride, y, C)) {
+      if (C % 128 == 0) {   // tiled path: 8-byte vectors keep 32 warps resident per SM
+        CONV_DISPATCH_W(conv_fwd_launch, T, 4, (const T*)x, x_batch_stride, x_row_stride, weight, bias, window, (T*)y, B,
+                        L, C, silu, st)
+      }
       CONV_DISPATCH_W(conv_fwd_launch, T, 8, (const T*)x, x_batch_stride, x_row_stride, weight, bias, window, (T*)y, B,
                       L, C, silu, st)
     }
@@ -568,6 +564,10 @@ extern "C" int orbit_conv1d_bwd(const void* x, int64_t x_batch_stride, int64_t x
     if (dtype == BF16) {
       using T = __nv_bfloat16;
       if (conv_vec_ok<T>(x, x_batch_stride, x_row_stride, dy, C, dx, dx_batch_stride, dx_row_stride)) {
+        if (C % 128 == 0 && dwindow == nullptr) {   // tiled path: 8-byte vectors keep 16 warps resident per SM
+          CONV_DISPATCH_W(conv_bwd_launch, T, 4, (const T*)x, x_batch_stride, x_row_stride, weight, bias, window,
+                          (const T*)dy, (T*)dx, dx_batch_stride, dx_row_stride, dwindow, part, B, L, C, silu, st, &nslots)
+        }
         CONV_DISPATCH_W(conv_bwd_launch, T, 8, (const T*)x, x_batch_stride, x_row_stride, weight, bias, window,
                         (const T*)dy, (T*)dx, dx_batch_stride, dx_row_stride, dwindow, part, B, L, C, silu, st, &nslots)
       }

@@ -166,6 +166,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
   float* wv = cs + 128;
   float* wdv = wv + 128;
   float* wsum = wdv + 128;
+  float* dgs = wsum + 8;                 // skip coefficients D[h, :] of the current head (zeros without a skip)
   __shared__ uint64_t bar_map, bar_x[2], bar_cb, bar_y;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -222,24 +223,29 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
   const uint32_t idesc_y = idesc_bf16(128, 64, 0, 1);
   __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(a.y);
 
-  float d_n = 0.f, wt_n = 0.f, wdt_n = 0.f;
+  float d_n = 0.f, wt_n = 0.f, wdt_n = 0.f, dg_n = 0.f;
   const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H + h0;
+  const bool dg_owner = a.Dg != nullptr && tid >= 128 && tid < 128 + TC_G;   // threads 128..191 fetch D[h, tid-128]
   if (tid < Tv) {
     d_n = a.dA[ck];
     wt_n = a.w[ck];
     wdt_n = a.wd[ck];
   }
+  if (dg_owner) dg_n = a.Dg[h0 * TC_G + tid - 128];
   for (int h = 0; h < Hl; ++h) {
     const int buf = h & 1;
-    const float d = d_n, wt = wt_n, wdt = wdt_n;
+    const float d = d_n, wt = wt_n, wdt = wdt_n, dgv = dg_n;
     if (tid < Tv && h + 1 < Hl) {
       d_n = a.dA[ck + h + 1];
       wt_n = a.w[ck + h + 1];
       wdt_n = a.wd[ck + h + 1];
     }
+    if (dg_owner && h + 1 < Hl) dg_n = a.Dg[(h0 + h + 1) * TC_G + tid - 128];
     if (tid < 128) {
       wv[tid] = wt;
       wdv[tid] = wdt;
+    } else if (tid < 128 + TC_G) {
+      dgs[tid - 128] = dgv;
     }
     chunk_prefix(d, cs, wsum);
     // masked scores: this thread owns row t, column slabs 2*wg and 2*wg+1 (32 columns each)
@@ -256,14 +262,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
           uint32_t r[32];
           tmem_ld32(tmem_addr(tbase, q * 32, TM_CB + j * 32), r);
           tmem_ld_wait();
+          // branch-free (selects only): the 32 exponentials of a slab are independent and overlap in the pipeline
           float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int s = j * 32 + i;
-            float wgt = 0.f;
-            if (s < t) wgt = __expf(cst - cs[s]) * wv[s];
-            else if (s == t) wgt = wdt_t;
-            v[i] = __uint_as_float(r[i]) * wgt;
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 c4 = *reinterpret_cast<const float4*>(cs + j * 32 + i4 * 4);
+            const float4 w4 = *reinterpret_cast<const float4*>(wv + j * 32 + i4 * 4);
+            const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, wq[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = i4 * 4 + e, s = j * 32 + i;
+              const float E = __expf(cst - cv[e]);          // may overflow above the diagonal: selected away below
+              const float wgt = s < t ? E * wq[e] : (s == t ? wdt_t : 0.f);
+              v[i] = __uint_as_float(r[i]) * wgt;
+            }
           }
 #pragma unroll
           for (int k = 0; k < 16; ++k) pk[k] = pack_bf16(v[2 * k], v[2 * k + 1]);
@@ -300,16 +312,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
       for (int k4 = 0; k4 < 4; ++k4) {
         uint4 uv = *reinterpret_cast<const uint4*>(sX + buf * BLK + sw128_offset(t, wg * 4 + k4));
         const uint32_t* up = reinterpret_cast<const uint32_t*>(&uv);
+        const float4 dlo = *reinterpret_cast<const float4*>(dgs + wg * 32 + k4 * 8);
+        const float4 dhi = *reinterpret_cast<const float4*>(dgs + wg * 32 + k4 * 8 + 4);
+        const float dd[8] = {dlo.x, dlo.y, dlo.z, dlo.w, dhi.x, dhi.y, dhi.z, dhi.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int i = k4 * 8 + k * 2;
           float u0, u1;
           unpack_bf16(up[k], u0, u1);
-          float d0 = 0.f, d1 = 0.f;
-          if (a.Dg) {
-            d0 = a.Dg[(h0 + h) * TC_G + wg * 32 + i];
-            d1 = a.Dg[(h0 + h) * TC_G + wg * 32 + i + 1];
-          }
+          const float d0 = dd[2 * k], d1 = dd[2 * k + 1];
           float y0 = __uint_as_float(r1[i]) + at * __uint_as_float(r2[i]) + d0 * u0;
           float y1 = __uint_as_float(r1[i + 1]) + at * __uint_as_float(r2[i + 1]) + d1 * u1;
           outp[k4 * 4 + k] = pack_bf16(y0, y1);
@@ -591,6 +602,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
   float* gcs = ddpart + 256;             // [128]
   float* wsum = gcs + 128;               // 8
   float* red = wsum + 8;                 // 8
+  float* dgs = red + 8;                  // [64] skip coefficients D[h, :] of the current head (zeros without a skip)
   __shared__ uint64_t bar_map, bar_x[2], bar_cb, bar_a, bar_b;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -656,18 +668,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
   const uint32_t id_dm = idesc_bf16(128, 128, 0, 0), id_x2 = idesc_bf16(128, 64, 0, 1), id_x1 = idesc_bf16(128, 64, 1, 1);
 
   // clocks (and what part 1 left in ddA / dw) of the next head are fetched one head ahead
-  float d_n = 0.f, wt_n = 0.f, wdt_n = 0.f, da_n = 0.f, datot_n;
+  float d_n = 0.f, wt_n = 0.f, wdt_n = 0.f, da_n = 0.f, datot_n, dg_n = 0.f;
   const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H + h0;
+  const bool dg_owner = a.Dg != nullptr && tid >= 128 && tid < 128 + TC_G;   // threads 128..191 fetch D[h, tid-128]
   if (tid < Tv) {
     d_n = a.dA[ck];
     wt_n = a.w[ck];
     wdt_n = a.wd[ck];
     da_n = a.ddA[ck];
   }
+  if (dg_owner) dg_n = a.Dg[h0 * TC_G + tid - 128];
   datot_n = a.dw[((int64_t)b * a.L + t0) * H + h0];
   for (int h = 0; h < Hl; ++h) {
     const int buf = h & 1;
-    const float d = d_n, wt = wt_n, wdt = wdt_n, da_t = da_n, datot = datot_n;
+    const float d = d_n, wt = wt_n, wdt = wdt_n, da_t = da_n, datot = datot_n, dgv = dg_n;
+    if (dg_owner && h + 1 < Hl) dg_n = a.Dg[(h0 + h + 1) * TC_G + tid - 128];
     const int64_t gi = ck + h;
     if (h + 1 < Hl) {
       if (tid < Tv) {
@@ -681,6 +696,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
     if (tid < 128) {
       wv[tid] = wt;
       wdv[tid] = wdt;
+    } else if (tid < 128 + TC_G) {
+      dgs[tid - 128] = dgv;
     }
     chunk_prefix(d, cs, wsum);
     if (tid == 0 && !*abort_flag) {
@@ -715,26 +732,31 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
           tmem_ld32(tmem_addr(tbase, q * 32, TM_DM + j * 32), rm);
           tmem_ld32(tmem_addr(tbase, q * 32, TM_CB + j * 32), rc);
           tmem_ld_wait();
+          // branch-free (selects only): the 32 exponentials of a slab are independent and overlap in the pipeline
           float mv[32];
+          float kd = 0.f;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int s = j * 32 + i;
-            const float dm = __uint_as_float(rm[i]), cb = __uint_as_float(rc[i]);
-            const float kv = dm * cb;
-            float wgt = 0.f, ce = 0.f;
-            if (s < t) {
-              const float E = __expf(cst - cs[s]);
-              wgt = E * wv[s];
-              ce = kv * E;
-              rowS = fmaf(ce, wv[s], rowS);
-            } else if (s == t) {
-              wgt = wdt_t;
-              kdiag[t] = kv;
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 c4 = *reinterpret_cast<const float4*>(cs + j * 32 + i4 * 4);
+            const float4 w4 = *reinterpret_cast<const float4*>(wv + j * 32 + i4 * 4);
+            const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, wq[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = i4 * 4 + e, s = j * 32 + i;
+              const float dm = __uint_as_float(rm[i]), cb = __uint_as_float(rc[i]);
+              const float kv = dm * cb;
+              const float E = __expf(cst - cv[e]);          // may overflow above the diagonal: selected away below
+              const bool below = s < t, diag = s == t;
+              const float wgt = below ? E * wq[e] : (diag ? wdt_t : 0.f);
+              const float ce = below ? kv * E : 0.f;
+              rowS = fmaf(ce, wq[e], rowS);
+              kd = diag ? kv : kd;
+              colv[i] = ce;
+              acc[jj][i] = fmaf(dm, wgt, acc[jj][i]);
+              mv[i] = cb * wgt;
             }
-            colv[i] = ce;
-            acc[jj][i] = fmaf(dm, wgt, acc[jj][i]);
-            mv[i] = cb * wgt;
           }
+          if (j == q) kdiag[t] = kd;
 #pragma unroll
           for (int k = 0; k < 16; ++k) pk[k] = pack_bf16(mv[2 * k], mv[2 * k + 1]);
         }
@@ -776,6 +798,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
         uint4 dv = *reinterpret_cast<const uint4*>(sDY + buf * BLK + sw128_offset(t, wg * 4 + k4));
         const uint32_t* up = reinterpret_cast<const uint32_t*>(&uv);
         const uint32_t* dp = reinterpret_cast<const uint32_t*>(&dv);
+        const float4 dlo = *reinterpret_cast<const float4*>(dgs + wg * 32 + k4 * 8);
+        const float4 dhi = *reinterpret_cast<const float4*>(dgs + wg * 32 + k4 * 8 + 4);
+        const float dd[8] = {dlo.x, dlo.y, dlo.z, dlo.w, dhi.x, dhi.y, dhi.z, dhi.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int i = k4 * 8 + k * 2;
@@ -783,11 +808,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
           unpack_bf16(up[k], u0, u1);
           unpack_bf16(dp[k], g0, g1);
           const float x20 = __uint_as_float(r2[i]), x21 = __uint_as_float(r2[i + 1]);
-          float d0 = 0.f, d1 = 0.f;
-          if (a.Dg) {
-            d0 = a.Dg[(h0 + h) * TC_G + wg * 32 + i];
-            d1 = a.Dg[(h0 + h) * TC_G + wg * 32 + i + 1];
-          }
+          const float d0 = dd[2 * k], d1 = dd[2 * k + 1];
           outp[k4 * 4 + k] = pack_bf16(__uint_as_float(r1[i]) + es * x20 + d0 * g0, __uint_as_float(r1[i + 1]) + es * x21 + d1 * g1);
           de_half = fmaf(u0, x20, fmaf(u1, x21, de_half));
           ddv[i] = g0 * u0;
