@@ -20,6 +20,9 @@ namespace orbit {
 using namespace tc;
 
 constexpr int TC_T = 128, TC_N = 128, TC_G = 64;
+constexpr int ISSUER = 128;      // thread that issues the per-head MMAs and TMA refills in the output / score-gradient kernels
+constexpr int OUT_CLK_LD = 448;  // floats per staged-clocks buffer of the output kernel
+constexpr int GS_CLK_LD = 592;   // floats per staged-clocks buffer of the score-gradient kernel
 
 // ------------------------------------------------------------------------------------------------------------------
 // chunk_state (mode 0):  Z[n,p] = sum_s B[s,n] e_s u[s,p],   e_s = exp(cs_T - cs_s) w_s          -> a.Sin, a.atot
@@ -163,10 +166,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
   uint8_t* sMs = sm + 6 * BLK;           // masked scores [128 t][128 s], 2 blocks
   uint8_t* sS = sm + 8 * BLK;            // entering state [128 n][64 p] bf16, 2 buffers
   float* cs = reinterpret_cast<float*>(sm + 10 * BLK);
-  float* wv = cs + 128;
-  float* wdv = wv + 128;
-  float* wsum = wdv + 128;
-  float* dgs = wsum + 8;                 // skip coefficients D[h, :] of the current head (zeros without a skip)
+  float* fs = cs + 128;                  // split decay factors of the columns (chunk_prefix_split)
+  float* fw = fs + 128;
+  float* wsum = fw + 128;
+  float* clk = wsum + 8;                 // [2][OUT_CLK_LD] per-head rows staged one head ahead (see stage_clocks)
   __shared__ uint64_t bar_map, bar_x[2], bar_cb, bar_y;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -223,31 +226,48 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
   const uint32_t idesc_y = idesc_bf16(128, 64, 0, 1);
   __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(a.y);
 
-  float d_n = 0.f, wt_n = 0.f, wdt_n = 0.f, dg_n = 0.f;
-  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H + h0;
-  const bool dg_owner = a.Dg != nullptr && tid >= 128 && tid < 128 + TC_G;   // threads 128..191 fetch D[h, tid-128]
-  if (tid < Tv) {
-    d_n = a.dA[ck];
-    wt_n = a.w[ck];
-    wdt_n = a.wd[ck];
-  }
-  if (dg_owner) dg_n = a.Dg[h0 * TC_G + tid - 128];
+  // Per-head rows are staged one head ahead by cp.async into clk[h & 1]: [dA | w | wd] x 128 tokens and the skip
+  // coefficients D[h, 0..63].  No registers are held across the head, so the loads really are in flight during the
+  // previous head.
+  const int64_t ckv = ((int64_t)b * a.L + t0 + min(tid, Tv - 1)) * H + h0;   // a mapped address for every thread
+  auto stage_clocks = [&](int hh) {
+    float* sc = clk + (hh & 1) * OUT_CLK_LD;
+    if (tid < 128) {
+      const bool ok = tid < Tv;
+      cp_async4z(sc + tid, a.dA + ckv + hh, ok);
+      cp_async4z(sc + 128 + tid, a.w + ckv + hh, ok);
+      cp_async4z(sc + 256 + tid, a.wd + ckv + hh, ok);
+    } else if (tid < 128 + TC_G) {
+      const bool ok = a.Dg != nullptr;
+      cp_async4z(sc + 384 + tid - 128, ok ? a.Dg + (h0 + hh) * TC_G + tid - 128 : a.dA, ok);
+    }
+    cp_async_commit();
+  };
+  stage_clocks(0);
   for (int h = 0; h < Hl; ++h) {
     const int buf = h & 1;
-    const float d = d_n, wt = wt_n, wdt = wdt_n, dgv = dg_n;
-    if (tid < Tv && h + 1 < Hl) {
-      d_n = a.dA[ck + h + 1];
-      wt_n = a.w[ck + h + 1];
-      wdt_n = a.wd[ck + h + 1];
+    const float* sc = clk + buf * OUT_CLK_LD;
+    const float *wv = sc + 128, *wdv = sc + 256, *dgs = sc + 384;
+    // The inter-chunk part C Sin of this head needs no mask: it runs under the mask pass.  The per-head MMAs and TMA
+    // refills are issued by thread 128, whose warp (rows 0..31, slabs 2 and 3) has no mask work.
+    bool x_ok = false;
+    if (tid == ISSUER && !*abort_flag) {
+      x_ok = wait_or_abort(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag);
+      if (x_ok) {
+        tc_fence_after_sync();
+        const uint32_t ac = smem_u32(sC), bs = smem_u32(sS + buf * BLK);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_Y2, desc_k(ac, ks), desc_mn(bs, ks), idesc_y, ks > 0 ? 1u : 0u);
+      }
     }
-    if (dg_owner && h + 1 < Hl) dg_n = a.Dg[(h0 + h + 1) * TC_G + tid - 128];
+    cp_async_wait_all();
+    float d = 0.f, wt = 0.f;
     if (tid < 128) {
-      wv[tid] = wt;
-      wdv[tid] = wdt;
-    } else if (tid < 128 + TC_G) {
-      dgs[tid - 128] = dgv;
+      d = sc[tid];
+      wt = sc[128 + tid];
     }
-    chunk_prefix(d, cs, wsum);
+    if (h + 1 < Hl) stage_clocks(h + 1);   // the other buffer: its readers finished before the previous head's last barrier
+    chunk_prefix_split(d, wt, cs, fs, fw, wsum);   // its barriers also publish the staged rows to every thread
     // masked scores: this thread owns row t, column slabs 2*wg and 2*wg+1 (32 columns each)
     if (cb_ok) {
       const float cst = cs[t], wdt_t = wdv[t];
@@ -262,8 +282,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
           uint32_t r[32];
           tmem_ld32(tmem_addr(tbase, q * 32, TM_CB + j * 32), r);
           tmem_ld_wait();
-          // branch-free (selects only): the 32 exponentials of a slab are independent and overlap in the pipeline
           float v[32];
+          if (j < q) {
+            // slab wholly below the diagonal: decay = (row factor) x (column factor), no exponential per element
+            const float g = __expf(cst - cs[j * 32 + 31]);
+#pragma unroll
+            for (int i4 = 0; i4 < 8; ++i4) {
+              const float4 f4 = *reinterpret_cast<const float4*>(fw + j * 32 + i4 * 4);
+              v[i4 * 4] = __uint_as_float(r[i4 * 4]) * (g * f4.x);
+              v[i4 * 4 + 1] = __uint_as_float(r[i4 * 4 + 1]) * (g * f4.y);
+              v[i4 * 4 + 2] = __uint_as_float(r[i4 * 4 + 2]) * (g * f4.z);
+              v[i4 * 4 + 3] = __uint_as_float(r[i4 * 4 + 3]) * (g * f4.w);
+            }
+          } else {
+          // diagonal slab, branch-free (selects only): the 32 exponentials are independent and overlap in the pipeline
 #pragma unroll
           for (int i4 = 0; i4 < 8; ++i4) {
             const float4 c4 = *reinterpret_cast<const float4*>(cs + j * 32 + i4 * 4);
@@ -277,6 +309,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
               v[i] = __uint_as_float(r[i]) * wgt;
             }
           }
+          }
 #pragma unroll
           for (int k = 0; k < 16; ++k) pk[k] = pack_bf16(v[2 * k], v[2 * k + 1]);
         }
@@ -289,16 +322,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
     tc_fence_before_sync();
     fence_proxy_async();
     __syncthreads();
-    if (tid == 0 && !*abort_flag) {
-      if (wait_or_abort(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag)) {
-        tc_fence_after_sync();
-        const uint32_t am = smem_u32(sMs), bx = smem_u32(sX + buf * BLK), ac = smem_u32(sC), bs = smem_u32(sS + buf * BLK);
+    if (tid == ISSUER && x_ok && !*abort_flag) {
+      tc_fence_after_sync();
+      const uint32_t am = smem_u32(sMs), bx = smem_u32(sX + buf * BLK);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_Y1, desc_k(am, ks), desc_mn(bx, ks), idesc_y, ks > 0 ? 1u : 0u);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_Y2, desc_k(ac, ks), desc_mn(bs, ks), idesc_y, ks > 0 ? 1u : 0u);
-        umma_commit(&bar_y);
-      }
+      for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_Y1, desc_k(am, ks), desc_mn(bx, ks), idesc_y, ks > 0 ? 1u : 0u);
+      umma_commit(&bar_y);   // covers the C Sin product issued at the top of the head too
     }
     if (wait_warp(&bar_y, (uint32_t)(h & 1), abort_flag)) {
       tc_fence_after_sync();
@@ -334,7 +363,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (tid == 0 && !*abort_flag && h + 2 < Hl) {
+    if (tid == ISSUER && !*abort_flag && h + 2 < Hl) {
       mbar_expect_tx(&bar_x[buf], 2 * BLK);
       tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
       tma_load_2d(sS + buf * BLK, &tmS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
@@ -592,9 +621,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
   uint8_t* sMs = sm + 8 * BLK;           // masked scores, later the summed score gradient; 2 blocks
   uint8_t* sdS = sm + 10 * BLK;          // dSo bf16 [n][p], 2 buffers
   float* cs = reinterpret_cast<float*>(sm + 12 * BLK);
-  float* wv = cs + 128;
-  float* wdv = wv + 128;
-  float* rowpart = wdv + 128;            // [2][128]
+  float* fs = cs + 128;                  // split decay factors of the columns (chunk_prefix_split)
+  float* fw = fs + 128;
+  float* rowpart = fw + 128;             // [2][128]
   float* colpart = rowpart + 256;        // [4][128]
   float* depart = colpart + 512;         // [2][128]
   float* kdiag = depart + 256;           // [128]
@@ -602,7 +631,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
   float* gcs = ddpart + 256;             // [128]
   float* wsum = gcs + 128;               // 8
   float* red = wsum + 8;                 // 8
-  float* dgs = red + 8;                  // [64] skip coefficients D[h, :] of the current head (zeros without a skip)
+  float* clk = red + 8;                  // [2][GS_CLK_LD] per-head rows staged one head ahead (see stage_clocks)
   __shared__ uint64_t bar_map, bar_x[2], bar_cb, bar_a, bar_b;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -667,51 +696,59 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
   __nv_bfloat16* duout = reinterpret_cast<__nv_bfloat16*>(a.du);
   const uint32_t id_dm = idesc_bf16(128, 128, 0, 0), id_x2 = idesc_bf16(128, 64, 0, 1), id_x1 = idesc_bf16(128, 64, 1, 1);
 
-  // clocks (and what part 1 left in ddA / dw) of the next head are fetched one head ahead
-  float d_n = 0.f, wt_n = 0.f, wdt_n = 0.f, da_n = 0.f, datot_n, dg_n = 0.f;
+  // Per-head rows are staged one head ahead by cp.async into clk[h & 1]: [dA | w | wd | da] x 128 tokens (da = what
+  // part 1 left in ddA), the skip coefficients D[h, 0..63] and datot (what part 1 left in dw).  No registers are held
+  // across the head, so the loads really are in flight during the previous head.
   const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H + h0;
-  const bool dg_owner = a.Dg != nullptr && tid >= 128 && tid < 128 + TC_G;   // threads 128..191 fetch D[h, tid-128]
-  if (tid < Tv) {
-    d_n = a.dA[ck];
-    wt_n = a.w[ck];
-    wdt_n = a.wd[ck];
-    da_n = a.ddA[ck];
-  }
-  if (dg_owner) dg_n = a.Dg[h0 * TC_G + tid - 128];
-  datot_n = a.dw[((int64_t)b * a.L + t0) * H + h0];
+  const int64_t ckv = ((int64_t)b * a.L + t0 + min(tid, Tv - 1)) * H + h0;   // a mapped address for every thread
+  auto stage_clocks = [&](int hh) {
+    float* sc = clk + (hh & 1) * GS_CLK_LD;
+    if (tid < 128) {
+      const bool ok = tid < Tv;
+      cp_async4z(sc + tid, a.dA + ckv + hh, ok);
+      cp_async4z(sc + 128 + tid, a.w + ckv + hh, ok);
+      cp_async4z(sc + 256 + tid, a.wd + ckv + hh, ok);
+      cp_async4z(sc + 384 + tid, a.ddA + ckv + hh, ok);
+    } else if (tid < 128 + TC_G) {
+      const bool ok = a.Dg != nullptr;
+      cp_async4z(sc + 512 + tid - 128, ok ? a.Dg + (h0 + hh) * TC_G + tid - 128 : a.dA, ok);
+    } else if (tid == 128 + TC_G) {
+      cp_async4z(sc + 576, a.dw + ((int64_t)b * a.L + t0) * H + h0 + hh, true);
+    }
+    cp_async_commit();
+  };
+  // MMA group A of head hh: dM = dy u^T and B dSo.  Issued as soon as the accumulators of the previous head are read
+  // out, so that it runs under the per-token stage of that head.
+  auto issue_group_a = [&](int hh) {
+    const int bf = hh & 1;
+    if (wait_or_abort(&bar_x[bf], (uint32_t)((hh >> 1) & 1), abort_flag)) {
+      tc_fence_after_sync();
+      const uint32_t ady = smem_u32(sDY + bf * BLK), bx = smem_u32(sX + bf * BLK), ab = smem_u32(sB),
+                     bd = smem_u32(sdS + bf * BLK);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) umma_bf16(tbase + TM_DM, desc_k(ady, ks), desc_k(bx, ks), id_dm, ks > 0 ? 1u : 0u);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DX2, desc_k(ab, ks), desc_mn(bd, ks), id_x2, ks > 0 ? 1u : 0u);
+      umma_commit(&bar_a);
+    }
+  };
+  stage_clocks(0);
+  if (tid == ISSUER && !*abort_flag && Hl > 0) issue_group_a(0);
   for (int h = 0; h < Hl; ++h) {
     const int buf = h & 1;
-    const float d = d_n, wt = wt_n, wdt = wdt_n, da_t = da_n, datot = datot_n, dgv = dg_n;
-    if (dg_owner && h + 1 < Hl) dg_n = a.Dg[(h0 + h + 1) * TC_G + tid - 128];
     const int64_t gi = ck + h;
-    if (h + 1 < Hl) {
-      if (tid < Tv) {
-        d_n = a.dA[ck + h + 1];
-        wt_n = a.w[ck + h + 1];
-        wdt_n = a.wd[ck + h + 1];
-        da_n = a.ddA[ck + h + 1];                        // part 1 left da here
-      }
-      datot_n = a.dw[((int64_t)b * a.L + t0) * H + h0 + h + 1];   // part 1 left datot here
-    }
+    const float* sc = clk + buf * GS_CLK_LD;
+    const float *wv = sc + 128, *wdv = sc + 256, *dgs = sc + 512;
+    cp_async_wait_all();
+    float d = 0.f, wt = 0.f, da_t = 0.f;
     if (tid < 128) {
-      wv[tid] = wt;
-      wdv[tid] = wdt;
-    } else if (tid < 128 + TC_G) {
-      dgs[tid - 128] = dgv;
+      d = sc[tid];
+      wt = sc[128 + tid];
+      da_t = sc[384 + tid];
     }
-    chunk_prefix(d, cs, wsum);
-    if (tid == 0 && !*abort_flag) {
-      if (wait_or_abort(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag)) {
-        tc_fence_after_sync();
-        const uint32_t ady = smem_u32(sDY + buf * BLK), bx = smem_u32(sX + buf * BLK), ab = smem_u32(sB),
-                       bd = smem_u32(sdS + buf * BLK);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) umma_bf16(tbase + TM_DM, desc_k(ady, ks), desc_k(bx, ks), id_dm, ks > 0 ? 1u : 0u);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DX2, desc_k(ab, ks), desc_mn(bd, ks), id_x2, ks > 0 ? 1u : 0u);
-        umma_commit(&bar_a);
-      }
-    }
+    if (h + 1 < Hl) stage_clocks(h + 1);   // the other buffer: its readers finished before the previous head's last barrier
+    chunk_prefix_split(d, wt, cs, fs, fw, wsum);   // its barriers also publish the staged rows to every thread
+    const float datot = sc[576];
     // ---- score pass: this thread owns row t, slabs j = 2*wg, 2*wg+1 ----
     float rowS = 0.f;
     if (wait_warp(&bar_a, (uint32_t)(h & 1), abort_flag) && cb_ok) {
@@ -732,8 +769,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
           tmem_ld32(tmem_addr(tbase, q * 32, TM_DM + j * 32), rm);
           tmem_ld32(tmem_addr(tbase, q * 32, TM_CB + j * 32), rc);
           tmem_ld_wait();
-          // branch-free (selects only): the 32 exponentials of a slab are independent and overlap in the pipeline
           float mv[32];
+          if (j < q) {
+            // slab wholly below the diagonal: decay = (row factor) x (column factor), no exponential per element;
+            // the column factor of K o E is applied after the column sums
+            const float g = __expf(cst - cs[j * 32 + 31]);
+#pragma unroll
+            for (int i4 = 0; i4 < 8; ++i4) {
+              const float4 f4 = *reinterpret_cast<const float4*>(fw + j * 32 + i4 * 4);
+              const float fq[4] = {f4.x, f4.y, f4.z, f4.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int i = i4 * 4 + e;
+                const float dm = __uint_as_float(rm[i]), cb = __uint_as_float(rc[i]);
+                const float kv = dm * cb, wgt = g * fq[e];
+                rowS = fmaf(kv, wgt, rowS);
+                colv[i] = kv * g;
+                acc[jj][i] = fmaf(dm, wgt, acc[jj][i]);
+                mv[i] = cb * wgt;
+              }
+            }
+          } else {
+          // diagonal slab, branch-free (selects only): the 32 exponentials are independent and overlap in the pipeline
           float kd = 0.f;
 #pragma unroll
           for (int i4 = 0; i4 < 8; ++i4) {
@@ -756,7 +813,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
               mv[i] = cb * wgt;
             }
           }
-          if (j == q) kdiag[t] = kd;
+          kdiag[t] = kd;
+          }
 #pragma unroll
           for (int k = 0; k < 16; ++k) pk[k] = pack_bf16(mv[2 * k], mv[2 * k + 1]);
         }
@@ -765,7 +823,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
         for (int k = 0; k < 4; ++k)
           *reinterpret_cast<uint4*>(dstb + sw128_offset(t, (j & 1) * 4 + k)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
         warp_colsum32(colv, lane);
-        colpart[q * 128 + j * 32 + lane] = colv[0];
+        colpart[q * 128 + j * 32 + lane] = j < q ? colv[0] * fs[j * 32 + lane] : colv[0];
       }
     }
     rowpart[wg * 128 + t] = rowS;
@@ -828,31 +886,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (tid == 0 && !*abort_flag && h + 2 < Hl) {
-      mbar_expect_tx(&bar_x[buf], 3 * BLK);
-      tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
-      tma_load_3d(sDY + buf * BLK, &tmDY, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
-      tma_load_2d(sdS + buf * BLK, &tmDS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
-    }
-    // ---- per-token clock gradients (threads 0..127 own token tid; every thread joins the reductions) ----
-    float g_cs = 0.f, g_w = 0.f, ede = 0.f;
-    if (tid < 128) {
+    if (warp >= 4) {
+      // Warps 4..7 have no per-token work: thread 128 issues what the next heads need meanwhile.  TMEM of this head is
+      // read out (barrier above), so group A of head h + 1 may overwrite it; the operand buffers of head h are free.
+      if (tid == ISSUER && !*abort_flag) {
+        if (h + 1 < Hl) issue_group_a(h + 1);
+        if (h + 2 < Hl) {
+          mbar_expect_tx(&bar_x[buf], 3 * BLK);
+          tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
+          tma_load_3d(sDY + buf * BLK, &tmDY, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
+          tma_load_2d(sdS + buf * BLK, &tmDS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
+        }
+      }
+    } else {
+      // ---- per-token clock gradients: thread tid owns token tid; reductions over warps 0..3 on a named barrier ----
       const float colS = colpart[tid] + colpart[128 + tid] + colpart[256 + tid] + colpart[384 + tid];
       const float rS = rowpart[tid] + rowpart[128 + tid];
       const float de = depart[tid] + depart[128 + tid];
       const float ET = __expf(cs[127] - cs[tid]);
-      g_cs = rS - colS * wt + __expf(cs[tid]) * da_t - ET * wt * de;
-      g_w = colS + ET * de;
-      ede = ET * wt * de;
-    }
-    const float tail = cta_sum(ede, red) + __expf(cs[127]) * datot;
-    if (tid == 127) g_cs += tail;
-    if (tid < 128) gcs[tid] = g_cs;
-    __syncthreads();
-    // reverse prefix: gcs[i] <- sum_{k<=i} g_cs[127-k]; the argument is read before chunk_prefix's first barrier,
-    // the result written after it
-    chunk_prefix(tid < 128 ? gcs[127 - tid] : 0.f, gcs, wsum);
-    if (tid < 128) {
+      float g_cs = rS - colS * wt + __expf(cs[tid]) * da_t - ET * wt * de;
+      const float g_w = colS + ET * de;
+      const float tail = sum_low128(ET * wt * de, red) + __expf(cs[127]) * datot;
+      if (tid == 127) g_cs += tail;
+      gcs[tid] = g_cs;
+      bar_low128();
+      // reverse prefix: gcs[i] <- sum_{k<=i} g_cs[127-k]; the argument is read before the prefix's first barrier, the
+      // result written after it
+      chunk_prefix_low128(gcs[127 - tid], gcs, wsum);
       const int tt = 127 - tid;          // prefix index tid holds the reverse-inclusive sum for token tt
       if (tt < Tv) {
         const int64_t go = ((int64_t)b * a.L + t0 + tt) * H + h0 + h;
@@ -862,9 +922,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
         a.dw[gi] = g_w;
         if (a.dwd) a.dwd[gi] = kdiag[tid];
       }
+      if (a.dDg_part && tid < 64)
+        a.dDg_part[(((int64_t)b * a.nc + c) * H + h0 + h) * TC_G + tid] = ddpart[tid] + ddpart[64 + tid] + ddpart[128 + tid] + ddpart[192 + tid];
     }
-    if (a.dDg_part && tid < 64)
-      a.dDg_part[(((int64_t)b * a.nc + c) * H + h0 + h) * TC_G + tid] = ddpart[tid] + ddpart[64 + tid] + ddpart[128 + tid] + ddpart[192 + tid];
     __syncthreads();
   }
 
@@ -961,7 +1021,7 @@ static int map_rows(CUtensorMap* m, const void* base, int cols, int64_t token_st
 }
 
 constexpr int SMEM_STATE = 6 * BLK + 2048 + 1024;
-constexpr int SMEM_OUT = 10 * BLK + 2048 + 1024;
+constexpr int SMEM_OUT = 10 * BLK + 5632 + 1024;
 
 // [B*nc*H*128 rows][64 p] bfloat16 view of a state-tile buffer: one [128 x 64] box per (batch, chunk, head)
 static int map_state(CUtensorMap* m, const void* base, const ScanArgs& a) {
@@ -1014,7 +1074,7 @@ int tc_launch_chunk_out(const ScanArgs& a, cudaStream_t st) {
 }
 
 constexpr int SMEM_GSTATE = 12 * BLK + 4096 + 1024;
-constexpr int SMEM_GSCORE = 12 * BLK + 8192 + 1024;
+constexpr int SMEM_GSCORE = 12 * BLK + 12800 + 1024;
 
 int tc_launch_chunk_grads(const ScanArgs& a, cudaStream_t st) {
   if (mimo_tc_geometry(a.R, a.O, a.G, a.N)) return mimo_tc_launch_grads(a, st);

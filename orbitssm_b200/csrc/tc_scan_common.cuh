@@ -68,6 +68,60 @@ __device__ __forceinline__ void chunk_prefix(float v, float* cs, float* wsum) {
   __syncthreads();
 }
 
+// chunk_prefix, plus the split of the decay exp(cs_t - cs_s) for a column s in an earlier 32-token slab than row t:
+//   exp(cs_t - cs_s) = exp(cs_t - cs_end(slab of s)) * fs[s],   fs[s] = exp(cs_end(slab of s) - cs_s),   fw[s] = fs[s] * w[s]
+// Both factors are <= 1 for non-positive steps, so neither overflows; the row factor costs one exponential per
+// (row, slab) instead of one per element.
+__device__ __forceinline__ void chunk_prefix_split(float v, float w, float* cs, float* fs, float* fw, float* wsum) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    float y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  const float tot = __shfl_sync(0xffffffffu, x, 31);
+  if (warp < 4 && lane == 31) wsum[warp] = x;
+  __syncthreads();
+  if (warp < 4) {
+    float off = 0.f;
+    for (int ww = 0; ww < warp; ++ww) off += wsum[ww];
+    cs[tid] = x + off;
+    const float f = __expf(tot - x);
+    fs[tid] = f;
+    fw[tid] = f * w;
+  }
+  __syncthreads();
+}
+
+// Variants for warps 0..3 only (threads 0..127), synchronised on named barrier 1 so that warps 4..7 can do other work
+// (issue MMAs and TMA copies) meanwhile.  Every thread of warps 0..3 must call them.
+__device__ __forceinline__ void bar_low128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void chunk_prefix_low128(float v, float* cs, float* wsum) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    float y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  if (lane == 31) wsum[warp] = x;
+  bar_low128();
+  float off = 0.f;
+  for (int ww = 0; ww < warp; ++ww) off += wsum[ww];
+  cs[tid] = x + off;
+  bar_low128();
+}
+// fixed-order sum of one float per thread of warps 0..3; `red` >= 4 floats
+__device__ __forceinline__ float sum_low128(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  bar_low128();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  bar_low128();
+  return (red[0] + red[1]) + (red[2] + red[3]);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
