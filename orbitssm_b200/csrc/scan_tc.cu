@@ -620,10 +620,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
   uint8_t* sDY = sm + 6 * BLK;           // 2 buffers
   uint8_t* sMs = sm + 8 * BLK;           // masked scores, later the summed score gradient; 2 blocks
   uint8_t* sdS = sm + 10 * BLK;          // dSo bf16 [n][p], 2 buffers
-  float* cs = reinterpret_cast<float*>(sm + 12 * BLK);
-  float* fs = cs + 128;                  // split decay factors of the columns (chunk_prefix_split)
-  float* fw = fs + 128;
-  float* rowpart = fw + 128;             // [2][128]
+  float* csb = reinterpret_cast<float*>(sm + 12 * BLK);   // [2][cs | fs | fw] x 128: prefix and split decay factors,
+                                                          // buffer h & 1 (filled during the previous head)
+  float* rowpart = csb + 768;            // [2][128]
   float* colpart = rowpart + 256;        // [4][128]
   float* depart = colpart + 512;         // [2][128]
   float* kdiag = depart + 256;           // [128]
@@ -631,7 +630,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
   float* gcs = ddpart + 256;             // [128]
   float* wsum = gcs + 128;               // 8
   float* red = wsum + 8;                 // 8
-  float* clk = red + 8;                  // [2][GS_CLK_LD] per-head rows staged one head ahead (see stage_clocks)
+  float* wsum2 = red + 8;                // 8 (prefix of the next head, warps 4..7)
+  float* clk = wsum2 + 8;                // [2][GS_CLK_LD] per-head rows staged one head ahead (see stage_clocks)
   __shared__ uint64_t bar_map, bar_x[2], bar_cb, bar_a, bar_b;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -732,23 +732,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
       umma_commit(&bar_a);
     }
   };
+  // Prefix of the steps and split decay factors of head hh from its staged rows, by warps 4..7 (which have no
+  // per-token work) while warps 0..3 finish the previous head.
+  auto prefix_high = [&](int hh) {
+    const float* scn = clk + (hh & 1) * GS_CLK_LD;
+    float* o = csb + (hh & 1) * 384;
+    chunk_prefix_split_high128(scn[tid - 128], scn[tid], o, o + 128, o + 256, wsum2);
+  };
   stage_clocks(0);
-  if (tid == ISSUER && !*abort_flag && Hl > 0) issue_group_a(0);
+  cp_async_wait_all();
+  __syncthreads();                         // staged rows of head 0 visible to every thread
+  if (warp >= 4) {
+    if (tid == ISSUER && !*abort_flag && Hl > 0) issue_group_a(0);
+    prefix_high(0);
+  }
+  __syncthreads();
   for (int h = 0; h < Hl; ++h) {
     const int buf = h & 1;
     const int64_t gi = ck + h;
     const float* sc = clk + buf * GS_CLK_LD;
     const float *wv = sc + 128, *wdv = sc + 256, *dgs = sc + 512;
-    cp_async_wait_all();
-    float d = 0.f, wt = 0.f, da_t = 0.f;
-    if (tid < 128) {
-      d = sc[tid];
-      wt = sc[128 + tid];
-      da_t = sc[384 + tid];
-    }
+    const float *cs = csb + buf * 384, *fs = cs + 128, *fw = cs + 256;
     if (h + 1 < Hl) stage_clocks(h + 1);   // the other buffer: its readers finished before the previous head's last barrier
-    chunk_prefix_split(d, wt, cs, fs, fw, wsum);   // its barriers also publish the staged rows to every thread
-    const float datot = sc[576];
     // ---- score pass: this thread owns row t, slabs j = 2*wg, 2*wg+1 ----
     float rowS = 0.f;
     if (wait_warp(&bar_a, (uint32_t)(h & 1), abort_flag) && cb_ok) {
@@ -884,11 +889,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
       warp_colsum32(ddv, lane);
       ddpart[q * 64 + wg * 32 + lane] = ddv[0];
     }
+    cp_async_wait_all();                   // this thread's share of the rows of head h + 1 (staged at the top of this head)
     tc_fence_before_sync();
     __syncthreads();
     if (warp >= 4) {
-      // Warps 4..7 have no per-token work: thread 128 issues what the next heads need meanwhile.  TMEM of this head is
-      // read out (barrier above), so group A of head h + 1 may overwrite it; the operand buffers of head h are free.
+      // Warps 4..7 have no per-token work: thread 128 issues what the next heads need, then the four warps form the
+      // prefix of head h + 1.  TMEM of this head is read out (barrier above), so group A of head h + 1 may overwrite
+      // it; the operand buffers of head h are free.
       if (tid == ISSUER && !*abort_flag) {
         if (h + 1 < Hl) issue_group_a(h + 1);
         if (h + 2 < Hl) {
@@ -898,8 +905,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
           tma_load_2d(sdS + buf * BLK, &tmDS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
         }
       }
+      if (h + 1 < Hl) prefix_high(h + 1);
     } else {
       // ---- per-token clock gradients: thread tid owns token tid; reductions over warps 0..3 on a named barrier ----
+      const float wt = sc[128 + tid], da_t = sc[384 + tid], datot = sc[576];
       const float colS = colpart[tid] + colpart[128 + tid] + colpart[256 + tid] + colpart[384 + tid];
       const float rS = rowpart[tid] + rowpart[128 + tid];
       const float de = depart[tid] + depart[128 + tid];
@@ -1074,7 +1083,7 @@ int tc_launch_chunk_out(const ScanArgs& a, cudaStream_t st) {
 }
 
 constexpr int SMEM_GSTATE = 12 * BLK + 4096 + 1024;
-constexpr int SMEM_GSCORE = 12 * BLK + 12800 + 1024;
+constexpr int SMEM_GSCORE = 12 * BLK + 14336 + 1024;
 
 int tc_launch_chunk_grads(const ScanArgs& a, cudaStream_t st) {
   if (mimo_tc_geometry(a.R, a.O, a.G, a.N)) return mimo_tc_launch_grads(a, st);

@@ -94,6 +94,28 @@ __device__ __forceinline__ void chunk_prefix_split(float v, float w, float* cs, 
   __syncthreads();
 }
 
+// chunk_prefix_split run by warps 4..7 alone (thread 128 + i owns token i), synchronised on named barrier 2, so that
+// it can run beside work of warps 0..3.  `wsum` >= 4 floats, not shared with the other variants while both may run.
+__device__ __forceinline__ void chunk_prefix_split_high128(float v, float w, float* cs, float* fs, float* fw, float* wsum) {
+  const int tok = threadIdx.x - 128, lane = tok & 31, warp = tok >> 5;
+  float x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    float y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  const float tot = __shfl_sync(0xffffffffu, x, 31);
+  if (lane == 31) wsum[warp] = x;
+  asm volatile("bar.sync 2, 128;" ::: "memory");
+  float off = 0.f;
+  for (int ww = 0; ww < warp; ++ww) off += wsum[ww];
+  cs[tok] = x + off;
+  const float f = __expf(tot - x);
+  fs[tok] = f;
+  fw[tok] = f * w;
+  asm volatile("bar.sync 2, 128;" ::: "memory");   // wsum may be rewritten by the next call
+}
+
 // Variants for warps 0..3 only (threads 0..127), synchronised on named barrier 1 so that warps 4..7 can do other work
 // (issue MMAs and TMA copies) meanwhile.  Every thread of warps 0..3 must call them.
 __device__ __forceinline__ void bar_low128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
