@@ -36,9 +36,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_state_kernel(const __g
   uint8_t* sM = sm;                      // map tile, 2 blocks
   uint8_t* sX = sm + 2 * BLK;            // raw drive tiles, 2 buffers
   uint8_t* sXs = sm + 4 * BLK;           // scaled drive tiles, 2 buffers
-  float* cs = reinterpret_cast<float*>(sm + 6 * BLK);
-  float* fv = cs + 128;
-  float* wsum = fv + 128;
+  float* fv = reinterpret_cast<float*>(sm + 6 * BLK);   // [2][128] per-token factors of heads h, h + 1
+  float* wsum = fv + 256;
   __shared__ uint64_t bar_map, bar_x[2], bar_mma[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -91,27 +90,57 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_state_kernel(const __g
     tc_fence_before_sync();
   };
 
-  // clocks of the next head are fetched one head ahead (their latency hides behind the current head's work)
+  // Two block-wide barriers per head.  The prefix of head h + 1 is formed beside the work of head h: its warp scans run
+  // in the interval of the scaling pass, its per-token factors fv[(h + 1) & 1] in the interval of the MMA issue and the
+  // read-out of head h - 1 (the chunk total is the sum of the four warp totals, known to every thread after the
+  // first barrier).  Clocks are fetched one head further ahead.
+  auto warp_scan = [&](float v) -> float {   // inclusive scan inside the warp; warp totals of warps 0..3 -> wsum
+    float x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      float y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (warp < 4 && lane == 31) wsum[warp] = x;
+    return x;
+  };
+  auto token_factor = [&](int hh, float x, float wt) {   // after the barrier that publishes wsum
+    if (tid < 128) {
+      const float w0 = wsum[0], w1 = wsum[1], w2 = wsum[2], w3 = wsum[3];
+      const float off = warp == 0 ? 0.f : (warp == 1 ? w0 : (warp == 2 ? w0 + w1 : (w0 + w1) + w2));
+      const float tot = ((w0 + w1) + w2) + w3, csv = x + off;
+      fv[(hh & 1) * 128 + tid] = mode == 0 ? __expf(tot - csv) * wt : __expf(csv);
+      if (tid == 0 && mode == 0) a.atot[((int64_t)b * a.nc + c) * H + hh] = __expf(tot);
+    }
+  };
   float d_n = 0.f, wt_n = 0.f;
   const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H;
   if (tid < Tv) {
     d_n = a.dA[ck];
     wt_n = a.w[ck];
   }
+  float x_cur = warp_scan(d_n), wt_cur = wt_n;
+  if (tid < Tv && 1 < H) {
+    d_n = a.dA[ck + 1];
+    wt_n = a.w[ck + 1];
+  }
+  __syncthreads();
+  token_factor(0, x_cur, wt_cur);
+  __syncthreads();
   for (int h = 0; h < H; ++h) {
     const int buf = h & 1;
-    const float d = d_n, wt = wt_n;
-    if (tid < Tv && h + 1 < H) {
-      d_n = a.dA[ck + h + 1];
-      wt_n = a.w[ck + h + 1];
+    // ---- interval 1: warp scans of head h + 1, scaling pass of head h
+    if (h + 1 < H) {
+      x_cur = warp_scan(d_n);
+      wt_cur = wt_n;
+      if (tid < Tv && h + 2 < H) {
+        d_n = a.dA[ck + h + 2];
+        wt_n = a.w[ck + h + 2];
+      }
     }
-    chunk_prefix(d, cs, wsum);
-    if (tid < 128) fv[tid] = mode == 0 ? __expf(cs[127] - cs[tid]) * wt : __expf(cs[tid]);
-    if (tid == 0 && mode == 0) a.atot[((int64_t)b * a.nc + c) * H + h] = __expf(cs[127]);
-    __syncthreads();
     if (wait_warp(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag)) {
       const int row = tid & 127, half = tid >> 7;
-      const float f = fv[row];
+      const float f = fv[buf * 128 + row];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const uint32_t off = buf * BLK + sw128_offset(row, half * 4 + j);
@@ -128,6 +157,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_state_kernel(const __g
     }
     fence_proxy_async();
     __syncthreads();
+    // ---- interval 2: factors of head h + 1, MMA of head h, read-out of head h - 1
     if (tid == 0 && !*abort_flag) {
       if (h + 2 < H) {
         mbar_expect_tx(&bar_x[buf], BLK);
@@ -142,7 +172,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_state_kernel(const __g
         umma_commit(&bar_mma[buf]);
       }
     }
+    if (h + 1 < H) token_factor(h + 1, x_cur, wt_cur);
     if (h > 0) epilogue(h - 1);
+    __syncthreads();
   }
   epilogue(H - 1);
   __syncthreads();
@@ -165,11 +197,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
   uint8_t* sX = sm + 4 * BLK;            // 2 buffers
   uint8_t* sMs = sm + 6 * BLK;           // masked scores [128 t][128 s], 2 blocks
   uint8_t* sS = sm + 8 * BLK;            // entering state [128 n][64 p] bf16, 2 buffers
-  float* cs = reinterpret_cast<float*>(sm + 10 * BLK);
-  float* fs = cs + 128;                  // split decay factors of the columns (chunk_prefix_split)
-  float* fw = fs + 128;
-  float* wsum = fw + 128;
-  float* clk = wsum + 8;                 // [2][OUT_CLK_LD] per-head rows staged one head ahead (see stage_clocks)
+  float* csb = reinterpret_cast<float*>(sm + 10 * BLK);   // [2][cs | fs | fw] x 128: prefix of the steps and split decay
+                                                          // factors, buffer h & 1 (filled during the previous head)
+  float* wsum = csb + 768;
+  float* clk = wsum + 8;                 // [3][OUT_CLK_LD] per-head rows staged two heads ahead (see stage_clocks)
   __shared__ uint64_t bar_map, bar_x[2], bar_cb, bar_y;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -226,28 +257,67 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
   const uint32_t idesc_y = idesc_bf16(128, 64, 0, 1);
   __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(a.y);
 
-  // Per-head rows are staged one head ahead by cp.async into clk[h & 1]: [dA | w | wd] x 128 tokens and the skip
-  // coefficients D[h, 0..63].  No registers are held across the head, so the loads really are in flight during the
-  // previous head.
+  // Per-head rows are staged two heads ahead by cp.async into clk[h % 3]: [dA | w | wd] x 128 tokens and the skip
+  // coefficients D[h, 0..63].  One commit group per head (empty past the last head), so that "all but the newest
+  // group" always means "up to head h + 1".
   const int64_t ckv = ((int64_t)b * a.L + t0 + min(tid, Tv - 1)) * H + h0;   // a mapped address for every thread
   auto stage_clocks = [&](int hh) {
-    float* sc = clk + (hh & 1) * OUT_CLK_LD;
-    if (tid < 128) {
-      const bool ok = tid < Tv;
-      cp_async4z(sc + tid, a.dA + ckv + hh, ok);
-      cp_async4z(sc + 128 + tid, a.w + ckv + hh, ok);
-      cp_async4z(sc + 256 + tid, a.wd + ckv + hh, ok);
-    } else if (tid < 128 + TC_G) {
-      const bool ok = a.Dg != nullptr;
-      cp_async4z(sc + 384 + tid - 128, ok ? a.Dg + (h0 + hh) * TC_G + tid - 128 : a.dA, ok);
+    if (hh < Hl) {
+      float* sc = clk + (hh % 3) * OUT_CLK_LD;
+      if (tid < 128) {
+        const bool ok = tid < Tv;
+        cp_async4z(sc + tid, a.dA + ckv + hh, ok);
+        cp_async4z(sc + 128 + tid, a.w + ckv + hh, ok);
+        cp_async4z(sc + 256 + tid, a.wd + ckv + hh, ok);
+      } else if (tid < 128 + TC_G) {
+        const bool ok = a.Dg != nullptr;
+        cp_async4z(sc + 384 + tid - 128, ok ? a.Dg + (h0 + hh) * TC_G + tid - 128 : a.dA, ok);
+      }
     }
     cp_async_commit();
   };
+  // Two block-wide barriers per head.  The prefix of head h + 1 is formed beside the work of head h: the warp scans in
+  // the interval of the mask pass, cs | fs | fw (csb[(h + 1) & 1]) in the interval of the MMA wait and read-out.
+  float x_n = 0.f, tot_n = 0.f, w_n = 0.f;
+  auto warp_scan = [&](int hh) {           // warps 0..3: inclusive scan of the steps of head hh inside the warp
+    if (warp < 4) {
+      const float* sc = clk + (hh % 3) * OUT_CLK_LD;
+      float x = sc[tid];
+      w_n = sc[128 + tid];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        float y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+      }
+      x_n = x;
+      tot_n = __shfl_sync(0xffffffffu, x, 31);
+      if (lane == 31) wsum[warp] = x;
+    }
+  };
+  auto token_factors = [&](int hh) {       // after the barrier that publishes wsum
+    if (warp < 4) {
+      const float w0 = wsum[0], w1 = wsum[1], w2 = wsum[2];
+      const float off = warp == 0 ? 0.f : (warp == 1 ? w0 : (warp == 2 ? w0 + w1 : (w0 + w1) + w2));
+      float* o = csb + (hh & 1) * 384;
+      const float f = __expf(tot_n - x_n);
+      o[tid] = x_n + off;
+      o[128 + tid] = f;
+      o[256 + tid] = f * w_n;
+    }
+  };
   stage_clocks(0);
+  stage_clocks(1);
+  cp_async_wait_group<1>();
+  warp_scan(0);
+  __syncthreads();
+  token_factors(0);
+  __syncthreads();
   for (int h = 0; h < Hl; ++h) {
     const int buf = h & 1;
-    const float* sc = clk + buf * OUT_CLK_LD;
+    const float* sc = clk + (h % 3) * OUT_CLK_LD;
     const float *wv = sc + 128, *wdv = sc + 256, *dgs = sc + 384;
+    const float *cs = csb + buf * 384, *fw = cs + 256;
+    stage_clocks(h + 2);                   // slot (h + 2) % 3: its readers (head h - 1) finished before the last barrier
     // The inter-chunk part C Sin of this head needs no mask: it runs under the mask pass.  The per-head MMAs and TMA
     // refills are issued by thread 128, whose warp (rows 0..31, slabs 2 and 3) has no mask work.
     bool x_ok = false;
@@ -260,14 +330,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
         for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_Y2, desc_k(ac, ks), desc_mn(bs, ks), idesc_y, ks > 0 ? 1u : 0u);
       }
     }
-    cp_async_wait_all();
-    float d = 0.f, wt = 0.f;
-    if (tid < 128) {
-      d = sc[tid];
-      wt = sc[128 + tid];
-    }
-    if (h + 1 < Hl) stage_clocks(h + 1);   // the other buffer: its readers finished before the previous head's last barrier
-    chunk_prefix_split(d, wt, cs, fs, fw, wsum);   // its barriers also publish the staged rows to every thread
+    cp_async_wait_group<1>();              // this thread's share of the rows of head h + 1
+    if (h + 1 < Hl) warp_scan(h + 1);
     // masked scores: this thread owns row t, column slabs 2*wg and 2*wg+1 (32 columns each)
     if (cb_ok) {
       const float cst = cs[t], wdt_t = wdv[t];
@@ -329,6 +393,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __gri
       for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_Y1, desc_k(am, ks), desc_mn(bx, ks), idesc_y, ks > 0 ? 1u : 0u);
       umma_commit(&bar_y);   // covers the C Sin product issued at the top of the head too
     }
+    if (h + 1 < Hl) token_factors(h + 1);
     if (wait_warp(&bar_y, (uint32_t)(h & 1), abort_flag)) {
       tc_fence_after_sync();
       uint32_t r1[32], r2[32];
@@ -1030,7 +1095,7 @@ static int map_rows(CUtensorMap* m, const void* base, int cols, int64_t token_st
 }
 
 constexpr int SMEM_STATE = 6 * BLK + 2048 + 1024;
-constexpr int SMEM_OUT = 10 * BLK + 5632 + 1024;
+constexpr int SMEM_OUT = 10 * BLK + 9216 + 1024;
 
 // [B*nc*H*128 rows][64 p] bfloat16 view of a state-tile buffer: one [128 x 64] box per (batch, chunk, head)
 static int map_state(CUtensorMap* m, const void* base, const ScanArgs& a) {
