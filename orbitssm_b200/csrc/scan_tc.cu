@@ -480,10 +480,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
   uint8_t* sEX = sm + 7 * BLK;           // e_s * u
   uint8_t* sS = sm + 8 * BLK;            // Sin  bf16 [n][p], 2 buffers
   uint8_t* sdS = sm + 10 * BLK;          // dSo  bf16 [n][p], 2 buffers
-  float* cs = reinterpret_cast<float*>(sm + 12 * BLK);
-  float* fa = cs + 128;                  // a_t
-  float* fe = fa + 128;                  // e_s
-  float* dapart = fe + 128;              // [2][128]
+  float* fab = reinterpret_cast<float*>(sm + 12 * BLK);   // [2][a_t | e_s] x 128, buffer h & 1
+  float* dapart = fab + 512;             // [2][128]
   float* wsum = dapart + 256;            // 8
   float* red = wsum + 8;                 // 8
   __shared__ uint64_t bar_map, bar_x[2], bar_m;
@@ -529,25 +527,52 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
   }
   const uint32_t id_y = idesc_bf16(128, 64, 0, 1), id_acc = idesc_bf16(128, 128, 0, 0);
 
+  // Two block-wide barriers per head.  The prefix of head h + 1 is formed beside the work of head h: its warp scans in
+  // the interval of the scaling pass, its per-token factors (fab[(h + 1) & 1]) in the interval of the MMAs.
+  auto warp_scan = [&](float v) -> float {   // inclusive scan inside the warp; warp totals of warps 0..3 -> wsum
+    float x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      float y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (warp < 4 && lane == 31) wsum[warp] = x;
+    return x;
+  };
+  auto token_factor = [&](int hh, float x, float wt) {   // after the barrier that publishes wsum
+    if (tid < 128) {
+      const float w0 = wsum[0], w1 = wsum[1], w2 = wsum[2], w3 = wsum[3];
+      const float off = warp == 0 ? 0.f : (warp == 1 ? w0 : (warp == 2 ? w0 + w1 : (w0 + w1) + w2));
+      const float tot = ((w0 + w1) + w2) + w3, csv = x + off;
+      fab[(hh & 1) * 256 + tid] = __expf(csv);
+      fab[(hh & 1) * 256 + 128 + tid] = __expf(tot - csv) * wt;
+    }
+  };
   float d_n = 0.f, wt_n = 0.f;
   const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H + h0;
   if (tid < Tv) {
     d_n = a.dA[ck];
     wt_n = a.w[ck];
   }
+  float x_cur = warp_scan(d_n), wt_cur = wt_n;
+  if (tid < Tv && 1 < Hl) {
+    d_n = a.dA[ck + 1];
+    wt_n = a.w[ck + 1];
+  }
+  __syncthreads();
+  token_factor(0, x_cur, wt_cur);
+  __syncthreads();
   for (int h = 0; h < Hl; ++h) {
     const int buf = h & 1;
-    const float d = d_n, wt = wt_n;
-    if (tid < Tv && h + 1 < Hl) {
-      d_n = a.dA[ck + h + 1];
-      wt_n = a.w[ck + h + 1];
+    const float *fa = fab + buf * 256, *fe = fa + 128;
+    if (h + 1 < Hl) {
+      x_cur = warp_scan(d_n);
+      wt_cur = wt_n;
+      if (tid < Tv && h + 2 < Hl) {
+        d_n = a.dA[ck + h + 2];
+        wt_n = a.w[ck + h + 2];
+      }
     }
-    chunk_prefix(d, cs, wsum);
-    if (tid < 128) {
-      fa[tid] = __expf(cs[tid]);
-      fe[tid] = __expf(cs[127] - cs[tid]) * wt;
-    }
-    __syncthreads();
     float part = 0.f;
     if (wait_warp(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag)) {
       const int row = tid & 127, half = tid >> 7;
@@ -588,8 +613,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
       }
     }
     fence_proxy_async();
-    const float datot = cta_sum(part, red);       // ends after a CTA barrier: the scaled tiles are complete
-    if (tid == 0) a.dw[((int64_t)b * a.L + t0) * H + h0 + h] = datot;
+    part = warp_sum(part);
+    if (lane == 0) red[warp] = part;
+    __syncthreads();                       // the scaled tiles, the warp sums and wsum are complete
+    if (h + 1 < Hl) token_factor(h + 1, x_cur, wt_cur);
+    if (tid == 0) {
+      float datot = 0.f;
+#pragma unroll
+      for (int ww = 0; ww < TC_THREADS / 32; ++ww) datot += red[ww];
+      a.dw[((int64_t)b * a.L + t0) * H + h0 + h] = datot;
+    }
     if (tid == 0 && !*abort_flag) {
       bool ok = (h > 0) || wait_or_abort(&bar_map, 0, abort_flag);
       if (ok) {
