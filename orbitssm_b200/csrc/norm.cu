@@ -76,6 +76,21 @@ __global__ void __launch_bounds__(NORM_THREADS) gate_norm_bwd_kernel(
   for (int k = 0; k < NV; ++k)
 #pragma unroll
     for (int i = 0; i < V; ++i) dwacc[k][i] = 0.f;
+  // The rows of this CTA are software-pipelined by one: the loads of the next row are issued before the block-wide sum
+  // of the current one, so they are in flight across its two barriers and the output pass.
+  Vec16<T> ra[NV], rd[NV], rb[NV];
+  auto fetch = [&](int64_t row) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      int c = (k * NORM_THREADS + threadIdx.x) * V;
+      if (c < D) {
+        ra[k].load(y + row * D + c);
+        rd[k].load(dout + row * D + c);
+        if (z != nullptr) rb[k].load(z + row * zrs + c);
+      }
+    }
+  };
+  if (blockIdx.x < M) fetch(blockIdx.x);
   for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
     float yv[NV][V], sz[NV][V], gz[NV][V], u[NV][V];
     const float rstd = w ? rstd_in[row] : 1.f;
@@ -84,12 +99,9 @@ __global__ void __launch_bounds__(NORM_THREADS) gate_norm_bwd_kernel(
     for (int k = 0; k < NV; ++k) {
       int c = (k * NORM_THREADS + threadIdx.x) * V;
       if (c < D) {
-        Vec16<T> a, d;
-        a.load(y + row * D + c);
-        d.load(dout + row * D + c);
+        const Vec16<T> a = ra[k], d = rd[k];
         if (z != nullptr) {
-          Vec16<T> b;
-          b.load(z + row * zrs + c);
+          const Vec16<T> b = rb[k];
 #pragma unroll
           for (int i = 0; i < V; ++i) {
             float zz = b.get(i);
@@ -115,6 +127,7 @@ __global__ void __launch_bounds__(NORM_THREADS) gate_norm_bwd_kernel(
         }
       }
     }
+    if (row + gridDim.x < M) fetch(row + gridDim.x);
     float m = 0.f;
     if (w != nullptr) m = block_sum(dot, red) / (float)D;
 #pragma unroll
