@@ -1,6 +1,7 @@
 """Residual containers around a mixer: `ResidualBlock` (``x + mixer(norm(x))``) and `BlockStack` (blocks, then a final
-RMSNorm), with per-layer State lists (reference: src/orbit_ssm/model.py:51-118 and 150-255).  No kernels here: the
-pre-norms are ATen's fused ``rms_norm``.  Only mixer-only blocks (``d_mlp = 0``) are built.
+RMSNorm), with per-layer State lists (reference: src/orbit_ssm/model.py:51-118 and 150-255).  The pre-norms run on
+this package's gate + RMSNorm kernels with no gate (one kernel forward, one backward plus the weight-gradient column
+sum).  Only mixer-only blocks (``d_mlp = 0``) are built.
 """
 from __future__ import annotations
 
@@ -8,11 +9,13 @@ import math
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
+
+from . import ops
 
 
 class RMSNorm(nn.Module):
-    """``weight * x * rsqrt(mean(x^2) + eps)`` in the input dtype (reference: src/orbit_ssm/layers/norms.py:10-58)."""
+    """``weight * x * rsqrt(mean(x^2) + eps)`` in the input dtype, fp32 accumulation and fp32 weight (reference:
+    src/orbit_ssm/layers/norms.py:10-58, the ``fused=True`` form the backbone norms use)."""
 
     def __init__(self, d, eps=1e-5):
         super().__init__()
@@ -20,7 +23,7 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(d))
 
     def forward(self, x):
-        return F.rms_norm(x, self.weight.shape, self.weight.to(x.dtype), self.eps)
+        return ops.GateNormFn.apply(x, None, self.weight, self.eps)
 
 
 class ResidualBlock(nn.Module):

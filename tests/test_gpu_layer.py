@@ -177,3 +177,38 @@ def test_hm_split_equals_whole_and_is_reproducible():
     assert rel(torch.cat(ys, 1), y_all) < 1e-5
     for k in s_all:
         assert rel(st[k], s_all[k]) < 1e-5, k
+
+
+@pytest.mark.parametrize("io", [torch.float32, torch.bfloat16])
+def test_block_stack_norms_match_aten(io, monkeypatch):
+    """BlockStack (pre-norm residual blocks + final norm) with its norms on this package's kernels against the same
+    stack with ATen's rms_norm (reference: src/orbit_ssm/model.py:51-118, 150-255; layers/norms.py:10-58)."""
+    import torch.nn.functional as F
+    from orbitssm_b200 import BlockStack, mamba2_config, model
+
+    torch.manual_seed(3)
+    cfg = mamba2_config(128, d_state=128, d_head=64)
+    precision = "ieee" if io == torch.float32 else "io"
+    mixers = [SSDMimoSSM(cfg, execution={"precision": precision}) for _ in range(2)]
+    stack = BlockStack.from_mixers(mixers, 128).to(DEV)
+    with torch.no_grad():
+        for b in stack.layers:
+            b.norm.weight.uniform_(0.5, 1.5)
+        stack.norm_f.weight.uniform_(0.5, 1.5)
+    x = torch.randn(2, 200, 128, device=DEV).to(io)
+    dy = torch.randn(2, 200, 128, device=DEV).to(io)
+
+    def run_once():
+        xx = x.clone().requires_grad_(True)
+        stack.zero_grad()
+        y = stack(xx)
+        y.backward(dy)
+        return y, xx.grad, stack.norm_f.weight.grad.clone(), stack.layers[0].norm.weight.grad.clone()
+
+    got = run_once()
+    monkeypatch.setattr(model.RMSNorm, "forward",
+                        lambda self, t: F.rms_norm(t.float(), self.weight.shape, self.weight, self.eps).to(t.dtype))
+    want = run_once()
+    tol = 1e-4 if io == torch.float32 else 3e-2
+    for g, w, what in zip(got, want, ("y", "dx", "d norm_f.weight", "d layers[0].norm.weight")):
+        assert rel(g, w) < tol, (what, rel(g, w))

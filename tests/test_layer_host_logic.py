@@ -270,3 +270,32 @@ def test_hm_step_equals_forward(cpu_hm_kernels):
     assert _rel(torch.cat(ys, 1), y_all) < 1e-5
     for k in s_all:
         assert _rel(st[k], s_all[k]) < 1e-5, k
+
+
+def test_block_stack_wiring(cpu_kernels):
+    """BlockStack = pre-norm residual blocks, then the final norm (reference: src/orbit_ssm/model.py:51-118, 150-255)."""
+    import torch.nn.functional as F
+    from orbitssm_b200 import BlockStack, mamba2_config
+
+    torch.manual_seed(5)
+    cfg = mamba2_config(32, d_state=16, d_head=8)
+    mixers = [SSDMimoSSM(cfg) for _ in range(2)]
+    stack = BlockStack.from_mixers(mixers, 32)
+    with torch.no_grad():
+        for b in stack.layers:
+            b.norm.weight.uniform_(0.5, 1.5)
+        stack.norm_f.weight.uniform_(0.5, 1.5)
+    x = torch.randn(2, 24, 32, requires_grad=True)
+    y, states = stack(x, return_state=True)
+    assert len(states) == 2 and y.shape == x.shape
+    y.square().mean().backward()
+    ref = x.detach().clone().requires_grad_(True)
+    h = ref
+    for b in stack.layers:
+        h = h + b.mixer(F.rms_norm(h, (32,), b.norm.weight, b.norm.eps))
+    yr = F.rms_norm(h, (32,), stack.norm_f.weight, stack.norm_f.eps)
+    assert _rel(y, yr) < 1e-5
+    g_norm = stack.norm_f.weight.grad.clone()
+    stack.zero_grad()
+    yr.square().mean().backward()
+    assert _rel(x.grad, ref.grad) < 1e-4 and _rel(g_norm, stack.norm_f.weight.grad) < 1e-4
