@@ -867,8 +867,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
       alive = __syncthreads_and(ok ? 1 : 0) != 0;
       if (!alive) break;
       stage(it + 1);          // the dM buffer is idle from here to the next kernel head's dM read-out
-      // ================= MMA group 3: every product of the masked tiles
-      if (tid == 0) {
+      // ================= MMA group 3: every product of the masked tiles (issued from warp 4, which has nothing else to do
+      // until these products are complete; warp 0 starts the clock gradients at once)
+      if (tid == 128) {
         tc_fence_after_sync();
         const uint32_t ac = smem_u32(sC), ab = smem_u32(sB), ads = smem_u32(sDSc), ams = smem_u32(sMs);
 #pragma unroll

@@ -50,53 +50,13 @@ __device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volati
   return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag) ? 1 : 0) != 0;
 }
 
-// Inclusive prefix over the 128 values held by threads 0..127 -> cs[0..127]; every thread of the CTA must call.
-__device__ __forceinline__ void chunk_prefix(float v, float* cs, float* wsum) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  float x = v;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    float y = __shfl_up_sync(0xffffffffu, x, o);
-    if (lane >= o) x += y;
-  }
-  if (warp < 4 && lane == 31) wsum[warp] = x;
-  __syncthreads();
-  if (warp < 4) {
-    float off = 0.f;
-    for (int w = 0; w < warp; ++w) off += wsum[w];
-    cs[tid] = x + off;
-  }
-  __syncthreads();
-}
-
-// chunk_prefix, plus the split of the decay exp(cs_t - cs_s) for a column s in an earlier 32-token slab than row t:
+// Inclusive prefix cs of 128 per-token steps, plus the split of the decay exp(cs_t - cs_s) for a column s in an earlier
+// 32-token slab than row t:
 //   exp(cs_t - cs_s) = exp(cs_t - cs_end(slab of s)) * fs[s],   fs[s] = exp(cs_end(slab of s) - cs_s),   fw[s] = fs[s] * w[s]
 // Both factors are <= 1 for non-positive steps, so neither overflows; the row factor costs one exponential per
-// (row, slab) instead of one per element.
-__device__ __forceinline__ void chunk_prefix_split(float v, float w, float* cs, float* fs, float* fw, float* wsum) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  float x = v;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    float y = __shfl_up_sync(0xffffffffu, x, o);
-    if (lane >= o) x += y;
-  }
-  const float tot = __shfl_sync(0xffffffffu, x, 31);
-  if (warp < 4 && lane == 31) wsum[warp] = x;
-  __syncthreads();
-  if (warp < 4) {
-    float off = 0.f;
-    for (int ww = 0; ww < warp; ++ww) off += wsum[ww];
-    cs[tid] = x + off;
-    const float f = __expf(tot - x);
-    fs[tid] = f;
-    fw[tid] = f * w;
-  }
-  __syncthreads();
-}
-
-// chunk_prefix_split run by warps 4..7 alone (thread 128 + i owns token i), synchronised on named barrier 2, so that
-// it can run beside work of warps 0..3.  `wsum` >= 4 floats, not shared with the other variants while both may run.
+// (row, slab) instead of one per element.  Run by warps 4..7 alone (thread 128 + i owns token i), synchronised on named
+// barrier 2, so that it can run beside work of warps 0..3.  `wsum` >= 4 floats, not shared with the other variants
+// while both may run.
 __device__ __forceinline__ void chunk_prefix_split_high128(float v, float w, float* cs, float* fs, float* fw, float* wsum) {
   const int tok = threadIdx.x - 128, lane = tok & 31, warp = tok >> 5;
   float x = v;
@@ -163,19 +123,6 @@ __device__ __forceinline__ uint64_t desc_k(uint32_t base, int ks) {
 }
 // MN-major descriptor of k-step `ks` (16 rows); 64-wide MN blocks are BLK bytes apart
 __device__ __forceinline__ uint64_t desc_mn(uint32_t base, int ks) { return smem_desc_sw128(base + (uint32_t)ks * 2048u, BLK, 1024u); }
-
-// Deterministic CTA-wide sum of one float per thread (fixed tree); result returned to every thread.  `red` >= 8 floats.
-__device__ __forceinline__ float cta_sum(float v, float* red) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float t = 0.f;
-#pragma unroll
-  for (int w = 0; w < TC_THREADS / 32; ++w) t += red[w];
-  return t;
-}
 
 // Column sums over the 32 rows held by a warp: in: v[i] = value of (row = lane, column i); out: v[0] = sum over the
 // warp's rows of column `lane` (butterfly reduce-scatter, 31 shuffles, fixed order).
