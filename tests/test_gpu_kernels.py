@@ -255,6 +255,33 @@ def test_scan_tc_backward(case):
         assert not bad3, ("head split", bad3)
 
 
+@pytest.mark.parametrize("scale,H", [(1.0, 8), (30.0, 2), (300.0, 3)])
+def test_scan_tc_strong_decay_many_heads(scale, H):
+    """Rank-1 tensor-core tiles with steps scaled up (per-chunk decay sums of several hundred: the split decay factors
+    exp(cs_t - cs_end) * exp(cs_end - cs_s) underflow to zero where the exact product does, never to inf/nan) and with
+    more heads than the staging rings are deep; forward and backward against the fp64 restatement, head ranges split
+    over 1, 2 and H CTAs."""
+    B, L = 2, 300
+    c = scan_case(B, L, H, 1, 1, 64, 128, torch.bfloat16, False, False, False, True, True, True, seed=21)
+    c["dA"] = c["dA"] * scale
+    geo = c["geo"]
+    args = (c["u"], c["Bhat"], None, c["Chat"], None, None, None, None, c["dA"], c["w"],
+            c["w"] if c["euler"] else c["wd"], c["Dg"])
+    y, S_fin, Sin, atot = ops.scan_fwd(geo, 128, _lib.PRECISION_IO, *args, c["S0"])
+    ops.check_device_status()
+    ry, rS, _, _ = R.scan_fwd(geo, 128, 0, *args, c["S0"])
+    assert torch.isfinite(y.float()).all() and torch.isfinite(S_fin).all()
+    assert rel(S_fin, rS) < 2e-3 and rel(y, ry) < 1e-2, (rel(S_fin, rS), rel(y, ry))
+    rg = R.scan_bwd(geo, 128, 0, *args, None, None, c["dy"], c["dS_fin"], c["euler"], True, S0=c["S0"])
+    for k in sorted({1, 2 if H % 2 == 0 else 1, H}):
+        g = ops.scan_bwd(geo, 128, _lib.PRECISION_IO, *args, Sin, atot, c["dy"], c["dS_fin"], c["euler"], True, hsplit=k)
+        ops.check_device_status()
+        for name, v in rg.items():
+            if v is not None:
+                assert torch.isfinite(g[name].float()).all(), (k, name)
+                assert rel(g[name], v) < 2e-2, ("hsplit", k, name, rel(g[name], v))
+
+
 # ---------------------------------------------------------------------------------------------------- scan, tcgen05 rank 4
 MIMO_CASES = [
     # B, L, H, gates, biases, chi, skip, trap, s0
