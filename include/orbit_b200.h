@@ -78,7 +78,10 @@ int orbit_gate_norm_bwd(const void* y, const void* z, int64_t z_row_stride, cons
  * library until the process exits) instead of a caller workspace.  Arguments and results are those of
  * orbit_gate_norm_bwd without `workspace`.
  *   Limit: min(M, 592) * D <= 592 * 4096 floats (any M when D <= 4096); larger problems are refused with
- *          ORBIT_ERR_UNSUPPORTED and a message naming the sizes.
+ *          ORBIT_ERR_UNSUPPORTED and a message naming the sizes.  A gate-only call (w == NULL) has no weight gradient,
+ *          uses no scratch and is served at any size.
+ *   The array is per device and is looked up for the CURRENT device: the buffers must live on the current device
+ *   (checked on `dy`; ORBIT_ERR_BAD_ARG otherwise).
  *   The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
  *   current) and remembers it; make that first call before any stream capture begins.
  *   It calls no cudaMalloc, cudaFree or other allocating routine.
@@ -291,6 +294,12 @@ int orbit_hm_scan_bwd(const orbit_hm_args* a, int dtype, void* stream);
  * K, N in {64, 128}.  *status (device int) becomes nonzero if a bounded device wait gave up.  No counterpart in the
  * reference (its kernels are Triton; there is no sm_100 path there). */
 int orbit_selftest_umma(const void* A, const void* B, float* D, int mode, int K, int N, int* status, void* stream);
+
+/* The wind-down of a bounded device-side wait, exercised without a fault: one CTA allocates tensor memory and waits at
+ * most `polls` (1..4096) polls on a barrier that nothing arrives on; the wait gives up, *status (device int) is set to
+ * 1, tensor memory is freed and the kernel returns.  A caller that reads *status == 1 maps it to
+ * ORBIT_ERR_DEVICE_TIMEOUT.  No counterpart in the reference. */
+int orbit_selftest_wait_timeout(int* status, int polls, void* stream);
 
 #ifdef __cplusplus
 }

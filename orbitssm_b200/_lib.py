@@ -16,6 +16,8 @@ PRECISION_IEEE, PRECISION_IO = 0, 1
 PHASE_CHUNK_STATE, PHASE_STATE_PASS, PHASE_CHUNK_OUT, PHASE_CHUNK_DSTATE, PHASE_STATE_PASS_BWD, PHASE_CHUNK_GRADS = range(6)
 PHASE_STATE_PASS_DRY, PHASE_STATE_PASS_BWD_DRY = 6, 7
 
+ERR_DEVICE_TIMEOUT = 5     # ORBIT_ERR_DEVICE_TIMEOUT: a bounded device-side wait gave up (read from the status word)
+
 _STATUS_EXC = {1: ValueError, 2: NotImplementedError, 3: RuntimeError, 4: ValueError, 5: RuntimeError}
 
 
@@ -91,6 +93,7 @@ SIGNATURES = {
     "orbit_hm_scan_fwd": (_I, [C.POINTER(HmArgs), _I, _P]),
     "orbit_hm_scan_bwd": (_I, [C.POINTER(HmArgs), _I, _P]),
     "orbit_selftest_umma": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
+    "orbit_selftest_wait_timeout": (_I, [_P, _I, _P]),
 }
 
 _lib = None

@@ -381,11 +381,6 @@ extern "C" int orbit_gate_norm_bwd_noalloc(const void* y, const void* z, int64_t
   ORBIT_REQUIRE(w == nullptr || (rstd != nullptr && dw != nullptr), ERR_BAD_ARG,
                 "orbit_gate_norm_bwd_noalloc: rstd and dw are required with a norm");
   ORBIT_REQUIRE(M >= 0 && D > 0, ERR_BAD_ARG, "orbit_gate_norm_bwd_noalloc: bad sizes M=%lld D=%d", (long long)M, D);
-  const int64_t need = (int64_t)norm_bwd_slots(M) * D;
-  ORBIT_REQUIRE(need <= NORM_NOALLOC_FLOATS, ERR_UNSUPPORTED,
-                "orbit_gate_norm_bwd_noalloc: min(M, 592) * D = %lld floats of scratch exceed the built-in %lld (M=%lld, D=%d); "
-                "use orbit_gate_norm_bwd with a caller workspace", (long long)need, (long long)NORM_NOALLOC_FLOATS,
-                (long long)M, D);
   cudaStream_t st = (cudaStream_t)stream;
   if (M == 0) {
     if (dw) ORBIT_CHECK_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * D, st));
@@ -393,6 +388,21 @@ extern "C" int orbit_gate_norm_bwd_noalloc(const void* y, const void* z, int64_t
   }
   float* part = nullptr;
   if (w != nullptr) {
+    // Only the weight gradient needs scratch: a gate-only call (w == NULL) of any size is served.
+    const int64_t need = (int64_t)norm_bwd_slots(M) * D;
+    ORBIT_REQUIRE(need <= NORM_NOALLOC_FLOATS, ERR_UNSUPPORTED,
+                  "orbit_gate_norm_bwd_noalloc: min(M, 592) * D = %lld floats of scratch exceed the built-in %lld (M=%lld, D=%d); "
+                  "use orbit_gate_norm_bwd with a caller workspace", (long long)need, (long long)NORM_NOALLOC_FLOATS,
+                  (long long)M, D);
+    // The built-in array is per device and its address is looked up for the CURRENT device: the buffers must live there
+    // too, or the kernel would be handed another GPU's scratch.
+    int dev = -1;
+    ORBIT_CHECK_CUDA(cudaGetDevice(&dev));
+    cudaPointerAttributes attr;
+    ORBIT_CHECK_CUDA(cudaPointerGetAttributes(&attr, dy));
+    ORBIT_REQUIRE(attr.type != cudaMemoryTypeDevice || attr.device == dev, ERR_BAD_ARG,
+                  "orbit_gate_norm_bwd_noalloc: dy lives on device %d but the current device is %d; make the buffers' device "
+                  "current before the call", attr.device, dev);
     int rc = norm_noalloc_scratch(&part);
     if (rc != OK) return rc;
     // nothing in the scratch has to start at zero: each CTA overwrites its whole row of partial sums before the

@@ -128,9 +128,41 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
   if (warp == 0) tmem_dealloc(tbase, 128);
 }
 
+// The wind-down every tensor-core kernel of this library performs when a bounded wait runs out, by itself: the CTA
+// holds TMEM and waits (at most `polls` polls) on an mbarrier that nothing arrives on; the wait gives up, the status
+// word is set, TMEM is freed and the kernel returns normally.
+__global__ void __launch_bounds__(128) wait_timeout_selftest_kernel(int* __restrict__ status, uint32_t polls) {
+  using namespace tc;
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 32);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_slot;
+  const bool done = mbar_wait(&bar, 0, polls);
+  if (!done && tid == 0) atomicExch(status, 1);
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 32);
+}
+
 }  // namespace orbit
 
 using namespace orbit;
+
+extern "C" int orbit_selftest_wait_timeout(int* status, int polls, void* stream) {
+  ORBIT_REQUIRE(status != nullptr, ERR_BAD_ARG, "orbit_selftest_wait_timeout: null status pointer");
+  ORBIT_REQUIRE(polls >= 1 && polls <= 4096, ERR_UNSUPPORTED, "orbit_selftest_wait_timeout: polls must be in [1, 4096], got %d", polls);
+  wait_timeout_selftest_kernel<<<1, 128, 0, (cudaStream_t)stream>>>(status, (uint32_t)polls);
+  ORBIT_CHECK_LAUNCH("wait_timeout_selftest_kernel");
+  return OK;
+}
 
 extern "C" int orbit_selftest_umma(const void* A, const void* B, float* D, int mode, int K, int N, int* status,
                                    void* stream) {

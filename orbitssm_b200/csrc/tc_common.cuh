@@ -28,9 +28,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Returns true when the phase with the given parity completed, false when the poll limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = WAIT_LIMIT) {
   uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"

@@ -11,6 +11,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
+from .config import as_execution
 
 
 class RMSNorm(nn.Module):
@@ -47,6 +48,14 @@ class ResidualBlock(nn.Module):
         y = x + y
         return (y, state) if return_state else y
 
+    def step(self, x_t, state=None):
+        """One token through the block: ``x_t [B, d_model]`` -> ``(x_t + mixer.step(norm(x_t)), State)`` (reference:
+        src/orbit_ssm/model.py:110-115).  A missing `state` starts from zero carries."""
+        if state is None:
+            state = self.init_state(x_t.shape[0], device=x_t.device)
+        y_t, state = self.mixer.step(self.norm(x_t), state)
+        return x_t + y_t, state
+
     def init_state(self, batch_size, **kw):
         return self.mixer.init_state(batch_size, **kw)
 
@@ -78,13 +87,24 @@ class BlockStack(nn.Module):
 
     def set_execution(self, execution):
         for m in self.ssm_layers:           # validate every target before changing any
-            m._check_execution(__import__("orbitssm_b200.config", fromlist=["as_execution"]).as_execution(execution))
+            m._check_execution(as_execution(execution))
         for m in self.ssm_layers:
             m.set_execution(execution)
         return self
 
     def init_state(self, batch_size, **kw):
         return [b.init_state(batch_size, **kw) for b in self.layers]
+
+    def step(self, x_t, state=None):
+        """One token through every block and the final norm: ``x_t [B, d_model]`` -> ``(y_t, [State per layer])``."""
+        states = list(state) if state is not None else [None] * len(self.layers)
+        if len(states) != len(self.layers):
+            raise ValueError(f"state must contain exactly {len(self.layers)} layer states")
+        out = []
+        for b, s in zip(self.layers, states):
+            x_t, s = b.step(x_t, s)
+            out.append(s)
+        return self.norm_f(x_t), out
 
     def forward(self, x, state=None, return_state=False):
         if state is None and not return_state:

@@ -9,6 +9,7 @@ A CPU tensor at any of these entries is refused by name (reference: src/orbit_ss
 from __future__ import annotations
 
 import ctypes as C
+import functools
 from dataclasses import dataclass
 
 import torch
@@ -83,6 +84,47 @@ def _f32(t):
 
 
 # ----------------------------------------------------------------------------------------------------
+#  first-order only: the kernels' backward passes record no autograd graph
+# ----------------------------------------------------------------------------------------------------
+class _SecondOrderTrap(torch.autograd.Function):
+    """Identity on a gradient a kernel produced; differentiating through it raises."""
+
+    @staticmethod
+    def forward(ctx, who, g, anchor):
+        ctx.who = who
+        return g.view_as(g)
+
+    @staticmethod
+    def backward(ctx, *_):
+        raise RuntimeError(
+            f"{ctx.who}: second-order gradients (create_graph=True, then differentiating the result) are not served: the "
+            "backward of this operator is a CUDA kernel that records no autograd graph, so a second derivative would "
+            "silently lack the kernel's part.  The reference's backend='torch' route is differentiable to any order.")
+
+
+def first_order_only(who):
+    """Decorator for an `autograd.Function.backward` that runs kernels.  With ``create_graph=True`` autograd calls the
+    backward in grad mode; the kernels then run under ``no_grad`` and each gradient they return is tied to a node whose
+    own backward raises, so a later attempt to differentiate it fails by name instead of returning a wrong number
+    (reference behaviour: src/orbit_ssm/kernels/autograd_guard.py).  In an ordinary backward this costs one test."""
+    def deco(bwd):
+        @functools.wraps(bwd)
+        def guarded(ctx, *grads):
+            if not torch.is_grad_enabled():
+                return bwd(ctx, *grads)
+            with torch.no_grad():
+                out = bwd(ctx, *grads)
+            ref = next((g for g in grads if torch.is_tensor(g)), None)
+            anchor = torch.zeros((), device=None if ref is None else ref.device, requires_grad=True)
+
+            def tie(o):
+                return _SecondOrderTrap.apply(who, o, anchor) if (torch.is_tensor(o) and o.is_floating_point()) else o
+            return tuple(tie(o) for o in out) if isinstance(out, tuple) else tie(out)
+        return guarded
+    return deco
+
+
+# ----------------------------------------------------------------------------------------------------
 #  fused projection output -> column views
 # ----------------------------------------------------------------------------------------------------
 class GradArena:
@@ -132,6 +174,7 @@ class SplitColumnsFn(torch.autograd.Function):
         return tuple(outs)
 
     @staticmethod
+    @first_order_only("SplitColumnsFn")
     def backward(ctx, *grads):
         ref = next(g for g in grads if g is not None)
         arena = ctx.arena
@@ -218,6 +261,7 @@ class CausalConvFn(torch.autograd.Function):
         return y
 
     @staticmethod
+    @first_order_only("causal conv1d")
     def backward(ctx, dy):
         x, w32, b32, win32 = ctx.saved_tensors
         wshape, wdt, bdt, windt = ctx.meta
@@ -297,6 +341,7 @@ class GateNormFn(torch.autograd.Function):
         return out.reshape(shp)
 
     @staticmethod
+    @first_order_only("gate + RMSNorm")
     def backward(ctx, dout):
         y2, z2, w32, rstd = ctx.saved_tensors
         shp, wdt = ctx.meta
@@ -442,6 +487,7 @@ class HaloFn(torch.autograd.Function):
         return win
 
     @staticmethod
+    @first_order_only("context-parallel conv halo")
     def backward(ctx, dwin):
         cp, W = ctx.cp, ctx.W
         dist = cp.dist
@@ -467,6 +513,8 @@ def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     _require_cuda("ssd_scan_fwd", u, Bhat, Chat, dA)
     B, L = u.shape[:2]
     H, R, O, G, N = geo.H, geo.R, geo.O, geo.G, geo.N
+    if T <= 0:
+        raise NotImplementedError(f"ssd_scan: no chunk length fits this geometry (R={R} O={O} G={G} N={N}) in shared memory")
     nc = max(1, -(-L // T))
     dev = u.device
     a = _lib.ScanArgs()
@@ -518,7 +566,8 @@ def check_device_status(device=None):
     for key, t in _STATUS.items():
         if int(t.item()) != 0:
             t.zero_()
-            raise RuntimeError(f"orbit_b200: a bounded device-side wait gave up on {key} (status {_lib.load() and 5})")
+            raise RuntimeError(f"orbit_b200: a bounded device-side wait gave up on {key}: the outputs of the affected launches "
+                               f"are incomplete (ORBIT_ERR_DEVICE_TIMEOUT, status {_lib.ERR_DEVICE_TIMEOUT})")
 
 
 def _fill_common(a, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg):
@@ -651,6 +700,7 @@ class SSDScanFn(torch.autograd.Function):
         return y, S_fin
 
     @staticmethod
+    @first_order_only("SSD-MIMO scan")
     def backward(ctx, dy, dS_fin):
         u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, Sin, atot, Sin16 = ctx.saved_tensors
         if Sin16 is not None:
@@ -728,6 +778,7 @@ class TokenMapFn(torch.autograd.Function):
         return out
 
     @staticmethod
+    @first_order_only("token map tail")
     def backward(ctx, dout):
         src, w32, rstd = ctx.saved_tensors
         X, N, wdt, bdt, slot = ctx.meta
@@ -833,6 +884,7 @@ class TokenClockFn(torch.autograd.Function):
             (o["lag0"] if o["lag0"] is not None else empty)
 
     @staticmethod
+    @first_order_only("token clock tail")
     def backward(ctx, ddA, dw, dwd, dchi, dlag0):
         dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix = ctx.saved_tensors
         a_act, a_per_sibling, H, R, slots = ctx.meta
@@ -976,6 +1028,7 @@ class HMScanFn(torch.autograd.Function):
         return y, hN, thN, wl
 
     @staticmethod
+    @first_order_only("HybridMamba scan")
     def backward(ctx, dy, dhN, dthN, dwl):
         *ins, hck, thck = ctx.saved_tensors
         x, delta, A_log, Bh, Ch, bb, bc, feat, thh, lam, D, h0, wp, th0 = ins

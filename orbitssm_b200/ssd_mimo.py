@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import contextlib
 import math
+import warnings
 
 import torch
 import torch.nn as nn
@@ -42,6 +43,26 @@ def _bc_bias_init(shape, mode, R, N):
     n = torch.arange(N).float()[None, :]
     dct = torch.cos(math.pi * k * (n + 0.5) / N)
     return base + (r_off[:, None] * dct)[None, :, :, None]
+
+
+class NonTensorCoreRouteWarning(UserWarning):
+    """A bf16 ``precision="io"`` layer ran its scan on the fp32 kernels because its geometry is outside the tcgen05
+    tile envelopes (the reason is in the message and in ``last_route()``)."""
+
+
+_WARNED_ROUTES = set()
+
+
+def _warn_fp32_route(reason):
+    """No silent demotion (reference rule: src/orbit_ssm/layers/routes.py:33-48): say once per reason that a layer asked
+    for the tensor-core precision and got the fp32 kernels, which are one to two orders of magnitude slower."""
+    if reason in _WARNED_ROUTES:
+        return
+    _WARNED_ROUTES.add(reason)
+    warnings.warn(f"SSDMimoSSM: precision='io' with bf16 activations asks for the tcgen05 scan kernels, but {reason}; the scan "
+                  "runs on the fp32 kernels instead (much slower).  Adapt the config to a tensor-core envelope "
+                  "(R = O = 1, N = 128, G = 64 with head-shared maps; or R = O = 4, N = 128, G = 16), or set "
+                  "precision='ieee' to ask for the fp32 kernels.", NonTensorCoreRouteWarning, stacklevel=4)
 
 
 class _BCConv(nn.Module):
@@ -414,10 +435,17 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
             if T > 0:
                 self._route_note = "tcgen05"
                 return _lib.PRECISION_IO, T
-            self._route_note = "fp32 (geometry outside the tensor-core tiles)"
+            why = (f"geometry R={geo.R} O={geo.O} G={geo.G} N={geo.N} is outside the tensor-core tiles" if (shared_maps or not rank1)
+                   else "the rank-1 tiles serve head-shared maps only (no gates, per-head biases or sibling mix)")
+            self._route_note = f"fp32 ({why})"
+            _warn_fp32_route(why)
         else:
             self._route_note = "fp32"
         T = ops.pick_chunk(geo, _lib.PRECISION_IEEE, needs_grad, limit)
+        if T <= 0:
+            raise NotImplementedError(
+                f"SSDMimoSSM: the fp32 scan kernels cannot hold one token of this geometry in shared memory "
+                f"(R={geo.R} O={geo.O} G={geo.G} N={geo.N}); reduce d_state or the head width")
         return _lib.PRECISION_IEEE, T
 
     def _last_write(self, u, law, Bsz):

@@ -60,3 +60,20 @@ def test_sizes_beyond_the_built_in_scratch_are_refused():
     y, z, w, rstd, dout = _case(600, 8192, torch.bfloat16, 2)
     with pytest.raises(NotImplementedError, match="exceed the built-in"):
         _noalloc(y, z, w, rstd, dout)
+
+
+def test_gate_only_call_needs_no_scratch_and_is_served_at_any_size():
+    # w == NULL: there is no weight gradient, hence no partial sums; a size that a norm would be refused at passes
+    M, D = 600, 8192
+    g = torch.Generator().manual_seed(3)
+    y = torch.randn(M, D, generator=g).to(torch.bfloat16).to(DEV)
+    z = torch.randn(M, D, generator=g).to(torch.bfloat16).to(DEV)
+    dout = torch.randn(M, D, generator=g).to(torch.bfloat16).to(DEV)
+    want_dy, want_dz, _ = ops.gate_norm_bwd(y, z, None, None, dout)
+    dy, dz = torch.empty_like(y), torch.empty_like(y)
+    lib = _lib.load()
+    st = lib.orbit_gate_norm_bwd_noalloc(_p(y), _p(z), z.stride(0), None, None, _p(dout), _p(dy), _p(dz), D, None, M, D,
+                                         _lib.BF16, C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(st, "orbit_gate_norm_bwd_noalloc")
+    torch.cuda.synchronize()
+    assert torch.equal(dy, want_dy) and torch.equal(dz, want_dz)
