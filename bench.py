@@ -4,17 +4,19 @@
 
 One "step" = y = layer(x); y.backward(dy) on one batch of synthetic input (x ~ N(0,1), fixed random dy; bf16
 activations over fp32 parameters).  Workloads (BASELINE.json `configs`):
-  cfg5a (default) BASELINE config 5a: 4-block BlockStack of the d_model-2048 SISO layer, batch-sharded, x [8, 4096, 2048]
-        per GPU: the d2048 bf16 configuration the metric is quoted on "at 1/2/4/8 B200" (weak scaling, no collective)
-  cfg5b BASELINE config 5b: one d_model-2048 layer, B = 1, L = 262144 split over the GPUs (context parallel, strong scaling)
+  cfg5a (default) BASELINE config 5a: 4-block BlockStack of the d_model-2048 SISO layer, global batch 64 x 4096 tokens split
+        over the GPUs by batch rows (64 / N rows per GPU: strong scaling, no collective on the data path): the d2048 bf16
+        configuration the metric is quoted on "at 1/2/4/8 B200"
+  cfg5b BASELINE config 5b: one d_model-2048 layer, B = 1, L = 262144 split over the GPUs (context parallel, strong
+        scaling); with N > 1 the default run also measures it for a few steps under "other_workloads"
   cfg3  SSD-MIMO rank-4 layer, d_model 2048, x [4, 4096, 2048] (rank-4 tcgen05 tiles); at N = 1 the default run also
-        measures it briefly and reports it under "other_workloads"
+        measures it (same steps and warm-up) and reports it, with its own roofline block, under "other_workloads"
   cfg4  HybridMamba layer (coordinate-decay rows, half of them rotating pairs), d_model 1024, x [8, 2048, 1024]; also
         reported under "other_workloads" by the default run
   cfg2  Mamba-2 preset SISO layer, d_model 1024, x [8, 2048, 1024]
   cfg5  one layer of cfg5a at x [4, 4096, 2048]
-With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same per-GPU batch on its own shard of the
-batch: no collective on the data path, weak scaling.  Prints ONE JSON line on rank 0.
+With N > 1 (launched by torchrun, one rank per GPU) every rank runs its own rows of the global batch; the ranks meet
+only at the barriers around the timed region.  Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
 
@@ -44,11 +46,11 @@ WORKLOADS = {
     "cfg4": dict(B=8, L=2048, d_model=1024, kind="hm", chunk_acct=32,
                  desc="HybridMamba layer (H=32, P=64, N=64: 32 real rows + 16 rotating pairs, coord_static, trapezoid, gated "
                       "RMSNorm), d_model 1024, x [8,2048,1024]"),
-    # BASELINE config 5: (a) a 4-block BlockStack of the d2048 SISO layer, batch-sharded, 8 rows per GPU (B = 64 at
-    # 8 GPUs); (b) one layer, B = 1, L = 262144, context-parallel over the GPUs (strong scaling)
-    "cfg5a": dict(B=8, L=4096, d_model=2048, kind="m2", chunk_acct=64, blocks=4,
+    # BASELINE config 5: (a) a 4-block BlockStack of the d2048 SISO layer, global batch 64 split over the GPUs by rows;
+    # (b) one layer, B = 1, L = 262144, context-parallel over the GPUs.  Both strong scaling.
+    "cfg5a": dict(B=64, L=4096, d_model=2048, kind="m2", chunk_acct=64, blocks=4, split_batch=True,
                   desc="4-block BlockStack of the SSD-MIMO SISO Mamba-2 preset layer (H=64, P=64, N=128), d_model 2048, "
-                       "x [8,4096,2048] per GPU"),
+                       "global x [64,4096,2048] split over the GPUs by batch rows"),
     "cfg5b": dict(B=1, L=262144, d_model=2048, kind="m2", chunk_acct=64, cp=True,
                   desc="one SSD-MIMO SISO Mamba-2 preset layer, d_model 2048, B=1, L=262144 split over the GPUs "
                        "(context parallel: chunk state all-gathered over NVLink)"),
@@ -64,8 +66,8 @@ WORKLOADS = {
 
 
 # DRAM bytes per token (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the profiling cases cfg5s /
-# cfg3s / cfg4s, divided by their token counts; profiles/scan_dram_traffic.md).  Traffic grows in proportion to the tokens
-# a launch processes, so `roofline.traffic` of a full-size launch is this figure times its tokens.
+# cfg3s / cfg4s, divided by their token counts).  Traffic grows in proportion to the tokens a launch processes, so
+# `roofline.traffic` of a full-size launch is this figure times its tokens.
 DRAM_BYTES_PER_TOKEN = {
     "m2": {"scan_chunk_grads": 68451.0, "scan_chunk_out": 23852.0, "scan_chunk_state": 22452.0},
     "mimo4": {"scan_chunk_grads": 416550.0},
@@ -219,76 +221,110 @@ def cpu_step_time(wl, sample_B, sample_L, steps, warmup):
 
 
 def run_reference(args, wl, name):
+    """The reference arm: the CPU route of the layer (the oracle port) on all host threads, rank 0 only."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the other ranks of this arm exit at once, so rank 0 takes the host
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
     sample_B, sample_L = 1, 256 if wl["kind"] == "m2" else 128
     t = cpu_step_time(wl, sample_B, sample_L, max(1, min(args.steps, 5)), max(1, min(args.warmup, 1)))
     tok = sample_B * sample_L / t
-    cores = torch.get_num_threads()
     sample = f"x [{sample_B},{sample_L},{wl['d_model']}] fp32 of the same layer (tokens/s is linear in tokens), median step"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": tok, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
+        "scaling": "strong" if (wl.get("cp") or wl.get("split_batch")) else "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic", "config": {"workload": name + ": " + wl["desc"]},
-        "cpu_baseline": {"value": tok, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample,
+        "cpu_baseline": {"value": tok, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample,
                          "host_cpus": os.cpu_count()},
         "e2e": {"value": tok, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
-
-
-def side_measure(wl, dev, steps=2, warmup=1):
-    """A short device-timed measurement of another workload (same step definition), reported beside the headline."""
-    torch.manual_seed(0)
-    layer = make_mixer(make_config(wl), execution={"precision": "io"})
-    init_params(layer)
-    layer = layer.to(dev)
-    x = torch.randn(wl["B"], wl["L"], wl["d_model"], device=dev).to(torch.bfloat16).requires_grad_(True)
-    dy = torch.randn(wl["B"], wl["L"], wl["d_model"], device=dev).to(torch.bfloat16)
-    ms = []
-    for i in range(warmup + steps):
-        x.grad = None
-        for p in layer.parameters():
-            p.grad = None
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        layer(x).backward(dy)
-        e1.record()
-        torch.cuda.synchronize()
-        if i >= warmup:
-            ms.append(e0.elapsed_time(e1))
-    t = statistics.mean(ms)
-    return {"workload": wl["desc"], "value": wl["B"] * wl["L"] / (t * 1e-3), "unit": "tokens/s", "ms_per_step": t,
-            "route": layer.last_route(), "steps": steps, "warmup": warmup}
 
 
 # ----------------------------------------------------------------------------------------------------
 #  GPU arm
 # ----------------------------------------------------------------------------------------------------
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="cfg5a", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    args = ap.parse_args()
-    wl = WORKLOADS[args.workload]
-    if args.impl == "reference":
-        return run_reference(args, wl, args.workload)
+class Env:
+    """Rank, world and device of this process (one process per GPU)."""
 
+    def __init__(self):
+        import torch.distributed as dist
+        self.dist = dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            # NCCL's own log (communicator sizes, transports) goes to stderr unless the caller chose otherwise: stdout
+            # carries the one JSON line
+            if "NCCL_DEBUG" not in os.environ:
+                os.environ["NCCL_DEBUG"] = "INFO"
+                os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
+                os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+            dist.init_process_group("nccl", device_id=self.dev)
+
+    def sync(self):
+        torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(self, values):
+        t = torch.tensor(values, device=self.dev, dtype=torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(v) for v in t]
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+def roofline_block(wl, spec, route, B, L, kern_ms, pk):
+    """`roofline` of the dominant kernel of one step over x [B, L, .] from the CUDA-event times per kernel group."""
+    if wl["kind"] == "hm":
+        # the coordinate scan has no contraction: it is bound by exp (MUFU) and FP32 issue; HBM is the nearest roofline
+        # the contract names.  Algorithmic bytes = compulsory IO of the launch: drive in, output (or its gradient) in/out,
+        # maps and clocks (and their gradients) once; checkpoints and partial-sum buffers are not counted.
+        es, D_in, Nn, Hh = 2, spec.d_inner, spec.N, spec.H
+        maps = B * L * (2 * Nn + spec.K + 2 * Hh) * 4
+        byts = {"hm_scan_fwd": B * L * D_in * es * 2 + maps, "hm_scan_bwd": B * L * D_in * es * 3 + 2 * maps}
+        dom = max(byts, key=lambda k: kern_ms.get(k, 0.0))
+        ach = byts[dom] / (kern_ms[dom] * 1e-3) / 1e9
+        roofline = dict(bound="hbm", kernel=dom, achieved=ach, peak=pk["hbm_gbs"], unit="GB/s", frac=ach / pk["hbm_gbs"],
+                        traffic=None, peak_source=pk["source"] + " (copy)", ms_per_launch=kern_ms[dom],
+                        note="issue-bound (one exp + ~10 FP32 ops per state element per token), not HBM-bound",
+                        state_updates_per_s=B * L * Hh * spec.P * Nn / (kern_ms[dom] * 1e-3), route=route)
+    else:
+        fl = scan_flops(spec, B, L, wl["chunk_acct"])
+        names = [k for k in kern_ms if k in fl]
+        if not names:
+            return None
+        dom = max(names, key=lambda k: kern_ms[k])
+        ach = fl[dom] / (kern_ms[dom] * 1e-3) / 1e12
+        roofline = dict(bound="tensor", kernel=dom, achieved=ach, peak=pk["tflops"], unit="TFLOP/s", frac=ach / pk["tflops"],
+                        traffic=None, peak_source=pk["source"] + " (sustained bf16 GEMM)", ms_per_launch=kern_ms[dom], route=route)
+        # the whole scan (all phases of both directions) against the same peak: 3 x forward flops
+        scan_ms = sum(v for k, v in kern_ms.items() if k.startswith("scan_"))
+        if scan_ms > 0:
+            roofline["whole_scan"] = dict(ms=scan_ms, achieved=3 * fl["fwd"] / (scan_ms * 1e-3) / 1e12,
+                                          frac=3 * fl["fwd"] / (scan_ms * 1e-3) / 1e12 / pk["tflops"])
+    per_tok = DRAM_BYTES_PER_TOKEN.get(wl["kind"], {}).get(roofline["kernel"])
+    if per_tok is not None:
+        roofline["traffic"] = per_tok * B * L
+        roofline["traffic_source"] = "ncu capture of the profiling case, scaled by tokens per launch"
+    return roofline
+
+
+def measure(env, wl, name, steps, warmup, e2e_regions=3, cp_world=None):
+    """Time `steps` fwd+bwd steps of workload `wl` on this rank's share after `warmup` untimed ones (CUDA events around
+    every step on the compute stream, L2 flushed between steps), then `e2e_regions` end-to-end regions of the same
+    steps with host buffers.  `cp_world`: ranks the sequence is split over (context parallel), None = env.world for a
+    context-parallel workload.  Returns a dict on every rank (times are max over ranks)."""
     from orbitssm_b200 import ops
-    import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        os.environ["NCCL_DEBUG"] = "WARN"          # keep NCCL's banner off stdout: the driver reads one JSON line
-        dist.init_process_group("nccl", device_id=dev)
-    args.warmup = max(args.warmup, 3)
-
+    dev, world, rank = env.dev, env.world, env.rank
     torch.manual_seed(0)
     cfg = make_config(wl)
     nblocks = wl.get("blocks", 1)
@@ -301,12 +337,21 @@ def main():
         layer = BlockStack.from_mixers(mixers, wl["d_model"]).to(dev)
     else:
         layer = mixer0.to(dev)
-    use_cp = bool(wl.get("cp")) and world > 1
+    B, L, dm = wl["B"], wl["L"], wl["d_model"]
+    if cp_world is None:
+        cp_world = world if wl.get("cp") else 1
+    use_cp = bool(wl.get("cp")) and cp_world > 1
     if use_cp:
         mixer0.set_context_parallel("world")
-    B, L, dm = wl["B"], wl["L"], wl["d_model"]
     if wl.get("cp"):
-        L = L // world                                                # this rank's segment of the sequence
+        L = L // cp_world                                             # this rank's segment of the sequence
+    shards = 1
+    if wl.get("split_batch"):
+        if B % world:
+            raise SystemExit(f"{name}: the global batch {B} does not split over {world} GPUs")
+        B, shards = B // world, world                                 # this rank's rows of the global batch
+    elif not wl.get("cp"):
+        shards = world                                                # every rank runs its own copy of the batch (weak)
     g = torch.Generator().manual_seed(100 + rank)                     # each rank: its own shard of the global batch
     x_host = torch.randn(B, L, dm, generator=g).to(torch.bfloat16).pin_memory()
     dy_host = torch.randn(B, L, dm, generator=g).to(torch.bfloat16).pin_memory()
@@ -315,7 +360,6 @@ def main():
     x = x_host.to(dev).requires_grad_(True)
     dy = dy_host.to(dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # > 126 MB L2
-
     bf16_cast = nblocks > 1       # the stack's own norms follow the activations: run it under bf16 autocast
 
     def step():
@@ -377,113 +421,161 @@ def main():
         torch.cuda.synchronize()
         return e0.elapsed_time(e1)
 
-    def sync_all():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
-    sync_all()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    env.sync()
     timing = []
     ops.set_timing(timing)
     launches0 = ops.LAUNCHES
     ev = []
-    sync_all()
-    for _ in range(args.steps):
+    env.sync()
+    for _ in range(steps):
         flush.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         step()
         e1.record()
         ev.append((e0, e1))
-    sync_all()
+    env.sync()
     launches = ops.LAUNCHES - launches0
     ops.set_timing(None)
+    ops.check_device_status()                 # a bounded device-side wait that gave up voids the numbers: raise, exit non-zero
     total_ms = sum(a.elapsed_time(b) for a, b in ev)
     per_kernel = {}
-    for name, a, b in timing:
-        per_kernel.setdefault(name, []).append(a.elapsed_time(b))
-    # end to end: host buffers in, host buffers out
-    run_e2e(2)
-    sync_all()
-    e2e_ms = run_e2e(args.steps)
-    sync_all()
+    for kname, a, b in timing:
+        per_kernel.setdefault(kname, []).append(a.elapsed_time(b))
+    # end to end: host buffers in, host buffers out; several regions, the median is reported
+    e2e = []
+    if e2e_regions:
+        run_e2e(2)
+        env.sync()
+        for _ in range(e2e_regions):
+            e2e.append(run_e2e(steps))
+            env.sync()
+        ops.check_device_status()
+    red = env.max_over_ranks([total_ms] + e2e)
+    total_ms, e2e = red[0], red[1:]
+    tokens = B * L * steps * (cp_world if wl.get("cp") else shards)
+    kern_ms = {k: statistics.mean(v) for k, v in per_kernel.items()}
+    out = dict(
+        value=tokens / (total_ms * 1e-3), ms_per_step=total_ms / steps, tokens_per_step=tokens // steps, B=B, L=L,
+        blocks=nblocks, use_cp=use_cp, launches=launches, kern_ms=kern_ms, route=mixer0.last_route(), spec=mixer0.spec,
+        kernel_ms_sum=sum(kern_ms[k] * len(per_kernel[k]) for k in kern_ms) / steps,
+        h2d=2 * x_host.numel() * 2, d2h=2 * y_host.numel() * 2)
+    if e2e:
+        med = statistics.median(e2e)
+        out["e2e"] = {"value": tokens / (med * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": out["h2d"],
+                      "d2h_bytes_per_step": out["d2h"], "regions": len(e2e), "region_steps": steps,
+                      "ms_per_step_median": med / steps, "ms_per_step_min": min(e2e) / steps, "ms_per_step_max": max(e2e) / steps,
+                      "copies": "pinned host buffers; upload of step i+1 and download of step i overlap the compute of their "
+                                "neighbours; the median of the regions is reported"}
+    if use_cp:
+        mixer0.set_context_parallel(None)
+    del layer, mixers, x, dy, flush
+    torch.cuda.empty_cache()
+    return out
+
+
+def other_workload(env, key, steps, warmup, pk, **kw):
+    """Another workload measured with the same step definition, steps and warm-up, reported beside the headline."""
+    wl = WORKLOADS[key]
+    m = measure(env, wl, key, steps, warmup, e2e_regions=0, **kw)
+    return {"workload": key + ": " + wl["desc"], "value": m["value"], "unit": "tokens/s", "ms_per_step": m["ms_per_step"],
+            "route": m["route"], "steps": steps, "warmup": warmup, "gpu_launches": m["launches"],
+            "roofline": roofline_block(wl, m["spec"], m["route"], m["B"], m["L"], m["kern_ms"], pk),
+            "kernel_ms": {k: round(v, 4) for k, v in sorted(m["kern_ms"].items())}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg5a", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-workloads", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return run_reference(args, wl, args.workload)
+
+    env = Env()
+    world, rank = env.world, env.rank
+    args.warmup = max(args.warmup, 3)
+    pk = peaks()
+    sampler = ClockSampler(env.local)
+    if rank == 0:
+        sampler.start()
+    m = measure(env, wl, args.workload, args.steps, args.warmup)
     clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([total_ms, e2e_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = float(t[0]), float(t[1])
+
+    others = {}
+    if args.workload == "cfg5a" and not args.no_other_workloads:
+        if world == 1:
+            # the other single-GPU configurations, same steps and warm-up, each with its own roofline block
+            for key in ("cfg3", "cfg4"):
+                others[key] = other_workload(env, key, args.steps, args.warmup, pk)
+        else:
+            # BASELINE config 5b: the one mode with communication on the data path.  Rank 0 first runs the whole sequence
+            # alone (the N = 1 time the strong-scaling figure divides by), then all ranks run it context-parallel.
+            k5 = max(3, min(args.steps, 5))
+            solo = None
+            if rank == 0:
+                solo_env = _Solo(env)
+                solo = other_workload(solo_env, "cfg5b", k5, args.warmup, pk, cp_world=1)
+            env.sync()
+            cpm = other_workload(env, "cfg5b", k5, args.warmup, pk)
+            if rank == 0:
+                cpm["n1_ms_per_step"] = solo["ms_per_step"]
+                cpm["scaling"] = "strong"
+                cpm["n_gpus"] = world
+                cpm["speedup_over_n1"] = solo["ms_per_step"] / cpm["ms_per_step"]
+                cpm["parallelism"] = f"context-parallel x{world}: all-gather of segment states + conv halos (NCCL)"
+                others["cfg5b"] = cpm
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        env.close()
         return
 
-    tokens = B * L * world * args.steps                              # cfg5b: L is the per-rank segment
-    value = tokens / (total_ms * 1e-3)
-    pk = peaks()
-    spec = mixer0.spec
-    kern_ms = {k: statistics.mean(v) for k, v in per_kernel.items()}
-    roofline = None
-    fl, dom = {}, None
-    if wl["kind"] == "hm":
-        # the coordinate scan has no contraction: it is bound by exp (MUFU) and FP32 issue; HBM is the nearest roofline
-        # the contract names.  Algorithmic bytes = compulsory IO of the launch: drive in, output (or its gradient) in/out,
-        # maps and clocks (and their gradients) once; checkpoints and partial-sum buffers are not counted.
-        es, D_in, Nn, Hh = 2, spec.d_inner, spec.N, spec.H
-        maps = B * L * (2 * Nn + spec.K + 2 * Hh) * 4
-        byts = {"hm_scan_fwd": B * L * D_in * es * 2 + maps, "hm_scan_bwd": B * L * D_in * es * 3 + 2 * maps}
-        dom = max(byts, key=lambda k: kern_ms.get(k, 0.0))
-        ach = byts[dom] / (kern_ms[dom] * 1e-3) / 1e9
-        upd = B * L * Hh * spec.P * Nn / (kern_ms[dom] * 1e-3)
-        roofline = dict(bound="hbm", kernel=dom, achieved=ach, peak=pk["hbm_gbs"], unit="GB/s", frac=ach / pk["hbm_gbs"],
-                        traffic=None, peak_source=pk["source"] + " (copy)", ms_per_launch=kern_ms[dom],
-                        note="issue-bound (one exp + ~10 FP32 ops per state element per token), not HBM-bound",
-                        state_updates_per_s=upd, route=mixer0.last_route())
-    else:
-        fl = scan_flops(spec, B, L, wl["chunk_acct"])
-        scan_names = [k for k in kern_ms if k in fl]
-        dom = max(scan_names, key=lambda k: kern_ms[k]) if scan_names else None
-    if dom and wl["kind"] != "hm":
-        ach = fl[dom] / (kern_ms[dom] * 1e-3) / 1e12
-        roofline = dict(bound="tensor", kernel=dom, achieved=ach, peak=pk["tflops"], unit="TFLOP/s", frac=ach / pk["tflops"],
-                        traffic=None, peak_source=pk["source"] + " (sustained bf16 GEMM)", ms_per_launch=kern_ms[dom],
-                        route=mixer0.last_route())
-    if roofline is not None:
-        per_tok = DRAM_BYTES_PER_TOKEN.get(wl["kind"], {}).get(roofline["kernel"])
-        if per_tok is not None:
-            roofline["traffic"] = per_tok * B * L
-            roofline["traffic_source"] = "ncu capture of the profiling case, scaled by tokens per launch"
+    B, L, nblocks = m["B"], m["L"], m["blocks"]
+    strong = bool(wl.get("cp") or wl.get("split_batch"))
     out = {
-        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong" if wl.get("cp") else "weak", "vs_baseline": None,
+        "metric": METRIC, "value": m["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": m["ms_per_step"], "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload + ": " + wl["desc"], "per_gpu_batch": B, "seq_len": L, "blocks": nblocks,
+        "config": {"workload": args.workload + ": " + wl["desc"], "global_batch": wl["B"] if strong else wl["B"] * world,
+                   "per_gpu_batch": B, "seq_len": L, "blocks": nblocks, "tokens_per_step": m["tokens_per_step"],
                    "l2": "256 MB buffer written between timed steps",
-                   "parallelism": (f"context-parallel x{world}: all-gather of segment states + conv halos" if use_cp
-                                   else f"batch-sharded x{world}, no collective")},
-        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * x_host.numel() * 2,
-                "copies": "pinned host buffers; upload of step i+1 and download of step i overlap the compute of their neighbours",
-                "d2h_bytes_per_step": 2 * y_host.numel() * 2},
-        "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
-        "kernel_ms": {k: round(v, 4) for k, v in sorted(kern_ms.items())},
-        "kernel_ms_sum": round(sum(kern_ms[k] * len(per_kernel[k]) for k in kern_ms) / args.steps, 4),
+                   "parallelism": (f"context-parallel x{world}: all-gather of segment states + conv halos" if m["use_cp"]
+                                   else f"batch rows split x{world}, no collective on the data path")},
+        "e2e": m.get("e2e"), "gpu_launches": m["launches"], "clocks": clocks,
+        "roofline": roofline_block(wl, m["spec"], m["route"], B, L, m["kern_ms"], pk),
+        "kernel_ms": {k: round(v, 4) for k, v in sorted(m["kern_ms"].items())},
+        "kernel_ms_sum": round(m["kernel_ms_sum"], 4),
     }
     if world == 1 and not args.no_cpu_baseline:
         sB, sL = 1, 256 if wl["kind"] == "m2" else 128
         tcpu = cpu_step_time(wl, sB, sL, 3, 1)
         out["cpu_baseline"] = {"value": sB * sL / tcpu, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-                               "sample": f"x [{sB},{sL},{dm}] fp32 of the same layer, median of 3 steps after 1 warm-up",
+                               "sample": f"x [{sB},{sL},{wl['d_model']}] fp32 of the same layer, median of 3 steps after 1 warm-up",
                                "host_cpus": os.cpu_count()}
-    if world == 1 and args.workload == "cfg5a" and not args.no_cpu_baseline:
-        out["other_workloads"] = {"cfg3": side_measure(WORKLOADS["cfg3"], dev), "cfg4": side_measure(WORKLOADS["cfg4"], dev)}
+    if others:
+        out["other_workloads"] = others
     print(json.dumps(out))
-    if world > 1:
-        dist.destroy_process_group()
+    env.close()
+
+
+class _Solo:
+    """An `Env` view for work that one rank does alone while the others wait at the next barrier."""
+
+    def __init__(self, env):
+        self.dev, self.local, self.rank, self.world, self.dist = env.dev, env.local, 0, 1, env.dist
+
+    def sync(self):
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, values):
+        return [float(v) for v in values]
 
 
 if __name__ == "__main__":

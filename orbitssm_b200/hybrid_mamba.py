@@ -165,7 +165,9 @@ class HybridMambaSSM(StateLifecycle, nn.Module):
         s = self.spec
         st = State(hidden_state=torch.zeros(batch_size, s.H, s.P, s.N, device=dev, dtype=dtype))
         if s.has_rot:
-            st["theta"] = torch.zeros(batch_size, s.H, len(s.rot_pairs), device=dev, dtype=dtype)
+            # the running phase is held in fp32 at least, whatever dtype the other carries take
+            st["theta"] = torch.zeros(batch_size, s.H, len(s.rot_pairs), device=dev,
+                                      dtype=torch.promote_types(dtype, torch.float32))
         if s.use_trap:
             st["write_prev"] = torch.zeros_like(st["hidden_state"])
         if self.conv1d is not None:

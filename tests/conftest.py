@@ -29,5 +29,7 @@ def load_golden(name):
     return torch.load(os.path.join(GOLDEN, name + ".pt"), weights_only=False)
 
 
-GOLDEN_CASES = ("cfg1_exact", "cfg2_small", "cfg3_small", "dyn_trap_conv", "softplus_sib", "euler_r2o1")
-HM_GOLDEN_CASES = ("hm_small", "hm_cfg4_small", "hm_euler")
+GOLDEN_CASES = ("cfg1_exact", "cfg2_small", "cfg3_small", "dyn_trap_conv", "softplus_sib", "euler_r2o1",
+                # several chunks of the tensor-core tiles, continuation cut inside a chunk
+                "cfg2_long", "cfg5_long", "cfg3_long")
+HM_GOLDEN_CASES = ("hm_small", "hm_cfg4_small", "hm_euler", "hm_cfg4_long")

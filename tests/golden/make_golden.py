@@ -2,7 +2,7 @@
 
 Usage (only where the reference checkout is available; the fixtures it writes are committed):
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [case ...]      (no case names = all of them)
 
 Every fixture is one ``torch.save`` dict: the config (field names shared by the reference's `SSDMimoConfig` and
 this package's), the reference layer's ``state_dict`` (every parameter moved off its init value so that
@@ -45,6 +45,15 @@ CASES = {
     "softplus_sib": dict(cfg=dict(d_model=32, d_state=8, expand=1.0, d_conv=3, d_ssm_in=2, d_ssm_out=2, n_groups=4,
                                   a_act="softplus", a_dyn_per_sibling=True, bc_bias="shared",
                                   skip_sharing="input_output"), B=1, L=21, split=8),
+    # The tensor-core tiles of this package work on 128-token (rank 1) and 32-token (rank 4) chunks: these cases are long
+    # enough to cross several chunk boundaries, and their continuation cut falls inside a chunk.
+    # config-2 geometry, 2 heads, 4 chunks of 128 (the last one partial), cut at 200 = 128 + 72
+    "cfg2_long": dict(preset=dict(d_model=64, d_state=128, d_head=64), B=2, L=416, split=200),
+    # config-5 head geometry (P = 64, N = 128) at 4 heads, cut at 150 = 128 + 22
+    "cfg5_long": dict(preset=dict(d_model=128, d_state=128, d_head=64), B=1, L=400, split=150),
+    # config-3 geometry at 2 heads, 7 chunks of 32, cut at 100 = 3 * 32 + 4
+    "cfg3_long": dict(cfg=dict(d_model=64, expand=2.0, d_state=128, d_ssm_in=4, d_ssm_out=4, n_heads=2, d_head=64,
+                               d_conv=4, write_rule="trapezoid", row_blocks=HS), B=1, L=224, split=100),
     "euler_r2o1": dict(cfg=dict(d_model=24, d_state=8, expand=1.0, d_conv=2, d_ssm_in=2, d_ssm_out=1, n_groups=3,
                                 write_rule="euler", row_blocks=HS, skip_sharing="channel", b_norm=False,
                                 r_mix="none", bc_bias="none"), B=2, L=18, split=5),
@@ -88,7 +97,10 @@ def run(layer, x, dy, state=None, gh=None, gw=None, exact=False):
 
 
 def main():
+    only = set(sys.argv[2:])
     for name, case in CASES.items():
+        if only and name not in only:
+            continue
         rec = {}
         for tag, dtype in (("f64", torch.float64), ("f32", torch.float32)):
             cfg, layer = build(case, dtype)

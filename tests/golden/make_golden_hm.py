@@ -1,6 +1,6 @@
 """Generate the HybridMamba golden vectors under tests/golden/ by RUNNING THE REFERENCE ITSELF on CPU.
 
-    python tests/golden/make_golden_hm.py /path/to/reference
+    python tests/golden/make_golden_hm.py /path/to/reference [case ...]      (no case names = all of them)
 
 Same recipe as make_golden.py, for `HybridMambaSSM` (`backend="torch"`): config, the reference layer's ``state_dict``
 (every parameter moved off its init value), seeded inputs, and the reference's fp64 / fp32 results: output, carried
@@ -32,6 +32,9 @@ CASES = {
     # config 4's head geometry (P = 64, N = 64: 32 real rows + 16 pairs) at 2 heads
     "hm_cfg4_small": dict(cfg=dict(d_model=64, d_state=64, expand=2, d_conv=4, out_norm=True, row_blocks=HALF),
                           B=1, L=48, split=20),
+    # the same geometry over ten 32-token checkpoint intervals of the backward kernel, cut at 143 = 4 * 32 + 15
+    "hm_cfg4_long": dict(cfg=dict(d_model=64, d_state=64, expand=2, d_conv=4, out_norm=True, row_blocks=HALF),
+                         B=1, L=320, split=143),
     # Euler write, real rows only, no output norm (gate, then out_proj)
     "hm_euler": dict(cfg=dict(d_model=32, d_state=8, expand=1, d_conv=3, out_norm=False, d_head=8, write_rule="euler",
                               row_blocks=[{"frac": 1.0, "decay": "coord_static"}]), B=2, L=19, split=7),
@@ -72,7 +75,10 @@ def run(layer, x, dy, state, gs):
 
 
 def main():
+    only = set(sys.argv[2:])
     for name, case in CASES.items():
+        if only and name not in only:
+            continue
         rec = {}
         for tag, dtype in (("f64", torch.float64), ("f32", torch.float32)):
             cfg, layer, fresh = build(case, dtype)

@@ -4,6 +4,8 @@ Tolerances (normwise relative error ||a - r|| / ||r||):
   fp32 IO: 2e-5 forward, 2e-4 gradients (fp32 arithmetic against an fp64 restatement; sums of O(chunk * N) terms);
   bf16 IO: 6e-3 (outputs are rounded once to bfloat16, eps = 2^-8 = 3.9e-3; inputs are identical rounded values).
 """
+import ctypes as C
+
 import pytest
 import torch
 
@@ -479,3 +481,18 @@ def test_token_clock(dtype, a_act, per_sib, trap, rmix):
             continue
         lim = 2e-5 if (dtype == torch.float32 or k in ("A_log", "r_mix")) else 6e-3
         assert rel(got[k].reshape(v.shape), v) < lim, (k, rel(got[k].reshape(v.shape), v))
+
+
+def test_bounded_wait_winds_down_and_reports():
+    """A device-side wait that runs out: the kernel sets the status word, frees its tensor memory and returns; the host
+    maps the word to ORBIT_ERR_DEVICE_TIMEOUT, and the next tensor-core launch works (nothing faulted, nothing leaked)."""
+    lib = _lib.load()
+    status = ops._status_word(torch.device(DEV, torch.cuda.current_device()))
+    status.zero_()
+    _lib.check(lib.orbit_selftest_wait_timeout(C.c_void_p(status.data_ptr()), 1000, C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+               "orbit_selftest_wait_timeout")
+    with pytest.raises(RuntimeError, match="ORBIT_ERR_DEVICE_TIMEOUT"):
+        ops.check_device_status()
+    assert int(status.item()) == 0                                   # the check clears the word
+    ops.check_device_status()
+    test_umma_tile(0, 128, 128)                                      # tensor memory was freed: a tile runs right after
