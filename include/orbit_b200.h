@@ -290,9 +290,10 @@ int orbit_hm_scan_bwd(const orbit_hm_args* a, int dtype, void* stream);
 /* ---- diagnostics ---------------------------------------------------------------------------------------------
  * One 128 x N x K tcgen05 tile through the same TMA boxes, shared-memory descriptors and TMEM read-out as the scan
  * kernels: D[128, N] fp32 = op(A) * op(B), A and B bfloat16.  mode bit 0: A given as [K, 128] (M contiguous) instead
- * of [128, K]; bit 1: B given as [K, N] instead of [N, K]; bit 2: A staged through registers with the manual swizzle.
- * K, N in {64, 128}.  *status (device int) becomes nonzero if a bounded device wait gave up.  No counterpart in the
- * reference (its kernels are Triton; there is no sm_100 path there). */
+ * of [128, K]; bit 1: B given as [K, N] instead of [N, K]; bit 2: A staged through registers with the manual swizzle;
+ * bit 3: A staged in tensor memory (packed bfloat16 pairs) instead of shared memory.  K, N in {64, 128}.
+ * *status (device int) becomes nonzero if a bounded device wait gave up.  No counterpart in the reference (its
+ * kernels are Triton; there is no sm_100 path there). */
 int orbit_selftest_umma(const void* A, const void* B, float* D, int mode, int K, int N, int* status, void* stream);
 
 /* The wind-down of a bounded device-side wait, exercised without a fault: one CTA allocates tensor memory and waits at

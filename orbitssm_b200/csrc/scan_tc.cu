@@ -21,37 +21,55 @@ using namespace tc;
 
 constexpr int TC_T = 128, TC_N = 128, TC_G = 64;
 constexpr int ISSUER = 128;      // thread that issues the per-head MMAs and TMA refills in the output / score-gradient kernels
-constexpr int OUT_CLK_LD = 448;  // floats per staged-clocks buffer of the output kernel
 constexpr int GS_CLK_LD = 592;   // floats per staged-clocks buffer of the score-gradient kernel
 
 // ------------------------------------------------------------------------------------------------------------------
 // chunk_state (mode 0):  Z[n,p] = sum_s B[s,n] e_s u[s,p],   e_s = exp(cs_T - cs_s) w_s          -> a.Sin, a.atot
 // chunk_dstate (mode 1): Gs[n,p] = sum_t C[t,n] a_t dy[t,p], a_t = exp(cs_t)                      -> a.dS
+//
+// Warp-specialised (10 warps): warps 0..3 read the accumulators out to global memory, warps 4..7 form the per-token
+// factors and scale the drive tile of the next head, one lane of warp 8 issues the TMA loads (4-stage ring), one lane
+// of warp 9 the MMAs (two accumulator sets); the roles meet only through mbarriers.
 // ------------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_state_kernel(const __grid_constant__ CUtensorMap tmM,
-                                                                       const __grid_constant__ CUtensorMap tmX,
-                                                                       const ScanArgs a, const int mode) {
+constexpr int ST_THREADS = 320;
+constexpr int ST_STAGES = 4;
+
+struct StateBars {
+  uint64_t map, x_full[ST_STAGES], x_empty[ST_STAGES], xs_full[2], xs_empty[2], acc_full[2], acc_empty[2];
+};
+
+__global__ void __launch_bounds__(ST_THREADS, 1) tc_chunk_state_kernel(const __grid_constant__ CUtensorMap tmM,
+                                                                        const __grid_constant__ CUtensorMap tmX,
+                                                                        const __grid_constant__ CUtensorMap tmZ,
+                                                                        const ScanArgs a, const int mode) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   uint8_t* sM = sm;                      // map tile, 2 blocks
-  uint8_t* sX = sm + 2 * BLK;            // raw drive tiles, 2 buffers
-  uint8_t* sXs = sm + 4 * BLK;           // scaled drive tiles, 2 buffers
-  float* fv = reinterpret_cast<float*>(sm + 6 * BLK);   // [2][128] per-token factors of heads h, h + 1
-  float* wsum = fv + 256;
-  __shared__ uint64_t bar_map, bar_x[2], bar_mma[2];
+  uint8_t* sX = sm + 2 * BLK;            // raw drive tiles, ST_STAGES buffers
+  uint8_t* sXs = sm + (2 + ST_STAGES) * BLK;   // scaled drive tiles, 2 buffers
+  uint8_t* sZ = sm + (4 + ST_STAGES) * BLK;    // fp32 result tiles on their way out: 2 buffers of two [128 n][32 p] halves
+  float* wsum = reinterpret_cast<float*>(sm + (8 + ST_STAGES) * BLK);
+  __shared__ StateBars bars;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = warp & 3, wg = warp >> 2;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = warp & 3, role = warp >> 2;
   const int c = blockIdx.x, b = blockIdx.y, t0 = c * TC_T;
   const int Tv = min(TC_T, a.L - t0);
   const int H = a.H;
+  const int t = q * 32 + lane;           // token row (scaling warps) or state row n (read-out warps)
 
   if (tid == 0) {
-    mbar_init(&bar_map, 1);
-    mbar_init(&bar_x[0], 1);
-    mbar_init(&bar_x[1], 1);
-    mbar_init(&bar_mma[0], 1);
-    mbar_init(&bar_mma[1], 1);
+    mbar_init(&bars.map, 1);
+    for (int i = 0; i < ST_STAGES; ++i) {
+      mbar_init(&bars.x_full[i], 1);
+      mbar_init(&bars.x_empty[i], 4);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars.xs_full[i], 4);
+      mbar_init(&bars.xs_empty[i], 1);
+      mbar_init(&bars.acc_full[i], 1);
+      mbar_init(&bars.acc_empty[i], 4);
+    }
     mbar_fence_init();
     s_abort = 0;
   }
@@ -61,122 +79,119 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_state_kernel(const __g
   tc_fence_after_sync();
   const uint32_t tbase = tmem_slot;
   volatile int* abort_flag = &s_abort;
+  bool dead = false;
 
-  if (tid == 0) {
-    mbar_expect_tx(&bar_map, 2 * BLK);
-    tma_load_3d(sM, &tmM, &bar_map, 0, t0, b);
-    tma_load_3d(sM + BLK, &tmM, &bar_map, 64, t0, b);
-    for (int i = 0; i < 2 && i < H; ++i) {
-      mbar_expect_tx(&bar_x[i], BLK);
-      tma_load_3d(sX + i * BLK, &tmX, &bar_x[i], i * TC_G, t0, b);
-    }
-  }
-  float* outbuf = mode == 0 ? a.Sin : a.dS;
-  const uint32_t idesc = idesc_bf16(128, 64, 1, 1);
-
-  auto epilogue = [&](int hh) {
-    const int be = hh & 1;
-    if (wait_warp(&bar_mma[be], (uint32_t)((hh >> 1) & 1), abort_flag)) {
-      tc_fence_after_sync();
-      uint32_t r[32];
-      tmem_ld32(tmem_addr(tbase, q * 32, be * 64 + wg * 32), r);
-      tmem_ld_wait();
-      float* dst = outbuf + ((((int64_t)b * a.nc + c) * H + hh) * TC_N + (q * 32 + lane)) * (int64_t)TC_G + wg * 32;
+  if (role == 2) {
+    if (warp == 8 && lane == 0) {
+      // ---- producer ----
+      mbar_expect_tx(&bars.map, 2 * BLK);
+      tma_load_3d(sM, &tmM, &bars.map, 0, t0, b);
+      tma_load_3d(sM + BLK, &tmM, &bars.map, 64, t0, b);
+      for (int h = 0; h < H; ++h) {
+        const int s = h % ST_STAGES;
+        if (h >= ST_STAGES && !lane_wait(&bars.x_empty[s], (uint32_t)((h / ST_STAGES - 1) & 1), abort_flag, dead)) break;
+        mbar_expect_tx(&bars.x_full[s], BLK);
+        tma_load_3d(sX + s * BLK, &tmX, &bars.x_full[s], h * TC_G, t0, b);
+      }
+    } else if (warp == 9 && lane == 0) {
+      // ---- MMA issuer ----
+      const uint32_t idesc = idesc_bf16(128, 64, 1, 1);
+      lane_wait(&bars.map, 0, abort_flag, dead);
+      for (int h = 0; h < H && !dead; ++h) {
+        const int k = h & 1;
+        if (!lane_wait(&bars.xs_full[k], (uint32_t)((h >> 1) & 1), abort_flag, dead)) break;
+        if (h >= 2 && !lane_wait(&bars.acc_empty[k], (uint32_t)(((h >> 1) - 1) & 1), abort_flag, dead)) break;
+        tc_fence_after_sync();
+        const uint32_t am = smem_u32(sM), bx = smem_u32(sXs + k * BLK);
 #pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                          __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-    }
-    tc_fence_before_sync();
-  };
-
-  // Two block-wide barriers per head.  The prefix of head h + 1 is formed beside the work of head h: its warp scans run
-  // in the interval of the scaling pass, its per-token factors fv[(h + 1) & 1] in the interval of the MMA issue and the
-  // read-out of head h - 1 (the chunk total is the sum of the four warp totals, known to every thread after the
-  // first barrier).  Clocks are fetched one head further ahead.
-  auto warp_scan = [&](float v) -> float {   // inclusive scan inside the warp; warp totals of warps 0..3 -> wsum
-    float x = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      float y = __shfl_up_sync(0xffffffffu, x, o);
-      if (lane >= o) x += y;
-    }
-    if (warp < 4 && lane == 31) wsum[warp] = x;
-    return x;
-  };
-  auto token_factor = [&](int hh, float x, float wt) {   // after the barrier that publishes wsum
-    if (tid < 128) {
-      const float w0 = wsum[0], w1 = wsum[1], w2 = wsum[2], w3 = wsum[3];
-      const float off = warp == 0 ? 0.f : (warp == 1 ? w0 : (warp == 2 ? w0 + w1 : (w0 + w1) + w2));
-      const float tot = ((w0 + w1) + w2) + w3, csv = x + off;
-      fv[(hh & 1) * 128 + tid] = mode == 0 ? __expf(tot - csv) * wt : __expf(csv);
-      if (tid == 0 && mode == 0) a.atot[((int64_t)b * a.nc + c) * H + hh] = __expf(tot);
-    }
-  };
-  float d_n = 0.f, wt_n = 0.f;
-  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H;
-  if (tid < Tv) {
-    d_n = a.dA[ck];
-    wt_n = a.w[ck];
-  }
-  float x_cur = warp_scan(d_n), wt_cur = wt_n;
-  if (tid < Tv && 1 < H) {
-    d_n = a.dA[ck + 1];
-    wt_n = a.w[ck + 1];
-  }
-  __syncthreads();
-  token_factor(0, x_cur, wt_cur);
-  __syncthreads();
-  for (int h = 0; h < H; ++h) {
-    const int buf = h & 1;
-    // ---- interval 1: warp scans of head h + 1, scaling pass of head h
-    if (h + 1 < H) {
-      x_cur = warp_scan(d_n);
-      wt_cur = wt_n;
-      if (tid < Tv && h + 2 < H) {
-        d_n = a.dA[ck + h + 2];
-        wt_n = a.w[ck + h + 2];
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + k * 64, desc_mn(am, ks), desc_mn(bx, ks), idesc, ks > 0 ? 1u : 0u);
+        umma_commit(&bars.xs_empty[k]);
+        umma_commit(&bars.acc_full[k]);
       }
     }
-    if (wait_warp(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag)) {
-      const int row = tid & 127, half = tid >> 7;
-      const float f = fv[buf * 128 + row];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t off = buf * BLK + sw128_offset(row, half * 4 + j);
-        uint4 v = *reinterpret_cast<const uint4*>(sX + off);
-        uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float lo, hi;
-          unpack_bf16(pv[k], lo, hi);
-          pv[k] = pack_bf16(lo * f, hi * f);
-        }
-        *reinterpret_cast<uint4*>(sXs + off) = v;
-      }
-    }
-    fence_proxy_async();
-    __syncthreads();
-    // ---- interval 2: factors of head h + 1, MMA of head h, read-out of head h - 1
-    if (tid == 0 && !*abort_flag) {
-      if (h + 2 < H) {
-        mbar_expect_tx(&bar_x[buf], BLK);
-        tma_load_3d(sX + buf * BLK, &tmX, &bar_x[buf], (h + 2) * TC_G, t0, b);
-      }
-      bool ok = (h > 0) || wait_or_abort(&bar_map, 0, abort_flag);
+    __syncwarp();
+  } else if (role == 0) {
+    // ---- read-out: accumulator rows (state rows n) -> fp32 tile in shared memory -> two TMA stores per head ----
+    const int64_t zrow0 = (((int64_t)b * a.nc + c) * H) * TC_N;
+    for (int h = 0; h < H; ++h) {
+      const int k = h & 1;
+      const bool ok = role_wait(&bars.acc_full[k], (uint32_t)((h >> 1) & 1), abort_flag, dead);
       if (ok) {
         tc_fence_after_sync();
-        const uint32_t am = smem_u32(sM), bx = smem_u32(sXs + buf * BLK);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + buf * 64, desc_mn(am, ks), desc_mn(bx, ks), idesc, ks > 0 ? 1u : 0u);
-        umma_commit(&bar_mma[buf]);
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld32(tmem_addr(tbase, q * 32, k * 64 + half * 32), r);
+          tmem_ld_wait();
+          uint8_t* dst = sZ + (k * 2 + half) * BLK;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(dst + sw128_offset(t, j)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        }
+      }
+      warp_arrive(&bars.acc_empty[k], true);
+      if (tid == 0) bulk_wait_group_read<0>();   // the stores of head h - 1 have read their tile (the buffer head h + 1 writes)
+      named_bar_sync(2, 128);
+      if (tid == 0 && ok) {
+        tma_store_2d(&tmZ, sZ + (k * 2) * BLK, 0, (int)(zrow0 + (int64_t)h * TC_N));
+        tma_store_2d(&tmZ, sZ + (k * 2 + 1) * BLK, 32, (int)(zrow0 + (int64_t)h * TC_N));
+        bulk_commit_group();
       }
     }
-    if (h + 1 < H) token_factor(h + 1, x_cur, wt_cur);
-    if (h > 0) epilogue(h - 1);
-    __syncthreads();
+    if (tid == 0) bulk_wait_group<0>();
+  } else {
+    // ---- scaling group: per-token factors of head h, scaled drive tile -> shared memory ----
+    const int64_t ck = ((int64_t)b * a.L + t0 + min(t, Tv - 1)) * H;
+    const bool live = t < Tv;
+    float d_n = 0.f, w_n = 0.f;
+    if (live) {
+      d_n = a.dA[ck];
+      w_n = a.w[ck];
+    }
+    for (int h = 0; h < H; ++h) {
+      const int s = h % ST_STAGES, k = h & 1;
+      const float wt = w_n;
+      float x = d_n;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+      }
+      if (lane == 31) wsum[(h & 1) * 4 + q] = x;       // two sets: the next head's totals may be written while a slow
+                                                       // warp still reads this head's
+      if (h + 1 < H && live) {
+        d_n = a.dA[ck + h + 1];
+        w_n = a.w[ck + h + 1];
+      }
+      named_bar_sync(1, 128);
+      const float* ws = wsum + (h & 1) * 4;
+      const float w0 = ws[0], w1 = ws[1], w2 = ws[2], w3 = ws[3];
+      const float off = q == 0 ? 0.f : (q == 1 ? w0 : (q == 2 ? w0 + w1 : (w0 + w1) + w2));
+      const float tot = ((w0 + w1) + w2) + w3, csv = x + off;
+      const float f = mode == 0 ? __expf(tot - csv) * wt : __expf(csv);
+      if (mode == 0 && t == 0) a.atot[((int64_t)b * a.nc + c) * H + h] = __expf(tot);
+      bool go = role_wait(&bars.x_full[s], (uint32_t)((h / ST_STAGES) & 1), abort_flag, dead);
+      if (h >= 2) go = role_wait(&bars.xs_empty[k], (uint32_t)(((h >> 1) - 1) & 1), abort_flag, dead) && go;
+      if (go) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t off8 = sw128_offset(t, j);
+          uint4 v = *reinterpret_cast<const uint4*>(sX + s * BLK + off8);
+          uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float lo, hi;
+            unpack_bf16(pv[e], lo, hi);
+            pv[e] = pack_bf16(lo * f, hi * f);
+          }
+          *reinterpret_cast<uint4*>(sXs + k * BLK + off8) = v;
+        }
+      }
+      warp_arrive(&bars.xs_full[k], true);
+      if (lane == 0) mbar_arrive(&bars.x_empty[s]);
+    }
   }
-  epilogue(H - 1);
+  tc_fence_before_sync();
   __syncthreads();
   if (tid == 0 && *abort_flag && a.status) atomicExch(a.status, 1);
   if (warp == 0) tmem_dealloc(tbase, 128);
@@ -184,259 +199,291 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_state_kernel(const __g
 
 // ------------------------------------------------------------------------------------------------------------------
 // chunk_out:  y[t,p] = sum_{s<=t} CB[t,s] W_h[t,s] u[s,p] + a_t sum_n C[t,n] Sin_h[n,p] + D[h,p] u[t,p]
+//
+// Warp-specialised: 14 warps in five roles that meet only through mbarriers, so that the stages of consecutive heads
+// overlap (TMA of head h+2 | decay mask of head h+1 | MMAs of head h | read-out of head h-1):
+//   warps 0..3   read-out: TMEM accumulators of a head -> y (scaled inter-chunk part, skip term, bf16, global)
+//   warps 4..7   mask group 0 (even heads): clock prefix, decay mask o CB -> masked-score tile in shared memory
+//   warps 8..11  mask group 1 (odd heads):  the same into the second tile
+//   warp 12      producer: one lane issues the TMA loads of drive and entering-state tiles into a 3-stage ring
+//   warp 13      MMA issuer: one lane issues the tcgen05 MMAs into one of two accumulator sets in TMEM
+// A warp reads the TMEM lanes 32 (warp mod 4) .. +31, i.e. token rows; thread = one token row throughout.
 // ------------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_out_kernel(const __grid_constant__ CUtensorMap tmB,
-                                                                     const __grid_constant__ CUtensorMap tmC,
-                                                                     const __grid_constant__ CUtensorMap tmU,
-                                                                     const __grid_constant__ CUtensorMap tmS,
-                                                                     const ScanArgs a) {
+constexpr int WS_THREADS = 448;
+constexpr int WS_XSTAGES = 4;           // drive tiles: a stage is free again once its head's y tile, written in place, has left
+constexpr int WS_SSTAGES = 2;           // entering-state tiles: free again when the head's MMAs are done
+constexpr int WS_AT_RING = 8;           // per-head rows kept for the read-out warps (a_t, skip coefficients), ring over heads
+
+struct OutBars {
+  uint64_t map, cb, u_full[WS_XSTAGES], u_empty[WS_XSTAGES], s_full[WS_SSTAGES], s_empty[WS_SSTAGES], ms_full[2], ms_empty[2],
+      acc_full[2], acc_empty[2];
+};
+
+__global__ void __launch_bounds__(WS_THREADS, 1) tc_chunk_out_kernel(const __grid_constant__ CUtensorMap tmB,
+                                                                      const __grid_constant__ CUtensorMap tmC,
+                                                                      const __grid_constant__ CUtensorMap tmU,
+                                                                      const __grid_constant__ CUtensorMap tmS,
+                                                                      const __grid_constant__ CUtensorMap tmY,
+                                                                      const ScanArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
-  uint8_t* sB = sm;                      // 2 blocks
-  uint8_t* sC = sm + 2 * BLK;            // 2 blocks
-  uint8_t* sX = sm + 4 * BLK;            // 2 buffers
-  uint8_t* sMs = sm + 6 * BLK;           // masked scores [128 t][128 s], 2 blocks
-  uint8_t* sS = sm + 8 * BLK;            // entering state [128 n][64 p] bf16, 2 buffers
-  float* csb = reinterpret_cast<float*>(sm + 10 * BLK);   // [2][cs | fs | fw] x 128: prefix of the steps and split decay
-                                                          // factors, buffer h & 1 (filled during the previous head)
-  float* wsum = csb + 768;
-  float* clk = wsum + 8;                 // [3][OUT_CLK_LD] per-head rows staged two heads ahead (see stage_clocks)
-  __shared__ uint64_t bar_map, bar_x[2], bar_cb, bar_y;
+  uint8_t* sC = sm;                      // C tile, 2 blocks
+  uint8_t* sMs = sm + 2 * BLK;           // [2 groups] masked scores [128 t][128 s], 2 blocks each; group 0's tile holds B first
+  uint8_t* sX = sm + 6 * BLK;            // drive tiles (later, in place, y tiles), WS_XSTAGES buffers
+  uint8_t* sS = sm + (6 + WS_XSTAGES) * BLK;   // entering state [128 n][64 p] bf16, WS_SSTAGES buffers
+  float* csb = reinterpret_cast<float*>(sm + (6 + WS_XSTAGES + WS_SSTAGES) * BLK);   // [2 groups][cs | fs | fw | w] x 128
+  float* atb = csb + 1024;               // [WS_AT_RING][128] a_t = exp(cs_t) of the last heads
+  float* dgb = atb + WS_AT_RING * 128;   // [WS_AT_RING][64] skip coefficients D[h, :] of the last heads
+  float* wsumb = dgb + WS_AT_RING * 64;  // [2 groups][8]
+  __shared__ OutBars bars;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = warp & 3, wg = warp >> 2;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = warp & 3, role = warp >> 2;
   const int c = blockIdx.x, b = blockIdx.y, t0 = c * TC_T;
   const int Tv = min(TC_T, a.L - t0);
   const int H = a.H;
-  // heads [h0, h0 + Hl) of this (batch, chunk): blockIdx.z splits the head loop (gradients of head-shared maps then go
-  // to per-split partial buffers); `h` below counts from h0
+  // heads [h0, h0 + Hl) of this (batch, chunk): blockIdx.z splits the head loop; `h` below counts from h0
   const int nsplit = gridDim.z, Hl = H / nsplit, h0 = blockIdx.z * Hl;
-  const int t = q * 32 + lane;           // this thread's token row in TMEM
+  const int t = q * 32 + lane;           // this thread's token row (TMEM lane) in every role that has one
   const int64_t srow0 = ((int64_t)b * a.nc + c) * H + h0;   // index of this chunk's first [128 x 64] state tile
 
   if (tid == 0) {
-    mbar_init(&bar_map, 1);
-    mbar_init(&bar_x[0], 1);
-    mbar_init(&bar_x[1], 1);
-    mbar_init(&bar_cb, 1);
-    mbar_init(&bar_y, 1);
+    mbar_init(&bars.map, 1);
+    mbar_init(&bars.cb, 1);
+    for (int i = 0; i < WS_XSTAGES; ++i) {
+      mbar_init(&bars.u_full[i], 1);
+      mbar_init(&bars.u_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars.s_full[i], 1);
+      mbar_init(&bars.s_empty[i], 1);
+      mbar_init(&bars.ms_full[i], 4);
+      mbar_init(&bars.ms_empty[i], 1);
+      mbar_init(&bars.acc_full[i], 1);
+      mbar_init(&bars.acc_empty[i], 4);
+    }
     mbar_fence_init();
     s_abort = 0;
   }
-  if (warp == 0) tmem_alloc(&tmem_slot, 256);
+  if (warp == 0) tmem_alloc(&tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tbase = tmem_slot;
   volatile int* abort_flag = &s_abort;
-  const uint32_t TM_CB = 0, TM_Y1 = 128, TM_Y2 = 192;
-
-  if (tid == 0) {
-    mbar_expect_tx(&bar_map, 4 * BLK);
-    tma_load_3d(sB, &tmB, &bar_map, 0, t0, b);
-    tma_load_3d(sB + BLK, &tmB, &bar_map, 64, t0, b);
-    tma_load_3d(sC, &tmC, &bar_map, 0, t0, b);
-    tma_load_3d(sC + BLK, &tmC, &bar_map, 64, t0, b);
-    for (int i = 0; i < 2 && i < Hl; ++i) {
-      mbar_expect_tx(&bar_x[i], 2 * BLK);
-      tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], (h0 + i) * TC_G, t0, b);
-      tma_load_2d(sS + i * BLK, &tmS, &bar_x[i], 0, (int)(srow0 + i) * TC_N);
-    }
-    if (wait_or_abort(&bar_map, 0, abort_flag)) {
-      tc_fence_after_sync();
-      const uint32_t ac = smem_u32(sC), bb = smem_u32(sB);
-      const uint32_t id = idesc_bf16(128, 128, 0, 0);
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_CB, desc_k(ac, ks), desc_k(bb, ks), id, ks > 0 ? 1u : 0u);
-      umma_commit(&bar_cb);
-    }
-  }
-  __syncthreads();
-  bool cb_ok = wait_warp(&bar_cb, 0, abort_flag);
-  tc_fence_after_sync();
+  const uint32_t TM_CB = 0, TM_ACC = 128;      // accumulator set j: Y1 at TM_ACC + 128 j, Y2 64 columns further
   const uint32_t idesc_y = idesc_bf16(128, 64, 0, 1);
-  __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(a.y);
+  bool dead = false;
 
-  // Per-head rows are staged two heads ahead by cp.async into clk[h % 3]: [dA | w | wd] x 128 tokens and the skip
-  // coefficients D[h, 0..63].  One commit group per head (empty past the last head), so that "all but the newest
-  // group" always means "up to head h + 1".
-  const int64_t ckv = ((int64_t)b * a.L + t0 + min(tid, Tv - 1)) * H + h0;   // a mapped address for every thread
-  auto stage_clocks = [&](int hh) {
-    if (hh < Hl) {
-      float* sc = clk + (hh % 3) * OUT_CLK_LD;
-      if (tid < 128) {
-        const bool ok = tid < Tv;
-        cp_async4z(sc + tid, a.dA + ckv + hh, ok);
-        cp_async4z(sc + 128 + tid, a.w + ckv + hh, ok);
-        cp_async4z(sc + 256 + tid, a.wd + ckv + hh, ok);
-      } else if (tid < 128 + TC_G) {
-        const bool ok = a.Dg != nullptr;
-        cp_async4z(sc + 384 + tid - 128, ok ? a.Dg + (h0 + hh) * TC_G + tid - 128 : a.dA, ok);
+  if (role == 3) {
+    if (warp == 12 && lane == 0) {
+      // ---- producer ----
+      mbar_expect_tx(&bars.map, 4 * BLK);
+      tma_load_3d(sMs, &tmB, &bars.map, 0, t0, b);
+      tma_load_3d(sMs + BLK, &tmB, &bars.map, 64, t0, b);
+      tma_load_3d(sC, &tmC, &bars.map, 0, t0, b);
+      tma_load_3d(sC + BLK, &tmC, &bars.map, 64, t0, b);
+      for (int h = 0; h < Hl; ++h) {
+        const int su = h % WS_XSTAGES, ss = h % WS_SSTAGES;
+        if (h >= WS_SSTAGES && !lane_wait(&bars.s_empty[ss], (uint32_t)((h / WS_SSTAGES - 1) & 1), abort_flag, dead)) break;
+        mbar_expect_tx(&bars.s_full[ss], BLK);
+        tma_load_2d(sS + ss * BLK, &tmS, &bars.s_full[ss], 0, (int)(srow0 + h) * TC_N);
+        if (h >= WS_XSTAGES && !lane_wait(&bars.u_empty[su], (uint32_t)((h / WS_XSTAGES - 1) & 1), abort_flag, dead)) break;
+        mbar_expect_tx(&bars.u_full[su], BLK);
+        tma_load_3d(sX + su * BLK, &tmU, &bars.u_full[su], (h0 + h) * TC_G, t0, b);
+      }
+    } else if (warp == 13 && lane == 0) {
+      // ---- MMA issuer ----
+      if (lane_wait(&bars.map, 0, abort_flag, dead)) {
+        tc_fence_after_sync();
+        const uint32_t ac = smem_u32(sC), bb = smem_u32(sMs);
+        const uint32_t id = idesc_bf16(128, 128, 0, 0);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_CB, desc_k(ac, ks), desc_k(bb, ks), id, ks > 0 ? 1u : 0u);
+        umma_commit(&bars.cb);
+      }
+      for (int h = 0; h < Hl && !dead; ++h) {
+        const int su = h % WS_XSTAGES, ss = h % WS_SSTAGES, k = h & 1;
+        const uint32_t acc = tbase + TM_ACC + 128u * k;
+        if (!lane_wait(&bars.s_full[ss], (uint32_t)((h / WS_SSTAGES) & 1), abort_flag, dead)) break;
+        if (h >= 2 && !lane_wait(&bars.acc_empty[k], (uint32_t)(((h >> 1) - 1) & 1), abort_flag, dead)) break;
+        tc_fence_after_sync();
+        // the inter-chunk part C Sin needs no mask: it runs while the mask group still works on this head
+        const uint32_t ac = smem_u32(sC), bs = smem_u32(sS + ss * BLK);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(acc + 64, desc_k(ac, ks), desc_mn(bs, ks), idesc_y, ks > 0 ? 1u : 0u);
+        umma_commit(&bars.s_empty[ss]);    // the state tile may be reloaded
+        if (!lane_wait(&bars.u_full[su], (uint32_t)((h / WS_XSTAGES) & 1), abort_flag, dead)) break;
+        if (!lane_wait(&bars.ms_full[k], (uint32_t)((h >> 1) & 1), abort_flag, dead)) break;
+        tc_fence_after_sync();
+        const uint32_t am = smem_u32(sMs + k * 2 * BLK), bx = smem_u32(sX + su * BLK);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(acc, desc_k(am, ks), desc_mn(bx, ks), idesc_y, ks > 0 ? 1u : 0u);
+        umma_commit(&bars.ms_empty[k]);    // the masked-score tile may be rewritten
+        umma_commit(&bars.acc_full[k]);    // both products of this head are in TMEM
       }
     }
-    cp_async_commit();
-  };
-  // Two block-wide barriers per head.  The prefix of head h + 1 is formed beside the work of head h: the warp scans in
-  // the interval of the mask pass, cs | fs | fw (csb[(h + 1) & 1]) in the interval of the MMA wait and read-out.
-  float x_n = 0.f, tot_n = 0.f, w_n = 0.f;
-  auto warp_scan = [&](int hh) {           // warps 0..3: inclusive scan of the steps of head hh inside the warp
-    if (warp < 4) {
-      const float* sc = clk + (hh % 3) * OUT_CLK_LD;
-      float x = sc[tid];
-      w_n = sc[128 + tid];
+    __syncwarp();
+  } else if (role == 0) {
+    // ---- read-out: y = Y1 + a_t Y2 + D u, written over the head's drive tile and sent off as one TMA store ----
+    for (int h = 0; h < Hl; ++h) {
+      const int su = h % WS_XSTAGES, k = h & 1;
+      const bool ok = role_wait(&bars.acc_full[k], (uint32_t)((h >> 1) & 1), abort_flag, dead);
+      if (ok) {
+        tc_fence_after_sync();
+        const float at = atb[(h % WS_AT_RING) * 128 + t];
+        const float* dgs = dgb + (h % WS_AT_RING) * 64;
+        uint8_t* tile = sX + su * BLK;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r1[32], r2[32];
+          tmem_ld32(tmem_addr(tbase, q * 32, TM_ACC + 128u * k + half * 32), r1);
+          tmem_ld32(tmem_addr(tbase, q * 32, TM_ACC + 128u * k + 64 + half * 32), r2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            uint4* slot = reinterpret_cast<uint4*>(tile + sw128_offset(t, half * 4 + k4));
+            const uint4 uv = *slot;
+            const uint32_t* up = reinterpret_cast<const uint32_t*>(&uv);
+            const float4 dlo = *reinterpret_cast<const float4*>(dgs + half * 32 + k4 * 8);
+            const float4 dhi = *reinterpret_cast<const float4*>(dgs + half * 32 + k4 * 8 + 4);
+            const float dd[8] = {dlo.x, dlo.y, dlo.z, dlo.w, dhi.x, dhi.y, dhi.z, dhi.w};
+            uint32_t outp[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = k4 * 8 + e * 2;
+              float u0, u1;
+              unpack_bf16(up[e], u0, u1);
+              const float y0 = fmaf(dd[2 * e], u0, fmaf(at, __uint_as_float(r2[i]), __uint_as_float(r1[i])));
+              const float y1 = fmaf(dd[2 * e + 1], u1, fmaf(at, __uint_as_float(r2[i + 1]), __uint_as_float(r1[i + 1])));
+              outp[e] = pack_bf16(y0, y1);
+            }
+            *slot = make_uint4(outp[0], outp[1], outp[2], outp[3]);
+          }
+        }
+      }
+      // the accumulator set is free again (arrivals also on the wind-down path, so nothing waits for them)
+      warp_arrive(&bars.acc_empty[k], true);
+      if (tid == 0) {
+        bulk_wait_group_read<0>();         // the store of head h - 1 has read its tile: that drive stage may be reloaded
+        if (h > 0) mbar_arrive(&bars.u_empty[(h - 1) % WS_XSTAGES]);
+      }
+      named_bar_sync(3, 128);              // every row of the y tile is written (and fenced for the async proxy)
+      if (tid == 0 && ok) {
+        tma_store_3d(&tmY, sX + su * BLK, (h0 + h) * TC_G, t0, b);   // rows past the end of the sequence are clipped
+        bulk_commit_group();
+      }
+    }
+    if (tid == 0) bulk_wait_group<0>();
+  } else {
+    // ---- mask group k: heads k, k + 2, ... ----
+    const int k = role - 1, bar_id = 1 + k;
+    float* cs = csb + k * 512;
+    float *fs = cs + 128, *fw = cs + 256, *wv = cs + 384;
+    float* wsum = wsumb + k * 8;
+    uint8_t* tile = sMs + k * 2 * BLK;
+    const bool cb_ok = role_wait(&bars.cb, 0, abort_flag, dead);   // CB is in TMEM; the B tile (group 0's buffer) is free
+    tc_fence_after_sync();
+    // columns above the diagonal never change: zero the slabs j > q of this row once
+    for (int j = q + 1; j < 4; ++j) {
+      uint8_t* dstb = tile + (j >> 1) * BLK;
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) *reinterpret_cast<uint4*>(dstb + sw128_offset(t, (j & 1) * 4 + kk)) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    const int64_t ck = ((int64_t)b * a.L + t0 + min(t, Tv - 1)) * H + h0;   // a mapped address for every thread
+    const bool live = t < Tv;
+    const bool dg_lane = a.Dg != nullptr && t < TC_G / 4;           // 16 threads carry the head's skip coefficients
+    float d_n = 0.f, w_n = 0.f, wd_n = 0.f;
+    float4 dg_n = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (k < Hl && live) {
+      d_n = a.dA[ck + k];
+      w_n = a.w[ck + k];
+      wd_n = a.wd[ck + k];
+    }
+    if (k < Hl && dg_lane) dg_n = *reinterpret_cast<const float4*>(a.Dg + (h0 + k) * TC_G + t * 4);
+    for (int h = k; h < Hl; h += 2) {
+      const float wt = w_n, wdt_t = wd_n;
+      const float4 dg = dg_n;
+      // inclusive prefix of the steps over the 128 tokens (warp scan + the four warp totals)
+      float x = d_n;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
-        float y = __shfl_up_sync(0xffffffffu, x, o);
+        const float y = __shfl_up_sync(0xffffffffu, x, o);
         if (lane >= o) x += y;
       }
-      x_n = x;
-      tot_n = __shfl_sync(0xffffffffu, x, 31);
-      if (lane == 31) wsum[warp] = x;
-    }
-  };
-  auto token_factors = [&](int hh) {       // after the barrier that publishes wsum
-    if (warp < 4) {
-      const float w0 = wsum[0], w1 = wsum[1], w2 = wsum[2];
-      const float off = warp == 0 ? 0.f : (warp == 1 ? w0 : (warp == 2 ? w0 + w1 : (w0 + w1) + w2));
-      float* o = csb + (hh & 1) * 384;
-      const float f = __expf(tot_n - x_n);
-      o[tid] = x_n + off;
-      o[128 + tid] = f;
-      o[256 + tid] = f * w_n;
-    }
-  };
-  stage_clocks(0);
-  stage_clocks(1);
-  cp_async_wait_group<1>();
-  warp_scan(0);
-  __syncthreads();
-  token_factors(0);
-  __syncthreads();
-  for (int h = 0; h < Hl; ++h) {
-    const int buf = h & 1;
-    const float* sc = clk + (h % 3) * OUT_CLK_LD;
-    const float *wv = sc + 128, *wdv = sc + 256, *dgs = sc + 384;
-    const float *cs = csb + buf * 384, *fw = cs + 256;
-    stage_clocks(h + 2);                   // slot (h + 2) % 3: its readers (head h - 1) finished before the last barrier
-    // The inter-chunk part C Sin of this head needs no mask: it runs under the mask pass.  The per-head MMAs and TMA
-    // refills are issued by thread 128, whose warp (rows 0..31, slabs 2 and 3) has no mask work.
-    bool x_ok = false;
-    if (tid == ISSUER && !*abort_flag) {
-      x_ok = wait_or_abort(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag);
-      if (x_ok) {
-        tc_fence_after_sync();
-        const uint32_t ac = smem_u32(sC), bs = smem_u32(sS + buf * BLK);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_Y2, desc_k(ac, ks), desc_mn(bs, ks), idesc_y, ks > 0 ? 1u : 0u);
+      const float tot = __shfl_sync(0xffffffffu, x, 31);
+      if (lane == 31) wsum[q] = x;
+      if (h + 2 < Hl) {                    // rows of this group's next head, in flight during the mask pass
+        if (live) {
+          d_n = a.dA[ck + h + 2];
+          w_n = a.w[ck + h + 2];
+          wd_n = a.wd[ck + h + 2];
+        }
+        if (dg_lane) dg_n = *reinterpret_cast<const float4*>(a.Dg + (h0 + h + 2) * TC_G + t * 4);
       }
-    }
-    cp_async_wait_group<1>();              // this thread's share of the rows of head h + 1
-    if (h + 1 < Hl) warp_scan(h + 1);
-    // masked scores: this thread owns row t, column slabs 2*wg and 2*wg+1 (32 columns each)
-    if (cb_ok) {
-      const float cst = cs[t], wdt_t = wdv[t];
-#pragma unroll
-      for (int jj = 0; jj < 2; ++jj) {
-        const int j = wg * 2 + jj;
-        uint32_t pk[16];
-        if (j > q) {   // the whole warp sits above the diagonal for this slab
-#pragma unroll
-          for (int k = 0; k < 16; ++k) pk[k] = 0u;
-        } else {
+      named_bar_sync(bar_id, 128);
+      {
+        const float w0 = wsum[0], w1 = wsum[1], w2 = wsum[2];
+        const float off = q == 0 ? 0.f : (q == 1 ? w0 : (q == 2 ? w0 + w1 : (w0 + w1) + w2));
+        const float csv = x + off, f = __expf(tot - x);
+        cs[t] = csv;
+        fs[t] = f;
+        fw[t] = f * wt;
+        wv[t] = wt;
+        atb[(h % WS_AT_RING) * 128 + t] = __expf(csv);
+        if (t < TC_G / 4) *reinterpret_cast<float4*>(dgb + (h % WS_AT_RING) * 64 + t * 4) = dg;
+      }
+      named_bar_sync(bar_id, 128);
+      bool go = cb_ok;
+      if (h >= 2) go = role_wait(&bars.ms_empty[k], (uint32_t)(((h >> 1) - 1) & 1), abort_flag, dead) && go;
+      if (go) {
+        const float cst = cs[t];
+        for (int j = 0; j <= q; ++j) {
           uint32_t r[32];
           tmem_ld32(tmem_addr(tbase, q * 32, TM_CB + j * 32), r);
           tmem_ld_wait();
-          float v[32];
+          uint32_t pk[16];
           if (j < q) {
             // slab wholly below the diagonal: decay = (row factor) x (column factor), no exponential per element
             const float g = __expf(cst - cs[j * 32 + 31]);
 #pragma unroll
             for (int i4 = 0; i4 < 8; ++i4) {
               const float4 f4 = *reinterpret_cast<const float4*>(fw + j * 32 + i4 * 4);
-              v[i4 * 4] = __uint_as_float(r[i4 * 4]) * (g * f4.x);
-              v[i4 * 4 + 1] = __uint_as_float(r[i4 * 4 + 1]) * (g * f4.y);
-              v[i4 * 4 + 2] = __uint_as_float(r[i4 * 4 + 2]) * (g * f4.z);
-              v[i4 * 4 + 3] = __uint_as_float(r[i4 * 4 + 3]) * (g * f4.w);
+              pk[i4 * 2] = pack_bf16(__uint_as_float(r[i4 * 4]) * (g * f4.x), __uint_as_float(r[i4 * 4 + 1]) * (g * f4.y));
+              pk[i4 * 2 + 1] = pack_bf16(__uint_as_float(r[i4 * 4 + 2]) * (g * f4.z), __uint_as_float(r[i4 * 4 + 3]) * (g * f4.w));
             }
           } else {
-          // diagonal slab, branch-free (selects only): the 32 exponentials are independent and overlap in the pipeline
+            // diagonal slab, branch-free (selects only): the 32 exponentials are independent and overlap in the pipeline
 #pragma unroll
-          for (int i4 = 0; i4 < 8; ++i4) {
-            const float4 c4 = *reinterpret_cast<const float4*>(cs + j * 32 + i4 * 4);
-            const float4 w4 = *reinterpret_cast<const float4*>(wv + j * 32 + i4 * 4);
-            const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, wq[4] = {w4.x, w4.y, w4.z, w4.w};
+            for (int i4 = 0; i4 < 8; ++i4) {
+              const float4 c4 = *reinterpret_cast<const float4*>(cs + j * 32 + i4 * 4);
+              const float4 w4 = *reinterpret_cast<const float4*>(wv + j * 32 + i4 * 4);
+              const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, wq[4] = {w4.x, w4.y, w4.z, w4.w};
+              float v[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i = i4 * 4 + e, s = j * 32 + i;
-              const float E = __expf(cst - cv[e]);          // may overflow above the diagonal: selected away below
-              const float wgt = s < t ? E * wq[e] : (s == t ? wdt_t : 0.f);
-              v[i] = __uint_as_float(r[i]) * wgt;
+              for (int e = 0; e < 4; ++e) {
+                const int i = i4 * 4 + e, s = j * 32 + i;
+                const float E = __expf(cst - cv[e]);          // may overflow above the diagonal: selected away below
+                const float wgt = s < t ? E * wq[e] : (s == t ? wdt_t : 0.f);
+                v[e] = __uint_as_float(r[i]) * wgt;
+              }
+              pk[i4 * 2] = pack_bf16(v[0], v[1]);
+              pk[i4 * 2 + 1] = pack_bf16(v[2], v[3]);
             }
           }
-          }
+          uint8_t* dstb = tile + (j >> 1) * BLK;
 #pragma unroll
-          for (int k = 0; k < 16; ++k) pk[k] = pack_bf16(v[2 * k], v[2 * k + 1]);
-        }
-        uint8_t* dstb = sMs + (j >> 1) * BLK;
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          *reinterpret_cast<uint4*>(dstb + sw128_offset(t, (j & 1) * 4 + k)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
-      }
-    }
-    tc_fence_before_sync();
-    fence_proxy_async();
-    __syncthreads();
-    if (tid == ISSUER && x_ok && !*abort_flag) {
-      tc_fence_after_sync();
-      const uint32_t am = smem_u32(sMs), bx = smem_u32(sX + buf * BLK);
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_Y1, desc_k(am, ks), desc_mn(bx, ks), idesc_y, ks > 0 ? 1u : 0u);
-      umma_commit(&bar_y);   // covers the C Sin product issued at the top of the head too
-    }
-    if (h + 1 < Hl) token_factors(h + 1);
-    if (wait_warp(&bar_y, (uint32_t)(h & 1), abort_flag)) {
-      tc_fence_after_sync();
-      uint32_t r1[32], r2[32];
-      tmem_ld32(tmem_addr(tbase, q * 32, TM_Y1 + wg * 32), r1);
-      tmem_ld32(tmem_addr(tbase, q * 32, TM_Y2 + wg * 32), r2);
-      tmem_ld_wait();
-      const float at = __expf(cs[t]);
-      uint32_t outp[16];
-#pragma unroll
-      for (int k4 = 0; k4 < 4; ++k4) {
-        uint4 uv = *reinterpret_cast<const uint4*>(sX + buf * BLK + sw128_offset(t, wg * 4 + k4));
-        const uint32_t* up = reinterpret_cast<const uint32_t*>(&uv);
-        const float4 dlo = *reinterpret_cast<const float4*>(dgs + wg * 32 + k4 * 8);
-        const float4 dhi = *reinterpret_cast<const float4*>(dgs + wg * 32 + k4 * 8 + 4);
-        const float dd[8] = {dlo.x, dlo.y, dlo.z, dlo.w, dhi.x, dhi.y, dhi.z, dhi.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int i = k4 * 8 + k * 2;
-          float u0, u1;
-          unpack_bf16(up[k], u0, u1);
-          const float d0 = dd[2 * k], d1 = dd[2 * k + 1];
-          float y0 = __uint_as_float(r1[i]) + at * __uint_as_float(r2[i]) + d0 * u0;
-          float y1 = __uint_as_float(r1[i + 1]) + at * __uint_as_float(r2[i + 1]) + d1 * u1;
-          outp[k4 * 4 + k] = pack_bf16(y0, y1);
+          for (int kk = 0; kk < 4; ++kk)
+            *reinterpret_cast<uint4*>(dstb + sw128_offset(t, (j & 1) * 4 + kk)) = make_uint4(pk[4 * kk], pk[4 * kk + 1], pk[4 * kk + 2], pk[4 * kk + 3]);
         }
       }
-      if (t < Tv) {
-        uint4* dst = reinterpret_cast<uint4*>(yout + ((int64_t)b * a.L + t0 + t) * (int64_t)(H * TC_G) + (h0 + h) * TC_G + wg * 32);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) dst[k] = make_uint4(outp[4 * k], outp[4 * k + 1], outp[4 * k + 2], outp[4 * k + 3]);
-      }
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid == ISSUER && !*abort_flag && h + 2 < Hl) {
-      mbar_expect_tx(&bar_x[buf], 2 * BLK);
-      tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
-      tma_load_2d(sS + buf * BLK, &tmS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
+      warp_arrive(&bars.ms_full[k], true);
     }
   }
+  tc_fence_before_sync();
   __syncthreads();
   if (tid == 0 && *abort_flag && a.status) atomicExch(a.status, 1);
-  if (warp == 0) tmem_dealloc(tbase, 256);
+  if (warp == 0) tmem_dealloc(tbase, 512);
 }
 
 // fp32 [128 n][64 p] state tile -> bf16 swizzled block; optionally accumulates sum(src * other) per thread
@@ -1127,8 +1174,8 @@ static int map_rows(CUtensorMap* m, const void* base, int cols, int64_t token_st
   return make_tensor_map_bf16(m, base, 3, dims, str, box);
 }
 
-constexpr int SMEM_STATE = 6 * BLK + 2048 + 1024;
-constexpr int SMEM_OUT = 10 * BLK + 9216 + 1024;
+constexpr int SMEM_STATE = (8 + ST_STAGES) * BLK + 64 + 1024;
+constexpr int SMEM_OUT = (6 + WS_XSTAGES + WS_SSTAGES) * BLK + (1024 + WS_AT_RING * 192 + 16) * 4 + 1024;
 
 // [B*nc*H*128 rows][64 p] bfloat16 view of a state-tile buffer: one [128 x 64] box per (batch, chunk, head)
 static int map_state(CUtensorMap* m, const void* base, const ScanArgs& a) {
@@ -1142,9 +1189,21 @@ static int map_state(CUtensorMap* m, const void* base, const ScanArgs& a) {
   return make_tensor_map_bf16(m, base, 2, dims, str, box);
 }
 
+// [B*nc*H*128 rows][64 p] float32 view of a state buffer, written as [128 x 32] boxes
+static int map_state_f32(CUtensorMap* m, const void* base, const ScanArgs& a) {
+  const uint64_t rows = (uint64_t)a.B * a.nc * a.H * TC_N;
+  ORBIT_REQUIRE(rows < (1ull << 31), ERR_UNSUPPORTED, "state buffer of %llu rows exceeds the tensor-map coordinate range",
+                (unsigned long long)rows);
+  uint64_t dims[2] = {(uint64_t)TC_G, rows};
+  uint64_t str[1] = {(uint64_t)TC_G * 4};
+  uint32_t box[2] = {32, 128};
+  return make_tensor_map_f32(m, base, 2, dims, str, box);
+}
+
 static int launch_state(const ScanArgs& a, int mode, cudaStream_t st) {
-  CUtensorMap tmM, tmX;
+  CUtensorMap tmM, tmX, tmZ;
   int rc;
+  if ((rc = map_state_f32(&tmZ, mode == 0 ? a.Sin : a.dS, a)) != OK) return rc;
   if (mode == 0) {
     if ((rc = map_rows(&tmM, a.Bhat, TC_N, a.b_ts, a.L, a.B)) != OK) return rc;
     if ((rc = map_rows(&tmX, a.u, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
@@ -1154,7 +1213,7 @@ static int launch_state(const ScanArgs& a, int mode, cudaStream_t st) {
     if ((rc = map_rows(&tmX, a.dy, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
   }
   ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_STATE));
-  tc_chunk_state_kernel<<<dim3(a.nc, a.B), TC_THREADS, SMEM_STATE, st>>>(tmM, tmX, a, mode);
+  tc_chunk_state_kernel<<<dim3(a.nc, a.B), ST_THREADS, SMEM_STATE, st>>>(tmM, tmX, tmZ, a, mode);
   ORBIT_CHECK_LAUNCH("tc_chunk_state_kernel");
   return OK;
 }
@@ -1168,14 +1227,16 @@ int tc_launch_chunk_dstate(const ScanArgs& a, cudaStream_t st) {
 
 int tc_launch_chunk_out(const ScanArgs& a, cudaStream_t st) {
   if (mimo_tc_geometry(a.R, a.O, a.G, a.N)) return mimo_tc_launch_out(a, st);
-  CUtensorMap tmB, tmC, tmU, tmS;
+  CUtensorMap tmB, tmC, tmU, tmS, tmY;
   int rc;
+  ORBIT_REQUIRE(aligned16(a.y), ERR_UNSUPPORTED, "y must be 16-byte aligned");
   if ((rc = map_rows(&tmB, a.Bhat, TC_N, a.b_ts, a.L, a.B)) != OK) return rc;
   if ((rc = map_rows(&tmC, a.Chat, TC_N, a.c_ts, a.L, a.B)) != OK) return rc;
   if ((rc = map_rows(&tmU, a.u, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
+  if ((rc = map_rows(&tmY, a.y, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
   if ((rc = map_state(&tmS, a.Sin16, a)) != OK) return rc;
   ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_OUT));
-  tc_chunk_out_kernel<<<dim3(a.nc, a.B, head_split(a)), TC_THREADS, SMEM_OUT, st>>>(tmB, tmC, tmU, tmS, a);
+  tc_chunk_out_kernel<<<dim3(a.nc, a.B, head_split(a)), WS_THREADS, SMEM_OUT, st>>>(tmB, tmC, tmU, tmS, tmY, a);
   ORBIT_CHECK_LAUNCH("tc_chunk_out_kernel");
   return OK;
 }

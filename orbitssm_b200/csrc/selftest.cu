@@ -3,6 +3,7 @@
 //   mode bit 0: A is MN-major (A given as [K, 128], the M axis contiguous)     else K-major (A given as [128, K])
 //   mode bit 1: B is MN-major (B given as [K, N],  the N axis contiguous)      else K-major (B given as [N, K])
 //   mode bit 2: A reaches shared memory through registers (manual 128-byte swizzle) instead of TMA (K-major only)
+//   mode bit 3: A is staged in TMEM (packed bf16 pairs written with tcgen05.st) instead of shared memory (K-major only)
 #include "common.cuh"
 #include "tc_common.cuh"
 #include "../../include/orbit_b200.h"
@@ -23,8 +24,8 @@ static EncodeTiledFn get_encode() {
   return fn;
 }
 
-int make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                         const uint32_t* box) {
+static int make_tensor_map(CUtensorMap* out, CUtensorMapDataType dt, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box) {
   EncodeTiledFn enc = get_encode();
   ORBIT_REQUIRE(enc != nullptr, ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   ORBIT_REQUIRE(rank >= 1 && rank <= 5, ERR_BAD_ARG, "tensor map rank %d", rank);
@@ -41,11 +42,20 @@ int make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uin
       gs[i - 1] = strides_bytes[i - 1];
     }
   }
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gd, gs, bx, es,
+  CUresult r = enc(out, dt, (cuuint32_t)rank, const_cast<void*>(base), gd, gs, bx, es,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   ORBIT_REQUIRE(r == CUDA_SUCCESS, ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
   return OK;
+}
+
+int make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                         const uint32_t* box) {
+  return make_tensor_map(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, rank, dims, strides_bytes, box);
+}
+int make_tensor_map_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                        const uint32_t* box) {
+  return make_tensor_map(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, rank, dims, strides_bytes, box);
 }
 
 __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -60,26 +70,27 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
   __shared__ uint64_t bar_load, bar_mma;
   __shared__ uint32_t tmem_slot;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool a_mn = mode & 1, b_mn = mode & 2, a_manual = mode & 4;
+  const bool a_mn = mode & 1, b_mn = mode & 2, a_manual = mode & 4, a_tmem = mode & 8;
 
   if (tid == 0) {
     mbar_init(&bar_load, 1);
     mbar_init(&bar_mma, 1);
     mbar_fence_init();
   }
-  if (warp == 0) tmem_alloc(&tmem_slot, 128);
+  if (warp == 0) tmem_alloc(&tmem_slot, 256);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tbase = tmem_slot;
+  const uint32_t TM_A = 128;             // A operand in TMEM: K / 2 columns
   bool ok = true;
 
   if (tid == 0) {
     uint32_t bytes = 0;
-    if (!a_manual) bytes += 128 * K * 2;
+    if (!a_manual && !a_tmem) bytes += 128 * K * 2;
     bytes += N * K * 2;
     mbar_expect_tx(&bar_load, bytes);
-    if (!a_manual) {
+    if (!a_manual && !a_tmem) {
       if (!a_mn) for (int kb = 0; kb < K / 64; ++kb) tma_load_2d(sA + kb * 16384, &tmA, &bar_load, kb * 64, 0);
       else for (int mb = 0; mb < 2; ++mb) tma_load_2d(sA + mb * (K * 128), &tmA, &bar_load, mb * 64, 0);
     }
@@ -94,6 +105,21 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
     }
     fence_proxy_async();
   }
+  if (a_tmem) {
+    // thread = row = TMEM lane; 32 bf16 (16 packed columns) per store
+    for (int c0 = 0; c0 < K / 32; ++c0) {
+      uint32_t r[16];
+      const uint4* src = reinterpret_cast<const uint4*>(Ag + (size_t)tid * K + c0 * 32);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 v = src[j];
+        r[4 * j] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
+      }
+      tmem_st16(tmem_addr(tbase, warp * 32, TM_A + c0 * 16), r);
+    }
+    tmem_st_wait();
+    tc_fence_before_sync();
+  }
   __syncthreads();
   if (!mbar_wait(&bar_load, 0)) ok = false;
   tc_fence_after_sync();
@@ -105,7 +131,8 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
                          : smem_desc_sw128(a0 + (ks / 4) * 16384 + (ks % 4) * 32, 16, 1024);
       uint64_t bd = b_mn ? smem_desc_sw128(b0 + ks * 2048, K * 128, 1024)
                          : smem_desc_sw128(b0 + (ks / 4) * (N * 128) + (ks % 4) * 32, 16, 1024);
-      umma_bf16(tbase, ad, bd, idesc, ks > 0 ? 1u : 0u);
+      if (a_tmem) umma_bf16_ta(tbase, tbase + TM_A + ks * 8, bd, idesc, ks > 0 ? 1u : 0u);
+      else umma_bf16(tbase, ad, bd, idesc, ks > 0 ? 1u : 0u);
     }
     umma_commit(&bar_mma);
   }
@@ -125,7 +152,7 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tbase, 128);
+  if (warp == 0) tmem_dealloc(tbase, 256);
 }
 
 // The wind-down every tensor-core kernel of this library performs when a bounded wait runs out, by itself: the CTA
@@ -167,8 +194,9 @@ extern "C" int orbit_selftest_wait_timeout(int* status, int polls, void* stream)
 extern "C" int orbit_selftest_umma(const void* A, const void* B, float* D, int mode, int K, int N, int* status,
                                    void* stream) {
   ORBIT_REQUIRE(A && B && D && status, ERR_BAD_ARG, "orbit_selftest_umma: null pointer");
-  ORBIT_REQUIRE((K == 64 || K == 128) && (N == 64 || N == 128) && mode >= 0 && mode < 8 && !((mode & 4) && (mode & 1)),
-                ERR_UNSUPPORTED, "orbit_selftest_umma: K, N in {64, 128}; manual A is K-major only");
+  ORBIT_REQUIRE((K == 64 || K == 128) && (N == 64 || N == 128) && mode >= 0 && mode < 16 && !((mode & 12) && (mode & 1)) &&
+                    (mode & 12) != 12,
+                ERR_UNSUPPORTED, "orbit_selftest_umma: K, N in {64, 128}; A through registers or TMEM is K-major only");
   CUtensorMap tmA, tmB;
   int rc;
   {

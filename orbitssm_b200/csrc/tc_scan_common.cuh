@@ -105,6 +105,34 @@ __device__ __forceinline__ float sum_low128(float v, float* red) {
   return (red[0] + red[1]) + (red[2] + red[3]);
 }
 
+// ---- warp-specialised kernels: role groups of 128 threads, named barriers, per-warp arrivals -----------------------
+// Named barrier `id` (1..15) over `count` threads; every thread of the participating warps must call it.
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+// One arrival per warp, after the whole warp is done with what the barrier publishes.  `smem_writes`: the warp wrote
+// operand tiles with ordinary stores that a tcgen05.mma or a TMA copy will read.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, bool smem_writes) {
+  if (smem_writes) fence_proxy_async();
+  tc_fence_before_sync();
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+// A role's bounded wait that never leaves its loop: once a wait of this thread's warp has failed (or another role has
+// raised the CTA's abort flag) `dead` stays set, later waits return at once and the caller skips the work but keeps its
+// barrier pattern, so that no other warp is left behind at a named barrier.
+__device__ __forceinline__ bool role_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, bool& dead) {
+  if (dead) return false;
+  if (!wait_warp(bar, parity, abort_flag)) dead = true;
+  return !dead;
+}
+// single-thread form (producer / MMA issuer lanes)
+__device__ __forceinline__ bool lane_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, bool& dead) {
+  if (dead) return false;
+  if (!wait_or_abort(bar, parity, abort_flag)) dead = true;
+  return !dead;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

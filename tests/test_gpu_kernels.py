@@ -178,7 +178,7 @@ def test_scan_chunk_length_is_scheduling_only(T):
 
 
 # ---------------------------------------------------------------------------------------------------- tcgen05 tile
-@pytest.mark.parametrize("mode", [0, 1, 2, 3, 4, 6])
+@pytest.mark.parametrize("mode", [0, 1, 2, 3, 4, 6, 8, 10])
 @pytest.mark.parametrize("K,N", [(64, 64), (128, 64), (128, 128), (64, 128)])
 def test_umma_tile(mode, K, N):
     g = torch.Generator().manual_seed(mode * 100 + K + N)

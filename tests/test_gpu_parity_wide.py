@@ -9,9 +9,12 @@
    mean(a - e) / rms(e); gain: <a - e, e> / <e, e>) not systematically away from zero: a failure needs |mean| >= bound / 4,
    |t| > 3 and |trimmed mean| >= bound / 4 together.
 
-Bounds (normwise relative error): about twice what these kernels measure (y and state 4e-3 .. 6e-3, gradients up to 1.5e-2),
-well inside the reference's own CUDA-vs-oracle bounds for bf16 (y 2.5e-2, gradients 6e-2; reference:
-tests/test_ssd_endpoint.py:252-274, 303, 326).
+Bounds (normwise relative error): about twice what these kernels measure (y 5e-3 .. 6e-3, carried state up to 8e-3, input
+gradient up to 7e-3, parameter gradients up to 1.5e-2), inside the reference's own CUDA-vs-oracle bounds for bf16 (y 2.5e-2,
+gradients 6e-2; reference: tests/test_ssd_endpoint.py:252-274, 303, 326).  Gradients of parameters with a handful of
+elements (per-head scalars, 16 pair frequencies) are sums over every token with heavy cancellation, so their relative
+error has a heavy tail from draw to draw; they follow the reference's typical-scale rule (reference:
+tests/_tolerance.py:1035-1049): median over the draws within the bound (6e-2), no single draw beyond twice that.
 """
 import math
 
@@ -26,7 +29,8 @@ from orbitssm_b200.config import resolve_ssd_spec
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-BOUND_Y, BOUND_G = 1.2e-2, 3e-2
+BOUND_Y, BOUND_H, BOUND_DX, BOUND_G = 1.2e-2, 1.6e-2, 1.4e-2, 3e-2
+SMALL, BOUND_SMALL = 256, 6e-2            # parameters with fewer elements than SMALL: typical-scale rule
 
 
 def rel(a, b):
@@ -71,10 +75,11 @@ def compare(got, want, what):
     """Returns {tensor name: (error, bound)}; asserts every bound."""
     y, h, dx, g = got
     yr, hr, dxr, gr = want
-    out = {"y": (rel(y, yr), BOUND_Y), "hidden_state": (rel(h, hr), BOUND_Y), "dx": (rel(dx, dxr), BOUND_G)}
+    out = {"y": (rel(y, yr), BOUND_Y), "hidden_state": (rel(h, hr), BOUND_H), "dx": (rel(dx, dxr), BOUND_DX)}
     for k, v in gr.items():
         assert k in g, (what, "missing gradient", k)
-        out["d " + k] = (rel(g[k], v), BOUND_G)
+        # a single draw of a small parameter may sit in the tail: twice the typical-scale bound
+        out["d " + k] = (rel(g[k], v), BOUND_G if v.numel() >= SMALL else 2 * BOUND_SMALL)
     print(what, {k: f"{e:.2e}" for k, (e, _) in out.items()})
     bad = {k: e for k, (e, b) in out.items() if not e < b}
     assert not bad, (what, "out of bound", bad)
@@ -121,7 +126,7 @@ def test_bf16_draws_within_bound_and_unbiased(case):
     layer.load_state_dict(rec["state_dict"], strict=True)
     layer = layer.to(DEV)
     B, L, dm = rec["x"].shape
-    pools = {}
+    pools, small = {}, {}
     for draw in range(5):
         g = torch.Generator().manual_seed(1000 + 7919 * draw)
         x = torch.randn(B, L, dm, generator=g).to(torch.bfloat16).float()
@@ -129,10 +134,13 @@ def test_bf16_draws_within_bound_and_unbiased(case):
         gh = torch.randn(B, layer.H, layer.P, layer.N, generator=g)
         got = gpu_run(layer, x, dy, gh)
         want = oracle_run(layer, x, dy, gh)
-        compare(got, want, f"{case} draw {draw}")
-        named = {"y": (got[0], want[0], BOUND_Y), "hidden_state": (got[1], want[1], BOUND_Y), "dx": (got[2], want[2], BOUND_G)}
+        errs = compare(got, want, f"{case} draw {draw}")
         for k, v in want[3].items():
-            if v.numel() >= 256:                      # a bias over a handful of elements is noise
+            if v.numel() < SMALL:
+                small.setdefault(k, []).append(errs["d " + k][0])
+        named = {"y": (got[0], want[0], BOUND_Y), "hidden_state": (got[1], want[1], BOUND_H), "dx": (got[2], want[2], BOUND_DX)}
+        for k, v in want[3].items():
+            if v.numel() >= SMALL:                    # a bias over a handful of elements is noise
                 named["d " + k] = (got[3][k], v, BOUND_G)
         for k, (a, e, b) in named.items():
             add, gain = signed_bias(a, e)
@@ -146,3 +154,5 @@ def test_bf16_draws_within_bound_and_unbiased(case):
             if fails:
                 biased[(k, kind)] = (mean, t, b / 4)
     assert not biased, ("systematic 16-bit bias (mean, t, limit)", biased)
+    off = {k: sorted(v)[len(v) // 2] for k, v in small.items() if not sorted(v)[len(v) // 2] < BOUND_SMALL}
+    assert not off, ("median error of a small parameter's gradient over the draws", off)
