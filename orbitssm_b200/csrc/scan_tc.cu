@@ -21,7 +21,6 @@ using namespace tc;
 
 constexpr int TC_T = 128, TC_N = 128, TC_G = 64;
 constexpr int ISSUER = 128;      // thread that issues the per-head MMAs and TMA refills in the output / score-gradient kernels
-constexpr int GS_CLK_LD = 592;   // floats per staged-clocks buffer of the score-gradient kernel
 
 // ------------------------------------------------------------------------------------------------------------------
 // chunk_state (mode 0):  Z[n,p] = sum_s B[s,n] e_s u[s,p],   e_s = exp(cs_T - cs_s) w_s          -> a.Sin, a.atot
@@ -87,6 +86,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) tc_chunk_state_kernel(const __g
       mbar_expect_tx(&bars.map, 2 * BLK);
       tma_load_3d(sM, &tmM, &bars.map, 0, t0, b);
       tma_load_3d(sM + BLK, &tmM, &bars.map, 64, t0, b);
+#pragma unroll 1
       for (int h = 0; h < H; ++h) {
         const int s = h % ST_STAGES;
         if (h >= ST_STAGES && !lane_wait(&bars.x_empty[s], (uint32_t)((h / ST_STAGES - 1) & 1), abort_flag, dead)) break;
@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) tc_chunk_state_kernel(const __g
       // ---- MMA issuer ----
       const uint32_t idesc = idesc_bf16(128, 64, 1, 1);
       lane_wait(&bars.map, 0, abort_flag, dead);
+#pragma unroll 1
       for (int h = 0; h < H && !dead; ++h) {
         const int k = h & 1;
         if (!lane_wait(&bars.xs_full[k], (uint32_t)((h >> 1) & 1), abort_flag, dead)) break;
@@ -113,6 +114,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) tc_chunk_state_kernel(const __g
   } else if (role == 0) {
     // ---- read-out: accumulator rows (state rows n) -> fp32 tile in shared memory -> two TMA stores per head ----
     const int64_t zrow0 = (((int64_t)b * a.nc + c) * H) * TC_N;
+#pragma unroll 1
     for (int h = 0; h < H; ++h) {
       const int k = h & 1;
       const bool ok = role_wait(&bars.acc_full[k], (uint32_t)((h >> 1) & 1), abort_flag, dead);
@@ -148,6 +150,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) tc_chunk_state_kernel(const __g
       d_n = a.dA[ck];
       w_n = a.w[ck];
     }
+#pragma unroll 1
     for (int h = 0; h < H; ++h) {
       const int s = h % ST_STAGES, k = h & 1;
       const float wt = w_n;
@@ -283,6 +286,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) tc_chunk_out_kernel(const __gri
       tma_load_3d(sMs + BLK, &tmB, &bars.map, 64, t0, b);
       tma_load_3d(sC, &tmC, &bars.map, 0, t0, b);
       tma_load_3d(sC + BLK, &tmC, &bars.map, 64, t0, b);
+#pragma unroll 1
       for (int h = 0; h < Hl; ++h) {
         const int su = h % WS_XSTAGES, ss = h % WS_SSTAGES;
         if (h >= WS_SSTAGES && !lane_wait(&bars.s_empty[ss], (uint32_t)((h / WS_SSTAGES - 1) & 1), abort_flag, dead)) break;
@@ -302,6 +306,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) tc_chunk_out_kernel(const __gri
         for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_CB, desc_k(ac, ks), desc_k(bb, ks), id, ks > 0 ? 1u : 0u);
         umma_commit(&bars.cb);
       }
+#pragma unroll 1
       for (int h = 0; h < Hl && !dead; ++h) {
         const int su = h % WS_XSTAGES, ss = h % WS_SSTAGES, k = h & 1;
         const uint32_t acc = tbase + TM_ACC + 128u * k;
@@ -326,6 +331,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) tc_chunk_out_kernel(const __gri
     __syncwarp();
   } else if (role == 0) {
     // ---- read-out: y = Y1 + a_t Y2 + D u, written over the head's drive tile and sent off as one TMA store ----
+#pragma unroll 1
     for (int h = 0; h < Hl; ++h) {
       const int su = h % WS_XSTAGES, k = h & 1;
       const bool ok = role_wait(&bars.acc_full[k], (uint32_t)((h >> 1) & 1), abort_flag, dead);
@@ -401,6 +407,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) tc_chunk_out_kernel(const __gri
       wd_n = a.wd[ck + k];
     }
     if (k < Hl && dg_lane) dg_n = *reinterpret_cast<const float4*>(a.Dg + (h0 + k) * TC_G + t * 4);
+#pragma unroll 1
     for (int h = k; h < Hl; h += 2) {
       const float wt = w_n, wdt_t = wd_n;
       const float4 dg = dg_n;
@@ -609,6 +616,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
   __syncthreads();
   token_factor(0, x_cur, wt_cur);
   __syncthreads();
+#pragma unroll 1
   for (int h = 0; h < Hl; ++h) {
     const int buf = h & 1;
     const float *fa = fab + buf * 256, *fe = fa + 128;
@@ -750,53 +758,90 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
 //   d cs, dw, dwd from row / column sums of K o E, da (part 1), de, datot (part 1);  d dA = reverse prefix of d cs
 //   dScoreSum += dM o W   (registers, summed over heads)
 // and after the head loop   dC = dScoreSum B + dCx,   dB = dScoreSum^T C + dBx   (dCx, dBx from part 1).
+// The write weight w_s of a column and the diagonal of W are kept out of the masked-score operand: with E' = E strictly
+// below the diagonal (zero on and above it) and X1 = (CB o E')^T dy from the tensor cores,
+//   sum_{t>=s} (CB o W)[t,s] dy[t,p] = w_s X1[s,p] + wd_s CB[s,s] dy[s,p],
+//   column sums of K o E:  sum_{t>s} K[t,s] E[t,s] = sum_p u[s,p] X1[s,p],      K[s,s] = CB[s,s] sum_p dy[s,p] u[s,p],
+// so every sum over t is a row dot product of the thread that owns row s of the accumulator, and the score pass keeps
+// only sums along its own rows.
+//
+// Warp-specialised, 16 warps that meet only through mbarriers, so that consecutive heads overlap:
+//   warps 0..3    du group: accumulators of MMA group B -> du (written over the head's drive tile, one TMA store), de, dD
+//   warps 4..11   score group: dM and CB from TMEM -> masked-score tile (shared memory), row / column sums, the summed
+//                 score gradient in registers; warp 4 + 4 g + q owns row quarter q, column slabs 2 g and 2 g + 1
+//   warp 12       producer: one lane issues the TMA loads (drive and dy: 3 stages, adjoint state: 2 stages)
+//   warp 13       MMA issuer: one lane; group A (dM) of head h + 1 is issued ahead of group B of head h
+//   warps 14, 15  token warps (two tokens per thread): clock prefix and split decay factors two heads ahead, then the
+//                 per-token clock gradients of head h from the partial sums of the other groups
 // ------------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(const __grid_constant__ CUtensorMap tmB,
-                                                                             const __grid_constant__ CUtensorMap tmC,
-                                                                             const __grid_constant__ CUtensorMap tmU,
-                                                                             const __grid_constant__ CUtensorMap tmDY,
-                                                                             const __grid_constant__ CUtensorMap tmDS,
-                                                                             const ScanArgs a) {
+constexpr int GS_THREADS = 512;
+constexpr int GS_XSTAGES = 3;
+constexpr int GS_ROWS = 3;              // ring of per-head rows (prefix, factors, part-1 results, skip coefficients)
+constexpr int GS_ROW_LD = 840;          // floats per ring slot: cs | fs | fw | w | wd | da (128 each), D (64), datot, pad
+
+struct GScoreBars {
+  uint64_t map, cb, x_full[GS_XSTAGES], x_empty[GS_XSTAGES], s_full[2], s_empty[2], rows_full[GS_ROWS], dm_full, dm_empty,
+      ms_full, ms_empty, dx_full, dx_empty, part_full[2], part_empty[2], fin_full, fin_c, fin_done;
+};
+
+__global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(const __grid_constant__ CUtensorMap tmB,
+                                                                              const __grid_constant__ CUtensorMap tmC,
+                                                                              const __grid_constant__ CUtensorMap tmU,
+                                                                              const __grid_constant__ CUtensorMap tmDY,
+                                                                              const __grid_constant__ CUtensorMap tmDS,
+                                                                              const __grid_constant__ CUtensorMap tmDU,
+                                                                              const ScanArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
-  uint8_t* sB = sm;                      // 2 blocks
-  uint8_t* sC = sm + 2 * BLK;            // 2 blocks
-  uint8_t* sX = sm + 4 * BLK;            // 2 buffers
-  uint8_t* sDY = sm + 6 * BLK;           // 2 buffers
-  uint8_t* sMs = sm + 8 * BLK;           // masked scores, later the summed score gradient; 2 blocks
-  uint8_t* sdS = sm + 10 * BLK;          // dSo bf16 [n][p], 2 buffers
-  float* csb = reinterpret_cast<float*>(sm + 12 * BLK);   // [2][cs | fs | fw] x 128: prefix and split decay factors,
-                                                          // buffer h & 1 (filled during the previous head)
-  float* rowpart = csb + 768;            // [2][128]
-  float* colpart = rowpart + 256;        // [4][128]
-  float* depart = colpart + 512;         // [2][128]
-  float* kdiag = depart + 256;           // [128]
-  float* ddpart = kdiag + 128;           // [4][64]
-  float* gcs = ddpart + 256;             // [128]
-  float* wsum = gcs + 128;               // 8
-  float* red = wsum + 8;                 // 8
-  float* wsum2 = red + 8;                // 8 (prefix of the next head, warps 4..7)
-  float* clk = wsum2 + 8;                // [2][GS_CLK_LD] per-head rows staged one head ahead (see stage_clocks)
-  __shared__ uint64_t bar_map, bar_x[2], bar_cb, bar_a, bar_b;
+  uint8_t* sB = sm;                      // B tile, 2 blocks
+  uint8_t* sMs = sm + 2 * BLK;           // C tile first; then masked scores [128 t][128 s]; at the end the summed score gradient
+  uint8_t* sX = sm + 4 * BLK;            // drive tiles (later, in place, du tiles), GS_XSTAGES buffers
+  uint8_t* sDY = sm + (4 + GS_XSTAGES) * BLK;   // dy tiles, GS_XSTAGES buffers
+  uint8_t* sdS = sm + (4 + 2 * GS_XSTAGES) * BLK;   // dSo bf16 [n][p], 2 buffers; at the end the C tile again
+  float* rows = reinterpret_cast<float*>(sm + (6 + 2 * GS_XSTAGES) * BLK);   // [GS_ROWS][GS_ROW_LD]
+  float* rowpart = rows + GS_ROWS * GS_ROW_LD;   // [2][2][128] row sums of K o W per score half
+  float* colsum = rowpart + 512;         // [2][128] column sums of K o E (du group)
+  float* depart = colsum + 256;          // [2][128] de (du group)
+  float* kdiag = depart + 256;           // [2][128] K[s,s] (du group)
+  float* ddpart = kdiag + 256;           // [2][4][64] dD partial sums per row quarter (du group)
+  float* cbd = ddpart + 512;             // [128] CB[s,s] of this chunk
+  float* tkred = cbd + 128;              // token warps: [16] scratch of their reductions
+  __shared__ GScoreBars bars;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = warp & 3, wg = warp >> 2;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = warp & 3;
   const int c = blockIdx.x, b = blockIdx.y, t0 = c * TC_T;
   const int Tv = min(TC_T, a.L - t0);
   const int H = a.H;
   // heads [h0, h0 + Hl) of this (batch, chunk): blockIdx.z splits the head loop (gradients of head-shared maps then go
   // to per-split partial buffers); `h` below counts from h0
   const int nsplit = gridDim.z, Hl = H / nsplit, h0 = blockIdx.z * Hl;
-  const int t = q * 32 + lane;
+  const int t = q * 32 + lane;           // token row (TMEM lane) of the du and score groups
   const int64_t srow0 = ((int64_t)b * a.nc + c) * H + h0;
 
   if (tid == 0) {
-    mbar_init(&bar_map, 1);
-    mbar_init(&bar_x[0], 1);
-    mbar_init(&bar_x[1], 1);
-    mbar_init(&bar_cb, 1);
-    mbar_init(&bar_a, 1);
-    mbar_init(&bar_b, 1);
+    mbar_init(&bars.map, 1);
+    mbar_init(&bars.cb, 1);
+    for (int i = 0; i < GS_XSTAGES; ++i) {
+      mbar_init(&bars.x_full[i], 1);
+      mbar_init(&bars.x_empty[i], 1);
+    }
+    for (int i = 0; i < GS_ROWS; ++i) mbar_init(&bars.rows_full[i], 2);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars.s_full[i], 1);
+      mbar_init(&bars.s_empty[i], 1);
+      mbar_init(&bars.part_full[i], 12);
+      mbar_init(&bars.part_empty[i], 2);
+    }
+    mbar_init(&bars.dm_full, 1);
+    mbar_init(&bars.dm_empty, 8);
+    mbar_init(&bars.ms_full, 8);
+    mbar_init(&bars.ms_empty, 1);
+    mbar_init(&bars.dx_full, 1);
+    mbar_init(&bars.dx_empty, 4);
+    mbar_init(&bars.fin_full, 8);
+    mbar_init(&bars.fin_c, 1);
+    mbar_init(&bars.fin_done, 1);
     mbar_fence_init();
     s_abort = 0;
   }
@@ -806,329 +851,449 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_score_kernel(con
   tc_fence_after_sync();
   const uint32_t tbase = tmem_slot;
   volatile int* abort_flag = &s_abort;
-  const uint32_t TM_CB = 0, TM_DM = 128, TM_DX1 = 128, TM_DX2 = 256;
+  // CB (constant), dM of the head in the score pass, the summed score gradient (fp32, updated in place), the du products
+  const uint32_t TM_CB = 0, TM_DM = 128, TM_ACC = 256, TM_DX1 = 384, TM_DX2 = 448;
+  bool dead = false;
 
-  if (tid == 0) {
-    mbar_expect_tx(&bar_map, 4 * BLK);
-    tma_load_3d(sB, &tmB, &bar_map, 0, t0, b);
-    tma_load_3d(sB + BLK, &tmB, &bar_map, 64, t0, b);
-    tma_load_3d(sC, &tmC, &bar_map, 0, t0, b);
-    tma_load_3d(sC + BLK, &tmC, &bar_map, 64, t0, b);
-    for (int i = 0; i < 2 && i < Hl; ++i) {
-      mbar_expect_tx(&bar_x[i], 3 * BLK);
-      tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], (h0 + i) * TC_G, t0, b);
-      tma_load_3d(sDY + i * BLK, &tmDY, &bar_x[i], (h0 + i) * TC_G, t0, b);
-      tma_load_2d(sdS + i * BLK, &tmDS, &bar_x[i], 0, (int)(srow0 + i) * TC_N);
+  if (warp == 12) {
+    if (lane == 0) {
+      // ---- producer ----
+      mbar_expect_tx(&bars.map, 4 * BLK);
+      tma_load_3d(sB, &tmB, &bars.map, 0, t0, b);
+      tma_load_3d(sB + BLK, &tmB, &bars.map, 64, t0, b);
+      tma_load_3d(sMs, &tmC, &bars.map, 0, t0, b);
+      tma_load_3d(sMs + BLK, &tmC, &bars.map, 64, t0, b);
+#pragma unroll 1
+      for (int h = 0; h < Hl; ++h) {
+        const int sx = h % GS_XSTAGES, ss = h & 1;
+        if (h >= GS_XSTAGES && !lane_wait(&bars.x_empty[sx], (uint32_t)((h / GS_XSTAGES - 1) & 1), abort_flag, dead)) break;
+        mbar_expect_tx(&bars.x_full[sx], 2 * BLK);
+        tma_load_3d(sX + sx * BLK, &tmU, &bars.x_full[sx], (h0 + h) * TC_G, t0, b);
+        tma_load_3d(sDY + sx * BLK, &tmDY, &bars.x_full[sx], (h0 + h) * TC_G, t0, b);
+        if (h >= 2 && !lane_wait(&bars.s_empty[ss], (uint32_t)(((h >> 1) - 1) & 1), abort_flag, dead)) break;
+        mbar_expect_tx(&bars.s_full[ss], BLK);
+        tma_load_2d(sdS + ss * BLK, &tmDS, &bars.s_full[ss], 0, (int)(srow0 + h) * TC_N);
+      }
+      // the C tile again, for the closing products, into the adjoint-state buffers once their last readers are done
+      for (int hh = max(0, Hl - 2); hh < Hl && !dead; ++hh) lane_wait(&bars.s_empty[hh & 1], (uint32_t)((hh >> 1) & 1), abort_flag, dead);
+      if (!dead) {
+        mbar_expect_tx(&bars.fin_c, 2 * BLK);
+        tma_load_3d(sdS, &tmC, &bars.fin_c, 0, t0, b);
+        tma_load_3d(sdS + BLK, &tmC, &bars.fin_c, 64, t0, b);
+      }
     }
-    if (wait_or_abort(&bar_map, 0, abort_flag)) {
-      tc_fence_after_sync();
-      const uint32_t ac = smem_u32(sC), bb = smem_u32(sB);
-      const uint32_t id = idesc_bf16(128, 128, 0, 0);
+    __syncwarp();
+  } else if (warp == 13) {
+    if (lane == 0) {
+      // ---- MMA issuer ----
+      const uint32_t id_dm = idesc_bf16(128, 128, 0, 0), id_x2 = idesc_bf16(128, 64, 0, 1), id_x1 = idesc_bf16(128, 64, 1, 1);
+      if (lane_wait(&bars.map, 0, abort_flag, dead)) {
+        tc_fence_after_sync();
+        const uint32_t ac = smem_u32(sMs), bb = smem_u32(sB);
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_CB, desc_k(ac, ks), desc_k(bb, ks), id, ks > 0 ? 1u : 0u);
-      umma_commit(&bar_cb);
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_CB, desc_k(ac, ks), desc_k(bb, ks), id_dm, ks > 0 ? 1u : 0u);
+        umma_commit(&bars.cb);
+      }
+      auto group_a = [&](int hh) {       // dM = dy u^T of head hh, once the score pass has read the previous head's
+        const int sx = hh % GS_XSTAGES;
+        if (!lane_wait(&bars.x_full[sx], (uint32_t)((hh / GS_XSTAGES) & 1), abort_flag, dead)) return;
+        if (hh >= 1 && !lane_wait(&bars.dm_empty, (uint32_t)((hh - 1) & 1), abort_flag, dead)) return;
+        tc_fence_after_sync();
+        const uint32_t ady = smem_u32(sDY + sx * BLK), bx = smem_u32(sX + sx * BLK);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) umma_bf16(tbase + TM_DM, desc_k(ady, ks), desc_k(bx, ks), id_dm, ks > 0 ? 1u : 0u);
+        umma_commit(&bars.dm_full);
+      };
+      if (!dead && Hl > 0) group_a(0);
+#pragma unroll 1
+      for (int h = 0; h < Hl && !dead; ++h) {
+        const int sx = h % GS_XSTAGES, ss = h & 1;
+        // X2 = B dSo needs nothing from the score pass: it runs under it
+        if (!lane_wait(&bars.s_full[ss], (uint32_t)((h >> 1) & 1), abort_flag, dead)) break;
+        if (h >= 1 && !lane_wait(&bars.dx_empty, (uint32_t)((h - 1) & 1), abort_flag, dead)) break;
+        tc_fence_after_sync();
+        const uint32_t ab = smem_u32(sB), bd = smem_u32(sdS + ss * BLK);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DX2, desc_k(ab, ks), desc_mn(bd, ks), id_x2, ks > 0 ? 1u : 0u);
+        umma_commit(&bars.s_empty[ss]);
+        // the score pass of head h is over: dM of head h + 1 first (the next score pass waits for it), then X1 = Ms^T dy
+        if (h + 1 < Hl) group_a(h + 1);
+        if (dead) break;
+        if (!lane_wait(&bars.ms_full, (uint32_t)(h & 1), abort_flag, dead)) break;
+        tc_fence_after_sync();
+        const uint32_t am = smem_u32(sMs), bdy = smem_u32(sDY + sx * BLK);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DX1, desc_mn(am, ks), desc_mn(bdy, ks), id_x1, ks > 0 ? 1u : 0u);
+        umma_commit(&bars.ms_empty);
+        umma_commit(&bars.dx_full);
+      }
+      // closing products: dC = dScoreSum B (K-major A) over dM, dB = dScoreSum^T C (MN-major A) over the summed gradient
+      if (!dead && lane_wait(&bars.fin_full, 0, abort_flag, dead) && lane_wait(&bars.fin_c, 0, abort_flag, dead)) {
+        tc_fence_after_sync();
+        const uint32_t am = smem_u32(sMs), bb = smem_u32(sB), bc = smem_u32(sdS);
+        const uint32_t id_c = idesc_bf16(128, 128, 0, 1), id_b = idesc_bf16(128, 128, 1, 1);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DM, desc_k(am, ks), desc_mn(bb, ks), id_c, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_ACC, desc_mn(am, ks), desc_mn(bc, ks), id_b, ks > 0 ? 1u : 0u);
+        umma_commit(&bars.fin_done);
+      }
     }
-  }
-  __syncthreads();
-  const bool cb_ok = wait_warp(&bar_cb, 0, abort_flag);
-  tc_fence_after_sync();
-
-  float acc[2][32];                      // summed score gradient of this thread's row, slabs 2*wg and 2*wg+1
-#pragma unroll
-  for (int jj = 0; jj < 2; ++jj)
-#pragma unroll
-    for (int i = 0; i < 32; ++i) acc[jj][i] = 0.f;
-  __nv_bfloat16* duout = reinterpret_cast<__nv_bfloat16*>(a.du);
-  const uint32_t id_dm = idesc_bf16(128, 128, 0, 0), id_x2 = idesc_bf16(128, 64, 0, 1), id_x1 = idesc_bf16(128, 64, 1, 1);
-
-  // Per-head rows are staged one head ahead by cp.async into clk[h & 1]: [dA | w | wd | da] x 128 tokens (da = what
-  // part 1 left in ddA), the skip coefficients D[h, 0..63] and datot (what part 1 left in dw).  No registers are held
-  // across the head, so the loads really are in flight during the previous head.
-  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H + h0;
-  const int64_t ckv = ((int64_t)b * a.L + t0 + min(tid, Tv - 1)) * H + h0;   // a mapped address for every thread
-  auto stage_clocks = [&](int hh) {
-    float* sc = clk + (hh & 1) * GS_CLK_LD;
-    if (tid < 128) {
-      const bool ok = tid < Tv;
-      cp_async4z(sc + tid, a.dA + ckv + hh, ok);
-      cp_async4z(sc + 128 + tid, a.w + ckv + hh, ok);
-      cp_async4z(sc + 256 + tid, a.wd + ckv + hh, ok);
-      cp_async4z(sc + 384 + tid, a.ddA + ckv + hh, ok);
-    } else if (tid < 128 + TC_G) {
-      const bool ok = a.Dg != nullptr;
-      cp_async4z(sc + 512 + tid - 128, ok ? a.Dg + (h0 + hh) * TC_G + tid - 128 : a.dA, ok);
-    } else if (tid == 128 + TC_G) {
-      cp_async4z(sc + 576, a.dw + ((int64_t)b * a.L + t0) * H + h0 + hh, true);
-    }
-    cp_async_commit();
-  };
-  // MMA group A of head hh: dM = dy u^T and B dSo.  Issued as soon as the accumulators of the previous head are read
-  // out, so that it runs under the per-token stage of that head.
-  auto issue_group_a = [&](int hh) {
-    const int bf = hh & 1;
-    if (wait_or_abort(&bar_x[bf], (uint32_t)((hh >> 1) & 1), abort_flag)) {
-      tc_fence_after_sync();
-      const uint32_t ady = smem_u32(sDY + bf * BLK), bx = smem_u32(sX + bf * BLK), ab = smem_u32(sB),
-                     bd = smem_u32(sdS + bf * BLK);
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) umma_bf16(tbase + TM_DM, desc_k(ady, ks), desc_k(bx, ks), id_dm, ks > 0 ? 1u : 0u);
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DX2, desc_k(ab, ks), desc_mn(bd, ks), id_x2, ks > 0 ? 1u : 0u);
-      umma_commit(&bar_a);
-    }
-  };
-  // Prefix of the steps and split decay factors of head hh from its staged rows, by warps 4..7 (which have no
-  // per-token work) while warps 0..3 finish the previous head.
-  auto prefix_high = [&](int hh) {
-    const float* scn = clk + (hh & 1) * GS_CLK_LD;
-    float* o = csb + (hh & 1) * 384;
-    chunk_prefix_split_high128(scn[tid - 128], scn[tid], o, o + 128, o + 256, wsum2);
-  };
-  stage_clocks(0);
-  cp_async_wait_all();
-  __syncthreads();                         // staged rows of head 0 visible to every thread
-  if (warp >= 4) {
-    if (tid == ISSUER && !*abort_flag && Hl > 0) issue_group_a(0);
-    prefix_high(0);
-  }
-  __syncthreads();
-  for (int h = 0; h < Hl; ++h) {
-    const int buf = h & 1;
-    const int64_t gi = ck + h;
-    const float* sc = clk + buf * GS_CLK_LD;
-    const float *wv = sc + 128, *wdv = sc + 256, *dgs = sc + 512;
-    const float *cs = csb + buf * 384, *fs = cs + 128, *fw = cs + 256;
-    if (h + 1 < Hl) stage_clocks(h + 1);   // the other buffer: its readers finished before the previous head's last barrier
-    // ---- score pass: this thread owns row t, slabs j = 2*wg, 2*wg+1 ----
-    float rowS = 0.f;
-    if (wait_warp(&bar_a, (uint32_t)(h & 1), abort_flag) && cb_ok) {
-      tc_fence_after_sync();
-      const float cst = cs[t], wdt_t = wdv[t];
-#pragma unroll
-      for (int jj = 0; jj < 2; ++jj) {
-        const int j = wg * 2 + jj;
-        uint32_t pk[16];
-        float colv[32];
-        if (j > q) {
-#pragma unroll
-          for (int k = 0; k < 16; ++k) pk[k] = 0u;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) colv[i] = 0.f;
-        } else {
-          uint32_t rm[32], rc[32];
-          tmem_ld32(tmem_addr(tbase, q * 32, TM_DM + j * 32), rm);
-          tmem_ld32(tmem_addr(tbase, q * 32, TM_CB + j * 32), rc);
+    __syncwarp();
+  } else if (warp < 4) {
+    // ---- du group: du = w_s X1 + e_s X2 + (wd_s CB[s,s] + D) dy, and the row dot products de, column sum, K[s,s], dD ----
+#pragma unroll 1
+    for (int h = 0; h < Hl; ++h) {
+      const int sx = h % GS_XSTAGES, pb = h & 1;
+      const float* rw = rows + (h % GS_ROWS) * GS_ROW_LD;
+      const bool ok = role_wait(&bars.dx_full, (uint32_t)(h & 1), abort_flag, dead);
+      float de = 0.f, cso = 0.f, dyu = 0.f;
+      if (ok) {
+        tc_fence_after_sync();
+        const float wt = rw[384 + t];
+        const float es = __expf(rw[127] - rw[t]) * wt;
+        const float dgv = rw[512 + t] * cbd[t];               // wd_s CB[s,s]
+        const float* dgs = rw + 768;
+        uint8_t* utile = sX + sx * BLK;
+        const uint8_t* dytile = sDY + sx * BLK;
+        // eight groups of eight columns; a short loop body that stays in the instruction cache
+#pragma unroll 1
+        for (int k8 = 0; k8 < 8; ++k8) {
+          uint32_t r1[8], r2[8];
+          tmem_ld8(tmem_addr(tbase, q * 32, TM_DX1 + k8 * 8), r1);
+          tmem_ld8(tmem_addr(tbase, q * 32, TM_DX2 + k8 * 8), r2);
+          const uint32_t off = sw128_offset(t, k8);
+          uint4* slot = reinterpret_cast<uint4*>(utile + off);
+          const uint4 uv = *slot;
+          const uint4 dv = *reinterpret_cast<const uint4*>(dytile + off);
+          const uint32_t* up = reinterpret_cast<const uint32_t*>(&uv);
+          const uint32_t* dp = reinterpret_cast<const uint32_t*>(&dv);
+          const float4 dlo = *reinterpret_cast<const float4*>(dgs + k8 * 8);
+          const float4 dhi = *reinterpret_cast<const float4*>(dgs + k8 * 8 + 4);
+          const float dd[8] = {dlo.x, dlo.y, dlo.z, dlo.w, dhi.x, dhi.y, dhi.z, dhi.w};
           tmem_ld_wait();
-          float mv[32];
-          if (j < q) {
-            // slab wholly below the diagonal: decay = (row factor) x (column factor), no exponential per element;
-            // the column factor of K o E is applied after the column sums
-            const float g = __expf(cst - cs[j * 32 + 31]);
+          uint32_t outp[4];
+          float ddv[8];
 #pragma unroll
-            for (int i4 = 0; i4 < 8; ++i4) {
-              const float4 f4 = *reinterpret_cast<const float4*>(fw + j * 32 + i4 * 4);
-              const float fq[4] = {f4.x, f4.y, f4.z, f4.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int i = i4 * 4 + e;
-                const float dm = __uint_as_float(rm[i]), cb = __uint_as_float(rc[i]);
-                const float kv = dm * cb, wgt = g * fq[e];
-                rowS = fmaf(kv, wgt, rowS);
-                colv[i] = kv * g;
-                acc[jj][i] = fmaf(dm, wgt, acc[jj][i]);
-                mv[i] = cb * wgt;
-              }
-            }
-          } else {
-          // diagonal slab, branch-free (selects only): the 32 exponentials are independent and overlap in the pipeline
-          float kd = 0.f;
-#pragma unroll
-          for (int i4 = 0; i4 < 8; ++i4) {
-            const float4 c4 = *reinterpret_cast<const float4*>(cs + j * 32 + i4 * 4);
-            const float4 w4 = *reinterpret_cast<const float4*>(wv + j * 32 + i4 * 4);
-            const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, wq[4] = {w4.x, w4.y, w4.z, w4.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i = i4 * 4 + e, s = j * 32 + i;
-              const float dm = __uint_as_float(rm[i]), cb = __uint_as_float(rc[i]);
-              const float kv = dm * cb;
-              const float E = __expf(cst - cv[e]);          // may overflow above the diagonal: selected away below
-              const bool below = s < t, diag = s == t;
-              const float wgt = below ? E * wq[e] : (diag ? wdt_t : 0.f);
-              const float ce = below ? kv * E : 0.f;
-              rowS = fmaf(ce, wq[e], rowS);
-              kd = diag ? kv : kd;
-              colv[i] = ce;
-              acc[jj][i] = fmaf(dm, wgt, acc[jj][i]);
-              mv[i] = cb * wgt;
-            }
+          for (int e = 0; e < 4; ++e) {
+            float u0, u1, g0, g1;
+            unpack_bf16(up[e], u0, u1);
+            unpack_bf16(dp[e], g0, g1);
+            const float x10 = __uint_as_float(r1[2 * e]), x11 = __uint_as_float(r1[2 * e + 1]);
+            const float x20 = __uint_as_float(r2[2 * e]), x21 = __uint_as_float(r2[2 * e + 1]);
+            outp[e] = pack_bf16(fmaf(dd[2 * e] + dgv, g0, fmaf(es, x20, wt * x10)),
+                                fmaf(dd[2 * e + 1] + dgv, g1, fmaf(es, x21, wt * x11)));
+            de = fmaf(u0, x20, fmaf(u1, x21, de));
+            cso = fmaf(u0, x10, fmaf(u1, x11, cso));
+            ddv[2 * e] = g0 * u0;
+            ddv[2 * e + 1] = g1 * u1;
+            dyu += ddv[2 * e] + ddv[2 * e + 1];
           }
-          kdiag[t] = kd;
+          *slot = make_uint4(outp[0], outp[1], outp[2], outp[3]);
+          if (a.dDg_part) {
+            const float csum = warp_colsum8(ddv, lane);
+            if ((lane & 3) == 0)
+              ddpart[(pb * 4 + q) * 64 + k8 * 8 + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = csum;
           }
-#pragma unroll
-          for (int k = 0; k < 16; ++k) pk[k] = pack_bf16(mv[2 * k], mv[2 * k + 1]);
         }
+      }
+      depart[pb * 128 + t] = de;
+      colsum[pb * 128 + t] = cso;
+      kdiag[pb * 128 + t] = cbd[t] * dyu;
+      warp_arrive(&bars.dx_empty, true);       // the DX accumulators are free; the du rows are fenced for the async proxy
+      if (lane == 0) mbar_arrive(&bars.part_full[pb]);
+      if (tid == 0) {
+        bulk_wait_group_read<0>();             // the store of head h - 1 has read its tile: that stage may be reloaded
+        if (h > 0) mbar_arrive(&bars.x_empty[(h - 1) % GS_XSTAGES]);
+      }
+      named_bar_sync(3, 128);
+      if (tid == 0 && ok) {
+        tma_store_3d(&tmDU, sX + sx * BLK, (h0 + h) * TC_G, t0, b);   // rows past the end of the sequence are clipped
+        bulk_commit_group();
+      }
+    }
+    if (tid == 0) bulk_wait_group<0>();
+    // ---- closing read-out: dC, dB (intra-chunk parts) added to what part 1 left in dChat / dBhat ----
+    if (role_wait(&bars.fin_done, 0, abort_flag, dead)) {
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int col = 0; col < 128; col += 32) {
+        uint32_t r1[32], r2[32];
+        tmem_ld32(tmem_addr(tbase, q * 32, TM_DM + col), r1);    // dC intra
+        tmem_ld32(tmem_addr(tbase, q * 32, TM_ACC + col), r2);   // dB intra
+        tmem_ld_wait();
+        if (t < Tv) {
+          float4* dc = reinterpret_cast<float4*>(a.dChat + (((int64_t)blockIdx.z * a.B + b) * a.L + t0 + t) * TC_N + col);
+          float4* db = reinterpret_cast<float4*>(a.dBhat + (((int64_t)blockIdx.z * a.B + b) * a.L + t0 + t) * TC_N + col);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 x = dc[j], y = db[j];
+            x.x += __uint_as_float(r1[4 * j]); x.y += __uint_as_float(r1[4 * j + 1]); x.z += __uint_as_float(r1[4 * j + 2]); x.w += __uint_as_float(r1[4 * j + 3]);
+            y.x += __uint_as_float(r2[4 * j]); y.y += __uint_as_float(r2[4 * j + 1]); y.z += __uint_as_float(r2[4 * j + 2]); y.w += __uint_as_float(r2[4 * j + 3]);
+            dc[j] = x;
+            db[j] = y;
+          }
+        }
+      }
+    }
+  } else if (warp < 12) {
+    // ---- score group ----
+    const int sg = (warp - 4) >> 2;        // column slabs 2 sg, 2 sg + 1 of row quarter q
+    const bool cb_ok = role_wait(&bars.cb, 0, abort_flag, dead);   // CB is in TMEM; the C tile's buffer is free for the scores
+    tc_fence_after_sync();
+    // The summed score gradient of this warp's slabs starts at zero.  What lies on and above the diagonal of the operand
+    // never changes: zero those slabs of this row once; the warp that owns the diagonal slab also publishes CB[s,s].
+    {
+      uint32_t z[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) z[i] = 0u;
+#pragma unroll 1
+      for (int pi = 0; pi < 4; ++pi) tmem_st16(tmem_addr(tbase, q * 32, TM_ACC + sg * 64 + pi * 16), z);
+      tmem_st_wait();
+    }
+#pragma unroll 1
+    for (int jj = 0; jj < 2; ++jj) {
+      const int j = 2 * sg + jj;
+      if (j > q) {
         uint8_t* dstb = sMs + (j >> 1) * BLK;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          *reinterpret_cast<uint4*>(dstb + sw128_offset(t, (j & 1) * 4 + k)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
-        warp_colsum32(colv, lane);
-        colpart[q * 128 + j * 32 + lane] = j < q ? colv[0] * fs[j * 32 + lane] : colv[0];
+        for (int kk = 0; kk < 4; ++kk) *reinterpret_cast<uint4*>(dstb + sw128_offset(t, (j & 1) * 4 + kk)) = make_uint4(0u, 0u, 0u, 0u);
+      } else if (j == q && cb_ok) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tbase, q * 32, TM_CB + j * 32), r);
+        tmem_ld_wait();
+        float dv = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dv = i == lane ? __uint_as_float(r[i]) : dv;
+        cbd[t] = dv;
       }
     }
-    rowpart[wg * 128 + t] = rowS;
-    tc_fence_before_sync();
-    fence_proxy_async();
-    __syncthreads();
-    if (tid == 0 && !*abort_flag) {
+    // live 16-column pieces of this warp: slab j = 2 sg + (pi >> 1) is live when j <= q
+    const int npieces = q < 2 * sg ? 0 : (q == 2 * sg ? 2 : 4);
+#pragma unroll 1
+    for (int h = 0; h < Hl; ++h) {
+      const int pb = h & 1;
+      const float* rw = rows + (h % GS_ROWS) * GS_ROW_LD;
+      const float *cs = rw, *fs = rw + 128, *fw = rw + 256, *wv = rw + 384, *wdv = rw + 512;
+      bool go = cb_ok;
+      go = role_wait(&bars.rows_full[h % GS_ROWS], (uint32_t)((h / GS_ROWS) & 1), abort_flag, dead) && go;
+      go = role_wait(&bars.dm_full, (uint32_t)(h & 1), abort_flag, dead) && go;
+      if (h >= 1) go = role_wait(&bars.ms_empty, (uint32_t)((h - 1) & 1), abort_flag, dead) && go;
+      if (h >= 2) go = role_wait(&bars.part_empty[pb], (uint32_t)(((h >> 1) - 1) & 1), abort_flag, dead) && go;
+      float rowS = 0.f;
+      if (go) {
+        tc_fence_after_sync();
+        const float cst = cs[t], wdt_t = wdv[t];
+#pragma unroll 1
+        for (int pi = 0; pi < npieces; ++pi) {
+          const int j = 2 * sg + (pi >> 1), col = j * 32 + (pi & 1) * 16;
+          uint32_t rm[16], rc[16], ra[16];
+          tmem_ld16(tmem_addr(tbase, q * 32, TM_DM + col), rm);
+          tmem_ld16(tmem_addr(tbase, q * 32, TM_CB + col), rc);
+          tmem_ld16(tmem_addr(tbase, q * 32, TM_ACC + col), ra);
+          uint32_t pk[8];
+          if (j < q) {
+            // slab wholly below the diagonal: decay = (row factor) x (column factor), no exponential per element
+            const float g = __expf(cst - cs[j * 32 + 31]);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e4 = 0; e4 < 4; ++e4) {
+              const float4 f4 = *reinterpret_cast<const float4*>(fs + col + e4 * 4);
+              const float4 w4 = *reinterpret_cast<const float4*>(fw + col + e4 * 4);
+              const float fq[4] = {f4.x, f4.y, f4.z, f4.w}, wq[4] = {w4.x, w4.y, w4.z, w4.w};
+              float mv[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int i = e4 * 4 + e;
+                const float dm = __uint_as_float(rm[i]), cb = __uint_as_float(rc[i]);
+                const float wgt = g * wq[e];                    // E w_s
+                rowS = fmaf(dm * cb, wgt, rowS);
+                ra[i] = __float_as_uint(fmaf(dm, wgt, __uint_as_float(ra[i])));
+                mv[e] = cb * (g * fq[e]);                       // CB E
+              }
+              pk[e4 * 2] = pack_bf16(mv[0], mv[1]);
+              pk[e4 * 2 + 1] = pack_bf16(mv[2], mv[3]);
+            }
+          } else {
+            // diagonal slab, branch-free (selects only)
+            tmem_ld_wait();
+#pragma unroll
+            for (int e4 = 0; e4 < 4; ++e4) {
+              const float4 c4 = *reinterpret_cast<const float4*>(cs + col + e4 * 4);
+              const float4 w4 = *reinterpret_cast<const float4*>(wv + col + e4 * 4);
+              const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, wq[4] = {w4.x, w4.y, w4.z, w4.w};
+              float mv[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int i = e4 * 4 + e, sc = col + i;
+                const float dm = __uint_as_float(rm[i]), cb = __uint_as_float(rc[i]);
+                const float E = sc < t ? __expf(cst - cv[e]) : 0.f;   // the argument is <= 0 wherever it is used
+                const float wgt = sc == t ? wdt_t : E * wq[e];
+                rowS = fmaf(dm * cb, E * wq[e], rowS);
+                ra[i] = __float_as_uint(fmaf(dm, wgt, __uint_as_float(ra[i])));
+                mv[e] = cb * E;
+              }
+              pk[e4 * 2] = pack_bf16(mv[0], mv[1]);
+              pk[e4 * 2 + 1] = pack_bf16(mv[2], mv[3]);
+            }
+          }
+          tmem_st16(tmem_addr(tbase, q * 32, TM_ACC + col), ra);
+          uint8_t* dstb = sMs + (j >> 1) * BLK;
+          const int ch = (j & 1) * 4 + (pi & 1) * 2;
+          *reinterpret_cast<uint4*>(dstb + sw128_offset(t, ch)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(dstb + sw128_offset(t, ch + 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
+        tmem_st_wait();
+      }
+      rowpart[(pb * 2 + sg) * 128 + t] = rowS;
+      // dM is read, the masked scores and this head's partial sums are written
+      fence_proxy_async();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&bars.dm_empty);
+        mbar_arrive(&bars.ms_full);
+        mbar_arrive(&bars.part_full[pb]);
+      }
+    }
+    // ---- summed score gradient -> shared memory (operand of the closing products) ----
+    bool fin = cb_ok;
+    if (Hl >= 1) fin = role_wait(&bars.ms_empty, (uint32_t)((Hl - 1) & 1), abort_flag, dead) && fin;
+    if (fin) {
       tc_fence_after_sync();
-      const uint32_t am = smem_u32(sMs), bdy = smem_u32(sDY + buf * BLK);
+#pragma unroll 1
+      for (int pi = 0; pi < 4; ++pi) {
+        const int j = 2 * sg + (pi >> 1), col = j * 32 + (pi & 1) * 16;
+        uint32_t ra[16];
+        tmem_ld16(tmem_addr(tbase, q * 32, TM_ACC + col), ra);
+        tmem_ld_wait();
+        uint8_t* dstb = sMs + (j >> 1) * BLK;
+        const int ch = (j & 1) * 4 + (pi & 1) * 2;
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DX1, desc_mn(am, ks), desc_mn(bdy, ks), id_x1, ks > 0 ? 1u : 0u);
-      umma_commit(&bar_b);
+        for (int c2 = 0; c2 < 2; ++c2)
+          *reinterpret_cast<uint4*>(dstb + sw128_offset(t, ch + c2)) =
+              make_uint4(pack_bf16(__uint_as_float(ra[8 * c2]), __uint_as_float(ra[8 * c2 + 1])),
+                         pack_bf16(__uint_as_float(ra[8 * c2 + 2]), __uint_as_float(ra[8 * c2 + 3])),
+                         pack_bf16(__uint_as_float(ra[8 * c2 + 4]), __uint_as_float(ra[8 * c2 + 5])),
+                         pack_bf16(__uint_as_float(ra[8 * c2 + 6]), __uint_as_float(ra[8 * c2 + 7])));
+      }
     }
-    // ---- du, de, dD ----
-    float de_half = 0.f;
-    float ddv[32];
+    warp_arrive(&bars.fin_full, true);
+  } else {
+    // ---- token warps: thread i owns tokens 2 i and 2 i + 1 ----
+    const int i = tid - 14 * 32, w2 = i >> 5;           // 0..63; warp 0 / 1 of the pair
+    const int ta = 2 * i, tb = 2 * i + 1;
+    const bool la = ta < Tv, lb = tb < Tv;
+    const int64_t cka = ((int64_t)b * a.L + t0 + min(ta, Tv - 1)) * H + h0, ckb = ((int64_t)b * a.L + t0 + min(tb, Tv - 1)) * H + h0;
+    const int64_t ck0 = ((int64_t)b * a.L + t0) * H + h0;
+    // rows of head hh: prefix of the steps, split decay factors, write weights, what part 1 left (da in ddA, datot in dw at
+    // the chunk's first token), skip coefficients
+    float ld[9];                           // rows of the next head to be prepared, loaded one iteration ahead
+    auto load_rows = [&](int hh) {
+      ld[0] = la ? a.dA[cka + hh] : 0.f;   ld[1] = lb ? a.dA[ckb + hh] : 0.f;
+      ld[2] = la ? a.w[cka + hh] : 0.f;    ld[3] = lb ? a.w[ckb + hh] : 0.f;
+      ld[4] = la ? a.wd[cka + hh] : 0.f;   ld[5] = lb ? a.wd[ckb + hh] : 0.f;
+      ld[6] = la ? a.ddA[cka + hh] : 0.f;  ld[7] = lb ? a.ddA[ckb + hh] : 0.f;
+      ld[8] = i == 0 ? a.dw[ck0 + hh] : (a.Dg ? a.Dg[(h0 + hh) * TC_G + i] : 0.f);   // thread 0 also needs D[hh, 0]: below
+    };
+    auto make_rows = [&](int hh) {
+      float* rw = rows + (hh % GS_ROWS) * GS_ROW_LD;
+      const float da_ = ld[0], db_ = ld[1], wa_ = ld[2], wb_ = ld[3];
+      float x = da_ + db_;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) ddv[i] = 0.f;
-    if (wait_warp(&bar_b, (uint32_t)(h & 1), abort_flag)) {
-      tc_fence_after_sync();
-      uint32_t r1[32], r2[32];
-      tmem_ld32(tmem_addr(tbase, q * 32, TM_DX1 + wg * 32), r1);
-      tmem_ld32(tmem_addr(tbase, q * 32, TM_DX2 + wg * 32), r2);
-      tmem_ld_wait();
-      const float es = __expf(cs[127] - cs[t]) * wv[t];
-      uint32_t outp[16];
+      for (int o = 1; o < 32; o <<= 1) {
+        const float y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+      }
+      if (lane == 31) tkred[w2] = x;
+      named_bar_sync(4, 64);
+      const float off = w2 == 0 ? 0.f : tkred[0];
+      const float csb_ = x + off, csa_ = csb_ - db_;      // inclusive prefixes of tokens 2 i + 1 and 2 i
+      // a 32-token slab = 16 consecutive threads: its last prefix is that of thread (i | 15), token 2 (i | 15) + 1
+      const float cend = __shfl_sync(0xffffffffu, csb_, lane | 15);
+      const float fa = __expf(cend - csa_), fb = __expf(cend - csb_);
+      rw[ta] = csa_;            rw[tb] = csb_;
+      rw[128 + ta] = fa;        rw[128 + tb] = fb;
+      rw[256 + ta] = fa * wa_;  rw[256 + tb] = fb * wb_;
+      rw[384 + ta] = wa_;       rw[384 + tb] = wb_;
+      rw[512 + ta] = ld[4];     rw[512 + tb] = ld[5];
+      rw[640 + ta] = ld[6];     rw[640 + tb] = ld[7];
+      if (i == 0) {
+        rw[832] = ld[8];
+        rw[768] = a.Dg ? a.Dg[(h0 + hh) * TC_G] : 0.f;
+      } else {
+        rw[768 + i] = ld[8];
+      }
+      named_bar_sync(4, 64);               // tkred may be rewritten; both warps' rows are complete
+      warp_arrive(&bars.rows_full[hh % GS_ROWS], false);
+    };
+    if (Hl > 0) {
+      load_rows(0);
+      make_rows(0);
+    }
+    if (Hl > 1) {
+      load_rows(1);
+      make_rows(1);
+    }
+    if (Hl > 2) load_rows(2);
+#pragma unroll 1
+    for (int h = 0; h < Hl; ++h) {
+      const int pb = h & 1;
+      if (h + 2 < Hl) make_rows(h + 2);    // slot (h + 2) % 3 = that of head h - 1, whose readers are all done
+      if (h + 3 < Hl) load_rows(h + 3);    // in flight during this head's gradients
+      const float* rw = rows + (h % GS_ROWS) * GS_ROW_LD;
+      const bool ok = role_wait(&bars.part_full[pb], (uint32_t)((h >> 1) & 1), abort_flag, dead);
+      {                                    // the named barriers below are met on the wind-down path too (stores are not)
+        const float cs127 = rw[127], datot = rw[832];
+        float gcs[2], gw[2], term[2];
 #pragma unroll
-      for (int k4 = 0; k4 < 4; ++k4) {
-        uint4 uv = *reinterpret_cast<const uint4*>(sX + buf * BLK + sw128_offset(t, wg * 4 + k4));
-        uint4 dv = *reinterpret_cast<const uint4*>(sDY + buf * BLK + sw128_offset(t, wg * 4 + k4));
-        const uint32_t* up = reinterpret_cast<const uint32_t*>(&uv);
-        const uint32_t* dp = reinterpret_cast<const uint32_t*>(&dv);
-        const float4 dlo = *reinterpret_cast<const float4*>(dgs + wg * 32 + k4 * 8);
-        const float4 dhi = *reinterpret_cast<const float4*>(dgs + wg * 32 + k4 * 8 + 4);
-        const float dd[8] = {dlo.x, dlo.y, dlo.z, dlo.w, dhi.x, dhi.y, dhi.z, dhi.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int i = k4 * 8 + k * 2;
-          float u0, u1, g0, g1;
-          unpack_bf16(up[k], u0, u1);
-          unpack_bf16(dp[k], g0, g1);
-          const float x20 = __uint_as_float(r2[i]), x21 = __uint_as_float(r2[i + 1]);
-          const float d0 = dd[2 * k], d1 = dd[2 * k + 1];
-          outp[k4 * 4 + k] = pack_bf16(__uint_as_float(r1[i]) + es * x20 + d0 * g0, __uint_as_float(r1[i + 1]) + es * x21 + d1 * g1);
-          de_half = fmaf(u0, x20, fmaf(u1, x21, de_half));
-          ddv[i] = g0 * u0;
-          ddv[i + 1] = g1 * u1;
+        for (int u2 = 0; u2 < 2; ++u2) {
+          const int tt = 2 * i + u2;
+          const float cst = rw[tt], wt = rw[384 + tt], da_t = rw[640 + tt];
+          const float colS = colsum[pb * 128 + tt];
+          const float rS = rowpart[(pb * 2 + 0) * 128 + tt] + rowpart[(pb * 2 + 1) * 128 + tt];
+          const float de = depart[pb * 128 + tt];
+          const float ET = __expf(cs127 - cst);
+          term[u2] = ET * wt * de;
+          gcs[u2] = rS - colS * wt + __expf(cst) * da_t - term[u2];
+          gw[u2] = colS + ET * de;
         }
-      }
-      if (t < Tv) {
-        uint4* dst = reinterpret_cast<uint4*>(duout + ((int64_t)b * a.L + t0 + t) * (int64_t)(H * TC_G) + (h0 + h) * TC_G + wg * 32);
+        // tail = sum over the chunk of ET w de + exp(cs_T) datot, added to the last token's d cs
+        float ts = term[0] + term[1];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) dst[k] = make_uint4(outp[4 * k], outp[4 * k + 1], outp[4 * k + 2], outp[4 * k + 3]);
-      }
-    }
-    depart[wg * 128 + t] = de_half;
-    if (a.dDg_part) {
-      warp_colsum32(ddv, lane);
-      ddpart[q * 64 + wg * 32 + lane] = ddv[0];
-    }
-    cp_async_wait_all();                   // this thread's share of the rows of head h + 1 (staged at the top of this head)
-    tc_fence_before_sync();
-    __syncthreads();
-    if (warp >= 4) {
-      // Warps 4..7 have no per-token work: thread 128 issues what the next heads need, then the four warps form the
-      // prefix of head h + 1.  TMEM of this head is read out (barrier above), so group A of head h + 1 may overwrite
-      // it; the operand buffers of head h are free.
-      if (tid == ISSUER && !*abort_flag) {
-        if (h + 1 < Hl) issue_group_a(h + 1);
-        if (h + 2 < Hl) {
-          mbar_expect_tx(&bar_x[buf], 3 * BLK);
-          tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
-          tma_load_3d(sDY + buf * BLK, &tmDY, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
-          tma_load_2d(sdS + buf * BLK, &tmDS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
+        for (int o = 16; o > 0; o >>= 1) ts += __shfl_xor_sync(0xffffffffu, ts, o);
+        if (lane == 0) tkred[4 + w2] = ts;
+        named_bar_sync(4, 64);
+        const float tail = (tkred[4] + tkred[5]) + __expf(cs127) * datot;
+        if (i == 63) gcs[1] += tail;
+        // reverse inclusive prefix of d cs over the 128 tokens: suffix sums
+        float x = gcs[0] + gcs[1];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float y = __shfl_down_sync(0xffffffffu, x, o);
+          if (lane + o < 32) x += y;
         }
-      }
-      if (h + 1 < Hl) prefix_high(h + 1);
-    } else {
-      // ---- per-token clock gradients: thread tid owns token tid; reductions over warps 0..3 on a named barrier ----
-      const float wt = sc[128 + tid], da_t = sc[384 + tid], datot = sc[576];
-      const float colS = colpart[tid] + colpart[128 + tid] + colpart[256 + tid] + colpart[384 + tid];
-      const float rS = rowpart[tid] + rowpart[128 + tid];
-      const float de = depart[tid] + depart[128 + tid];
-      const float ET = __expf(cs[127] - cs[tid]);
-      float g_cs = rS - colS * wt + __expf(cs[tid]) * da_t - ET * wt * de;
-      const float g_w = colS + ET * de;
-      const float tail = sum_low128(ET * wt * de, red) + __expf(cs[127]) * datot;
-      if (tid == 127) g_cs += tail;
-      gcs[tid] = g_cs;
-      bar_low128();
-      // reverse prefix: gcs[i] <- sum_{k<=i} g_cs[127-k]; the argument is read before the prefix's first barrier, the
-      // result written after it
-      chunk_prefix_low128(gcs[127 - tid], gcs, wsum);
-      const int tt = 127 - tid;          // prefix index tid holds the reverse-inclusive sum for token tt
-      if (tt < Tv) {
-        const int64_t go = ((int64_t)b * a.L + t0 + tt) * H + h0 + h;
-        a.ddA[go] = gcs[tid];
-      }
-      if (tid < Tv) {
-        a.dw[gi] = g_w;
-        if (a.dwd) a.dwd[gi] = kdiag[tid];
-      }
-      if (a.dDg_part && tid < 64)
-        a.dDg_part[(((int64_t)b * a.nc + c) * H + h0 + h) * TC_G + tid] = ddpart[tid] + ddpart[64 + tid] + ddpart[128 + tid] + ddpart[192 + tid];
-    }
-    __syncthreads();
-  }
-
-  // ---- summed score gradient -> dC, dB ----
-  {
-#pragma unroll
-    for (int jj = 0; jj < 2; ++jj) {
-      const int j = wg * 2 + jj;
-      uint8_t* dstb = sMs + (j >> 1) * BLK;
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        *reinterpret_cast<uint4*>(dstb + sw128_offset(t, (j & 1) * 4 + k)) =
-            make_uint4(pack_bf16(acc[jj][8 * k], acc[jj][8 * k + 1]), pack_bf16(acc[jj][8 * k + 2], acc[jj][8 * k + 3]),
-                       pack_bf16(acc[jj][8 * k + 4], acc[jj][8 * k + 5]), pack_bf16(acc[jj][8 * k + 6], acc[jj][8 * k + 7]));
-    }
-  }
-  tc_fence_before_sync();
-  fence_proxy_async();
-  __syncthreads();
-  if (tid == 0 && !*abort_flag) {
-    tc_fence_after_sync();
-    const uint32_t am = smem_u32(sMs), bb = smem_u32(sB), bc = smem_u32(sC);
-    const uint32_t id_c = idesc_bf16(128, 128, 0, 1), id_b = idesc_bf16(128, 128, 1, 1);
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + 128, desc_k(am, ks), desc_mn(bb, ks), id_c, ks > 0 ? 1u : 0u);
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + 0, desc_mn(am, ks), desc_mn(bc, ks), id_b, ks > 0 ? 1u : 0u);
-    umma_commit(&bar_cb);
-  }
-  if (wait_warp(&bar_cb, 1, abort_flag)) {
-    tc_fence_after_sync();
-#pragma unroll
-    for (int jj = 0; jj < 2; ++jj) {
-      const int col = wg * 64 + jj * 32;
-      uint32_t r1[32], r2[32];
-      tmem_ld32(tmem_addr(tbase, q * 32, 128 + col), r1);   // dC intra
-      tmem_ld32(tmem_addr(tbase, q * 32, 0 + col), r2);     // dB intra
-      tmem_ld_wait();
-      if (t < Tv) {
-        float4* dc = reinterpret_cast<float4*>(a.dChat + (((int64_t)blockIdx.z * a.B + b) * a.L + t0 + t) * TC_N + col);
-        float4* db = reinterpret_cast<float4*>(a.dBhat + (((int64_t)blockIdx.z * a.B + b) * a.L + t0 + t) * TC_N + col);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float4 x = dc[j], y = db[j];
-          x.x += __uint_as_float(r1[4 * j]); x.y += __uint_as_float(r1[4 * j + 1]); x.z += __uint_as_float(r1[4 * j + 2]); x.w += __uint_as_float(r1[4 * j + 3]);
-          y.x += __uint_as_float(r2[4 * j]); y.y += __uint_as_float(r2[4 * j + 1]); y.z += __uint_as_float(r2[4 * j + 2]); y.w += __uint_as_float(r2[4 * j + 3]);
-          dc[j] = x;
-          db[j] = y;
+        if (lane == 0) tkred[8 + w2] = x;
+        named_bar_sync(4, 64);
+        const float offr = w2 == 0 ? tkred[9] : 0.f;
+        const float sa = x + offr, sb = sa - gcs[0];         // suffix sums from token 2 i and from token 2 i + 1
+        const int64_t ga = ((int64_t)b * a.L + t0 + ta) * H + h0 + h, gb = ((int64_t)b * a.L + t0 + tb) * H + h0 + h;
+        if (la && ok) {
+          a.ddA[ga] = sa;
+          a.dw[ga] = gw[0];
+          if (a.dwd) a.dwd[ga] = kdiag[pb * 128 + ta];
         }
+        if (lb && ok) {
+          a.ddA[gb] = sb;
+          a.dw[gb] = gw[1];
+          if (a.dwd) a.dwd[gb] = kdiag[pb * 128 + tb];
+        }
+        if (a.dDg_part && ok)
+          a.dDg_part[(((int64_t)b * a.nc + c) * H + h0 + h) * TC_G + i] =
+              (ddpart[(pb * 4 + 0) * 64 + i] + ddpart[(pb * 4 + 1) * 64 + i]) + (ddpart[(pb * 4 + 2) * 64 + i] + ddpart[(pb * 4 + 3) * 64 + i]);
+        named_bar_sync(4, 64);             // tkred is free for the next prefix
       }
+      warp_arrive(&bars.part_empty[pb], false);
     }
   }
   tc_fence_before_sync();
@@ -1242,11 +1407,11 @@ int tc_launch_chunk_out(const ScanArgs& a, cudaStream_t st) {
 }
 
 constexpr int SMEM_GSTATE = 12 * BLK + 4096 + 1024;
-constexpr int SMEM_GSCORE = 12 * BLK + 14336 + 1024;
+constexpr int SMEM_GSCORE = (6 + 2 * GS_XSTAGES) * BLK + (GS_ROWS * GS_ROW_LD + 512 + 256 + 256 + 256 + 512 + 128 + 16) * 4 + 1024;
 
 int tc_launch_chunk_grads(const ScanArgs& a, cudaStream_t st) {
   if (mimo_tc_geometry(a.R, a.O, a.G, a.N)) return mimo_tc_launch_grads(a, st);
-  CUtensorMap tmB, tmC, tmU, tmDY, tmS, tmDS;
+  CUtensorMap tmB, tmC, tmU, tmDY, tmS, tmDS, tmDU;
   int rc;
   if ((rc = map_state(&tmS, a.Sin16, a)) != OK) return rc;
   if ((rc = map_state(&tmDS, a.dS16, a)) != OK) return rc;
@@ -1256,11 +1421,12 @@ int tc_launch_chunk_grads(const ScanArgs& a, cudaStream_t st) {
   if ((rc = map_rows(&tmC, a.Chat, TC_N, a.c_ts, a.L, a.B)) != OK) return rc;
   if ((rc = map_rows(&tmU, a.u, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
   if ((rc = map_rows(&tmDY, a.dy, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
+  if ((rc = map_rows(&tmDU, a.du, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
   ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_grads_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GSTATE));
   ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_grads_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GSCORE));
   tc_chunk_grads_state_kernel<<<dim3(a.nc, a.B, head_split(a)), TC_THREADS, SMEM_GSTATE, st>>>(tmC, tmU, tmDY, tmS, tmDS, a);
   ORBIT_CHECK_LAUNCH("tc_chunk_grads_state_kernel");
-  tc_chunk_grads_score_kernel<<<dim3(a.nc, a.B, head_split(a)), TC_THREADS, SMEM_GSCORE, st>>>(tmB, tmC, tmU, tmDY, tmDS, a);
+  tc_chunk_grads_score_kernel<<<dim3(a.nc, a.B, head_split(a)), GS_THREADS, SMEM_GSCORE, st>>>(tmB, tmC, tmU, tmDY, tmDS, tmDU, a);
   ORBIT_CHECK_LAUNCH("tc_chunk_grads_score_kernel");
   return OK;
 }

@@ -12,7 +12,11 @@
 namespace orbit {
 namespace tc {
 
-constexpr uint32_t WAIT_LIMIT = 1u << 21;   // polls (each a try_wait with a hardware time slice) before giving up
+// A wait is a loop of mbarrier.try_wait, each of which suspends the thread in hardware until the phase completes or
+// WAIT_SLICE_NS have passed (without the time hint the hardware returns after a short slice and the loop would spin,
+// taking issue slots from the warps that work); after WAIT_LIMIT slices (about two seconds) the waiter gives up.
+constexpr uint32_t WAIT_SLICE_NS = 1000000u;
+constexpr uint32_t WAIT_LIMIT = 2048u;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -30,14 +34,15 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // Returns true when the phase with the given parity completed, false when the poll limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = WAIT_LIMIT) {
   uint32_t addr = smem_u32(bar);
+#pragma unroll 1
   for (uint32_t i = 0; i < limit; ++i) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(addr), "r"(parity)
+        : "r"(addr), "r"(parity), "r"(WAIT_SLICE_NS)
         : "memory");
     if (ok) return true;
   }

@@ -29,17 +29,18 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // ---- bounded waits with a CTA-wide abort flag --------------------------------------------------------------------
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   uint32_t addr = smem_u32(bar);
+#pragma unroll 1
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(addr), "r"(parity)
+        : "r"(addr), "r"(parity), "r"(WAIT_SLICE_NS)
         : "memory");
     if (ok) return true;
-    if ((i & 63u) == 63u && *abort_flag) return false;
+    if (*abort_flag) return false;
   }
   *abort_flag = 1;
   return false;
@@ -167,5 +168,34 @@ __device__ __forceinline__ void warp_colsum32(float (&v)[32], int lane) {
   }
 }
 
+// The same for 8 columns: in v[i] = value of (row = lane, column i); returns the sum over the warp's rows of column
+// ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1), the same value on the four lanes that differ in their two
+// low bits.  Fixed order, 9 shuffles.
+__device__ __forceinline__ float warp_colsum8(float (&v)[8], int lane) {
+  {
+    const bool up = (lane & 16) != 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float send = up ? v[k] : v[k + 4], keep = up ? v[k + 4] : v[k];
+      v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+  }
+  {
+    const bool up = (lane & 8) != 0;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const float send = up ? v[k] : v[k + 2], keep = up ? v[k + 2] : v[k];
+      v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+  }
+  {
+    const bool up = (lane & 4) != 0;
+    const float send = up ? v[0] : v[1], keep = up ? v[1] : v[0];
+    v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+  }
+  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
+  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+  return v[0];
+}
 
 }  // namespace orbit

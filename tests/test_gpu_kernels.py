@@ -489,7 +489,7 @@ def test_bounded_wait_winds_down_and_reports():
     lib = _lib.load()
     status = ops._status_word(torch.device(DEV, torch.cuda.current_device()))
     status.zero_()
-    _lib.check(lib.orbit_selftest_wait_timeout(C.c_void_p(status.data_ptr()), 1000, C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+    _lib.check(lib.orbit_selftest_wait_timeout(C.c_void_p(status.data_ptr()), 200, C.c_void_p(torch.cuda.current_stream().cuda_stream)),
                "orbit_selftest_wait_timeout")
     with pytest.raises(RuntimeError, match="ORBIT_ERR_DEVICE_TIMEOUT"):
         ops.check_device_status()
