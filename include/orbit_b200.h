@@ -138,9 +138,11 @@ typedef struct orbit_scan_args {
   float* dgamma_part; /* [B*nc, H, R, O, N]  out or NULL                                             */
   float* dDg_part;    /* [B*nc, H, G, R, O]  out or NULL                                             */
   int* status;        /* device int or NULL: set to 1 by a kernel whose bounded wait gave up         */
-  void* Sin16;        /* [B, nc, H, R, N, G] bfloat16 copy of Sin written by the forward pass, or NULL;
-                         required (with dS16 in backward) by precision "io", whose tiles read it by TMA */
-  void* dS16;         /* [B, nc, H, R, N, G] bfloat16 copy of dS written by the reverse pass, or NULL  */
+  void* Sin16;        /* [B, nc, H, R, N, G] bfloat16 state tiles written by the forward pass, or NULL; required (with
+                         dS16 in backward) by precision "io" at rank 1 (R = O = 1), whose tiles read them by TMA.
+                         There the pass writes ONLY these tiles: Sin keeps the chunk-local states of CHUNK_STATE and
+                         may be NULL in the backward phases                                                       */
+  void* dS16;         /* [B, nc, H, R, N, G] bfloat16 tiles of dS written by the reverse pass, or NULL (as Sin16)  */
   float* du32;        /* [B, L, H, G, R] fp32 scratch, or NULL; required by CHUNK_GRADS of precision "io" at rank 4
                          (R = O = 4), which sums the drive gradient of a head over its siblings there          */
 } orbit_scan_args;

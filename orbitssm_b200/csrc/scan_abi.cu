@@ -30,9 +30,11 @@ int fail(int code, const char* fmt, ...) {
 // With REVERSE the walk runs from the last chunk down (the adjoint pass):
 //   D <- dS_fin;  for c = nc-1..0: g = buf[c]; buf[c] = D; D = atot[c] * D + g;   dS0 <- D
 // `copy16` (optional) receives a bfloat16 copy of what is written to buf (operand tiles of the tensor-core kernels).
+// With WRITE32 false only that copy is written: the rank-1 tensor-core kernels read nothing but the bfloat16 tiles, so
+// the fp32 write-back (40 % of this kernel's traffic) is left out and buf keeps the chunk-local values.
 constexpr int PASS_NB = 8;
 
-template <int VEC, bool REVERSE, bool WRITE>
+template <int VEC, bool REVERSE, bool WRITE, bool WRITE32>
 __global__ void __launch_bounds__(256, 3) state_pass_kernel(float* __restrict__ buf, const float* __restrict__ atot,
                                                          const float* __restrict__ s_in, float* __restrict__ s_out,
                                                          __nv_bfloat16* __restrict__ copy16, int nc, int HR, int NG) {
@@ -67,14 +69,14 @@ __global__ void __launch_bounds__(256, 3) state_pass_kernel(float* __restrict__ 
         if constexpr (!WRITE) {
           // dry walk: only the carried value is wanted (context-parallel exchange), the buffer keeps its content
         } else if constexpr (VEC == 4) {
-          *reinterpret_cast<float4*>(buf + base + cc * cstride) = make_float4(S[0], S[1], S[2], S[3]);
+          if constexpr (WRITE32) *reinterpret_cast<float4*>(buf + base + cc * cstride) = make_float4(S[0], S[1], S[2], S[3]);
           if (copy16) {
             __nv_bfloat162 lo = __floats2bfloat162_rn(S[0], S[1]), hi = __floats2bfloat162_rn(S[2], S[3]);
             *reinterpret_cast<uint2*>(copy16 + base + cc * cstride) =
                 make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
           }
         } else {
-          buf[base + cc * cstride] = S[0];
+          if constexpr (WRITE32) buf[base + cc * cstride] = S[0];
           if (copy16) copy16[base + cc * cstride] = __float2bfloat16_rn(S[0]);
         }
 #pragma unroll
@@ -88,30 +90,35 @@ __global__ void __launch_bounds__(256, 3) state_pass_kernel(float* __restrict__ 
   }
 }
 
-template <bool REVERSE, bool WRITE>
+template <bool REVERSE, bool WRITE, bool WRITE32>
 static int launch_state_pass(float* buf, const float* atot, const float* s_in, float* s_out, void* copy16,
                              const ScanArgs& a, cudaStream_t st) {
   const int NG = a.N * a.G, HR = a.H * a.R;
   const bool vec = NG % 4 == 0 && aligned16(buf) && (copy16 == nullptr || (reinterpret_cast<uintptr_t>(copy16) & 7u) == 0);
   if (vec) {
     dim3 grid((NG / 4 + 255) / 256, HR, a.B);
-    state_pass_kernel<4, REVERSE, WRITE><<<grid, 256, 0, st>>>(buf, atot, s_in, s_out, (__nv_bfloat16*)copy16, a.nc, HR, NG);
+    state_pass_kernel<4, REVERSE, WRITE, WRITE32><<<grid, 256, 0, st>>>(buf, atot, s_in, s_out, (__nv_bfloat16*)copy16, a.nc, HR, NG);
   } else {
     dim3 grid((NG + 255) / 256, HR, a.B);
-    state_pass_kernel<1, REVERSE, WRITE><<<grid, 256, 0, st>>>(buf, atot, s_in, s_out, (__nv_bfloat16*)copy16, a.nc, HR, NG);
+    state_pass_kernel<1, REVERSE, WRITE, WRITE32><<<grid, 256, 0, st>>>(buf, atot, s_in, s_out, (__nv_bfloat16*)copy16, a.nc, HR, NG);
   }
   ORBIT_CHECK_LAUNCH("state_pass_kernel");
   return OK;
 }
 
+// The rank-1 tensor-core kernels (R = O = 1 with bfloat16 state tiles supplied) read the bfloat16 tiles only.
+static bool tiles_only(const ScanArgs& a, const void* copy16) { return copy16 != nullptr && a.R == 1 && a.O == 1; }
+
 int launch_state_pass_fwd(const ScanArgs& a, const float* S0, float* S_fin, cudaStream_t st, bool dry = false) {
-  if (dry) return launch_state_pass<false, false>(a.Sin, a.atot, S0, S_fin, nullptr, a, st);
-  return launch_state_pass<false, true>(a.Sin, a.atot, S0, S_fin, a.Sin16, a, st);
+  if (dry) return launch_state_pass<false, false, false>(a.Sin, a.atot, S0, S_fin, nullptr, a, st);
+  if (tiles_only(a, a.Sin16)) return launch_state_pass<false, true, false>(a.Sin, a.atot, S0, S_fin, a.Sin16, a, st);
+  return launch_state_pass<false, true, true>(a.Sin, a.atot, S0, S_fin, a.Sin16, a, st);
 }
 
 int launch_state_pass_bwd(const ScanArgs& a, const float* dS_fin, float* dS0, cudaStream_t st, bool dry = false) {
-  if (dry) return launch_state_pass<true, false>(a.dS, a.atot, dS_fin, dS0, nullptr, a, st);
-  return launch_state_pass<true, true>(a.dS, a.atot, dS_fin, dS0, a.dS16, a, st);
+  if (dry) return launch_state_pass<true, false, false>(a.dS, a.atot, dS_fin, dS0, nullptr, a, st);
+  if (tiles_only(a, a.dS16)) return launch_state_pass<true, true, false>(a.dS, a.atot, dS_fin, dS0, a.dS16, a, st);
+  return launch_state_pass<true, true, true>(a.dS, a.atot, dS_fin, dS0, a.dS16, a, st);
 }
 
 // precision "ieee" phase launchers (scan_generic.cu)
@@ -137,7 +144,7 @@ static int check_common(const ScanArgs* a, int dtype, const char* who) {
                 "%s: ranks up to %d are served, got R=%d O=%d", who, SCAN_MAX_RANK, a->R, a->O);
   ORBIT_REQUIRE(a->T > 0 && a->nc == (a->L + a->T - 1) / a->T, ERR_BAD_ARG, "%s: nc=%d does not match L=%d, T=%d", who,
                 a->nc, a->L, a->T);
-  ORBIT_REQUIRE(a->u && a->Bhat && a->Chat && a->dA && a->w && a->wd && a->Sin && a->atot, ERR_BAD_ARG,
+  ORBIT_REQUIRE(a->u && a->Bhat && a->Chat && a->dA && a->w && a->wd && (a->Sin || a->Sin16) && a->atot, ERR_BAD_ARG,
                 "%s: null u/Bhat/Chat/dA/w/wd/Sin/atot", who);
   return OK;
 }

@@ -493,55 +493,45 @@ __global__ void __launch_bounds__(WS_THREADS, 1) tc_chunk_out_kernel(const __gri
   if (warp == 0) tmem_dealloc(tbase, 512);
 }
 
-// fp32 [128 n][64 p] state tile -> bf16 swizzled block; optionally accumulates sum(src * other) per thread
-__device__ __forceinline__ float load_state_bf16(const float* __restrict__ src, const float* __restrict__ other, uint8_t* dst) {
-  float acc = 0.f;
-  const float4* s4 = reinterpret_cast<const float4*>(src);
-  const float4* o4 = reinterpret_cast<const float4*>(other);
-#pragma unroll
-  for (int it = 0; it < 8; ++it) {
-    const int idx = it * TC_THREADS + threadIdx.x;
-    const int n = idx >> 4, c4 = idx & 15;
-    float4 v = s4[idx];
-    if (other != nullptr) {
-      float4 o = o4[idx];
-      acc = fmaf(v.x, o.x, fmaf(v.y, o.y, fmaf(v.z, o.z, fmaf(v.w, o.w, acc))));
-    }
-    *reinterpret_cast<uint2*>(dst + sw128_offset(n, c4 >> 1) + (c4 & 1) * 8) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
-  }
-  return acc;
-}
-
 // ------------------------------------------------------------------------------------------------------------------
 // chunk_grads, part 1 (state path).  Per head:
 //   da[t]   = sum_p dy[t,p] (C Sin)[t,p]                       -> a.ddA (scratch use; part 2 turns it into d dA)
 //   datot   = sum_{n,p} dSo[n,p] Sin[n,p]                      -> a.dw at the chunk's first token (scratch use)
 //   dCx[t,n] += a_t sum_p dy[t,p] Sin[n,p]                     accumulated over heads in TMEM -> a.dChat
 //   dBx[s,n] += e_s sum_p u[s,p]  dSo[n,p]                     accumulated over heads in TMEM -> a.dBhat
+//
+// Warp-specialised (10 warps): warps 0..3 read C Sin out of TMEM and form da; warps 4..7 form the per-token factors, write
+// the scaled tiles a_t dy and e_s u straight into TMEM (A operands of the accumulating products, so they never touch shared
+// memory) and sum <dSo, Sin>; one lane of warp 8 issues the TMA loads, one lane of warp 9 the MMAs.
 // ------------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(const __grid_constant__ CUtensorMap tmC,
-                                                                             const __grid_constant__ CUtensorMap tmU,
-                                                                             const __grid_constant__ CUtensorMap tmDY,
-                                                                             const __grid_constant__ CUtensorMap tmS,
-                                                                             const __grid_constant__ CUtensorMap tmDS,
-                                                                             const ScanArgs a) {
+constexpr int GT_THREADS = 320;
+constexpr int GT_XSTAGES = 3;           // u | dy tiles
+constexpr int GT_SSTAGES = 2;           // Sin | dSo tiles
+
+struct GStateBars {
+  uint64_t map, x_full[GT_XSTAGES], x_empty[GT_XSTAGES], s_full[GT_SSTAGES], s_empty[GT_SSTAGES], a_full[2], a_empty[2],
+      y_full[2], y_empty[2], fin;
+};
+
+__global__ void __launch_bounds__(GT_THREADS, 1) tc_chunk_grads_state_kernel(const __grid_constant__ CUtensorMap tmC,
+                                                                              const __grid_constant__ CUtensorMap tmU,
+                                                                              const __grid_constant__ CUtensorMap tmDY,
+                                                                              const __grid_constant__ CUtensorMap tmS,
+                                                                              const __grid_constant__ CUtensorMap tmDS,
+                                                                              const ScanArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   uint8_t* sC = sm;                      // 2 blocks
-  uint8_t* sX = sm + 2 * BLK;            // 2 buffers
-  uint8_t* sDY = sm + 4 * BLK;           // 2 buffers
-  uint8_t* sADY = sm + 6 * BLK;          // a_t * dy
-  uint8_t* sEX = sm + 7 * BLK;           // e_s * u
-  uint8_t* sS = sm + 8 * BLK;            // Sin  bf16 [n][p], 2 buffers
-  uint8_t* sdS = sm + 10 * BLK;          // dSo  bf16 [n][p], 2 buffers
-  float* fab = reinterpret_cast<float*>(sm + 12 * BLK);   // [2][a_t | e_s] x 128, buffer h & 1
-  float* dapart = fab + 512;             // [2][128]
-  float* wsum = dapart + 256;            // 8
-  float* red = wsum + 8;                 // 8
-  __shared__ uint64_t bar_map, bar_x[2], bar_m;
+  uint8_t* sX = sm + 2 * BLK;            // drive tiles, GT_XSTAGES buffers
+  uint8_t* sDY = sm + (2 + GT_XSTAGES) * BLK;
+  uint8_t* sS = sm + (2 + 2 * GT_XSTAGES) * BLK;               // Sin bf16 [n][p], GT_SSTAGES buffers
+  uint8_t* sdS = sm + (2 + 2 * GT_XSTAGES + GT_SSTAGES) * BLK; // dSo bf16 [n][p]
+  float* wsum = reinterpret_cast<float*>(sm + (2 + 2 * GT_XSTAGES + 2 * GT_SSTAGES) * BLK);   // [2][4] warp totals of the prefix
+  float* red = wsum + 8;                 // [2][4] warp sums of <dSo, Sin>
+  __shared__ GStateBars bars;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = warp & 3, wg = warp >> 2;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = warp & 3, role = warp >> 2;
   const int c = blockIdx.x, b = blockIdx.y, t0 = c * TC_T;
   const int Tv = min(TC_T, a.L - t0);
   const int H = a.H;
@@ -552,10 +542,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
   const int64_t srow0 = ((int64_t)b * a.nc + c) * H + h0;
 
   if (tid == 0) {
-    mbar_init(&bar_map, 1);
-    mbar_init(&bar_x[0], 1);
-    mbar_init(&bar_x[1], 1);
-    mbar_init(&bar_m, 1);
+    mbar_init(&bars.map, 1);
+    for (int i = 0; i < GT_XSTAGES; ++i) {
+      mbar_init(&bars.x_full[i], 1);
+      mbar_init(&bars.x_empty[i], 8);          // the scaling warps and the da warps
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars.s_full[i], 1);
+      mbar_init(&bars.s_empty[i], 5);          // the MMAs (one commit) and the four scaling warps (<dSo, Sin>)
+      mbar_init(&bars.a_full[i], 4);
+      mbar_init(&bars.a_empty[i], 1);
+      mbar_init(&bars.y_full[i], 1);
+      mbar_init(&bars.y_empty[i], 4);
+    }
+    mbar_init(&bars.fin, 1);
     mbar_fence_init();
     s_abort = 0;
   }
@@ -565,184 +565,197 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_chunk_grads_state_kernel(con
   tc_fence_after_sync();
   const uint32_t tbase = tmem_slot;
   volatile int* abort_flag = &s_abort;
-  const uint32_t TM_DCX = 0, TM_DBX = 128, TM_YCU = 256;
+  // accumulated cross terms, C Sin of two heads in flight, scaled operand tiles (packed bf16 pairs) of two heads in flight
+  const uint32_t TM_DCX = 0, TM_DBX = 128, TM_YCU = 256, TM_ADY = 384, TM_EX = 448;
+  bool dead = false;
 
-  if (tid == 0) {
-    mbar_expect_tx(&bar_map, 2 * BLK);
-    tma_load_3d(sC, &tmC, &bar_map, 0, t0, b);
-    tma_load_3d(sC + BLK, &tmC, &bar_map, 64, t0, b);
-    for (int i = 0; i < 2 && i < Hl; ++i) {
-      mbar_expect_tx(&bar_x[i], 4 * BLK);
-      tma_load_3d(sX + i * BLK, &tmU, &bar_x[i], (h0 + i) * TC_G, t0, b);
-      tma_load_3d(sDY + i * BLK, &tmDY, &bar_x[i], (h0 + i) * TC_G, t0, b);
-      tma_load_2d(sS + i * BLK, &tmS, &bar_x[i], 0, (int)(srow0 + i) * TC_N);
-      tma_load_2d(sdS + i * BLK, &tmDS, &bar_x[i], 0, (int)(srow0 + i) * TC_N);
-    }
-  }
-  const uint32_t id_y = idesc_bf16(128, 64, 0, 1), id_acc = idesc_bf16(128, 128, 0, 0);
-
-  // Two block-wide barriers per head.  The prefix of head h + 1 is formed beside the work of head h: its warp scans in
-  // the interval of the scaling pass, its per-token factors (fab[(h + 1) & 1]) in the interval of the MMAs.
-  auto warp_scan = [&](float v) -> float {   // inclusive scan inside the warp; warp totals of warps 0..3 -> wsum
-    float x = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      float y = __shfl_up_sync(0xffffffffu, x, o);
-      if (lane >= o) x += y;
-    }
-    if (warp < 4 && lane == 31) wsum[warp] = x;
-    return x;
-  };
-  auto token_factor = [&](int hh, float x, float wt) {   // after the barrier that publishes wsum
-    if (tid < 128) {
-      const float w0 = wsum[0], w1 = wsum[1], w2 = wsum[2], w3 = wsum[3];
-      const float off = warp == 0 ? 0.f : (warp == 1 ? w0 : (warp == 2 ? w0 + w1 : (w0 + w1) + w2));
-      const float tot = ((w0 + w1) + w2) + w3, csv = x + off;
-      fab[(hh & 1) * 256 + tid] = __expf(csv);
-      fab[(hh & 1) * 256 + 128 + tid] = __expf(tot - csv) * wt;
-    }
-  };
-  float d_n = 0.f, wt_n = 0.f;
-  const int64_t ck = ((int64_t)b * a.L + t0 + tid) * H + h0;
-  if (tid < Tv) {
-    d_n = a.dA[ck];
-    wt_n = a.w[ck];
-  }
-  float x_cur = warp_scan(d_n), wt_cur = wt_n;
-  if (tid < Tv && 1 < Hl) {
-    d_n = a.dA[ck + 1];
-    wt_n = a.w[ck + 1];
-  }
-  __syncthreads();
-  token_factor(0, x_cur, wt_cur);
-  __syncthreads();
+  if (role == 2) {
+    if (warp == 8 && lane == 0) {
+      // ---- producer ----
+      mbar_expect_tx(&bars.map, 2 * BLK);
+      tma_load_3d(sC, &tmC, &bars.map, 0, t0, b);
+      tma_load_3d(sC + BLK, &tmC, &bars.map, 64, t0, b);
 #pragma unroll 1
-  for (int h = 0; h < Hl; ++h) {
-    const int buf = h & 1;
-    const float *fa = fab + buf * 256, *fe = fa + 128;
-    if (h + 1 < Hl) {
-      x_cur = warp_scan(d_n);
-      wt_cur = wt_n;
-      if (tid < Tv && h + 2 < Hl) {
-        d_n = a.dA[ck + h + 2];
-        wt_n = a.w[ck + h + 2];
+      for (int h = 0; h < Hl; ++h) {
+        const int sx = h % GT_XSTAGES, ss = h % GT_SSTAGES;
+        if (h >= GT_XSTAGES && !lane_wait(&bars.x_empty[sx], (uint32_t)((h / GT_XSTAGES - 1) & 1), abort_flag, dead)) break;
+        mbar_expect_tx(&bars.x_full[sx], 2 * BLK);
+        tma_load_3d(sX + sx * BLK, &tmU, &bars.x_full[sx], (h0 + h) * TC_G, t0, b);
+        tma_load_3d(sDY + sx * BLK, &tmDY, &bars.x_full[sx], (h0 + h) * TC_G, t0, b);
+        if (h >= GT_SSTAGES && !lane_wait(&bars.s_empty[ss], (uint32_t)((h / GT_SSTAGES - 1) & 1), abort_flag, dead)) break;
+        mbar_expect_tx(&bars.s_full[ss], 2 * BLK);
+        tma_load_2d(sS + ss * BLK, &tmS, &bars.s_full[ss], 0, (int)(srow0 + h) * TC_N);
+        tma_load_2d(sdS + ss * BLK, &tmDS, &bars.s_full[ss], 0, (int)(srow0 + h) * TC_N);
+      }
+    } else if (warp == 9 && lane == 0) {
+      // ---- MMA issuer ----
+      const uint32_t id_y = idesc_bf16(128, 64, 0, 1), id_acc = idesc_bf16(128, 128, 0, 0);
+      lane_wait(&bars.map, 0, abort_flag, dead);
+#pragma unroll 1
+      for (int h = 0; h < Hl && !dead; ++h) {
+        const int ss = h % GT_SSTAGES, k = h & 1;
+        if (!lane_wait(&bars.s_full[ss], (uint32_t)((h / GT_SSTAGES) & 1), abort_flag, dead)) break;
+        if (h >= 2 && !lane_wait(&bars.y_empty[k], (uint32_t)(((h >> 1) - 1) & 1), abort_flag, dead)) break;
+        tc_fence_after_sync();
+        const uint32_t ac = smem_u32(sC), bs = smem_u32(sS + ss * BLK), bd = smem_u32(sdS + ss * BLK);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_YCU + 64u * k, desc_k(ac, ks), desc_mn(bs, ks), id_y, ks > 0 ? 1u : 0u);
+        umma_commit(&bars.y_full[k]);
+        if (!lane_wait(&bars.a_full[k], (uint32_t)((h >> 1) & 1), abort_flag, dead)) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_bf16_ta(tbase + TM_DCX, tbase + TM_ADY + 32u * k + 8u * ks, desc_k(bs, ks), id_acc, (h > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_bf16_ta(tbase + TM_DBX, tbase + TM_EX + 32u * k + 8u * ks, desc_k(bd, ks), id_acc, (h > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&bars.a_empty[k]);
+        umma_commit(&bars.s_empty[ss]);
+        if (h == Hl - 1) umma_commit(&bars.fin);
       }
     }
-    float part = 0.f;
-    if (wait_warp(&bar_x[buf], (uint32_t)((h >> 1) & 1), abort_flag)) {
-      const int row = tid & 127, half = tid >> 7;
-      const float f1 = fa[row], f2 = fe[row];
-      // <dSo, Sin> over this thread's share of the two state tiles (bf16 operands, fp32 sum)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t off = buf * BLK + sw128_offset(row, half * 4 + j);
-        uint4 p1 = *reinterpret_cast<const uint4*>(sS + off);
-        uint4 p2 = *reinterpret_cast<const uint4*>(sdS + off);
-        const uint32_t* q1 = reinterpret_cast<const uint32_t*>(&p1);
-        const uint32_t* q2 = reinterpret_cast<const uint32_t*>(&p2);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float a0, a1, b0, b1;
-          unpack_bf16(q1[k], a0, a1);
-          unpack_bf16(q2[k], b0, b1);
-          part = fmaf(a0, b0, fmaf(a1, b1, part));
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t off = sw128_offset(row, half * 4 + j);
-        uint4 v = *reinterpret_cast<const uint4*>(sDY + buf * BLK + off);
-        uint4 x = *reinterpret_cast<const uint4*>(sX + buf * BLK + off);
-        uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
-        uint32_t* px = reinterpret_cast<uint32_t*>(&x);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float lo, hi;
-          unpack_bf16(pv[k], lo, hi);
-          pv[k] = pack_bf16(lo * f1, hi * f1);
-          unpack_bf16(px[k], lo, hi);
-          px[k] = pack_bf16(lo * f2, hi * f2);
-        }
-        *reinterpret_cast<uint4*>(sADY + off) = v;
-        *reinterpret_cast<uint4*>(sEX + off) = x;
-      }
-    }
-    fence_proxy_async();
-    part = warp_sum(part);
-    if (lane == 0) red[warp] = part;
-    __syncthreads();                       // the scaled tiles, the warp sums and wsum are complete
-    if (h + 1 < Hl) token_factor(h + 1, x_cur, wt_cur);
-    if (tid == 0) {
-      float datot = 0.f;
-#pragma unroll
-      for (int ww = 0; ww < TC_THREADS / 32; ++ww) datot += red[ww];
-      a.dw[((int64_t)b * a.L + t0) * H + h0 + h] = datot;
-    }
-    if (tid == 0 && !*abort_flag) {
-      bool ok = (h > 0) || wait_or_abort(&bar_map, 0, abort_flag);
+    __syncwarp();
+  } else if (role == 0) {
+    // ---- da group: da[t] = <dy[t,:], (C Sin)[t,:]> ----
+#pragma unroll 1
+    for (int h = 0; h < Hl; ++h) {
+      const int sx = h % GT_XSTAGES, k = h & 1;
+      bool ok = role_wait(&bars.y_full[k], (uint32_t)((h >> 1) & 1), abort_flag, dead);
+      ok = role_wait(&bars.x_full[sx], (uint32_t)((h / GT_XSTAGES) & 1), abort_flag, dead) && ok;
+      float dsum = 0.f;
       if (ok) {
         tc_fence_after_sync();
-        const uint32_t ac = smem_u32(sC), bs = smem_u32(sS + buf * BLK), bd = smem_u32(sdS + buf * BLK), aa = smem_u32(sADY),
-                       ae = smem_u32(sEX);
+        const uint8_t* dytile = sDY + sx * BLK;
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld32(tmem_addr(tbase, q * 32, TM_YCU + 64u * k + half * 32), r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_YCU, desc_k(ac, ks), desc_mn(bs, ks), id_y, ks > 0 ? 1u : 0u);
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const uint4 dv = *reinterpret_cast<const uint4*>(dytile + sw128_offset(t, half * 4 + k4));
+            const uint32_t* dp = reinterpret_cast<const uint32_t*>(&dv);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) umma_bf16(tbase + TM_DCX, desc_k(aa, ks), desc_k(bs, ks), id_acc, (h > 0 || ks > 0) ? 1u : 0u);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) umma_bf16(tbase + TM_DBX, desc_k(ae, ks), desc_k(bd, ks), id_acc, (h > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&bar_m);
+            for (int e = 0; e < 4; ++e) {
+              float lo, hi;
+              unpack_bf16(dp[e], lo, hi);
+              dsum = fmaf(lo, __uint_as_float(r[k4 * 8 + 2 * e]), dsum);
+              dsum = fmaf(hi, __uint_as_float(r[k4 * 8 + 2 * e + 1]), dsum);
+            }
+          }
+        }
+        if (t < Tv) a.ddA[((int64_t)b * a.L + t0 + t) * H + h0 + h] = dsum;
       }
+      warp_arrive(&bars.y_empty[k], false);
+      if (lane == 0) mbar_arrive(&bars.x_empty[sx]);
     }
-    float dsum = 0.f;
-    if (wait_warp(&bar_m, (uint32_t)(h & 1), abort_flag)) {
+    // ---- accumulated cross terms -> global (fp32 rows of N) ----
+    if (role_wait(&bars.fin, 0, abort_flag, dead)) {
       tc_fence_after_sync();
-      uint32_t r[32];
-      tmem_ld32(tmem_addr(tbase, q * 32, TM_YCU + wg * 32), r);
-      tmem_ld_wait();
+#pragma unroll 1
+      for (int col = 0; col < 128; col += 32) {
+        uint32_t r1[32], r2[32];
+        tmem_ld32(tmem_addr(tbase, q * 32, TM_DCX + col), r1);
+        tmem_ld32(tmem_addr(tbase, q * 32, TM_DBX + col), r2);
+        tmem_ld_wait();
+        if (t < Tv) {
+          float* dc = a.dChat + (((int64_t)blockIdx.z * a.B + b) * a.L + t0 + t) * TC_N + col;
+          float* db = a.dBhat + (((int64_t)blockIdx.z * a.B + b) * a.L + t0 + t) * TC_N + col;
 #pragma unroll
-      for (int k4 = 0; k4 < 4; ++k4) {
-        uint4 dv = *reinterpret_cast<const uint4*>(sDY + buf * BLK + sw128_offset(t, wg * 4 + k4));
-        const uint32_t* dp = reinterpret_cast<const uint32_t*>(&dv);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float lo, hi;
-          unpack_bf16(dp[k], lo, hi);
-          dsum = fmaf(lo, __uint_as_float(r[k4 * 8 + 2 * k]), dsum);
-          dsum = fmaf(hi, __uint_as_float(r[k4 * 8 + 2 * k + 1]), dsum);
+          for (int j = 0; j < 32; j += 4) {
+            *reinterpret_cast<float4*>(dc + j) = make_float4(__uint_as_float(r1[j]), __uint_as_float(r1[j + 1]), __uint_as_float(r1[j + 2]), __uint_as_float(r1[j + 3]));
+            *reinterpret_cast<float4*>(db + j) = make_float4(__uint_as_float(r2[j]), __uint_as_float(r2[j + 1]), __uint_as_float(r2[j + 2]), __uint_as_float(r2[j + 3]));
+          }
         }
       }
     }
-    dapart[wg * 128 + t] = dsum;
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid < Tv) a.ddA[((int64_t)b * a.L + t0 + tid) * H + h0 + h] = dapart[tid] + dapart[128 + tid];
-    if (tid == 0 && !*abort_flag && h + 2 < Hl) {
-      mbar_expect_tx(&bar_x[buf], 4 * BLK);
-      tma_load_3d(sX + buf * BLK, &tmU, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
-      tma_load_3d(sDY + buf * BLK, &tmDY, &bar_x[buf], (h0 + h + 2) * TC_G, t0, b);
-      tma_load_2d(sS + buf * BLK, &tmS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
-      tma_load_2d(sdS + buf * BLK, &tmDS, &bar_x[buf], 0, (int)(srow0 + h + 2) * TC_N);
+  } else {
+    // ---- scaling group: factors of head h, a_t dy and e_s u -> TMEM, <dSo, Sin> ----
+    const int64_t ck = ((int64_t)b * a.L + t0 + min(t, Tv - 1)) * H + h0;
+    const bool live = t < Tv;
+    float d_n = 0.f, w_n = 0.f;
+    if (live && Hl > 0) {
+      d_n = a.dA[ck];
+      w_n = a.w[ck];
     }
-  }
-  // accumulated cross terms -> global (fp32 rows of N)
-  if (!*abort_flag) {
-    tc_fence_after_sync();
+#pragma unroll 1
+    for (int h = 0; h < Hl; ++h) {
+      const int sx = h % GT_XSTAGES, ss = h % GT_SSTAGES, k = h & 1;
+      const float wt = w_n;
+      float x = d_n;
 #pragma unroll
-    for (int jj = 0; jj < 2; ++jj) {
-      const int col = wg * 64 + jj * 32;
-      uint32_t r1[32], r2[32];
-      tmem_ld32(tmem_addr(tbase, q * 32, TM_DCX + col), r1);
-      tmem_ld32(tmem_addr(tbase, q * 32, TM_DBX + col), r2);
-      tmem_ld_wait();
-      if (t < Tv) {
-        float* dc = a.dChat + (((int64_t)blockIdx.z * a.B + b) * a.L + t0 + t) * TC_N + col;
-        float* db = a.dBhat + (((int64_t)blockIdx.z * a.B + b) * a.L + t0 + t) * TC_N + col;
+      for (int o = 1; o < 32; o <<= 1) {
+        const float y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+      }
+      if (lane == 31) wsum[k * 4 + q] = x;
+      if (h + 1 < Hl && live) {
+        d_n = a.dA[ck + h + 1];
+        w_n = a.w[ck + h + 1];
+      }
+      named_bar_sync(1, 128);
+      const float* ws = wsum + k * 4;
+      const float w0 = ws[0], w1 = ws[1], w2 = ws[2], w3 = ws[3];
+      const float off = q == 0 ? 0.f : (q == 1 ? w0 : (q == 2 ? w0 + w1 : (w0 + w1) + w2));
+      const float tot = ((w0 + w1) + w2) + w3, csv = x + off;
+      const float f1 = __expf(csv), f2 = __expf(tot - csv) * wt;
+      bool go = role_wait(&bars.x_full[sx], (uint32_t)((h / GT_XSTAGES) & 1), abort_flag, dead);
+      if (h >= 2) go = role_wait(&bars.a_empty[k], (uint32_t)(((h >> 1) - 1) & 1), abort_flag, dead) && go;
+      if (go) {
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          uint32_t pa[16], pe[16];
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          *reinterpret_cast<float4*>(dc + j) = make_float4(__uint_as_float(r1[j]), __uint_as_float(r1[j + 1]), __uint_as_float(r1[j + 2]), __uint_as_float(r1[j + 3]));
-          *reinterpret_cast<float4*>(db + j) = make_float4(__uint_as_float(r2[j]), __uint_as_float(r2[j + 1]), __uint_as_float(r2[j + 2]), __uint_as_float(r2[j + 3]));
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t off8 = sx * BLK + sw128_offset(t, half * 4 + j);
+            const uint4 dv = *reinterpret_cast<const uint4*>(sDY + off8);
+            const uint4 xv = *reinterpret_cast<const uint4*>(sX + off8);
+            const uint32_t* dp = reinterpret_cast<const uint32_t*>(&dv);
+            const uint32_t* xp = reinterpret_cast<const uint32_t*>(&xv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float lo, hi;
+              unpack_bf16(dp[e], lo, hi);
+              pa[j * 4 + e] = pack_bf16(lo * f1, hi * f1);
+              unpack_bf16(xp[e], lo, hi);
+              pe[j * 4 + e] = pack_bf16(lo * f2, hi * f2);
+            }
+          }
+          tmem_st16(tmem_addr(tbase, q * 32, TM_ADY + 32u * k + half * 16), pa);
+          tmem_st16(tmem_addr(tbase, q * 32, TM_EX + 32u * k + half * 16), pe);
+        }
+        tmem_st_wait();
+      }
+      warp_arrive(&bars.a_full[k], false);
+      if (lane == 0) mbar_arrive(&bars.x_empty[sx]);
+      // <dSo, Sin> over this thread's share of the two state tiles (bf16 operands, fp32 sum)
+      float part = 0.f;
+      if (role_wait(&bars.s_full[ss], (uint32_t)((h / GT_SSTAGES) & 1), abort_flag, dead)) {
+        const int gt = tid - 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t off8 = ss * BLK + sw128_offset(gt, j);
+          const uint4 p1 = *reinterpret_cast<const uint4*>(sS + off8);
+          const uint4 p2 = *reinterpret_cast<const uint4*>(sdS + off8);
+          const uint32_t* q1 = reinterpret_cast<const uint32_t*>(&p1);
+          const uint32_t* q2 = reinterpret_cast<const uint32_t*>(&p2);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float a0, a1, b0, b1;
+            unpack_bf16(q1[e], a0, a1);
+            unpack_bf16(q2[e], b0, b1);
+            part = fmaf(a0, b0, fmaf(a1, b1, part));
+          }
         }
       }
+      part = warp_sum(part);
+      if (lane == 0) {
+        red[k * 4 + q] = part;
+        mbar_arrive(&bars.s_empty[ss]);
+      }
+      named_bar_sync(1, 128);
+      if (tid == 128) a.dw[((int64_t)b * a.L + t0) * H + h0 + h] = (red[k * 4] + red[k * 4 + 1]) + (red[k * 4 + 2] + red[k * 4 + 3]);
     }
   }
   tc_fence_before_sync();
@@ -803,7 +816,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
   float* colsum = rowpart + 512;         // [2][128] column sums of K o E (du group)
   float* depart = colsum + 256;          // [2][128] de (du group)
   float* kdiag = depart + 256;           // [2][128] K[s,s] (du group)
-  float* ddpart = kdiag + 256;           // [2][4][64] dD partial sums per row quarter (du group)
+  float* ddpart = kdiag + 256;           // [2][2][64] dD partial sums over the upper / lower 64 tokens
   float* cbd = ddpart + 512;             // [128] CB[s,s] of this chunk
   float* tkred = cbd + 128;              // token warps: [16] scratch of their reductions
   __shared__ GScoreBars bars;
@@ -908,7 +921,11 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
 #pragma unroll 1
       for (int h = 0; h < Hl && !dead; ++h) {
         const int sx = h % GS_XSTAGES, ss = h & 1;
-        // X2 = B dSo needs nothing from the score pass: it runs under it
+        // the score pass of head h is over: dM of head h + 1 first (the next score pass waits for nothing else), then
+        // the two du products of head h once the du group has read out those of head h - 1
+        if (!lane_wait(&bars.ms_full, (uint32_t)(h & 1), abort_flag, dead)) break;
+        if (h + 1 < Hl) group_a(h + 1);
+        if (dead) break;
         if (!lane_wait(&bars.s_full[ss], (uint32_t)((h >> 1) & 1), abort_flag, dead)) break;
         if (h >= 1 && !lane_wait(&bars.dx_empty, (uint32_t)((h - 1) & 1), abort_flag, dead)) break;
         tc_fence_after_sync();
@@ -916,11 +933,6 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DX2, desc_k(ab, ks), desc_mn(bd, ks), id_x2, ks > 0 ? 1u : 0u);
         umma_commit(&bars.s_empty[ss]);
-        // the score pass of head h is over: dM of head h + 1 first (the next score pass waits for it), then X1 = Ms^T dy
-        if (h + 1 < Hl) group_a(h + 1);
-        if (dead) break;
-        if (!lane_wait(&bars.ms_full, (uint32_t)(h & 1), abort_flag, dead)) break;
-        tc_fence_after_sync();
         const uint32_t am = smem_u32(sMs), bdy = smem_u32(sDY + sx * BLK);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DX1, desc_mn(am, ks), desc_mn(bdy, ks), id_x1, ks > 0 ? 1u : 0u);
@@ -957,7 +969,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
         uint8_t* utile = sX + sx * BLK;
         const uint8_t* dytile = sDY + sx * BLK;
         // eight groups of eight columns; a short loop body that stays in the instruction cache
-#pragma unroll 1
+#pragma unroll 2
         for (int k8 = 0; k8 < 8; ++k8) {
           uint32_t r1[8], r2[8];
           tmem_ld8(tmem_addr(tbase, q * 32, TM_DX1 + k8 * 8), r1);
@@ -973,7 +985,6 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
           const float dd[8] = {dlo.x, dlo.y, dlo.z, dlo.w, dhi.x, dhi.y, dhi.z, dhi.w};
           tmem_ld_wait();
           uint32_t outp[4];
-          float ddv[8];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             float u0, u1, g0, g1;
@@ -985,16 +996,9 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
                                 fmaf(dd[2 * e + 1] + dgv, g1, fmaf(es, x21, wt * x11)));
             de = fmaf(u0, x20, fmaf(u1, x21, de));
             cso = fmaf(u0, x10, fmaf(u1, x11, cso));
-            ddv[2 * e] = g0 * u0;
-            ddv[2 * e + 1] = g1 * u1;
-            dyu += ddv[2 * e] + ddv[2 * e + 1];
+            dyu = fmaf(g0, u0, fmaf(g1, u1, dyu));
           }
           *slot = make_uint4(outp[0], outp[1], outp[2], outp[3]);
-          if (a.dDg_part) {
-            const float csum = warp_colsum8(ddv, lane);
-            if ((lane & 3) == 0)
-              ddpart[(pb * 4 + q) * 64 + k8 * 8 + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = csum;
-          }
         }
       }
       depart[pb * 128 + t] = de;
@@ -1068,8 +1072,11 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
         cbd[t] = dv;
       }
     }
-    // live 16-column pieces of this warp: slab j = 2 sg + (pi >> 1) is live when j <= q
+    // live 16-column pieces of this warp: slab j = 2 sg + (pi >> 1) is live when j <= q.  The two warps without any
+    // (row quarters 0 and 1 of the upper slab pair) sum dD[p] = sum_t dy[t,p] u[t,p] over 64 tokens each instead: a lane
+    // owns two columns and walks down the rows of the two tiles, so the sum needs no exchange between threads.
     const int npieces = q < 2 * sg ? 0 : (q == 2 * sg ? 2 : 4);
+    const bool dd_warp = npieces == 0 && a.dDg_part != nullptr;
 #pragma unroll 1
     for (int h = 0; h < Hl; ++h) {
       const int pb = h & 1;
@@ -1081,6 +1088,25 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
       if (h >= 1) go = role_wait(&bars.ms_empty, (uint32_t)((h - 1) & 1), abort_flag, dead) && go;
       if (h >= 2) go = role_wait(&bars.part_empty[pb], (uint32_t)(((h >> 1) - 1) & 1), abort_flag, dead) && go;
       float rowS = 0.f;
+      if (dd_warp) {
+        const int sx = h % GS_XSTAGES;
+        if (role_wait(&bars.x_full[sx], (uint32_t)((h / GS_XSTAGES) & 1), abort_flag, dead)) {
+          const uint8_t* ut = sX + sx * BLK;
+          const uint8_t* dt = sDY + sx * BLK;
+          float s0 = 0.f, s1 = 0.f;
+#pragma unroll 4
+          for (int r = 0; r < 64; ++r) {
+            const int row = q * 64 + r;
+            const uint32_t off = sw128_offset(row, lane >> 2) + (lane & 3) * 4;
+            float u0, u1, g0, g1;
+            unpack_bf16(*reinterpret_cast<const uint32_t*>(ut + off), u0, u1);
+            unpack_bf16(*reinterpret_cast<const uint32_t*>(dt + off), g0, g1);
+            s0 = fmaf(g0, u0, s0);
+            s1 = fmaf(g1, u1, s1);
+          }
+          *reinterpret_cast<float2*>(ddpart + (pb * 2 + q) * 64 + lane * 2) = make_float2(s0, s1);
+        }
+      }
       if (go) {
         tc_fence_after_sync();
         const float cst = cs[t], wdt_t = wdv[t];
@@ -1289,8 +1315,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
           if (a.dwd) a.dwd[gb] = kdiag[pb * 128 + tb];
         }
         if (a.dDg_part && ok)
-          a.dDg_part[(((int64_t)b * a.nc + c) * H + h0 + h) * TC_G + i] =
-              (ddpart[(pb * 4 + 0) * 64 + i] + ddpart[(pb * 4 + 1) * 64 + i]) + (ddpart[(pb * 4 + 2) * 64 + i] + ddpart[(pb * 4 + 3) * 64 + i]);
+          a.dDg_part[(((int64_t)b * a.nc + c) * H + h0 + h) * TC_G + i] = ddpart[(pb * 2 + 0) * 64 + i] + ddpart[(pb * 2 + 1) * 64 + i];
         named_bar_sync(4, 64);             // tkred is free for the next prefix
       }
       warp_arrive(&bars.part_empty[pb], false);
@@ -1406,8 +1431,8 @@ int tc_launch_chunk_out(const ScanArgs& a, cudaStream_t st) {
   return OK;
 }
 
-constexpr int SMEM_GSTATE = 12 * BLK + 4096 + 1024;
-constexpr int SMEM_GSCORE = (6 + 2 * GS_XSTAGES) * BLK + (GS_ROWS * GS_ROW_LD + 512 + 256 + 256 + 256 + 512 + 128 + 16) * 4 + 1024;
+constexpr int SMEM_GSTATE = (2 + 2 * GT_XSTAGES + 2 * GT_SSTAGES) * BLK + 64 + 1024;
+constexpr int SMEM_GSCORE = (6 + 2 * GS_XSTAGES) * BLK + (GS_ROWS * GS_ROW_LD + 512 + 256 + 256 + 256 + 512 + 128 + 16) * 4 + 1024;   // ddpart keeps its 512-float slot
 
 int tc_launch_chunk_grads(const ScanArgs& a, cudaStream_t st) {
   if (mimo_tc_geometry(a.R, a.O, a.G, a.N)) return mimo_tc_launch_grads(a, st);
@@ -1424,7 +1449,7 @@ int tc_launch_chunk_grads(const ScanArgs& a, cudaStream_t st) {
   if ((rc = map_rows(&tmDU, a.du, a.H * TC_G, (int64_t)a.H * TC_G, a.L, a.B)) != OK) return rc;
   ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_grads_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GSTATE));
   ORBIT_CHECK_CUDA(cudaFuncSetAttribute(tc_chunk_grads_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GSCORE));
-  tc_chunk_grads_state_kernel<<<dim3(a.nc, a.B, head_split(a)), TC_THREADS, SMEM_GSTATE, st>>>(tmC, tmU, tmDY, tmS, tmDS, a);
+  tc_chunk_grads_state_kernel<<<dim3(a.nc, a.B, head_split(a)), GT_THREADS, SMEM_GSTATE, st>>>(tmC, tmU, tmDY, tmS, tmDS, a);
   ORBIT_CHECK_LAUNCH("tc_chunk_grads_state_kernel");
   tc_chunk_grads_score_kernel<<<dim3(a.nc, a.B, head_split(a)), GS_THREADS, SMEM_GSCORE, st>>>(tmB, tmC, tmU, tmDY, tmDS, tmDU, a);
   ORBIT_CHECK_LAUNCH("tc_chunk_grads_score_kernel");

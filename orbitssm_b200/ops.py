@@ -508,7 +508,8 @@ class HaloFn(torch.autograd.Function):
 
 def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0, cp=None):
     """Forward scan.  Returns (y [B, L, H*G*O], S_fin [B, H, R, N, G] fp32, Sin, atot); with the tensor-core precision
-    `Sin` is the pair (Sin fp32, Sin16 bfloat16 tiles) that the backward needs.  With `cp` (a `ContextParallel`) the
+    `Sin` is the pair (None, Sin16): the backward of the rank-1 tiles reads the bfloat16 state tiles only (the fp32 buffer holds
+    chunk-local values after the state pass and is dropped); the rank-4 tiles keep the fp32 states.  With `cp` (a `ContextParallel`) the
     segment is continued from its predecessors' segments and S_fin is the state at this segment's end."""
     _require_cuda("ssd_scan_fwd", u, Bhat, Chat, dA)
     B, L = u.shape[:2]
@@ -547,7 +548,7 @@ def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     run_phase(a, "scan_state_pass", _lib.PHASE_STATE_PASS, S0, S_fin, dt, precision)
     run_phase(a, "scan_chunk_out", _lib.PHASE_CHUNK_OUT, None, None, dt, precision)
     del keep
-    return y, S_fin, (Sin if Sin16 is None else (Sin, Sin16)), atot
+    return y, S_fin, (Sin if Sin16 is None else (None, Sin16)), atot
 
 
 _STATUS = {}
@@ -595,7 +596,7 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     B, L = u.shape[:2]
     H, R, O, G, N = geo.H, geo.R, geo.O, geo.G, geo.N
     Sin, Sin16 = Sin if isinstance(Sin, tuple) else (Sin, None)
-    nc = Sin.shape[1]
+    nc = (Sin if Sin is not None else Sin16).shape[1]
     dev = u.device
     f32 = dict(device=dev, dtype=torch.float32)
     a = _lib.ScanArgs()
@@ -622,7 +623,8 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     elif precision == _lib.PRECISION_IO:                 # rank-4 tiles sum du over the siblings of a head in fp32
         du32 = torch.empty(u.shape, **f32)
         a.du32 = du32.data_ptr()
-    a.Sin, a.atot, a.dS, a.dy, a.du = Sin.data_ptr(), atot.data_ptr(), dS.data_ptr(), dy.data_ptr(), out["du"].data_ptr()
+    a.Sin = Sin.data_ptr() if Sin is not None else None
+    a.atot, a.dS, a.dy, a.du = atot.data_ptr(), dS.data_ptr(), dy.data_ptr(), out["du"].data_ptr()
     a.dBhat, a.dChat, a.ddA, a.dw = (out[k].data_ptr() for k in ("dBhat", "dChat", "ddA", "dw"))
     # The rank-1 gradient kernels keep one CTA per (batch, chunk) by default: their per-CTA epilogue (128 KB of map
     # gradients written, then read and written again) outweighs the wave-quantisation gain of a head split (measured at
