@@ -289,6 +289,24 @@ int orbit_hm_scan_fwd(const orbit_hm_args* a, int dtype, void* stream);
  * accumulation into caller memory, no atomics): the caller sums them over their leading axis. */
 int orbit_hm_scan_bwd(const orbit_hm_args* a, int dtype, void* stream);
 
+/* ---- context parallelism: the exchange step of the SSD-MIMO scan ------------------------------------------------
+ * A sequence split over W ranks (rank j holds segment j) needs one all-gather per direction.  Rank j contributes the
+ * record [ F_j | A_j ] (forward) or [ E_j | A_j | X_j ] (backward), all float32:
+ *   F_j [B, H, R, N, G]  state its segment leaves when started from zero (ORBIT_PHASE_STATE_PASS_DRY writes it in place)
+ *   A_j [B, H, R]        total log-decay of its segment (orbit_cp_state_pack sums dA over the segment into the record)
+ *   E_j [B, H, R, N, G]  what its segment's outputs ask of the entering state (ORBIT_PHASE_STATE_PASS_BWD_DRY)
+ *   X_j [B, H, R, N, G]  gradient a caller put on the state rank j returned (zeros if none)
+ * orbit_cp_state_combine reads the W gathered records ([W][stride] floats, in this GPU's memory) and writes
+ *   forward   S_r = sum_{j<r} exp(A_{j+1} + .. + A_{r-1}) F_j        the state entering this rank's segment
+ *   backward  d_r: d_{W-1} = X_{W-1}, d_{j-1} = X_{j-1} + E_j + exp(A_j) d_j     gradient of the state leaving it.
+ * n_state = B*H*R*N*G, per_head = N*G, BHR = B*H*R.  No counterpart in the reference, which is single-process; the terms
+ * are those of its chunk-parallel pass (src/orbit_ssm/kernels/ssd_mimo/chunkpar.py:19-25) and of its State continuation
+ * contract (src/orbit_ssm/ssm/ssd_mimo_torch.py:677-679). */
+int64_t orbit_cp_record_floats(int64_t n_state, int BHR, int backward);
+int orbit_cp_state_pack(const float* dA, float* record, int B, int L, int HR, int64_t n_state, void* stream);
+int orbit_cp_state_combine(const float* records, int64_t stride, int world, int rank, int64_t n_state, int per_head, int BHR,
+                           int backward, float* out, void* stream);
+
 /* ---- diagnostics ---------------------------------------------------------------------------------------------
  * One 128 x N x K tcgen05 tile through the same TMA boxes, shared-memory descriptors and TMEM read-out as the scan
  * kernels: D[128, N] fp32 = op(A) * op(B), A and B bfloat16.  mode bit 0: A given as [K, 128] (M contiguous) instead

@@ -452,3 +452,23 @@ def run_clock(a, name, backward, dtype_code, compute=torch.float64):
     if t.get("g_alog") is not None:
         # per-row term of dA_log: d dA / d A_log = dA itself (rate = exp(A_log))
         t["g_alog"].copy_(_f(t["ddA"], compute) * out["dA"].detach())
+
+
+# ---- context-parallel exchange records (torch restatements of orbit_cp_state_pack / orbit_cp_state_combine) ----------
+def cp_pack(dA, record, n_state):
+    record[n_state:n_state + dA.shape[0] * dA.shape[2] * dA.shape[3]] = dA.sum(1).reshape(-1).to(record.dtype)
+
+
+def cp_combine(records, world, rank, n_state, per_head, BHR, backward):
+    st = records[:, :n_state].double()
+    dec = records[:, n_state:n_state + BHR].double().exp().repeat_interleave(per_head, dim=1)
+    if not backward:
+        S = torch.zeros(n_state, dtype=torch.float64)
+        for j in range(rank):
+            S = dec[j] * S + st[j]
+        return S.to(records.dtype)
+    ext = records[:, n_state + BHR:n_state + BHR + n_state].double()
+    d = ext[world - 1]
+    for j in range(world - 1, rank, -1):
+        d = ext[j - 1] + st[j] + dec[j] * d
+    return d.to(records.dtype)

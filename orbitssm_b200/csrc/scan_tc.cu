@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) tc_chunk_state_kernel(const __g
         tc_fence_after_sync();
         const uint32_t am = smem_u32(sM), bx = smem_u32(sXs + k * BLK);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + k * 64, desc_mn(am, ks), desc_mn(bx, ks), idesc, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < 8; ++ks) umma_bf16_h(tbase + k * 64, lo_mn(am) + inc_mn(ks), lo_mn(bx) + inc_mn(ks), idesc, ks > 0 ? 1u : 0u);
         umma_commit(&bars.xs_empty[k]);
         umma_commit(&bars.acc_full[k]);
       }
@@ -303,7 +303,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) tc_chunk_out_kernel(const __gri
         const uint32_t ac = smem_u32(sC), bb = smem_u32(sMs);
         const uint32_t id = idesc_bf16(128, 128, 0, 0);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_CB, desc_k(ac, ks), desc_k(bb, ks), id, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < 8; ++ks) umma_bf16_h(tbase + TM_CB, lo_k(ac) + inc_k(ks), lo_k(bb) + inc_k(ks), id, ks > 0 ? 1u : 0u);
         umma_commit(&bars.cb);
       }
 #pragma unroll 1
@@ -316,14 +316,14 @@ __global__ void __launch_bounds__(WS_THREADS, 1) tc_chunk_out_kernel(const __gri
         // the inter-chunk part C Sin needs no mask: it runs while the mask group still works on this head
         const uint32_t ac = smem_u32(sC), bs = smem_u32(sS + ss * BLK);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(acc + 64, desc_k(ac, ks), desc_mn(bs, ks), idesc_y, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < 8; ++ks) umma_bf16_h(acc + 64, lo_k(ac) + inc_k(ks), lo_mn(bs) + inc_mn(ks), idesc_y, ks > 0 ? 1u : 0u);
         umma_commit(&bars.s_empty[ss]);    // the state tile may be reloaded
         if (!lane_wait(&bars.u_full[su], (uint32_t)((h / WS_XSTAGES) & 1), abort_flag, dead)) break;
         if (!lane_wait(&bars.ms_full[k], (uint32_t)((h >> 1) & 1), abort_flag, dead)) break;
         tc_fence_after_sync();
         const uint32_t am = smem_u32(sMs + k * 2 * BLK), bx = smem_u32(sX + su * BLK);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(acc, desc_k(am, ks), desc_mn(bx, ks), idesc_y, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < 8; ++ks) umma_bf16_h(acc, lo_k(am) + inc_k(ks), lo_mn(bx) + inc_mn(ks), idesc_y, ks > 0 ? 1u : 0u);
         umma_commit(&bars.ms_empty[k]);    // the masked-score tile may be rewritten
         umma_commit(&bars.acc_full[k]);    // both products of this head are in TMEM
       }
@@ -334,6 +334,10 @@ __global__ void __launch_bounds__(WS_THREADS, 1) tc_chunk_out_kernel(const __gri
 #pragma unroll 1
     for (int h = 0; h < Hl; ++h) {
       const int su = h % WS_XSTAGES, k = h & 1;
+      if (tid == 0 && h > 0) {
+        bulk_wait_group_read<0>();         // the store of head h - 1 (issued a head ago) has read its tile:
+        mbar_arrive(&bars.u_empty[(h - 1) % WS_XSTAGES]);   // that drive stage may be reloaded
+      }
       const bool ok = role_wait(&bars.acc_full[k], (uint32_t)((h >> 1) & 1), abort_flag, dead);
       if (ok) {
         tc_fence_after_sync();
@@ -370,10 +374,6 @@ __global__ void __launch_bounds__(WS_THREADS, 1) tc_chunk_out_kernel(const __gri
       }
       // the accumulator set is free again (arrivals also on the wind-down path, so nothing waits for them)
       warp_arrive(&bars.acc_empty[k], true);
-      if (tid == 0) {
-        bulk_wait_group_read<0>();         // the store of head h - 1 has read its tile: that drive stage may be reloaded
-        if (h > 0) mbar_arrive(&bars.u_empty[(h - 1) % WS_XSTAGES]);
-      }
       named_bar_sync(3, 128);              // every row of the y tile is written (and fenced for the async proxy)
       if (tid == 0 && ok) {
         tma_store_3d(&tmY, sX + su * BLK, (h0 + h) * TC_G, t0, b);   // rows past the end of the sequence are clipped
@@ -500,9 +500,9 @@ __global__ void __launch_bounds__(WS_THREADS, 1) tc_chunk_out_kernel(const __gri
 //   dCx[t,n] += a_t sum_p dy[t,p] Sin[n,p]                     accumulated over heads in TMEM -> a.dChat
 //   dBx[s,n] += e_s sum_p u[s,p]  dSo[n,p]                     accumulated over heads in TMEM -> a.dBhat
 //
-// Warp-specialised (10 warps): warps 0..3 read C Sin out of TMEM and form da; warps 4..7 form the per-token factors, write
-// the scaled tiles a_t dy and e_s u straight into TMEM (A operands of the accumulating products, so they never touch shared
-// memory) and sum <dSo, Sin>; one lane of warp 8 issues the TMA loads, one lane of warp 9 the MMAs.
+// Warp-specialised (10 warps): warps 0..3 read C Sin out of TMEM, form da and sum <dSo, Sin>; warps 4..7 form the per-token
+// factors and write the scaled tiles a_t dy and e_s u straight into TMEM (A operands of the accumulating products, so they
+// never touch shared memory); one lane of warp 8 issues the TMA loads, one lane of warp 9 the MMAs.
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int GT_THREADS = 320;
 constexpr int GT_XSTAGES = 3;           // u | dy tiles
@@ -549,7 +549,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) tc_chunk_grads_state_kernel(con
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars.s_full[i], 1);
-      mbar_init(&bars.s_empty[i], 5);          // the MMAs (one commit) and the four scaling warps (<dSo, Sin>)
+      mbar_init(&bars.s_empty[i], 5);          // the MMAs (one commit) and the four da warps (<dSo, Sin>)
       mbar_init(&bars.a_full[i], 4);
       mbar_init(&bars.a_empty[i], 1);
       mbar_init(&bars.y_full[i], 1);
@@ -599,16 +599,16 @@ __global__ void __launch_bounds__(GT_THREADS, 1) tc_chunk_grads_state_kernel(con
         tc_fence_after_sync();
         const uint32_t ac = smem_u32(sC), bs = smem_u32(sS + ss * BLK), bd = smem_u32(sdS + ss * BLK);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_YCU + 64u * k, desc_k(ac, ks), desc_mn(bs, ks), id_y, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < 8; ++ks) umma_bf16_h(tbase + TM_YCU + 64u * k, lo_k(ac) + inc_k(ks), lo_mn(bs) + inc_mn(ks), id_y, ks > 0 ? 1u : 0u);
         umma_commit(&bars.y_full[k]);
         if (!lane_wait(&bars.a_full[k], (uint32_t)((h >> 1) & 1), abort_flag, dead)) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          umma_bf16_ta(tbase + TM_DCX, tbase + TM_ADY + 32u * k + 8u * ks, desc_k(bs, ks), id_acc, (h > 0 || ks > 0) ? 1u : 0u);
+          umma_bf16_ta_h(tbase + TM_DCX, tbase + TM_ADY + 32u * k + 8u * ks, lo_k(bs) + inc_k(ks), id_acc, (h > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          umma_bf16_ta(tbase + TM_DBX, tbase + TM_EX + 32u * k + 8u * ks, desc_k(bd, ks), id_acc, (h > 0 || ks > 0) ? 1u : 0u);
+          umma_bf16_ta_h(tbase + TM_DBX, tbase + TM_EX + 32u * k + 8u * ks, lo_k(bd) + inc_k(ks), id_acc, (h > 0 || ks > 0) ? 1u : 0u);
         umma_commit(&bars.a_empty[k]);
         umma_commit(&bars.s_empty[ss]);
         if (h == Hl - 1) umma_commit(&bars.fin);
@@ -648,6 +648,33 @@ __global__ void __launch_bounds__(GT_THREADS, 1) tc_chunk_grads_state_kernel(con
       }
       warp_arrive(&bars.y_empty[k], false);
       if (lane == 0) mbar_arrive(&bars.x_empty[sx]);
+      // <dSo, Sin> over this thread's share of the two state tiles (bf16 operands, fp32 sum, fixed order)
+      const int ss = h % GT_SSTAGES;
+      float part = 0.f;
+      if (role_wait(&bars.s_full[ss], (uint32_t)((h / GT_SSTAGES) & 1), abort_flag, dead)) {
+#pragma unroll 2
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t off8 = ss * BLK + sw128_offset(t, j);
+          const uint4 p1 = *reinterpret_cast<const uint4*>(sS + off8);
+          const uint4 p2 = *reinterpret_cast<const uint4*>(sdS + off8);
+          const uint32_t* q1 = reinterpret_cast<const uint32_t*>(&p1);
+          const uint32_t* q2 = reinterpret_cast<const uint32_t*>(&p2);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float a0, a1, b0, b1;
+            unpack_bf16(q1[e], a0, a1);
+            unpack_bf16(q2[e], b0, b1);
+            part = fmaf(a0, b0, fmaf(a1, b1, part));
+          }
+        }
+      }
+      part = warp_sum(part);
+      if (lane == 0) {
+        red[k * 4 + q] = part;
+        mbar_arrive(&bars.s_empty[ss]);
+      }
+      named_bar_sync(2, 128);
+      if (tid == 0) a.dw[((int64_t)b * a.L + t0) * H + h0 + h] = (red[k * 4] + red[k * 4 + 1]) + (red[k * 4 + 2] + red[k * 4 + 3]);
     }
     // ---- accumulated cross terms -> global (fp32 rows of N) ----
     if (role_wait(&bars.fin, 0, abort_flag, dead)) {
@@ -670,7 +697,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) tc_chunk_grads_state_kernel(con
       }
     }
   } else {
-    // ---- scaling group: factors of head h, a_t dy and e_s u -> TMEM, <dSo, Sin> ----
+    // ---- scaling group: factors of head h, a_t dy and e_s u -> TMEM ----
     const int64_t ck = ((int64_t)b * a.L + t0 + min(t, Tv - 1)) * H + h0;
     const bool live = t < Tv;
     float d_n = 0.f, w_n = 0.f;
@@ -729,33 +756,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1) tc_chunk_grads_state_kernel(con
       }
       warp_arrive(&bars.a_full[k], false);
       if (lane == 0) mbar_arrive(&bars.x_empty[sx]);
-      // <dSo, Sin> over this thread's share of the two state tiles (bf16 operands, fp32 sum)
-      float part = 0.f;
-      if (role_wait(&bars.s_full[ss], (uint32_t)((h / GT_SSTAGES) & 1), abort_flag, dead)) {
-        const int gt = tid - 128;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t off8 = ss * BLK + sw128_offset(gt, j);
-          const uint4 p1 = *reinterpret_cast<const uint4*>(sS + off8);
-          const uint4 p2 = *reinterpret_cast<const uint4*>(sdS + off8);
-          const uint32_t* q1 = reinterpret_cast<const uint32_t*>(&p1);
-          const uint32_t* q2 = reinterpret_cast<const uint32_t*>(&p2);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float a0, a1, b0, b1;
-            unpack_bf16(q1[e], a0, a1);
-            unpack_bf16(q2[e], b0, b1);
-            part = fmaf(a0, b0, fmaf(a1, b1, part));
-          }
-        }
-      }
-      part = warp_sum(part);
-      if (lane == 0) {
-        red[k * 4 + q] = part;
-        mbar_arrive(&bars.s_empty[ss]);
-      }
-      named_bar_sync(1, 128);
-      if (tid == 128) a.dw[((int64_t)b * a.L + t0) * H + h0 + h] = (red[k * 4] + red[k * 4 + 1]) + (red[k * 4 + 2] + red[k * 4 + 3]);
     }
   }
   tc_fence_before_sync();
@@ -904,7 +904,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
         tc_fence_after_sync();
         const uint32_t ac = smem_u32(sMs), bb = smem_u32(sB);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_CB, desc_k(ac, ks), desc_k(bb, ks), id_dm, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < 8; ++ks) umma_bf16_h(tbase + TM_CB, lo_k(ac) + inc_k(ks), lo_k(bb) + inc_k(ks), id_dm, ks > 0 ? 1u : 0u);
         umma_commit(&bars.cb);
       }
       auto group_a = [&](int hh) {       // dM = dy u^T of head hh, once the score pass has read the previous head's
@@ -914,7 +914,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
         tc_fence_after_sync();
         const uint32_t ady = smem_u32(sDY + sx * BLK), bx = smem_u32(sX + sx * BLK);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) umma_bf16(tbase + TM_DM, desc_k(ady, ks), desc_k(bx, ks), id_dm, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < 4; ++ks) umma_bf16_h(tbase + TM_DM, lo_k(ady) + inc_k(ks), lo_k(bx) + inc_k(ks), id_dm, ks > 0 ? 1u : 0u);
         umma_commit(&bars.dm_full);
       };
       if (!dead && Hl > 0) group_a(0);
@@ -929,14 +929,14 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
         if (!lane_wait(&bars.s_full[ss], (uint32_t)((h >> 1) & 1), abort_flag, dead)) break;
         if (h >= 1 && !lane_wait(&bars.dx_empty, (uint32_t)((h - 1) & 1), abort_flag, dead)) break;
         tc_fence_after_sync();
-        const uint32_t ab = smem_u32(sB), bd = smem_u32(sdS + ss * BLK);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DX2, desc_k(ab, ks), desc_mn(bd, ks), id_x2, ks > 0 ? 1u : 0u);
-        umma_commit(&bars.s_empty[ss]);
         const uint32_t am = smem_u32(sMs), bdy = smem_u32(sDY + sx * BLK);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DX1, desc_mn(am, ks), desc_mn(bdy, ks), id_x1, ks > 0 ? 1u : 0u);
-        umma_commit(&bars.ms_empty);
+        for (int ks = 0; ks < 8; ++ks) umma_bf16_h(tbase + TM_DX1, lo_mn(am) + inc_mn(ks), lo_mn(bdy) + inc_mn(ks), id_x1, ks > 0 ? 1u : 0u);
+        umma_commit(&bars.ms_empty);       // the masked-score tile may be rewritten while X2 still runs
+        const uint32_t ab = smem_u32(sB), bd = smem_u32(sdS + ss * BLK);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16_h(tbase + TM_DX2, lo_k(ab) + inc_k(ks), lo_mn(bd) + inc_mn(ks), id_x2, ks > 0 ? 1u : 0u);
+        umma_commit(&bars.s_empty[ss]);
         umma_commit(&bars.dx_full);
       }
       // closing products: dC = dScoreSum B (K-major A) over dM, dB = dScoreSum^T C (MN-major A) over the summed gradient
@@ -945,9 +945,9 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
         const uint32_t am = smem_u32(sMs), bb = smem_u32(sB), bc = smem_u32(sdS);
         const uint32_t id_c = idesc_bf16(128, 128, 0, 1), id_b = idesc_bf16(128, 128, 1, 1);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_DM, desc_k(am, ks), desc_mn(bb, ks), id_c, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < 8; ++ks) umma_bf16_h(tbase + TM_DM, lo_k(am) + inc_k(ks), lo_mn(bb) + inc_mn(ks), id_c, ks > 0 ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16(tbase + TM_ACC, desc_mn(am, ks), desc_mn(bc, ks), id_b, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < 8; ++ks) umma_bf16_h(tbase + TM_ACC, lo_mn(am) + inc_mn(ks), lo_mn(bc) + inc_mn(ks), id_b, ks > 0 ? 1u : 0u);
         umma_commit(&bars.fin_done);
       }
     }
@@ -958,6 +958,10 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
     for (int h = 0; h < Hl; ++h) {
       const int sx = h % GS_XSTAGES, pb = h & 1;
       const float* rw = rows + (h % GS_ROWS) * GS_ROW_LD;
+      if (tid == 0 && h > 0) {
+        bulk_wait_group_read<0>();             // the store of head h - 1 (issued a head ago) has read its tile:
+        mbar_arrive(&bars.x_empty[(h - 1) % GS_XSTAGES]);   // that stage may be reloaded while this head is worked on
+      }
       const bool ok = role_wait(&bars.dx_full, (uint32_t)(h & 1), abort_flag, dead);
       float de = 0.f, cso = 0.f, dyu = 0.f;
       if (ok) {
@@ -968,6 +972,8 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
         const float* dgs = rw + 768;
         uint8_t* utile = sX + sx * BLK;
         const uint8_t* dytile = sDY + sx * BLK;
+        const float2 es2 = make_float2(es, es), wt2 = make_float2(wt, wt);
+        float2 de2 = make_float2(0.f, 0.f), cso2 = de2, dyu2 = de2;
         // eight groups of eight columns; a short loop body that stays in the instruction cache
 #pragma unroll 2
         for (int k8 = 0; k8 < 8; ++k8) {
@@ -987,29 +993,27 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
           uint32_t outp[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            float u0, u1, g0, g1;
-            unpack_bf16(up[e], u0, u1);
-            unpack_bf16(dp[e], g0, g1);
-            const float x10 = __uint_as_float(r1[2 * e]), x11 = __uint_as_float(r1[2 * e + 1]);
-            const float x20 = __uint_as_float(r2[2 * e]), x21 = __uint_as_float(r2[2 * e + 1]);
-            outp[e] = pack_bf16(fmaf(dd[2 * e] + dgv, g0, fmaf(es, x20, wt * x10)),
-                                fmaf(dd[2 * e + 1] + dgv, g1, fmaf(es, x21, wt * x11)));
-            de = fmaf(u0, x20, fmaf(u1, x21, de));
-            cso = fmaf(u0, x10, fmaf(u1, x11, cso));
-            dyu = fmaf(g0, u0, fmaf(g1, u1, dyu));
+            float2 u2, gy;
+            unpack_bf16(up[e], u2.x, u2.y);
+            unpack_bf16(dp[e], gy.x, gy.y);
+            const float2 x1 = f2(r1[2 * e], r1[2 * e + 1]), x2 = f2(r2[2 * e], r2[2 * e + 1]);
+            const float2 y2 = fma2(make_float2(dd[2 * e] + dgv, dd[2 * e + 1] + dgv), gy, fma2(es2, x2, mul2(wt2, x1)));
+            outp[e] = pack_bf16(y2.x, y2.y);
+            de2 = fma2(u2, x2, de2);
+            cso2 = fma2(u2, x1, cso2);
+            dyu2 = fma2(gy, u2, dyu2);
           }
           *slot = make_uint4(outp[0], outp[1], outp[2], outp[3]);
         }
+        de = de2.x + de2.y;
+        cso = cso2.x + cso2.y;
+        dyu = dyu2.x + dyu2.y;
       }
       depart[pb * 128 + t] = de;
       colsum[pb * 128 + t] = cso;
       kdiag[pb * 128 + t] = cbd[t] * dyu;
       warp_arrive(&bars.dx_empty, true);       // the DX accumulators are free; the du rows are fenced for the async proxy
       if (lane == 0) mbar_arrive(&bars.part_full[pb]);
-      if (tid == 0) {
-        bulk_wait_group_read<0>();             // the store of head h - 1 has read its tile: that stage may be reloaded
-        if (h > 0) mbar_arrive(&bars.x_empty[(h - 1) % GS_XSTAGES]);
-      }
       named_bar_sync(3, 128);
       if (tid == 0 && ok) {
         tma_store_3d(&tmDU, sX + sx * BLK, (h0 + h) * TC_G, t0, b);   // rows past the end of the sequence are clipped
@@ -1042,41 +1046,45 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
     }
   } else if (warp < 12) {
     // ---- score group ----
-    const int sg = (warp - 4) >> 2;        // column slabs 2 sg, 2 sg + 1 of row quarter q
+    // Row quarter q has 2 q + 2 live 16-column pieces (columns 0 .. 32 q + 31; the last two lie on the diagonal and cost
+    // about twice as much).  Its two warps split them so that both carry about the same work: the first (sg = 0) takes
+    // pieces [0, nA), the second the rest; the second warps of quarters 0 and 1, which get only one diagonal piece, also sum
+    // dD[p] = sum_t dy[t,p] u[t,p] over 64 tokens each (a lane owns two columns and walks down the rows of the two tiles, so
+    // that sum needs no exchange between threads).
+    const int sg = (warp - 4) >> 2;
+    const int nA = q == 0 ? 1 : (q == 1 ? 3 : q + 2);
+    const int p_lo = sg == 0 ? 0 : nA, p_hi = sg == 0 ? nA : 2 * q + 2;      // live pieces of this warp
+    const bool dd_warp = sg == 1 && q < 2 && a.dDg_part != nullptr;
     const bool cb_ok = role_wait(&bars.cb, 0, abort_flag, dead);   // CB is in TMEM; the C tile's buffer is free for the scores
     tc_fence_after_sync();
-    // The summed score gradient of this warp's slabs starts at zero.  What lies on and above the diagonal of the operand
-    // never changes: zero those slabs of this row once; the warp that owns the diagonal slab also publishes CB[s,s].
+    // The summed score gradient starts at zero (every warp clears the pieces it owns; the second warp of a quarter also
+    // owns what lies above the diagonal, which stays zero, in the accumulator and in the masked-score operand).  The second
+    // warp publishes CB[s,s] of its rows as well.
     {
       uint32_t z[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) z[i] = 0u;
+      const int z_hi = sg == 0 ? nA : 8;
 #pragma unroll 1
-      for (int pi = 0; pi < 4; ++pi) tmem_st16(tmem_addr(tbase, q * 32, TM_ACC + sg * 64 + pi * 16), z);
+      for (int pi = p_lo; pi < z_hi; ++pi) {
+        tmem_st16(tmem_addr(tbase, q * 32, TM_ACC + pi * 16), z);
+        if (pi >= 2 * q + 2) {
+          uint8_t* dstb = sMs + (pi >> 2) * BLK;
+          *reinterpret_cast<uint4*>(dstb + sw128_offset(t, (pi & 3) * 2)) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(dstb + sw128_offset(t, (pi & 3) * 2 + 1)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
       tmem_st_wait();
     }
-#pragma unroll 1
-    for (int jj = 0; jj < 2; ++jj) {
-      const int j = 2 * sg + jj;
-      if (j > q) {
-        uint8_t* dstb = sMs + (j >> 1) * BLK;
+    if (sg == 1 && cb_ok) {
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tbase, q * 32, TM_CB + q * 32), r);
+      tmem_ld_wait();
+      float dv = 0.f;
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) *reinterpret_cast<uint4*>(dstb + sw128_offset(t, (j & 1) * 4 + kk)) = make_uint4(0u, 0u, 0u, 0u);
-      } else if (j == q && cb_ok) {
-        uint32_t r[32];
-        tmem_ld32(tmem_addr(tbase, q * 32, TM_CB + j * 32), r);
-        tmem_ld_wait();
-        float dv = 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) dv = i == lane ? __uint_as_float(r[i]) : dv;
-        cbd[t] = dv;
-      }
+      for (int i = 0; i < 32; ++i) dv = i == lane ? __uint_as_float(r[i]) : dv;
+      cbd[t] = dv;
     }
-    // live 16-column pieces of this warp: slab j = 2 sg + (pi >> 1) is live when j <= q.  The two warps without any
-    // (row quarters 0 and 1 of the upper slab pair) sum dD[p] = sum_t dy[t,p] u[t,p] over 64 tokens each instead: a lane
-    // owns two columns and walks down the rows of the two tiles, so the sum needs no exchange between threads.
-    const int npieces = q < 2 * sg ? 0 : (q == 2 * sg ? 2 : 4);
-    const bool dd_warp = npieces == 0 && a.dDg_part != nullptr;
 #pragma unroll 1
     for (int h = 0; h < Hl; ++h) {
       const int pb = h & 1;
@@ -1085,8 +1093,9 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
       bool go = cb_ok;
       go = role_wait(&bars.rows_full[h % GS_ROWS], (uint32_t)((h / GS_ROWS) & 1), abort_flag, dead) && go;
       go = role_wait(&bars.dm_full, (uint32_t)(h & 1), abort_flag, dead) && go;
-      if (h >= 1) go = role_wait(&bars.ms_empty, (uint32_t)((h - 1) & 1), abort_flag, dead) && go;
       if (h >= 2) go = role_wait(&bars.part_empty[pb], (uint32_t)(((h >> 1) - 1) & 1), abort_flag, dead) && go;
+      bool tile_free = h == 0;             // the previous head's X1 product must have read the masked-score tile before
+                                           // this head's first store into it; the first piece is computed meanwhile
       float rowS = 0.f;
       if (dd_warp) {
         const int sx = h % GS_XSTAGES;
@@ -1111,8 +1120,8 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
         tc_fence_after_sync();
         const float cst = cs[t], wdt_t = wdv[t];
 #pragma unroll 1
-        for (int pi = 0; pi < npieces; ++pi) {
-          const int j = 2 * sg + (pi >> 1), col = j * 32 + (pi & 1) * 16;
+        for (int pi = p_lo; pi < p_hi; ++pi) {
+          const int j = pi >> 1, col = pi * 16;
           uint32_t rm[16], rc[16], ra[16];
           tmem_ld16(tmem_addr(tbase, q * 32, TM_DM + col), rm);
           tmem_ld16(tmem_addr(tbase, q * 32, TM_CB + col), rc);
@@ -1121,25 +1130,27 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
           if (j < q) {
             // slab wholly below the diagonal: decay = (row factor) x (column factor), no exponential per element
             const float g = __expf(cst - cs[j * 32 + 31]);
+            const float2 g2 = make_float2(g, g);
+            float2 rs2 = make_float2(0.f, 0.f);
             tmem_ld_wait();
 #pragma unroll
             for (int e4 = 0; e4 < 4; ++e4) {
               const float4 f4 = *reinterpret_cast<const float4*>(fs + col + e4 * 4);
               const float4 w4 = *reinterpret_cast<const float4*>(fw + col + e4 * 4);
-              const float fq[4] = {f4.x, f4.y, f4.z, f4.w}, wq[4] = {w4.x, w4.y, w4.z, w4.w};
-              float mv[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int i = e4 * 4 + e;
-                const float dm = __uint_as_float(rm[i]), cb = __uint_as_float(rc[i]);
-                const float wgt = g * wq[e];                    // E w_s
-                rowS = fmaf(dm * cb, wgt, rowS);
-                ra[i] = __float_as_uint(fmaf(dm, wgt, __uint_as_float(ra[i])));
-                mv[e] = cb * (g * fq[e]);                       // CB E
+              for (int e = 0; e < 2; ++e) {
+                const int i = e4 * 4 + 2 * e;
+                const float2 dm = f2(rm[i], rm[i + 1]), cb = f2(rc[i], rc[i + 1]);
+                const float2 wgt = mul2(g2, e ? make_float2(w4.z, w4.w) : make_float2(w4.x, w4.y));   // E w_s
+                rs2 = fma2(mul2(dm, cb), wgt, rs2);
+                const float2 an = fma2(dm, wgt, f2(ra[i], ra[i + 1]));
+                ra[i] = __float_as_uint(an.x);
+                ra[i + 1] = __float_as_uint(an.y);
+                const float2 mv = mul2(cb, mul2(g2, e ? make_float2(f4.z, f4.w) : make_float2(f4.x, f4.y)));   // CB E
+                pk[e4 * 2 + e] = pack_bf16(mv.x, mv.y);
               }
-              pk[e4 * 2] = pack_bf16(mv[0], mv[1]);
-              pk[e4 * 2 + 1] = pack_bf16(mv[2], mv[3]);
             }
+            rowS += rs2.x + rs2.y;
           } else {
             // diagonal slab, branch-free (selects only)
             tmem_ld_wait();
@@ -1164,8 +1175,12 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
             }
           }
           tmem_st16(tmem_addr(tbase, q * 32, TM_ACC + col), ra);
-          uint8_t* dstb = sMs + (j >> 1) * BLK;
-          const int ch = (j & 1) * 4 + (pi & 1) * 2;
+          if (!tile_free) {
+            tile_free = true;
+            if (!role_wait(&bars.ms_empty, (uint32_t)((h - 1) & 1), abort_flag, dead)) break;
+          }
+          uint8_t* dstb = sMs + (pi >> 2) * BLK;
+          const int ch = (pi & 3) * 2;
           *reinterpret_cast<uint4*>(dstb + sw128_offset(t, ch)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
           *reinterpret_cast<uint4*>(dstb + sw128_offset(t, ch + 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
         }
@@ -1188,13 +1203,12 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
     if (fin) {
       tc_fence_after_sync();
 #pragma unroll 1
-      for (int pi = 0; pi < 4; ++pi) {
-        const int j = 2 * sg + (pi >> 1), col = j * 32 + (pi & 1) * 16;
+      for (int pi = p_lo; pi < (sg == 0 ? nA : 8); ++pi) {
         uint32_t ra[16];
-        tmem_ld16(tmem_addr(tbase, q * 32, TM_ACC + col), ra);
+        tmem_ld16(tmem_addr(tbase, q * 32, TM_ACC + pi * 16), ra);
         tmem_ld_wait();
-        uint8_t* dstb = sMs + (j >> 1) * BLK;
-        const int ch = (j & 1) * 4 + (pi & 1) * 2;
+        uint8_t* dstb = sMs + (pi >> 2) * BLK;
+        const int ch = (pi & 3) * 2;
 #pragma unroll
         for (int c2 = 0; c2 < 2; ++c2)
           *reinterpret_cast<uint4*>(dstb + sw128_offset(t, ch + c2)) =

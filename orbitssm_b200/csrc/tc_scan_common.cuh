@@ -134,6 +134,25 @@ __device__ __forceinline__ bool lane_wait(uint64_t* bar, uint32_t parity, volati
   return !dead;
 }
 
+// Packed fp32 pairs (one instruction for two lanes of arithmetic: the per-element passes of these kernels are bound by
+// instruction issue, not by the FP32 pipes).
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 f2(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -152,6 +171,14 @@ __device__ __forceinline__ uint64_t desc_k(uint32_t base, int ks) {
 }
 // MN-major descriptor of k-step `ks` (16 rows); 64-wide MN blocks are BLK bytes apart
 __device__ __forceinline__ uint64_t desc_mn(uint32_t base, int ks) { return smem_desc_sw128(base + (uint32_t)ks * 2048u, BLK, 1024u); }
+
+// Low descriptor halves of a tile's first k-step, and the (compile-time) increment to k-step `ks`:
+//   K-major [128 x 128] operand in two 64-column blocks: 32 bytes per k-step inside a block, BLK between the blocks;
+//   MN-major operand: 2048 bytes (16 rows of 128 bytes) per k-step.
+__device__ __forceinline__ uint32_t lo_k(uint32_t base) { return desc_lo(base, 16u); }
+__device__ __forceinline__ uint32_t lo_mn(uint32_t base) { return desc_lo(base, BLK); }
+__device__ __forceinline__ constexpr uint32_t inc_k(int ks) { return (uint32_t)(((ks >> 2) * (int)BLK + (ks & 3) * 32) >> 4); }
+__device__ __forceinline__ constexpr uint32_t inc_mn(int ks) { return (uint32_t)((ks * 2048) >> 4); }
 
 // Column sums over the 32 rows held by a warp: in: v[i] = value of (row = lane, column i); out: v[0] = sum over the
 // warp's rows of column `lane` (butterfly reduce-scatter, 31 shuffles, fixed order).

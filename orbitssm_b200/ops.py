@@ -419,15 +419,33 @@ def run_phase(a, name, phase, state_in, state_out, dtype_code, precision):
                                                     _stream()), "orbit_ssd_scan_phase(" + name + ")")
 
 
+def cp_pack(dA, record, n_state):
+    """Sum the segment's log-decays dA [B, L, H, R] over L into the record behind its state part (`orbit_cp_state_pack`)."""
+    B, L, H, R = dA.shape
+    with _timed("cp_state_pack", 1):
+        _lib.check(_lib.load().orbit_cp_state_pack(_ptr(dA), _ptr(record), B, L, H * R, int(n_state), _stream()), "orbit_cp_state_pack")
+
+
+def cp_combine(records, world, rank, n_state, per_head, BHR, backward):
+    """Entering state (forward) or leaving-state gradient (backward) of rank `rank` from the gathered records
+    [world, stride] (`orbit_cp_state_combine`).  Returns a flat fp32 tensor of n_state elements."""
+    out = torch.empty((n_state,), device=records.device, dtype=torch.float32)
+    with _timed("cp_state_combine", 1):
+        _lib.check(_lib.load().orbit_cp_state_combine(_ptr(records), records.stride(0), int(world), int(rank), int(n_state),
+                                                      int(per_head), int(BHR), int(bool(backward)), _ptr(out), _stream()),
+                   "orbit_cp_state_combine")
+    return out
+
+
 class ContextParallel:
     """The ranks of one context-parallel group: consecutive ranks hold consecutive segments of the sequence.
 
     The recurrence is linear in the state, so a rank needs from its predecessors only what their segments contribute:
-    F_j (final state of segment j started from zero) and A_j (its total log-decay per kernel head).  One all-gather of
-    (F, A) per direction replaces a serial hand-off:  S_r = sum_{j<r} exp(A_{j+1} + .. + A_{r-1}) F_j  (and the mirror
-    image for the state gradient in backward).  The same terms as the reference's in-GPU chunk-parallel pass
-    (src/orbit_ssm/kernels/ssd_mimo/chunkpar.py:19-25) and its state continuation contract
-    (src/orbit_ssm/ssm/ssd_mimo_torch.py:677-679).
+    F_j (final state of segment j started from zero) and A_j (its total log-decay per kernel head).  ONE all-gather of
+    the packed records (F, A) per direction replaces a serial hand-off, and one small kernel forms
+    S_r = sum_{j<r} exp(A_{j+1} + .. + A_{r-1}) F_j  (and the mirror image for the state gradient in backward).  The same
+    terms as the reference's in-GPU chunk-parallel pass (src/orbit_ssm/kernels/ssd_mimo/chunkpar.py:19-25) and its state
+    continuation contract (src/orbit_ssm/ssm/ssd_mimo_torch.py:677-679).
     """
 
     def __init__(self, group=None):
@@ -435,30 +453,12 @@ class ContextParallel:
         self.dist, self.group = dist, group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
 
-    def all_gather(self, t):
-        outs = [torch.empty_like(t) for _ in range(self.world)]
-        self.dist.all_gather(outs, t.contiguous(), group=self.group)
-        return outs
-
-    def entering(self, F, logA):
-        """State entering this rank's segment (None on rank 0: the sequence starts from zero):
-        S_0 = 0,  S_{j+1} = exp(A_j) S_j + F_j."""
-        Fs, As = self.all_gather(F), self.all_gather(logA)
-        S = None
-        for j in range(self.rank):
-            S = Fs[j] if S is None else S * As[j].exp()[..., None, None] + Fs[j]
-        return S
-
-    def leaving_grad(self, E, logA, ext):
-        """Gradient of the state LEAVING this rank's segment.  E_j: what segment j's own outputs ask of its entering
-        state; ext_j: gradient a caller put on the state returned by rank j (None = zero).  With d_j the gradient of
-        the state leaving segment j:  d_{W-1} = ext_{W-1},  d_{j-1} = ext_{j-1} + E_j + exp(A_j) d_j."""
-        Es, As = self.all_gather(E), self.all_gather(logA)
-        Xs = self.all_gather(ext if ext is not None else torch.zeros_like(E))
-        d = Xs[self.world - 1]
-        for j in range(self.world - 1, self.rank, -1):
-            d = Xs[j - 1] + Es[j] + d * As[j].exp()[..., None, None]
-        return d
+    def gather_records(self, record):
+        """record [stride] fp32 of this rank -> [world, stride], one collective."""
+        record = record.contiguous()
+        out = torch.empty((self.world * record.numel(),), device=record.device, dtype=record.dtype)
+        self.dist.all_gather_into_tensor(out, record, group=self.group)
+        return out.view(self.world, record.numel())
 
 
 class HaloFn(torch.autograd.Function):
@@ -538,13 +538,15 @@ def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     dt = _dtype_code("ssd_scan_fwd", u)
     run_phase(a, "scan_chunk_state", _lib.PHASE_CHUNK_STATE, None, None, dt, precision)
     if cp is not None:
-        F = torch.empty_like(S_fin)
-        run_phase(a, "scan_state_pass_dry", _lib.PHASE_STATE_PASS_DRY, None, F, dt, precision)
-        if S0 is not None:
-            raise NotImplementedError("ssd_scan: an initial state together with context parallelism is not served")
-        S0 = cp.entering(F, dA.sum(1))
-        if S0 is not None:
-            S0 = S0.contiguous()
+        # this rank's record [F | A]: the dry pass writes F (started from the sequence's initial state on rank 0, from zero
+        # elsewhere: an initial state is a property of the whole sequence, so only rank 0's is read) straight into it
+        n_state, BHR = S_fin.numel(), B * H * R
+        rec = torch.empty((n_state + BHR,), device=dev, dtype=torch.float32)
+        first = S0 if cp.rank == 0 else None
+        run_phase(a, "scan_state_pass_dry", _lib.PHASE_STATE_PASS_DRY, first, rec[:n_state].view_as(S_fin), dt, precision)
+        cp_pack(dA, rec, n_state)
+        recs = cp.gather_records(rec)
+        S0 = first if cp.rank == 0 else cp_combine(recs, cp.world, cp.rank, n_state, N * G, BHR, False).view_as(S_fin)
     run_phase(a, "scan_state_pass", _lib.PHASE_STATE_PASS, S0, S_fin, dt, precision)
     run_phase(a, "scan_chunk_out", _lib.PHASE_CHUNK_OUT, None, None, dt, precision)
     del keep
@@ -667,9 +669,17 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     dt = _dtype_code("ssd_scan_bwd", u)
     run_phase(a, "scan_chunk_dstate", _lib.PHASE_CHUNK_DSTATE, None, None, dt, precision)
     if cp is not None:
-        E = torch.empty((B, H, R, N, G), **f32)
-        run_phase(a, "scan_state_pass_bwd_dry", _lib.PHASE_STATE_PASS_BWD_DRY, None, E, dt, precision)
-        dS_fin = cp.leaving_grad(E, dA.sum(1), dS_fin).contiguous()
+        # this rank's record [E | A | X]; one all-gather, then the gradient of the state leaving this segment
+        n_state, BHR = B * H * R * N * G, B * H * R
+        rec = torch.empty((2 * n_state + BHR,), **f32)
+        run_phase(a, "scan_state_pass_bwd_dry", _lib.PHASE_STATE_PASS_BWD_DRY, None, rec[:n_state].view(B, H, R, N, G), dt, precision)
+        cp_pack(dA, rec, n_state)
+        if dS_fin is not None:
+            rec[n_state + BHR:].copy_(dS_fin.reshape(-1))
+        else:
+            rec[n_state + BHR:].zero_()
+        recs = cp.gather_records(rec)
+        dS_fin = cp_combine(recs, cp.world, cp.rank, n_state, N * G, BHR, True).view(B, H, R, N, G)
     run_phase(a, "scan_state_pass_bwd", _lib.PHASE_STATE_PASS_BWD, dS_fin, dS0, dt, precision)
     run_phase(a, "scan_chunk_grads", _lib.PHASE_CHUNK_GRADS, None, None, dt, precision)
     del keep

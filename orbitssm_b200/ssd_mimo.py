@@ -178,7 +178,9 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         """Split the SEQUENCE across the ranks of `group` (a torch.distributed process group; "world" = the default
         group; None switches it off): rank r's `forward` then takes the r-th contiguous segment of the sequence and
         returns that segment's outputs.  The chunk state and the conv windows cross ranks inside the layer, forward
-        and backward.  No counterpart in the reference, which is single-process; the exchanged quantities are those
+        and backward.  A `state` passed to `forward` is the state BEFORE the whole sequence: rank 0 reads it, the other
+        ranks' is ignored; the State a rank returns is the one at the end of its own segment (the last rank's is the
+        sequence's).  No counterpart in the reference, which is single-process; the exchanged quantities are those
         of its State continuation contract (reference: src/orbit_ssm/ssm/ssd_mimo.py:4377-4400, 4565)."""
         if group is None:
             self._cp = None
@@ -335,8 +337,6 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         H, G, R, O, N, P = s.H, s.G, s.R, s.O, s.N, s.P
         cp = self._cp if (self._cp is not None and self._cp.world > 1) else None
         if cp is not None:
-            if state is not None:
-                raise NotImplementedError("SSDMimoSSM: a carried `state` together with context parallelism is not served")
             if s.use_trap:
                 raise NotImplementedError("SSDMimoSSM: context parallelism serves write_rule='euler' (the two-endpoint "
                                           "write needs the neighbour's lag term)")
@@ -364,7 +364,7 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
             if self.conv1d is not None:
                 win = state["conv_state"] if state is not None else None
                 if cp is not None:
-                    win = ops.HaloFn.apply(drive_raw[:, L - (s.d_conv - 1):], cp, s.d_conv)
+                    win = _cp_window(win, ops.HaloFn.apply(drive_raw[:, L - (s.d_conv - 1):], cp, s.d_conv), cp)
                 u = (ops.CausalConvFn.apply(drive_raw, self.conv1d.weight, self.conv1d.bias, win, (arena, 0)) if L > 0
                      else drive_raw.contiguous())
                 if want_state:
@@ -376,7 +376,7 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
                 bc_raw = parts["BC"]                                           # B | C adjacent at the slab head
                 win = state["bc_conv_state"] if state is not None else None
                 if cp is not None:
-                    win = ops.HaloFn.apply(bc_raw[:, L - (s.d_conv - 1):], cp, s.d_conv)
+                    win = _cp_window(win, ops.HaloFn.apply(bc_raw[:, L - (s.d_conv - 1):], cp, s.d_conv), cp)
                 bc = (ops.CausalConvFn.apply(bc_raw, self.bc_conv1d.conv.weight, self.bc_conv1d.conv.bias, win,
                                              (arena, slot_of["BC"])) if L > 0
                       else bc_raw.contiguous())
@@ -482,6 +482,15 @@ class _OutNorm(nn.Module):
         super().__init__()
         self.eps = eps
         self.weight = nn.Parameter(torch.ones(d))
+
+
+def _cp_window(carried, halo, cp):
+    """Conv window of a context-parallel segment: the previous rank's last rows (`halo`); on rank 0, where the halo is zero,
+    the window carried in by the caller's State (an initial state belongs to the whole sequence: only rank 0's is read).
+    The sum keeps rank 0's halo in the autograd graph, so that its backward still receives what rank 1 sends."""
+    if carried is None or cp.rank != 0:
+        return halo
+    return carried.to(halo.dtype) + halo
 
 
 def _next_window(prev, raw, W):

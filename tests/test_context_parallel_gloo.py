@@ -13,7 +13,7 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, cont=False):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
@@ -25,7 +25,7 @@ def _worker(rank, world, port, out):
         from orbitssm_b200.ssd_mimo import SSDMimoSSM
         from oracle import abi_reference as R
         for name in ("conv1d_fwd", "conv1d_bwd", "gate_norm_fwd", "gate_norm_bwd", "pick_chunk", "run_phase", "token_map_fwd",
-                     "token_map_bwd", "run_clock"):
+                     "token_map_bwd", "run_clock", "cp_pack", "cp_combine"):
             setattr(ops, name, getattr(R, name))
         ops.on_device = lambda t: True
         ops._require_cuda = lambda who, *t: None
@@ -37,14 +37,23 @@ def _worker(rank, world, port, out):
         layer.set_context_parallel("world")
         L = rec["x"].shape[1]
         cuts = [0, 41, L] if world == 2 else [0, 30, 61, L]
+        state, want, xs, dys = None, rec["f64"], rec["x"], rec["dy"]
+        if cont:
+            # the continuation fixture: the sequence after the cut, started from the reference's carried State.  The State
+            # belongs to the whole sequence: rank 0 reads it, the other ranks' copy is ignored.
+            c = rec["f64_cont"]
+            s0 = c["split"]
+            xs, dys, want = rec["x"][:, s0:], rec["dy"][:, s0:], c
+            state = {k: v.clone().float().requires_grad_(rank == 0) for k, v in c["state_in"].items()}
+            L = xs.shape[1]
+            cuts = [0, 23, L] if world == 2 else [0, 17, 38, L]
         a, b = cuts[rank], cuts[rank + 1]
-        x = rec["x"][:, a:b].clone().requires_grad_(True)
-        y, st = layer(x, return_state=True)
-        loss = (y * rec["dy"][:, a:b]).sum()
+        x = xs[:, a:b].clone().requires_grad_(True)
+        y, st = layer(x, state=state, return_state=True)
+        loss = (y * dys[:, a:b]).sum()
         if rank == world - 1:
             loss = loss + (st["hidden_state"] * rec["gh"]).sum()
         loss.backward()
-        want = rec["f64"]
 
         def rel(p, q):
             p, q = p.detach().double(), q.double()
@@ -53,6 +62,9 @@ def _worker(rank, world, port, out):
         errs = {"y": rel(y, want["y"][:, a:b]), "dx": rel(x.grad, want["grads"]["x"][:, a:b])}
         if rank == world - 1:
             errs["hidden"] = rel(st["hidden_state"], want["state"]["hidden_state"])
+        if cont and rank == 0:
+            for k, v in state.items():
+                errs["dstate." + k] = rel(v.grad, want["grads"]["state." + k])
         for n, p in layer.named_parameters():
             g = p.grad.clone()
             dist.all_reduce(g)                                   # parameter gradients add over the segments
@@ -62,12 +74,12 @@ def _worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_two_segments_equal_the_whole_sequence(world):
-    port = 29500 + (os.getpid() % 2000) + world
+@pytest.mark.parametrize("world,cont", [(2, False), (3, False), (2, True), (3, True)])
+def test_two_segments_equal_the_whole_sequence(world, cont):
+    port = 29500 + (os.getpid() % 2000) + world + 10 * int(cont)
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(world, port, out), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, out, cont), nprocs=world, join=True)
     for rank in range(world):
         bad = {k: e for k, e in out[rank].items() if not e < 2e-4}
         assert not bad, (rank, bad)
