@@ -412,15 +412,18 @@ def measure(env, wl, name, steps, warmup, e2e_regions=3, cp_world=None):
             ev_done[b].record(main)
             down.wait_event(ev_done[b])
             with torch.cuda.stream(down):
-                y_host.copy_(y, non_blocking=True)
+                # detached: copying a graph-carrying tensor into y_host would chain every step's graph behind y_host
+                y_host.copy_(y.detach(), non_blocking=True)
                 dx_host.copy_(xd.grad, non_blocking=True)
             y.record_stream(down)
             xd.grad.record_stream(down)
+            del y, xd            # drop this step's autograd graph before the next forward allocates its own
         main.wait_stream(down)
         e1.record(main)
         torch.cuda.synchronize()
         return e0.elapsed_time(e1)
 
+    torch.cuda.reset_peak_memory_stats(dev)
     for _ in range(warmup):
         step()
     env.sync()
@@ -441,6 +444,7 @@ def measure(env, wl, name, steps, warmup, e2e_regions=3, cp_world=None):
     ops.set_timing(None)
     ops.check_device_status()                 # a bounded device-side wait that gave up voids the numbers: raise, exit non-zero
     total_ms = sum(a.elapsed_time(b) for a, b in ev)
+    mem_gb = {"timed": round(torch.cuda.max_memory_allocated(dev) / 2**30, 2)}
     per_kernel = {}
     for kname, a, b in timing:
         per_kernel.setdefault(kname, []).append(a.elapsed_time(b))
@@ -453,6 +457,7 @@ def measure(env, wl, name, steps, warmup, e2e_regions=3, cp_world=None):
             e2e.append(run_e2e(steps))
             env.sync()
         ops.check_device_status()
+        mem_gb["e2e"] = round(torch.cuda.max_memory_allocated(dev) / 2**30, 2)
     red = env.max_over_ranks([total_ms] + e2e)
     total_ms, e2e = red[0], red[1:]
     tokens = B * L * steps * (cp_world if wl.get("cp") else shards)
@@ -461,7 +466,7 @@ def measure(env, wl, name, steps, warmup, e2e_regions=3, cp_world=None):
         value=tokens / (total_ms * 1e-3), ms_per_step=total_ms / steps, tokens_per_step=tokens // steps, B=B, L=L,
         blocks=nblocks, use_cp=use_cp, launches=launches, kern_ms=kern_ms, route=mixer0.last_route(), spec=mixer0.spec,
         kernel_ms_sum=sum(kern_ms[k] * len(per_kernel[k]) for k in kern_ms) / steps,
-        h2d=2 * x_host.numel() * 2, d2h=2 * y_host.numel() * 2)
+        h2d=2 * x_host.numel() * 2, d2h=2 * y_host.numel() * 2, mem_gb=mem_gb)
     if e2e:
         med = statistics.median(e2e)
         out["e2e"] = {"value": tokens / (med * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": out["h2d"],
@@ -492,11 +497,15 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="cfg5a", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's (global) batch rows")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-workloads", action="store_true")
     args = ap.parse_args()
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.batch > 0:
+        wl["B"] = args.batch
+        wl["desc"] += f" (batch rows overridden to {args.batch})"
     if args.impl == "reference":
         return run_reference(args, wl, args.workload)
 
@@ -551,7 +560,7 @@ def main():
         "e2e": m.get("e2e"), "gpu_launches": m["launches"], "clocks": clocks,
         "roofline": roofline_block(wl, m["spec"], m["route"], B, L, m["kern_ms"], pk),
         "kernel_ms": {k: round(v, 4) for k, v in sorted(m["kern_ms"].items())},
-        "kernel_ms_sum": round(m["kernel_ms_sum"], 4),
+        "kernel_ms_sum": round(m["kernel_ms_sum"], 4), "peak_device_memory_gib": m["mem_gb"],
     }
     if world == 1 and not args.no_cpu_baseline:
         sB, sL = 1, 256 if wl["kind"] == "m2" else 128
