@@ -4,9 +4,11 @@
 //
 // Replaces the reference's Triton conv (src/orbit_ssm/kernels/conv_triton.py:888-1010, host entry
 // src/orbit_ssm/layers/conv.py:219-328).  Layout here is token-major [B, L, C] with an arbitrary row stride, so
-// the kernel reads a column slice of the fused input-projection output in place; one thread owns one 16-byte
-// channel vector and slides over a run of tokens, so every warp access is a contiguous 512-byte row segment.
-// HBM-bound: forward 2*B*L*C*es bytes, backward 3*B*L*C*es (x, dy in; dx out).
+// the kernel reads a column slice of the fused input-projection output in place; one thread owns one channel
+// vector and slides over a run of tokens, so every warp access is a contiguous row segment.
+// HBM-bound: forward 2*B*L*C*es bytes, backward 3*B*L*C*es (x, dy in; dx out).  Channel counts that fill whole warps
+// with 4-channel vectors take the streaming kernels (cp.async rings, packed fp32 pairs); the rest and calls that ask
+// for the carried window's gradient take the plain per-thread kernels above them.
 #include "common.cuh"
 #include "../../include/orbit_b200.h"
 #include <type_traits>
@@ -226,205 +228,358 @@ __global__ void __launch_bounds__(128) conv_bwd_kernel(const T* __restrict__ x, 
   }
 }
 
-// ---- shared-memory tiled variants (the fast path) ---------------------------------------------------------------------
-// A CTA stages a [TT + halo tokens] x [32 channel vectors] tile with every 16-byte load in flight at once, then warp w
-// slides over tokens 8w..8w+7 of the tile with lane = channel vector.  Rows before the sequence start come from the
-// carried window (or zeros).  Used when C is a multiple of 32 vectors and no window gradient is asked for.
-constexpr int CT_TT = 64;        // tokens per tile
-constexpr int CT_WARPS = 8;      // 8 tokens per warp
+// ---- streaming variants (the fast path) -------------------------------------------------------------------------------
+// A thread owns one channel vector (8 or 16 bytes of consecutive channels) and walks a run of consecutive tokens.  Its
+// rows arrive through a private ring of cp.async stages in shared memory (CS_ROWS rows per stage, CS_STAGES stages), so
+// loads of the rows ahead are in flight while the current rows are computed and no thread waits on another: the kernel
+// has no barrier.  A CTA is `cx` channel vectors wide (a warp reads one contiguous 256- or 512-byte segment per row) and
+// 128 / cx token runs deep.  Arithmetic is on packed fp32 pairs; rows before the sequence start come from the carried
+// window (or zeros) and are written to the ring by the thread itself.
+constexpr int CS_THREADS = 128;
+constexpr int CS_ROWS = 4;
+constexpr int CS_STAGES = 4;
 
-template <typename T, int VEC, int W>
-__device__ __forceinline__ void tile_row(RawVec<T, VEC>& out, const T* x, int64_t xbs, int64_t xrs, const float* window,
-                                         int b, int t, int L, int c0, int C) {
-  if (t >= 0 && t < L) {
-    out.load(x + b * xbs + (int64_t)t * xrs + c0);
-  } else {
-    T tmp[VEC];
+template <int BYTES> __device__ __forceinline__ void cs_copy(void* smem_dst, const void* gsrc);
+template <> __device__ __forceinline__ void cs_copy<16>(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+template <> __device__ __forceinline__ void cs_copy<8>(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cs_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cs_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// channel vector <-> packed fp32 pairs
+template <typename T, int VEC> struct Pairs {
+  using Raw = typename RawStore<VEC * (int)sizeof(T)>::type;
+  float2 p[VEC / 2];
+  __device__ __forceinline__ void from_raw(const Raw& r) {
+    if constexpr (std::is_same<T, float>::value) {
+      const float* f = reinterpret_cast<const float*>(&r);
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-      float v = 0.f;
-      if (t < 0 && window != nullptr && t >= -(W - 1)) v = window[((int64_t)b * C + c0 + i) * W + (W + t)];
-      stf(&tmp[i], v);
+      for (int i = 0; i < VEC / 2; ++i) p[i] = make_float2(f[2 * i], f[2 * i + 1]);
+    } else {
+      const uint32_t* u = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+      for (int i = 0; i < VEC / 2; ++i) p[i] = make_float2(__uint_as_float(u[i] << 16), __uint_as_float(u[i] & 0xffff0000u));
     }
-    out.r = *reinterpret_cast<const typename RawVec<T, VEC>::Store*>(tmp);
+  }
+  __device__ __forceinline__ Raw to_raw() const {
+    Raw r;
+    if constexpr (std::is_same<T, float>::value) {
+      float* f = reinterpret_cast<float*>(&r);
+#pragma unroll
+      for (int i = 0; i < VEC / 2; ++i) { f[2 * i] = p[i].x; f[2 * i + 1] = p[i].y; }
+    } else {
+      uint32_t* u = reinterpret_cast<uint32_t*>(&r);
+#pragma unroll
+      for (int i = 0; i < VEC / 2; ++i) u[i] = pack_bf16(p[i].x, p[i].y);
+    }
+    return r;
+  }
+};
+
+// silu(v) and d silu / dv on a pair: bfloat16 activations take the single-MUFU tanh form (as Act<__nv_bfloat16>)
+template <typename T> __device__ __forceinline__ float2 silu2(float2 v) {
+  if constexpr (std::is_same<T, float>::value) {
+    return make_float2(silu_t<float>(v.x), silu_t<float>(v.y));
+  } else {
+    const float2 h = mul2(v, make_float2(0.5f, 0.5f));
+    const float2 th = make_float2(tanh_approx_(h.x), tanh_approx_(h.y));
+    return fma2(h, th, h);
+  }
+}
+template <typename T> __device__ __forceinline__ float2 silu_grad2(float2 v) {
+  if constexpr (std::is_same<T, float>::value) {
+    return make_float2(silu_grad_t<float>(v.x), silu_grad_t<float>(v.y));
+  } else {
+    const float2 half = make_float2(0.5f, 0.5f), one = make_float2(1.f, 1.f);
+    const float2 h = mul2(v, half);
+    const float2 th = make_float2(tanh_approx_(h.x), tanh_approx_(h.y));
+    const float2 s = fma2(half, th, half);
+    const float2 om = fma2(s, make_float2(-1.f, -1.f), one);
+    return mul2(s, fma2(v, om, one));
   }
 }
 
-// taps and bias of VEC consecutive channels (one 16-byte load per channel when W == 4)
 template <int VEC, int W>
-__device__ __forceinline__ void load_taps(float (&w)[VEC][W], float (&bs)[VEC], const float* __restrict__ weight,
-                                          const float* __restrict__ bias, int c0) {
+__device__ __forceinline__ void load_taps2(float2 (&w2)[W][VEC / 2], float2 (&b2)[VEC / 2], const float* __restrict__ weight,
+                                           const float* __restrict__ bias, int c0) {
+#pragma unroll
+  for (int i = 0; i < VEC / 2; ++i) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) w2[j][i] = make_float2(weight[(size_t)(c0 + 2 * i) * W + j], weight[(size_t)(c0 + 2 * i + 1) * W + j]);
+    b2[i] = bias ? make_float2(bias[c0 + 2 * i], bias[c0 + 2 * i + 1]) : make_float2(0.f, 0.f);
+  }
+}
+
+// row of the carried window (token t < 0) as a raw channel vector
+template <typename T, int VEC, int W>
+__device__ __forceinline__ typename Pairs<T, VEC>::Raw window_row(const float* __restrict__ window, int b, int t, int c0, int C) {
+  T tmp[VEC];
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
-    if constexpr (W == 4) {
-      float4 v = *reinterpret_cast<const float4*>(weight + (size_t)(c0 + i) * 4);
-      w[i][0] = v.x; w[i][1] = v.y; w[i][2] = v.z; w[i][3] = v.w;
+    float v = 0.f;
+    if (window != nullptr && t >= -(W - 1)) v = window[((int64_t)b * C + c0 + i) * W + (W + t)];
+    stf(&tmp[i], v);
+  }
+  return *reinterpret_cast<const typename Pairs<T, VEC>::Raw*>(tmp);
+}
+
+template <typename T, int VEC, int W, bool SILU>
+__global__ void __launch_bounds__(CS_THREADS) conv_fwd_stream_kernel(const T* __restrict__ x, int64_t xbs, int64_t xrs,
+                                                                     const float* __restrict__ weight, const float* __restrict__ bias,
+                                                                     const float* __restrict__ window, T* __restrict__ y, int L, int C,
+                                                                     int run, int cx) {
+  using P = Pairs<T, VEC>;
+  using Raw = typename P::Raw;
+  constexpr int BYTES = VEC * (int)sizeof(T);
+  __shared__ Raw ring[CS_STAGES][CS_ROWS][CS_THREADS];
+  const int tid = threadIdx.x;
+  const int c0 = (blockIdx.y * cx + (tid & (cx - 1))) * VEC;
+  const int b = blockIdx.z;
+  const int t0 = (blockIdx.x * (CS_THREADS / cx) + tid / cx) * run;
+  if (t0 >= L) return;
+  const int ntok = min(run, L - t0);
+  const int nrows = ntok + W - 1;                       // row i <-> token t0 - (W-1) + i
+  const int nst = (nrows + CS_ROWS - 1) / CS_ROWS;
+  const T* xb = x + b * xbs + c0;
+  auto issue = [&](int s) {
+    if (s < nst) {
+#pragma unroll
+      for (int r = 0; r < CS_ROWS; ++r) {
+        const int i = s * CS_ROWS + r, t = t0 - (W - 1) + i;
+        Raw* dst = &ring[s & (CS_STAGES - 1)][r][tid];
+        if (i < nrows) {
+          if (t >= 0) cs_copy<BYTES>(dst, xb + (int64_t)t * xrs);
+          else *dst = window_row<T, VEC, W>(window, b, t, c0, C);
+        }
+      }
+    }
+    cs_commit();
+  };
+  float2 w2[W][VEC / 2], b2[VEC / 2];
+#pragma unroll
+  for (int s = 0; s < CS_STAGES - 1; ++s) issue(s);
+  load_taps2<VEC, W>(w2, b2, weight, bias, c0);
+  P xr[W];                                              // xr[j] = input row of token t - (W-1) + j
+#pragma unroll
+  for (int j = 0; j < W; ++j)
+#pragma unroll
+    for (int i = 0; i < VEC / 2; ++i) xr[j].p[i] = make_float2(0.f, 0.f);
+  T* yb = y + ((int64_t)b * L + t0) * C + c0;
+  // one row of the walk; FULL: the row is known to be inside the run and past the halo (no tests, so that the rows of a
+  // stage form one straight-line block the compiler can interleave)
+  auto row = [&](int s, int r, auto full) {
+    constexpr bool FULL = decltype(full)::value;
+    const int i = s * CS_ROWS + r;
+    if (FULL || i < nrows) {
+      const Raw raw = ring[s & (CS_STAGES - 1)][r][tid];
+#pragma unroll
+      for (int j = 0; j < W - 1; ++j) xr[j] = xr[j + 1];
+      xr[W - 1].from_raw(raw);
+      if (FULL || i >= W - 1) {
+        P o;
+#pragma unroll
+        for (int k = 0; k < VEC / 2; ++k) {
+          float2 acc = b2[k];
+#pragma unroll
+          for (int j = 0; j < W; ++j) acc = fma2(w2[j][k], xr[j].p[k], acc);
+          o.p[k] = SILU ? silu2<T>(acc) : acc;
+        }
+        *reinterpret_cast<Raw*>(yb + (int64_t)(i - (W - 1)) * C) = o.to_raw();
+      }
+    }
+  };
+  for (int s = 0; s < nst; ++s) {
+    issue(s + CS_STAGES - 1);
+    cs_wait<CS_STAGES - 1>();
+    if (s >= 1 && s * CS_ROWS + CS_ROWS <= nrows) {
+#pragma unroll
+      for (int r = 0; r < CS_ROWS; ++r) row(s, r, std::true_type{});
     } else {
 #pragma unroll
-      for (int j = 0; j < W; ++j) w[i][j] = weight[(c0 + i) * W + j];
-    }
-    bs[i] = bias ? bias[c0 + i] : 0.f;
-  }
-}
-
-constexpr int CT_NT = 4;         // consecutive token tiles per CTA (taps stay in registers across them)
-
-template <typename T, int VEC, int W, bool SILU>
-__global__ void __launch_bounds__(256, (VEC * sizeof(T) >= 16) ? 2 : 4) conv_fwd_tiled_kernel(const T* __restrict__ x, int64_t xbs, int64_t xrs,
-                                                             const float* __restrict__ weight, const float* __restrict__ bias,
-                                                             const float* __restrict__ window, T* __restrict__ y, int L, int C) {
-  __shared__ RawVec<T, VEC> tile[CT_TT + W - 1][32];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int c0 = (blockIdx.y * 32 + lane) * VEC;
-  const int b = blockIdx.z;
-  float w[VEC][W], bs[VEC];
-  load_taps<VEC, W>(w, bs, weight, bias, c0);
-  for (int it = 0; it < CT_NT; ++it) {
-    const int t0 = (blockIdx.x * CT_NT + it) * CT_TT;
-    if (t0 >= L) break;
-    __syncthreads();
-    for (int r = warp; r < CT_TT + W - 1; r += CT_WARPS) tile_row<T, VEC, W>(tile[r][lane], x, xbs, xrs, window, b, t0 - (W - 1) + r, L, c0, C);
-    __syncthreads();
-    const int tw = warp * (CT_TT / CT_WARPS);
-    ChanVec<T, VEC> ring[W];
-#pragma unroll
-    for (int j = 0; j < W - 1; ++j) ring[j + 1].from_raw(tile[tw + j][lane]);
-#pragma unroll
-    for (int k = 0; k < CT_TT / CT_WARPS; ++k) {
-      const int t = t0 + tw + k;
-#pragma unroll
-      for (int j = 0; j < W - 1; ++j) ring[j] = ring[j + 1];
-      ring[W - 1].from_raw(tile[tw + k + W - 1][lane]);
-      if (t < L) {
-        ChanVec<T, VEC> o;
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-          float acc = bs[i];
-#pragma unroll
-          for (int j = 0; j < W; ++j) acc = fmaf(w[i][j], ring[j].v[i], acc);
-          o.v[i] = SILU ? silu_t<T>(acc) : acc;
-        }
-        o.store(y + ((int64_t)b * L + t) * C + c0);
-      }
+      for (int r = 0; r < CS_ROWS; ++r) row(s, r, std::false_type{});
     }
   }
 }
 
-// Backward, tiled.  Warp w owns dx (and the dw/db contributions) of tokens 8w..8w+7; it forms dz for 8 + (W-1) tokens.
-// dw/db: per-thread sums -> shared [warp][lane] -> fixed-order sum over the 8 warps -> part[(b, tile)][C][W+1].
-constexpr int CTB_TT = 32;       // backward: tokens per tile
-constexpr int CTB_WARPS = 4;
-
+// Backward, streaming.  A thread owns dx (and the dw / db contributions) of the tokens of its run; it forms dz for W - 1
+// more tokens past the run so that every dx it owns is complete (pre-activations recomputed from x).  Row i of its walk
+// is token t0 - (W-1) + i: x rows from i = 0, dy rows from i = W - 1, dx rows leave from i = 2 (W - 1).  dw / db: per-thread
+// sums over the owned tokens -> part[(b, run)][C][W + 1], reduced in a fixed order by conv_reduce_kernel.
 template <typename T, int VEC, int W, bool SILU>
-__global__ void __launch_bounds__(CTB_WARPS * 32, (VEC * sizeof(T) >= 16) ? 2 : 4) conv_bwd_tiled_kernel(const T* __restrict__ x, int64_t xbs, int64_t xrs,
-                                                             const float* __restrict__ weight, const float* __restrict__ bias,
-                                                             const float* __restrict__ window, const T* __restrict__ dy,
-                                                             T* __restrict__ dx, int64_t dxbs, int64_t dxrs,
-                                                             float* __restrict__ part, int L, int C, int ntiles) {
-  constexpr int TW = CTB_TT / CTB_WARPS;
-  constexpr int XR = CTB_TT + 2 * (W - 1), GR = CTB_TT + W - 1, RED_E = VEC * (W + 1) + 1;
-  constexpr size_t TILE_BYTES = sizeof(RawVec<T, VEC>) * 32 * (XR + GR), RED_BYTES = sizeof(float) * CTB_WARPS * 32 * RED_E;
-  __shared__ __align__(16) unsigned char sraw[TILE_BYTES > RED_BYTES ? TILE_BYTES : RED_BYTES];
-  RawVec<T, VEC>(*xt)[32] = reinterpret_cast<RawVec<T, VEC>(*)[32]>(sraw);                                 // x rows t0-(W-1) ..
-  RawVec<T, VEC>(*gt)[32] = reinterpret_cast<RawVec<T, VEC>(*)[32]>(sraw + sizeof(RawVec<T, VEC>) * 32 * XR);  // dy rows t0 ..
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int c0 = (blockIdx.y * 32 + lane) * VEC;
+__global__ void __launch_bounds__(CS_THREADS) conv_bwd_stream_kernel(const T* __restrict__ x, int64_t xbs, int64_t xrs,
+                                                                     const float* __restrict__ weight, const float* __restrict__ bias,
+                                                                     const float* __restrict__ window, const T* __restrict__ dy,
+                                                                     T* __restrict__ dx, int64_t dxbs, int64_t dxrs,
+                                                                     float* __restrict__ part, int L, int C, int run, int cx, int nruns) {
+  using P = Pairs<T, VEC>;
+  using Raw = typename P::Raw;
+  constexpr int BYTES = VEC * (int)sizeof(T);
+  constexpr int NSTG = BYTES >= 16 ? 3 : 4;          // two rings: 48 KB of static shared memory at most
+  __shared__ Raw ringx[NSTG][CS_ROWS][CS_THREADS];
+  __shared__ Raw ringg[NSTG][CS_ROWS][CS_THREADS];
+  const int tid = threadIdx.x;
+  const int c0 = (blockIdx.y * cx + (tid & (cx - 1))) * VEC;
   const int b = blockIdx.z;
-  float w[VEC][W], bs[VEC], dwacc[VEC][W], dbacc[VEC];
-  load_taps<VEC, W>(w, bs, weight, bias, c0);
+  const int ridx = blockIdx.x * (CS_THREADS / cx) + tid / cx;
+  const int t0 = ridx * run;
+  if (t0 >= L) return;
+  const int ntok = min(run, L - t0);
+  const int nrows = ntok + 2 * (W - 1);
+  const int nst = (nrows + CS_ROWS - 1) / CS_ROWS;
+  const T* xb = x + b * xbs + c0;
+  const T* gb = dy + (int64_t)b * L * C + c0;
+  auto issue = [&](int s) {
+    if (s < nst) {
 #pragma unroll
-  for (int i = 0; i < VEC; ++i) {
-    dbacc[i] = 0.f;
-#pragma unroll
-    for (int j = 0; j < W; ++j) dwacc[i][j] = 0.f;
-  }
-  for (int it = 0; it < CT_NT; ++it) {
-    const int t0 = (blockIdx.x * CT_NT + it) * CTB_TT;
-    if (t0 >= L) break;
-    __syncthreads();
-    for (int r = warp; r < XR; r += CTB_WARPS) tile_row<T, VEC, W>(xt[r][lane], x, xbs, xrs, window, b, t0 - (W - 1) + r, L, c0, C);
-    for (int r = warp; r < GR; r += CTB_WARPS) tile_row<T, VEC, W>(gt[r][lane], dy, (int64_t)L * C, C, nullptr, b, (t0 + r < L) ? t0 + r : -W, L, c0, C);
-    __syncthreads();
-    const int tw = warp * TW;
-    ChanVec<T, VEC> ring[W];
-    float dz[W][VEC];
-#pragma unroll
-    for (int k = 0; k < W; ++k)
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) dz[k][i] = 0.f;
-#pragma unroll
-    for (int j = 0; j < W - 1; ++j) ring[j + 1].from_raw(xt[tw + j][lane]);      // x rows (t0+tw)-(W-1) ..
-#pragma unroll
-    for (int k = 0; k < TW + W - 1; ++k) {
-      const int t = t0 + tw + k;
-#pragma unroll
-      for (int kk = W - 1; kk > 0; --kk)
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) dz[kk][i] = dz[kk - 1][i];
-#pragma unroll
-      for (int j = 0; j < W - 1; ++j) ring[j] = ring[j + 1];
-      ring[W - 1].from_raw(xt[tw + k + W - 1][lane]);
-      ChanVec<T, VEC> gv;
-      gv.from_raw(gt[tw + k][lane]);                    // zero past the sequence end
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        float pre = bs[i];
-#pragma unroll
-        for (int j = 0; j < W; ++j) pre = fmaf(w[i][j], ring[j].v[i], pre);
-        float d = SILU ? gv.v[i] * silu_grad_t<T>(pre) : gv.v[i];
-        dz[0][i] = d;
-        if (k < TW) {
-          dbacc[i] += d;
-#pragma unroll
-          for (int j = 0; j < W; ++j) dwacc[i][j] = fmaf(d, ring[j].v[i], dwacc[i][j]);
+      for (int r = 0; r < CS_ROWS; ++r) {
+        const int i = s * CS_ROWS + r, t = t0 - (W - 1) + i;
+        const int st = s % NSTG;
+        if (i < nrows && t < L) {
+          if (t >= 0) cs_copy<BYTES>(&ringx[st][r][tid], xb + (int64_t)t * xrs);
+          else ringx[st][r][tid] = window_row<T, VEC, W>(window, b, t, c0, C);
+          if (i >= W - 1) cs_copy<BYTES>(&ringg[st][r][tid], gb + (int64_t)t * C);
         }
       }
-      if (k >= W - 1) {
-        const int tp = t - (W - 1);
-        if (tp < L) {
-          ChanVec<T, VEC> o;
+    }
+    cs_commit();
+  };
+  float2 w2[W][VEC / 2], b2[VEC / 2], dw2[W][VEC / 2], db2[VEC / 2];
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) {
-            float acc = 0.f;
+  for (int s = 0; s < NSTG - 1; ++s) issue(s);
+  load_taps2<VEC, W>(w2, b2, weight, bias, c0);
+  P xr[W];                                              // xr[j] = input row of token t - (W-1) + j
+  float2 dz[W][VEC / 2];                                // dz[k] = dz at token t - k
 #pragma unroll
-            for (int j = 0; j < W; ++j) acc = fmaf(w[i][j], dz[j][i], acc);
-            o.v[i] = acc;
+  for (int j = 0; j < W; ++j)
+#pragma unroll
+    for (int i = 0; i < VEC / 2; ++i) {
+      xr[j].p[i] = make_float2(0.f, 0.f);
+      dz[j][i] = make_float2(0.f, 0.f);
+      dw2[j][i] = make_float2(0.f, 0.f);
+    }
+#pragma unroll
+  for (int i = 0; i < VEC / 2; ++i) db2[i] = make_float2(0.f, 0.f);
+  T* dxb = dx + b * dxbs + (int64_t)t0 * dxrs + c0;
+  // one row of the walk; FULL: an owned token past both halos (x, dy present; dw / db taken; a dx row leaves): no tests
+  auto row = [&](int s, int r, auto full) {
+    constexpr bool FULL = decltype(full)::value;
+    const int i = s * CS_ROWS + r;
+    if (FULL || i < nrows) {
+      const int t = t0 - (W - 1) + i;
+      const int st = s % NSTG;
+#pragma unroll
+      for (int k = W - 1; k > 0; --k)
+#pragma unroll
+        for (int e = 0; e < VEC / 2; ++e) dz[k][e] = dz[k - 1][e];
+      if (FULL || t < L) {
+#pragma unroll
+        for (int j = 0; j < W - 1; ++j) xr[j] = xr[j + 1];
+        xr[W - 1].from_raw(ringx[st][r][tid]);
+      }
+      if (FULL || (t < L && i >= W - 1)) {
+        P g;
+        g.from_raw(ringg[st][r][tid]);
+        const bool own = FULL || i < ntok + W - 1;
+#pragma unroll
+        for (int e = 0; e < VEC / 2; ++e) {
+          float2 pre = b2[e];
+#pragma unroll
+          for (int j = 0; j < W; ++j) pre = fma2(w2[j][e], xr[j].p[e], pre);
+          const float2 d = SILU ? mul2(g.p[e], silu_grad2<T>(pre)) : g.p[e];
+          dz[0][e] = d;
+          if (own) {
+            db2[e] = add2(db2[e], d);
+#pragma unroll
+            for (int j = 0; j < W; ++j) dw2[j][e] = fma2(d, xr[j].p[e], dw2[j][e]);
           }
-          o.store(dx + b * dxbs + (int64_t)tp * dxrs + c0);
         }
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC / 2; ++e) dz[0][e] = make_float2(0.f, 0.f);
       }
+      if (FULL || i >= 2 * (W - 1)) {                   // dx of token t - (W-1) = sum_j w[j] dz(t - j)
+        P o;
+#pragma unroll
+        for (int e = 0; e < VEC / 2; ++e) {
+          float2 acc = mul2(w2[0][e], dz[0][e]);
+#pragma unroll
+          for (int j = 1; j < W; ++j) acc = fma2(w2[j][e], dz[j][e], acc);
+          o.p[e] = acc;
+        }
+        *reinterpret_cast<Raw*>(dxb + (int64_t)(i - 2 * (W - 1)) * dxrs) = o.to_raw();
+      }
+    }
+  };
+  for (int s = 0; s < nst; ++s) {
+    issue(s + NSTG - 1);
+    cs_wait<NSTG - 1>();
+    if (s * CS_ROWS >= 2 * (W - 1) && s * CS_ROWS + CS_ROWS <= ntok + W - 1) {
+#pragma unroll
+      for (int r = 0; r < CS_ROWS; ++r) row(s, r, std::true_type{});
+    } else {
+#pragma unroll
+      for (int r = 0; r < CS_ROWS; ++r) row(s, r, std::false_type{});
     }
   }
   if (part != nullptr) {
-    __syncthreads();                                   // the tiles are dead: their storage becomes the reduction buffer
-    float(*red)[32][RED_E] = reinterpret_cast<float(*)[32][RED_E]>(sraw);
+    float* p = part + ((int64_t)(b * nruns + ridx) * C + c0) * (W + 1);
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) {
+    for (int e = 0; e < VEC / 2; ++e) {
 #pragma unroll
-      for (int j = 0; j < W; ++j) red[warp][lane][i * (W + 1) + j] = dwacc[i][j];
-      red[warp][lane][i * (W + 1) + W] = dbacc[i];
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < 32 * VEC * (W + 1); idx += CTB_WARPS * 32) {
-      const int l = idx / (VEC * (W + 1)), e = idx % (VEC * (W + 1));
-      float acc = 0.f;
-#pragma unroll
-      for (int ww = 0; ww < CTB_WARPS; ++ww) acc += red[ww][l][e];
-      part[((int64_t)(b * ntiles + blockIdx.x) * C + (blockIdx.y * 32 + l) * VEC) * (W + 1) + e] = acc;
+      for (int j = 0; j < W; ++j) {
+        p[(2 * e) * (W + 1) + j] = dw2[j][e].x;
+        p[(2 * e + 1) * (W + 1) + j] = dw2[j][e].y;
+      }
+      p[(2 * e) * (W + 1) + W] = db2[e].x;
+      p[(2 * e + 1) * (W + 1) + W] = db2[e].y;
     }
   }
 }
 
-// out[c, k] = sum over partial slots (fixed order), k < W -> dweight[c,k], k == W -> dbias[c]
-__global__ void conv_reduce_kernel(const float* __restrict__ part, float* __restrict__ dweight,
-                                   float* __restrict__ dbias, int nslots, int C, int W) {
-  int idx = blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= C * (W + 1)) return;
+// Width of a CTA in channel vectors (0: the streaming kernels do not serve this channel count) and the token run of a
+// thread: the longest of 256..32 that still leaves a few CTAs per SM slot (shorter runs only cost halo rows).
+static inline int stream_cx(int C, int VEC) {
+  if (C % VEC) return 0;
+  const int cv = C / VEC;
+  return cv % 128 == 0 ? 128 : (cv % 64 == 0 ? 64 : (cv % 32 == 0 ? 32 : 0));
+}
+static inline int stream_run(int B, int L, int cv, int cx) {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int ty = CS_THREADS / cx;
+  for (int run = 256; run > 32; run >>= 1) {
+    const int64_t nr = (L + run - 1) / run;
+    const int64_t ctas = (int64_t)B * ((nr + ty - 1) / ty) * (cv / cx);
+    if (ctas >= (int64_t)sms * 12) return run;
+  }
+  return 32;
+}
+
+// out[c, k] = sum over partial slots in a fixed order (k < W -> dweight[c,k], k == W -> dbias[c]): a CTA owns 32
+// columns; warp g sums the slots congruent to g modulo 8, then the 8 partial sums are added in order.
+__global__ void __launch_bounds__(256) conv_reduce_kernel(const float* __restrict__ part, float* __restrict__ dweight,
+                                                          float* __restrict__ dbias, int nslots, int C, int W) {
+  __shared__ float red[8][33];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int idx = blockIdx.x * 32 + lane, n = C * (W + 1);
   float acc = 0.f;
-  for (int s = 0; s < nslots; ++s) acc += part[(int64_t)s * C * (W + 1) + idx];
-  int c = idx / (W + 1), k = idx % (W + 1);
-  if (k < W) dweight[c * W + k] = acc;
-  else if (dbias) dbias[c] = acc;
+  if (idx < n) {
+#pragma unroll 4
+    for (int s = grp; s < nslots; s += 8) acc += part[(int64_t)s * n + idx];
+  }
+  red[grp][lane] = acc;
+  __syncthreads();
+  if (grp == 0 && idx < n) {
+    float v = red[0][lane];
+#pragma unroll
+    for (int g = 1; g < 8; ++g) v += red[g][lane];
+    const int c = idx / (W + 1), k = idx % (W + 1);
+    if (k < W) dweight[c * W + k] = v;
+    else if (dbias) dbias[c] = v;
+  }
 }
 
 static inline void conv_grid(int B, int L, int C, int VEC, dim3& grid, dim3& block) {
@@ -439,12 +594,15 @@ static inline void conv_grid(int B, int L, int C, int VEC, dim3& grid, dim3& blo
 template <typename T, int VEC, int W>
 static int conv_fwd_launch(const T* x, int64_t xbs, int64_t xrs, const float* w, const float* b, const float* win,
                            T* y, int B, int L, int C, int silu, cudaStream_t st) {
-  if (VEC > 1 && C % (32 * VEC) == 0) {
-    dim3 tg((L + CT_TT * CT_NT - 1) / (CT_TT * CT_NT), C / (32 * VEC), B);
-    if (silu) conv_fwd_tiled_kernel<T, VEC, W, true><<<tg, 256, 0, st>>>(x, xbs, xrs, w, b, win, y, L, C);
-    else conv_fwd_tiled_kernel<T, VEC, W, false><<<tg, 256, 0, st>>>(x, xbs, xrs, w, b, win, y, L, C);
-    ORBIT_CHECK_LAUNCH("conv_fwd_tiled_kernel");
-    return OK;
+  if constexpr (VEC == 4) {   // the streaming kernels are built for 4 channels per thread (8 bytes bf16, 16 bytes fp32)
+    if (const int cx = stream_cx(C, VEC)) {
+      const int cv = C / VEC, run = stream_run(B, L, cv, cx), ty = CS_THREADS / cx;
+      dim3 tg(((L + run - 1) / run + ty - 1) / ty, cv / cx, B);
+      if (silu) conv_fwd_stream_kernel<T, VEC, W, true><<<tg, CS_THREADS, 0, st>>>(x, xbs, xrs, w, b, win, y, L, C, run, cx);
+      else conv_fwd_stream_kernel<T, VEC, W, false><<<tg, CS_THREADS, 0, st>>>(x, xbs, xrs, w, b, win, y, L, C, run, cx);
+      ORBIT_CHECK_LAUNCH("conv_fwd_stream_kernel");
+      return OK;
+    }
   }
   dim3 grid, block;
   conv_grid(B, L, C, VEC, grid, block);
@@ -459,14 +617,17 @@ static int conv_bwd_launch(const T* x, int64_t xbs, int64_t xrs, const float* w,
                            const T* dy, T* dx, int64_t dxbs, int64_t dxrs, float* dwin, float* part, int B, int L,
                            int C, int silu, cudaStream_t st, int* nslots) {
   *nslots = B * ((L + CONV_TL - 1) / CONV_TL);
-  if (VEC > 1 && C % (32 * VEC) == 0 && dwin == nullptr) {
-    const int ntiles = (L + CTB_TT * CT_NT - 1) / (CTB_TT * CT_NT);
-    *nslots = B * ntiles;
-    dim3 tg(ntiles, C / (32 * VEC), B);
-    if (silu) conv_bwd_tiled_kernel<T, VEC, W, true><<<tg, CTB_WARPS * 32, 0, st>>>(x, xbs, xrs, w, b, win, dy, dx, dxbs, dxrs, part, L, C, ntiles);
-    else conv_bwd_tiled_kernel<T, VEC, W, false><<<tg, CTB_WARPS * 32, 0, st>>>(x, xbs, xrs, w, b, win, dy, dx, dxbs, dxrs, part, L, C, ntiles);
-    ORBIT_CHECK_LAUNCH("conv_bwd_tiled_kernel");
-    return OK;
+  if constexpr (VEC == 4) {
+    const int cx = dwin == nullptr ? stream_cx(C, VEC) : 0;
+    if (cx) {
+      const int cv = C / VEC, run = stream_run(B, L, cv, cx), ty = CS_THREADS / cx, nruns = (L + run - 1) / run;
+      *nslots = B * nruns;
+      dim3 tg((nruns + ty - 1) / ty, cv / cx, B);
+      if (silu) conv_bwd_stream_kernel<T, VEC, W, true><<<tg, CS_THREADS, 0, st>>>(x, xbs, xrs, w, b, win, dy, dx, dxbs, dxrs, part, L, C, run, cx, nruns);
+      else conv_bwd_stream_kernel<T, VEC, W, false><<<tg, CS_THREADS, 0, st>>>(x, xbs, xrs, w, b, win, dy, dx, dxbs, dxrs, part, L, C, run, cx, nruns);
+      ORBIT_CHECK_LAUNCH("conv_bwd_stream_kernel");
+      return OK;
+    }
   }
   dim3 grid, block;
   conv_grid(B, L, C, VEC, grid, block);
@@ -516,7 +677,7 @@ extern "C" int orbit_conv1d_fwd(const void* x, int64_t x_batch_stride, int64_t x
   if (dtype == BF16) {
     using T = __nv_bfloat16;
     if (conv_vec_ok<T>(x, x_batch_stride, x_row_stride, y, C)) {
-      if (C % 128 == 0) {   // tiled path: 8-byte vectors keep 32 warps resident per SM
+      if (stream_cx(C, 4)) {   // streaming path: 8-byte channel vectors (measured faster than 16-byte ones: more warps resident)
         CONV_DISPATCH_W(conv_fwd_launch, T, 4, (const T*)x, x_batch_stride, x_row_stride, weight, bias, window, (T*)y, B,
                         L, C, silu, st)
       }
@@ -564,7 +725,7 @@ extern "C" int orbit_conv1d_bwd(const void* x, int64_t x_batch_stride, int64_t x
     if (dtype == BF16) {
       using T = __nv_bfloat16;
       if (conv_vec_ok<T>(x, x_batch_stride, x_row_stride, dy, C, dx, dx_batch_stride, dx_row_stride)) {
-        if (C % 128 == 0 && dwindow == nullptr) {   // tiled path: 8-byte vectors keep 16 warps resident per SM
+        if (dwindow == nullptr && stream_cx(C, 4)) {   // streaming path: 8-byte channel vectors
           CONV_DISPATCH_W(conv_bwd_launch, T, 4, (const T*)x, x_batch_stride, x_row_stride, weight, bias, window,
                           (const T*)dy, (T*)dx, dx_batch_stride, dx_row_stride, dwindow, part, B, L, C, silu, st, &nslots)
         }
@@ -588,7 +749,7 @@ extern "C" int orbit_conv1d_bwd(const void* x, int64_t x_batch_stride, int64_t x
   if (rc != OK) return rc;
   if (dweight) {
     int n = C * (W + 1);
-    conv_reduce_kernel<<<(n + 255) / 256, 256, 0, st>>>(part, dweight, dbias, nslots, C, W);
+    conv_reduce_kernel<<<(n + 31) / 32, 256, 0, st>>>(part, dweight, dbias, nslots, C, W);
     ORBIT_CHECK_LAUNCH("conv_reduce_kernel");
   }
   return OK;

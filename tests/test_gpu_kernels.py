@@ -53,6 +53,31 @@ def test_conv(dtype, B, L, C, W, pad, use_win):
     assert torch.equal(dw, dw2) and torch.equal(db, db2) and torch.equal(dx, dx2)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,L,C,W,pad,fwd_win", [(2, 333, 256, 4, 64, True), (1, 70, 1024, 4, 0, False), (3, 37, 128, 3, 8, True),
+                                                 (2, 129, 512, 2, 16, False), (1, 2, 256, 4, 0, True), (2, 1100, 128, 4, 0, True)])
+def test_conv_streaming_path(dtype, B, L, C, W, pad, fwd_win):
+    """Channel counts the streaming kernels serve (whole warps of 8- or 16-byte channel vectors): several token runs per
+    row, ragged run ends, a carried window read by the first run, no window gradient."""
+    g = torch.Generator().manual_seed(1)
+    wide = torch.randn(B, L, C + pad, generator=g).to(dtype).to(DEV)
+    x = wide[..., pad // 2: pad // 2 + C] if pad else wide
+    weight = (torch.randn(C, W, generator=g) * 0.5).to(DEV)
+    bias = torch.randn(C, generator=g).to(DEV)
+    win = torch.randn(B, C, W, generator=g).to(DEV) if fwd_win else None
+    dy = torch.randn(B, L, C, generator=g).to(dtype).to(DEV)
+    y = ops.conv1d_fwd(x, weight, bias, win)
+    assert rel(y, R.conv1d_fwd(x, weight, bias, win)) < tol(dtype)
+    dxw = torch.full((B, L, C + 16), float("nan"), device=DEV, dtype=dtype)
+    dx_out = dxw[..., 8:8 + C]                                          # dx written in place into a strided column range
+    dx, _, dw, db = ops.conv1d_bwd(x, weight, bias, win, dy, dx_out=dx_out)
+    rx, _, rw, rb = R.conv1d_bwd(x, weight, bias, win, dy)
+    assert dx.data_ptr() == dx_out.data_ptr() and torch.isnan(dxw[..., :8]).all() and torch.isnan(dxw[..., 8 + C:]).all()
+    assert rel(dx, rx) < tol(dtype, True) and rel(dw, rw) < tol(dtype, True) and rel(db, rb) < tol(dtype, True)
+    dx2, _, dw2, db2 = ops.conv1d_bwd(x, weight, bias, win, dy)
+    assert torch.equal(dw, dw2) and torch.equal(db, db2) and torch.equal(dx, dx2)
+
+
 def test_conv_empty_and_refusals():
     x = torch.zeros(2, 0, 16, device=DEV)
     w = torch.zeros(16, 4, device=DEV)
