@@ -226,12 +226,25 @@ __global__ void __launch_bounds__(NORM_THREADS) gate_norm_bwd_scalar_kernel(
   }
 }
 
-__global__ void colsum_kernel(const float* __restrict__ part, float* __restrict__ out, int nslots, int D) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
+// out[c] = sum over partial slots in a fixed order: a CTA owns 32 columns, warp g sums the slots congruent to g modulo 8,
+// then the 8 partial sums are added in order (deterministic; 8 x the loads in flight of a single walk).
+__global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ part, float* __restrict__ out, int nslots, int D) {
+  __shared__ float red[8][33];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float acc = 0.f;
-  for (int s = 0; s < nslots; ++s) acc += part[(int64_t)s * D + c];
-  out[c] = acc;
+  if (c < D) {
+#pragma unroll 4
+    for (int s = grp; s < nslots; s += 8) acc += part[(int64_t)s * D + c];
+  }
+  red[grp][lane] = acc;
+  __syncthreads();
+  if (grp == 0 && c < D) {
+    float v = red[0][lane];
+#pragma unroll
+    for (int g = 1; g < 8; ++g) v += red[g][lane];
+    out[c] = v;
+  }
 }
 
 static int norm_bwd_slots(int64_t M) {
@@ -300,7 +313,7 @@ static int gate_norm_bwd_t(const void* y, const void* z, int64_t zrs, const floa
                                                                   (T*)dy, (T*)dz, dzrs, part, M, D);
     ORBIT_CHECK_LAUNCH("gate_norm_bwd_scalar_kernel");
     if (dw != nullptr) {
-      colsum_kernel<<<(D + 255) / 256, 256, 0, st>>>(part, dw, slots, D);
+      colsum_kernel<<<(D + 31) / 32, 256, 0, st>>>(part, dw, slots, D);
       ORBIT_CHECK_LAUNCH("colsum_kernel");
     }
     return OK;
@@ -310,7 +323,7 @@ static int gate_norm_bwd_t(const void* y, const void* z, int64_t zrs, const floa
 #undef L_
   ORBIT_CHECK_LAUNCH("gate_norm_bwd_kernel");
   if (dw != nullptr) {
-    colsum_kernel<<<(D + 255) / 256, 256, 0, st>>>(part, dw, slots, D);
+    colsum_kernel<<<(D + 31) / 32, 256, 0, st>>>(part, dw, slots, D);
     ORBIT_CHECK_LAUNCH("colsum_kernel");
   }
   return OK;

@@ -242,7 +242,7 @@ class HybridMambaSSM(StateLifecycle, nn.Module):
         f = torch.float32
         with torch.autocast("cuda", enabled=False):
             xa = x.to(io)
-            proj = F.linear(xa, self._fused_weight(io))
+            proj = ops.ProjectFn.apply(xa, self._proj_pad, None, 0, self.in_proj.weight, *[m.weight for _, m in self._slab])
             arena = ops.GradArena()        # conv and gate backward write d(drive), dz straight into d(proj)
             drive_raw, z, slab = ops.SplitColumnsFn.apply(proj, arena, s.d_inner, s.d_inner, self.tok_width)
             new = State()
@@ -267,7 +267,7 @@ class HybridMambaSSM(StateLifecycle, nn.Module):
             self._route_note = "fp32 coordinate scan"
             y = ops.GateNormFn.apply(y.reshape(Bsz, L, s.d_inner), z, self.norm.weight if s.out_norm else None, s.norm_eps,
                                      (arena, 1))
-            out = F.linear(y, self.out_proj.weight.to(io))
+            out = ops.ProjectFn.apply(y, 0, None, 0, self.out_proj.weight)
         if not return_state:
             return out
         new["hidden_state"] = hN

@@ -13,6 +13,7 @@ import functools
 from dataclasses import dataclass
 
 import torch
+import torch.nn.functional as F
 
 from . import _lib
 
@@ -193,6 +194,69 @@ class SplitColumnsFn(torch.autograd.Function):
         if o < ctx.shape[-1]:
             out[..., o:].zero_()
         return (out, None) + (None,) * len(ctx.sizes)
+
+
+def _mm_f32(a, b):
+    """a @ b accumulated and returned in float32 (16-bit operands on a CUDA device: one GEMM with an fp32 result, no
+    16-bit rounding of the product and no cast pass after it)."""
+    if a.is_cuda and a.dtype in (torch.bfloat16, torch.float16):
+        return torch.mm(a, b, out_dtype=torch.float32)
+    return (a @ b).to(torch.float32)
+
+
+class ProjectFn(torch.autograd.Function):
+    """``x @ cat(weights)^T`` (+ `bias` on the columns from `bias_off`, + `pad` zero columns) as ONE node over the
+    parameters themselves: the projections of a layer that share an input (drive | gate | token slab; reference:
+    src/orbit_ssm/ssm/ssd_mimo.py:4545-4558, src/orbit_ssm/ssm/hybrid_mamba.py:2729-2759) or a single projection.
+
+    The fp32 master weights are cast into one buffer of the IO dtype in a single pass (no concatenated fp32 copy);
+    backward forms the weight gradient as one GEMM with an fp32 result and hands each parameter its row range of it
+    (no cast or split pass), and reduces the bias gradient over the biased columns only (a linear layer's own backward
+    would sum every column of the gradient)."""
+
+    @staticmethod
+    def forward(ctx, x, pad, bias, bias_off, *weights):
+        io, K = x.dtype, x.shape[-1]
+        sizes = [int(w.shape[0]) for w in weights]
+        n_tot = sum(sizes) + int(pad)
+        wcat = torch.empty((n_tot, K), device=x.device, dtype=io)
+        o = 0
+        for w, n in zip(weights, sizes):
+            wcat[o:o + n].copy_(w)
+            o += n
+        if pad:
+            wcat[o:].zero_()
+        x2 = x.reshape(-1, K)
+        bfull = None
+        if bias is not None:
+            bfull = torch.zeros((n_tot,), device=x.device, dtype=io)
+            bfull[bias_off:bias_off + bias.shape[0]].copy_(bias)
+        out = F.linear(x2, wcat, bfull)
+        ctx.save_for_backward(x2, wcat)
+        ctx.meta = (sizes, [w.dtype for w in weights], None if bias is None else (int(bias_off), int(bias.shape[0]), bias.dtype),
+                    x.shape)
+        return out.view(*x.shape[:-1], n_tot)
+
+    @staticmethod
+    @first_order_only("fused projection")
+    def backward(ctx, dproj):
+        x2, wcat = ctx.saved_tensors
+        sizes, wdts, bmeta, xshape = ctx.meta
+        d2 = dproj.reshape(-1, dproj.shape[-1])
+        dx = (d2 @ wcat).view(xshape) if ctx.needs_input_grad[0] else None
+        dws = [None] * len(sizes)
+        if any(ctx.needs_input_grad[4:]):
+            dW = _mm_f32(d2.t(), x2)
+            o = 0
+            for i, (n, dt) in enumerate(zip(sizes, wdts)):
+                if ctx.needs_input_grad[4 + i]:
+                    dws[i] = dW[o:o + n] if dt == torch.float32 else dW[o:o + n].to(dt)
+                o += n
+        db = None
+        if bmeta is not None and ctx.needs_input_grad[2]:
+            off, nb, bdt = bmeta
+            db = d2[:, off:off + nb].sum(0).to(bdt)      # fp32 accumulation, result in the IO dtype (as a linear layer's own backward)
+        return (dx, None, db, None, *dws)
 
 
 # ----------------------------------------------------------------------------------------------------

@@ -263,6 +263,14 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
             bs.append(b if b is not None else ws[0].new_zeros(wd_))
         return torch.cat(ws, 0), torch.cat(bs, 0)
 
+    def _tok_bias(self):
+        """Bias of the token slab columns (zeros where a map has none), or None when no map has one."""
+        if all(getattr(self, a).bias is None for a in self._proj_attrs):
+            return None
+        ref = getattr(self, self._proj_attrs[0]).weight
+        return torch.cat([getattr(self, a).bias if getattr(self, a).bias is not None else ref.new_zeros(wd_)
+                          for a, wd_ in zip(self._proj_attrs, self._proj_widths)], 0)
+
     def _fused_weight(self, dtype):
         wt, bt = self.tok_proj_weight()
         parts_w = [self.in_proj.weight, wt]
@@ -352,8 +360,9 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         want_state = return_state
         with torch.autocast("cuda", enabled=False):
             xa = x.to(io)
-            wcat, bcat = self._fused_weight(io)
-            proj = F.linear(xa, wcat, bcat)                                    # [B, L, drive | z | slab | pad]
+            # [B, L, drive | z | slab | pad]: one GEMM over the parameters themselves (cast once into the IO dtype)
+            proj = ops.ProjectFn.apply(xa, self._proj_pad, self._tok_bias(), s.d_inner + self.d_gate, self.in_proj.weight,
+                                       *[getattr(self, a).weight for a in self._proj_attrs])
             # every consumer of a column range writes that range of d(proj) in place (conv, gate, token tails)
             arena = ops.GradArena()
             keys, widths = self._part_keys, self._part_widths
@@ -382,7 +391,7 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
                       else bc_raw.contiguous())
                 if want_state:
                     new["bc_conv_state"] = _next_window(win, bc_raw, s.d_conv)
-                b_src, c_src = bc[..., :wb], bc[..., wb:]
+                b_src, c_src = ops.SplitColumnsFn.apply(bc, None, wb, wc)
             else:
                 b_src, c_src = parts["B"], parts["C"]
 
@@ -411,7 +420,7 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
                 if want_state and s.use_trap:
                     v_last = self._last_write(u, law, Bsz)
             y = ops.GateNormFn.apply(y, z, self.norm.weight if s.out_norm else None, s.norm_eps, (arena, 1)) if L > 0 else y
-            out = F.linear(y, self.out_proj.weight.to(io))
+            out = ops.ProjectFn.apply(y, 0, None, 0, self.out_proj.weight)
         if not want_state:
             return out
         new["hidden_state"] = hidden
