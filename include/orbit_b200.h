@@ -303,7 +303,10 @@ int orbit_hm_scan_bwd(const orbit_hm_args* a, int dtype, void* stream);
  * are those of its chunk-parallel pass (src/orbit_ssm/kernels/ssd_mimo/chunkpar.py:19-25) and of its State continuation
  * contract (src/orbit_ssm/ssm/ssd_mimo_torch.py:677-679). */
 int64_t orbit_cp_record_floats(int64_t n_state, int BHR, int backward);
-int orbit_cp_state_pack(const float* dA, float* record, int B, int L, int HR, int64_t n_state, void* stream);
+int64_t orbit_cp_state_pack_workspace_bytes(int B, int L, int HR);
+/* workspace: slice sums of the two-stage (fixed-order) reduction over the segment, written in full before they are read. */
+int orbit_cp_state_pack(const float* dA, float* record, int B, int L, int HR, int64_t n_state, void* workspace,
+                        int64_t workspace_bytes, void* stream);
 int orbit_cp_state_combine(const float* records, int64_t stride, int world, int rank, int64_t n_state, int per_head, int BHR,
                            int backward, float* out, void* stream);
 

@@ -93,7 +93,8 @@ SIGNATURES = {
     "orbit_hm_scan_fwd": (_I, [C.POINTER(HmArgs), _I, _P]),
     "orbit_hm_scan_bwd": (_I, [C.POINTER(HmArgs), _I, _P]),
     "orbit_cp_record_floats": (_L, [_L, _I, _I]),
-    "orbit_cp_state_pack": (_I, [_P, _P, _I, _I, _I, _L, _P]),
+    "orbit_cp_state_pack_workspace_bytes": (_L, [_I, _I, _I]),
+    "orbit_cp_state_pack": (_I, [_P, _P, _I, _I, _I, _L, _P, _L, _P]),
     "orbit_cp_state_combine": (_I, [_P, _L, _I, _I, _L, _I, _I, _I, _P, _P]),
     "orbit_selftest_umma": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
     "orbit_selftest_wait_timeout": (_I, [_P, _I, _P]),

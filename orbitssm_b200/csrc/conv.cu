@@ -7,8 +7,8 @@
 // the kernel reads a column slice of the fused input-projection output in place; one thread owns one channel
 // vector and slides over a run of tokens, so every warp access is a contiguous row segment.
 // HBM-bound: forward 2*B*L*C*es bytes, backward 3*B*L*C*es (x, dy in; dx out).  Channel counts that fill whole warps
-// with 4-channel vectors take the streaming kernels (cp.async rings, packed fp32 pairs); the rest and calls that ask
-// for the carried window's gradient take the plain per-thread kernels above them.
+// with 4-channel vectors take the streaming kernels (cp.async rings, packed fp32 pairs); the rest take the plain
+// per-thread kernels above them.
 #include "common.cuh"
 #include "../../include/orbit_b200.h"
 #include <type_traits>
@@ -413,7 +413,8 @@ __global__ void __launch_bounds__(CS_THREADS) conv_bwd_stream_kernel(const T* __
                                                                      const float* __restrict__ weight, const float* __restrict__ bias,
                                                                      const float* __restrict__ window, const T* __restrict__ dy,
                                                                      T* __restrict__ dx, int64_t dxbs, int64_t dxrs,
-                                                                     float* __restrict__ part, int L, int C, int run, int cx, int nruns) {
+                                                                     float* __restrict__ dwindow, float* __restrict__ part, int L,
+                                                                     int C, int run, int cx, int nruns) {
   using P = Pairs<T, VEC>;
   using Raw = typename P::Raw;
   constexpr int BYTES = VEC * (int)sizeof(T);
@@ -510,6 +511,17 @@ __global__ void __launch_bounds__(CS_THREADS) conv_bwd_stream_kernel(const T* __
           o.p[e] = acc;
         }
         *reinterpret_cast<Raw*>(dxb + (int64_t)(i - 2 * (W - 1)) * dxrs) = o.to_raw();
+      } else if (!FULL && dwindow != nullptr && t0 == 0 && i >= W - 1) {
+        // the first run also owns the gradient of the carried window: its slot W + tp is the input of token tp < 0
+        const int tp = i - 2 * (W - 1);
+#pragma unroll
+        for (int e = 0; e < VEC / 2; ++e) {
+          float2 acc = mul2(w2[0][e], dz[0][e]);
+#pragma unroll
+          for (int j = 1; j < W; ++j) acc = fma2(w2[j][e], dz[j][e], acc);
+          dwindow[((int64_t)b * C + c0 + 2 * e) * W + (W + tp)] = acc.x;
+          dwindow[((int64_t)b * C + c0 + 2 * e + 1) * W + (W + tp)] = acc.y;
+        }
       }
     }
   };
@@ -618,13 +630,13 @@ static int conv_bwd_launch(const T* x, int64_t xbs, int64_t xrs, const float* w,
                            int C, int silu, cudaStream_t st, int* nslots) {
   *nslots = B * ((L + CONV_TL - 1) / CONV_TL);
   if constexpr (VEC == 4) {
-    const int cx = dwin == nullptr ? stream_cx(C, VEC) : 0;
+    const int cx = stream_cx(C, VEC);
     if (cx) {
       const int cv = C / VEC, run = stream_run(B, L, cv, cx), ty = CS_THREADS / cx, nruns = (L + run - 1) / run;
       *nslots = B * nruns;
       dim3 tg((nruns + ty - 1) / ty, cv / cx, B);
-      if (silu) conv_bwd_stream_kernel<T, VEC, W, true><<<tg, CS_THREADS, 0, st>>>(x, xbs, xrs, w, b, win, dy, dx, dxbs, dxrs, part, L, C, run, cx, nruns);
-      else conv_bwd_stream_kernel<T, VEC, W, false><<<tg, CS_THREADS, 0, st>>>(x, xbs, xrs, w, b, win, dy, dx, dxbs, dxrs, part, L, C, run, cx, nruns);
+      if (silu) conv_bwd_stream_kernel<T, VEC, W, true><<<tg, CS_THREADS, 0, st>>>(x, xbs, xrs, w, b, win, dy, dx, dxbs, dxrs, dwin, part, L, C, run, cx, nruns);
+      else conv_bwd_stream_kernel<T, VEC, W, false><<<tg, CS_THREADS, 0, st>>>(x, xbs, xrs, w, b, win, dy, dx, dxbs, dxrs, dwin, part, L, C, run, cx, nruns);
       ORBIT_CHECK_LAUNCH("conv_bwd_stream_kernel");
       return OK;
     }
@@ -725,7 +737,7 @@ extern "C" int orbit_conv1d_bwd(const void* x, int64_t x_batch_stride, int64_t x
     if (dtype == BF16) {
       using T = __nv_bfloat16;
       if (conv_vec_ok<T>(x, x_batch_stride, x_row_stride, dy, C, dx, dx_batch_stride, dx_row_stride)) {
-        if (dwindow == nullptr && stream_cx(C, 4)) {   // streaming path: 8-byte channel vectors
+        if (stream_cx(C, 4)) {   // streaming path: 8-byte channel vectors
           CONV_DISPATCH_W(conv_bwd_launch, T, 4, (const T*)x, x_batch_stride, x_row_stride, weight, bias, window,
                           (const T*)dy, (T*)dx, dx_batch_stride, dx_row_stride, dwindow, part, B, L, C, silu, st, &nslots)
         }

@@ -14,16 +14,46 @@
 
 namespace orbit {
 
-// A_j[b, hr] = sum_t dA[b, t, hr] written behind the state part of this rank's record.  One warp per (b, hr).
-__global__ void cp_pack_kernel(const float* __restrict__ dA, float* __restrict__ rec_logA, int L, int HR, int BHR) {
-  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+// A_j[b, hr] = sum_t dA[b, t, hr], written behind the state part of this rank's record, in two fixed-order stages.
+// Stage 1: a CTA owns 32 consecutive kernel heads (one 128-byte row segment per token) and one of S slices of the
+// segment; warp g sums the tokens of the slice congruent to g modulo 8, the 8 sums are added in order -> part[b][slice][hr].
+// Stage 2: one thread per (b, hr) adds the S slice sums in order.
+constexpr int CP_SLICES_MAX = 512;
+constexpr int CP_SLICE_MIN = 256;     // tokens per slice at least
+
+static inline int cp_slices(int L) {
+  const int s = (L + CP_SLICE_MIN - 1) / CP_SLICE_MIN;
+  return s < 1 ? 1 : (s > CP_SLICES_MAX ? CP_SLICES_MAX : s);
+}
+
+__global__ void __launch_bounds__(256) cp_pack_stage1(const float* __restrict__ dA, float* __restrict__ part, int L, int HR, int S) {
+  __shared__ float red[8][33];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int hr = blockIdx.x * 32 + lane, sl = blockIdx.y, b = blockIdx.z;
+  const int per = (L + S - 1) / S, t0 = sl * per, t1 = min(t0 + per, L);
+  float acc = 0.f;
+  if (hr < HR) {
+    const float* p = dA + (int64_t)b * L * HR + hr;
+#pragma unroll 4
+    for (int t = t0 + grp; t < t1; t += 8) acc += p[(int64_t)t * HR];
+  }
+  red[grp][lane] = acc;
+  __syncthreads();
+  if (grp == 0 && hr < HR) {
+    float v = red[0][lane];
+#pragma unroll
+    for (int g = 1; g < 8; ++g) v += red[g][lane];
+    part[((int64_t)b * S + sl) * HR + hr] = v;
+  }
+}
+
+__global__ void cp_pack_stage2(const float* __restrict__ part, float* __restrict__ rec_logA, int HR, int BHR, int S) {
+  const int w = blockIdx.x * blockDim.x + threadIdx.x;
   if (w >= BHR) return;
   const int b = w / HR, hr = w - b * HR;
-  const float* p = dA + (int64_t)b * L * HR + hr;
   float s = 0.f;
-  for (int t = lane; t < L; t += 32) s += p[(int64_t)t * HR];
-  s = warp_sum(s);
-  if (lane == 0) rec_logA[w] = s;
+  for (int sl = 0; sl < S; ++sl) s += part[((int64_t)b * S + sl) * HR + hr];
+  rec_logA[w] = s;
 }
 
 // One thread per state element.  recs: [W][stride] floats, record j = [ state (n_state) | logA (BHR) | ext (n_state, bwd) ].
@@ -58,12 +88,23 @@ extern "C" int64_t orbit_cp_record_floats(int64_t n_state, int BHR, int backward
   return n_state + BHR + (backward ? n_state : 0);
 }
 
-extern "C" int orbit_cp_state_pack(const float* dA, float* record, int B, int L, int HR, int64_t n_state, void* stream) {
+extern "C" int64_t orbit_cp_state_pack_workspace_bytes(int B, int L, int HR) {
+  if (B <= 0 || L <= 0 || HR <= 0) return 0;
+  return (int64_t)B * cp_slices(L) * HR * (int64_t)sizeof(float);
+}
+
+extern "C" int orbit_cp_state_pack(const float* dA, float* record, int B, int L, int HR, int64_t n_state, void* workspace,
+                                   int64_t workspace_bytes, void* stream) {
   ORBIT_REQUIRE(dA && record, ERR_BAD_ARG, "orbit_cp_state_pack: null dA/record");
   ORBIT_REQUIRE(B > 0 && L > 0 && HR > 0 && n_state > 0, ERR_BAD_ARG, "orbit_cp_state_pack: bad sizes B=%d L=%d HR=%d", B, L, HR);
-  const int BHR = B * HR;
-  cp_pack_kernel<<<(BHR * 32 + 255) / 256, 256, 0, (cudaStream_t)stream>>>(dA, record + n_state, L, HR, BHR);
-  ORBIT_CHECK_LAUNCH("cp_pack_kernel");
+  ORBIT_REQUIRE(workspace && workspace_bytes >= orbit_cp_state_pack_workspace_bytes(B, L, HR), ERR_WORKSPACE,
+                "orbit_cp_state_pack: workspace of %lld bytes needed", (long long)orbit_cp_state_pack_workspace_bytes(B, L, HR));
+  const int BHR = B * HR, S = cp_slices(L);
+  float* part = (float*)workspace;
+  cp_pack_stage1<<<dim3((HR + 31) / 32, S, B), 256, 0, (cudaStream_t)stream>>>(dA, part, L, HR, S);
+  ORBIT_CHECK_LAUNCH("cp_pack_stage1");
+  cp_pack_stage2<<<(BHR + 127) / 128, 128, 0, (cudaStream_t)stream>>>(part, record + n_state, HR, BHR, S);
+  ORBIT_CHECK_LAUNCH("cp_pack_stage2");
   return OK;
 }
 

@@ -486,8 +486,12 @@ def run_phase(a, name, phase, state_in, state_out, dtype_code, precision):
 def cp_pack(dA, record, n_state):
     """Sum the segment's log-decays dA [B, L, H, R] over L into the record behind its state part (`orbit_cp_state_pack`)."""
     B, L, H, R = dA.shape
-    with _timed("cp_state_pack", 1):
-        _lib.check(_lib.load().orbit_cp_state_pack(_ptr(dA), _ptr(record), B, L, H * R, int(n_state), _stream()), "orbit_cp_state_pack")
+    lib = _lib.load()
+    nbytes = int(lib.orbit_cp_state_pack_workspace_bytes(B, L, H * R))
+    ws = torch.empty((max(nbytes, 4),), device=dA.device, dtype=torch.uint8)
+    with _timed("cp_state_pack", 2):
+        _lib.check(lib.orbit_cp_state_pack(_ptr(dA), _ptr(record), B, L, H * R, int(n_state), _ptr(ws), nbytes, _stream()),
+                   "orbit_cp_state_pack")
 
 
 def cp_combine(records, world, rank, n_state, per_head, BHR, backward):

@@ -76,6 +76,34 @@ def test_conv_streaming_path(dtype, B, L, C, W, pad, fwd_win):
     assert rel(dx, rx) < tol(dtype, True) and rel(dw, rw) < tol(dtype, True) and rel(db, rb) < tol(dtype, True)
     dx2, _, dw2, db2 = ops.conv1d_bwd(x, weight, bias, win, dy)
     assert torch.equal(dw, dw2) and torch.equal(db, db2) and torch.equal(dx, dx2)
+    if fwd_win:                                                         # the same kernels also return the window's gradient
+        dx3, dwin, dw3, _ = ops.conv1d_bwd(x, weight, bias, win, dy, want_dwindow=True)
+        _, rwin, _, _ = R.conv1d_bwd(x, weight, bias, win, dy, want_dwindow=True)
+        assert rel(dwin, rwin) < tol(dtype, True) and torch.equal(dx3, dx) and torch.equal(dw3, dw)
+
+
+def test_cp_state_pack_and_combine():
+    """The exchange-step kernels of context parallelism against their torch restatements: the segment's summed log-decay
+    (two-stage, fixed order: bitwise reproducible) and the combination of W gathered records, both directions."""
+    g = torch.Generator().manual_seed(3)
+    B, L, H, Rk, N, G, W = 2, 1000, 6, 2, 8, 4, 5
+    n_state, BHR = B * H * Rk * N * G, B * H * Rk
+    dA = (-torch.rand(B, L, H, Rk, generator=g) * 0.01).to(DEV)
+    rec = torch.zeros(n_state + BHR, device=DEV)
+    ops.cp_pack(dA, rec, n_state)
+    want = torch.zeros(n_state + BHR)
+    R.cp_pack(dA.cpu(), want, n_state)
+    assert rel(rec[n_state:], want[n_state:]) < 1e-6
+    rec2 = torch.zeros_like(rec)
+    ops.cp_pack(dA, rec2, n_state)
+    assert torch.equal(rec, rec2)
+    for backward in (False, True):
+        stride = n_state + BHR + (n_state if backward else 0)
+        recs = torch.randn(W, stride, generator=g)
+        recs[:, n_state:n_state + BHR] = -torch.rand(W, BHR, generator=g) * 3.0
+        for rank in (0, 2, W - 1):
+            got = ops.cp_combine(recs.to(DEV), W, rank, n_state, N * G, BHR, backward)
+            assert rel(got, R.cp_combine(recs, W, rank, n_state, N * G, BHR, backward)) < 1e-6, (backward, rank)
 
 
 def test_conv_empty_and_refusals():
