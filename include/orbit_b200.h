@@ -289,6 +289,37 @@ int orbit_hm_scan_fwd(const orbit_hm_args* a, int dtype, void* stream);
  * accumulation into caller memory, no atomics): the caller sums them over their leading axis. */
 int orbit_hm_scan_bwd(const orbit_hm_args* a, int dtype, void* stream);
 
+/* ---- HybridMamba clock tail ------------------------------------------------------------------------------------
+ * Replaces the clock part of the reference's `_fused_hm_tails` (src/orbit_ssm/ssm/hybrid_mamba.py:1890-1931; `dt_softplus_cf`,
+ * src/orbit_ssm/layers/tails.py:1086), its angle feature (`_theta_feature`, hybrid_mamba.py:971-1000) and the exact sigmoid of
+ * the trapezoid weight (src/orbit_ssm/layers/layout.py:115-148).  Per row m = (batch, token):
+ *   delta[m,h] = softplus(dt_raw[m,h] + dt_bias[h]) (threshold 20);  lam[m,h] = sigmoid(trap_raw[m,h] + trap_bias[h]);
+ *   feat[m,k]  = omega[j] tanh(th_raw[m,j]) at k = rot_idx[j], 0 at the other row pairs.
+ * Raw inputs are slab columns [M, .] in the IO dtype with their own row strides; outputs are fp32.  Backward writes the raw
+ * gradients in the IO dtype (their own row strides) and the parameter-shaped gradients through `part` (two fixed-order stages). */
+typedef struct orbit_hm_tail_args {
+  int64_t M;                  /* rows = B * L                                                                       */
+  int H, K, Krot;             /* heads; row pairs N / 2; rotating pairs                                             */
+  const void* dt_raw;   int64_t dt_rs;        /* [M, H]                                                             */
+  const void* trap_raw; int64_t trap_rs;      /* [M, H] or NULL (Euler write)                                       */
+  const void* th_raw;   int64_t th_rs;        /* [M, Krot] or NULL (no rotating pairs)                              */
+  const float* dt_bias;       /* [H]                                                                                */
+  const float* trap_bias;     /* [H] or NULL                                                                        */
+  const float* omega;         /* [Krot] angular rate of each rotating pair                                          */
+  const int* rot_idx;         /* [Krot] row-pair index of each rotating pair, distinct, in [0, K)                   */
+  float *delta, *lam, *feat;  /* out [M, H], [M, H], [M, K]; forward writes them, backward reads lam                */
+  /* backward */
+  const float *ddelta, *dlam, *dfeat;         /* [M, H], [M, H], [M, K]; each may be NULL (taken as zero)           */
+  void* d_dt_raw;   int64_t d_dt_rs;
+  void* d_trap_raw; int64_t d_trap_rs;
+  void* d_th_raw;   int64_t d_th_rs;
+  float *d_dt_bias, *d_trap_bias, *d_omega;   /* out [H], [H], [Krot]; each may be NULL                             */
+  float* part; int64_t part_bytes;            /* workspace of orbit_hm_tail_bwd_workspace_bytes(M, H, Krot) bytes   */
+} orbit_hm_tail_args;
+int orbit_hm_tail_fwd(const orbit_hm_tail_args* a, int dtype, void* stream);
+int64_t orbit_hm_tail_bwd_workspace_bytes(int64_t M, int H, int Krot);
+int orbit_hm_tail_bwd(const orbit_hm_tail_args* a, int dtype, void* stream);
+
 /* ---- context parallelism: the exchange step of the SSD-MIMO scan ------------------------------------------------
  * A sequence split over W ranks (rank j holds segment j) needs one all-gather per direction.  Rank j contributes the
  * record [ F_j | A_j ] (forward) or [ E_j | A_j | X_j ] (backward), all float32:

@@ -454,6 +454,44 @@ def run_clock(a, name, backward, dtype_code, compute=torch.float64):
         t["g_alog"].copy_(_f(t["ddA"], compute) * out["dA"].detach())
 
 
+# ---- HybridMamba clock tail (torch restatement of orbit_hm_tail_fwd / orbit_hm_tail_bwd) ---------------------------------
+def _hm_tail(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K, compute):
+    delta = torch.nn.functional.softplus(dt_raw.to(compute) + dt_bias.to(compute))
+    lam = None
+    if trap_raw is not None:
+        lam = torch.sigmoid(trap_raw.to(compute) + (trap_bias.to(compute) if trap_bias is not None else 0.0))
+    feat = None
+    if th_raw is not None:
+        q = th_raw.to(compute)
+        feat = q.new_zeros(*q.shape[:-1], K).index_copy(-1, rot_idx.long(), omega.to(compute) * torch.tanh(q))
+    return delta, lam, feat
+
+
+def hm_tail_fwd(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K, compute=torch.float64):
+    with torch.no_grad():
+        delta, lam, feat = _hm_tail(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K, compute)
+    f = torch.float32
+    return delta.to(f), None if lam is None else lam.to(f), None if feat is None else feat.to(f)
+
+
+def hm_tail_bwd(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K, lam, ddelta, dlam, dfeat, compute=torch.float64):
+    ins = [None if v is None else v.detach().to(compute).requires_grad_(True) for v in (dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega)]
+    with torch.enable_grad():
+        outs = _hm_tail(*ins, rot_idx, K, compute)
+        loss = 0.0
+        for o, g in zip(outs, (ddelta, dlam, dfeat)):
+            if o is not None and g is not None:
+                loss = loss + (o * g.to(compute)).sum()
+    have = [v for v in ins if v is not None]
+    grads = iter(torch.autograd.grad(loss, have, allow_unused=True)) if torch.is_tensor(loss) else iter([None] * len(have))
+    full = [None if v is None else next(grads) for v in ins]
+    full = [torch.zeros_like(v) if (g is None and v is not None) else g for g, v in zip(full, ins)]
+    io = dt_raw.dtype
+    f = torch.float32
+    return (full[0].to(io), None if full[1] is None else full[1].to(io), None if full[2] is None else full[2].to(io),
+            full[3].to(f), None if (full[4] is None or trap_raw is None) else full[4].to(f), None if full[5] is None else full[5].to(f))
+
+
 # ---- context-parallel exchange records (torch restatements of orbit_cp_state_pack / orbit_cp_state_combine) ----------
 def cp_pack(dA, record, n_state):
     record[n_state:n_state + dA.shape[0] * dA.shape[2] * dA.shape[3]] = dA.sum(1).reshape(-1).to(record.dtype)

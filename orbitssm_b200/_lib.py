@@ -65,6 +65,22 @@ class ClockArgs(C.Structure):
     ]
 
 
+class HmTailArgs(C.Structure):
+    """Mirror of ``orbit_hm_tail_args`` (include/orbit_b200.h); field order and types must match the header."""
+    _fields_ = [
+        ("M", C.c_int64), ("H", C.c_int), ("K", C.c_int), ("Krot", C.c_int),
+        ("dt_raw", C.c_void_p), ("dt_rs", C.c_int64), ("trap_raw", C.c_void_p), ("trap_rs", C.c_int64),
+        ("th_raw", C.c_void_p), ("th_rs", C.c_int64),
+        ("dt_bias", C.c_void_p), ("trap_bias", C.c_void_p), ("omega", C.c_void_p), ("rot_idx", C.c_void_p),
+        ("delta", C.c_void_p), ("lam", C.c_void_p), ("feat", C.c_void_p),
+        ("ddelta", C.c_void_p), ("dlam", C.c_void_p), ("dfeat", C.c_void_p),
+        ("d_dt_raw", C.c_void_p), ("d_dt_rs", C.c_int64), ("d_trap_raw", C.c_void_p), ("d_trap_rs", C.c_int64),
+        ("d_th_raw", C.c_void_p), ("d_th_rs", C.c_int64),
+        ("d_dt_bias", C.c_void_p), ("d_trap_bias", C.c_void_p), ("d_omega", C.c_void_p),
+        ("part", C.c_void_p), ("part_bytes", C.c_int64),
+    ]
+
+
 HM_CHUNK = 32     # checkpoint interval (tokens) the HybridMamba backward kernel is written for
 
 _P, _I, _L, _F = C.c_void_p, C.c_int, C.c_int64, C.c_float
@@ -92,6 +108,9 @@ SIGNATURES = {
     "orbit_token_clock_bwd": (_I, [C.POINTER(ClockArgs), _I, _P]),
     "orbit_hm_scan_fwd": (_I, [C.POINTER(HmArgs), _I, _P]),
     "orbit_hm_scan_bwd": (_I, [C.POINTER(HmArgs), _I, _P]),
+    "orbit_hm_tail_fwd": (_I, [C.POINTER(HmTailArgs), _I, _P]),
+    "orbit_hm_tail_bwd_workspace_bytes": (_L, [_L, _I, _I]),
+    "orbit_hm_tail_bwd": (_I, [C.POINTER(HmTailArgs), _I, _P]),
     "orbit_cp_record_floats": (_L, [_L, _I, _I]),
     "orbit_cp_state_pack_workspace_bytes": (_L, [_I, _I, _I]),
     "orbit_cp_state_pack": (_I, [_P, _P, _I, _I, _I, _L, _P, _L, _P]),

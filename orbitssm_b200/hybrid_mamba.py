@@ -188,37 +188,42 @@ class HybridMambaSSM(StateLifecycle, nn.Module):
             parts.append(parts[0].new_zeros(self._proj_pad, self.d_model))
         return torch.cat(parts, 0).to(dtype)
 
+    def _rot_idx32(self, device):
+        """Row-pair index of each rotating pair as int32 on `device` (what the clock-tail kernel scatters by)."""
+        t = getattr(self, "_rot_idx32_cache", None)
+        if t is None or t.device != device:
+            t = self.rot_pair_idx.to(device=device, dtype=torch.int32).contiguous()
+            self._rot_idx32_cache = t
+        return t
+
     def _maps(self, slab, io):
         """Scan operands from the slab columns (reference: hybrid_mamba.py:1695-1740, 1950-2013, 971-1011); fp32."""
         s = self.spec
         f = torch.float32
-        out, off = {}, 0
-        for key, m in self._slab:
-            w = m.weight.shape[0]
-            out[key] = slab[..., off:off + w]
-            off += w
+        keys = [key for key, _ in self._slab]
+        cols = ops.SplitColumnsFn.apply(slab, None, *[m.weight.shape[0] for _, m in self._slab])
+        out = dict(zip(keys, cols))
         dt_lin = out["dt"]
         if self.dt_low is not None:
             dt_lin = F.linear(dt_lin, self.dt_proj.weight.to(io))
-        delta = F.softplus(dt_lin.to(f) + self.dt_bias.to(f))
+        # clocks and angle feature in the clock-tail kernel (fp32 out); the rotation rate omega is a [Krot] parameter map
+        om = None
+        if s.has_rot:
+            om = (math.pi * torch.tanh(self.theta_freq.to(f)) if s.learn_theta_freq
+                  else torch.full((len(s.rot_pairs),), math.pi, dtype=f, device=slab.device))
+        delta, lam, feat = ops.HMTailFn.apply(dt_lin, out["trap"] if s.use_trap else None, out["theta"] if s.has_rot else None,
+                                              self.dt_bias, self.trap_proj.bias if s.use_trap else None, om,
+                                              self._rot_idx32(slab.device) if s.has_rot else None, s.K)
         # B / C maps: RMSNorm over the N state rows in the token-tail kernel (IO dtype out, like the drive)
         Braw, Craw = out["bc"][..., :s.N], out["bc"][..., s.N:]
         Bh = (ops.TokenMapFn.apply(Braw, self.b_norm.weight, None, 0.0, s.norm_eps, 1, s.N, None).squeeze(2)
               if self.b_norm is not None else Braw.to(f))
         Ch = (ops.TokenMapFn.apply(Craw, self.c_norm.weight, None, 0.0, s.norm_eps, 1, s.N, None).squeeze(2)
               if self.c_norm is not None else Craw.to(f))
-        feat = th_h = None
-        if s.has_rot:
-            q = out["theta"].to(f)
-            om = (math.pi * torch.tanh(self.theta_freq.to(f)) if s.learn_theta_freq
-                  else torch.full((len(s.rot_pairs),), math.pi, dtype=f, device=q.device))
-            feat = q.new_zeros(*q.shape[:-1], s.K).index_copy(-1, self.rot_pair_idx, om * torch.tanh(q))
-            if s.use_theta_h:
-                # the scan rotates the read map by Theta + offset with the offset in its own frame: -theta_h
-                th_h = q.new_zeros(s.H, s.K).index_copy(-1, self.rot_pair_idx, -self.theta_h.to(f))
-        lam = None
-        if s.use_trap:
-            lam = torch.sigmoid(out["trap"].to(f) + self.trap_proj.bias.to(f))
+        th_h = None
+        if s.has_rot and s.use_theta_h:
+            # the scan rotates the read map by Theta + offset with the offset in its own frame: -theta_h
+            th_h = delta.new_zeros(s.H, s.K).index_copy(-1, self.rot_pair_idx, -self.theta_h.to(f))
         return delta, Bh, Ch, feat, th_h, lam
 
     # -- forward --------------------------------------------------------------------------------------------------

@@ -982,6 +982,95 @@ class TokenClockFn(torch.autograd.Function):
 
 
 # ----------------------------------------------------------------------------------------------------
+#  HybridMamba clock tail (step size, trapezoid weight, angle feature)
+# ----------------------------------------------------------------------------------------------------
+def hm_tail_fwd(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K):
+    """Slab columns [B, L, .] (IO dtype, any uniform row stride) -> (delta [B, L, H], lam [B, L, H] | None,
+    feat [B, L, K] | None), fp32 (`orbit_hm_tail_fwd`)."""
+    _require_cuda("hm_tail_fwd", dt_raw, trap_raw, th_raw)
+    B, L, H = dt_raw.shape
+    f32 = dict(device=dt_raw.device, dtype=torch.float32)
+    delta = torch.empty((B, L, H), **f32)
+    lam = torch.empty((B, L, H), **f32) if trap_raw is not None else None
+    feat = torch.empty((B, L, K), **f32) if th_raw is not None else None
+    a = _lib.HmTailArgs()
+    a.M, a.H, a.K, a.Krot = B * L, H, K, (0 if th_raw is None else th_raw.shape[-1])
+    for key, rs, v in (("dt_raw", "dt_rs", dt_raw), ("trap_raw", "trap_rs", trap_raw), ("th_raw", "th_rs", th_raw)):
+        if v is not None:
+            setattr(a, rs, _row_view("hm_tail", v)[1])
+            setattr(a, key, v.data_ptr())
+    keep = [_f32(dt_bias), _f32(trap_bias), _f32(omega), rot_idx]
+    a.dt_bias, a.trap_bias, a.omega = _ptr(keep[0]), _ptr(keep[1]), _ptr(keep[2])
+    a.rot_idx = _ptr(rot_idx) if th_raw is not None else None
+    a.delta, a.lam, a.feat = _ptr(delta), _ptr(lam), _ptr(feat)
+    with _timed("hm_tail_fwd", 1 if B * L else 0):
+        _lib.check(_lib.load().orbit_hm_tail_fwd(C.byref(a), _dtype_code("hm_tail_fwd", dt_raw), _stream()), "orbit_hm_tail_fwd")
+    del keep
+    return delta, lam, feat
+
+
+def hm_tail_bwd(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K, lam, ddelta, dlam, dfeat):
+    """Returns (d dt_raw, d trap_raw | None, d th_raw | None) in the IO dtype and (d dt_bias, d trap_bias | None,
+    d omega | None) fp32 (`orbit_hm_tail_bwd`); a missing upstream gradient counts as zero."""
+    _require_cuda("hm_tail_bwd", dt_raw, trap_raw, th_raw)
+    B, L, H = dt_raw.shape
+    dev, io = dt_raw.device, dt_raw.dtype
+    f32 = dict(device=dev, dtype=torch.float32)
+    Krot = 0 if th_raw is None else th_raw.shape[-1]
+    d_dt = torch.empty((B, L, H), device=dev, dtype=io)
+    d_trap = torch.empty((B, L, H), device=dev, dtype=io) if trap_raw is not None else None
+    d_th = torch.empty((B, L, Krot), device=dev, dtype=io) if th_raw is not None else None
+    g_dtb = torch.empty((H,), **f32)
+    g_trb = torch.empty((H,), **f32) if trap_raw is not None else None
+    g_om = torch.empty((Krot,), **f32) if th_raw is not None else None
+    lib = _lib.load()
+    nbytes = int(lib.orbit_hm_tail_bwd_workspace_bytes(B * L, H, Krot))
+    ws = torch.empty((max(nbytes, 4),), device=dev, dtype=torch.uint8)
+    a = _lib.HmTailArgs()
+    a.M, a.H, a.K, a.Krot = B * L, H, K, Krot
+    for key, rs, v in (("dt_raw", "dt_rs", dt_raw), ("trap_raw", "trap_rs", trap_raw), ("th_raw", "th_rs", th_raw),
+                       ("d_dt_raw", "d_dt_rs", d_dt), ("d_trap_raw", "d_trap_rs", d_trap), ("d_th_raw", "d_th_rs", d_th)):
+        if v is not None:
+            setattr(a, rs, _row_view("hm_tail", v)[1])
+            setattr(a, key, v.data_ptr())
+    keep = [_f32(dt_bias), _f32(trap_bias), _f32(omega), rot_idx] + [None if g is None else _f32(g).contiguous() for g in (ddelta, dlam, dfeat)]
+    a.dt_bias, a.trap_bias, a.omega = _ptr(keep[0]), _ptr(keep[1]), _ptr(keep[2])
+    a.rot_idx = _ptr(rot_idx) if th_raw is not None else None
+    a.lam = _ptr(lam)
+    a.ddelta, a.dlam, a.dfeat = _ptr(keep[4]), _ptr(keep[5]), _ptr(keep[6])
+    a.d_dt_bias, a.d_trap_bias, a.d_omega = _ptr(g_dtb), _ptr(g_trb), _ptr(g_om)
+    a.part, a.part_bytes = _ptr(ws), nbytes
+    with _timed("hm_tail_bwd", 2 if B * L else 0):
+        _lib.check(lib.orbit_hm_tail_bwd(C.byref(a), _dtype_code("hm_tail_bwd", dt_raw), _stream()), "orbit_hm_tail_bwd")
+    del keep
+    return d_dt, d_trap, d_th, g_dtb, g_trb, g_om
+
+
+class HMTailFn(torch.autograd.Function):
+    """Clocks and angle feature of the HybridMamba scan as one node: (dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega)
+    -> (delta, lam, feat); reference: src/orbit_ssm/ssm/hybrid_mamba.py:1890-1931, 971-1000."""
+
+    @staticmethod
+    def forward(ctx, dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K):
+        delta, lam, feat = hm_tail_fwd(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K)
+        ctx.save_for_backward(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, lam)
+        ctx.K = K
+        ctx.set_materialize_grads(False)
+        return delta, lam, feat
+
+    @staticmethod
+    @first_order_only("HybridMamba clock tail")
+    def backward(ctx, ddelta, dlam, dfeat):
+        dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, lam = ctx.saved_tensors
+        d_dt, d_trap, d_th, g_dtb, g_trb, g_om = hm_tail_bwd(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, ctx.K,
+                                                             lam, ddelta, dlam, dfeat)
+
+        def like(g, p):
+            return None if (g is None or p is None) else g.to(p.dtype)
+        return (d_dt, d_trap, d_th, like(g_dtb, dt_bias), like(g_trb, trap_bias), like(g_om, omega), None, None)
+
+
+# ----------------------------------------------------------------------------------------------------
 #  HybridMamba coordinate-decay scan
 # ----------------------------------------------------------------------------------------------------
 def run_hm(a, name, backward, dtype_code):

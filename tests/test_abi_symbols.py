@@ -26,7 +26,8 @@ def test_every_declared_symbol_is_exported_and_bound():
 import pytest
 
 
-@pytest.mark.parametrize("struct,mirror", [("orbit_scan_args", "ScanArgs"), ("orbit_hm_args", "HmArgs"), ("orbit_clock_args", "ClockArgs")])
+@pytest.mark.parametrize("struct,mirror", [("orbit_scan_args", "ScanArgs"), ("orbit_hm_args", "HmArgs"), ("orbit_clock_args", "ClockArgs"),
+                                           ("orbit_hm_tail_args", "HmTailArgs")])
 def test_args_mirror_matches_header_field_order(struct, mirror):
     text = open(os.path.join(ROOT, "include", "orbit_b200.h")).read()
     body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (struct, struct), text, flags=re.S).group(1)

@@ -82,6 +82,37 @@ def test_conv_streaming_path(dtype, B, L, C, W, pad, fwd_win):
         assert rel(dwin, rwin) < tol(dtype, True) and torch.equal(dx3, dx) and torch.equal(dw3, dw)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,L,H,K,Krot,trap", [(2, 77, 32, 32, 16, True), (1, 5, 3, 4, 1, True), (3, 130, 8, 8, 8, False),
+                                               (2, 300, 40, 16, 0, True), (1, 1, 2, 1, 1, False)])
+def test_hm_tail(dtype, B, L, H, K, Krot, trap):
+    """HybridMamba clock tail (step size, trapezoid weight, angle feature scattered to its row pairs) and its backward
+    against the torch restatement; raw inputs are column slices of a wider buffer; parameter gradients reproducible."""
+    g = torch.Generator().manual_seed(11)
+    wide = (torch.randn(B, L, 2 * H + Krot + 6, generator=g) * 2.0).to(dtype).to(DEV)
+    dt_raw = wide[..., 2:2 + H]
+    trap_raw = wide[..., 2 + H:2 + 2 * H] if trap else None
+    th_raw = wide[..., 4 + 2 * H:4 + 2 * H + Krot] if Krot else None
+    dt_bias = torch.randn(H, generator=g).to(DEV)
+    trap_bias = torch.randn(H, generator=g).to(DEV) if trap else None
+    omega = (torch.randn(Krot, generator=g) * 2.0).to(DEV) if Krot else None
+    rot_idx = torch.randperm(K, generator=g)[:Krot].sort().values.to(torch.int32).to(DEV) if Krot else None
+    delta, lam, feat = ops.hm_tail_fwd(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K)
+    rd, rl, rf = R.hm_tail_fwd(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K)
+    assert rel(delta, rd) < 2e-6 and (lam is None or rel(lam, rl) < 2e-6) and (feat is None or rel(feat, rf) < 2e-6)
+    ddelta = torch.randn(B, L, H, generator=g).to(DEV)
+    dlam = torch.randn(B, L, H, generator=g).to(DEV) if trap else None
+    dfeat = torch.randn(B, L, K, generator=g).to(DEV) if Krot else None
+    got = ops.hm_tail_bwd(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K, lam, ddelta, dlam, dfeat)
+    want = R.hm_tail_bwd(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K, lam, ddelta, dlam, dfeat)
+    for i, (a_, b_) in enumerate(zip(got, want)):
+        assert (a_ is None) == (b_ is None), i
+        if a_ is not None:
+            assert rel(a_, b_) < (tol(dtype, True) if i < 3 else 2e-5), (i, rel(a_, b_))
+    again = ops.hm_tail_bwd(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K, lam, ddelta, dlam, dfeat)
+    assert all(a_ is None or torch.equal(a_, b_) for a_, b_ in zip(got, again))
+
+
 def test_cp_state_pack_and_combine():
     """The exchange-step kernels of context parallelism against their torch restatements: the segment's summed log-decay
     (two-stage, fixed order: bitwise reproducible) and the combination of W gathered records, both directions."""

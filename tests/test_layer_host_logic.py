@@ -167,7 +167,8 @@ from orbitssm_b200.hybrid_mamba import HybridMambaSSM                   # noqa: 
 
 @pytest.fixture
 def cpu_hm_kernels(monkeypatch):
-    for name in ("conv1d_fwd", "conv1d_bwd", "gate_norm_fwd", "gate_norm_bwd", "run_hm", "token_map_fwd", "token_map_bwd"):
+    for name in ("conv1d_fwd", "conv1d_bwd", "gate_norm_fwd", "gate_norm_bwd", "run_hm", "token_map_fwd", "token_map_bwd",
+                 "hm_tail_fwd", "hm_tail_bwd"):
         monkeypatch.setattr(ops, name, getattr(R, name))
     monkeypatch.setattr(ops, "on_device", lambda t: True)
     monkeypatch.setattr(ops, "_require_cuda", lambda who, *t: None)
