@@ -182,6 +182,12 @@ int orbit_ssd_scan_fwd(const orbit_scan_args* a, const float* S0, float* S_fin, 
 int orbit_ssd_scan_bwd(const orbit_scan_args* a, const float* dS_fin, float* dS0, int dtype, int precision,
                        void* stream);
 
+/* One token (decode): the scan at L = 1 in one launch, any geometry the argument block can state; inference only.
+ * Replaces the reference's `_step_core` inside `ssd_step` / `mixer_step_fast` (src/orbit_ssm/ssm/ssd_mimo_torch.py:388-490).
+ * Reads u, the maps, clocks, chi, Dg of the block (all for the one token; a->L must be 1) and S0 [B, H, R, N, G] (NULL = zero);
+ * writes a->y and the state after the token S1 (may alias S0: every element is read before it is written by its own thread). */
+int orbit_ssd_scan_step(const orbit_scan_args* a, const float* S0, float* S1, int dtype, void* stream);
+
 /* ---- token tails of the SSD-MIMO layer -------------------------------------------------------------------------
  * Replace the reference's `token_law` (src/orbit_ssm/ssm/ssd_mimo_torch.py:161-267; fused CUDA form `token_tails`,
  * src/orbit_ssm/layers/tails.py:829).  Slab columns are read in place (row strides in elements); gradients are written

@@ -454,6 +454,16 @@ def run_clock(a, name, backward, dtype_code, compute=torch.float64):
         t["g_alog"].copy_(_f(t["ddA"], compute) * out["dA"].detach())
 
 
+def run_step(a, S0, S_fin, dtype_code, compute=torch.float64):
+    """Restatement of orbit_ssd_scan_step: the forward scan on the one token."""
+    t = a.t
+    geo = t["geo"]
+    y, S, _, _ = scan_fwd(geo, 1, 0, t["u"], t["Bhat"], t["gBp"], t["Chat"], t["gCp"], t["beta"], t["gamma"], t["chi"], t["dA"],
+                          t["w"], t["wd"], t["Dg"], S0, compute=compute)
+    t["y"].copy_(y.to(t["y"].dtype))
+    S_fin.copy_(S.to(S_fin.dtype))
+
+
 # ---- HybridMamba clock tail (torch restatement of orbit_hm_tail_fwd / orbit_hm_tail_bwd) ---------------------------------
 def _hm_tail(dt_raw, trap_raw, th_raw, dt_bias, trap_bias, omega, rot_idx, K, compute):
     delta = torch.nn.functional.softplus(dt_raw.to(compute) + dt_bias.to(compute))

@@ -101,6 +101,7 @@ SIGNATURES = {
     "orbit_ssd_scan_phase": (_I, [C.POINTER(ScanArgs), _I, _P, _P, _I, _I, _P]),
     "orbit_ssd_scan_fwd": (_I, [C.POINTER(ScanArgs), _P, _P, _I, _I, _P]),
     "orbit_ssd_scan_bwd": (_I, [C.POINTER(ScanArgs), _P, _P, _I, _I, _P]),
+    "orbit_ssd_scan_step": (_I, [C.POINTER(ScanArgs), _P, _P, _I, _P]),
     "orbit_token_map_fwd": (_I, [_P, _L, _P, _P, _F, _F, _P, _P, _L, _I, _I, _I, _P]),
     "orbit_token_map_bwd_workspace_bytes": (_L, [_I]),
     "orbit_token_map_bwd": (_I, [_P, _L, _P, _P, _P, _P, _L, _P, _P, _P, _L, _L, _I, _I, _I, _P]),

@@ -468,6 +468,8 @@ def pick_chunk(geo: ScanGeometry, precision: int, backward: bool, limit: int) ->
 
 def _tok_stride(who, t, inner):
     """Token stride (elements) of a [B, L, X, N] map whose [X, N] block is contiguous and whose batch stride is L * token stride."""
+    if t.dim() == 4 and t.shape[1] == 1 and (t.shape[3] == 1 or t.stride(3) == 1) and (t.shape[2] == 1 or t.stride(2) == t.shape[3]):
+        return t.stride(0)                    # one token per batch row: the kernels' (b * L + t) * stride is b * batch stride
     ok = (t.dim() == 4 and (t.shape[3] == 1 or t.stride(3) == 1) and (t.shape[2] == 1 or t.stride(2) == t.shape[3])
           and (t.shape[0] == 1 or t.stride(0) == t.shape[1] * t.stride(1)))
     if not ok:
@@ -761,6 +763,33 @@ def scan_bwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w
     out["dDg"] = pd.sum(0) if pd is not None else None
     out["dS0"] = dS0
     return out
+
+
+def scan_step(geo, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0):
+    """One token of the scan in one launch (`orbit_ssd_scan_step`; inference only): operands as `scan_fwd` with L = 1.
+    Returns (y [B, 1, H*G*O], S_fin [B, H, R, N, G] fp32)."""
+    _require_cuda("ssd_scan_step", u, Bhat, Chat, dA)
+    B, L = u.shape[:2]
+    if L != 1:
+        raise ValueError(f"ssd_scan_step: one token per call, got L={L}")
+    H, R, O, G, N = geo.H, geo.R, geo.O, geo.G, geo.N
+    a = _lib.ScanArgs()
+    a.B, a.L, a.H, a.R, a.O, a.G, a.N, a.T, a.nc = B, 1, H, R, O, G, N, 1, 1
+    u = u.contiguous()
+    y = torch.empty((B, 1, H * G * O), device=u.device, dtype=u.dtype)
+    S_fin = torch.empty((B, H, R, N, G), device=u.device, dtype=torch.float32)
+    keep = _fill_common(a, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg)
+    a.y = y.data_ptr() if y.is_cuda else None
+    a.t = dict(geo=geo, u=u, Bhat=Bhat, gBp=gBp, Chat=Chat, gCp=gCp, beta=beta, gamma=gamma, chi=chi, dA=dA, w=w, wd=wd, Dg=Dg, y=y)
+    run_step(a, S0, S_fin, _dtype_code("ssd_scan_step", u))
+    del keep
+    return y, S_fin
+
+
+def run_step(a, S0, S_fin, dtype_code):
+    """The one-token scan launch through the C-ABI (`a.t`: the tensors behind the pointers, for the CPU host-logic tests)."""
+    with _timed("scan_step", 1):
+        _lib.check(_lib.load().orbit_ssd_scan_step(C.byref(a), _ptr(S0), _ptr(S_fin), dtype_code, _stream()), "orbit_ssd_scan_step")
 
 
 class SSDScanFn(torch.autograd.Function):

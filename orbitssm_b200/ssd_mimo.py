@@ -411,10 +411,17 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
                             * law["lag0"][..., None, None]
                     S0 = S0.contiguous()
                 geo = ops.ScanGeometry(H=H, R=R, O=O, G=G, N=N)
-                precision, T = self._route(io, geo, torch.is_grad_enabled())
-                y, S_fin = ops.SSDScanFn.apply(geo, T, precision, not s.use_trap, u, law["Bhat"], law["gBp"], law["Chat"],
-                                               law["gCp"], law["beta"], law["gamma"], law["chi"], law["dA"], law["w"],
-                                               law["wd"], law["Dg"], S0, cp)
+                if L == 1 and cp is None and not torch.is_grad_enabled():
+                    # decode: the one-token law in one launch (no chunk tiles, no state pass)
+                    self._route_note = "step"
+                    y, S_fin = ops.scan_step(geo, u, law["Bhat"], law["gBp"], law["Chat"], law["gCp"], law["beta"], law["gamma"],
+                                             law["chi"], law["dA"], law["w"], law["w"] if not s.use_trap else law["wd"],
+                                             law["Dg"], S0)
+                else:
+                    precision, T = self._route(io, geo, torch.is_grad_enabled())
+                    y, S_fin = ops.SSDScanFn.apply(geo, T, precision, not s.use_trap, u, law["Bhat"], law["gBp"], law["Chat"],
+                                                   law["gCp"], law["beta"], law["gamma"], law["chi"], law["dA"], law["w"],
+                                                   law["wd"], law["Dg"], S0, cp)
                 hidden = S_fin.permute(0, 1, 4, 2, 3).reshape(Bsz, H, P, N)
                 v_last = None
                 if want_state and s.use_trap:
@@ -473,9 +480,10 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
 
     def step(self, x_t, state=None):
         """One token: ``x_t [B, d_model]``, ``state`` from `init_state` or a previous call -> ``(y_t [B, d_model], State)``
-        (reference: ssd_mimo.py:4629).  Runs the layer on a length-1 sequence: the same kernels and the same carry contract as
-        `forward`, so a sequence stepped token by token equals the sequence run at once; there is no separate decode
-        kernel (a step costs the layer's launch count)."""
+        (reference: ssd_mimo.py:4629, ssd_mimo_torch.py:388-490).  Runs the layer on a length-1 sequence with the same carry
+        contract as `forward`, so a sequence stepped token by token equals the sequence run at once.  Under
+        ``torch.no_grad()`` (decoding) the scan of the token is the one-launch step kernel; with gradients enabled it is the
+        chunked scan on a one-token chunk."""
         if x_t.dim() != 2 or x_t.shape[-1] != self.d_model:
             raise ValueError(f"SSDMimoSSM.step: expected x_t of shape [B, {self.d_model}], got {tuple(x_t.shape)}")
         if state is None:

@@ -252,6 +252,39 @@ def test_scan_ieee(dtype, case):
             assert torch.equal(v, g2[k]), ("not reproducible", k)
 
 
+STEP_CASES = [
+    # B, H, R, O, G, N, gates, biases, chi, skip, trap, s0
+    (2, 3, 1, 1, 64, 128, False, False, False, True, False, True),      # SISO preset head
+    (3, 64, 1, 1, 64, 128, False, False, False, True, False, True),
+    (2, 4, 4, 4, 16, 128, True, True, True, True, True, True),          # rank-4 head
+    (2, 3, 2, 1, 3, 8, False, False, False, True, False, False),
+    (1, 2, 2, 3, 4, 8, True, True, True, False, True, True),
+    (5, 2, 1, 1, 300, 16, False, False, False, True, False, True),      # more (g, o) pairs than threads
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", STEP_CASES)
+def test_scan_step(case, dtype):
+    """The one-launch decode step against the fp64 restatement of the scan on the one token (output and state after
+    it), and against the chunked scan kernels at L = 1, which it must reproduce to fp32 rounding."""
+    B, H, Rk, O, G, N, gates, biases, chi, skip, trap, s0 = case
+    c = scan_case(B, 1, H, Rk, O, G, N, dtype, gates, biases, chi, skip, trap, s0, seed=13)
+    geo = c["geo"]
+    args = (c["u"], c["Bhat"], c["gBp"], c["Chat"], c["gCp"], c["beta"], c["gamma"], c["chi"], c["dA"], c["w"],
+            c["w"] if c["euler"] else c["wd"], c["Dg"])
+    y, S = ops.scan_step(geo, *args, c["S0"])
+    ry, rS, _, _ = R.scan_fwd(geo, 1, 0, *args, c["S0"])
+    assert rel(S, rS) < 2e-6, ("S", rel(S, rS))
+    assert rel(y, ry) < (6e-3 if dtype == torch.bfloat16 else 2e-5), ("y", rel(y, ry))
+    T = ops.pick_chunk(geo, _lib.PRECISION_IEEE, False, 64)
+    if T > 0:
+        y2, S2, _, _ = ops.scan_fwd(geo, T, _lib.PRECISION_IEEE, *args, c["S0"])
+        assert rel(S, S2) < 2e-6 and rel(y, y2) < (6e-3 if dtype == torch.bfloat16 else 2e-6)
+    y3, S3 = ops.scan_step(geo, *args, c["S0"])
+    assert torch.equal(y, y3) and torch.equal(S, S3)
+
+
 @pytest.mark.parametrize("T", [8, 16, 32, 64])
 def test_scan_chunk_length_is_scheduling_only(T):
     c = scan_case(2, 100, 2, 1, 1, 16, 32, torch.float32, False, False, False, True, True, True, seed=3)

@@ -212,3 +212,26 @@ def test_block_stack_norms_match_aten(io, monkeypatch):
     tol = 1e-4 if io == torch.float32 else 3e-2
     for g, w, what in zip(got, want, ("y", "dx", "d norm_f.weight", "d layers[0].norm.weight")):
         assert rel(g, w) < tol, (what, rel(g, w))
+
+
+@pytest.mark.parametrize("name,io", [("dyn_trap_conv", torch.float32), ("cfg2_small", torch.float32), ("cfg2_small", torch.bfloat16),
+                                     ("cfg3_small", torch.bfloat16)])
+def test_step_equals_forward_on_device(name, io):
+    """Decoding: `step` under no_grad (the one-launch step kernel for the scan of the token) token by token from a carried
+    State equals `forward` on the same tokens, for the output and every carry (reference contract:
+    src/orbit_ssm/ssm/ssd_mimo_torch.py:388-490)."""
+    rec = load_golden(name)
+    layer = build(rec, "ieee" if io == torch.float32 else "io")
+    x = rec["x"][:, :12].to(DEV).to(io)
+    with torch.no_grad():
+        y_all, s_all = layer(x, return_state=True)
+        y_head, st = layer(x[:, :7], return_state=True)
+        ys = [y_head]
+        for t in range(7, 12):
+            y_t, st = layer.step(x[:, t], st)
+            assert layer.last_route() == "step"
+            ys.append(y_t.unsqueeze(1))
+    ty = 1e-5 if io == torch.float32 else 2.5e-2
+    assert rel(torch.cat(ys, 1), y_all) < ty, rel(torch.cat(ys, 1), y_all)
+    for k in s_all:
+        assert rel(st[k], s_all[k]) < ty, (k, rel(st[k], s_all[k]))

@@ -15,7 +15,7 @@ from oracle import abi_reference as R
 def cpu_kernels(monkeypatch):
     # the scan goes through the product's own phase sequencing (ops.scan_fwd / scan_bwd); only the C-ABI call is replaced
     for name in ("conv1d_fwd", "conv1d_bwd", "gate_norm_fwd", "gate_norm_bwd", "run_phase", "pick_chunk", "token_map_fwd",
-                 "token_map_bwd", "run_clock"):
+                 "token_map_bwd", "run_clock", "run_step"):
         monkeypatch.setattr(ops, name, getattr(R, name))
     monkeypatch.setattr(ops, "on_device", lambda t: True)
     monkeypatch.setattr(ops, "_require_cuda", lambda who, *t: None)
