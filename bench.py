@@ -69,7 +69,7 @@ WORKLOADS = {
 # cfg3s / cfg4s, divided by their token counts).  Traffic grows in proportion to the tokens a launch processes, so
 # `roofline.traffic` of a full-size launch is this figure times its tokens.
 DRAM_BYTES_PER_TOKEN = {
-    "m2": {"scan_chunk_grads": 68451.0, "scan_chunk_out": 23852.0, "scan_chunk_state": 22452.0},
+    "m2": {"scan_chunk_grads": 69695.0, "scan_chunk_out": 24008.0, "scan_chunk_state": 22630.0},
     "mimo4": {"scan_chunk_grads": 416550.0},
     "hm": {"hm_scan_bwd": 41920.0, "hm_scan_fwd": 13610.0},
 }

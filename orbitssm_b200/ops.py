@@ -576,6 +576,49 @@ class HaloFn(torch.autograd.Function):
         return recv, None, None
 
 
+class LagHaloFn(torch.autograd.Function):
+    """Trapezoid write across a context-parallel cut.  The scan works on one-tap weights w_t = wd_t + lag_{t+1}: the lagged
+    half of token t + 1's write, lag_{t+1} = dt_{t+1} (1 - lam_{t+1}), multiplies the write of token t (reference:
+    src/orbit_ssm/ssm/ssd_mimo_torch.py:769-788).  For the last token of a segment, t + 1 is the first token of the NEXT
+    rank: every rank sends the lag of its first token [B, H, R] to its predecessor and gets its successor's (zeros on the
+    last rank).  Backward returns the gradient to its owner the other way."""
+
+    @staticmethod
+    def forward(ctx, lag0, cp):
+        ctx.cp = cp
+        dist = cp.dist
+        lag0 = lag0.contiguous()
+        recv = torch.zeros_like(lag0)
+        peer = (lambda r: dist.get_global_rank(cp.group, r) if cp.group else r)
+        reqs = []
+        if cp.rank > 0:
+            reqs.append(dist.P2POp(dist.isend, lag0, peer(cp.rank - 1), group=cp.group))
+        if cp.rank + 1 < cp.world:
+            reqs.append(dist.P2POp(dist.irecv, recv, peer(cp.rank + 1), group=cp.group))
+        if reqs:
+            for r in dist.batch_isend_irecv(reqs):
+                r.wait()
+        return recv
+
+    @staticmethod
+    @first_order_only("context-parallel trapezoid lag")
+    def backward(ctx, dnext):
+        cp = ctx.cp
+        dist = cp.dist
+        send = dnext.contiguous()                      # gradient of the successor's lag, computed here
+        recv = torch.zeros_like(send)                  # gradient of this rank's own lag, computed by the predecessor
+        peer = (lambda r: dist.get_global_rank(cp.group, r) if cp.group else r)
+        reqs = []
+        if cp.rank + 1 < cp.world:
+            reqs.append(dist.P2POp(dist.isend, send, peer(cp.rank + 1), group=cp.group))
+        if cp.rank > 0:
+            reqs.append(dist.P2POp(dist.irecv, recv, peer(cp.rank - 1), group=cp.group))
+        if reqs:
+            for r in dist.batch_isend_irecv(reqs):
+                r.wait()
+        return recv, None
+
+
 def scan_fwd(geo, T, precision, u, Bhat, gBp, Chat, gCp, beta, gamma, chi, dA, w, wd, Dg, S0, cp=None):
     """Forward scan.  Returns (y [B, L, H*G*O], S_fin [B, H, R, N, G] fp32, Sin, atot); with the tensor-core precision
     `Sin` is the pair (None, Sin16): the backward of the rank-1 tiles reads the bfloat16 state tiles only (the fp32 buffer holds

@@ -345,9 +345,6 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         H, G, R, O, N, P = s.H, s.G, s.R, s.O, s.N, s.P
         cp = self._cp if (self._cp is not None and self._cp.world > 1) else None
         if cp is not None:
-            if s.use_trap:
-                raise NotImplementedError("SSDMimoSSM: context parallelism serves write_rule='euler' (the two-endpoint "
-                                          "write needs the neighbour's lag term)")
             if L < max(s.d_conv, 1):
                 raise ValueError(f"SSDMimoSSM: a context-parallel segment needs at least d_conv={s.d_conv} tokens")
         if state is not None:
@@ -397,12 +394,20 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
 
             h0 = state["hidden_state"] if state is not None else None
             wp = state.get("write_prev") if state is not None else None
+            if cp is not None and cp.rank > 0:
+                h0 = wp = None            # an initial State belongs to the whole sequence: only rank 0 reads it
             if L == 0:
                 y = u.new_zeros(Bsz, 0, self.d_out)
                 hidden = h0.to(torch.float32) if h0 is not None else u.new_zeros(Bsz, H, P, N, dtype=torch.float32)
                 v_last = wp.to(torch.float32) if wp is not None else torch.zeros_like(hidden)
             else:
                 law = self._token_law(parts, b_src, c_src, io, arena, slot_of)
+                if cp is not None and s.use_trap:
+                    # two-endpoint write across the cut: the lagged half of the next segment's first write rides on this
+                    # segment's last token (its own lag0 goes to the previous rank the same way)
+                    nxt = ops.LagHaloFn.apply(law["lag0"], cp)
+                    last = torch.tensor([L - 1], device=nxt.device)
+                    law["w"] = law["w"].index_add(1, last, nxt.unsqueeze(1))
                 S0 = None
                 if h0 is not None:
                     S0 = h0.to(torch.float32).reshape(Bsz, H, G, R, N).permute(0, 1, 3, 4, 2)

@@ -13,7 +13,7 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, out, cont=False):
+def _worker(rank, world, port, out, cont=False, fixture="cfg2_small"):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
@@ -31,12 +31,12 @@ def _worker(rank, world, port, out, cont=False):
         ops._require_cuda = lambda who, *t: None
         ops._dtype_code = lambda who, t: 0
         torch.set_num_threads(2)
-        rec = load_golden("cfg2_small")
+        rec = load_golden(fixture)
         layer = SSDMimoSSM(SSDMimoConfig(**rec["config"]))
         layer.load_state_dict(rec["state_dict"])
         layer.set_context_parallel("world")
         L = rec["x"].shape[1]
-        cuts = [0, 41, L] if world == 2 else [0, 30, 61, L]
+        cuts = [0, 41 * L // 96, L] if world == 2 else [0, 30 * L // 96, 61 * L // 96, L]
         state, want, xs, dys = None, rec["f64"], rec["x"], rec["dy"]
         if cont:
             # the continuation fixture: the sequence after the cut, started from the reference's carried State.  The State
@@ -46,13 +46,15 @@ def _worker(rank, world, port, out, cont=False):
             xs, dys, want = rec["x"][:, s0:], rec["dy"][:, s0:], c
             state = {k: v.clone().float().requires_grad_(rank == 0) for k, v in c["state_in"].items()}
             L = xs.shape[1]
-            cuts = [0, 23, L] if world == 2 else [0, 17, 38, L]
+            cuts = [0, (2 * L) // 5, L] if world == 2 else [0, L // 3, (2 * L) // 3, L]
         a, b = cuts[rank], cuts[rank + 1]
         x = xs[:, a:b].clone().requires_grad_(True)
         y, st = layer(x, state=state, return_state=True)
         loss = (y * dys[:, a:b]).sum()
         if rank == world - 1:
             loss = loss + (st["hidden_state"] * rec["gh"]).sum()
+            if "write_prev" in st:
+                loss = loss + (st["write_prev"] * rec["gw"]).sum()
         loss.backward()
 
         def rel(p, q):
@@ -61,10 +63,13 @@ def _worker(rank, world, port, out, cont=False):
 
         errs = {"y": rel(y, want["y"][:, a:b]), "dx": rel(x.grad, want["grads"]["x"][:, a:b])}
         if rank == world - 1:
-            errs["hidden"] = rel(st["hidden_state"], want["state"]["hidden_state"])
+            for k, v in want["state"].items():
+                if k in ("hidden_state", "write_prev"):
+                    errs[k] = rel(st[k], v)
         if cont and rank == 0:
             for k, v in state.items():
-                errs["dstate." + k] = rel(v.grad, want["grads"]["state." + k])
+                if v.grad is not None or ("state." + k) in want["grads"]:
+                    errs["dstate." + k] = rel(v.grad, want["grads"]["state." + k])
         for n, p in layer.named_parameters():
             g = p.grad.clone()
             dist.all_reduce(g)                                   # parameter gradients add over the segments
@@ -74,12 +79,15 @@ def _worker(rank, world, port, out, cont=False):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,cont", [(2, False), (3, False), (2, True), (3, True)])
-def test_two_segments_equal_the_whole_sequence(world, cont):
-    port = 29500 + (os.getpid() % 2000) + world + 10 * int(cont)
+@pytest.mark.parametrize("world,cont,fixture", [(2, False, "cfg2_small"), (3, False, "cfg2_small"), (2, True, "cfg2_small"),
+                                                (3, True, "cfg2_small"), (2, False, "dyn_trap_conv"), (3, True, "dyn_trap_conv")])
+def test_two_segments_equal_the_whole_sequence(world, cont, fixture):
+    """Euler write (config-2 geometry) and the two-endpoint trapezoid write (whose lag term crosses the cut), from a zero
+    state and continued from a carried State."""
+    port = 29500 + (os.getpid() % 2000) + world + 10 * int(cont) + 20 * int(fixture != "cfg2_small")
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(world, port, out, cont), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, out, cont, fixture), nprocs=world, join=True)
     for rank in range(world):
         bad = {k: e for k, e in out[rank].items() if not e < 2e-4}
         assert not bad, (rank, bad)

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, io_name, out):
+def _worker(rank, world, port, io_name, out, fixture="cfg2_small"):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
@@ -25,18 +25,21 @@ def _worker(rank, world, port, io_name, out):
         from orbitssm_b200.config import SSDMimoConfig
         from orbitssm_b200.ssd_mimo import SSDMimoSSM
         io = getattr(torch, io_name)
-        rec = load_golden("cfg2_small")
+        rec = load_golden(fixture)
         layer = SSDMimoSSM(SSDMimoConfig(**rec["config"]), execution={"precision": "ieee" if io == torch.float32 else "io"})
         layer.load_state_dict(rec["state_dict"])
         layer = layer.to("cuda")
         layer.set_context_parallel("world")
         L = rec["x"].shape[1]
-        a, b = (0, 41) if rank == 0 else (41, L)
+        cut = (41 * L) // 96
+        a, b = (0, cut) if rank == 0 else (cut, L)
         x = rec["x"][:, a:b].to("cuda").to(io).requires_grad_(True)
         y, st = layer(x, return_state=True)
         loss = (y.float() * rec["dy"][:, a:b].to("cuda")).sum()
         if rank == world - 1:
             loss = loss + (st["hidden_state"] * rec["gh"].to("cuda")).sum()
+            if "write_prev" in st:
+                loss = loss + (st["write_prev"] * rec["gw"].to("cuda")).sum()
         loss.backward()
         want = rec["f64"]
 
@@ -47,6 +50,8 @@ def _worker(rank, world, port, io_name, out):
         errs = {"y": rel(y, want["y"][:, a:b]), "dx": rel(x.grad, want["grads"]["x"][:, a:b])}
         if rank == world - 1:
             errs["hidden"] = rel(st["hidden_state"], want["state"]["hidden_state"])
+            if "write_prev" in st:
+                errs["hidden.write_prev"] = rel(st["write_prev"], want["state"]["write_prev"])
         for n, p in layer.named_parameters():
             g = p.grad.clone()
             dist.all_reduce(g)
@@ -56,13 +61,16 @@ def _worker(rank, world, port, io_name, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("io_name", ["float32", "bfloat16"])
-def test_two_gpus_equal_the_whole_sequence(io_name):
+@pytest.mark.parametrize("io_name,fixture", [("float32", "cfg2_small"), ("bfloat16", "cfg2_small"), ("float32", "dyn_trap_conv"),
+                                             ("bfloat16", "cfg3_small")])
+def test_two_gpus_equal_the_whole_sequence(io_name, fixture):
+    """Euler write at config-2 geometry, and the two-endpoint trapezoid write (its lag term crosses the cut): the fp32
+    kernels on a small dynamic-decay layer and the rank-4 tensor-core tiles at config-3 geometry."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     out = mp.Manager().dict()
-    mp.spawn(_worker, args=(2, 29650 + (os.getpid() % 300), io_name, out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, 29650 + (os.getpid() % 300), io_name, out, fixture), nprocs=2, join=True)
     ty, tg = (2e-4, 5e-3) if io_name == "float32" else (2.5e-2, 6e-2)
     for rank in range(2):
-        bad = {k: e for k, e in out[rank].items() if not e < (ty if k in ("y", "hidden") else tg)}
+        bad = {k: e for k, e in out[rank].items() if not e < (ty if k in ("y", "hidden", "hidden.write_prev") else tg)}
         assert not bad, (rank, bad, dict(out[rank]))
