@@ -14,139 +14,195 @@ namespace orbit {
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_MAXV = 4;   // 16-byte vectors per thread kept in registers
 
-template <typename T, int NV>
+
+// Sums of ROWS values over the CTA with ONE barrier: warp sums go to red[r][warp], then every thread adds the 8 warp sums
+// of each value in order.  `red` must not be rewritten before every thread has read it: callers alternate two buffers.
+template <int ROWS>
+__device__ __forceinline__ void block_sum_rows(float (&v)[ROWS], float (*red)[NORM_THREADS / 32]) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    v[r] = warp_sum(v[r]);
+    if (lane == 0) red[r][wid] = v[r];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    float t = red[r][0];
+#pragma unroll
+    for (int w = 1; w < NORM_THREADS / 32; ++w) t += red[r][w];
+    v[r] = t;
+  }
+}
+
+// Forward: a CTA owns ROWS consecutive rows (narrow rows are grouped so that a thread has several 16-byte loads in
+// flight and the one barrier serves all of them); every load is issued before the first use.
+template <typename T, int NV, int ROWS, bool GATED>
 __global__ void __launch_bounds__(NORM_THREADS) gate_norm_fwd_kernel(const T* __restrict__ y,
                                                                      const T* __restrict__ z, int64_t zrs,
                                                                      const float* __restrict__ w, T* __restrict__ out,
-                                                                     float* __restrict__ rstd_out, int D, float eps) {
+                                                                     float* __restrict__ rstd_out, int64_t M, int D, float eps) {
   constexpr int V = Vec16<T>::N;
-  __shared__ float red[32];
-  const int64_t row = blockIdx.x;
-  float g[NV][V];
-  float ss = 0.f;
+  __shared__ float red[ROWS][NORM_THREADS / 32];
+  const int64_t row0 = (int64_t)blockIdx.x * ROWS;
+  Vec16<T> ra[ROWS][NV], rb[ROWS][NV];
 #pragma unroll
-  for (int k = 0; k < NV; ++k) {
-    int c = (k * NORM_THREADS + threadIdx.x) * V;
-    if (c < D) {
-      Vec16<T> a;
-      a.load(y + row * D + c);
-      if (z != nullptr) {
-        Vec16<T> b;
-        b.load(z + row * zrs + c);
+  for (int r = 0; r < ROWS; ++r)
 #pragma unroll
-        for (int i = 0; i < V; ++i) g[k][i] = a.get(i) * silu_t<T>(b.get(i));
-      } else {
-#pragma unroll
-        for (int i = 0; i < V; ++i) g[k][i] = a.get(i);
+    for (int k = 0; k < NV; ++k) {
+      const int c = (k * NORM_THREADS + threadIdx.x) * V;
+      if (c < D && row0 + r < M) {
+        ra[r][k].load(y + (row0 + r) * D + c);
+        if (GATED) rb[r][k].load(z + (row0 + r) * zrs + c);
       }
+    }
+  float g[ROWS][NV][V], ss[ROWS];
 #pragma unroll
-      for (int i = 0; i < V; ++i) ss = fmaf(g[k][i], g[k][i], ss);
+  for (int r = 0; r < ROWS; ++r) {
+    ss[r] = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c = (k * NORM_THREADS + threadIdx.x) * V;
+      if (c < D && row0 + r < M) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          g[r][k][i] = GATED ? ra[r][k].get(i) * silu_t<T>(rb[r][k].get(i)) : ra[r][k].get(i);
+          ss[r] = fmaf(g[r][k][i], g[r][k][i], ss[r]);
+        }
+      }
     }
   }
-  float rstd = 1.f;
+  float rstd[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) rstd[r] = 1.f;
   if (w != nullptr) {
-    ss = block_sum(ss, red);
-    rstd = rsqrtf(ss / (float)D + eps);
-    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+    block_sum_rows<ROWS>(ss, red);
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      rstd[r] = rsqrtf(ss[r] / (float)D + eps);
+      if (threadIdx.x == 0 && rstd_out && row0 + r < M) rstd_out[row0 + r] = rstd[r];
+    }
   }
 #pragma unroll
   for (int k = 0; k < NV; ++k) {
-    int c = (k * NORM_THREADS + threadIdx.x) * V;
+    const int c = (k * NORM_THREADS + threadIdx.x) * V;
     if (c < D) {
-      Vec16<T> o;
+      float wv[V];
 #pragma unroll
-      for (int i = 0; i < V; ++i) o.set(i, w ? g[k][i] * rstd * w[c + i] : g[k][i]);
-      o.store(out + row * D + c);
+      for (int i = 0; i < V; ++i) wv[i] = w ? w[c + i] : 1.f;
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        if (row0 + r < M) {
+          Vec16<T> o;
+#pragma unroll
+          for (int i = 0; i < V; ++i) o.set(i, w ? g[r][k][i] * rstd[r] * wv[i] : g[r][k][i]);
+          o.store(out + (row0 + r) * D + c);
+        }
+      }
     }
   }
 }
 
-// Backward: each CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; dw partial sums stay in registers and go to
-// `part` [gridDim.x, D] (fixed-order second stage below -> deterministic).
+// Backward: each CTA walks groups of ROWS rows (group blockIdx.x, blockIdx.x + gridDim.x, ...); dw partial sums stay in
+// registers and go to `part` [gridDim.x, D] (fixed-order second stage below -> deterministic).
 //   xh = g*rstd, u = dout*w, m = mean(xh*u), dg = rstd*(u - xh*m), dy = dg*silu(z), dz = dg*y*silu'(z)
-template <typename T, int NV>
-__global__ void __launch_bounds__(NORM_THREADS) gate_norm_bwd_kernel(
+template <typename T, int NV, int ROWS, bool GATED>
+__global__ void __launch_bounds__(NORM_THREADS, (GATED && NV == 4) ? 1 : 2) gate_norm_bwd_kernel(
     const T* __restrict__ y, const T* __restrict__ z, int64_t zrs, const float* __restrict__ w,
     const float* __restrict__ rstd_in, const T* __restrict__ dout, T* __restrict__ dy, T* __restrict__ dz,
     int64_t dzrs, float* __restrict__ part, int64_t M, int D) {
   constexpr int V = Vec16<T>::N;
-  __shared__ float red[32];
+  __shared__ float red[2][ROWS][NORM_THREADS / 32];
   float dwacc[NV][V];
 #pragma unroll
   for (int k = 0; k < NV; ++k)
 #pragma unroll
     for (int i = 0; i < V; ++i) dwacc[k][i] = 0.f;
-  // The rows of this CTA are software-pipelined by one: the loads of the next row are issued before the block-wide sum
-  // of the current one, so they are in flight across its two barriers and the output pass.
-  Vec16<T> ra[NV], rd[NV], rb[NV];
-  auto fetch = [&](int64_t row) {
+  // The row groups of a CTA are software-pipelined by one: the loads of the next group are issued before the block-wide sum
+  // of the current one, so they are in flight across its barrier and the output pass.  (A deeper cp.async ring through shared
+  // memory was measured slower: the kernel is not bound by load latency.)
+  Vec16<T> ra[ROWS][NV], rd[ROWS][NV], rb[GATED ? ROWS : 1][NV];
+  auto fetch = [&](int64_t row0) {
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      int c = (k * NORM_THREADS + threadIdx.x) * V;
-      if (c < D) {
-        ra[k].load(y + row * D + c);
-        rd[k].load(dout + row * D + c);
-        if (z != nullptr) rb[k].load(z + row * zrs + c);
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int c = (k * NORM_THREADS + threadIdx.x) * V;
+        if (c < D && row0 + r < M) {
+          ra[r][k].load(y + (row0 + r) * D + c);
+          rd[r][k].load(dout + (row0 + r) * D + c);
+          if (GATED) rb[GATED ? r : 0][k].load(z + (row0 + r) * zrs + c);
+        }
       }
-    }
   };
-  if (blockIdx.x < M) fetch(blockIdx.x);
-  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
-    float yv[NV][V], sz[NV][V], gz[NV][V], u[NV][V];
-    const float rstd = w ? rstd_in[row] : 1.f;
-    float dot = 0.f;
+  const int64_t stride = (int64_t)gridDim.x * ROWS;
+  if ((int64_t)blockIdx.x * ROWS < M) fetch((int64_t)blockIdx.x * ROWS);
+  float wv[NV][V];                                    // the norm weights of this thread's columns, once per kernel
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      int c = (k * NORM_THREADS + threadIdx.x) * V;
-      if (c < D) {
-        const Vec16<T> a = ra[k], d = rd[k];
-        if (z != nullptr) {
-          const Vec16<T> b = rb[k];
+  for (int k = 0; k < NV; ++k) {
+    const int c = (k * NORM_THREADS + threadIdx.x) * V;
+#pragma unroll
+    for (int i = 0; i < V; ++i) wv[k][i] = (w != nullptr && c < D) ? w[c + i] : 1.f;
+  }
+  int par = 0;
+  for (int64_t row0 = (int64_t)blockIdx.x * ROWS; row0 < M; row0 += stride, par ^= 1) {
+    float yv[ROWS][NV][V], sz[GATED ? ROWS : 1][NV][V], gz[GATED ? ROWS : 1][NV][V], u[ROWS][NV][V];
+    float rstd[ROWS], dot[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      rstd[r] = (w && row0 + r < M) ? rstd_in[row0 + r] : 1.f;
+      dot[r] = 0.f;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int c = (k * NORM_THREADS + threadIdx.x) * V;
+        if (c < D && row0 + r < M) {
 #pragma unroll
           for (int i = 0; i < V; ++i) {
-            float zz = b.get(i);
-            sz[k][i] = silu_t<T>(zz);
-            gz[k][i] = silu_grad_t<T>(zz);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < V; ++i) { sz[k][i] = 1.f; gz[k][i] = 0.f; }
-        }
-#pragma unroll
-        for (int i = 0; i < V; ++i) {
-          yv[k][i] = a.get(i);
-          float dd = d.get(i);
-          if (w != nullptr) {
-            float xh = yv[k][i] * sz[k][i] * rstd;
-            u[k][i] = dd * w[c + i];
-            dot = fmaf(xh, u[k][i], dot);
-            dwacc[k][i] = fmaf(dd, xh, dwacc[k][i]);
-          } else {
-            u[k][i] = dd;
+            float s1 = 1.f;
+            if (GATED) {
+              const float zz = rb[GATED ? r : 0][k].get(i);
+              s1 = silu_t<T>(zz);
+              sz[GATED ? r : 0][k][i] = s1;
+              gz[GATED ? r : 0][k][i] = silu_grad_t<T>(zz);
+            }
+            yv[r][k][i] = ra[r][k].get(i);
+            const float dd = rd[r][k].get(i);
+            if (w != nullptr) {
+              const float xh = yv[r][k][i] * s1 * rstd[r];
+              u[r][k][i] = dd * wv[k][i];
+              dot[r] = fmaf(xh, u[r][k][i], dot[r]);
+              dwacc[k][i] = fmaf(dd, xh, dwacc[k][i]);
+            } else {
+              u[r][k][i] = dd;
+            }
           }
         }
       }
     }
-    if (row + gridDim.x < M) fetch(row + gridDim.x);
-    float m = 0.f;
-    if (w != nullptr) m = block_sum(dot, red) / (float)D;
+    if (row0 + stride < M) fetch(row0 + stride);
+    if (w != nullptr) block_sum_rows<ROWS>(dot, red[par]);
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      int c = (k * NORM_THREADS + threadIdx.x) * V;
-      if (c < D) {
-        Vec16<T> oy, oz;
+    for (int r = 0; r < ROWS; ++r) {
+      const float m = dot[r] / (float)D;
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-          float dg = u[k][i];
-          if (w != nullptr) {
-            float xh = yv[k][i] * sz[k][i] * rstd;
-            dg = rstd * (u[k][i] - xh * m);
+      for (int k = 0; k < NV; ++k) {
+        const int c = (k * NORM_THREADS + threadIdx.x) * V;
+        if (c < D && row0 + r < M) {
+          Vec16<T> oy, oz;
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            const float s1 = GATED ? sz[GATED ? r : 0][k][i] : 1.f;
+            float dg = u[r][k][i];
+            if (w != nullptr) {
+              const float xh = yv[r][k][i] * s1 * rstd[r];
+              dg = rstd[r] * (u[r][k][i] - xh * m);
+            }
+            oy.set(i, dg * s1);
+            if (GATED) oz.set(i, dg * yv[r][k][i] * gz[GATED ? r : 0][k][i]);
           }
-          oy.set(i, dg * sz[k][i]);
-          oz.set(i, dg * yv[k][i] * gz[k][i]);
+          oy.store(dy + (row0 + r) * D + c);
+          if (GATED) oz.store(dz + (row0 + r) * dzrs + c);
         }
-        oy.store(dy + row * D + c);
-        if (z != nullptr) oz.store(dz + row * dzrs + c);
       }
     }
   }
@@ -280,8 +336,10 @@ static int gate_norm_fwd_t(const void* y, const void* z, int64_t zrs, const floa
     ORBIT_CHECK_LAUNCH("gate_norm_fwd_scalar_kernel");
     return OK;
   }
-#define L_(NV) gate_norm_fwd_kernel<T, NV><<<grid, NORM_THREADS, 0, st>>>((const T*)y, (const T*)z, zrs, w, (T*)out, rstd, D, eps)
-  if (nv <= 1) L_(1); else if (nv == 2) L_(2); else L_(4);
+  // a gate doubles the bytes per row; ungated narrow rows (the backbone norms) are grouped 4 or 2 to a CTA
+#define L_(NV, ROWS, G) gate_norm_fwd_kernel<T, NV, ROWS, G><<<(unsigned)((M + ROWS - 1) / ROWS), NORM_THREADS, 0, st>>>((const T*)y, (const T*)z, zrs, w, (T*)out, rstd, M, D, eps)
+  if (z != nullptr) { if (nv <= 1) L_(1, 4, true); else if (nv == 2) L_(2, 2, true); else L_(4, 1, true); }
+  else { if (nv <= 1) L_(1, 4, false); else if (nv == 2) L_(2, 2, false); else L_(4, 1, false); }
 #undef L_
   ORBIT_CHECK_LAUNCH("gate_norm_fwd_kernel");
   return OK;
@@ -318,8 +376,9 @@ static int gate_norm_bwd_t(const void* y, const void* z, int64_t zrs, const floa
     }
     return OK;
   }
-#define L_(NV) gate_norm_bwd_kernel<T, NV><<<grid, NORM_THREADS, 0, st>>>((const T*)y, (const T*)z, zrs, w, rstd, (const T*)dout, (T*)dy, (T*)dz, dzrs, part, M, D)
-  if (nv <= 1) L_(1); else if (nv == 2) L_(2); else L_(4);
+#define L_(NV, ROWS, G) gate_norm_bwd_kernel<T, NV, ROWS, G><<<grid, NORM_THREADS, 0, st>>>((const T*)y, (const T*)z, zrs, w, rstd, (const T*)dout, (T*)dy, (T*)dz, dzrs, part, M, D)
+  if (z != nullptr) { if (nv <= 1) L_(1, 2, true); else if (nv == 2) L_(2, 1, true); else L_(4, 1, true); }
+  else { if (nv <= 1) L_(1, 4, false); else if (nv == 2) L_(2, 2, false); else L_(4, 1, false); }
 #undef L_
   ORBIT_CHECK_LAUNCH("gate_norm_bwd_kernel");
   if (dw != nullptr) {
