@@ -220,7 +220,7 @@ def cpu_step_time(wl, sample_B, sample_L, steps, warmup):
     return statistics.median(times)
 
 
-def run_reference(args, wl, name):
+def run_reference(args, wl, name, out_stream=sys.stdout):
     """The reference arm: the CPU route of the layer (the oracle port) on all host threads, rank 0 only."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -239,7 +239,7 @@ def run_reference(args, wl, name):
         "dtype": "f32", "data": "synthetic", "config": {"workload": name + ": " + wl["desc"]},
         "cpu_baseline": {"value": tok, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample,
                          "host_cpus": os.cpu_count()},
-        "e2e": {"value": tok, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        "e2e": {"value": tok, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), file=out_stream, flush=True)
 
 
 # ----------------------------------------------------------------------------------------------------
@@ -491,7 +491,17 @@ def other_workload(env, key, steps, warmup, pk, **kw):
             "kernel_ms": {k: round(v, 4) for k, v in sorted(m["kern_ms"].items())}}
 
 
+def _json_only_stdout():
+    """Keep the process's real stdout for the one JSON line: everything else that writes to file descriptor 1 (NCCL's
+    version banner with NCCL_DEBUG=INFO, library chatter) goes to stderr from here on.  Returns the stream to print to."""
+    real = os.fdopen(os.dup(1), "w")
+    sys.stdout.flush()
+    os.dup2(2, 1)
+    return real
+
+
 def main():
+    out_stream = _json_only_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
@@ -507,7 +517,7 @@ def main():
         wl["B"] = args.batch
         wl["desc"] += f" (batch rows overridden to {args.batch})"
     if args.impl == "reference":
-        return run_reference(args, wl, args.workload)
+        return run_reference(args, wl, args.workload, out_stream)
 
     env = Env()
     world, rank = env.world, env.rank
@@ -570,7 +580,7 @@ def main():
                                "host_cpus": os.cpu_count()}
     if others:
         out["other_workloads"] = others
-    print(json.dumps(out))
+    print(json.dumps(out), file=out_stream, flush=True)
     env.close()
 
 
