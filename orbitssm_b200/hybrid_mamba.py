@@ -227,7 +227,10 @@ class HybridMambaSSM(StateLifecycle, nn.Module):
         return delta, Bh, Ch, feat, th_h, lam
 
     # -- forward --------------------------------------------------------------------------------------------------
-    def forward(self, x, *, state=None, return_state=False):
+    #: `forward` takes the block's residual stream and returns ``residual + mixer(x)`` (added in the output GEMM's epilogue)
+    fused_residual = True
+
+    def forward(self, x, *, state=None, return_state=False, _residual=None):
         """x [B, L, d_model] -> y [B, L, d_model], or (y, State) with ``return_state=True``; ``state`` continues a
         previous call (reference: hybrid_mamba.py:2706-2830)."""
         if x.dim() != 3 or x.shape[-1] != self.d_model:
@@ -247,7 +250,7 @@ class HybridMambaSSM(StateLifecycle, nn.Module):
         f = torch.float32
         with torch.autocast("cuda", enabled=False):
             xa = x.to(io)
-            proj = ops.ProjectFn.apply(xa, self._proj_pad, None, 0, self.in_proj.weight, *[m.weight for _, m in self._slab])
+            proj = ops.ProjectFn.apply(xa, None, self._proj_pad, None, 0, self.in_proj.weight, *[m.weight for _, m in self._slab])
             arena = ops.GradArena()        # conv and gate backward write d(drive), dz straight into d(proj)
             drive_raw, z, slab = ops.SplitColumnsFn.apply(proj, arena, s.d_inner, s.d_inner, self.tok_width)
             new = State()
@@ -272,7 +275,10 @@ class HybridMambaSSM(StateLifecycle, nn.Module):
             self._route_note = "fp32 coordinate scan"
             y = ops.GateNormFn.apply(y.reshape(Bsz, L, s.d_inner), z, self.norm.weight if s.out_norm else None, s.norm_eps,
                                      (arena, 1))
-            out = ops.ProjectFn.apply(y, 0, None, 0, self.out_proj.weight)
+            fuse = _residual is not None and _residual.dtype == io and _residual.shape == x.shape
+            out = ops.ProjectFn.apply(y, _residual if fuse else None, 0, None, 0, self.out_proj.weight)
+            if _residual is not None and not fuse:
+                out = _residual + out
         if not return_state:
             return out
         new["hidden_state"] = hN

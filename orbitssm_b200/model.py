@@ -42,10 +42,14 @@ class ResidualBlock(nn.Module):
     n_residuals = 1
 
     def forward(self, x, state=None, return_state=False):
+        fused = getattr(self.mixer, "fused_residual", False)      # this package's mixers add the residual in their output GEMM
         if state is None and not return_state:
-            return x + self.mixer(self.norm(x))
-        y, state = self.mixer(self.norm(x), state=state, return_state=True)
-        y = x + y
+            return self.mixer(self.norm(x), _residual=x) if fused else x + self.mixer(self.norm(x))
+        if fused:
+            y, state = self.mixer(self.norm(x), state=state, return_state=True, _residual=x)
+        else:
+            y, state = self.mixer(self.norm(x), state=state, return_state=True)
+            y = x + y
         return (y, state) if return_state else y
 
     def step(self, x_t, state=None):

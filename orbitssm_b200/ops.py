@@ -205,7 +205,7 @@ def _mm_f32(a, b):
 
 
 class ProjectFn(torch.autograd.Function):
-    """``x @ cat(weights)^T`` (+ `bias` on the columns from `bias_off`, + `pad` zero columns) as ONE node over the
+    """``x @ cat(weights)^T`` (+ `bias` on the columns from `bias_off`, + `pad` zero columns, or + `residual`) as ONE node over the
     parameters themselves: the projections of a layer that share an input (drive | gate | token slab; reference:
     src/orbit_ssm/ssm/ssd_mimo.py:4545-4558, src/orbit_ssm/ssm/hybrid_mamba.py:2729-2759) or a single projection.
 
@@ -215,7 +215,7 @@ class ProjectFn(torch.autograd.Function):
     would sum every column of the gradient)."""
 
     @staticmethod
-    def forward(ctx, x, pad, bias, bias_off, *weights):
+    def forward(ctx, x, residual, pad, bias, bias_off, *weights):
         io, K = x.dtype, x.shape[-1]
         sizes = [int(w.shape[0]) for w in weights]
         n_tot = sum(sizes) + int(pad)
@@ -231,7 +231,13 @@ class ProjectFn(torch.autograd.Function):
         if bias is not None:
             bfull = torch.zeros((n_tot,), device=x.device, dtype=io)
             bfull[bias_off:bias_off + bias.shape[0]].copy_(bias)
-        out = F.linear(x2, wcat, bfull)
+        if residual is not None:
+            # residual + x W^T in the GEMM's own epilogue (beta = 1): the block's residual add costs no pass of its own
+            if bias is not None or pad or residual.dtype != io:
+                raise ValueError("ProjectFn: a residual goes with one unpadded, unbiased projection in the IO dtype")
+            out = torch.addmm(residual.reshape(-1, n_tot), x2, wcat.t())
+        else:
+            out = F.linear(x2, wcat, bfull)
         ctx.save_for_backward(x2, wcat)
         ctx.meta = (sizes, [w.dtype for w in weights], None if bias is None else (int(bias_off), int(bias.shape[0]), bias.dtype),
                     x.shape)
@@ -244,19 +250,20 @@ class ProjectFn(torch.autograd.Function):
         sizes, wdts, bmeta, xshape = ctx.meta
         d2 = dproj.reshape(-1, dproj.shape[-1])
         dx = (d2 @ wcat).view(xshape) if ctx.needs_input_grad[0] else None
+        dres = dproj if ctx.needs_input_grad[1] else None
         dws = [None] * len(sizes)
-        if any(ctx.needs_input_grad[4:]):
+        if any(ctx.needs_input_grad[5:]):
             dW = _mm_f32(d2.t(), x2)
             o = 0
             for i, (n, dt) in enumerate(zip(sizes, wdts)):
-                if ctx.needs_input_grad[4 + i]:
+                if ctx.needs_input_grad[5 + i]:
                     dws[i] = dW[o:o + n] if dt == torch.float32 else dW[o:o + n].to(dt)
                 o += n
         db = None
-        if bmeta is not None and ctx.needs_input_grad[2]:
+        if bmeta is not None and ctx.needs_input_grad[3]:
             off, nb, bdt = bmeta
             db = d2[:, off:off + nb].sum(0).to(bdt)      # fp32 accumulation, result in the IO dtype (as a linear layer's own backward)
-        return (dx, None, db, None, *dws)
+        return (dx, dres, None, db, None, *dws)
 
 
 # ----------------------------------------------------------------------------------------------------

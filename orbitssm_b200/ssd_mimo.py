@@ -332,7 +332,10 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         return dict(Bhat=Bhat, Chat=Chat, gBp=gBp, gCp=gCp, beta=beta, gamma=gamma, dA=dA, w=w, wd=wd_, chi=chi, Dg=Dg, lag0=lag0)
 
     # -- forward -------------------------------------------------------------------------------------------
-    def forward(self, x, *, state=None, return_state=False):
+    #: `forward` takes the block's residual stream and returns ``residual + mixer(x)`` (added in the output GEMM's epilogue)
+    fused_residual = True
+
+    def forward(self, x, *, state=None, return_state=False, _residual=None):
         """x [B, L, d_model] -> y [B, L, d_model], or (y, State) with ``return_state=True``; ``state`` continues a
         previous call (reference: ssd_mimo.py:4367-4400)."""
         if x.dim() != 3 or x.shape[-1] != self.d_model:
@@ -358,7 +361,7 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         with torch.autocast("cuda", enabled=False):
             xa = x.to(io)
             # [B, L, drive | z | slab | pad]: one GEMM over the parameters themselves (cast once into the IO dtype)
-            proj = ops.ProjectFn.apply(xa, self._proj_pad, self._tok_bias(), s.d_inner + self.d_gate, self.in_proj.weight,
+            proj = ops.ProjectFn.apply(xa, None, self._proj_pad, self._tok_bias(), s.d_inner + self.d_gate, self.in_proj.weight,
                                        *[getattr(self, a).weight for a in self._proj_attrs])
             # every consumer of a column range writes that range of d(proj) in place (conv, gate, token tails)
             arena = ops.GradArena()
@@ -432,7 +435,10 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
                 if want_state and s.use_trap:
                     v_last = self._last_write(u, law, Bsz)
             y = ops.GateNormFn.apply(y, z, self.norm.weight if s.out_norm else None, s.norm_eps, (arena, 1)) if L > 0 else y
-            out = ops.ProjectFn.apply(y, 0, None, 0, self.out_proj.weight)
+            fuse = _residual is not None and _residual.dtype == io and _residual.shape == x.shape
+            out = ops.ProjectFn.apply(y, _residual if fuse else None, 0, None, 0, self.out_proj.weight)
+            if _residual is not None and not fuse:
+                out = _residual + out
         if not want_state:
             return out
         new["hidden_state"] = hidden
