@@ -7,8 +7,9 @@ declared in ``include/orbit_b200.h``.
 from .config import Execution, HybridMambaConfig, SSDMimoConfig, mamba2_config
 from .hybrid_mamba import HybridMambaSSM
 from .model import BlockStack, ResidualBlock
+from .ops import check_device_status
 from .ssd_mimo import SSDMimoSSM
 from .state import State
 
 __all__ = ["BlockStack", "ResidualBlock", "Execution", "HybridMambaConfig", "HybridMambaSSM", "SSDMimoConfig", "SSDMimoSSM",
-           "State", "mamba2_config"]
+           "State", "check_device_status", "mamba2_config"]

@@ -170,6 +170,10 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
 
         self.backend, self.precision, self.chunk_size, self.kernel_options = "cuda", "io", "auto", {}
         self._route_note = None
+        #: opt-in: read the device status word at the end of every forward (one host synchronisation per call) and raise if
+        #: a bounded device-side wait of the tensor-core kernels gave up (ORBIT_ERR_DEVICE_TIMEOUT); `check_device_status()`
+        #: does the same on demand, e.g. once per training step
+        self.check_waits = False
         self._final_state = None
         self._cp = None
         self.set_execution(as_execution(execution))
@@ -230,6 +234,12 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
             yield self
         finally:
             self.set_execution(old)
+
+    @staticmethod
+    def check_device_status():
+        """Raise `RuntimeError` (ORBIT_ERR_DEVICE_TIMEOUT) if a tensor-core kernel launched since the last check reported a
+        bounded wait that ran out: its outputs are incomplete.  Synchronises the device."""
+        ops.check_device_status()
 
     def last_route(self):
         """Which scan kernels the last forward used ("tcgen05" or "fp32"), and why when it was not the first."""
@@ -439,6 +449,8 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
             out = ops.ProjectFn.apply(y, _residual if fuse else None, 0, None, 0, self.out_proj.weight)
             if _residual is not None and not fuse:
                 out = _residual + out
+        if self.check_waits:
+            ops.check_device_status()
         if not want_state:
             return out
         new["hidden_state"] = hidden

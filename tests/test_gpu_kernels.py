@@ -151,7 +151,8 @@ def test_conv_empty_and_refusals():
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("M,D,gate,norm", [(37, 256, True, True), (5, 2048, True, True), (64, 4096, True, True),
                                            (19, 64, False, True), (19, 64, True, False), (300, 1024, True, True), (7, 12, True, True),
-                                           (9, 9000, True, True)])
+                                           (9, 9000, True, True), (1001, 2048, False, True), (3, 4096, False, True),
+                                           (2501, 512, False, True), (2501, 512, True, True)])
 def test_gate_norm(dtype, M, D, gate, norm):
     g = torch.Generator().manual_seed(1)
     y = torch.randn(M, D, generator=g).to(dtype).to(DEV)
@@ -612,4 +613,15 @@ def test_bounded_wait_winds_down_and_reports():
         ops.check_device_status()
     assert int(status.item()) == 0                                   # the check clears the word
     ops.check_device_status()
-    test_umma_tile(0, 128, 128)                                      # tensor memory was freed: a tile runs right after
+    test_umma_tile(0, 128, 128)
+    # the layer's opt-in check: with `check_waits` a forward whose launches left the word set raises instead of returning
+    from orbitssm_b200 import SSDMimoSSM, mamba2_config
+    layer = SSDMimoSSM(mamba2_config(128, d_state=128, d_head=64), execution={"precision": "io"}).to(DEV)
+    layer.check_waits = True
+    x = torch.randn(1, 130, 128, device=DEV, dtype=torch.bfloat16)
+    layer(x)                                                         # clean run: nothing to report
+    _lib.check(lib.orbit_selftest_wait_timeout(C.c_void_p(status.data_ptr()), 200, C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+               "orbit_selftest_wait_timeout")
+    with pytest.raises(RuntimeError, match="ORBIT_ERR_DEVICE_TIMEOUT"):
+        layer(x)
+    layer(x)                                      # tensor memory was freed: a tile runs right after
