@@ -3,11 +3,11 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5a|cfg5b|cfg5|cfg4|cfg3|cfg2] [--impl reference]
 
 One "step" = y = layer(x); y.backward(dy) on one batch of synthetic input (x ~ N(0,1), fixed random dy; bf16
-activations over fp32 parameters).  Workloads (BASELINE.json `configs`):
-  cfg5a (default) BASELINE config 5a: 4-block BlockStack of the d_model-2048 SISO layer, global batch 64 x 4096 tokens split
+activations over fp32 parameters).  Workloads (the benchmark configurations this metric is defined on):
+  cfg5a (default) configuration 5a: 4-block BlockStack of the d_model-2048 SISO layer, global batch 64 x 4096 tokens split
         over the GPUs by batch rows (64 / N rows per GPU: strong scaling, no collective on the data path): the d2048 bf16
         configuration the metric is quoted on "at 1/2/4/8 B200"
-  cfg5b BASELINE config 5b: one d_model-2048 layer, B = 1, L = 262144 split over the GPUs (context parallel, strong
+  cfg5b configuration 5b: one d_model-2048 layer, B = 1, L = 262144 split over the GPUs (context parallel, strong
         scaling); with N > 1 the default run also measures it for a few steps under "other_workloads"
   cfg3  SSD-MIMO rank-4 layer, d_model 2048, x [4, 4096, 2048] (rank-4 tcgen05 tiles); at N = 1 the default run also
         measures it (same steps and warm-up) and reports it, with its own roofline block, under "other_workloads"
@@ -46,7 +46,7 @@ WORKLOADS = {
     "cfg4": dict(B=8, L=2048, d_model=1024, kind="hm", chunk_acct=32,
                  desc="HybridMamba layer (H=32, P=64, N=64: 32 real rows + 16 rotating pairs, coord_static, trapezoid, gated "
                       "RMSNorm), d_model 1024, x [8,2048,1024]"),
-    # BASELINE config 5: (a) a 4-block BlockStack of the d2048 SISO layer, global batch 64 split over the GPUs by rows;
+    # configuration 5: (a) a 4-block BlockStack of the d2048 SISO layer, global batch 64 split over the GPUs by rows;
     # (b) one layer, B = 1, L = 262144, context-parallel over the GPUs.  Both strong scaling.
     "cfg5a": dict(B=64, L=4096, d_model=2048, kind="m2", chunk_acct=64, blocks=4, split_batch=True,
                   desc="4-block BlockStack of the SSD-MIMO SISO Mamba-2 preset layer (H=64, P=64, N=128), d_model 2048, "
@@ -95,7 +95,7 @@ def make_mixer(cfg, execution=None):
 
 
 def init_params(layer, seed=0):
-    """A_log <- log U(log 1, log 16) per (head, sibling) as BASELINE.json states; everything else default init
+    """A_log <- log U(log 1, log 16) per (head, sibling) as the benchmark configurations state; everything else default init
     (HybridMamba keeps its default per-coordinate ladder)."""
     g = torch.Generator().manual_seed(seed)
     with torch.no_grad():
@@ -536,7 +536,7 @@ def main():
             for key in ("cfg3", "cfg4"):
                 others[key] = other_workload(env, key, args.steps, args.warmup, pk)
         else:
-            # BASELINE config 5b: the one mode with communication on the data path.  Rank 0 first runs the whole sequence
+            # configuration 5b: the one mode with communication on the data path.  Rank 0 first runs the whole sequence
             # alone (the N = 1 time the strong-scaling figure divides by), then all ranks run it context-parallel.
             k5 = max(3, min(args.steps, 5))
             solo = None

@@ -31,7 +31,7 @@ OUT = os.path.dirname(os.path.abspath(__file__))
 
 HS = [{"frac": 1.0, "decay": "head_static"}]
 CASES = {
-    # BASELINE config 1 exactly: default init under seed 0, x = randn(2, 256, 64), loss mean(y^2)
+    # Benchmark configuration 1 exactly: default init under seed 0, x = randn(2, 256, 64), loss mean(y^2)
     "cfg1_exact": dict(cfg=dict(d_model=64, d_state=16, expand=1.0, d_conv=0, d_ssm_in=1, d_ssm_out=1, n_groups=16),
                        B=2, L=256, exact=True),
     # config-2 geometry (Mamba-2 preset: P=64, N=128, Euler, joint B|C conv, output norm) at 2 heads

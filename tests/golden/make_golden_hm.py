@@ -26,7 +26,7 @@ from orbit_ssm import HybridMambaSSM, HybridMambaConfig          # noqa: E402  (
 OUT = os.path.dirname(os.path.abspath(__file__))
 HALF = [{"frac": .5, "decay": "coord_static"}, {"frac": .5, "decay": "coord_static", "complex": True}]
 CASES = {
-    # BASELINE config 4's structure (half real rows, half rotating pairs, trapezoid, gated RMSNorm) at toy width
+    # benchmark configuration 4's structure (half real rows, half rotating pairs, trapezoid, gated RMSNorm) at toy width
     "hm_small": dict(cfg=dict(d_model=64, d_state=16, expand=2, d_conv=4, out_norm=True, d_head=16, row_blocks=HALF),
                      B=2, L=40, split=17),
     # config 4's head geometry (P = 64, N = 64: 32 real rows + 16 pairs) at 2 heads

@@ -1,4 +1,4 @@
-"""-m gpu: the layers at the BASELINE configurations' full sizes, checked through size-independent properties (no CPU
+"""-m gpu: the layers at the benchmark configurations' full sizes, checked through size-independent properties (no CPU
 checker finishes these sizes in seconds): a sequence run in two segments with the carried State equals the whole
 sequence; repeated runs are bitwise identical; outputs and every gradient are finite; the scan is linear in the drive
 path (the output gradient of 2*dy is twice the gradient of dy)."""

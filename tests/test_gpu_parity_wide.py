@@ -1,6 +1,6 @@
-"""-m gpu: value parity at the BASELINE configurations' full WIDTH, and the 16-bit test policy over several input draws.
+"""-m gpu: value parity at the benchmark configurations' full WIDTH, and the 16-bit test policy over several input draws.
 
-1. Every single-GPU BASELINE configuration (2, 3, 4 and the config-5 layer) at its full width and head count on a
+1. Every single-GPU benchmark configuration (2, 3, 4 and the config-5 layer) at its full width and head count on a
    [1, 512, d_model] slice of its input, bf16 activations over fp32 parameters on the tensor-core / coordinate-scan
    kernels, against the CPU oracle in fp64 on the same seeded inputs and weights: output, carried state, input
    gradient and every parameter gradient.

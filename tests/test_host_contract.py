@@ -13,7 +13,9 @@ from conftest import load_golden
 from test_layer_host_logic import _layer, _rel, cpu_hm_kernels, cpu_kernels  # noqa: F401  (fixtures)
 from orbitssm_b200 import BlockStack, HybridMambaConfig, HybridMambaSSM, SSDMimoConfig, SSDMimoSSM, State, mamba2_config
 
-REFERENCE = os.environ.get("ORBIT_REFERENCE", "/root/reference")
+# the reference checkout: $ORBIT_REFERENCE, else a directory "reference" beside this repository
+REFERENCE = os.environ.get("ORBIT_REFERENCE") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 
 # ---------------------------------------------------------------------------------------------------- carries

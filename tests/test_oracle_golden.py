@@ -67,7 +67,7 @@ def test_oracle_matches_reference_fp64(name, route):
 
 
 def test_config1_known_answer():
-    """BASELINE config 1: seed 0 default init, x = randn(2,256,64): mean(y^2) recorded from the reference."""
+    """Benchmark configuration 1: seed 0 default init, x = randn(2,256,64): mean(y^2) recorded from the reference."""
     rec = load_golden("cfg1_exact")
     spec = resolve_ssd_spec(SSDMimoConfig(**rec["config"]))
     y = O.ssd_layer(spec, rec["state_dict"], rec["x"])
