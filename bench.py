@@ -500,6 +500,50 @@ def _json_only_stdout():
     return real
 
 
+def graphed_workload(env, key, steps, warmup):
+    """A launch-bound workload (small layer) stepped eagerly and as one captured CUDA graph (`orbitssm_b200.GraphedStep`):
+    the same forward + backward, CUDA events around every step, L2 flushed between steps."""
+    from orbitssm_b200 import GraphedStep
+    wl = WORKLOADS[key]
+    torch.manual_seed(0)
+    layer = make_mixer(make_config(wl), execution={"precision": "io"}).to(env.dev)
+    init_params(layer)
+    x = torch.randn(wl["B"], wl["L"], wl["d_model"], device=env.dev, dtype=torch.bfloat16)
+    dy = torch.randn_like(x)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=env.dev)
+    xe = x.clone().requires_grad_(True)
+
+    def eager():
+        xe.grad = None
+        for p in layer.parameters():
+            p.grad = None
+        layer(xe).backward(dy)
+
+    g = GraphedStep(layer, x, dy, warmup=max(3, warmup))
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        ev = []
+        for _ in range(steps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            ev.append((a, b))
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in ev) / steps
+
+    t_eager = timed(eager)
+    t_graph = timed(lambda: g.step(x, dy))
+    tokens = wl["B"] * wl["L"]
+    del g, layer, flush
+    torch.cuda.empty_cache()
+    return {"workload": key + ": " + wl["desc"] + ", one step captured as a CUDA graph", "value": tokens / (t_graph * 1e-3),
+            "unit": "tokens/s", "ms_per_step": t_graph, "eager_ms_per_step": t_eager, "steps": steps, "warmup": warmup}
+
+
 def main():
     out_stream = _json_only_stdout()
     ap = argparse.ArgumentParser()
@@ -535,6 +579,8 @@ def main():
             # the other single-GPU configurations, same steps and warm-up, each with its own roofline block
             for key in ("cfg3", "cfg4"):
                 others[key] = other_workload(env, key, args.steps, args.warmup, pk)
+            # a launch-bound size: the d_model-1024 layer eagerly and as one captured graph
+            others["cfg2_graphed"] = graphed_workload(env, "cfg2", args.steps, args.warmup)
         else:
             # configuration 5b: the one mode with communication on the data path.  Rank 0 first runs the whole sequence
             # alone (the N = 1 time the strong-scaling figure divides by), then all ranks run it context-parallel.

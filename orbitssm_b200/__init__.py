@@ -5,11 +5,12 @@ Host side mirrors the reference's config + execution interface (`SSDMimoConfig`,
 declared in ``include/orbit_b200.h``.
 """
 from .config import Execution, HybridMambaConfig, SSDMimoConfig, mamba2_config
+from .graphs import CaptureError, GraphedDecode, GraphedStep
 from .hybrid_mamba import HybridMambaSSM
 from .model import BlockStack, ResidualBlock
 from .ops import check_device_status
 from .ssd_mimo import SSDMimoSSM
 from .state import State
 
-__all__ = ["BlockStack", "ResidualBlock", "Execution", "HybridMambaConfig", "HybridMambaSSM", "SSDMimoConfig", "SSDMimoSSM",
+__all__ = ["BlockStack", "ResidualBlock", "CaptureError", "Execution", "GraphedDecode", "GraphedStep", "HybridMambaConfig", "HybridMambaSSM", "SSDMimoConfig", "SSDMimoSSM",
            "State", "check_device_status", "mamba2_config"]

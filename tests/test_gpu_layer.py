@@ -235,3 +235,53 @@ def test_step_equals_forward_on_device(name, io):
     assert rel(torch.cat(ys, 1), y_all) < ty, rel(torch.cat(ys, 1), y_all)
     for k in s_all:
         assert rel(st[k], s_all[k]) < ty, (k, rel(st[k], s_all[k]))
+
+
+def test_graphed_training_step_equals_eager():
+    """One captured forward + backward (CUDA graph, static buffers) replayed on two different inputs against the same
+    steps run eagerly: output, input gradient and every parameter gradient (reference: src/orbit_ssm/graphs.py:449)."""
+    from orbitssm_b200 import BlockStack, GraphedStep, mamba2_config
+    torch.manual_seed(3)
+    cfg = mamba2_config(128, d_state=128, d_head=64)
+    stack = BlockStack.from_mixers([SSDMimoSSM(cfg, execution={"precision": "io"}) for _ in range(2)], 128).to(DEV)
+    xs = [torch.randn(2, 300, 128, device=DEV, dtype=torch.bfloat16) for _ in range(2)]
+    dys = [torch.randn(2, 300, 128, device=DEV, dtype=torch.bfloat16) for _ in range(2)]
+    g = GraphedStep(stack, xs[0], dys[0], amp_dtype=torch.bfloat16)
+    # the eager comparison below runs on another stream than the one the capture made the gradient accumulators on
+    torch.autograd.graph.set_warn_on_accumulate_grad_stream_mismatch(False)
+    for x, dy in zip(xs, dys):
+        y = g.step(x, dy).clone()
+        got = {n: p.grad.clone() for n, p in stack.named_parameters()}      # step() re-attaches its static gradient buffers
+        gx = g.x_grad.clone()
+        for p in stack.parameters():
+            p.grad = None
+        xe = x.clone().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            ye = stack(xe)
+        ye.backward(dy)
+        assert rel(y, ye) < 1e-3 and rel(gx, xe.grad) < 1e-3
+        for n, p in stack.named_parameters():
+            assert rel(got[n], p.grad) < 1e-3, n
+        for p in stack.parameters():
+            p.grad = None
+
+
+def test_graphed_decode_equals_eager_steps():
+    """Decode steps replayed from one CUDA graph with the State at fixed addresses against eager `step` calls."""
+    from orbitssm_b200 import BlockStack, GraphedDecode, mamba2_config
+    torch.manual_seed(4)
+    cfg = mamba2_config(128, d_state=128, d_head=64)
+    stack = BlockStack.from_mixers([SSDMimoSSM(cfg, execution={"precision": "io"}) for _ in range(2)], 128).to(DEV)
+    x = torch.randn(3, 6, 128, device=DEV, dtype=torch.bfloat16)
+    with torch.no_grad():
+        st, ys = None, []
+        for t in range(x.shape[1]):
+            y_t, st = stack.step(x[:, t], st)
+            ys.append(y_t)
+    dec = GraphedDecode(stack, 3, device=DEV, dtype=torch.bfloat16)
+    for t in range(x.shape[1]):
+        y_t = dec.step(x[:, t])
+        assert rel(y_t, ys[t]) < 1e-3, t
+    for a_, b_ in zip(dec.state, st):
+        for k in b_:
+            assert rel(a_[k], b_[k]) < 1e-3, k
