@@ -230,8 +230,13 @@ typedef struct orbit_clock_args {
   void* d_trap_raw; int64_t dtrap_rs;
   void* d_rmix_raw; int64_t drmix_rs;
   float* g_alog;             /* out [M, H, R]: per-row term of dA_log (a_act 0); the caller sums it over rows      */
+  /* optional: column sums over the rows of the UNROUNDED raw gradients = gradients of the slab biases, fp32, in the order
+   * [ dt: H*R | a: H*R or H (a_act != 0) | trap: H (trapezoid) ]; fixed-order two-stage reduction                     */
+  float* sum_part; int64_t sum_part_bytes;   /* workspace of orbit_token_clock_bwd_workspace_bytes(...) bytes, or NULL   */
+  float* bias_sums;                          /* out [columns as above]; required with sum_part                           */
 } orbit_clock_args;
 int orbit_token_clock_fwd(const orbit_clock_args* a, int dtype, void* stream);
+int64_t orbit_token_clock_bwd_workspace_bytes(int64_t M, int H, int R, int a_act, int a_per_sibling, int trap);
 int orbit_token_clock_bwd(const orbit_clock_args* a, int dtype, void* stream);
 
 /* ---- HybridMamba coordinate-decay scan -----------------------------------------------------------------------

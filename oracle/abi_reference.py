@@ -452,6 +452,10 @@ def run_clock(a, name, backward, dtype_code, compute=torch.float64):
     if t.get("g_alog") is not None:
         # per-row term of dA_log: d dA / d A_log = dA itself (rate = exp(A_log))
         t["g_alog"].copy_(_f(t["ddA"], compute) * out["dA"].detach())
+    if t.get("bias_sums") is not None:
+        # gradients of the slab biases: column sums of the unrounded raw gradients, [ dt | a | trap ]
+        cols = [gs[k].reshape(-1, gs[k].shape[-1]).sum(0) for k in ("dt_raw", "a_raw", "trap_raw") if leaves.get(k) is not None and gs.get(k) is not None]
+        t["bias_sums"].copy_(torch.cat(cols).to(t["bias_sums"].dtype))
 
 
 def run_step(a, S0, S_fin, dtype_code, compute=torch.float64):

@@ -62,6 +62,7 @@ class ClockArgs(C.Structure):
         ("d_dt_raw", C.c_void_p), ("ddt_rs", C.c_int64), ("d_a_raw", C.c_void_p), ("da_rs", C.c_int64),
         ("d_trap_raw", C.c_void_p), ("dtrap_rs", C.c_int64), ("d_rmix_raw", C.c_void_p), ("drmix_rs", C.c_int64),
         ("g_alog", C.c_void_p),
+        ("sum_part", C.c_void_p), ("sum_part_bytes", C.c_int64), ("bias_sums", C.c_void_p),
     ]
 
 
@@ -106,6 +107,7 @@ SIGNATURES = {
     "orbit_token_map_bwd_workspace_bytes": (_L, [_I]),
     "orbit_token_map_bwd": (_I, [_P, _L, _P, _P, _P, _P, _L, _P, _P, _P, _L, _L, _I, _I, _I, _P]),
     "orbit_token_clock_fwd": (_I, [C.POINTER(ClockArgs), _I, _P]),
+    "orbit_token_clock_bwd_workspace_bytes": (_L, [_L, _I, _I, _I, _I, _I]),
     "orbit_token_clock_bwd": (_I, [C.POINTER(ClockArgs), _I, _P]),
     "orbit_hm_scan_fwd": (_I, [C.POINTER(HmArgs), _I, _P]),
     "orbit_hm_scan_bwd": (_I, [C.POINTER(HmArgs), _I, _P]),

@@ -177,49 +177,140 @@ __global__ void __launch_bounds__(256) clock_fwd_kernel(const ClockArgs a) {
 // One thread per (row m, head h): loops the R siblings so that the per-head raw gradients (trap, shared a) are summed in
 // a fixed order by their single owner.  With a static rate the per-element term of dA_log goes to g_alog [M, H*R]
 // (the caller sums it over rows); d r_mix is the row sum of dchi and needs no kernel.
+// The grid strides over the rows by a multiple of H, so a thread keeps its head and can sum the UNROUNDED raw gradients
+// of its rows in registers: these column sums are the gradients of the slab biases (dt, a, trap), exact in fp32 where a
+// sum over the bf16-rounded slab gradient would carry the rounding of every row.  Per-CTA sums (threads of a head added
+// in thread order) go to sum_part [gridDim.x][ncol]; clock_colsum_kernel adds the CTAs in order.
+constexpr int CLK_MAXR = 4;      // = the rank limit of the scan argument block
+
+__host__ __device__ inline int clock_sum_cols(int H, int R, int a_act, int a_per_sibling, bool trap) {
+  return H * R + (a_act != 0 ? (a_per_sibling ? H * R : H) : 0) + (trap ? H : 0);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) clock_bwd_kernel(const ClockArgs a) {
+  __shared__ float sacc[2 * CLK_MAXR + 1][256];
   const int HR = a.H * a.R;
-  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= a.M * a.H) return;
-  const int64_t m = e / a.H;
-  const int h = (int)(e % a.H);
-  const int t = (int)(m % a.L);
   const T* dtp = (const T*)a.dt_raw;
   const T* tp = (const T*)a.trap_raw;
-  float lam = 1.f;
-  if (tp != nullptr) lam = sigmoidf_(ldf(tp + m * a.trap_rs + h));
-  float g_trap = 0.f, g_ah = 0.f;
-  for (int r = 0; r < a.R; ++r) {
-    const int hr = h * a.R + r;
-    const int64_t idx = m * HR + hr;
-    const float raw = ldf(dtp + m * a.dt_rs + hr);
-    const float dt = softplus20(raw);
-    float rate, dmag = 0.f;
-    if (a.a_act == 0) rate = __expf(a.A_log[hr]);
-    else rate_act(a.a_act, ldf((const T*)a.a_raw + m * a.a_rs + (a.a_per_sibling ? hr : h)), rate, dmag);
-    const float gdA = a.ddA[idx];
-    float g_dt = -gdA * rate;
-    const float g_rate = -gdA * dt;
-    if (a.a_act == 0) a.g_alog[idx] = g_rate * rate;
-    else if (a.a_per_sibling) stf((T*)a.d_a_raw + m * a.da_rs + hr, g_rate * dmag);
-    else g_ah = fmaf(g_rate, dmag, g_ah);
-    if (tp != nullptr) {
-      // w_t = lam_t dt_t + lag_{t+1};  lag_t = dt_t (1 - lam_t) enters w_{t-1} (and lag0 at t = 0)
-      const float gsum = a.dw[idx] + (a.dwd ? a.dwd[idx] : 0.f);
-      float glag = 0.f;
-      if (t > 0) glag = a.dw[idx - HR];
-      else if (a.dlag0 != nullptr) glag = a.dlag0[(m / a.L) * HR + hr];
-      g_dt += gsum * lam + glag * (1.f - lam);
-      g_trap = fmaf((gsum - glag) * dt, lam * (1.f - lam), g_trap);
-    } else {
-      g_dt += a.dw[idx];
+  const int64_t total = a.M * a.H, stride = (int64_t)gridDim.x * blockDim.x;
+  float acc_dt[CLK_MAXR], acc_a[CLK_MAXR], acc_trap = 0.f;
+#pragma unroll
+  for (int r = 0; r < CLK_MAXR; ++r) { acc_dt[r] = 0.f; acc_a[r] = 0.f; }
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const int64_t m = e / a.H;
+    const int h = (int)(e % a.H);
+    const int t = (int)(m % a.L);
+    float lam = 1.f;
+    if (tp != nullptr) lam = sigmoidf_(ldf(tp + m * a.trap_rs + h));
+    float g_trap = 0.f, g_ah = 0.f;
+#pragma unroll
+    for (int r = 0; r < CLK_MAXR; ++r) {
+      if (r >= a.R) break;
+      const int hr = h * a.R + r;
+      const int64_t idx = m * HR + hr;
+      const float raw = ldf(dtp + m * a.dt_rs + hr);
+      const float dt = softplus20(raw);
+      float rate, dmag = 0.f;
+      if (a.a_act == 0) rate = __expf(a.A_log[hr]);
+      else rate_act(a.a_act, ldf((const T*)a.a_raw + m * a.a_rs + (a.a_per_sibling ? hr : h)), rate, dmag);
+      const float gdA = a.ddA[idx];
+      float g_dt = -gdA * rate;
+      const float g_rate = -gdA * dt;
+      if (a.a_act == 0) a.g_alog[idx] = g_rate * rate;
+      else if (a.a_per_sibling) {
+        stf((T*)a.d_a_raw + m * a.da_rs + hr, g_rate * dmag);
+        acc_a[r] += g_rate * dmag;
+      } else g_ah = fmaf(g_rate, dmag, g_ah);
+      if (tp != nullptr) {
+        // w_t = lam_t dt_t + lag_{t+1};  lag_t = dt_t (1 - lam_t) enters w_{t-1} (and lag0 at t = 0)
+        const float gsum = a.dw[idx] + (a.dwd ? a.dwd[idx] : 0.f);
+        float glag = 0.f;
+        if (t > 0) glag = a.dw[idx - HR];
+        else if (a.dlag0 != nullptr) glag = a.dlag0[(m / a.L) * HR + hr];
+        g_dt += gsum * lam + glag * (1.f - lam);
+        g_trap = fmaf((gsum - glag) * dt, lam * (1.f - lam), g_trap);
+      } else {
+        g_dt += a.dw[idx];
+      }
+      const float g_raw = g_dt * dsoftplus20(raw);
+      stf((T*)a.d_dt_raw + m * a.ddt_rs + hr, g_raw);
+      acc_dt[r] += g_raw;
+      if (a.d_rmix_raw != nullptr) stf((T*)a.d_rmix_raw + m * a.drmix_rs + hr, a.dchi ? a.dchi[idx] : 0.f);
     }
-    stf((T*)a.d_dt_raw + m * a.ddt_rs + hr, g_dt * dsoftplus20(raw));
-    if (a.d_rmix_raw != nullptr) stf((T*)a.d_rmix_raw + m * a.drmix_rs + hr, a.dchi ? a.dchi[idx] : 0.f);
+    if (tp != nullptr) {
+      stf((T*)a.d_trap_raw + m * a.dtrap_rs + h, g_trap);
+      acc_trap += g_trap;
+    }
+    if (a.a_act != 0 && !a.a_per_sibling) {
+      stf((T*)a.d_a_raw + m * a.da_rs + h, g_ah);
+      acc_a[0] += g_ah;
+    }
   }
-  if (tp != nullptr) stf((T*)a.d_trap_raw + m * a.dtrap_rs + h, g_trap);
-  if (a.a_act != 0 && !a.a_per_sibling) stf((T*)a.d_a_raw + m * a.da_rs + h, g_ah);
+  if (a.sum_part == nullptr) return;
+  // ---- per-CTA column sums: thread i holds head (blockIdx.x * 256 + i) mod H
+#pragma unroll
+  for (int r = 0; r < CLK_MAXR; ++r) {
+    sacc[r][threadIdx.x] = acc_dt[r];
+    sacc[CLK_MAXR + r][threadIdx.x] = acc_a[r];
+  }
+  sacc[2 * CLK_MAXR][threadIdx.x] = acc_trap;
+  __syncthreads();
+  const int ncol = clock_sum_cols(a.H, a.R, a.a_act, a.a_per_sibling, tp != nullptr);
+  const int off_a = HR, off_t = HR + (a.a_act != 0 ? (a.a_per_sibling ? HR : a.H) : 0);
+  float* part = a.sum_part + (int64_t)blockIdx.x * ncol;
+  const int phase = (int)(((int64_t)blockIdx.x * blockDim.x) % a.H);
+  for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
+    const int i0 = ((h - phase) % a.H + a.H) % a.H;      // first thread of this CTA that holds head h
+    float sdt[CLK_MAXR], sa[CLK_MAXR], st = 0.f;
+#pragma unroll
+    for (int r = 0; r < CLK_MAXR; ++r) { sdt[r] = 0.f; sa[r] = 0.f; }
+    for (int i = i0; i < (int)blockDim.x; i += a.H) {
+#pragma unroll
+      for (int r = 0; r < CLK_MAXR; ++r) { sdt[r] += sacc[r][i]; sa[r] += sacc[CLK_MAXR + r][i]; }
+      st += sacc[2 * CLK_MAXR][i];
+    }
+    for (int r = 0; r < a.R; ++r) {
+      part[h * a.R + r] = sdt[r];
+      if (a.a_act != 0 && a.a_per_sibling) part[off_a + h * a.R + r] = sa[r];
+    }
+    if (a.a_act != 0 && !a.a_per_sibling) part[off_a + h] = sa[0];
+    if (tp != nullptr) part[off_t + h] = st;
+  }
+}
+
+// out[c] = sum over the CTAs' partial sums in a fixed order: a CTA owns 32 columns, warp g adds the slots congruent to g
+// modulo 8, then the 8 sums are added in order.
+__global__ void __launch_bounds__(256) clock_colsum_kernel(const float* __restrict__ part, int slots, int ncol, float* __restrict__ out) {
+  __shared__ float red[8][33];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  float acc = 0.f;
+  if (c < ncol) {
+#pragma unroll 4
+    for (int s = grp; s < slots; s += 8) acc += part[(int64_t)s * ncol + c];
+  }
+  red[grp][lane] = acc;
+  __syncthreads();
+  if (grp == 0 && c < ncol) {
+    float v = red[0][lane];
+#pragma unroll
+    for (int g = 1; g < 8; ++g) v += red[g][lane];
+    out[c] = v;
+  }
+}
+
+// CTAs of the backward: a multiple of H / gcd(256, H), so that the grid stride is a multiple of H
+static int clock_bwd_grid(int64_t M, int H) {
+  int g = 256, hh = H;
+  while (hh) { const int tmp = g % hh; g = hh; hh = tmp; }       // g = gcd(256, H)
+  const int unit = H / g;
+  const int64_t need = (M * H + 255) / 256;
+  int64_t cap = 148 * 4;
+  if (need < cap) cap = need;
+  int64_t grid = (cap / unit) * unit;
+  if (grid < unit) grid = unit;
+  return (int)grid;
 }
 
 static int map_nv(int N) { return (N + 31) / 32; }
@@ -314,14 +405,30 @@ extern "C" int orbit_token_clock_fwd(const orbit_clock_args* a, int dtype, void*
   return OK;
 }
 
+extern "C" int64_t orbit_token_clock_bwd_workspace_bytes(int64_t M, int H, int R, int a_act, int a_per_sibling, int trap) {
+  if (M <= 0 || H <= 0 || R <= 0) return 0;
+  return (int64_t)clock_bwd_grid(M, H) * clock_sum_cols(H, R, a_act, a_per_sibling, trap != 0) * (int64_t)sizeof(float);
+}
+
 extern "C" int orbit_token_clock_bwd(const orbit_clock_args* a, int dtype, void* stream) {
   int rc = clock_check(a, dtype, "orbit_token_clock_bwd", true);
   if (rc != OK) return rc;
   if (a->M == 0) return OK;
-  const int64_t n = a->M * a->H;
-  const int grid = (int)((n + 255) / 256);
+  ORBIT_REQUIRE(a->R <= CLK_MAXR, ERR_UNSUPPORTED, "orbit_token_clock_bwd: ranks up to %d are served, got R=%d", CLK_MAXR, a->R);
+  const int grid = clock_bwd_grid(a->M, a->H);
+  const int ncol = clock_sum_cols(a->H, a->R, a->a_act, a->a_per_sibling, a->trap_raw != nullptr);
+  if (a->sum_part != nullptr) {
+    ORBIT_REQUIRE(a->bias_sums != nullptr && a->sum_part_bytes >= orbit_token_clock_bwd_workspace_bytes(a->M, a->H, a->R, a->a_act,
+                                                                                                   a->a_per_sibling, a->trap_raw != nullptr),
+                  ERR_WORKSPACE, "orbit_token_clock_bwd: bias_sums and a workspace of %lld bytes are needed for the column sums",
+                  (long long)orbit_token_clock_bwd_workspace_bytes(a->M, a->H, a->R, a->a_act, a->a_per_sibling, a->trap_raw != nullptr));
+  }
   if (dtype == BF16) clock_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(*a);
   else clock_bwd_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(*a);
   ORBIT_CHECK_LAUNCH("clock_bwd_kernel");
+  if (a->sum_part != nullptr) {
+    clock_colsum_kernel<<<(ncol + 31) / 32, 256, 0, (cudaStream_t)stream>>>(a->sum_part, grid, ncol, a->bias_sums);
+    ORBIT_CHECK_LAUNCH("clock_colsum_kernel");
+  }
   return OK;
 }

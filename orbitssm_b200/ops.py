@@ -959,10 +959,13 @@ def _fill_clock(a, t):
             setattr(a, rs, stride)
             if v.is_cuda:
                 setattr(a, key, v.data_ptr())
-    for key in ("A_log", "r_mix", "dA", "w", "wd", "chi", "lag0", "ddA", "dw", "dwd", "dchi", "dlag0", "g_alog"):
+    for key in ("A_log", "r_mix", "dA", "w", "wd", "chi", "lag0", "ddA", "dw", "dwd", "dchi", "dlag0", "g_alog", "sum_part",
+                "bias_sums"):
         v = t.get(key)
         if v is not None and v.is_cuda:
             setattr(a, key, v.data_ptr())
+    if t.get("sum_part") is not None:
+        a.sum_part_bytes = t["sum_part"].numel() * t["sum_part"].element_size()
     a.t = t
 
 
@@ -991,9 +994,11 @@ def token_clock_fwd(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, a_pe
     return {k: t[k] for k in ("dA", "w", "wd", "chi", "lag0")}
 
 
-def token_clock_bwd(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, a_per_sibling, H, R, g, outs=None):
+def token_clock_bwd(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, a_per_sibling, H, R, g, outs=None, bias_sums=False):
     """`g`: dict of gradients ddA, dw, dwd, dchi, dlag0 (None = zero).  Returns dict(dt_raw, a_raw, trap_raw, rmix_raw,
-    A_log, r_mix); `outs` may carry in-place destinations for the four raw gradients."""
+    A_log, r_mix); `outs` may carry in-place destinations for the four raw gradients.  With `bias_sums` the dict also has
+    dt_bias [H*R], a_bias ([H*R] or [H], dynamic rate only) and trap_bias ([H], trapezoid only): the sums over rows of the raw
+    gradients BEFORE they are rounded to the IO dtype, i.e. the gradients of the slab biases in fp32."""
     B, L = dt_raw.shape[:2]
     dev = dt_raw.device
     f32 = dict(device=dev, dtype=torch.float32)
@@ -1020,19 +1025,35 @@ def token_clock_bwd(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, a_pe
     t["d_trap_raw"] = dest("trap_raw", trap_raw)
     t["d_rmix_raw"] = dest("rmix_raw", rmix_raw)
     t["g_alog"] = torch.empty((B, L, H, R), **f32) if a_act == 0 else None
+    n_a = 0 if a_act == 0 else (H * R if a_per_sibling else H)
+    n_t = H if trap_raw is not None else 0
+    if bias_sums:
+        nbytes = int(_lib.load().orbit_token_clock_bwd_workspace_bytes(B * L, H, R, int(a_act), int(bool(a_per_sibling)), int(n_t > 0)))
+        t["sum_part"] = torch.empty((max(nbytes // 4, 1),), **f32)
+        t["bias_sums"] = torch.empty((H * R + n_a + n_t,), **f32)
     a = _lib.ClockArgs()
     _fill_clock(a, t)
     run_clock(a, "token_clock_bwd", True, _dtype_code("token_clock_bwd", dt_raw))
-    return dict(dt_raw=t["d_dt_raw"], a_raw=t["d_a_raw"], trap_raw=t["d_trap_raw"], rmix_raw=t["d_rmix_raw"],
-                A_log=None if t["g_alog"] is None else t["g_alog"].sum((0, 1)),
-                r_mix=None if t["dchi"] is None else t["dchi"].sum((0, 1)))
+    out = dict(dt_raw=t["d_dt_raw"], a_raw=t["d_a_raw"], trap_raw=t["d_trap_raw"], rmix_raw=t["d_rmix_raw"],
+               A_log=None if t["g_alog"] is None else t["g_alog"].sum((0, 1)),
+               r_mix=None if t["dchi"] is None else t["dchi"].sum((0, 1)))
+    if bias_sums:
+        bs = t["bias_sums"]
+        out["dt_bias"] = bs[:H * R]
+        out["a_bias"] = bs[H * R:H * R + n_a] if n_a else None
+        out["trap_bias"] = bs[H * R + n_a:] if n_t else None
+    return out
 
 
 class TokenClockFn(torch.autograd.Function):
     """Clocks of the scan from the raw slab columns; absent outputs (wd, chi, lag0) come back as empty tensors."""
 
     @staticmethod
-    def forward(ctx, dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, a_per_sibling, H, R, slots=None):
+    def forward(ctx, dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, a_per_sibling, H, R, slots=None,
+                dt_bias=None, a_bias=None, trap_bias=None):
+        # The three biases are already inside the raw columns (added in the projection's epilogue); they are inputs here only
+        # so that their gradients come from this node: the sums of the unrounded raw gradients, not of the rounded slab.
+        ctx.bias_meta = [None if b is None else (b.shape, b.dtype) for b in (dt_bias, a_bias, trap_bias)]
         o = token_clock_fwd(dt_raw, a_raw, trap_raw, rmix_raw, None if A_log is None else A_log.detach(),
                             None if r_mix is None else r_mix.detach(), a_act, a_per_sibling, H, R)
         ctx.save_for_backward(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix)
@@ -1051,13 +1072,20 @@ class TokenClockFn(torch.autograd.Function):
         for key, like in (("dt_raw", dt_raw), ("a_raw", a_raw), ("trap_raw", trap_raw), ("rmix_raw", rmix_raw)):
             if like is not None and key in slots:
                 outs[key] = slots[key][0].view(slots[key][1], like)
+        want_bias = any(ctx.needs_input_grad[11:14])
         g = token_clock_bwd(dt_raw, a_raw, trap_raw, rmix_raw, None if A_log is None else A_log.detach(),
                             None if r_mix is None else r_mix.detach(), a_act, a_per_sibling, H, R,
-                            dict(ddA=ddA, dw=dw, dwd=dwd, dchi=dchi, dlag0=dlag0), outs)
+                            dict(ddA=ddA, dw=dw, dwd=dwd, dchi=dchi, dlag0=dlag0), outs, bias_sums=want_bias)
+
+        def bias_grad(i, key):
+            meta = ctx.bias_meta[i]
+            if meta is None or not ctx.needs_input_grad[11 + i] or g.get(key) is None:
+                return None
+            return g[key].reshape(meta[0]).to(meta[1])
         return (g["dt_raw"], g["a_raw"], g["trap_raw"], g["rmix_raw"],
                 None if (A_log is None or g["A_log"] is None) else g["A_log"].reshape(A_log.shape).to(A_log.dtype),
                 None if (r_mix is None or g["r_mix"] is None) else g["r_mix"].reshape(r_mix.shape).to(r_mix.dtype),
-                None, None, None, None, None)
+                None, None, None, None, None, bias_grad(0, "dt_bias"), bias_grad(1, "a_bias"), bias_grad(2, "trap_bias"))
 
 
 # ----------------------------------------------------------------------------------------------------

@@ -321,10 +321,13 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         rmix_raw = parts.get("rmix") if (s.r_mix_mode != "none" and s.r_mix_dyn) else None
         slots = {k2: slot(k) for k, k2 in (("dt", "dt_raw"), ("a", "a_raw"), ("trap", "trap_raw"), ("rmix", "rmix_raw"))
                  if slot(k) is not None}
+        # the clock node also owns the gradients of the slab biases (the projection got them detached): it sums the raw
+        # gradients before they are rounded into the slab gradient
         dA, w, wd_, chi, lag0 = ops.TokenClockFn.apply(
             parts["dt"], parts.get("a") if s.a_dyn else None, parts.get("trap") if s.use_trap else None, rmix_raw,
             None if s.a_dyn else self.A_log, self.r_mix if s.r_mix_mode != "none" else None, a_act,
-            bool(s.a_dyn and s.a_dyn_per_sibling), H, R, slots)
+            bool(s.a_dyn and s.a_dyn_per_sibling), H, R, slots, self.dt_proj.bias,
+            self.a_dyn_proj.bias if s.a_dyn else None, self.trap_proj.bias if s.use_trap else None)
         if not s.use_trap:
             wd_, lag0 = None, None
         if s.r_mix_mode == "none":
@@ -371,7 +374,9 @@ class SSDMimoSSM(StateLifecycle, nn.Module):
         with torch.autocast("cuda", enabled=False):
             xa = x.to(io)
             # [B, L, drive | z | slab | pad]: one GEMM over the parameters themselves (cast once into the IO dtype)
-            proj = ops.ProjectFn.apply(xa, None, self._proj_pad, self._tok_bias(), s.d_inner + self.d_gate, self.in_proj.weight,
+            tok_bias = self._tok_bias()                  # dt / a / trap biases: their gradients come from the clock node
+            proj = ops.ProjectFn.apply(xa, None, self._proj_pad, None if tok_bias is None else tok_bias.detach(),
+                                       s.d_inner + self.d_gate, self.in_proj.weight,
                                        *[getattr(self, a).weight for a in self._proj_attrs])
             # every consumer of a column range writes that range of d(proj) in place (conv, gate, token tails)
             arena = ops.GradArena()

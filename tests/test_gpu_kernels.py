@@ -564,17 +564,18 @@ def test_token_map(dtype, B, L, X, N, norm, bias, add):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("a_act,per_sib,trap,rmix", [(0, False, False, False), (0, False, True, True), (1, False, True, True),
                                                      (1, True, False, True), (2, True, True, False)])
-def test_token_clock(dtype, a_act, per_sib, trap, rmix):
+@pytest.mark.parametrize("B,L,H,Rr", [(2, 23, 3, 2), (3, 700, 64, 1), (2, 257, 24, 4)])
+def test_token_clock(dtype, a_act, per_sib, trap, rmix, B, L, H, Rr):
     import ctypes as C
-    B, L, H, Rr = 2, 23, 3, 2
     g = torch.Generator().manual_seed(a_act * 10 + trap)
-    slab = torch.randn(B, L, 64, generator=g).to(dtype).to(DEV)
-    dt_raw = slab[..., 0:H * Rr]
-    a_raw = (slab[..., 8:8 + (H * Rr if per_sib else H)] * 2.0) if a_act else None
+    HR = H * Rr
+    slab = torch.randn(B, L, 4 * HR + 16, generator=g).to(dtype).to(DEV)
+    dt_raw = slab[..., 0:HR]
+    a_raw = (slab[..., HR + 2:HR + 2 + (HR if per_sib else H)] * 2.0) if a_act else None
     if a_raw is not None:
         a_raw = a_raw.contiguous()
-    trap_raw = slab[..., 20:20 + H] if trap else None
-    rmix_raw = slab[..., 32:32 + H * Rr] if rmix else None
+    trap_raw = slab[..., 2 * HR + 4:2 * HR + 4 + H] if trap else None
+    rmix_raw = slab[..., 3 * HR + 8:3 * HR + 8 + HR] if rmix else None
     A_log = torch.randn(H, Rr, generator=g).to(DEV) if a_act == 0 else None
     r_mix = torch.randn(H, Rr, generator=g).to(DEV) if rmix else None
     o = ops.token_clock_fwd(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, per_sib, H, Rr)
@@ -588,7 +589,7 @@ def test_token_clock(dtype, a_act, per_sib, trap, rmix):
             assert rel(o[k], ro[k]) < 2e-6, (k, rel(o[k], ro[k]))
     gr = {k: torch.randn(B, L, H, Rr, generator=g).to(DEV) for k in ("ddA", "dw", "dwd", "dchi")}
     gr["dlag0"] = torch.randn(B, H, Rr, generator=g).to(DEV)
-    got = ops.token_clock_bwd(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, per_sib, H, Rr, gr)
+    got = ops.token_clock_bwd(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, per_sib, H, Rr, gr, bias_sums=True)
     with torch.enable_grad():
         ro, leaves = R._clock(t, torch.float64, leaves=True)
         loss = sum((ro[k] * gr["d" + k].double()).sum() for k in ("dA", "w", "wd", "chi", "lag0") if ro[k] is not None)
@@ -599,6 +600,16 @@ def test_token_clock(dtype, a_act, per_sib, trap, rmix):
             continue
         lim = 2e-5 if (dtype == torch.float32 or k in ("A_log", "r_mix")) else 6e-3
         assert rel(got[k].reshape(v.shape), v) < lim, (k, rel(got[k].reshape(v.shape), v))
+    # gradients of the slab biases: column sums of the raw gradients taken BEFORE the rounding to the IO dtype, so fp32-exact
+    # for bf16 activations too; fixed-order two-stage reduction: bitwise reproducible
+    for key, raw in (("dt_bias", "dt_raw"), ("a_bias", "a_raw"), ("trap_bias", "trap_raw")):
+        if want.get(raw) is None:
+            assert got.get(key) is None, key
+            continue
+        ref = want[raw].reshape(-1, want[raw].shape[-1]).sum(0)
+        assert rel(got[key], ref) < 2e-5, (key, rel(got[key], ref))
+    again = ops.token_clock_bwd(dt_raw, a_raw, trap_raw, rmix_raw, A_log, r_mix, a_act, per_sib, H, Rr, gr, bias_sums=True)
+    assert torch.equal(again["dt_bias"], got["dt_bias"])
 
 
 def test_bounded_wait_winds_down_and_reports():
