@@ -37,12 +37,13 @@ __host__ __device__ inline HmGeo hm_geo(int P, int N) {
 
 // Shared-memory tile of 8 tokens (+ the token before them in row 0).
 struct HmTile {
-  float *xs, *dts, *lams, *Bt, *Ct, *cB, *sB, *cC, *sC, *dys, *thc;
+  float *xs, *dts, *lams, *Bt, *Ct, *cB, *sB, *cC, *sC, *dys, *thc, *thn;
+  float *rotm, *thh, *bb, *bc;     // per-head constants of the builder: rotating-pair mask, phase offset of the C map, map biases
 };
 __host__ __device__ inline size_t r4(size_t n) { return (n + 3) & ~(size_t)3; }
 // Every array starts on a 16-byte boundary (xs, Bt, Ct, dys rows are read as float4).
 __host__ __device__ inline size_t hm_tile_floats(const HmGeo& g, bool bwd) {
-  size_t n = 9 * g.P + 9 * g.N + 9 * g.N + 12 + 12 + r4(g.K);
+  size_t n = 9 * g.P + 9 * g.N + 9 * g.N + 12 + 12 + 4 * r4(g.K) + 2 * g.N;
   if (bwd) n += 8 * g.P + 4 * r4(9 * g.K);
   return n;
 }
@@ -55,6 +56,11 @@ __device__ inline float* hm_tile_carve(HmTile& t, float* p, const HmGeo& g, bool
   t.dts = p; p += 12;
   t.lams = p; p += 12;
   t.thc = p; p += r4(g.K);
+  t.thn = p; p += r4(g.K);
+  t.rotm = p; p += r4(g.K);
+  t.thh = p; p += r4(g.K);
+  t.bb = p; p += g.N;
+  t.bc = p; p += g.N;
   if (bwd) {
     t.cB = p; p += r4(9 * g.K);
     t.sB = p; p += r4(9 * g.K);
@@ -62,6 +68,17 @@ __device__ inline float* hm_tile_carve(HmTile& t, float* p, const HmGeo& g, bool
     t.sC = p; p += r4(9 * g.K);
   }
   return p;
+}
+// The per-head constants, written once per CTA (the opening barrier of the first tile build publishes them).
+__device__ __forceinline__ void hm_tile_consts(const HmArgs& a, const HmGeo& g, const HmTile& tl, int h) {
+  for (int k = threadIdx.x; k < g.K; k += blockDim.x) {
+    tl.rotm[k] = (a.feat != nullptr && a.rot[k]) ? 1.f : 0.f;
+    tl.thh[k] = a.theta_h ? a.theta_h[h * g.K + k] : 0.f;
+  }
+  for (int n = threadIdx.x; n < g.N; n += blockDim.x) {
+    tl.bb[n] = a.beta_b ? a.beta_b[h * g.N + n] : 0.f;
+    tl.bc[n] = a.beta_c ? a.beta_c[h * g.N + n] : 0.f;
+  }
 }
 
 // ---- raw staging of the next tile (cp.async, double-buffered): the global-memory latency of a tile is paid while the
@@ -86,43 +103,120 @@ __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc, bool
   const int sz = valid ? 4 : 0;                 // src-size 0: the 4 destination bytes are zero-filled
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gsrc), "r"(sz) : "memory");
 }
+__device__ __forceinline__ void cp_async16s(uint32_t smem_dst, const void* gsrc, bool valid) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(sz) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
+// Staging plan of a tile in 16-byte units.  Which unit copies what is the same for every tile of a CTA, so the split of a
+// unit index into (array, row, column) is done once and kept in shared memory: unit u = {destination byte offset inside
+// the raw buffer | array << 24 | (row's token offset + 1) << 28, source byte offset inside the token's row}.
+// Arrays: 0 drive, 1 dy, 2 B map, 3 C map, 4 angle feature.  Used when every row is a whole number of 16-byte units and
+// every base pointer is 16-byte aligned; otherwise the tile is staged word by word.
+struct HmPlan {
+  const uint2* unit;
+  int n;
+  bool vec;
+};
+__host__ __device__ inline size_t hm_plan_floats(const HmGeo& g) {      // sized for 4-byte elements (the upper bound)
+  return r4(2 * ((size_t)17 * (g.P / 4) + 18 * (g.N / 4) + 8 * ((g.K + 3) / 4)));
+}
+template <typename T, bool BWD>
+__device__ __forceinline__ HmPlan hm_plan_build(const HmArgs& a, const HmGeo& g, uint2* tab, const HmRaw& rw) {
+  HmPlan pl;
+  pl.unit = tab;
+  constexpr int esz = (int)sizeof(T);
+  const int nux = g.P * esz / 16, nun = g.N / 4, nuk = g.K / 4;
+  uintptr_t al = (uintptr_t)a.x | (uintptr_t)a.Bh | (uintptr_t)a.Ch;
+  if (BWD) al |= (uintptr_t)a.dy;
+  if (a.feat != nullptr) al |= (uintptr_t)a.feat;
+  pl.vec = (g.P * esz) % 16 == 0 && g.N % 8 == 0 && (al & 15) == 0;
+  const int n0 = 9 * nux, n1 = n0 + (BWD ? 8 * nux : 0), n2 = n1 + 9 * nun, n3 = n2 + 9 * nun, n4 = n3 + (a.feat != nullptr ? 8 * nuk : 0);
+  pl.n = pl.vec ? n4 : 0;
+  for (int u = threadIdx.x; u < pl.n; u += blockDim.x) {
+    int kind, r, c, dr;
+    uint32_t dst;
+    if (u < n0) {
+      kind = 0; r = u / nux; c = u % nux; dr = r - 1;
+      dst = (uint32_t)(r * g.P * esz + c * 16);
+    } else if (u < n1) {
+      const int v = u - n0;
+      kind = 1; r = v / nux; c = v % nux; dr = r;
+      dst = (uint32_t)(rw.dy - rw.x) + (uint32_t)(r * g.P * esz + c * 16);
+    } else if (u < n2) {
+      const int v = u - n1;
+      kind = 2; r = v / nun; c = v % nun; dr = r - 1;
+      dst = (uint32_t)(reinterpret_cast<const unsigned char*>(rw.B) - rw.x) + (uint32_t)((r * g.N + c * 4) * 4);
+    } else if (u < n3) {
+      const int v = u - n2;
+      kind = 3; r = v / nun; c = v % nun; dr = r - 1;
+      dst = (uint32_t)(reinterpret_cast<const unsigned char*>(rw.C) - rw.x) + (uint32_t)((r * g.N + c * 4) * 4);
+    } else {
+      const int v = u - n3;
+      kind = 4; r = v / nuk; c = v % nuk; dr = r;
+      dst = (uint32_t)(reinterpret_cast<const unsigned char*>(rw.feat) - rw.x) + (uint32_t)((r * g.K + c * 4) * 4);
+    }
+    tab[u] = make_uint2(dst | ((uint32_t)kind << 24) | ((uint32_t)(dr + 1) << 28), (uint32_t)(c * 16));
+  }
+  return pl;
+}
+
 // Issue the copies of tokens [t0 - 1, t0 + 8) (t0 < 0: nothing).  Tokens outside [0, L) are zero-filled.
 template <typename T, bool BWD>
-__device__ __forceinline__ void hm_prefetch(const HmArgs& a, const HmGeo& g, const HmRaw& rw, int b, int h, int t0) {
+__device__ __forceinline__ void hm_prefetch(const HmArgs& a, const HmGeo& g, const HmPlan& pl, const HmRaw& rw, int b, int h, int t0) {
   if (t0 >= 0) {
     const int tid = threadIdx.x, nt = blockDim.x;
-    constexpr int EPW = 4 / (int)sizeof(T);          // elements per 4-byte word
-    const int wpr = g.P / EPW;                       // words per row
-    const T* x = (const T*)a.x;
-    for (int idx = tid; idx < 9 * wpr; idx += nt) {
-      const int r = idx / wpr, w = idx % wpr, tok = t0 - 1 + r;
-      const bool ok = tok >= 0 && tok < a.L;
-      cp_async4(rw.x + (size_t)idx * 4, x + ((int64_t)b * a.L + (ok ? tok : 0)) * a.H * g.P + h * g.P + w * EPW, ok);
-    }
-    if (BWD) {
-      const T* dy = (const T*)a.dy;
-      for (int idx = tid; idx < 8 * wpr; idx += nt) {
-        const int r = idx / wpr, w = idx % wpr, tok = t0 + r;
-        const bool ok = tok < a.L;
-        cp_async4(rw.dy + (size_t)idx * 4, dy + ((int64_t)b * a.L + (ok ? tok : 0)) * a.H * g.P + h * g.P + w * EPW, ok);
+    if (pl.vec) {
+      const uint32_t base = (uint32_t)__cvta_generic_to_shared(rw.x);
+      const int64_t bl = (int64_t)b * a.L;
+      const int64_t sx = (int64_t)a.H * g.P * (int)sizeof(T), sn = (int64_t)g.N * 4, sk = (int64_t)g.K * 4;   // bytes per token
+      const char* px = reinterpret_cast<const char*>(a.x) + (int64_t)h * g.P * (int)sizeof(T);
+      const char* pdy = BWD ? reinterpret_cast<const char*>(a.dy) + (int64_t)h * g.P * (int)sizeof(T) : px;
+      for (int u = tid; u < pl.n; u += nt) {
+        const uint2 d = pl.unit[u];
+        const int kind = (int)(d.x >> 24) & 7, tok = t0 + (int)(d.x >> 28) - 1;
+        const bool ok = tok >= 0 && tok < a.L;
+        const int64_t row = bl + (ok ? tok : 0);
+        const char* src = kind == 0   ? px + row * sx
+                          : kind == 1 ? pdy + row * sx
+                          : kind == 2 ? reinterpret_cast<const char*>(a.Bh) + row * sn
+                          : kind == 3 ? reinterpret_cast<const char*>(a.Ch) + row * sn
+                                      : reinterpret_cast<const char*>(a.feat) + row * sk;
+        cp_async16s(base + (d.x & 0xffffffu), src + d.y, ok);
       }
-    }
-    for (int idx = tid; idx < 9 * g.N; idx += nt) {
-      const int r = idx / g.N, n = idx % g.N, tok = t0 - 1 + r;
-      const bool ok = tok >= 0 && tok < a.L;
-      const int64_t o = ((int64_t)b * a.L + (ok ? tok : 0)) * g.N + n;
-      cp_async4(rw.B + idx, a.Bh + o, ok);
-      cp_async4(rw.C + idx, a.Ch + o, ok);
-    }
-    if (a.feat != nullptr)
-      for (int idx = tid; idx < 8 * g.K; idx += nt) {
-        const int r = idx / g.K, k = idx % g.K, tok = t0 + r;
-        const bool ok = tok < a.L;
-        cp_async4(rw.feat + idx, a.feat + ((int64_t)b * a.L + (ok ? tok : 0)) * g.K + k, ok);
+    } else {
+      constexpr int EPW = 4 / (int)sizeof(T);          // elements per 4-byte word
+      const int wpr = g.P / EPW;                       // words per row
+      const T* x = (const T*)a.x;
+      for (int idx = tid; idx < 9 * wpr; idx += nt) {
+        const int r = idx / wpr, w = idx % wpr, tok = t0 - 1 + r;
+        const bool ok = tok >= 0 && tok < a.L;
+        cp_async4(rw.x + (size_t)idx * 4, x + ((int64_t)b * a.L + (ok ? tok : 0)) * a.H * g.P + h * g.P + w * EPW, ok);
       }
+      if (BWD) {
+        const T* dy = (const T*)a.dy;
+        for (int idx = tid; idx < 8 * wpr; idx += nt) {
+          const int r = idx / wpr, w = idx % wpr, tok = t0 + r;
+          const bool ok = tok < a.L;
+          cp_async4(rw.dy + (size_t)idx * 4, dy + ((int64_t)b * a.L + (ok ? tok : 0)) * a.H * g.P + h * g.P + w * EPW, ok);
+        }
+      }
+      for (int idx = tid; idx < 9 * g.N; idx += nt) {
+        const int r = idx / g.N, n = idx % g.N, tok = t0 - 1 + r;
+        const bool ok = tok >= 0 && tok < a.L;
+        const int64_t o = ((int64_t)b * a.L + (ok ? tok : 0)) * g.N + n;
+        cp_async4(rw.B + idx, a.Bh + o, ok);
+        cp_async4(rw.C + idx, a.Ch + o, ok);
+      }
+      if (a.feat != nullptr)
+        for (int idx = tid; idx < 8 * g.K; idx += nt) {
+          const int r = idx / g.K, k = idx % g.K, tok = t0 + r;
+          const bool ok = tok < a.L;
+          cp_async4(rw.feat + idx, a.feat + ((int64_t)b * a.L + (ok ? tok : 0)) * g.K + k, ok);
+        }
+    }
     if (tid < 9) {
       const int tok = t0 - 1 + tid;
       const bool ok = tok >= 0 && tok < a.L;
@@ -135,7 +229,9 @@ __device__ __forceinline__ void hm_prefetch(const HmArgs& a, const HmGeo& g, con
 }
 
 // Build the tile of tokens [t0 - 1, t0 + 8) from its staged raw copy.  tile.thc holds the phase entering token t0 and
-// leaves holding the phase after token t0 + 7.  Ends with a __syncthreads().
+// leaves holding the phase after token t0 + 7.  Two barriers: one before the raw copy is read, one after the tile is
+// written.  Every (row, pair) item forms its own phase, the running sum from the entering phase in token order (row r
+// takes the first r terms), so no item waits for another; the item of the last row leaves the next entering phase.
 template <typename T, bool BWD>
 __device__ __forceinline__ void hm_build_tile(const HmArgs& a, const HmGeo& g, HmTile& tl, const HmRaw& rw, int b, int h, int t0) {
   const int tid = threadIdx.x, nt = blockDim.x;
@@ -151,48 +247,38 @@ __device__ __forceinline__ void hm_build_tile(const HmArgs& a, const HmGeo& g, H
     tl.dts[tid] = rw.dt[tid];
     tl.lams[tid] = a.lam ? rw.lam[tid] : 1.f;
   }
-  // running phase per pair: row 0 (token t0 - 1) sees the entering phase, row r the phase after token t0 + r - 1
-  float* ang = tl.Ct;   // rows of Ct are not yet written: borrow [9][K] of it for the angles
-  if (a.feat != nullptr && tid < g.K) {
-    float th = tl.thc[tid];
-    ang[tid] = th;
-#pragma unroll
-    for (int r = 1; r < 9; ++r) {
-      th = fmaf(rw.dt[r], rw.feat[(r - 1) * g.K + tid], th);       // zero-filled past the end of the sequence
-      ang[r * g.K + tid] = th;
-    }
-    tl.thc[tid] = th;
-  }
-  __syncthreads();
-  // maps: bias -> rotate.  The angles are read before Ct is overwritten (a pair's Ct entries sit at [r][2k], [r][2k+1],
-  // its angle at [r][k]: a different thread's pair may own that slot), so stage the angles in registers first.
-  const int npair = 9 * g.K;
-  constexpr int MAXP = 20;
-  float angs[MAXP];
-  int cnt = 0;
-  for (int idx = tid; idx < npair && cnt < MAXP; idx += nt) angs[cnt++] = a.feat ? ang[idx] : 0.f;
-  __syncthreads();
-  cnt = 0;
-  for (int idx = tid; idx < npair && cnt < MAXP; idx += nt, ++cnt) {
-    const int r = idx / g.K, k = idx % g.K, tok = t0 - 1 + r;
+  const bool rotating = a.feat != nullptr;
+  const int lgK = 31 - __clz(g.K);                      // K = N / 2 is a power of two
+  for (int idx = tid; idx < 9 * g.K; idx += nt) {
+    const int r = idx >> lgK, k = idx & (g.K - 1), tok = t0 - 1 + r;
     float b0 = 0.f, b1 = 0.f, c0 = 0.f, c1 = 0.f;
     if (tok >= 0 && tok < a.L) {
-      b0 = rw.B[r * g.N + 2 * k]; b1 = rw.B[r * g.N + 2 * k + 1]; c0 = rw.C[r * g.N + 2 * k]; c1 = rw.C[r * g.N + 2 * k + 1];
-      if (a.beta_b) { b0 += a.beta_b[h * g.N + 2 * k]; b1 += a.beta_b[h * g.N + 2 * k + 1]; }
-      if (a.beta_c) { c0 += a.beta_c[h * g.N + 2 * k]; c1 += a.beta_c[h * g.N + 2 * k + 1]; }
+      const float2 bv = *reinterpret_cast<const float2*>(rw.B + r * g.N + 2 * k), cv = *reinterpret_cast<const float2*>(rw.C + r * g.N + 2 * k);
+      const float2 bbv = *reinterpret_cast<const float2*>(tl.bb + 2 * k), bcv = *reinterpret_cast<const float2*>(tl.bc + 2 * k);
+      b0 = bv.x + bbv.x; b1 = bv.y + bbv.y; c0 = cv.x + bcv.x; c1 = cv.y + bcv.y;
     }
     float cb = 1.f, sb = 0.f, cc = 1.f, sc = 0.f;
-    if (a.feat != nullptr && a.rot[k]) {
-      sincosf(angs[cnt], &sb, &cb);
-      sincosf(a.theta_h ? angs[cnt] + a.theta_h[h * g.K + k] : angs[cnt], &sc, &cc);
+    if (rotating) {
+      // row 0 (token t0 - 1) sees the entering phase, row r the phase after token t0 + r - 1 (clocks and features are
+      // zero-filled past the end of the sequence)
+      float th = tl.thc[k];
+      for (int j = 1; j <= r; ++j) th = fmaf(rw.dt[j], rw.feat[(j - 1) * g.K + k], th);
+      if (r == 8) tl.thn[k] = th;
+      if (tl.rotm[k] != 0.f) {
+        sincosf(th, &sb, &cb);
+        sincosf(th + tl.thh[k], &sc, &cc);
+      }
     }
-    tl.Bt[r * g.N + 2 * k] = b0 * cb - b1 * sb;
-    tl.Bt[r * g.N + 2 * k + 1] = b0 * sb + b1 * cb;
-    tl.Ct[r * g.N + 2 * k] = c0 * cc - c1 * sc;
-    tl.Ct[r * g.N + 2 * k + 1] = c0 * sc + c1 * cc;
+    *reinterpret_cast<float2*>(tl.Bt + r * g.N + 2 * k) = make_float2(b0 * cb - b1 * sb, b0 * sb + b1 * cb);
+    *reinterpret_cast<float2*>(tl.Ct + r * g.N + 2 * k) = make_float2(c0 * cc - c1 * sc, c0 * sc + c1 * cc);
     if (BWD) { tl.cB[idx] = cb; tl.sB[idx] = sb; tl.cC[idx] = cc; tl.sC[idx] = sc; }
   }
   __syncthreads();
+  if (rotating) {
+    float* t = tl.thc;
+    tl.thc = tl.thn;
+    tl.thn = t;
+  }
 }
 
 // sum over the NG consecutive lanes of a row group (NG a power of two <= 32)
@@ -288,9 +374,12 @@ __global__ void __launch_bounds__(256) hm_fwd_kernel(const HmArgs a) {
   float* ys = hm_tile_carve(tl, smf, g, false);      // [8][P]
   HmRaw raw[2];
   float* rp = hm_raw_carve(raw[0], ys + 8 * g.P, g);
-  hm_raw_carve(raw[1], rp, g);
+  rp = hm_raw_carve(raw[1], rp, g);
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
-  hm_prefetch<T, false>(a, g, raw[0], b, h, 0);
+  const HmPlan plan = hm_plan_build<T, false>(a, g, reinterpret_cast<uint2*>(rp), raw[0]);
+  hm_tile_consts(a, g, tl, h);
+  __syncthreads();
+  hm_prefetch<T, false>(a, g, plan, raw[0], b, h, 0);
   const HmThread th = hm_thread(g);
   constexpr bool trap = TRAP;
   const int64_t bh = (int64_t)b * a.H + h;
@@ -312,7 +401,7 @@ __global__ void __launch_bounds__(256) hm_fwd_kernel(const HmArgs a) {
     }
     const int it = t0 / HM_TT;
     hm_build_tile<T, false>(a, g, tl, raw[it & 1], b, h, t0);
-    hm_prefetch<T, false>(a, g, raw[(it + 1) & 1], b, h, t0 + HM_TT < a.L ? t0 + HM_TT : -1);
+    hm_prefetch<T, false>(a, g, plan, raw[(it + 1) & 1], b, h, t0 + HM_TT < a.L ? t0 + HM_TT : -1);
     const int nv = min(HM_TT, a.L - t0);
 #pragma unroll
     for (int tt = 0; tt < HM_TT; ++tt) {
@@ -371,12 +460,16 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
   float* partC = p; p += 8 * g.nwarp * g.N;
   float* partS = p; p += 8 * g.nwarp * 2;                // [tt][warp][ddelta, dlam]
   float* dxs = p;   p += 8 * g.P;
-  float* phs = p;   p += 8 * g.K;                        // [tt][k] feat * suffix (phase part of ddelta)
+  float* phs = p;   p += 8 * g.K;                        // [tt][k] phase gradient of the token, then feat * suffix (phase part of ddelta)
+  float* dcs = p;   p += 8 * g.K;                        // [tt][k] the C map's share of the phase gradient (-> dtheta_h)
   float* Ssuf = p;  p += r4(g.K);                          // suffix sum of dTheta carried backwards in time
   float* red = p;   p += 32;
   HmRaw raw[2];
   p = hm_raw_carve(raw[0], p, g);
   p = hm_raw_carve(raw[1], p, g);
+  const HmPlan plan = hm_plan_build<T, true>(a, g, reinterpret_cast<uint2*>(p), raw[0]);
+  hm_tile_consts(a, g, tl, blockIdx.x);
+  __syncthreads();
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // The tiles are visited in a fixed order: per chunk (last first) the first nsub - 1 sub-chunks forwards (replay), then
   // all nsub sub-chunks backwards.  item_t0(c, k) = first token of the k-th visit of chunk c, continuing into chunk c - 1.
@@ -392,7 +485,7 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
     return c * HM_TC + (k < ns - 1 ? k : (ns - 1) - (k - (ns - 1))) * HM_TT;
   };
   int seq = 0;
-  hm_prefetch<T, true>(a, g, raw[0], b, h, item_t0(a.nck - 1, 0));
+  hm_prefetch<T, true>(a, g, plan, raw[0], b, h, item_t0(a.nck - 1, 0));
   const HmThread th = hm_thread(g);
   constexpr bool trap = TRAP;
   const int64_t bh = (int64_t)b * a.H + h;
@@ -404,7 +497,7 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
   if (a.dh_final) load16(G, a.dh_final + bh * PN, th, g.N);
   if (tid < g.K) Ssuf[tid] = a.dtheta_final ? a.dtheta_final[bh * g.K + tid] : 0.f;
   float lagn = 0.f;                       // delta_{t+1} (1 - lam_{t+1}) of the token processed just before (in reverse)
-  float acc_bb = 0.f, acc_bc = 0.f;       // thread n < N: dbeta_b[n], dbeta_c[n]
+  float acc_bb = 0.f, acc_bc = 0.f;       // the last N threads: dbeta_b[n], dbeta_c[n] of row n = tid - (threads - N)
   float acc_th = 0.f;                     // thread k < K: dtheta_h[k]
   float acc_D = 0.f;                      // thread p < P: partial of dD
   const float Dh = a.D ? a.D[h] : 0.f;
@@ -429,7 +522,7 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
         hm_build_tile<T, false>(a, g, tl, raw[seq & 1], b, h, t0);
         ++item;
         ++seq;
-        hm_prefetch<T, true>(a, g, raw[seq & 1], b, h, item_t0(c, item));
+        hm_prefetch<T, true>(a, g, plan, raw[seq & 1], b, h, item_t0(c, item));
         if (j == 0) {
 #pragma unroll
           for (int e = 0; e < 16; ++e) prv[e] = 0.f;
@@ -464,7 +557,7 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
       hm_build_tile<T, true>(a, g, tl, raw[seq & 1], b, h, t0);
       ++item;
       ++seq;
-      hm_prefetch<T, true>(a, g, raw[seq & 1], b, h, item_t0(c, item));
+      hm_prefetch<T, true>(a, g, plan, raw[seq & 1], b, h, item_t0(c, item));
       // The sub-chunk is walked in two halves of 4 tokens (second half first): a half's 4 states are held in registers;
       // the first half is replayed once more from the sub-chunk boundary.  (Keeping all 8 states costs 128 registers
       // and an unrolled body that no longer fits the instruction cache.)
@@ -599,56 +692,60 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
         partC[(tt * g.nwarp) * g.N + n] = sc;
       }
       __syncthreads();
+      {
+        // back through the rotation: every (token, pair) is its own item; its phase gradient goes to phs / dcs
+        const int lgK = 31 - __clz(g.K);
+        for (int idx = tid; idx < HM_TT * g.K; idx += blockDim.x) {
+          const int tt = idx >> lgK, k = idx & (g.K - 1);
+          float dB = 0.f, dC = 0.f;
+          if (t0 + tt < a.L && tl.rotm[k] != 0.f) {
+            float2* gb = reinterpret_cast<float2*>(partB + (tt * g.nwarp) * g.N + 2 * k);
+            float2* gc = reinterpret_cast<float2*>(partC + (tt * g.nwarp) * g.N + 2 * k);
+            const float2 vb = *gb, vc = *gc;
+            const int r = tt + 1;
+            const float2 Bv = *reinterpret_cast<const float2*>(tl.Bt + r * g.N + 2 * k), Cv = *reinterpret_cast<const float2*>(tl.Ct + r * g.N + 2 * k);
+            dB = vb.y * Bv.x - vb.x * Bv.y;
+            dC = vc.y * Cv.x - vc.x * Cv.y;
+            const float cb = tl.cB[r * g.K + k], sb = tl.sB[r * g.K + k], cc = tl.cC[r * g.K + k], sc = tl.sC[r * g.K + k];
+            *gb = make_float2(vb.x * cb + vb.y * sb, -vb.x * sb + vb.y * cb);
+            *gc = make_float2(vc.x * cc + vc.y * sc, -vc.x * sc + vc.y * cc);
+          }
+          phs[idx] = dB + dC;
+          dcs[idx] = dC;
+        }
+      }
+      __syncthreads();
+      // Three independent jobs on different warps: the suffix sum of the phase gradient (first K threads, newest token
+      // first), the map-gradient rows (last N threads), the drive gradient (everyone).
       if (tid < g.K) {
-        // back through the rotation, newest token first (suffix sum of the phase gradient)
         const int k = tid;
         float S = Ssuf[k];
+        const bool rot = tl.rotm[k] != 0.f;
         for (int tt = HM_TT - 1; tt >= 0; --tt) {
           const int tok = t0 + tt;
           if (tok >= a.L) { phs[tt * g.K + k] = 0.f; continue; }
-          float* gb = partB + (tt * g.nwarp) * g.N + 2 * k;
-          float* gc = partC + (tt * g.nwarp) * g.N + 2 * k;
           float ph = 0.f;
-          if (a.feat != nullptr && a.rot[k]) {
-            const int r = tt + 1;
-            const float B0 = tl.Bt[r * g.N + 2 * k], B1 = tl.Bt[r * g.N + 2 * k + 1];
-            const float C0 = tl.Ct[r * g.N + 2 * k], C1 = tl.Ct[r * g.N + 2 * k + 1];
-            const float dthB = gb[1] * B0 - gb[0] * B1, dthC = gc[1] * C0 - gc[0] * C1;
-            const float cb = tl.cB[r * g.K + k], sb = tl.sB[r * g.K + k], cc = tl.cC[r * g.K + k], sc = tl.sC[r * g.K + k];
-            const float g0 = gb[0] * cb + gb[1] * sb, g1 = -gb[0] * sb + gb[1] * cb;
-            const float e0 = gc[0] * cc + gc[1] * sc, e1 = -gc[0] * sc + gc[1] * cc;
-            gb[0] = g0; gb[1] = g1; gc[0] = e0; gc[1] = e1;
-            acc_th += dthC;
-            S += dthB + dthC;
-            const float ft = raw[(seq + 1) & 1].feat[tt * g.K + k];      // this tile's staged copy (seq already advanced)
-            ph = ft * S;
-            if (a.dfeat_part) a.dfeat_part[(((int64_t)h * a.B + b) * a.L + tok) * g.K + k] = tl.dts[r] * S;
-          } else if (a.dfeat_part) {
-            a.dfeat_part[(((int64_t)h * a.B + b) * a.L + tok) * g.K + k] = 0.f;
+          if (rot) {
+            acc_th += dcs[tt * g.K + k];
+            S += phs[tt * g.K + k];
+            ph = raw[(seq + 1) & 1].feat[tt * g.K + k] * S;      // this tile's staged copy (seq already advanced)
           }
+          if (a.dfeat_part) a.dfeat_part[(((int64_t)h * a.B + b) * a.L + tok) * g.K + k] = rot ? tl.dts[tt + 1] * S : 0.f;
           phs[tt * g.K + k] = ph;
         }
         Ssuf[k] = S;
       }
-      __syncthreads();
-      if (tid < g.N) {
+      if (tid >= (int)blockDim.x - g.N) {
+        const int n = tid - ((int)blockDim.x - g.N);
         for (int tt = 0; tt < HM_TT; ++tt) {
           const int tok = t0 + tt;
           if (tok >= a.L) break;
-          const float vb = partB[(tt * g.nwarp) * g.N + tid], vc = partC[(tt * g.nwarp) * g.N + tid];
-          a.dBh_part[(((int64_t)h * a.B + b) * a.L + tok) * g.N + tid] = vb;
-          a.dCh_part[(((int64_t)h * a.B + b) * a.L + tok) * g.N + tid] = vc;
+          const float vb = partB[(tt * g.nwarp) * g.N + n], vc = partC[(tt * g.nwarp) * g.N + n];
+          a.dBh_part[(((int64_t)h * a.B + b) * a.L + tok) * g.N + n] = vb;
+          a.dCh_part[(((int64_t)h * a.B + b) * a.L + tok) * g.N + n] = vc;
           acc_bb += vb;
           acc_bc += vc;
         }
-      }
-      if (tid < HM_TT && t0 + tid < a.L) {
-        const int tt = tid, tok = t0 + tt;
-        float sD = 0.f, sL = 0.f;
-        for (int w = 0; w < g.nwarp; ++w) { sD += partS[(tt * g.nwarp + w) * 2]; sL += partS[(tt * g.nwarp + w) * 2 + 1]; }
-        for (int k = 0; k < g.K; ++k) sD += phs[tt * g.K + k];
-        a.ddelta[((int64_t)b * a.L + tok) * a.H + h] = sD;
-        if (a.dlam) a.dlam[((int64_t)b * a.L + tok) * a.H + h] = sL;
       }
       for (int idx = tid; idx < HM_TT * g.P; idx += blockDim.x) {
         const int tt = idx / g.P, pp = idx % g.P;
@@ -656,6 +753,24 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
       }
       if (tid < g.P)
         for (int tt = 0; tt < HM_TT; ++tt) acc_D = fmaf(tl.dys[tt * g.P + tid], tl.xs[(tt + 1) * g.P + tid], acc_D);
+      __syncthreads();
+      // clock gradients: one warp per token sums the per-warp partials and the phase parts (lanes take strided slices, the
+      // lane sums meet in a butterfly: a fixed order)
+      for (int tt = warp; tt < HM_TT; tt += g.nwarp) {
+        if (t0 + tt >= a.L) continue;
+        float sD = 0.f, sL = 0.f;
+        for (int w = lane; w < g.nwarp; w += 32) { sD += partS[(tt * g.nwarp + w) * 2]; sL += partS[(tt * g.nwarp + w) * 2 + 1]; }
+        for (int k = lane; k < g.K; k += 32) sD += phs[tt * g.K + k];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          sD += __shfl_xor_sync(0xffffffffu, sD, o);
+          sL += __shfl_xor_sync(0xffffffffu, sL, o);
+        }
+        if (lane == 0) {
+          a.ddelta[((int64_t)b * a.L + t0 + tt) * a.H + h] = sD;
+          if (a.dlam) a.dlam[((int64_t)b * a.L + t0 + tt) * a.H + h] = sL;
+        }
+      }
       __syncthreads();
     }
   }
@@ -672,9 +787,10 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
     for (int e = 0; e < 16; ++e) dA[e] *= HM_LN2;       // the sums were taken with rate2 = rate log2(e)
     store16(dA, a.dA_log_part + bh * PN, th, g.N);
   }
-  if (tid < g.N) {
-    if (a.dbeta_b_part) a.dbeta_b_part[bh * g.N + tid] = acc_bb;
-    if (a.dbeta_c_part) a.dbeta_c_part[bh * g.N + tid] = acc_bc;
+  if (tid >= (int)blockDim.x - g.N) {
+    const int n = tid - ((int)blockDim.x - g.N);
+    if (a.dbeta_b_part) a.dbeta_b_part[bh * g.N + n] = acc_bb;
+    if (a.dbeta_c_part) a.dbeta_c_part[bh * g.N + n] = acc_bc;
   }
   if (tid < g.K) {
     if (a.dtheta_h_part) a.dtheta_h_part[bh * g.K + tid] = acc_th;
@@ -697,6 +813,12 @@ static int hm_check(const HmArgs* a, int dtype, const char* who, bool bwd) {
   const int NG = a->N / 4;
   ORBIT_REQUIRE(a->P % 4 == 0 && a->N % 4 == 0 && NG <= 32 && (NG & (NG - 1)) == 0 && (a->P / 4) * NG <= 256, ERR_UNSUPPORTED,
                 "%s: serves P and N multiples of 4 with N/4 a power of two <= 32 and (P/4)(N/4) <= 256, got P=%d N=%d", who, a->P, a->N);
+  {
+    const HmGeo g = hm_geo(a->P, a->N);
+    ORBIT_REQUIRE(g.nthr >= a->N && g.nthr >= a->P, ERR_UNSUPPORTED,
+                  "%s: a CTA of (P/4)(N/4) threads, rounded up to a warp, must cover P and N (P=%d N=%d give %d threads)", who, a->P, a->N,
+                  g.nthr);
+  }
   ORBIT_REQUIRE(a->x && a->delta && a->A_log && a->Bh && a->Ch, ERR_BAD_ARG, "%s: null x/delta/A_log/Bh/Ch", who);
   ORBIT_REQUIRE(a->feat == nullptr || a->rot != nullptr, ERR_BAD_ARG, "%s: feat needs the rot mask", who);
   ORBIT_REQUIRE(a->Tc > 0 && a->Tc % HM_TT == 0 && a->nck == (a->L + a->Tc - 1) / a->Tc, ERR_BAD_ARG,
@@ -719,10 +841,10 @@ static int hm_check(const HmArgs* a, int dtype, const char* who, bool bwd) {
   return OK;
 }
 
-static size_t hm_smem_fwd(const HmGeo& g) { return sizeof(float) * (hm_tile_floats(g, false) + 8 * g.P + 2 * hm_raw_floats(g)); }
+static size_t hm_smem_fwd(const HmGeo& g) { return sizeof(float) * (hm_tile_floats(g, false) + 8 * g.P + 2 * hm_raw_floats(g) + hm_plan_floats(g)); }
 static size_t hm_smem_bwd(const HmGeo& g) {
   return sizeof(float) * (hm_tile_floats(g, true) + (size_t)HM_SUB * g.P * g.N + r4(HM_SUB * g.K) + 2 * 8 * g.nwarp * g.N +
-                          8 * g.nwarp * 2 + 8 * g.P + 8 * g.K + r4(g.K) + 32 + 2 * hm_raw_floats(g));
+                          8 * g.nwarp * 2 + 8 * g.P + 2 * 8 * g.K + r4(g.K) + 32 + 2 * hm_raw_floats(g) + hm_plan_floats(g));
 }
 
 }  // namespace orbit
