@@ -26,9 +26,10 @@ constexpr int HM_SUB = HM_TC / HM_TT;
 struct HmGeo {
   int P, N, K, NG, active, nthr, nwarp;
 };
-__host__ __device__ inline HmGeo hm_geo(int P, int N) {
-  HmGeo g;
-  g.P = P; g.N = N; g.K = N / 2; g.NG = N / 4;
+// A thread owns 4 channels x NJ rows of the state (NJ = 4, or 2 for twice the threads at half the registers each).
+__host__ __device__ constexpr HmGeo hm_geo(int P, int N, int NJ = 4) {
+  HmGeo g{};
+  g.P = P; g.N = N; g.K = N / 2; g.NG = N / NJ;
   g.active = (P / 4) * g.NG;
   g.nthr = (g.active + 31) / 32 * 32;
   g.nwarp = g.nthr / 32;
@@ -332,16 +333,26 @@ __device__ __forceinline__ float fast_ex2(float x) {
 }
 
 // one forward token on the thread's 4 x 4 tile.  rate2 = -exp(A_log) log2(e), so that a = 2^(rate2 delta).
-template <bool TRAP>
-__device__ __forceinline__ void hm_step(float (&hs)[16], float (&prv)[16], const float (&rate2)[16], const float4 x4,
-                                        const float4 b4, float d, float lm) {
-  const float xv[4] = {x4.x, x4.y, x4.z, x4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+template <int NJ>
+__device__ __forceinline__ void load_rows(float (&v)[NJ], const float* p) {
+  if constexpr (NJ == 4) {
+    const float4 r = *reinterpret_cast<const float4*>(p);
+    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+  } else {
+    const float2 r = *reinterpret_cast<const float2*>(p);
+    v[0] = r.x; v[1] = r.y;
+  }
+}
+template <bool TRAP, int NJ>
+__device__ __forceinline__ void hm_step(float (&hs)[4 * NJ], float (&prv)[4 * NJ], const float (&rate2)[4 * NJ], const float4 x4,
+                                        const float (&bv)[NJ], float d, float lm) {
+  const float xv[4] = {x4.x, x4.y, x4.z, x4.w};
   const float dl = d * lm, dg = d * (1.f - lm);
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int e = i * 4 + j;
+    for (int j = 0; j < NJ; ++j) {
+      const int e = i * NJ + j;
       const float av = fast_ex2(rate2[e] * d);
       const float raw = xv[i] * bv[j];
       if (TRAP) hs[e] = fmaf(av, fmaf(dg, prv[e], hs[e]), dl * raw);
@@ -350,26 +361,36 @@ __device__ __forceinline__ void hm_step(float (&hs)[16], float (&prv)[16], const
     }
 }
 
-__device__ __forceinline__ void load16(float (&v)[16], const float* base, const HmThread& th, int N) {
+// the thread's 4 x NJ tile of a [P, N] array
+template <int NJ>
+__device__ __forceinline__ void load_tile(float (&v)[4 * NJ], const float* base, const HmThread& th, int N) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float4 r = *reinterpret_cast<const float4*>(base + (int64_t)(th.pg * 4 + i) * N + th.ng * 4);
-    v[i * 4] = r.x; v[i * 4 + 1] = r.y; v[i * 4 + 2] = r.z; v[i * 4 + 3] = r.w;
+    float r[NJ];
+    load_rows<NJ>(r, base + (int64_t)(th.pg * 4 + i) * N + th.ng * NJ);
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) v[i * NJ + j] = r[j];
   }
 }
-__device__ __forceinline__ void store16(const float (&v)[16], float* base, const HmThread& th, int N) {
+template <int NJ>
+__device__ __forceinline__ void store_tile(const float (&v)[4 * NJ], float* base, const HmThread& th, int N) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
-    *reinterpret_cast<float4*>(base + (int64_t)(th.pg * 4 + i) * N + th.ng * 4) = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+  for (int i = 0; i < 4; ++i) {
+    float* q = base + (int64_t)(th.pg * 4 + i) * N + th.ng * NJ;
+    if constexpr (NJ == 4) *reinterpret_cast<float4*>(q) = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+    else *reinterpret_cast<float2*>(q) = make_float2(v[i * 2], v[i * 2 + 1]);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------------------------------------------
-template <typename T, bool TRAP>
+// CP, CN > 0: the geometry P, N as compile-time constants (every shared-memory offset and index split folds away, which
+// is worth tens of registers); 0: read from the arguments.
+template <typename T, bool TRAP, int CP, int CN>
 __global__ void __launch_bounds__(256) hm_fwd_kernel(const HmArgs a) {
   extern __shared__ __align__(16) float smf[];
-  const HmGeo g = hm_geo(a.P, a.N);
+  const HmGeo g = CP > 0 ? hm_geo(CP, CN) : hm_geo(a.P, a.N);
   HmTile tl;
   float* ys = hm_tile_carve(tl, smf, g, false);      // [8][P]
   HmRaw raw[2];
@@ -384,11 +405,11 @@ __global__ void __launch_bounds__(256) hm_fwd_kernel(const HmArgs a) {
   constexpr bool trap = TRAP;
   const int64_t bh = (int64_t)b * a.H + h;
   float hs[16], prv[16], rate[16];
-  load16(rate, a.A_log + (int64_t)h * g.P * g.N, th, g.N);
+  load_tile<4>(rate, a.A_log + (int64_t)h * g.P * g.N, th, g.N);
 #pragma unroll
   for (int e = 0; e < 16; ++e) { rate[e] = -__expf(rate[e]) * HM_LOG2E; hs[e] = 0.f; prv[e] = 0.f; }
-  if (a.h_init) load16(hs, a.h_init + bh * g.P * g.N, th, g.N);
-  if (a.write_prev && trap) load16(prv, a.write_prev + bh * g.P * g.N, th, g.N);
+  if (a.h_init) load_tile<4>(hs, a.h_init + bh * g.P * g.N, th, g.N);
+  if (a.write_prev && trap) load_tile<4>(prv, a.write_prev + bh * g.P * g.N, th, g.N);
   if (tid < g.K) tl.thc[tid] = a.theta_init ? a.theta_init[bh * g.K + tid] : 0.f;
   const float Dh = a.D ? a.D[h] : 0.f;
   __syncthreads();
@@ -396,7 +417,7 @@ __global__ void __launch_bounds__(256) hm_fwd_kernel(const HmArgs a) {
   for (int t0 = 0; t0 < a.L; t0 += HM_TT) {
     if (a.hck != nullptr && t0 % a.Tc == 0) {
       const int c = t0 / a.Tc;
-      if (th.active) store16(hs, a.hck + (bh * a.nck + c) * g.P * g.N, th, g.N);
+      if (th.active) store_tile<4>(hs, a.hck + (bh * a.nck + c) * g.P * g.N, th, g.N);
       if (a.thck != nullptr && tid < g.K) a.thck[(bh * a.nck + c) * g.K + tid] = tl.thc[tid];
     }
     const int it = t0 / HM_TT;
@@ -407,10 +428,11 @@ __global__ void __launch_bounds__(256) hm_fwd_kernel(const HmArgs a) {
     for (int tt = 0; tt < HM_TT; ++tt) {
       if (tt < nv) {
         const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + (tt + 1) * g.P + th.pg * 4);
-        const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + (tt + 1) * g.N + th.ng * 4);
-        const float4 c4 = *reinterpret_cast<const float4*>(tl.Ct + (tt + 1) * g.N + th.ng * 4);
-        hm_step<TRAP>(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1]);
-        const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, xv[4] = {x4.x, x4.y, x4.z, x4.w};
+        float bv[4], cv[4];
+        load_rows<4>(bv, tl.Bt + (tt + 1) * g.N + th.ng * 4);
+        load_rows<4>(cv, tl.Ct + (tt + 1) * g.N + th.ng * 4);
+        hm_step<TRAP, 4>(hs, prv, rate, x4, bv, tl.dts[tt + 1], tl.lams[tt + 1]);
+        const float xv[4] = {x4.x, x4.y, x4.z, x4.w};
         float yp[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -439,8 +461,8 @@ __global__ void __launch_bounds__(256) hm_fwd_kernel(const HmArgs a) {
     // the next tile's builder starts with writes to xs (not ys) and syncs before anything reads ys again
   }
   if (th.active) {
-    store16(hs, a.h_final + bh * g.P * g.N, th, g.N);
-    if (a.write_last) store16(prv, a.write_last + bh * g.P * g.N, th, g.N);
+    store_tile<4>(hs, a.h_final + bh * g.P * g.N, th, g.N);
+    if (a.write_last) store_tile<4>(prv, a.write_last + bh * g.P * g.N, th, g.N);
   }
   if (a.theta_final != nullptr && tid < g.K) a.theta_final[bh * g.K + tid] = tl.thc[tid];
 }
@@ -448,10 +470,12 @@ __global__ void __launch_bounds__(256) hm_fwd_kernel(const HmArgs a) {
 // ---------------------------------------------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------------------------------------------
-template <typename T, bool TRAP>
-__global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
+// NJ = rows of the state per thread (4 x NJ tile).  CP, CN as in the forward kernel.
+template <typename T, bool TRAP, int NJ, int CP, int CN>
+__global__ void __launch_bounds__(NJ == 2 ? 512 : 256, 1) hm_bwd_kernel(const HmArgs a) {
+  constexpr int E = 4 * NJ;
   extern __shared__ __align__(16) float smf[];
-  const HmGeo g = hm_geo(a.P, a.N);
+  const HmGeo g = CP > 0 ? hm_geo(CP, CN, NJ) : hm_geo(a.P, a.N, NJ);
   HmTile tl;
   float* p = hm_tile_carve(tl, smf, g, true);
   float* hsub = p;  p += (size_t)HM_SUB * g.P * g.N;     // state entering each sub-chunk of the current chunk
@@ -490,11 +514,11 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
   constexpr bool trap = TRAP;
   const int64_t bh = (int64_t)b * a.H + h;
   const int64_t PN = (int64_t)g.P * g.N;
-  float rate[16], G[16], dA[16];
-  load16(rate, a.A_log + (int64_t)h * PN, th, g.N);
+  float rate[E], G[E], dA[E];
+  load_tile<NJ>(rate, a.A_log + (int64_t)h * PN, th, g.N);
 #pragma unroll
-  for (int e = 0; e < 16; ++e) { rate[e] = -__expf(rate[e]) * HM_LOG2E; G[e] = 0.f; dA[e] = 0.f; }
-  if (a.dh_final) load16(G, a.dh_final + bh * PN, th, g.N);
+  for (int e = 0; e < E; ++e) { rate[e] = -__expf(rate[e]) * HM_LOG2E; G[e] = 0.f; dA[e] = 0.f; }
+  if (a.dh_final) load_tile<NJ>(G, a.dh_final + bh * PN, th, g.N);
   if (tid < g.K) Ssuf[tid] = a.dtheta_final ? a.dtheta_final[bh * g.K + tid] : 0.f;
   float lagn = 0.f;                       // delta_{t+1} (1 - lam_{t+1}) of the token processed just before (in reverse)
   float acc_bb = 0.f, acc_bc = 0.f;       // the last N threads: dbeta_b[n], dbeta_c[n] of row n = tid - (threads - N)
@@ -509,14 +533,14 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
     int item = 0;
     // ---- replay the chunk once, keeping the state and phase that enter each sub-chunk
     {
-      float hs[16], prv[16];
-      load16(hs, a.hck + (bh * a.nck + c) * PN, th, g.N);
+      float hs[E], prv[E];
+      load_tile<NJ>(hs, a.hck + (bh * a.nck + c) * PN, th, g.N);
       if (tid < g.K) tl.thc[tid] = a.thck ? a.thck[(bh * a.nck + c) * g.K + tid] : 0.f;
       __syncthreads();
       for (int j = 0; j < HM_SUB; ++j) {
         const int t0 = tc0 + j * HM_TT;
         if (t0 >= a.L) break;
-        if (th.active) store16(hs, hsub + (size_t)j * PN, th, g.N);
+        if (th.active) store_tile<NJ>(hs, hsub + (size_t)j * PN, th, g.N);
         if (tid < g.K) thsub[j * g.K + tid] = tl.thc[tid];
         if (j == n_sub(c) - 1) break;      // the last sub-chunk is replayed below anyway
         hm_build_tile<T, false>(a, g, tl, raw[seq & 1], b, h, t0);
@@ -525,24 +549,26 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
         hm_prefetch<T, true>(a, g, plan, raw[seq & 1], b, h, item_t0(c, item));
         if (j == 0) {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) prv[e] = 0.f;
+          for (int e = 0; e < E; ++e) prv[e] = 0.f;
           if (trap) {
             if (t0 == 0) {
-              if (a.write_prev) load16(prv, a.write_prev + bh * PN, th, g.N);
+              if (a.write_prev) load_tile<NJ>(prv, a.write_prev + bh * PN, th, g.N);
             } else {
               const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + th.pg * 4);
-              const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + th.ng * 4);
-              const float xv[4] = {x4.x, x4.y, x4.z, x4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+              const float xv[4] = {x4.x, x4.y, x4.z, x4.w};
+              float bv[NJ];
+              load_rows<NJ>(bv, tl.Bt + th.ng * NJ);
 #pragma unroll
-              for (int e = 0; e < 16; ++e) prv[e] = xv[e >> 2] * bv[e & 3];
+              for (int e = 0; e < E; ++e) prv[e] = xv[e / NJ] * bv[e % NJ];
             }
           }
         }
         const int nv = min(HM_TT, a.L - t0);
         for (int tt = 0; tt < nv; ++tt) {
           const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + (tt + 1) * g.P + th.pg * 4);
-          const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + (tt + 1) * g.N + th.ng * 4);
-          hm_step<TRAP>(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1]);
+          float bv[NJ];
+          load_rows<NJ>(bv, tl.Bt + (tt + 1) * g.N + th.ng * NJ);
+          hm_step<TRAP, NJ>(hs, prv, rate, x4, bv, tl.dts[tt + 1], tl.lams[tt + 1]);
         }
         __syncthreads();
       }
@@ -561,44 +587,47 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
       // The sub-chunk is walked in two halves of 4 tokens (second half first): a half's 4 states are held in registers;
       // the first half is replayed once more from the sub-chunk boundary.  (Keeping all 8 states costs 128 registers
       // and an unrolled body that no longer fits the instruction cache.)
-      float hist[4][16];
+      float hist[4][E];
 #pragma unroll 1
       for (int half = 1; half >= 0; --half) {
-      float prv0[16];                            // raw write of the token before token 4 * half
+      float prv0[E];                            // raw write of the token before token 4 * half
       {
-        float hs[16], prv[16];
-        load16(hs, hsub + (size_t)j * PN, th, g.N);
+        float hs[E], prv[E];
+        load_tile<NJ>(hs, hsub + (size_t)j * PN, th, g.N);
 #pragma unroll
-        for (int e = 0; e < 16; ++e) prv[e] = 0.f;
+        for (int e = 0; e < E; ++e) prv[e] = 0.f;
         if (trap) {
           if (t0 == 0) {
-            if (a.write_prev) load16(prv, a.write_prev + bh * PN, th, g.N);
+            if (a.write_prev) load_tile<NJ>(prv, a.write_prev + bh * PN, th, g.N);
           } else {
             const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + th.pg * 4);
-            const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + th.ng * 4);
-            const float xv[4] = {x4.x, x4.y, x4.z, x4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+            const float xv[4] = {x4.x, x4.y, x4.z, x4.w};
+            float bv[NJ];
+            load_rows<NJ>(bv, tl.Bt + th.ng * NJ);
 #pragma unroll
-            for (int e = 0; e < 16; ++e) prv[e] = xv[e >> 2] * bv[e & 3];
+            for (int e = 0; e < E; ++e) prv[e] = xv[e / NJ] * bv[e % NJ];
           }
         }
         if (half == 1) {
 #pragma unroll
           for (int tt = 0; tt < 4; ++tt) {
             const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + (tt + 1) * g.P + th.pg * 4);
-            const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + (tt + 1) * g.N + th.ng * 4);
-            hm_step<TRAP>(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1]);
+            float bv[NJ];
+            load_rows<NJ>(bv, tl.Bt + (tt + 1) * g.N + th.ng * NJ);
+            hm_step<TRAP, NJ>(hs, prv, rate, x4, bv, tl.dts[tt + 1], tl.lams[tt + 1]);
           }
         }
 #pragma unroll
-        for (int e = 0; e < 16; ++e) prv0[e] = prv[e];
+        for (int e = 0; e < E; ++e) prv0[e] = prv[e];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {              // tokens past L: zero clock and drive leave the state unchanged
           const int tt = half * 4 + k;
           const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + (tt + 1) * g.P + th.pg * 4);
-          const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + (tt + 1) * g.N + th.ng * 4);
-          hm_step<TRAP>(hs, prv, rate, x4, b4, tl.dts[tt + 1], tl.lams[tt + 1]);
+          float bv[NJ];
+          load_rows<NJ>(bv, tl.Bt + (tt + 1) * g.N + th.ng * NJ);
+          hm_step<TRAP, NJ>(hs, prv, rate, x4, bv, tl.dts[tt + 1], tl.lams[tt + 1]);
 #pragma unroll
-          for (int e = 0; e < 16; ++e) hist[k][e] = hs[e];
+          for (int e = 0; e < E; ++e) hist[k][e] = hs[e];
         }
       }
       // ---- reverse walk
@@ -609,14 +638,16 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
         const float d = tl.dts[tt + 1], lm = tl.lams[tt + 1];
         const float4 x4 = *reinterpret_cast<const float4*>(tl.xs + (tt + 1) * g.P + th.pg * 4);
         const float4 xp4 = *reinterpret_cast<const float4*>(tl.xs + tt * g.P + th.pg * 4);
-        const float4 b4 = *reinterpret_cast<const float4*>(tl.Bt + (tt + 1) * g.N + th.ng * 4);
-        const float4 bp4 = *reinterpret_cast<const float4*>(tl.Bt + tt * g.N + th.ng * 4);
-        const float4 c4 = *reinterpret_cast<const float4*>(tl.Ct + (tt + 1) * g.N + th.ng * 4);
         const float4 dy4 = *reinterpret_cast<const float4*>(tl.dys + tt * g.P + th.pg * 4);
         const float xv[4] = {x4.x, x4.y, x4.z, x4.w}, xpv[4] = {xp4.x, xp4.y, xp4.z, xp4.w};
-        const float bv[4] = {b4.x, b4.y, b4.z, b4.w}, bpv[4] = {bp4.x, bp4.y, bp4.z, bp4.w};
-        const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, dyv[4] = {dy4.x, dy4.y, dy4.z, dy4.w};
-        float px[4] = {0.f, 0.f, 0.f, 0.f}, pB[4] = {0.f, 0.f, 0.f, 0.f}, pC[4] = {0.f, 0.f, 0.f, 0.f};
+        const float dyv[4] = {dy4.x, dy4.y, dy4.z, dy4.w};
+        float bv[NJ], bpv[NJ], cv[NJ];
+        load_rows<NJ>(bv, tl.Bt + (tt + 1) * g.N + th.ng * NJ);
+        load_rows<NJ>(bpv, tl.Bt + tt * g.N + th.ng * NJ);
+        load_rows<NJ>(cv, tl.Ct + (tt + 1) * g.N + th.ng * NJ);
+        float px[4] = {0.f, 0.f, 0.f, 0.f}, pB[NJ], pC[NJ];
+#pragma unroll
+        for (int jn = 0; jn < NJ; ++jn) { pB[jn] = 0.f; pC[jn] = 0.f; }
         float sQ = 0.f, S1 = 0.f, S2 = 0.f;        // sums of dlog rate2, G raw, (a G) raw_prev over this thread's tile
         const float dl = d * lm, dg = d * (1.f - lm);
         const bool last = (tok == a.L - 1) && a.dwrite_last != nullptr;
@@ -624,8 +655,8 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
 #pragma unroll
           for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int jn = 0; jn < 4; ++jn) {
-              const int e = i * 4 + jn;
+            for (int jn = 0; jn < NJ; ++jn) {
+              const int e = i * NJ + jn;
               const float Gt = fmaf(cv[jn], dyv[i], G[e]);
               pC[jn] = fmaf(dyv[i], hist[k][e], pC[jn]);
               const float raw = xv[i] * bv[jn];
@@ -635,7 +666,7 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
               sQ += q;
               const float aG = fast_ex2(rate[e] * d) * Gt;
               float draw = fmaf(dl, Gt, lagn * G[e]);
-              if (last) draw += a.dwrite_last[bh * PN + (int64_t)(th.pg * 4 + i) * g.N + th.ng * 4 + jn];
+              if (last) draw += a.dwrite_last[bh * PN + (int64_t)(th.pg * 4 + i) * g.N + th.ng * NJ + jn];
               S1 += u1;
               if (TRAP) {
                 const float rawp = (k == 0) ? prv0[e] : xpv[i] * bpv[jn];
@@ -661,13 +692,13 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
           }
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < NJ; ++i) {
           float vb = th.active ? pB[i] : 0.f, vc = th.active ? pC[i] : 0.f;
           vb = cross_group_sum(vb, g.NG);
           vc = cross_group_sum(vc, g.NG);
           if (lane < g.NG) {
-            partB[(tt * g.nwarp + warp) * g.N + lane * 4 + i] = vb;
-            partC[(tt * g.nwarp + warp) * g.N + lane * 4 + i] = vc;
+            partB[(tt * g.nwarp + warp) * g.N + lane * NJ + i] = vb;
+            partC[(tt * g.nwarp + warp) * g.N + lane * NJ + i] = vc;
           }
         }
         {
@@ -683,10 +714,11 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
       }   // half
       __syncthreads();
       // ---- finish the sub-chunk: sum the per-warp partials in warp order
-      // A warp holds 32 / NG channel groups; when NG == 32 lanes map 1:1 to row groups.  Rows n = ng * 4 + i.
+      // A warp holds 32 / NG channel groups; when NG == 32 lanes map 1:1 to row groups.  Rows n = ng * NJ + i.
       for (int idx = tid; idx < 8 * g.N; idx += blockDim.x) {
         const int tt = idx / g.N, n = idx % g.N;
         float sb = 0.f, sc = 0.f;
+#pragma unroll 4
         for (int w = 0; w < g.nwarp; ++w) { sb += partB[(tt * g.nwarp + w) * g.N + n]; sc += partC[(tt * g.nwarp + w) * g.N + n]; }
         partB[(tt * g.nwarp) * g.N + n] = sb;      // slot of warp 0 now holds the total
         partC[(tt * g.nwarp) * g.N + n] = sc;
@@ -721,6 +753,7 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
         const int k = tid;
         float S = Ssuf[k];
         const bool rot = tl.rotm[k] != 0.f;
+#pragma unroll
         for (int tt = HM_TT - 1; tt >= 0; --tt) {
           const int tok = t0 + tt;
           if (tok >= a.L) { phs[tt * g.K + k] = 0.f; continue; }
@@ -776,16 +809,16 @@ __global__ void __launch_bounds__(256, 1) hm_bwd_kernel(const HmArgs a) {
   }
   // ---- what is left after token 0
   if (th.active) {
-    if (a.dh_init) store16(G, a.dh_init + bh * PN, th, g.N);
+    if (a.dh_init) store_tile<NJ>(G, a.dh_init + bh * PN, th, g.N);
     if (a.dwrite_prev) {
-      float wv[16];
+      float wv[E];
 #pragma unroll
-      for (int e = 0; e < 16; ++e) wv[e] = lagn * G[e];
-      store16(wv, a.dwrite_prev + bh * PN, th, g.N);
+      for (int e = 0; e < E; ++e) wv[e] = lagn * G[e];
+      store_tile<NJ>(wv, a.dwrite_prev + bh * PN, th, g.N);
     }
 #pragma unroll
-    for (int e = 0; e < 16; ++e) dA[e] *= HM_LN2;       // the sums were taken with rate2 = rate log2(e)
-    store16(dA, a.dA_log_part + bh * PN, th, g.N);
+    for (int e = 0; e < E; ++e) dA[e] *= HM_LN2;       // the sums were taken with rate2 = rate log2(e)
+    store_tile<NJ>(dA, a.dA_log_part + bh * PN, th, g.N);
   }
   if (tid >= (int)blockDim.x - g.N) {
     const int n = tid - ((int)blockDim.x - g.N);
@@ -865,8 +898,12 @@ extern "C" int orbit_hm_scan_fwd(const orbit_hm_args* a, int dtype, void* stream
     return OK;
   };
   const bool trap = a->lam != nullptr;
-  rc = dtype == BF16 ? (trap ? go(hm_fwd_kernel<__nv_bfloat16, true>) : go(hm_fwd_kernel<__nv_bfloat16, false>))
-                     : (trap ? go(hm_fwd_kernel<float, true>) : go(hm_fwd_kernel<float, false>));
+  if (a->P == 64 && a->N == 64)
+    rc = dtype == BF16 ? (trap ? go(hm_fwd_kernel<__nv_bfloat16, true, 64, 64>) : go(hm_fwd_kernel<__nv_bfloat16, false, 64, 64>))
+                       : (trap ? go(hm_fwd_kernel<float, true, 64, 64>) : go(hm_fwd_kernel<float, false, 64, 64>));
+  else
+    rc = dtype == BF16 ? (trap ? go(hm_fwd_kernel<__nv_bfloat16, true, 0, 0>) : go(hm_fwd_kernel<__nv_bfloat16, false, 0, 0>))
+                       : (trap ? go(hm_fwd_kernel<float, true, 0, 0>) : go(hm_fwd_kernel<float, false, 0, 0>));
   if (rc != OK) return rc;
   ORBIT_CHECK_LAUNCH("hm_fwd_kernel");
   return OK;
@@ -875,7 +912,9 @@ extern "C" int orbit_hm_scan_fwd(const orbit_hm_args* a, int dtype, void* stream
 extern "C" int orbit_hm_scan_bwd(const orbit_hm_args* a, int dtype, void* stream) {
   int rc = hm_check(a, dtype, "orbit_hm_scan_bwd", true);
   if (rc != OK) return rc;
-  const HmGeo g = hm_geo(a->P, a->N);
+  // Four rows per thread.  Two (twice the warps at half the registers each) measured the same with compile-time geometry
+  // and slower with run-time geometry (spills), so it is not instantiated.
+  const HmGeo g = hm_geo(a->P, a->N, 4);
   const size_t smem = hm_smem_bwd(g);
   ORBIT_REQUIRE(smem <= 220 * 1024, ERR_UNSUPPORTED, "orbit_hm_scan_bwd: P=%d, N=%d need %zu bytes of shared memory (limit 220 KiB)",
                 a->P, a->N, smem);
@@ -887,8 +926,12 @@ extern "C" int orbit_hm_scan_bwd(const orbit_hm_args* a, int dtype, void* stream
     return OK;
   };
   const bool trap = a->lam != nullptr;
-  rc = dtype == BF16 ? (trap ? go(hm_bwd_kernel<__nv_bfloat16, true>) : go(hm_bwd_kernel<__nv_bfloat16, false>))
-                     : (trap ? go(hm_bwd_kernel<float, true>) : go(hm_bwd_kernel<float, false>));
+  if (a->P == 64 && a->N == 64)
+    rc = dtype == BF16 ? (trap ? go(hm_bwd_kernel<__nv_bfloat16, true, 4, 64, 64>) : go(hm_bwd_kernel<__nv_bfloat16, false, 4, 64, 64>))
+                       : (trap ? go(hm_bwd_kernel<float, true, 4, 64, 64>) : go(hm_bwd_kernel<float, false, 4, 64, 64>));
+  else
+    rc = dtype == BF16 ? (trap ? go(hm_bwd_kernel<__nv_bfloat16, true, 4, 0, 0>) : go(hm_bwd_kernel<__nv_bfloat16, false, 4, 0, 0>))
+                       : (trap ? go(hm_bwd_kernel<float, true, 4, 0, 0>) : go(hm_bwd_kernel<float, false, 4, 0, 0>));
   if (rc != OK) return rc;
   ORBIT_CHECK_LAUNCH("hm_bwd_kernel");
   return OK;
