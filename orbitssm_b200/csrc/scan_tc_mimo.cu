@@ -271,6 +271,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) mimo_chunk_state_kernel(const S
 // in the epilogue (the scale differs per sibling, so they cannot share an accumulator).
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int TAB_LD = 33;
+constexpr int TAB_LD2 = 34;    // gradient kernel: even, so that a thread reads its row two entries at a time (8-byte aligned)
 struct MimoOutSmem {
   static constexpr uint32_t C = 0, B = 2 * BLK, MS = 4 * BLK, GB = 6 * BLK, UT = 8 * BLK, SINT = UT + 2 * XT_BLK,
                             TAB = SINT + 2 * XT_BLK, CLK = TAB + 32 * TAB_LD * 4, YST = CLK + 12 * 32 * 4,
@@ -555,7 +556,7 @@ struct MimoGradSmem {
   static constexpr uint32_t XT_SZ = 2 * XT_BLK;
   static constexpr uint32_t UT = XT, DYT = XT + XT_SZ, FDYT = XT + 2 * XT_SZ, EUT = XT + 3 * XT_SZ, SINT = XT + 4 * XT_SZ,
                             DSOT = XT + 5 * XT_SZ, RS = XT + 6 * XT_SZ, CB = XT + 7 * XT_SZ;
-  static constexpr uint32_t TABW = XT + 8 * XT_SZ, TABE = TABW + 32 * TAB_LD * 4, CLK = TABE + 32 * TAB_LD * 4,
+  static constexpr uint32_t TABW = XT + 8 * XT_SZ, TABE = TABW + 32 * TAB_LD2 * 4, CLK = TABE + 32 * TAB_LD2 * 4,
                             PART = CLK + 8 * 32 * 4, XBAR = PART + 6 * 8 * 32 * 4, DU = XBAR + 2 * 64 * 4 + 64 + 256,
                             TOTAL = DU + 32 * 65 * 4 + 1024;
 };
@@ -712,8 +713,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
         float e = 0.f, wv = 0.f;
         if (s < t) { e = __expf(s_cs[t] - s_cs[s]); wv = e * s_w[s]; }
         else if (s == t) wv = s_wd[t];
-        tabE[t * TAB_LD + s] = e;
-        tabW[t * TAB_LD + s] = wv;
+        tabE[t * TAB_LD2 + s] = e;
+        tabW[t * TAB_LD2 + s] = wv;
       }
       if (tid < 64) sDg[tid] = a.Dg ? rawDg[tid] : 0.f;
       build_xt_pair(sUT, sEUT, slotU[tid], s_e);
@@ -760,7 +761,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
         const uint8_t* src = tid < 64 ? sFDYT : sEUT;
         const int g = (tid & 63) >> 2, x = tid & 3;
         float acc = 0.f;
-        for (int s = 0; s < 32; ++s) acc += xt_read(src, g, x * 32 + s);
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {            // 8 consecutive tokens of a row are one 16-byte chunk of the tile
+          const uint4 v = *reinterpret_cast<const uint4*>(src + xt_offset(g, x * 32 + c8 * 8));
+          const uint32_t* vp = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            float a0, a1;
+            unpack_bf16(vp[k], a0, a1);
+            acc += a0;
+            acc += a1;
+          }
+        }
         xbar[(tid >> 6) * 64 + x * 16 + g] = acc;
       }
       bool ok = wait_warp(&bar_a, par, abort_flag);
@@ -812,15 +824,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
       if (ok) {
         tc_fence_after_sync();
         const float chi_t = s_chi[lane];
-        float prow = 0.f, pdiag = 0.f;
+        const float2 chi2 = make_float2(chi_t, chi_t);
+        float2 prow2 = make_float2(0.f, 0.f);
+        float pdiag = 0.f;
         float vE[32];
+        const float2* rowW = reinterpret_cast<const float2*>(tabW + lane * TAB_LD2);
+        const float2* rowE = reinterpret_cast<const float2*>(tabE + lane * TAB_LD2);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           uint32_t v[32];
           float vR[32];
           tmem_ld32(tmem_addr(tbase, qw * 32, TS + wg * 64 + j * 32), v);
           tmem_ld_wait();
-          float cbsum = 0.f;
+          float2 cb2 = make_float2(0.f, 0.f);
 #pragma unroll
           for (int cc = 0; cc < 4; ++cc) {
             const uint4 dmv = *reinterpret_cast<const uint4*>(sDM + wg * BLK + sw128_offset(row, j * 4 + cc));
@@ -828,35 +844,36 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
             uint32_t w1[4], w2[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-              float dm[2], ds[2], ms[2];
-              unpack_bf16(dmp[k], dm[0], dm[1]);
-#pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                const int s = cc * 8 + 2 * k + e;
-                const float sc = __uint_as_float(v[s]);
-                const float Wt = tabW[lane * TAB_LD + s], Et = tabE[lane * TAB_LD + s];
-                const float p = dm[e] * sc;
-                prow = fmaf(p, Wt, prow);
-                pdiag += (s == lane) ? p : 0.f;
-                const float pe = chi_t * p * Et;
-                vE[s] = j == 0 ? pe : vE[s] + pe;
-                const float cw = chi_t * Wt;
-                ds[e] = dm[e] * cw;
-                ms[e] = sc * cw;
-                cbsum += ds[e];
-                vR[s] = ds[e];
-              }
-              w1[k] = pack_bf16(ds[0], ds[1]);
-              w2[k] = pack_bf16(ms[0], ms[1]);
+              // two columns s, s + 1 at a time (packed fp32)
+              const int s = cc * 8 + 2 * k;
+              float2 dm;
+              unpack_bf16(dmp[k], dm.x, dm.y);
+              const float2 sc = f2(v[s], v[s + 1]);
+              const float2 Wt = rowW[s >> 1], Et = rowE[s >> 1];
+              const float2 p = mul2(dm, sc);
+              prow2 = fma2(p, Wt, prow2);
+              pdiag += (s == lane) ? p.x : 0.f;
+              pdiag += (s + 1 == lane) ? p.y : 0.f;
+              const float2 pe = mul2(mul2(p, chi2), Et);
+              if (j == 0) { vE[s] = pe.x; vE[s + 1] = pe.y; }
+              else { const float2 t2 = add2(make_float2(vE[s], vE[s + 1]), pe); vE[s] = t2.x; vE[s + 1] = t2.y; }
+              const float2 cw = mul2(chi2, Wt);
+              const float2 ds = mul2(dm, cw), ms = mul2(sc, cw);
+              cb2 = add2(cb2, ds);
+              vR[s] = ds.x;
+              vR[s + 1] = ds.y;
+              w1[k] = pack_bf16(ds.x, ds.y);
+              w2[k] = pack_bf16(ms.x, ms.y);
             }
             *reinterpret_cast<uint4*>(sDSc + wg * BLK + sw128_offset(row, j * 4 + cc)) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
             *reinterpret_cast<uint4*>(sMs + wg * BLK + sw128_offset(row, j * 4 + cc)) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
           }
           const int q = wg * 2 + j;
-          *reinterpret_cast<__nv_bfloat16*>(sCB + xt_offset(q, row)) = __float2bfloat16_rn(cbsum);
+          *reinterpret_cast<__nv_bfloat16*>(sCB + xt_offset(q, row)) = __float2bfloat16_rn(cb2.x + cb2.y);
           warp_colsum32(vR, lane);
           *reinterpret_cast<__nv_bfloat16*>(sRS + xt_offset(qw, q * 32 + lane)) = __float2bfloat16_rn(vR[0]);
         }
+        const float prow = prow2.x + prow2.y;
         warp_colsum32(vE, lane);
         p_row[warp * 32 + lane] = prow;
         p_diag[warp * 32 + lane] = pdiag;
@@ -914,11 +931,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mimo_chunk_grads_kernel(const S
           if (a.dwd) a.dwd[i] = chi_t * diag;
           if (a.dchi) a.dchi[i] = g_chi;
         }
-      } else if ((warp == 2 || warp == 3) && a.dDg_part != nullptr) {
-        const int idx = tid - 64, o = idx & 3, g = idx >> 2;
+      }
+      if (a.dDg_part != nullptr) {
+        // skip-gain partials: 64 (g, o) dot products over the chunk's tokens, four threads each (8 tokens = one 16-byte
+        // chunk of both tiles), summed over the four by two shuffles
+        const int item = tid >> 2, j = tid & 3, o = item & 3, g = item >> 2;
+        const uint4 dv = *reinterpret_cast<const uint4*>(sDYT + xt_offset(g, o * 32 + j * 8));
+        const uint4 uv = *reinterpret_cast<const uint4*>(sUT + xt_offset(g, r * 32 + j * 8));
+        const float4 c0 = *reinterpret_cast<const float4*>(s_chi + j * 8), c1 = *reinterpret_cast<const float4*>(s_chi + j * 8 + 4);
+        const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const uint32_t *dp = reinterpret_cast<const uint32_t*>(&dv), *upk = reinterpret_cast<const uint32_t*>(&uv);
         float acc = 0.f;
-        for (int t = 0; t < 32; ++t) acc = fmaf(s_chi[t] * xt_read(sDYT, g, o * 32 + t), xt_read(sUT, g, r * 32 + t), acc);
-        a.dDg_part[(slot * H + h) * (MM_G * MM_R * 4) + (g * MM_R + r) * 4 + o] = acc;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float d0, d1, u0, u1;
+          unpack_bf16(dp[k], d0, d1);
+          unpack_bf16(upk[k], u0, u1);
+          acc = fmaf(cv[2 * k] * d0, u0, acc);
+          acc = fmaf(cv[2 * k + 1] * d1, u1, acc);
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        if (j == 0) a.dDg_part[(slot * H + h) * (MM_G * MM_R * 4) + (g * MM_R + r) * 4 + o] = acc;
       }
       ok = wait_warp(&bar_c, par, abort_flag);
       if (ok) {
