@@ -285,3 +285,51 @@ def test_graphed_decode_equals_eager_steps():
     for a_, b_ in zip(dec.state, st):
         for k in b_:
             assert rel(a_[k], b_[k]) < 1e-3, k
+
+
+@pytest.mark.parametrize("io", [torch.float32, torch.bfloat16])
+def test_input_forms(io):
+    """What a caller may hand the layer besides a contiguous, grad-requiring input: strided views (every other token, a
+    column window of a wider tensor), an input without gradient, `no_grad` / `inference_mode`, and an output gradient that
+    is an expanded scalar (`y.sum().backward()`: every stride 0).  Each must give what the contiguous call gives: outputs
+    bit for bit, gradients to rounding (the library GEMMs may pick another split for another operand layout)."""
+    rec = load_golden("cfg2_long")
+    layer = build(rec, "ieee" if io == torch.float32 else "io")
+    x0 = rec["x"].to(DEV).to(io)
+    B, L, D = x0.shape
+    tol = 1e-5 if io == torch.float32 else 1e-2
+
+    def grads_of(x, loss_of):
+        layer.zero_grad()
+        y = layer(x)
+        loss_of(y).backward()
+        return y.detach(), {n: p.grad.clone() for n, p in layer.named_parameters() if p.grad is not None}
+
+    def same(got, want, what):
+        for n in want:
+            assert rel(got[n], want[n]) < tol, (what, n, rel(got[n], want[n]))
+
+    xc = x0.clone().requires_grad_(True)
+    y_ref, g_ref = grads_of(xc, lambda y: (y * torch.ones_like(y)).sum())
+    dx_ref = xc.grad.clone()
+    # the same gradient as an expanded scalar
+    xc2 = x0.clone().requires_grad_(True)
+    y2, g2 = grads_of(xc2, lambda y: y.sum())
+    assert torch.equal(y2, y_ref) and rel(xc2.grad, dx_ref) < tol
+    same(g2, g_ref, "expanded output gradient")
+    # strided views of the same values
+    wide = torch.zeros(B, 2 * L, D + 16, device=DEV, dtype=io)
+    wide[:, ::2, 8:8 + D] = x0
+    xs = wide[:, ::2, 8:8 + D].detach().requires_grad_(True)
+    assert not xs.is_contiguous()
+    y3, g3 = grads_of(xs, lambda y: (y * torch.ones_like(y)).sum())
+    assert torch.equal(y3, y_ref) and rel(xs.grad, dx_ref) < tol
+    same(g3, g_ref, "strided input")
+    # no input gradient wanted
+    y4, g4 = grads_of(x0.clone(), lambda y: (y * torch.ones_like(y)).sum())
+    assert torch.equal(y4, y_ref)
+    same(g4, g_ref, "input without gradient")
+    with torch.no_grad():
+        assert torch.equal(layer(x0), y_ref)
+    with torch.inference_mode():
+        assert torch.equal(layer(x0), y_ref)
