@@ -816,7 +816,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
   float* colsum = rowpart + 512;         // [2][128] column sums of K o E (du group)
   float* depart = colsum + 256;          // [2][128] de (du group)
   float* kdiag = depart + 256;           // [2][128] K[s,s] (du group)
-  float* ddpart = kdiag + 256;           // [2][2][64] dD partial sums over the upper / lower 64 tokens
+  float* ddpart = kdiag + 256;           // [3][2][64] dD partial sums over the upper / lower 64 tokens, a ring over the heads
   float* cbd = ddpart + 512;             // [128] CB[s,s] of this chunk
   float* tkred = cbd + 128;              // token warps: [16] scratch of their reductions
   __shared__ GScoreBars bars;
@@ -1050,7 +1050,8 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
     // about twice as much).  Its two warps split them so that both carry about the same work: the first (sg = 0) takes
     // pieces [0, nA), the second the rest; the second warps of quarters 0 and 1, which get only one diagonal piece, also sum
     // dD[p] = sum_t dy[t,p] u[t,p] over 64 tokens each (a lane owns two columns and walks down the rows of the two tiles, so
-    // that sum needs no exchange between threads).
+    // that sum needs no exchange between threads), one head ahead: after they have arrived for head h they sum head h + 1
+    // while the tensor cores form that head's dM, so the sums are on nobody's critical path.
     const int sg = (warp - 4) >> 2;
     const int nA = q == 0 ? 1 : (q == 1 ? 3 : q + 2);
     const int p_lo = sg == 0 ? 0 : nA, p_hi = sg == 0 ? nA : 2 * q + 2;      // live pieces of this warp
@@ -1085,6 +1086,29 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
       for (int i = 0; i < 32; ++i) dv = i == lane ? __uint_as_float(r[i]) : dv;
       cbd[t] = dv;
     }
+    // dD[p] = sum_t dy[t,p] u[t,p] of head hh over this warp's 64 tokens, into slot hh % 3 of a ring of three: the slot's
+    // last reader (the token warps' pass over head hh - 3) ended before this warp's wait for part_empty of head hh - 1's
+    // iteration returned, so the ring needs no barrier of its own; the head's tiles were loaded several heads ahead.
+    auto dd_sums = [&](int hh) {
+      const int sx = hh % GS_XSTAGES;
+      if (role_wait(&bars.x_full[sx], (uint32_t)((hh / GS_XSTAGES) & 1), abort_flag, dead)) {
+        const uint8_t* ut = sX + sx * BLK;
+        const uint8_t* dt = sDY + sx * BLK;
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll 4
+        for (int r = 0; r < 64; ++r) {
+          const int row = q * 64 + r;
+          const uint32_t off = sw128_offset(row, lane >> 2) + (lane & 3) * 4;
+          float u0, u1, g0, g1;
+          unpack_bf16(*reinterpret_cast<const uint32_t*>(ut + off), u0, u1);
+          unpack_bf16(*reinterpret_cast<const uint32_t*>(dt + off), g0, g1);
+          s0 = fmaf(g0, u0, s0);
+          s1 = fmaf(g1, u1, s1);
+        }
+        *reinterpret_cast<float2*>(ddpart + ((hh % 3) * 2 + q) * 64 + lane * 2) = make_float2(s0, s1);
+      }
+    };
+    if (dd_warp && Hl > 0) dd_sums(0);
 #pragma unroll 1
     for (int h = 0; h < Hl; ++h) {
       const int pb = h & 1;
@@ -1097,25 +1121,6 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
       bool tile_free = h == 0;             // the previous head's X1 product must have read the masked-score tile before
                                            // this head's first store into it; the first piece is computed meanwhile
       float rowS = 0.f;
-      if (dd_warp) {
-        const int sx = h % GS_XSTAGES;
-        if (role_wait(&bars.x_full[sx], (uint32_t)((h / GS_XSTAGES) & 1), abort_flag, dead)) {
-          const uint8_t* ut = sX + sx * BLK;
-          const uint8_t* dt = sDY + sx * BLK;
-          float s0 = 0.f, s1 = 0.f;
-#pragma unroll 4
-          for (int r = 0; r < 64; ++r) {
-            const int row = q * 64 + r;
-            const uint32_t off = sw128_offset(row, lane >> 2) + (lane & 3) * 4;
-            float u0, u1, g0, g1;
-            unpack_bf16(*reinterpret_cast<const uint32_t*>(ut + off), u0, u1);
-            unpack_bf16(*reinterpret_cast<const uint32_t*>(dt + off), g0, g1);
-            s0 = fmaf(g0, u0, s0);
-            s1 = fmaf(g1, u1, s1);
-          }
-          *reinterpret_cast<float2*>(ddpart + (pb * 2 + q) * 64 + lane * 2) = make_float2(s0, s1);
-        }
-      }
       if (go) {
         tc_fence_after_sync();
         const float cst = cs[t], wdt_t = wdv[t];
@@ -1196,6 +1201,8 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
         mbar_arrive(&bars.ms_full);
         mbar_arrive(&bars.part_full[pb]);
       }
+      // the next head's dD sums now, under the tensor cores' dM of that head (this warp has arrived: nobody waits for it)
+      if (dd_warp && h + 1 < Hl) dd_sums(h + 1);
     }
     // ---- summed score gradient -> shared memory (operand of the closing products) ----
     bool fin = cb_ok;
@@ -1329,7 +1336,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
           if (a.dwd) a.dwd[gb] = kdiag[pb * 128 + tb];
         }
         if (a.dDg_part && ok)
-          a.dDg_part[(((int64_t)b * a.nc + c) * H + h0 + h) * TC_G + i] = ddpart[(pb * 2 + 0) * 64 + i] + ddpart[(pb * 2 + 1) * 64 + i];
+          a.dDg_part[(((int64_t)b * a.nc + c) * H + h0 + h) * TC_G + i] = ddpart[((h % 3) * 2 + 0) * 64 + i] + ddpart[((h % 3) * 2 + 1) * 64 + i];
         named_bar_sync(4, 64);             // tkred is free for the next prefix
       }
       warp_arrive(&bars.part_empty[pb], false);
