@@ -29,6 +29,18 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // ---- bounded waits with a CTA-wide abort flag --------------------------------------------------------------------
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   uint32_t addr = smem_u32(bar);
+  {
+    // most waits of the pipelined roles find their phase complete: ask once without the suspending form
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
 #pragma unroll 1
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
     uint32_t ok;
