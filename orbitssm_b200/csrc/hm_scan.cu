@@ -346,19 +346,26 @@ __device__ __forceinline__ void load_rows(float (&v)[NJ], const float* p) {
 template <bool TRAP, int NJ>
 __device__ __forceinline__ void hm_step(float (&hs)[4 * NJ], float (&prv)[4 * NJ], const float (&rate2)[4 * NJ], const float4 x4,
                                         const float (&bv)[NJ], float d, float lm) {
+  // two rows at a time (packed fp32): the per-element work of these kernels is bound by instruction issue
   const float xv[4] = {x4.x, x4.y, x4.z, x4.w};
   const float dl = d * lm, dg = d * (1.f - lm);
+  const float2 d2 = make_float2(d, d), dl2 = make_float2(dl, dl), dg2 = make_float2(dg, dg);
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < 4; ++i) {
+    const float2 x2 = make_float2(xv[i], xv[i]);
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
+    for (int j = 0; j < NJ; j += 2) {
       const int e = i * NJ + j;
-      const float av = fast_ex2(rate2[e] * d);
-      const float raw = xv[i] * bv[j];
-      if (TRAP) hs[e] = fmaf(av, fmaf(dg, prv[e], hs[e]), dl * raw);
-      else hs[e] = fmaf(av, hs[e], d * raw);
-      prv[e] = raw;
+      const float2 rd = mul2(make_float2(rate2[e], rate2[e + 1]), d2);
+      const float2 av = make_float2(fast_ex2(rd.x), fast_ex2(rd.y));
+      const float2 raw = mul2(x2, make_float2(bv[j], bv[j + 1]));
+      float2 h2 = make_float2(hs[e], hs[e + 1]);
+      if (TRAP) h2 = fma2(av, fma2(dg2, make_float2(prv[e], prv[e + 1]), h2), mul2(dl2, raw));
+      else h2 = fma2(av, h2, mul2(d2, raw));
+      hs[e] = h2.x; hs[e + 1] = h2.y;
+      prv[e] = raw.x; prv[e + 1] = raw.y;
     }
+  }
 }
 
 // the thread's 4 x NJ tile of a [P, N] array
@@ -645,38 +652,72 @@ __global__ void __launch_bounds__(NJ == 2 ? 512 : 256, 1) hm_bwd_kernel(const Hm
         load_rows<NJ>(bv, tl.Bt + (tt + 1) * g.N + th.ng * NJ);
         load_rows<NJ>(bpv, tl.Bt + tt * g.N + th.ng * NJ);
         load_rows<NJ>(cv, tl.Ct + (tt + 1) * g.N + th.ng * NJ);
-        float px[4] = {0.f, 0.f, 0.f, 0.f}, pB[NJ], pC[NJ];
-#pragma unroll
-        for (int jn = 0; jn < NJ; ++jn) { pB[jn] = 0.f; pC[jn] = 0.f; }
+        float px[4], pB[NJ], pC[NJ];
         float sQ = 0.f, S1 = 0.f, S2 = 0.f;        // sums of dlog rate2, G raw, (a G) raw_prev over this thread's tile
         const float dl = d * lm, dg = d * (1.f - lm);
         const bool last = (tok == a.L - 1) && a.dwrite_last != nullptr;
         if (tok < a.L) {
+          // two rows at a time (packed fp32); the pair's lanes are summed where a sum over rows is wanted
+          const float2 d2 = make_float2(d, d), dl2 = make_float2(dl, dl), ndl2 = make_float2(-dl, -dl), lag2 = make_float2(lagn, lagn);
+          float2 px2[4], pB2[NJ / 2], pC2[NJ / 2];
+          float2 sQ2 = make_float2(0.f, 0.f), S12 = sQ2, S22 = sQ2;
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
+          for (int jp = 0; jp < NJ / 2; ++jp) { pB2[jp] = make_float2(0.f, 0.f); pC2[jp] = make_float2(0.f, 0.f); }
 #pragma unroll
-            for (int jn = 0; jn < NJ; ++jn) {
-              const int e = i * NJ + jn;
-              const float Gt = fmaf(cv[jn], dyv[i], G[e]);
-              pC[jn] = fmaf(dyv[i], hist[k][e], pC[jn]);
-              const float raw = xv[i] * bv[jn];
-              const float u1 = Gt * raw;
-              const float q = fmaf(Gt, hist[k][e], -dl * u1) * rate[e];   // dL / d log a_t, times rate2
-              dA[e] = fmaf(q, d, dA[e]);
-              sQ += q;
-              const float aG = fast_ex2(rate[e] * d) * Gt;
-              float draw = fmaf(dl, Gt, lagn * G[e]);
-              if (last) draw += a.dwrite_last[bh * PN + (int64_t)(th.pg * 4 + i) * g.N + th.ng * NJ + jn];
-              S1 += u1;
+          for (int i = 0; i < 4; ++i) {
+            const float2 dy2 = make_float2(dyv[i], dyv[i]), x2 = make_float2(xv[i], xv[i]), xp2 = make_float2(xpv[i], xpv[i]);
+            px2[i] = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int jp = 0; jp < NJ / 2; ++jp) {
+              const int e = i * NJ + 2 * jp;
+              const float2 G2 = make_float2(G[e], G[e + 1]), h2 = make_float2(hist[k][e], hist[k][e + 1]);
+              const float2 r2 = make_float2(rate[e], rate[e + 1]), b2 = make_float2(bv[2 * jp], bv[2 * jp + 1]);
+              const float2 Gt = fma2(make_float2(cv[2 * jp], cv[2 * jp + 1]), dy2, G2);
+              pC2[jp] = fma2(dy2, h2, pC2[jp]);
+              const float2 raw = mul2(x2, b2);
+              const float2 u1 = mul2(Gt, raw);
+              const float2 q = mul2(fma2(Gt, h2, mul2(ndl2, u1)), r2);   // dL / d log a_t, times rate2
+              const float2 dA2 = fma2(q, d2, make_float2(dA[e], dA[e + 1]));
+              dA[e] = dA2.x; dA[e + 1] = dA2.y;
+              sQ2 = add2(sQ2, q);
+              const float2 rd = mul2(r2, d2);
+              const float2 aG = mul2(make_float2(fast_ex2(rd.x), fast_ex2(rd.y)), Gt);
+              const float2 draw = fma2(dl2, Gt, mul2(lag2, G2));
+              S12 = add2(S12, u1);
               if (TRAP) {
-                const float rawp = (k == 0) ? prv0[e] : xpv[i] * bpv[jn];
-                S2 = fmaf(aG, rawp, S2);
+                const float2 rawp = (k == 0) ? make_float2(prv0[e], prv0[e + 1]) : mul2(xp2, make_float2(bpv[2 * jp], bpv[2 * jp + 1]));
+                S22 = fma2(aG, rawp, S22);
               }
-              px[i] = fmaf(draw, bv[jn], px[i]);
-              pB[jn] = fmaf(draw, xv[i], pB[jn]);
-              G[e] = aG;
+              px2[i] = fma2(draw, b2, px2[i]);
+              pB2[jp] = fma2(draw, x2, pB2[jp]);
+              G[e] = aG.x; G[e + 1] = aG.y;
             }
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) px[i] = px2[i].x + px2[i].y;
+#pragma unroll
+          for (int jp = 0; jp < NJ / 2; ++jp) {
+            pB[2 * jp] = pB2[jp].x; pB[2 * jp + 1] = pB2[jp].y;
+            pC[2 * jp] = pC2[jp].x; pC[2 * jp + 1] = pC2[jp].y;
+          }
+          sQ = sQ2.x + sQ2.y; S1 = S12.x + S12.y; S2 = S22.x + S22.y;
+          if (last) {
+            // the gradient of the carried raw write joins the last token's write gradient (one token of the whole sequence)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int jn = 0; jn < NJ; ++jn) {
+                const float w = a.dwrite_last[bh * PN + (int64_t)(th.pg * 4 + i) * g.N + th.ng * NJ + jn];
+                px[i] = fmaf(w, bv[jn], px[i]);
+                pB[jn] = fmaf(w, xv[i], pB[jn]);
+              }
+          }
           lagn = dg;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) px[i] = 0.f;
+#pragma unroll
+          for (int jn = 0; jn < NJ; ++jn) { pB[jn] = 0.f; pC[jn] = 0.f; }
         }
         float sD = fmaf(HM_LN2, sQ, fmaf(lm, S1, (1.f - lm) * S2)), sL = d * (S1 - S2);
         if (!th.active) { sD = 0.f; sL = 0.f; }
