@@ -229,20 +229,55 @@ __device__ __forceinline__ void hm_prefetch(const HmArgs& a, const HmGeo& g, con
   cp_async_commit();
 }
 
+// sin and cos of a running phase.  Phases of this size are first brought to [-pi, pi] (two-constant reduction: 6.28125 is
+// exact in 8 bits, so k * 6.28125 is exact for every k that can occur), where the MUFU sine and cosine are good to 4e-7
+// absolute; anything larger takes the library's full-range path.
+__device__ __forceinline__ void phase_sincos(float x, float* s, float* c) {
+  if (fabsf(x) > 8192.f) {
+    sincosf(x, s, c);
+    return;
+  }
+  const float k = rintf(x * 0.15915494309189535f);
+  float r = fmaf(k, -6.28125f, x);
+  r = fmaf(k, -1.9353071795864769e-3f, r);
+  *s = __sinf(r);
+  *c = __cosf(r);
+}
+
 // Build the tile of tokens [t0 - 1, t0 + 8) from its staged raw copy.  tile.thc holds the phase entering token t0 and
 // leaves holding the phase after token t0 + 7.  Two barriers: one before the raw copy is read, one after the tile is
 // written.  Every (row, pair) item forms its own phase, the running sum from the entering phase in token order (row r
 // takes the first r terms), so no item waits for another; the item of the last row leaves the next entering phase.
+// eight consecutive elements of the IO dtype -> fp32 (both addresses 16-byte aligned)
+__device__ __forceinline__ void cvt8(float* dst, const float* src) {
+  *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+  *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(src + 4);
+}
+__device__ __forceinline__ void cvt8(float* dst, const __nv_bfloat16* src) {
+  const uint4 v = *reinterpret_cast<const uint4*>(src);
+  float f[8];
+  unpack_bf16(v.x, f[0], f[1]); unpack_bf16(v.y, f[2], f[3]); unpack_bf16(v.z, f[4], f[5]); unpack_bf16(v.w, f[6], f[7]);
+  *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+
 template <typename T, bool BWD>
 __device__ __forceinline__ void hm_build_tile(const HmArgs& a, const HmGeo& g, HmTile& tl, const HmRaw& rw, int b, int h, int t0) {
   const int tid = threadIdx.x, nt = blockDim.x;
   cp_async_wait_all();
   __syncthreads();
   const T* rx = reinterpret_cast<const T*>(rw.x);
-  for (int idx = tid; idx < 9 * g.P; idx += nt) tl.xs[idx] = ldf(rx + idx);
-  if (BWD) {
-    const T* rdy = reinterpret_cast<const T*>(rw.dy);
-    for (int idx = tid; idx < 8 * g.P; idx += nt) tl.dys[idx] = ldf(rdy + idx);
+  const T* rdy = reinterpret_cast<const T*>(rw.dy);
+  if (g.P % 8 == 0) {
+    const int nx = 9 * g.P / 8, ny = BWD ? 8 * g.P / 8 : 0;
+    for (int idx = tid; idx < nx + ny; idx += nt) {
+      if (idx < nx) cvt8(tl.xs + idx * 8, rx + idx * 8);
+      else cvt8(tl.dys + (idx - nx) * 8, rdy + (idx - nx) * 8);
+    }
+  } else {
+    for (int idx = tid; idx < 9 * g.P; idx += nt) tl.xs[idx] = ldf(rx + idx);
+    if (BWD)
+      for (int idx = tid; idx < 8 * g.P; idx += nt) tl.dys[idx] = ldf(rdy + idx);
   }
   if (tid < 9) {
     tl.dts[tid] = rw.dt[tid];
@@ -250,29 +285,43 @@ __device__ __forceinline__ void hm_build_tile(const HmArgs& a, const HmGeo& g, H
   }
   const bool rotating = a.feat != nullptr;
   const int lgK = 31 - __clz(g.K);                      // K = N / 2 is a power of two
-  for (int idx = tid; idx < 9 * g.K; idx += nt) {
-    const int r = idx >> lgK, k = idx & (g.K - 1), tok = t0 - 1 + r;
+  // Rows 1..8 (the tile's tokens): both maps.  Row r sees the phase after token t0 + r - 1 (clocks and features are
+  // zero-filled past the end of the sequence).
+  for (int idx = tid; idx < 8 * g.K; idx += nt) {
+    const int r = 1 + (idx >> lgK), k = idx & (g.K - 1), tok = t0 - 1 + r;
     float b0 = 0.f, b1 = 0.f, c0 = 0.f, c1 = 0.f;
-    if (tok >= 0 && tok < a.L) {
+    if (tok < a.L) {
       const float2 bv = *reinterpret_cast<const float2*>(rw.B + r * g.N + 2 * k), cv = *reinterpret_cast<const float2*>(rw.C + r * g.N + 2 * k);
       const float2 bbv = *reinterpret_cast<const float2*>(tl.bb + 2 * k), bcv = *reinterpret_cast<const float2*>(tl.bc + 2 * k);
       b0 = bv.x + bbv.x; b1 = bv.y + bbv.y; c0 = cv.x + bcv.x; c1 = cv.y + bcv.y;
     }
     float cb = 1.f, sb = 0.f, cc = 1.f, sc = 0.f;
     if (rotating) {
-      // row 0 (token t0 - 1) sees the entering phase, row r the phase after token t0 + r - 1 (clocks and features are
-      // zero-filled past the end of the sequence)
       float th = tl.thc[k];
-      for (int j = 1; j <= r; ++j) th = fmaf(rw.dt[j], rw.feat[(j - 1) * g.K + k], th);
+#pragma unroll
+      for (int j = 1; j <= 8; ++j)
+        if (j <= r) th = fmaf(rw.dt[j], rw.feat[(j - 1) * g.K + k], th);
       if (r == 8) tl.thn[k] = th;
       if (tl.rotm[k] != 0.f) {
-        sincosf(th, &sb, &cb);
-        sincosf(th + tl.thh[k], &sc, &cc);
+        phase_sincos(th, &sb, &cb);
+        phase_sincos(th + tl.thh[k], &sc, &cc);
       }
     }
     *reinterpret_cast<float2*>(tl.Bt + r * g.N + 2 * k) = make_float2(b0 * cb - b1 * sb, b0 * sb + b1 * cb);
     *reinterpret_cast<float2*>(tl.Ct + r * g.N + 2 * k) = make_float2(c0 * cc - c1 * sc, c0 * sc + c1 * cc);
-    if (BWD) { tl.cB[idx] = cb; tl.sB[idx] = sb; tl.cC[idx] = cc; tl.sC[idx] = sc; }
+    if (BWD) { const int o = r * g.K + k; tl.cB[o] = cb; tl.sB[o] = sb; tl.cC[o] = cc; tl.sC[o] = sc; }
+  }
+  // Row 0 (token t0 - 1, at the entering phase): only its B map is ever read (the previous token's write of the trapezoid
+  // rule).  Dealt from the last thread down, so that it does not land on the warp that gets the first rows again.
+  for (int k = nt - 1 - tid; k < g.K; k += nt) {
+    float b0 = 0.f, b1 = 0.f;
+    if (t0 >= 1) {
+      const float2 bv = *reinterpret_cast<const float2*>(rw.B + 2 * k), bbv = *reinterpret_cast<const float2*>(tl.bb + 2 * k);
+      b0 = bv.x + bbv.x; b1 = bv.y + bbv.y;
+    }
+    float cb = 1.f, sb = 0.f;
+    if (rotating && tl.rotm[k] != 0.f) phase_sincos(tl.thc[k], &sb, &cb);
+    *reinterpret_cast<float2*>(tl.Bt + 2 * k) = make_float2(b0 * cb - b1 * sb, b0 * sb + b1 * cb);
   }
   __syncthreads();
   if (rotating) {
