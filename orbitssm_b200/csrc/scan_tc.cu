@@ -19,6 +19,13 @@
 namespace orbit {
 using namespace tc;
 
+// 2^x on the MUFU pipe (flush-to-zero of denormal results is harmless for a decay factor)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 constexpr int TC_T = 128, TC_N = 128, TC_G = 64;
 constexpr int ISSUER = 128;      // thread that issues the per-head MMAs and TMA refills in the output / score-gradient kernels
 
@@ -461,21 +468,23 @@ __global__ void __launch_bounds__(WS_THREADS, 1) tc_chunk_out_kernel(const __gri
             }
           } else {
             // diagonal slab, branch-free (selects only): the 32 exponentials are independent and overlap in the pipeline
+            const float2 l2e2 = make_float2(1.4426950408889634f, 1.4426950408889634f), neg2 = make_float2(-1.f, -1.f);
+            const float2 cst2 = make_float2(cst, cst);
+            const int dcol = t - j * 32;              // column dcol of this slab is the diagonal; the columns before it are live
 #pragma unroll
             for (int i4 = 0; i4 < 8; ++i4) {
               const float4 c4 = *reinterpret_cast<const float4*>(cs + j * 32 + i4 * 4);
               const float4 w4 = *reinterpret_cast<const float4*>(wv + j * 32 + i4 * 4);
-              const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, wq[4] = {w4.x, w4.y, w4.z, w4.w};
-              float v[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int i = i4 * 4 + e, s = j * 32 + i;
-                const float E = __expf(cst - cv[e]);          // may overflow above the diagonal: selected away below
-                const float wgt = s < t ? E * wq[e] : (s == t ? wdt_t : 0.f);
-                v[e] = __uint_as_float(r[i]) * wgt;
+              for (int e = 0; e < 2; ++e) {                  // two columns at a time (packed fp32)
+                const int i = i4 * 4 + 2 * e;
+                // (cs_t - cs_s) log2 e; may overflow above the diagonal: selected away below
+                const float2 x2 = mul2(fma2(e ? make_float2(c4.z, c4.w) : make_float2(c4.x, c4.y), neg2, cst2), l2e2);
+                const float2 Ew = mul2(make_float2(ex2_approx(x2.x), ex2_approx(x2.y)), e ? make_float2(w4.z, w4.w) : make_float2(w4.x, w4.y));
+                const float2 wgt = make_float2(i < dcol ? Ew.x : (i == dcol ? wdt_t : 0.f), i + 1 < dcol ? Ew.y : (i + 1 == dcol ? wdt_t : 0.f));
+                const float2 v = mul2(f2(r[i], r[i + 1]), wgt);
+                pk[i4 * 2 + e] = pack_bf16(v.x, v.y);
               }
-              pk[i4 * 2] = pack_bf16(v[0], v[1]);
-              pk[i4 * 2 + 1] = pack_bf16(v[2], v[3]);
             }
           }
           uint8_t* dstb = tile + (j >> 1) * BLK;
@@ -1157,27 +1166,36 @@ __global__ void __launch_bounds__(GS_THREADS, 1) tc_chunk_grads_score_kernel(con
             }
             rowS += rs2.x + rs2.y;
           } else {
-            // diagonal slab, branch-free (selects only)
+            // diagonal slab, branch-free (selects only), two columns at a time (packed fp32)
             tmem_ld_wait();
+            const float2 l2e2 = make_float2(1.4426950408889634f, 1.4426950408889634f), neg2 = make_float2(-1.f, -1.f);
+            const float2 cst2 = make_float2(cst, cst);
+            const int dcol = t - col;                 // column dcol of this piece is the diagonal; the columns before it are live
+            float2 rs2 = make_float2(0.f, 0.f);
 #pragma unroll
             for (int e4 = 0; e4 < 4; ++e4) {
               const float4 c4 = *reinterpret_cast<const float4*>(cs + col + e4 * 4);
               const float4 w4 = *reinterpret_cast<const float4*>(wv + col + e4 * 4);
-              const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, wq[4] = {w4.x, w4.y, w4.z, w4.w};
-              float mv[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int i = e4 * 4 + e, sc = col + i;
-                const float dm = __uint_as_float(rm[i]), cb = __uint_as_float(rc[i]);
-                const float E = sc < t ? __expf(cst - cv[e]) : 0.f;   // the argument is <= 0 wherever it is used
-                const float wgt = sc == t ? wdt_t : E * wq[e];
-                rowS = fmaf(dm * cb, E * wq[e], rowS);
-                ra[i] = __float_as_uint(fmaf(dm, wgt, __uint_as_float(ra[i])));
-                mv[e] = cb * E;
+              for (int e = 0; e < 2; ++e) {
+                const int i = e4 * 4 + 2 * e;
+                const float2 dm = f2(rm[i], rm[i + 1]), cb = f2(rc[i], rc[i + 1]);
+                // (cs_t - cs_s) log2 e: the difference first (exact for neighbouring prefixes), then the scale
+                const float2 x2 = mul2(fma2(e ? make_float2(c4.z, c4.w) : make_float2(c4.x, c4.y), neg2, cst2), l2e2);
+                float2 E;                                  // the argument is <= 0 wherever the exponential is kept
+                E.x = i < dcol ? ex2_approx(x2.x) : 0.f;
+                E.y = i + 1 < dcol ? ex2_approx(x2.y) : 0.f;
+                const float2 Ew = mul2(E, e ? make_float2(w4.z, w4.w) : make_float2(w4.x, w4.y));
+                const float2 wgt = make_float2(i == dcol ? wdt_t : Ew.x, i + 1 == dcol ? wdt_t : Ew.y);
+                rs2 = fma2(mul2(dm, cb), Ew, rs2);
+                const float2 an = fma2(dm, wgt, f2(ra[i], ra[i + 1]));
+                ra[i] = __float_as_uint(an.x);
+                ra[i + 1] = __float_as_uint(an.y);
+                const float2 mv = mul2(cb, E);
+                pk[e4 * 2 + e] = pack_bf16(mv.x, mv.y);
               }
-              pk[e4 * 2] = pack_bf16(mv[0], mv[1]);
-              pk[e4 * 2 + 1] = pack_bf16(mv[2], mv[3]);
             }
+            rowS += rs2.x + rs2.y;
           }
           tmem_st16(tmem_addr(tbase, q * 32, TM_ACC + col), ra);
           if (!tile_free) {
