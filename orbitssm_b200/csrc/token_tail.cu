@@ -188,7 +188,7 @@ __host__ __device__ inline int clock_sum_cols(int H, int R, int a_act, int a_per
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) clock_bwd_kernel(const ClockArgs a) {
+__global__ void __launch_bounds__(256, 3) clock_bwd_kernel(const ClockArgs a) {
   __shared__ float sacc[2 * CLK_MAXR + 1][256];
   const int HR = a.H * a.R;
   const T* dtp = (const T*)a.dt_raw;
@@ -197,10 +197,24 @@ __global__ void __launch_bounds__(256) clock_bwd_kernel(const ClockArgs a) {
   float acc_dt[CLK_MAXR], acc_a[CLK_MAXR], acc_trap = 0.f;
 #pragma unroll
   for (int r = 0; r < CLK_MAXR; ++r) { acc_dt[r] = 0.f; acc_a[r] = 0.f; }
-  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
-    const int64_t m = e / a.H;
-    const int h = (int)(e % a.H);
-    const int t = (int)(m % a.L);
+  // The stride is a multiple of H (the launch sees to it), so the thread keeps its head: row and token advance by fixed
+  // steps, and the divisions of the flat index are paid once, not per element.
+  const int64_t e0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool keeps_head = stride % a.H == 0;
+  int64_t m = e0 / a.H;
+  int h = (int)(e0 % a.H);
+  int t = (int)(m % a.L);
+  const int64_t dm = stride / a.H;
+  const int dtl = (int)(dm % a.L);
+  float rate_c[CLK_MAXR];
+#pragma unroll
+  for (int r = 0; r < CLK_MAXR; ++r) rate_c[r] = (a.a_act == 0 && r < a.R) ? __expf(a.A_log[h * a.R + r]) : 0.f;
+  for (int64_t e = e0; e < total; e += stride, m += dm, t = t + dtl >= a.L ? t + dtl - a.L : t + dtl) {
+    if (!keeps_head) {
+      m = e / a.H;
+      h = (int)(e % a.H);
+      t = (int)(m % a.L);
+    }
     float lam = 1.f;
     if (tp != nullptr) lam = sigmoidf_(ldf(tp + m * a.trap_rs + h));
     float g_trap = 0.f, g_ah = 0.f;
@@ -212,7 +226,7 @@ __global__ void __launch_bounds__(256) clock_bwd_kernel(const ClockArgs a) {
       const float raw = ldf(dtp + m * a.dt_rs + hr);
       const float dt = softplus20(raw);
       float rate, dmag = 0.f;
-      if (a.a_act == 0) rate = __expf(a.A_log[hr]);
+      if (a.a_act == 0) rate = keeps_head ? rate_c[r] : __expf(a.A_log[hr]);
       else rate_act(a.a_act, ldf((const T*)a.a_raw + m * a.a_rs + (a.a_per_sibling ? hr : h)), rate, dmag);
       const float gdA = a.ddA[idx];
       float g_dt = -gdA * rate;
@@ -306,7 +320,7 @@ static int clock_bwd_grid(int64_t M, int H) {
   while (hh) { const int tmp = g % hh; g = hh; hh = tmp; }       // g = gcd(256, H)
   const int unit = H / g;
   const int64_t need = (M * H + 255) / 256;
-  int64_t cap = 148 * 4;
+  int64_t cap = 148 * 3;            // what is resident at once (three CTAs per SM by the launch bounds): one even wave
   if (need < cap) cap = need;
   int64_t grid = (cap / unit) * unit;
   if (grid < unit) grid = unit;
