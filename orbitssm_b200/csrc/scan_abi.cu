@@ -50,7 +50,11 @@ __global__ void __launch_bounds__(256, 3) state_pass_kernel(float* __restrict__ 
   for (int c0 = 0; c0 < nc; c0 += PASS_NB) {
     float z[PASS_NB][VEC], av[PASS_NB];
 #pragma unroll
-    for (int k = 0; k < PASS_NB; ++k) {
+    for (int kk = 0; kk < PASS_NB; ++kk) {
+      // The loads of a batch are issued from the highest address down in both directions: measured, the forward walk ran
+      // 1.45 x longer than the reverse one for the same traffic when its eight loads (2 MiB apart at the config-5 size)
+      // went out lowest address first.
+      const int k = REVERSE ? kk : PASS_NB - 1 - kk;
       const int cc = REVERSE ? nc - 1 - (c0 + k) : c0 + k;
       if (c0 + k < nc) {
         av[k] = ap[(int64_t)cc * HR];
