@@ -246,9 +246,18 @@ __global__ void __launch_bounds__(TC_THREADS, 2) mimo_chunk_state_kernel(const S
       if (tid < 64) {                            // xbar[x][g] = sum_s XT[g][x * 32 + s]
         const int g = tid >> 2, x = tid & 3;
         float acc = 0.f;
-#pragma unroll 8
-        for (int s = 0; s < 32; ++s)
-          acc += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(sXT + buf * 2 * XT_BLK + xt_offset(g, x * 32 + s)));
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {          // 8 consecutive tokens of a row are one 16-byte chunk of the tile
+          const uint4 v = *reinterpret_cast<const uint4*>(sXT + buf * 2 * XT_BLK + xt_offset(g, x * 32 + c8 * 8));
+          const uint32_t* vp = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            float a0, a1;
+            unpack_bf16(vp[k], a0, a1);
+            acc += a0;
+            acc += a1;
+          }
+        }
         xbar[buf * 64 + x * 16 + g] = acc;
       }
       if (tid == 0 && !*abort_flag) {
