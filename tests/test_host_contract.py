@@ -163,3 +163,19 @@ def test_layer_drops_into_the_reference_causal_lm(cpu_kernels):
     l2o = ours(ids, state=[State(s).detach() for s in so])
     l2r = ref(ids, state=[s.detach() for s in sr])
     assert _rel(l2o, l2r) < 1e-4
+
+
+def test_graph_capture_refuses_by_name_without_cuda():
+    """No silent eager fallback: where a step cannot be captured the helpers raise `CaptureError` with a reason tag
+    (reference: src/orbit_ssm/graphs.py:449, `graphed_step` refuses instead of running eagerly)."""
+    import torch
+    from orbitssm_b200 import CaptureError, GraphedDecode, GraphedStep
+    if torch.cuda.is_available():
+        pytest.skip("needs a host without CUDA")
+    lin = torch.nn.Linear(4, 4)
+    with pytest.raises(CaptureError) as e:
+        GraphedStep(lin, torch.zeros(2, 4))
+    assert e.value.reason == "no-cuda"
+    with pytest.raises(CaptureError) as e:
+        GraphedDecode(lin, 2)
+    assert e.value.reason == "no-cuda"
