@@ -37,7 +37,7 @@ constexpr int ISSUER = 128;      // thread that issues the per-head MMAs and TMA
 // factors and scale the drive tile of the next head, one lane of warp 8 issues the TMA loads (4-stage ring), one lane
 // of warp 9 the MMAs (two accumulator sets); the roles meet only through mbarriers.
 // ------------------------------------------------------------------------------------------------------------------
-constexpr int ST_THREADS = 320;
+constexpr int ST_THREADS = 512;          // warps 0-3 read-out, 4-7 and 12-15 scaling (two column halves), 8 producer, 9 MMA issuer
 constexpr int ST_STAGES = 4;
 
 struct StateBars {
@@ -68,10 +68,10 @@ __global__ void __launch_bounds__(ST_THREADS, 1) tc_chunk_state_kernel(const __g
     mbar_init(&bars.map, 1);
     for (int i = 0; i < ST_STAGES; ++i) {
       mbar_init(&bars.x_full[i], 1);
-      mbar_init(&bars.x_empty[i], 4);
+      mbar_init(&bars.x_empty[i], 8);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars.xs_full[i], 4);
+      mbar_init(&bars.xs_full[i], 8);
       mbar_init(&bars.xs_empty[i], 1);
       mbar_init(&bars.acc_full[i], 1);
       mbar_init(&bars.acc_empty[i], 4);
@@ -148,57 +148,84 @@ __global__ void __launch_bounds__(ST_THREADS, 1) tc_chunk_state_kernel(const __g
       }
     }
     if (tid == 0) bulk_wait_group<0>();
-  } else {
-    // ---- scaling group: per-token factors of head h, scaled drive tile -> shared memory ----
+  } else if (role == 1 || role == 3) {
+    // ---- scaling group: two sets of four warps; a thread owns a token row and one half of its 64 channels.  The decay
+    // factors of four heads are formed at once (four independent 128-token prefixes in flight, one barrier per four heads)
+    // and stay in the thread's registers; both halves form them on their own, so the halves never meet. ----
+    constexpr int GH = 4;
+    const int hf = role == 1 ? 0 : 1, bar_id = hf == 0 ? 1 : 3;
+    float* ws_h = wsum + hf * (2 * GH * 4);              // [2 sets][GH heads][4 warps]
     const int64_t ck = ((int64_t)b * a.L + t0 + min(t, Tv - 1)) * H;
     const bool live = t < Tv;
-    float d_n = 0.f, w_n = 0.f;
-    if (live) {
-      d_n = a.dA[ck];
-      w_n = a.w[ck];
-    }
-#pragma unroll 1
-    for (int h = 0; h < H; ++h) {
-      const int s = h % ST_STAGES, k = h & 1;
-      const float wt = w_n;
-      float x = d_n;
+    float d_n[GH], w_n[GH];
+    auto load_group = [&](int hg) {
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const float y = __shfl_up_sync(0xffffffffu, x, o);
-        if (lane >= o) x += y;
-      }
-      if (lane == 31) wsum[(h & 1) * 4 + q] = x;       // two sets: the next head's totals may be written while a slow
-                                                       // warp still reads this head's
-      if (h + 1 < H && live) {
-        d_n = a.dA[ck + h + 1];
-        w_n = a.w[ck + h + 1];
-      }
-      named_bar_sync(1, 128);
-      const float* ws = wsum + (h & 1) * 4;
-      const float w0 = ws[0], w1 = ws[1], w2 = ws[2], w3 = ws[3];
-      const float off = q == 0 ? 0.f : (q == 1 ? w0 : (q == 2 ? w0 + w1 : (w0 + w1) + w2));
-      const float tot = ((w0 + w1) + w2) + w3, csv = x + off;
-      const float f = mode == 0 ? __expf(tot - csv) * wt : __expf(csv);
-      if (mode == 0 && t == 0) a.atot[((int64_t)b * a.nc + c) * H + h] = __expf(tot);
-      bool go = role_wait(&bars.x_full[s], (uint32_t)((h / ST_STAGES) & 1), abort_flag, dead);
-      if (h >= 2) go = role_wait(&bars.xs_empty[k], (uint32_t)(((h >> 1) - 1) & 1), abort_flag, dead) && go;
-      if (go) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t off8 = sw128_offset(t, j);
-          uint4 v = *reinterpret_cast<const uint4*>(sX + s * BLK + off8);
-          uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float lo, hi;
-            unpack_bf16(pv[e], lo, hi);
-            pv[e] = pack_bf16(lo * f, hi * f);
-          }
-          *reinterpret_cast<uint4*>(sXs + k * BLK + off8) = v;
+      for (int i = 0; i < GH; ++i) {
+        d_n[i] = 0.f;                                    // predicated loads straight into the registers: a select on the
+        w_n[i] = 0.f;                                    // loaded value would make the warp wait for it here
+        if (live && hg + i < H) {
+          d_n[i] = a.dA[ck + hg + i];
+          w_n[i] = a.w[ck + hg + i];
         }
       }
-      warp_arrive(&bars.xs_full[k], true);
-      if (lane == 0) mbar_arrive(&bars.x_empty[s]);
+    };
+    load_group(0);
+#pragma unroll 1
+    for (int hg = 0; hg < H; hg += GH) {
+      float x[GH], wt[GH], f[GH];
+#pragma unroll
+      for (int i = 0; i < GH; ++i) { x[i] = d_n[i]; wt[i] = w_n[i]; }
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1)
+#pragma unroll
+        for (int i = 0; i < GH; ++i) {
+          const float y = __shfl_up_sync(0xffffffffu, x[i], o);
+          if (lane >= o) x[i] += y;
+        }
+      const int set = (hg / GH) & 1;                     // two sets: the next group's totals may be written while a slow
+                                                         // warp still reads this group's
+      if (lane == 31)
+#pragma unroll
+        for (int i = 0; i < GH; ++i) ws_h[(set * GH + i) * 4 + q] = x[i];
+      named_bar_sync(bar_id, 128);
+#pragma unroll
+      for (int i = 0; i < GH; ++i) {
+        const float* ws = ws_h + (set * GH + i) * 4;
+        const float w0 = ws[0], w1 = ws[1], w2 = ws[2], w3 = ws[3];
+        const float off = q == 0 ? 0.f : (q == 1 ? w0 : (q == 2 ? w0 + w1 : (w0 + w1) + w2));
+        const float tot = ((w0 + w1) + w2) + w3, csv = x[i] + off;
+        f[i] = mode == 0 ? __expf(tot - csv) * wt[i] : __expf(csv);
+        if (mode == 0 && hf == 0 && t == 0 && hg + i < H) a.atot[((int64_t)b * a.nc + c) * H + hg + i] = __expf(tot);
+      }
+      if (hg + GH < H) load_group(hg + GH);              // the next group's clocks: in flight during this group's four tiles
+#pragma unroll
+      for (int i = 0; i < GH; ++i) {
+        const int h = hg + i;
+        if (h < H) {
+          const int s = h % ST_STAGES, k = h & 1;
+          bool go = role_wait(&bars.x_full[s], (uint32_t)((h / ST_STAGES) & 1), abort_flag, dead);
+          if (h >= 2) go = role_wait(&bars.xs_empty[k], (uint32_t)(((h >> 1) - 1) & 1), abort_flag, dead) && go;
+          if (go) {
+            const float2 f2v = make_float2(f[i], f[i]);
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              const uint32_t off8 = sw128_offset(t, hf * 4 + jj);
+              uint4 v = *reinterpret_cast<const uint4*>(sX + s * BLK + off8);
+              uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float2 xv;
+                unpack_bf16(pv[e], xv.x, xv.y);
+                xv = mul2(xv, f2v);
+                pv[e] = pack_bf16(xv.x, xv.y);
+              }
+              *reinterpret_cast<uint4*>(sXs + k * BLK + off8) = v;
+            }
+          }
+          warp_arrive(&bars.xs_full[k], true);
+          if (lane == 0) mbar_arrive(&bars.x_empty[s]);
+        }
+      }
     }
   }
   tc_fence_before_sync();
@@ -1403,7 +1430,7 @@ static int map_rows(CUtensorMap* m, const void* base, int cols, int64_t token_st
   return make_tensor_map_bf16(m, base, 3, dims, str, box);
 }
 
-constexpr int SMEM_STATE = (8 + ST_STAGES) * BLK + 64 + 1024;
+constexpr int SMEM_STATE = (8 + ST_STAGES) * BLK + 512 + 1024;
 constexpr int SMEM_OUT = (6 + WS_XSTAGES + WS_SSTAGES) * BLK + (1024 + WS_AT_RING * 192 + 16) * 4 + 1024;
 
 // [B*nc*H*128 rows][64 p] bfloat16 view of a state-tile buffer: one [128 x 64] box per (batch, chunk, head)
