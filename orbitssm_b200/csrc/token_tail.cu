@@ -144,9 +144,19 @@ __global__ void __launch_bounds__(256) clock_fwd_kernel(const ClockArgs a) {
   const int HR = a.H * a.R;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= a.M * HR) return;
-  const int64_t m = idx / HR;
-  const int hr = (int)(idx % HR), h = hr / a.R;
-  const int t = (int)(m % a.L);
+  int64_t m;
+  int hr, t;
+  if (a.M * HR < (int64_t)1 << 31) {          // the usual case: 32-bit index splits (a 64-bit division costs ~5 x as much)
+    const uint32_t i32 = (uint32_t)idx, m32 = i32 / (uint32_t)HR;
+    m = m32;
+    hr = (int)(i32 - m32 * (uint32_t)HR);
+    t = (int)(m32 % (uint32_t)a.L);
+  } else {
+    m = idx / HR;
+    hr = (int)(idx % HR);
+    t = (int)(m % a.L);
+  }
+  const int h = hr / a.R;
   const T* dtp = (const T*)a.dt_raw;
   const float dt = softplus20(ldf(dtp + m * a.dt_rs + hr));
   float rate;
