@@ -40,35 +40,51 @@ __host__ __device__ constexpr HmGeo hm_geo(int P, int N, int NJ = 4) {
 struct HmTile {
   float *xs, *dts, *lams, *Bt, *Ct, *cB, *sB, *cC, *sC, *dys, *thc, *thn;
   float *rotm, *thh, *bb, *bc;     // per-head constants of the builder: rotating-pair mask, phase offset of the C map, map biases
+  float *featc;                    // backward: the tile's angle features (its staged copy is gone by the time they are used)
 };
 __host__ __device__ inline size_t r4(size_t n) { return (n + 3) & ~(size_t)3; }
 // Every array starts on a 16-byte boundary (xs, Bt, Ct, dys rows are read as float4).
-__host__ __device__ inline size_t hm_tile_floats(const HmGeo& g, bool bwd) {
-  size_t n = 9 * g.P + 9 * g.N + 9 * g.N + 12 + 12 + 4 * r4(g.K) + 2 * g.N;
-  if (bwd) n += 8 * g.P + 4 * r4(9 * g.K);
+// The forward kernel has one tile; the backward with compile-time geometry keeps the tiles of a chunk's four sub-chunks
+// (built once, in the chunk's replay, and used again by the reverse walk); with run-time geometry, where four tiles may
+// not fit the shared memory, it has one tile and builds a sub-chunk's tile again for the reverse walk.  Shared between
+// the tiles: the running phase and the per-head constants.
+__host__ __device__ inline size_t hm_slot_floats(const HmGeo& g, bool bwd) {
+  size_t n = 9 * g.P + 9 * g.N + 9 * g.N + 12 + 12;
+  if (bwd) n += 8 * g.P + 4 * r4(9 * g.K) + r4(8 * g.K);
   return n;
 }
-__device__ inline float* hm_tile_carve(HmTile& t, float* p, const HmGeo& g, bool bwd) {
+__host__ __device__ inline size_t hm_tile_floats(const HmGeo& g, bool bwd, int slots = 1) {
+  return 4 * r4(g.K) + 2 * g.N + slots * hm_slot_floats(g, bwd);
+}
+// point the per-tile arrays of `t` at slot `j` of the tile area `base`
+__device__ __forceinline__ void hm_tile_slot(HmTile& t, float* base, int j, const HmGeo& g, bool bwd) {
+  float* p = base + (size_t)j * hm_slot_floats(g, bwd);
   t.xs = p; p += 9 * g.P;
   t.Bt = p; p += 9 * g.N;
   t.Ct = p; p += 9 * g.N;
-  t.cB = t.sB = t.cC = t.sC = t.dys = nullptr;
-  if (bwd) { t.dys = p; p += 8 * g.P; }
   t.dts = p; p += 12;
   t.lams = p; p += 12;
+  t.cB = t.sB = t.cC = t.sC = t.dys = t.featc = nullptr;
+  if (bwd) {
+    t.dys = p; p += 8 * g.P;
+    t.cB = p; p += r4(9 * g.K);
+    t.sB = p; p += r4(9 * g.K);
+    t.cC = p; p += r4(9 * g.K);
+    t.sC = p; p += r4(9 * g.K);
+    t.featc = p;
+  }
+}
+// carve the shared arrays and the tile area (slot 0 selected); returns the first float after the area
+__device__ inline float* hm_tile_carve(HmTile& t, float* p, const HmGeo& g, bool bwd, float** area = nullptr, int slots = 1) {
   t.thc = p; p += r4(g.K);
   t.thn = p; p += r4(g.K);
   t.rotm = p; p += r4(g.K);
   t.thh = p; p += r4(g.K);
   t.bb = p; p += g.N;
   t.bc = p; p += g.N;
-  if (bwd) {
-    t.cB = p; p += r4(9 * g.K);
-    t.sB = p; p += r4(9 * g.K);
-    t.cC = p; p += r4(9 * g.K);
-    t.sC = p; p += r4(9 * g.K);
-  }
-  return p;
+  if (area != nullptr) *area = p;
+  hm_tile_slot(t, p, 0, g, bwd);
+  return p + slots * hm_slot_floats(g, bwd);
 }
 // The per-head constants, written once per CTA (the opening barrier of the first tile build publishes them).
 __device__ __forceinline__ void hm_tile_consts(const HmArgs& a, const HmGeo& g, const HmTile& tl, int h) {
@@ -284,6 +300,8 @@ __device__ __forceinline__ void hm_build_tile(const HmArgs& a, const HmGeo& g, H
     tl.lams[tid] = a.lam ? rw.lam[tid] : 1.f;
   }
   const bool rotating = a.feat != nullptr;
+  if (BWD && rotating)
+    for (int idx = tid; idx < 8 * g.K; idx += nt) tl.featc[idx] = rw.feat[idx];
   const int lgK = 31 - __clz(g.K);                      // K = N / 2 is a power of two
   // Rows 1..8 (the tile's tokens): both maps.  Row r sees the phase after token t0 + r - 1 (clocks and features are
   // zero-filled past the end of the sequence).
@@ -532,10 +550,12 @@ __global__ void __launch_bounds__(NJ == 2 ? 512 : 256, 1) hm_bwd_kernel(const Hm
   constexpr int E = 4 * NJ;
   extern __shared__ __align__(16) float smf[];
   const HmGeo g = CP > 0 ? hm_geo(CP, CN, NJ) : hm_geo(a.P, a.N, NJ);
+  constexpr bool CACHE = CP > 0;          // keep the four tiles of a chunk (see hm_slot_floats)
   HmTile tl;
-  float* p = hm_tile_carve(tl, smf, g, true);
+  float* tiles;
+  float* p = hm_tile_carve(tl, smf, g, true, &tiles, CACHE ? HM_SUB : 1);
   float* hsub = p;  p += (size_t)HM_SUB * g.P * g.N;     // state entering each sub-chunk of the current chunk
-  float* thsub = p; p += r4(HM_SUB * g.K);               // phase entering each sub-chunk
+  float* thsub = p; p += r4(HM_SUB * g.K);               // phase entering each sub-chunk (used when the tiles are rebuilt)
   float* partB = p; p += 8 * g.nwarp * g.N;              // [tt][warp][n]
   float* partC = p; p += 8 * g.nwarp * g.N;
   float* partS = p; p += 8 * g.nwarp * 2;                // [tt][warp][ddelta, dlam]
@@ -551,17 +571,19 @@ __global__ void __launch_bounds__(NJ == 2 ? 512 : 256, 1) hm_bwd_kernel(const Hm
   hm_tile_consts(a, g, tl, blockIdx.x);
   __syncthreads();
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // The tiles are visited in a fixed order: per chunk (last first) the first nsub - 1 sub-chunks forwards (replay), then
-  // all nsub sub-chunks backwards.  item_t0(c, k) = first token of the k-th visit of chunk c, continuing into chunk c - 1.
+  // The tiles are staged in a fixed order, chunks from the last to the first.  With kept tiles: the sub-chunks of a chunk
+  // forwards, once.  With rebuilt tiles: the first nsub - 1 sub-chunks forwards (replay), then all nsub backwards.
+  // item_t0(c, k) = first token of the k-th tile of chunk c, continuing into chunk c - 1.
   auto n_sub = [&](int c) { return min(HM_SUB, (a.L - c * HM_TC + HM_TT - 1) / HM_TT); };
   auto item_t0 = [&](int c, int k) -> int {
     int ns = n_sub(c);
-    if (k >= 2 * ns - 1) {
+    if (k >= (CACHE ? ns : 2 * ns - 1)) {
       c -= 1;
       k = 0;
       if (c < 0) return -1;
       ns = HM_SUB;
     }
+    if (CACHE) return c * HM_TC + k * HM_TT;
     return c * HM_TC + (k < ns - 1 ? k : (ns - 1) - (k - (ns - 1))) * HM_TT;
   };
   int seq = 0;
@@ -587,22 +609,29 @@ __global__ void __launch_bounds__(NJ == 2 ? 512 : 256, 1) hm_bwd_kernel(const Hm
   for (int c = a.nck - 1; c >= 0; --c) {
     const int tc0 = c * HM_TC;
     int item = 0;
-    // ---- replay the chunk once, keeping the state and phase that enter each sub-chunk
+    // ---- replay the chunk once: build the tile of every sub-chunk (kept for the reverse walk) and keep the state that
+    // enters each sub-chunk
     {
       float hs[E], prv[E];
       load_tile<NJ>(hs, a.hck + (bh * a.nck + c) * PN, th, g.N);
       if (tid < g.K) tl.thc[tid] = a.thck ? a.thck[(bh * a.nck + c) * g.K + tid] : 0.f;
       __syncthreads();
-      for (int j = 0; j < HM_SUB; ++j) {
+      const int ns = n_sub(c);
+      for (int j = 0; j < ns; ++j) {
         const int t0 = tc0 + j * HM_TT;
-        if (t0 >= a.L) break;
         if (th.active) store_tile<NJ>(hs, hsub + (size_t)j * PN, th, g.N);
-        if (tid < g.K) thsub[j * g.K + tid] = tl.thc[tid];
-        if (j == n_sub(c) - 1) break;      // the last sub-chunk is replayed below anyway
-        hm_build_tile<T, false>(a, g, tl, raw[seq & 1], b, h, t0);
+        if (!CACHE) {
+          if (tid < g.K) thsub[j * g.K + tid] = tl.thc[tid];
+          if (j == ns - 1) break;          // the last sub-chunk's tile is built by the reverse walk
+          hm_build_tile<T, false>(a, g, tl, raw[seq & 1], b, h, t0);
+        } else {
+          hm_tile_slot(tl, tiles, j, g, true);
+          hm_build_tile<T, true>(a, g, tl, raw[seq & 1], b, h, t0);
+        }
         ++item;
         ++seq;
         hm_prefetch<T, true>(a, g, plan, raw[seq & 1], b, h, item_t0(c, item));
+        if (j == ns - 1) break;            // the last sub-chunk's states are formed by the reverse walk's own replays
         if (j == 0) {
 #pragma unroll
           for (int e = 0; e < E; ++e) prv[e] = 0.f;
@@ -626,7 +655,7 @@ __global__ void __launch_bounds__(NJ == 2 ? 512 : 256, 1) hm_bwd_kernel(const Hm
           load_rows<NJ>(bv, tl.Bt + (tt + 1) * g.N + th.ng * NJ);
           hm_step<TRAP, NJ>(hs, prv, rate, x4, bv, tl.dts[tt + 1], tl.lams[tt + 1]);
         }
-        __syncthreads();
+        if (!CACHE) __syncthreads();       // one tile: every warp is done with it before the next build writes it
       }
       __syncthreads();
     }
@@ -634,12 +663,16 @@ __global__ void __launch_bounds__(NJ == 2 ? 512 : 256, 1) hm_bwd_kernel(const Hm
     for (int j = HM_SUB - 1; j >= 0; --j) {
       const int t0 = tc0 + j * HM_TT;
       if (t0 >= a.L) continue;
-      if (tid < g.K) tl.thc[tid] = thsub[j * g.K + tid];
-      __syncthreads();
-      hm_build_tile<T, true>(a, g, tl, raw[seq & 1], b, h, t0);
-      ++item;
-      ++seq;
-      hm_prefetch<T, true>(a, g, plan, raw[seq & 1], b, h, item_t0(c, item));
+      if (CACHE) {
+        hm_tile_slot(tl, tiles, j, g, true);
+      } else {
+        if (tid < g.K) tl.thc[tid] = thsub[j * g.K + tid];
+        __syncthreads();
+        hm_build_tile<T, true>(a, g, tl, raw[seq & 1], b, h, t0);
+        ++item;
+        ++seq;
+        hm_prefetch<T, true>(a, g, plan, raw[seq & 1], b, h, item_t0(c, item));
+      }
       // The sub-chunk is walked in two halves of 4 tokens (second half first): a half's 4 states are held in registers;
       // the first half is replayed once more from the sub-chunk boundary.  (Keeping all 8 states costs 128 registers
       // and an unrolled body that no longer fits the instruction cache.)
@@ -851,7 +884,7 @@ __global__ void __launch_bounds__(NJ == 2 ? 512 : 256, 1) hm_bwd_kernel(const Hm
           if (rot) {
             acc_th += dcs[tt * g.K + k];
             S += phs[tt * g.K + k];
-            ph = raw[(seq + 1) & 1].feat[tt * g.K + k] * S;      // this tile's staged copy (seq already advanced)
+            ph = tl.featc[tt * g.K + k] * S;
           }
           if (a.dfeat_part) a.dfeat_part[(((int64_t)h * a.B + b) * a.L + tok) * g.K + k] = rot ? tl.dts[tt + 1] * S : 0.f;
           phs[tt * g.K + k] = ph;
@@ -965,9 +998,9 @@ static int hm_check(const HmArgs* a, int dtype, const char* who, bool bwd) {
 }
 
 static size_t hm_smem_fwd(const HmGeo& g) { return sizeof(float) * (hm_tile_floats(g, false) + 8 * g.P + 2 * hm_raw_floats(g) + hm_plan_floats(g)); }
-static size_t hm_smem_bwd(const HmGeo& g) {
-  return sizeof(float) * (hm_tile_floats(g, true) + (size_t)HM_SUB * g.P * g.N + r4(HM_SUB * g.K) + 2 * 8 * g.nwarp * g.N +
-                          8 * g.nwarp * 2 + 8 * g.P + 2 * 8 * g.K + r4(g.K) + 32 + 2 * hm_raw_floats(g) + hm_plan_floats(g));
+static size_t hm_smem_bwd(const HmGeo& g, bool keep_tiles) {
+  return sizeof(float) * (hm_tile_floats(g, true, keep_tiles ? HM_SUB : 1) + (size_t)HM_SUB * g.P * g.N + r4(HM_SUB * g.K) + 2 * 8 * g.nwarp * g.N +
+                          8 * g.nwarp * 2 + 8 * g.P + 2 * 8 * g.K + r4(g.K) + 32 + 2 * hm_raw_floats(g) + hm_plan_floats(g));   // (tiles: four slots)
 }
 
 }  // namespace orbit
@@ -1005,7 +1038,7 @@ extern "C" int orbit_hm_scan_bwd(const orbit_hm_args* a, int dtype, void* stream
   // Four rows per thread.  Two (twice the warps at half the registers each) measured the same with compile-time geometry
   // and slower with run-time geometry (spills), so it is not instantiated.
   const HmGeo g = hm_geo(a->P, a->N, 4);
-  const size_t smem = hm_smem_bwd(g);
+  const size_t smem = hm_smem_bwd(g, a->P == 64 && a->N == 64);
   ORBIT_REQUIRE(smem <= 220 * 1024, ERR_UNSUPPORTED, "orbit_hm_scan_bwd: P=%d, N=%d need %zu bytes of shared memory (limit 220 KiB)",
                 a->P, a->N, smem);
   cudaStream_t st = (cudaStream_t)stream;
