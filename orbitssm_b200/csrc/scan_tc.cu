@@ -27,7 +27,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 constexpr int TC_T = 128, TC_N = 128, TC_G = 64;
-constexpr int ISSUER = 128;      // thread that issues the per-head MMAs and TMA refills in the output / score-gradient kernels
 
 // ------------------------------------------------------------------------------------------------------------------
 // chunk_state (mode 0):  Z[n,p] = sum_s B[s,n] e_s u[s,p],   e_s = exp(cs_T - cs_s) w_s          -> a.Sin, a.atot
@@ -743,7 +742,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) tc_chunk_grads_state_kernel(con
     }
 #pragma unroll 1
     for (int h = 0; h < Hl; ++h) {
-      const int sx = h % GT_XSTAGES, ss = h % GT_SSTAGES, k = h & 1;
+      const int sx = h % GT_XSTAGES, k = h & 1;
       const float wt = w_n;
       float x = d_n;
 #pragma unroll
